@@ -1,0 +1,221 @@
+/*
+ * tachyon_b200 -- C ABI of the B200 (sm_100a) decode / prefill hot path.
+ *
+ * Every entry point returns an int status (TB_OK == 0) and never aborts; tb_last_error() gives the calling thread's
+ * last failure as text.  Pointers named `dev_*` or documented as device memory must come from tb_alloc (or any CUDA
+ * allocation of the same device); everything else is host memory.  One host thread owns a context; nothing here is
+ * thread-safe across contexts sharing a GPU stream, as in the reference (crates/tachyon/src/cuda/mod.rs:3-6).
+ *
+ * Each declaration cites the reference interface it stands in for (paths relative to the reference repository).
+ */
+#ifndef TACHYON_B200_H
+#define TACHYON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TB_API __attribute__((visibility("default")))
+#else
+#define TB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; mirror crates/tachyon/src/error.rs:8-50. */
+enum {
+    TB_OK = 0,
+    TB_NO_DRIVER = 1,       /* Error::NoDriver */
+    TB_UNSUPPORTED_GPU = 2, /* Error::UnsupportedGpu: not compute capability 10.x */
+    TB_OUT_OF_RANGE = 3,    /* Error::OutOfRange: a launch descriptor failed validation, nothing was launched */
+    TB_CUDA = 4,            /* Error::Cuda(code) */
+    TB_FORMAT = 5,          /* Error::Format */
+    TB_TOO_LONG = 6,        /* Error::TooLong: the sequence would pass the context */
+    TB_OUT_OF_MEMORY = 7,   /* Error::OutOfMemory */
+    TB_NO_MODEL = 8,        /* Error::NoModel: a tensor is missing */
+    TB_UNSUPPORTED = 9,     /* Error::Unsupported: a shape this build has no kernel for */
+    TB_DEVICE_WAIT = 10     /* a kernel gave up a bounded wait; see tb_status */
+};
+
+typedef struct tb_context tb_context;
+typedef struct tb_decoder tb_decoder;
+typedef struct tb_event tb_event;
+
+/* The calling thread's last error message ("" when none). */
+TB_API const char* tb_last_error(void);
+
+/* ---- context, memory, stream: crates/tachyon/src/cuda/mod.rs:157-458 (Context, DevBuf, HostBuf, Stream, Event) ---- */
+
+/* Context::new (cuda/mod.rs:177-187): binds GPU `gpu`, requires compute capability 10.x, creates the stream. */
+TB_API int tb_context_new(int gpu, tb_context** out);
+TB_API void tb_context_free(tb_context* ctx);
+/* Context::info().sms */
+TB_API int tb_context_sms(const tb_context* ctx);
+/* Turns programmatic dependent launch on (default) or off for kernels launched after the call. */
+TB_API int tb_context_set_overlap(tb_context* ctx, int on);
+/* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
+TB_API int tb_status(tb_context* ctx, uint32_t* word);
+
+/* Context::alloc / DevBuf drop (cuda/mod.rs:292-298, 337-375). */
+TB_API int tb_alloc(tb_context* ctx, size_t bytes, void** dev);
+TB_API int tb_free(tb_context* ctx, void* dev);
+/* Context::alloc_host: pinned, device-mapped host memory. */
+TB_API int tb_alloc_host(tb_context* ctx, size_t bytes, void** host);
+TB_API int tb_free_host(tb_context* ctx, void* host);
+/* Stream::upload / download / fill / sync (cuda/mod.rs:382-411).  Copies are queued on the context's stream; the
+ * caller keeps host memory alive until tb_sync. */
+TB_API int tb_upload(tb_context* ctx, void* dev, const void* host, size_t bytes);
+TB_API int tb_download(tb_context* ctx, void* host, const void* dev, size_t bytes);
+TB_API int tb_fill(tb_context* ctx, void* dev, int byte, size_t bytes);
+TB_API int tb_sync(tb_context* ctx);
+/* Event (cuda/mod.rs:427-458). */
+TB_API int tb_event_new(tb_context* ctx, tb_event** out);
+TB_API void tb_event_free(tb_event* ev);
+TB_API int tb_event_record(tb_context* ctx, tb_event* ev);
+TB_API int tb_event_sync(tb_event* ev);
+TB_API int tb_event_elapsed_ms(tb_event* start, tb_event* end, float* ms);
+
+/* ---- kernels, one call per launch: the (name, grid, block, args) seam of Stream::launch (cuda/mod.rs:417-425) ---- */
+
+enum { TB_F32 = 0, TB_F16 = 1 };
+
+/*
+ * y = W x.  W: device int8 [rows, cols] row-major; scales: device f16 [rows, cols/32]; x: device [cols] of x_dtype;
+ * y: device [rows] of y_dtype; f32 accumulation.  Stands in for gemv_q4 / gemv_q4_narrow
+ * (crates/tachyon/src/ptx/gemv.rs:1-27, 156-195) with this build's Q8 weights and unquantised activations.
+ * cols must be a multiple of 32; 2048, 4096, 8192 and 16384 take the staged kernel.
+ */
+TB_API int tb_gemv_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols);
+
+/*
+ * The residual / RMS-norm step fused in front of the product: h' = (h + w1 * rmsnorm(y_res)) * hscale (y_res NULL:
+ * h' = h), x = w2 * rmsnorm(h') (w2 NULL: x = h'), y = W x; h_out (may be NULL) receives h'.  cols must be 2048.
+ * Stands in for norm_q8 followed by gemv_q4 (ptx/mod.rs:24-30, 404-511).  `geglu` != 0: rows are (gate_j, up_j) pairs
+ * and y (f32 [rows/2]) receives gelu_tanh(gate_j) * up_j -- geglu_q8 (ptx/mod.rs:376-393).
+ */
+TB_API int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, const float* h, const float* y_res, const float* w1, const float* w2,
+                    float eps, float hscale, float* h_out, float* y, uint32_t rows, uint32_t cols, int geglu);
+
+/*
+ * LM head and greedy pick in one launch: logits = W x (written to `logits` when not NULL), token = argmax with the lowest
+ * index among equals; writes state[1] = token, state[0] += 1 and *token_out (device-visible, may be NULL).
+ * scratch: 16 bytes of device memory, zero before the first launch, left zero.  Stands in for gemv_q4 over the tied
+ * embedding followed by sample in greedy mode (ptx/sample.rs:21-27, 91-97).
+ */
+TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, float* logits, uint32_t rows, uint32_t cols,
+                      void* scratch, uint32_t* state, uint32_t* token_out);
+
+/* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
+TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
+            float* x_out);
+
+/* Row *token of a Q8 table times `scale` as f32 [cols]: embed_q4 (ptx/mod.rs:531-598). token: device word. */
+TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint32_t* token, uint32_t cols, float scale, float* out);
+
+/*
+ * Decode attention for one new token; argument meaning follows attend_256 (crates/tachyon/src/ptx/attend.rs:21-32).
+ * head size 256; heads / kv_heads in {1, 2, 4}.
+ */
+typedef struct tb_attend {
+    const float* qkv;      /* device f32 [(heads + 2*kv_heads) * 256]: queries, new keys, new values */
+    const float* q_norm;   /* device f32 [256] or NULL: NULL (with k_norm NULL) = plain mode, no norms */
+    const float* k_norm;
+    const float* freq;     /* device f32 [128] RoPE frequencies, or NULL for no rotation */
+    uint16_t* k_cache;     /* device f16 [kv_heads][cap][256] */
+    uint16_t* v_cache;
+    const uint32_t* pos;   /* device word: position of the new token */
+    uint32_t cap;          /* slots per kv head; the new token goes to slot pos % cap */
+    uint32_t window;       /* attends the newest min(pos + 1, window) positions; window <= cap */
+    uint32_t fresh;        /* != 0: normalise/rotate the new key and value, store them, use them unrounded */
+    uint32_t heads, kv_heads;
+    float scale;           /* softmax scale (1 in Gemma 4, 1/sqrt(256) in the plain configuration) */
+    float eps;
+    float* partial;        /* device scratch, tb_attend_scratch_bytes(...) bytes; NULL allowed when splits == 1 */
+    uint32_t* count;       /* device, kv_heads words, zero before the first launch, left zero */
+    uint32_t splits;       /* blocks per kv head */
+    void* out;             /* device [heads * 256], f32 or f16 */
+    int out_dtype;
+} tb_attend;
+TB_API size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits);
+TB_API int tb_attend_decode(tb_context* ctx, const tb_attend* args);
+
+/*
+ * Greedy sampler over f32 logits with the reference's transform (soft cap, allowed mask, repetition penalty):
+ * sample in greedy mode (ptx/sample.rs:21-27; Sampling, :38-78).  seen / allowed: device bitmaps or NULL.
+ * scratch as in tb_gemv_q8_argmax.  Sets the token's bit in `seen` when given.
+ */
+TB_API int tb_sample_greedy(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, uint32_t* seen, const uint32_t* allowed,
+                     void* scratch, uint32_t* state, uint32_t* token_out);
+/* The k largest logits, largest first, lowest index first among equals. idx, val: device [k]. */
+TB_API int tb_topk(tb_context* ctx, const float* logits, uint32_t vocab, uint32_t k, uint32_t* idx, float* val);
+
+/* Seeded synthetic tensors (this build's generators; the reference's benches are synthetic too, benches/gemv.rs:8-9). */
+TB_API int tb_fill_codes(tb_context* ctx, uint64_t seed, uint64_t stream_id, int8_t* dev, size_t n);
+TB_API int tb_fill_scales(tb_context* ctx, uint64_t seed, uint64_t stream_id, uint16_t* dev, size_t n, float mul);
+TB_API int tb_fill_gauss_f16(tb_context* ctx, uint64_t seed, uint64_t stream_id, uint16_t* dev, size_t n, float mul);
+TB_API int tb_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, float* dev, size_t n, float lo, float hi);
+
+/* ---- decoder: crates/tachyon/src/model/decode.rs (Decoder, Settings) and model/mod.rs:27-61 (Config) ---- */
+
+typedef struct tb_config {
+    uint32_t hidden, ffn, heads, kv_heads, head_dim, vocab, layers, window;
+    const uint8_t* global;  /* [layers], != 0 where a layer attends globally (Config::global); NULL: use global_every */
+    uint32_t global_every;  /* with global == NULL: layer i is global iff (i + 1) % global_every == 0; 0 = none */
+    float theta_sliding, theta_global, fraction_global; /* Config::theta, Config::fraction */
+    float eps, softcap;
+    float attn_scale;       /* softmax scale; Gemma 4 uses 1 */
+} tb_config;
+
+/* model::Settings (decode.rs:64-76) plus what this build adds. */
+typedef struct tb_settings {
+    uint32_t context;      /* positions a global layer keeps */
+    uint32_t chunk;        /* extra ring slots of sliding layers (the reference's prefill chunk) */
+    uint32_t keep_logits;  /* != 0: every step also stores the f32 logits for tb_decoder_logits */
+} tb_settings;
+
+/* Decoder::open without the file loader: allocates weights, caches and step buffers for `cfg`. */
+TB_API int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, tb_decoder** out);
+TB_API void tb_decoder_close(tb_decoder* dec);
+/*
+ * Uploads one tensor by its converted-model name (model/mod.rs:178-286): matrices as `<name>.w` (int8 codes) and
+ * `<name>.s` (f16 scales, one per 32 along a row) for embed, {i}.qkv, {i}.o, {i}.gate_up (gate rows, then up rows),
+ * {i}.down; f32 vectors {i}.q_norm, {i}.k_norm, {i}.input_layernorm, {i}.post_attention_layernorm,
+ * {i}.pre_feedforward_layernorm, {i}.post_feedforward_layernorm, {i}.layer_scalar, norm.
+ */
+TB_API int tb_decoder_load(tb_decoder* dec, const char* name, const void* data, size_t bytes);
+/* Fills every tensor from the seeded generators (stream ids documented in decoder.cu). */
+TB_API int tb_decoder_fill_random(tb_decoder* dec, uint64_t seed);
+/* Fills the first `positions` positions of every cache with seeded N(0,1) values and sets the position. */
+TB_API int tb_decoder_fill_cache(tb_decoder* dec, uint64_t seed, uint32_t positions);
+/* Records the step's graphs (Decoder::build, decode.rs:250-272); call after loading, before stepping. */
+TB_API int tb_decoder_build(tb_decoder* dec);
+/* Decoder::reset (decode.rs:297-301): position 0. */
+TB_API int tb_decoder_reset(tb_decoder* dec);
+/* Decoder::step (decode.rs:305-310): host token in, sampled token out, one graph launch, waits for it. */
+TB_API int tb_decoder_step(tb_decoder* dec, uint32_t token, uint32_t* next);
+/* Decoder::start / next_token / stop (decode.rs:313-345): keeps one step queued behind the running one. */
+TB_API int tb_decoder_start(tb_decoder* dec, uint32_t token);
+TB_API int tb_decoder_next_token(tb_decoder* dec, uint32_t* token);
+TB_API int tb_decoder_stop(tb_decoder* dec);
+/* Queues `steps` chained steps (each feeds the token the one before sampled) without touching the host between
+ * them, starting from `token`; for throughput measurement.  tokens_out (host, may be NULL) receives them after a sync. */
+TB_API int tb_decoder_run(tb_decoder* dec, uint32_t token, uint32_t steps, uint32_t* tokens_out);
+/* Decoder::prefill (decode.rs:346-364): feeds `n` prompt tokens, no sampling result kept. */
+TB_API int tb_decoder_prefill(tb_decoder* dec, const uint32_t* tokens, uint32_t n);
+/* Decoder::logits (decode.rs:439-445): the last step's logits, needs settings.keep_logits. */
+TB_API int tb_decoder_logits(tb_decoder* dec, float* host_out);
+/* Current position. */
+TB_API int tb_decoder_position(tb_decoder* dec, uint32_t* pos);
+/* Bytes of weights and of key/value cache one step reads at the current position (the roofline's numerator). */
+TB_API int tb_decoder_step_bytes(tb_decoder* dec, uint64_t* weight_bytes, uint64_t* cache_bytes);
+/* Kernels one step launches. */
+TB_API int tb_decoder_step_launches(tb_decoder* dec, uint32_t* launches);
+/* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */
+TB_API int tb_decoder_hidden(tb_decoder* dec, float* host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,213 @@
+"""ctypes binding of the CPU oracle (``oracle/tachyon_oracle.c``).
+
+Test infrastructure only: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline legs of
+``bench.py``.  The shipped package never imports it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compiles the oracle with gcc when the library is missing or older than its source."""
+    src = os.path.join(_HERE, "tachyon_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-s", "-B"], check=True)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _declare(_lib)
+    return _lib
+
+
+class Config(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "ffn", "heads", "kv_heads", "head_dim", "vocab", "layers", "window", "context")] + [
+        (n, C.c_float) for n in ("theta_sliding", "theta_global", "fraction_global", "eps", "softcap", "attn_scale", "embed_scale")
+    ]
+
+
+class Layer(C.Structure):
+    _fields_ = (
+        [(n, C.c_void_p) for n in ("qkv", "o", "gate_up", "down", "qkv_s", "o_s", "gate_up_s", "down_s")]
+        + [(n, C.c_void_p) for n in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")]
+        + [("layer_scalar", C.c_float), ("global_", C.c_int32), ("kc", C.c_void_p), ("vc", C.c_void_p), ("cap", C.c_int32)]
+    )
+
+
+class Model(C.Structure):
+    _fields_ = [("cfg", Config), ("embed", C.c_void_p), ("embed_s", C.c_void_p), ("norm", C.c_void_p), ("layers", C.POINTER(Layer))]
+
+
+def _declare(l: C.CDLL) -> None:
+    vp, sz, u32, u64, i32, f32, f64 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_double
+    sig = {
+        "tbo_f16_bits": (C.c_uint16, [f32]),
+        "tbo_f16_value": (f32, [C.c_uint16]),
+        "tbo_q4": (None, [vp, sz, vp, vp]),
+        "tbo_q8_blocks": (None, [vp, sz, i32, vp, vp]),
+        "tbo_q8p_pairs": (None, [vp, sz]),
+        "tbo_product_q4": (None, [vp, vp, vp, sz, sz, vp, vp]),
+        "tbo_gemv_q8": (None, [vp, vp, vp, sz, sz, vp, vp, vp]),
+        "tbo_normalize": (None, [vp, sz, vp, f64]),
+        "tbo_rotate": (None, [vp, sz, vp, u32]),
+        "tbo_rope_freq": (None, [f32, i32, f32, vp]),
+        "tbo_gelu_tanh": (f64, [f64]),
+        "tbo_norm_step": (None, [vp, vp, vp, vp, sz, f64, f64, vp, vp]),
+        "tbo_attend_decode": (None, [vp, vp, vp, vp, vp, vp, u32, u32, u32, i32, i32, i32, i32, f64, f64, vp]),
+        "tbo_sample_transform": (f64, [f32, sz, f32, f32, f32, vp, vp]),
+        "tbo_sample_greedy": (u32, [vp, sz, f32, f32, vp, vp, vp]),
+        "tbo_sample_topk": (None, [vp, sz, i32, vp, vp]),
+        "tbo_fill_codes": (None, [u64, u64, vp, sz]),
+        "tbo_fill_scales": (None, [u64, u64, vp, sz, f32]),
+        "tbo_fill_uniform": (None, [u64, u64, vp, sz, f32, f32]),
+        "tbo_fill_gauss_f16": (None, [u64, u64, vp, sz, f32]),
+        "tbo_fill_gauss_f32": (None, [u64, u64, vp, sz, f32]),
+        "tbo_decoder_step": (C.c_int32, [C.POINTER(Model), u32, u32, vp, i32, vp]),
+        "tbo_threads": (i32, []),
+        "tbo_set_threads": (None, [i32]),
+    }
+    for name, (res, args) in sig.items():
+        f = getattr(l, name)
+        f.restype, f.argtypes = res, args
+
+
+def ptr(a):
+    """Address of a C-contiguous numpy array, or None."""
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# numpy-facing helpers
+# ---------------------------------------------------------------------------------------------------------------
+
+def f16_bits(v: float) -> int:
+    return int(lib().tbo_f16_bits(float(np.float32(v))))
+
+
+def f16_value(h: int) -> float:
+    return float(lib().tbo_f16_value(int(h)))
+
+
+def q4(w: np.ndarray):
+    w = np.ascontiguousarray(w, dtype=np.float32).ravel()
+    packed, scales = np.zeros(w.size // 2, np.uint8), np.zeros(w.size // 64, np.uint16)
+    lib().tbo_q4(ptr(w), w.size, ptr(packed), ptr(scales))
+    return packed, scales
+
+
+def q8(x: np.ndarray, block: int = 32):
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    q, pairs = np.zeros(x.size, np.int8), np.zeros((x.size // block, 2), np.float32)
+    lib().tbo_q8_blocks(ptr(x), x.size, block, ptr(q), ptr(pairs))
+    return q, pairs
+
+
+def q8p(x: np.ndarray):
+    q, pairs = q8(x, 64)
+    lib().tbo_q8p_pairs(ptr(pairs), pairs.shape[0])
+    return q, pairs
+
+
+def product_q4(packed, scales, x, rows):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    s, b = np.zeros(rows, np.float64), np.zeros(rows, np.float64)
+    lib().tbo_product_q4(ptr(packed), ptr(scales), ptr(x), rows, x.size, ptr(s), ptr(b))
+    return s, b
+
+
+def gemv_q8(w: np.ndarray, scales: np.ndarray, x: np.ndarray):
+    """(f32-accumulated y, f64 y, bound) for int8 ``w`` [rows, cols], f16-bit ``scales`` [rows, cols/32], f32 ``x``."""
+    rows, cols = w.shape
+    w, scales = np.ascontiguousarray(w, np.int8), np.ascontiguousarray(scales, np.uint16)
+    x = np.ascontiguousarray(x, np.float32)
+    y, e, b = np.zeros(rows, np.float32), np.zeros(rows, np.float64), np.zeros(rows, np.float64)
+    lib().tbo_gemv_q8(ptr(w), ptr(scales), ptr(x), rows, cols, ptr(y), ptr(e), ptr(b))
+    return y, e, b
+
+
+def rope_freq(theta: float, d: int, fraction: float) -> np.ndarray:
+    f = np.zeros(d // 2, np.float32)
+    lib().tbo_rope_freq(theta, d, fraction, ptr(f))
+    return f
+
+
+def norm_step(h, y, w1, w2, eps, scale):
+    h = np.ascontiguousarray(h, np.float32)
+    ho, xo = np.zeros(h.size, np.float64), np.zeros(h.size, np.float64)
+    cv = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
+    y, w1, w2 = cv(y), cv(w1), cv(w2)
+    lib().tbo_norm_step(ptr(h), ptr(y), ptr(w1), ptr(w2), h.size, eps, scale, ptr(ho), ptr(xo))
+    return ho, xo
+
+
+def attend_decode(qkv, qn, kn, freq, kc, vc, pos, cap, window, fresh, heads, kv_heads, d, scale, eps=1e-6):
+    """Returns f64 out [heads*d]; ``kc``/``vc`` (uint16 f16 bits, [kv_heads, cap, d]) are updated in place when fresh."""
+    qkv = np.ascontiguousarray(qkv, np.float32)
+    out = np.zeros(heads * d, np.float64)
+    cv = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
+    qn, kn, freq = cv(qn), cv(kn), cv(freq)
+    assert kc.dtype == np.uint16 and vc.dtype == np.uint16
+    lib().tbo_attend_decode(ptr(qkv), ptr(qn), ptr(kn), ptr(freq), ptr(kc), ptr(vc), pos, cap, window, int(fresh), heads, kv_heads, d,
+                            scale, eps, ptr(out))
+    return out
+
+
+def sample_greedy(logits, softcap=0.0, penalty=1.0, seen=None, allowed=None):
+    logits = np.ascontiguousarray(logits, np.float32)
+    gap = C.c_double(0)
+    t = lib().tbo_sample_greedy(ptr(logits), logits.size, softcap, penalty, ptr(seen), ptr(allowed), C.byref(gap))
+    return int(t), gap.value
+
+
+def sample_topk(logits, k):
+    logits = np.ascontiguousarray(logits, np.float32)
+    idx, val = np.zeros(k, np.uint32), np.zeros(k, np.float32)
+    lib().tbo_sample_topk(ptr(logits), logits.size, k, ptr(idx), ptr(val))
+    return idx, val
+
+
+def fill_codes(seed, stream, n):
+    w = np.zeros(n, np.int8)
+    lib().tbo_fill_codes(seed, stream, ptr(w), n)
+    return w
+
+
+def fill_scales(seed, stream, n, mul):
+    s = np.zeros(n, np.uint16)
+    lib().tbo_fill_scales(seed, stream, ptr(s), n, mul)
+    return s
+
+
+def fill_uniform(seed, stream, n, lo, hi):
+    x = np.zeros(n, np.float32)
+    lib().tbo_fill_uniform(seed, stream, ptr(x), n, lo, hi)
+    return x
+
+
+def fill_gauss_f16(seed, stream, n, mul=1.0):
+    x = np.zeros(n, np.uint16)
+    lib().tbo_fill_gauss_f16(seed, stream, ptr(x), n, mul)
+    return x
+
+
+def fill_gauss_f32(seed, stream, n, mul=1.0):
+    x = np.zeros(n, np.float32)
+    lib().tbo_fill_gauss_f32(seed, stream, ptr(x), n, mul)
+    return x

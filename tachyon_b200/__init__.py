@@ -1,0 +1,267 @@
+"""tachyon_b200: the B200 (sm_100a) decode hot path of the tachyon engine behind a C ABI.
+
+This package is a thin host-side mirror of the reference's Rust API names (``Context``, ``DevBuf``, ``Decoder``,
+``Config``, ``Settings``; crates/tachyon/src/cuda/mod.rs, crates/tachyon/src/model/decode.rs) over
+``libtachyon_b200.so``.  All computation happens in the library's CUDA kernels; nothing here computes on the CPU and
+nothing falls back when the library or a GPU is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import Attend, Config, Settings
+
+F32, F16 = 0, 1
+
+
+class Error(RuntimeError):
+    """A non-zero status from the library; ``status`` is the TB_* code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"tachyon_b200 status {status}: {message}")
+        self.status = status
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise Error(status, _lib.load().tb_last_error().decode())
+
+
+class DevBuf:
+    """Device memory owned by a context (cuda/mod.rs DevBuf): freed on ``free`` or with the object."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx, self.nbytes = ctx, nbytes
+        p = C.c_void_p()
+        check(ctx.lib.tb_alloc(ctx.handle, nbytes, C.byref(p)))
+        self.ptr = p.value
+
+    def free(self) -> None:
+        if self.ptr is not None and self.ctx.handle:
+            self.ctx.lib.tb_free(self.ctx.handle, self.ptr)
+        self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def upload(self, a: np.ndarray) -> "DevBuf":
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        check(self.ctx.lib.tb_upload(self.ctx.handle, self.ptr, a.ctypes.data, a.nbytes))
+        self.ctx.sync()
+        return self
+
+    def download(self, dtype, count: int | None = None) -> np.ndarray:
+        dtype = np.dtype(dtype)
+        n = self.nbytes // dtype.itemsize if count is None else count
+        out = np.empty(n, dtype)
+        check(self.ctx.lib.tb_download(self.ctx.handle, out.ctypes.data, self.ptr, out.nbytes))
+        self.ctx.sync()
+        return out
+
+    def zero(self) -> "DevBuf":
+        check(self.ctx.lib.tb_fill(self.ctx.handle, self.ptr, 0, self.nbytes))
+        return self
+
+
+class Context:
+    """One GPU and its stream (cuda/mod.rs Context + Stream)."""
+
+    def __init__(self, gpu: int = 0):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        check(self.lib.tb_context_new(gpu, C.byref(h)))
+        self.handle = h.value
+        self.gpu = gpu
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_context_free(self.handle)
+            self.handle = None
+
+    @property
+    def sms(self) -> int:
+        return self.lib.tb_context_sms(self.handle)
+
+    def set_overlap(self, on: bool) -> None:
+        check(self.lib.tb_context_set_overlap(self.handle, int(on)))
+
+    def sync(self) -> None:
+        check(self.lib.tb_sync(self.handle))
+
+    def status(self) -> int:
+        w = C.c_uint32(0)
+        check(self.lib.tb_status(self.handle, C.byref(w)))
+        return w.value
+
+    def alloc(self, nbytes: int) -> DevBuf:
+        return DevBuf(self, nbytes)
+
+    def upload(self, a: np.ndarray) -> DevBuf:
+        a = np.ascontiguousarray(a)
+        return DevBuf(self, max(a.nbytes, 16)).upload(a)
+
+    def zeros(self, nbytes: int) -> DevBuf:
+        b = DevBuf(self, nbytes).zero()
+        self.sync()
+        return b
+
+    # ---- events ----
+    def event(self) -> "Event":
+        return Event(self)
+
+    # ---- kernels (one launch each) ----
+    def gemv_q8(self, w: DevBuf, s: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, y_dtype: int, rows: int, cols: int) -> None:
+        check(self.lib.tb_gemv_q8(self.handle, w.ptr, s.ptr, x.ptr, x_dtype, y.ptr, y_dtype, rows, cols))
+
+    def gemv_q8_norm(self, w, s, h, y_res, w1, w2, eps, hscale, h_out, y, rows, cols, geglu=False) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_gemv_q8_norm(self.handle, w.ptr, s.ptr, h.ptr, p(y_res), p(w1), p(w2), eps, hscale, p(h_out), y.ptr, rows, cols, int(geglu)))
+
+    def gemv_q8_argmax(self, w, s, x, x_dtype, logits, rows, cols, scratch, state, token_out=None) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_gemv_q8_argmax(self.handle, w.ptr, s.ptr, x.ptr, x_dtype, p(logits), rows, cols, scratch.ptr, state.ptr, p(token_out)))
+
+    def norm(self, h, y_res, w1, w2, n, eps, hscale, h_out, x_out) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_norm(self.handle, h.ptr, p(y_res), p(w1), p(w2), n, eps, hscale, p(h_out), p(x_out)))
+
+    def embed_q8(self, w, s, token, cols, scale, out) -> None:
+        check(self.lib.tb_embed_q8(self.handle, w.ptr, s.ptr, token.ptr, cols, scale, out.ptr))
+
+    def attend_decode(self, args: Attend) -> None:
+        check(self.lib.tb_attend_decode(self.handle, C.byref(args)))
+
+    def attend_scratch_bytes(self, heads: int, kv_heads: int, splits: int) -> int:
+        return self.lib.tb_attend_scratch_bytes(heads, kv_heads, splits)
+
+    def sample_greedy(self, logits, vocab, softcap, penalty, seen, allowed, scratch, state, token_out=None) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_sample_greedy(self.handle, logits.ptr, vocab, softcap, penalty, p(seen), p(allowed), scratch.ptr, state.ptr, p(token_out)))
+
+    def topk(self, logits, vocab, k, idx, val) -> None:
+        check(self.lib.tb_topk(self.handle, logits.ptr, vocab, k, idx.ptr, val.ptr))
+
+
+class Event:
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        h = C.c_void_p()
+        check(ctx.lib.tb_event_new(ctx.handle, C.byref(h)))
+        self.handle = h.value
+
+    def record(self) -> "Event":
+        check(self.ctx.lib.tb_event_record(self.ctx.handle, self.handle))
+        return self
+
+    def sync(self) -> None:
+        check(self.ctx.lib.tb_event_sync(self.handle))
+
+    def elapsed_ms(self, end: "Event") -> float:
+        ms = C.c_float(0)
+        check(self.ctx.lib.tb_event_elapsed_ms(self.handle, end.handle, C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.ctx.lib.tb_event_free(self.handle)
+        except Exception:
+            pass
+
+
+def gemma4_e4b_shape(layers: int = 35, ffn: int = 16384, vocab: int = 262144) -> Config:
+    """The benchmark's Gemma-4-E4B-shaped configuration: 35 layers, width 2048, 8 query / 2 key-value heads of 256,
+    GeGLU 16384, four sliding-window (512) layers to one global, tied vocabulary of 262144."""
+    return Config(hidden=2048, ffn=ffn, heads=8, kv_heads=2, head_dim=256, vocab=vocab, layers=layers, window=512, global_=None, global_every=5,
+                  theta_sliding=1e4, theta_global=1e6, fraction_global=0.25, eps=1e-6, softcap=30.0, attn_scale=1.0)
+
+
+class Decoder:
+    """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
+
+    def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False):
+        self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
+        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits))
+        h = C.c_void_p()
+        check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
+        self.handle = h.value
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_decoder_close(self.handle)
+            self.handle = None
+
+    def load(self, name: str, a: np.ndarray) -> None:
+        a = np.ascontiguousarray(a)
+        check(self.lib.tb_decoder_load(self.handle, name.encode(), a.ctypes.data, a.nbytes))
+
+    def fill_random(self, seed: int) -> None:
+        check(self.lib.tb_decoder_fill_random(self.handle, seed))
+
+    def fill_cache(self, seed: int, positions: int) -> None:
+        check(self.lib.tb_decoder_fill_cache(self.handle, seed, positions))
+
+    def build(self) -> None:
+        check(self.lib.tb_decoder_build(self.handle))
+
+    def reset(self) -> None:
+        check(self.lib.tb_decoder_reset(self.handle))
+
+    def step(self, token: int) -> int:
+        out = C.c_uint32(0)
+        check(self.lib.tb_decoder_step(self.handle, token, C.byref(out)))
+        return out.value
+
+    def start(self, token: int) -> None:
+        check(self.lib.tb_decoder_start(self.handle, token))
+
+    def next_token(self) -> int:
+        out = C.c_uint32(0)
+        check(self.lib.tb_decoder_next_token(self.handle, C.byref(out)))
+        return out.value
+
+    def stop(self) -> None:
+        check(self.lib.tb_decoder_stop(self.handle))
+
+    def run(self, token: int, steps: int, want_tokens: bool = True):
+        out = np.zeros(steps, np.uint32) if want_tokens else None
+        check(self.lib.tb_decoder_run(self.handle, token, steps, None if out is None else out.ctypes.data))
+        return out
+
+    def prefill(self, tokens) -> None:
+        t = np.ascontiguousarray(tokens, np.uint32)
+        check(self.lib.tb_decoder_prefill(self.handle, t.ctypes.data, t.size))
+
+    def logits(self) -> np.ndarray:
+        out = np.empty(self.cfg.vocab, np.float32)
+        check(self.lib.tb_decoder_logits(self.handle, out.ctypes.data))
+        return out
+
+    def hidden(self) -> np.ndarray:
+        out = np.empty(self.cfg.hidden, np.float32)
+        check(self.lib.tb_decoder_hidden(self.handle, out.ctypes.data))
+        return out
+
+    @property
+    def position(self) -> int:
+        p = C.c_uint32(0)
+        check(self.lib.tb_decoder_position(self.handle, C.byref(p)))
+        return p.value
+
+    def step_bytes(self) -> tuple[int, int]:
+        w, kv = C.c_uint64(0), C.c_uint64(0)
+        check(self.lib.tb_decoder_step_bytes(self.handle, C.byref(w), C.byref(kv)))
+        return w.value, kv.value
+
+    @property
+    def step_launches(self) -> int:
+        n = C.c_uint32(0)
+        check(self.lib.tb_decoder_step_launches(self.handle, C.byref(n)))
+        return n.value

@@ -1,0 +1,105 @@
+"""ctypes declarations of ``libtachyon_b200.so`` (see ``include/tachyon_b200.h``).
+
+There is no fallback: if the library has not been built (``python -m tachyon_b200.build``) loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PATH = os.path.join(HERE, "_native", "libtachyon_b200.so")
+
+u32, u64, i32, f32, vp, sz, cp = C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_char_p
+pp = C.POINTER(C.c_void_p)
+
+
+class Attend(C.Structure):
+    _fields_ = [
+        ("qkv", vp), ("q_norm", vp), ("k_norm", vp), ("freq", vp), ("k_cache", vp), ("v_cache", vp), ("pos", vp),
+        ("cap", u32), ("window", u32), ("fresh", u32), ("heads", u32), ("kv_heads", u32),
+        ("scale", f32), ("eps", f32), ("partial", vp), ("count", vp), ("splits", u32), ("out", vp), ("out_dtype", i32),
+    ]
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("hidden", u32), ("ffn", u32), ("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("vocab", u32), ("layers", u32), ("window", u32),
+        ("global_", vp), ("global_every", u32),
+        ("theta_sliding", f32), ("theta_global", f32), ("fraction_global", f32), ("eps", f32), ("softcap", f32), ("attn_scale", f32),
+    ]
+
+
+class Settings(C.Structure):
+    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32)]
+
+
+# name -> (restype, argtypes); every symbol the header declares.
+SIGNATURES = {
+    "tb_last_error": (cp, []),
+    "tb_context_new": (i32, [i32, pp]),
+    "tb_context_free": (None, [vp]),
+    "tb_context_sms": (i32, [vp]),
+    "tb_context_set_overlap": (i32, [vp, i32]),
+    "tb_status": (i32, [vp, C.POINTER(u32)]),
+    "tb_alloc": (i32, [vp, sz, pp]),
+    "tb_free": (i32, [vp, vp]),
+    "tb_alloc_host": (i32, [vp, sz, pp]),
+    "tb_free_host": (i32, [vp, vp]),
+    "tb_upload": (i32, [vp, vp, vp, sz]),
+    "tb_download": (i32, [vp, vp, vp, sz]),
+    "tb_fill": (i32, [vp, vp, i32, sz]),
+    "tb_sync": (i32, [vp]),
+    "tb_event_new": (i32, [vp, pp]),
+    "tb_event_free": (None, [vp]),
+    "tb_event_record": (i32, [vp, vp]),
+    "tb_event_sync": (i32, [vp]),
+    "tb_event_elapsed_ms": (i32, [vp, vp, C.POINTER(f32)]),
+    "tb_gemv_q8": (i32, [vp, vp, vp, vp, i32, vp, i32, u32, u32]),
+    "tb_gemv_q8_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, f32, f32, vp, vp, u32, u32, i32]),
+    "tb_gemv_q8_argmax": (i32, [vp, vp, vp, vp, i32, vp, u32, u32, vp, vp, vp]),
+    "tb_norm": (i32, [vp, vp, vp, vp, vp, u32, f32, f32, vp, vp]),
+    "tb_embed_q8": (i32, [vp, vp, vp, vp, u32, f32, vp]),
+    "tb_attend_scratch_bytes": (sz, [u32, u32, u32]),
+    "tb_attend_decode": (i32, [vp, C.POINTER(Attend)]),
+    "tb_sample_greedy": (i32, [vp, vp, u32, f32, f32, vp, vp, vp, vp, vp]),
+    "tb_topk": (i32, [vp, vp, u32, u32, vp, vp]),
+    "tb_fill_codes": (i32, [vp, u64, u64, vp, sz]),
+    "tb_fill_scales": (i32, [vp, u64, u64, vp, sz, f32]),
+    "tb_fill_gauss_f16": (i32, [vp, u64, u64, vp, sz, f32]),
+    "tb_fill_uniform": (i32, [vp, u64, u64, vp, sz, f32, f32]),
+    "tb_decoder_open": (i32, [vp, C.POINTER(Config), C.POINTER(Settings), pp]),
+    "tb_decoder_close": (None, [vp]),
+    "tb_decoder_load": (i32, [vp, cp, vp, sz]),
+    "tb_decoder_fill_random": (i32, [vp, u64]),
+    "tb_decoder_fill_cache": (i32, [vp, u64, u32]),
+    "tb_decoder_build": (i32, [vp]),
+    "tb_decoder_reset": (i32, [vp]),
+    "tb_decoder_step": (i32, [vp, u32, C.POINTER(u32)]),
+    "tb_decoder_start": (i32, [vp, u32]),
+    "tb_decoder_next_token": (i32, [vp, C.POINTER(u32)]),
+    "tb_decoder_stop": (i32, [vp]),
+    "tb_decoder_run": (i32, [vp, u32, u32, vp]),
+    "tb_decoder_prefill": (i32, [vp, vp, u32]),
+    "tb_decoder_logits": (i32, [vp, vp]),
+    "tb_decoder_position": (i32, [vp, C.POINTER(u32)]),
+    "tb_decoder_step_bytes": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
+    "tb_decoder_step_launches": (i32, [vp, C.POINTER(u32)]),
+    "tb_decoder_hidden": (i32, [vp, vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """The library, loaded once.  Raises when it is missing: there is no other code path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(PATH):
+            raise ImportError(f"{PATH} is not built; run `python -m tachyon_b200.build` (needs nvcc). There is no CPU or PyTorch fallback.")
+        lib = C.CDLL(PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

@@ -1,0 +1,273 @@
+// The C ABI's context, memory, event and per-kernel entry points (include/tachyon_b200.h).  Each validates its
+// descriptor on the host and launches nothing when validation fails, as the reference's `within()` checks do
+// (crates/tachyon/src/cuda/mod.rs:377-379).
+#include "../../include/tachyon_b200.h"
+#include "common.cuh"
+#include "internal.h"
+
+#include <string>
+
+namespace tb {
+
+static thread_local std::string g_error;
+
+int fail(int status, const std::string& what) {
+    g_error = what;
+    return status;
+}
+
+int cuda_fail(cudaError_t e, const char* where) {
+    cudaGetLastError();  // clear the sticky "last error" of non-fatal failures
+    const int status = e == cudaErrorMemoryAllocation ? OUT_OF_MEMORY
+                       : (e == cudaErrorInsufficientDriver || e == cudaErrorNoDevice || e == cudaErrorInitializationError) ? NO_DRIVER
+                                                                                                                           : CUDA;
+    return fail(status, std::string(where) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+}  // namespace tb
+
+using namespace tb;
+
+struct tb_event {
+    cudaEvent_t ev = nullptr;
+};
+
+extern "C" {
+
+const char* tb_last_error(void) { return g_error.c_str(); }
+
+int tb_context_new(int gpu, tb_context** out) {
+    if (out == nullptr) return fail(OUT_OF_RANGE, "tb_context_new: null out");
+    *out = nullptr;
+    int count = 0;
+    TB_CUDA(cudaGetDeviceCount(&count));
+    if (gpu < 0 || gpu >= count) return fail(OUT_OF_RANGE, "tb_context_new: no such GPU");
+    cudaDeviceProp prop;
+    TB_CUDA(cudaGetDeviceProperties(&prop, gpu));
+    if (prop.major != 10) return fail(UNSUPPORTED_GPU, std::string("tb_context_new: ") + prop.name + " is not an sm_100 device; this library has no other code path");
+    TB_CUDA(cudaSetDevice(gpu));
+    tb_context* ctx = new tb_context();
+    ctx->gpu = gpu;
+    ctx->sms = prop.multiProcessorCount;
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->status, 256);
+    if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, 256);
+    if (e == cudaSuccess) e = cudaHostAlloc(&ctx->status_host, 256, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        tb_context_free(ctx);
+        return cuda_fail(e, "tb_context_new");
+    }
+    const char* env = getenv("TACHYON_B200_NO_OVERLAP");
+    ctx->pdl = !(env != nullptr && env[0] == '1');
+    *out = ctx;
+    return OK;
+}
+
+void tb_context_free(tb_context* ctx) {
+    if (ctx == nullptr) return;
+    cudaSetDevice(ctx->gpu);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream), cudaStreamDestroy(ctx->stream);
+    if (ctx->status) cudaFree(ctx->status);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    delete ctx;
+}
+
+int tb_context_sms(const tb_context* ctx) { return ctx ? ctx->sms : 0; }
+
+int tb_context_set_overlap(tb_context* ctx, int on) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    ctx->pdl = on != 0;
+    return OK;
+}
+
+int tb_status(tb_context* ctx, uint32_t* word) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    TB_CUDA(cudaMemcpyAsync(ctx->status_host, ctx->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (word) *word = *ctx->status_host;
+    if (*ctx->status_host != 0) return fail(DEVICE_WAIT, "a kernel gave up a bounded wait (code " + std::to_string(*ctx->status_host) + ")");
+    return OK;
+}
+
+int tb_alloc(tb_context* ctx, size_t bytes, void** dev) {
+    if (!ctx || !dev) return fail(OUT_OF_RANGE, "tb_alloc: null argument");
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaMalloc(dev, bytes ? bytes : 1));
+    return OK;
+}
+
+int tb_free(tb_context* ctx, void* dev) {
+    if (!ctx) return fail(OUT_OF_RANGE, "tb_free: null context");
+    TB_CUDA(cudaStreamSynchronize(ctx->stream));
+    TB_CUDA(cudaFree(dev));
+    return OK;
+}
+
+int tb_alloc_host(tb_context* ctx, size_t bytes, void** host) {
+    if (!ctx || !host) return fail(OUT_OF_RANGE, "tb_alloc_host: null argument");
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaHostAlloc(host, bytes ? bytes : 1, cudaHostAllocMapped));
+    return OK;
+}
+
+int tb_free_host(tb_context* ctx, void* host) {
+    if (!ctx) return fail(OUT_OF_RANGE, "tb_free_host: null context");
+    TB_CUDA(cudaFreeHost(host));
+    return OK;
+}
+
+int tb_upload(tb_context* ctx, void* dev, const void* host, size_t bytes) {
+    if (!ctx || (bytes && (!dev || !host))) return fail(OUT_OF_RANGE, "tb_upload: null argument");
+    TB_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return OK;
+}
+
+int tb_download(tb_context* ctx, void* host, const void* dev, size_t bytes) {
+    if (!ctx || (bytes && (!dev || !host))) return fail(OUT_OF_RANGE, "tb_download: null argument");
+    TB_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return OK;
+}
+
+int tb_fill(tb_context* ctx, void* dev, int byte, size_t bytes) {
+    if (!ctx || (bytes && !dev)) return fail(OUT_OF_RANGE, "tb_fill: null argument");
+    TB_CUDA(cudaMemsetAsync(dev, byte, bytes, ctx->stream));
+    return OK;
+}
+
+int tb_sync(tb_context* ctx) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    TB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return OK;
+}
+
+int tb_event_new(tb_context* ctx, tb_event** out) {
+    if (!ctx || !out) return fail(OUT_OF_RANGE, "tb_event_new: null argument");
+    tb_event* ev = new tb_event();
+    cudaError_t e = cudaEventCreate(&ev->ev);
+    if (e != cudaSuccess) {
+        delete ev;
+        return cuda_fail(e, "cudaEventCreate");
+    }
+    *out = ev;
+    return OK;
+}
+
+void tb_event_free(tb_event* ev) {
+    if (!ev) return;
+    cudaEventDestroy(ev->ev);
+    delete ev;
+}
+
+int tb_event_record(tb_context* ctx, tb_event* ev) {
+    if (!ctx || !ev) return fail(OUT_OF_RANGE, "tb_event_record: null argument");
+    TB_CUDA(cudaEventRecord(ev->ev, ctx->stream));
+    return OK;
+}
+
+int tb_event_sync(tb_event* ev) {
+    if (!ev) return fail(OUT_OF_RANGE, "tb_event_sync: null event");
+    TB_CUDA(cudaEventSynchronize(ev->ev));
+    return OK;
+}
+
+int tb_event_elapsed_ms(tb_event* start, tb_event* end, float* ms) {
+    if (!start || !end || !ms) return fail(OUT_OF_RANGE, "tb_event_elapsed_ms: null argument");
+    TB_CUDA(cudaEventElapsedTime(ms, start->ev, end->ev));
+    return OK;
+}
+
+// ---- kernels ----------------------------------------------------------------------------------------------------
+
+static int dtype_ok(int d) { return d == TB_F32 || d == TB_F16; }
+
+int tb_gemv_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return fail(OUT_OF_RANGE, "tb_gemv_q8: unknown dtype");
+    GemvParams p;
+    p.w = w, p.s = reinterpret_cast<const __half*>(scales), p.rows = rows, p.cols = cols;
+    p.xmode = x_dtype == TB_F16 ? X_F16 : X_F32, p.x = x;
+    p.epi = y_dtype == TB_F16 ? EPI_F16 : EPI_F32, p.y = y;
+    return launch_gemv(ctx, p);
+}
+
+int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, const float* h, const float* y_res, const float* w1, const float* w2, float eps,
+                    float hscale, float* h_out, float* y, uint32_t rows, uint32_t cols, int geglu) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    GemvParams p;
+    p.w = w, p.s = reinterpret_cast<const __half*>(scales), p.rows = rows, p.cols = cols;
+    p.xmode = X_NORM, p.h = h, p.yres = y_res, p.w1 = w1, p.w2 = w2, p.eps = eps, p.hscale = hscale, p.h_out = h_out;
+    p.epi = geglu ? EPI_GEGLU : EPI_F32, p.y = y;
+    return launch_gemv(ctx, p);
+}
+
+int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, float* logits, uint32_t rows, uint32_t cols,
+                      void* scratch, uint32_t* state, uint32_t* token_out) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (!dtype_ok(x_dtype) || !scratch || (reinterpret_cast<uintptr_t>(scratch) & 7)) return fail(OUT_OF_RANGE, "tb_gemv_q8_argmax: bad dtype or scratch");
+    GemvParams p;
+    p.w = w, p.s = reinterpret_cast<const __half*>(scales), p.rows = rows, p.cols = cols;
+    p.xmode = x_dtype == TB_F16 ? X_F16 : X_F32, p.x = x;
+    p.epi = EPI_ARGMAX, p.y = logits;
+    p.best = static_cast<unsigned long long*>(scratch), p.count = reinterpret_cast<uint32_t*>(static_cast<char*>(scratch) + 8);
+    p.state = state, p.token_out = token_out;
+    return launch_gemv(ctx, p);
+}
+
+int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
+            float* x_out) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_norm(ctx, h, y_res, w1, w2, n, eps, hscale, h_out, x_out);
+}
+
+int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint32_t* token, uint32_t cols, float scale, float* out) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_embed_q8(ctx, w, reinterpret_cast<const __half*>(scales), token, cols, scale, out);
+}
+
+size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits) {
+    if (kv_heads == 0) return 0;
+    return attend_partial_floats(heads, kv_heads, splits) * sizeof(float);
+}
+
+int tb_attend_decode(tb_context* ctx, const tb_attend* a) {
+    if (!ctx || !a) return fail(OUT_OF_RANGE, "tb_attend_decode: null argument");
+    if (!dtype_ok(a->out_dtype)) return fail(OUT_OF_RANGE, "tb_attend_decode: unknown dtype");
+    AttendParams p;
+    p.qkv = a->qkv, p.q_norm = a->q_norm, p.k_norm = a->k_norm, p.freq = a->freq;
+    p.kc = reinterpret_cast<__half*>(a->k_cache), p.vc = reinterpret_cast<__half*>(a->v_cache);
+    p.pos = a->pos, p.cap = a->cap, p.window = a->window, p.fresh = a->fresh, p.heads = a->heads, p.kv_heads = a->kv_heads;
+    p.scale = a->scale, p.eps = a->eps, p.partial = a->partial, p.count = a->count, p.splits = a->splits;
+    p.out = a->out, p.out_f16 = a->out_dtype == TB_F16;
+    return launch_attend(ctx, p);
+}
+
+int tb_sample_greedy(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, uint32_t* seen, const uint32_t* allowed,
+                     void* scratch, uint32_t* state, uint32_t* token_out) {
+    if (!ctx || !scratch || (reinterpret_cast<uintptr_t>(scratch) & 7)) return fail(OUT_OF_RANGE, "tb_sample_greedy: bad scratch");
+    return launch_sample(ctx, logits, vocab, softcap, penalty, seen, allowed, static_cast<unsigned long long*>(scratch),
+                         reinterpret_cast<uint32_t*>(static_cast<char*>(scratch) + 8), state, seen, token_out);
+}
+
+int tb_topk(tb_context* ctx, const float* logits, uint32_t vocab, uint32_t k, uint32_t* idx, float* val) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_topk(ctx, logits, vocab, k, idx, val, nullptr);
+}
+
+int tb_fill_codes(tb_context* ctx, uint64_t seed, uint64_t stream_id, int8_t* dev, size_t n) {
+    if (!ctx || !dev) return fail(OUT_OF_RANGE, "tb_fill_codes: null argument");
+    return launch_fill_codes(ctx, seed, stream_id, dev, n);
+}
+int tb_fill_scales(tb_context* ctx, uint64_t seed, uint64_t stream_id, uint16_t* dev, size_t n, float mul) {
+    if (!ctx || !dev) return fail(OUT_OF_RANGE, "tb_fill_scales: null argument");
+    return launch_fill_scales(ctx, seed, stream_id, reinterpret_cast<__half*>(dev), n, mul);
+}
+int tb_fill_gauss_f16(tb_context* ctx, uint64_t seed, uint64_t stream_id, uint16_t* dev, size_t n, float mul) {
+    if (!ctx || !dev) return fail(OUT_OF_RANGE, "tb_fill_gauss_f16: null argument");
+    return launch_fill_gauss_f16(ctx, seed, stream_id, reinterpret_cast<__half*>(dev), n, mul);
+}
+int tb_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, float* dev, size_t n, float lo, float hi) {
+    if (!ctx || !dev) return fail(OUT_OF_RANGE, "tb_fill_uniform: null argument");
+    return launch_fill_uniform(ctx, seed, stream_id, dev, n, lo, hi);
+}
+
+}  // extern "C"

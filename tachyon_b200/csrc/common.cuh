@@ -1,0 +1,122 @@
+// Shared device helpers for the sm_100a kernels: bulk asynchronous copies with mbarrier completion, programmatic
+// dependent launch, bounded waits, and small numeric utilities.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+// Error words a kernel can leave in the context's device status word (0 = fine).
+enum : uint32_t { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_DRAIN = 3 };
+
+// Longest a thread polls one barrier before it gives up and reports: two seconds of %globaltimer.
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase with `parity` to complete, at most WAIT_LIMIT_NS; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = global_ns();
+    for (uint32_t spins = 0;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 255u) == 255u && global_ns() - start > WAIT_LIMIT_NS) return false;
+    }
+}
+
+// One-dimensional bulk copy global -> shared; `bytes` a multiple of 16, both addresses 16-byte aligned.  Completion
+// is counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+// Prefetch a range into L2 without a destination.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its independent prologue / wait for the
+// kernels before this one to have finished and their writes to be visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// dp4a with signed weights: against signed / unsigned activation bytes.
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Loads that bypass L1: activations written by an earlier (possibly overlapping) kernel.
+__device__ __forceinline__ float4 ld_cg_f4(const void* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ float ld_cg_f(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ uint32_t ld_cg_u(const uint32_t* p) { return __ldcg(p); }
+
+// tanh-form GELU, as the reference's decoder computes it (crates/tachyon/src/ptx/mod.rs:376-390):
+// x / (1 + 2^(-2*sqrt(2/pi)*log2(e)*(x + 0.044715 x^3))).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float u = x + 0.044715f * x * x * x;
+    return x / (1.0f + exp2f(-2.0f * 0.7978845608028654f * 1.4426950408889634f * u));
+}
+
+// A float's bits as an unsigned key with the same order (for atomicMax on values).
+__device__ __forceinline__ uint32_t float_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+}  // namespace tb

@@ -1,0 +1,596 @@
+// The decoder: buffers, the op list of one decode step, its capture into CUDA graphs and the calls that replay it.
+// Host-side counterpart of crates/tachyon/src/model/decode.rs (layout 151-181, control 190-204, step 569-592,
+// attention 603-618, mlp 631-662, record 525-528, step/start/next_token/stop 305-345) for a model without per-layer
+// inputs, shared caches or experts, with this build's Q8 weights.
+//
+// One step is 2 + 5 * layers launches:
+//   embed -> per layer { qkv (norm prologue) -> attention -> o -> gate_up (residual + norm prologue, GeGLU epilogue) ->
+//   down } -> LM head (residual + final norm prologue, greedy pick epilogue).
+// The residual additions and every RMS-norm run inside the prologue of the product that consumes them; the token and
+// the position live on the device (state = [position, token]) and are advanced by the last kernel, so steps chain
+// without the host.
+//
+// Seeded synthetic models (tb_decoder_fill_random): tensor k of layer i uses generator stream 32*i + k with k =
+// 0 qkv.w, 1 qkv.s, 2 o.w, 3 o.s, 4 gate_up.w, 5 gate_up.s (gate rows then up rows), 6 down.w, 7 down.s, 8 q_norm,
+// 9 k_norm, 10 input_layernorm, 11 post_attention_layernorm, 12 pre_feedforward_layernorm,
+// 13 post_feedforward_layernorm, 14 layer_scalar; 2^20 embed.w, 2^20+1 embed.s, 2^20+2 norm; caches 2^21 + 2*i (+1).
+// Codes are uniform in [-127, 127], scales |N(0,1)|*0.02/127, norm weights uniform in [0.5, 1.5), q/k norm weights in
+// [0.15, 0.35), layer scalars in [0.5, 1).
+#include "../../include/tachyon_b200.h"
+#include "common.cuh"
+#include "internal.h"
+
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+using namespace tb;
+
+namespace {
+
+struct Mat {
+    int8_t* w = nullptr;
+    __half* s = nullptr;
+    uint32_t rows = 0, cols = 0;
+    size_t code_bytes() const { return (size_t)rows * cols; }
+    size_t scale_bytes() const { return (size_t)rows * (cols / 32) * 2; }
+};
+
+struct Layer {
+    Mat qkv, o, gate_up, down;
+    float *q_norm = nullptr, *k_norm = nullptr, *input_ln = nullptr, *post_attn = nullptr, *pre_ffn = nullptr, *post_ffn = nullptr;
+    float layer_scalar = 1.0f;
+    bool global = false;
+    __half *kc = nullptr, *vc = nullptr;
+    uint32_t cap = 0, window = 0, splits = 1;
+};
+
+constexpr uint32_t TRACE = 1u << 16;  // tokens remembered by position (a power of two)
+
+}  // namespace
+
+struct tb_decoder {
+    tb_context* ctx = nullptr;
+    tb_config cfg = {};
+    tb_settings settings = {};
+    std::vector<uint8_t> global;
+    std::vector<Layer> layers;
+    Mat embed;
+    float* norm = nullptr;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    // step buffers
+    float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *y = nullptr, *g = nullptr, *logits = nullptr, *partial = nullptr;
+    float* freq[2] = {nullptr, nullptr};
+    uint32_t *count = nullptr, *state = nullptr, *trace = nullptr;
+    unsigned long long* best = nullptr;
+    uint32_t* words = nullptr;  // pinned host: [0], [1] the tokens the two graphs write; [2] staging for the token fed in
+    cudaGraphExec_t graphs[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    int at = 0;
+    bool running = false, built = false;
+    uint32_t pos = 0;  // host mirror of the position
+    uint32_t launches = 0;
+    int final_x = 0;  // which of x[0], x[1] holds the hidden state after the last layer
+    float embed_scale = 1.0f;
+};
+
+namespace {
+
+uint32_t nq(const tb_config& c) { return c.heads * c.head_dim; }
+uint32_t nkv(const tb_config& c) { return c.kv_heads * c.head_dim; }
+
+float bf16_round(float v) {
+    uint32_t b;
+    memcpy(&b, &v, 4);
+    b = (b + 0x7fffu + ((b >> 16) & 1u)) & 0xffff0000u;
+    memcpy(&v, &b, 4);
+    return v;
+}
+
+// crates/tachyon/src/ptx/attend.rs:62-65
+std::vector<float> rope_freq(float theta, uint32_t d, float fraction) {
+    std::vector<float> f(d / 2);
+    const uint32_t turned = (uint32_t)(fraction * (float)(d / 2));
+    for (uint32_t i = 0; i < d / 2; i++) f[i] = i < turned ? powf(theta, -((float)(2 * i)) / (float)d) : 0.0f;
+    return f;
+}
+
+int validate(const tb_config& c, const tb_settings& s) {
+    if (c.hidden != 2048) return fail(UNSUPPORTED, "decoder: hidden must be 2048 (the width the fused norm prologue is built for)");
+    if (c.head_dim != 256) return fail(UNSUPPORTED, "decoder: head_dim must be 256");
+    if (c.heads == 0 || c.kv_heads == 0 || c.heads % c.kv_heads != 0) return fail(UNSUPPORTED, "decoder: heads must be a multiple of kv_heads");
+    const uint32_t group = c.heads / c.kv_heads;
+    if (group != 1 && group != 2 && group != 4) return fail(UNSUPPORTED, "decoder: 1, 2 or 4 query heads per key-value head");
+    const uint32_t qcols = c.heads * c.head_dim;
+    if (qcols != 2048 && qcols != 4096 && qcols != 8192 && qcols != 16384 && qcols % 32 != 0) return fail(UNSUPPORTED, "decoder: heads*head_dim must be a multiple of 32");
+    if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
+    if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
+    if (s.context == 0 || s.context > TRACE) return fail(OUT_OF_RANGE, "decoder: context must be in 1..65536");
+    return OK;
+}
+
+struct Taker {
+    size_t end = 0;
+    size_t take(size_t bytes) {
+        const size_t at = end;
+        end += (bytes + 255) / 256 * 256;
+        return at;
+    }
+};
+
+// Lays everything out from offset 0 (the reference's `layout`, decode.rs:151-181); with base == nullptr only sizes it.
+void layout(tb_decoder* d, char* base) {
+    const tb_config& c = d->cfg;
+    Taker t;
+    auto mat = [&](Mat& m, uint32_t rows, uint32_t cols) {
+        m.rows = rows, m.cols = cols;
+        m.w = reinterpret_cast<int8_t*>(base + t.take(m.code_bytes()));
+        m.s = reinterpret_cast<__half*>(base + t.take(m.scale_bytes()));
+    };
+    auto vec = [&](float*& v, size_t n) { v = reinterpret_cast<float*>(base + t.take(n * 4)); };
+    mat(d->embed, c.vocab, c.hidden);
+    vec(d->norm, c.hidden);
+    uint32_t max_splits = 1;
+    for (uint32_t i = 0; i < c.layers; i++) {
+        Layer& L = d->layers[i];
+        L.global = d->global[i] != 0;
+        mat(L.qkv, nq(c) + 2 * nkv(c), c.hidden);
+        mat(L.o, c.hidden, nq(c));
+        mat(L.gate_up, 2 * c.ffn, c.hidden);
+        mat(L.down, c.hidden, c.ffn);
+        vec(L.q_norm, c.head_dim), vec(L.k_norm, c.head_dim);
+        vec(L.input_ln, c.hidden), vec(L.post_attn, c.hidden), vec(L.pre_ffn, c.hidden), vec(L.post_ffn, c.hidden);
+        // Caches: a global layer keeps `context` positions, a sliding one a ring of window + chunk (decode.rs:152).
+        L.window = L.global ? d->settings.context : c.window;
+        L.cap = L.global ? d->settings.context : c.window + d->settings.chunk;
+        const size_t cache = (size_t)c.kv_heads * L.cap * c.head_dim * 2;
+        L.kc = reinterpret_cast<__half*>(base + t.take(cache));
+        L.vc = reinterpret_cast<__half*>(base + t.take(cache));
+        // Blocks per key-value head: spans of about 32 positions (sliding) or 64 (global), within the machine.
+        const uint32_t per = L.global ? 64 : 32;
+        L.splits = (L.window + per - 1) / per;
+        const uint32_t most = (uint32_t)(2 * d->ctx->sms) / c.kv_heads;
+        if (L.splits > most) L.splits = most;
+        if (L.splits == 0) L.splits = 1;
+        if (L.splits > max_splits) max_splits = L.splits;
+    }
+    vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
+    vec(d->qkv, nq(c) + 2 * nkv(c)), vec(d->att, nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
+    vec(d->logits, d->settings.keep_logits ? c.vocab : 1);
+    vec(d->partial, attend_partial_floats(c.heads, c.kv_heads, max_splits));
+    vec(d->freq[0], c.head_dim / 2), vec(d->freq[1], c.head_dim / 2);
+    d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.kv_heads * 4));
+    d->state = reinterpret_cast<uint32_t*>(base + t.take(8));
+    d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
+    d->trace = reinterpret_cast<uint32_t*>(base + t.take((size_t)TRACE * 4));
+    d->arena_bytes = t.end;
+}
+
+int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
+    p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols;
+    d->launches++;
+    return launch_gemv(d->ctx, p);
+}
+
+// The op list of one step (decode.rs:569-592), launched on the context's stream.
+int step_ops(tb_decoder* d, uint32_t* token_word) {
+    const tb_config& c = d->cfg;
+    d->launches = 0;
+    int cur = 0;
+    TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0]));
+    d->launches++;
+    for (uint32_t i = 0; i < c.layers; i++) {
+        Layer& L = d->layers[i];
+        GemvParams q;
+        q.xmode = X_NORM, q.h = d->x[cur], q.w2 = L.input_ln, q.eps = c.eps;
+        if (i > 0) {
+            // The previous layer's closing residual: x = (x + post_ffn_norm(down)) * layer_scalar (decode.rs:631-662).
+            const Layer& P = d->layers[i - 1];
+            q.yres = d->y, q.w1 = P.post_ffn, q.hscale = P.layer_scalar, q.h_out = d->x[1 - cur];
+            cur = 1 - cur;
+        }
+        q.epi = EPI_F32, q.y = d->qkv;
+        TB_TRY(gemv(d, L.qkv, q));
+
+        AttendParams a;
+        a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0];
+        a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = 1;
+        a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
+        a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
+        TB_TRY(launch_attend(d->ctx, a));
+        d->launches++;
+
+        GemvParams o;
+        o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
+        TB_TRY(gemv(d, L.o, o));
+
+        GemvParams gu;
+        gu.xmode = X_NORM, gu.h = d->x[cur], gu.yres = d->y, gu.w1 = L.post_attn, gu.hscale = 1.0f, gu.w2 = L.pre_ffn, gu.eps = c.eps;
+        gu.h_out = d->x[1 - cur];
+        cur = 1 - cur;
+        gu.epi = EPI_GEGLU, gu.y = d->g;
+        TB_TRY(gemv(d, L.gate_up, gu));
+
+        GemvParams dn;
+        dn.xmode = X_F32, dn.x = d->g, dn.epi = EPI_F32, dn.y = d->y;
+        TB_TRY(gemv(d, L.down, dn));
+    }
+    const Layer& P = d->layers[c.layers - 1];
+    GemvParams h;
+    h.xmode = X_NORM, h.h = d->x[cur], h.yres = d->y, h.w1 = P.post_ffn, h.hscale = P.layer_scalar, h.w2 = d->norm, h.eps = c.eps;
+    h.h_out = d->x[1 - cur];
+    h.epi = EPI_ARGMAX, h.y = d->settings.keep_logits ? d->logits : nullptr;
+    h.best = d->best, h.count = reinterpret_cast<uint32_t*>(d->best + 1), h.state = d->state, h.token_out = token_word;
+    h.trace = d->trace, h.trace_mask = TRACE - 1;
+    TB_TRY(gemv(d, d->embed, h));
+    d->final_x = 1 - cur;
+    return OK;
+}
+
+struct Named {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int kind = 0;  // 0 plain, 1 gate_up codes, 2 gate_up scales, 3 layer scalar
+    uint32_t layer = 0;
+};
+
+bool find_tensor(tb_decoder* d, const std::string& name, Named& out) {
+    const tb_config& c = d->cfg;
+    auto mat = [&](Mat& m, const std::string& suffix, int gate_up) {
+        if (suffix == ".w") out = {m.w, m.code_bytes(), gate_up ? 1 : 0, 0};
+        else if (suffix == ".s") out = {m.s, m.scale_bytes(), gate_up ? 2 : 0, 0};
+        else return false;
+        return true;
+    };
+    if (name.rfind("embed", 0) == 0) return mat(d->embed, name.substr(5), 0);
+    if (name == "norm") return out = {d->norm, (size_t)c.hidden * 4, 0, 0}, true;
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos || dot == 0) return false;
+    uint32_t i = 0;
+    for (size_t k = 0; k < dot; k++) {
+        if (name[k] < '0' || name[k] > '9') return false;
+        i = i * 10 + (uint32_t)(name[k] - '0');
+    }
+    if (i >= c.layers) return false;
+    Layer& L = d->layers[i];
+    const std::string rest = name.substr(dot + 1);
+    if (rest.rfind("qkv", 0) == 0) return mat(L.qkv, rest.substr(3), 0);
+    if (rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), 0);
+    if (rest.rfind("gate_up", 0) == 0) return mat(L.gate_up, rest.substr(7), 1);
+    if (rest.rfind("down", 0) == 0) return mat(L.down, rest.substr(4), 0);
+    const size_t hb = (size_t)c.hidden * 4, db = (size_t)c.head_dim * 4;
+    if (rest == "q_norm") return out = {L.q_norm, db, 0, i}, true;
+    if (rest == "k_norm") return out = {L.k_norm, db, 0, i}, true;
+    if (rest == "input_layernorm") return out = {L.input_ln, hb, 0, i}, true;
+    if (rest == "post_attention_layernorm") return out = {L.post_attn, hb, 0, i}, true;
+    if (rest == "pre_feedforward_layernorm") return out = {L.pre_ffn, hb, 0, i}, true;
+    if (rest == "post_feedforward_layernorm") return out = {L.post_ffn, hb, 0, i}, true;
+    if (rest == "layer_scalar") return out = {nullptr, 4, 3, i}, true;
+    return false;
+}
+
+int set_position(tb_decoder* d, uint32_t pos) {
+    d->words[2] = pos;
+    TB_CUDA(cudaMemcpyAsync(d->state, d->words + 2, 4, cudaMemcpyHostToDevice, d->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    d->pos = pos;
+    return OK;
+}
+
+int queue(tb_decoder* d, int g) {
+    TB_CUDA(cudaGraphLaunch(d->graphs[g], d->ctx->stream));
+    TB_CUDA(cudaEventRecord(d->done[g], d->ctx->stream));
+    d->pos++;
+    return OK;
+}
+
+int feed_token(tb_decoder* d, uint32_t token) {
+    if (token >= d->cfg.vocab) return fail(OUT_OF_RANGE, "decoder: token outside the vocabulary");
+    d->words[2] = token;
+    TB_CUDA(cudaMemcpyAsync(d->state + 1, d->words + 2, 4, cudaMemcpyHostToDevice, d->ctx->stream));
+    return OK;
+}
+
+int ready(tb_decoder* d, uint32_t steps) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    if (!d->built) return fail(NO_MODEL, "decoder: tb_decoder_build has not run");
+    if ((uint64_t)d->pos + steps > d->settings.context) return fail(TOO_LONG, "decoder: the sequence would pass the context");
+    return OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, tb_decoder** out) {
+    if (!ctx || !cfg || !settings || !out) return fail(OUT_OF_RANGE, "tb_decoder_open: null argument");
+    *out = nullptr;
+    TB_TRY(validate(*cfg, *settings));
+    tb_decoder* d = new tb_decoder();
+    d->ctx = ctx, d->cfg = *cfg, d->settings = *settings;
+    d->global.resize(cfg->layers);
+    for (uint32_t i = 0; i < cfg->layers; i++)
+        d->global[i] = cfg->global ? cfg->global[i] : (cfg->global_every ? ((i + 1) % cfg->global_every == 0) : 0);
+    d->cfg.global = nullptr;
+    d->layers.resize(cfg->layers);
+    // The embedding's scale is sqrt(hidden) rounded to bfloat16 (decode.rs:571, 689-693).
+    d->embed_scale = bf16_round(sqrtf((float)cfg->hidden));
+    layout(d, nullptr);
+    cudaError_t e = cudaSetDevice(ctx->gpu);
+    if (e == cudaSuccess) e = cudaMalloc(&d->arena, d->arena_bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d->arena, 0, d->arena_bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaHostAlloc(&d->words, 64, cudaHostAllocMapped);
+    for (int g = 0; g < 2 && e == cudaSuccess; g++) e = cudaEventCreateWithFlags(&d->done[g], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        const int s = cuda_fail(e, "tb_decoder_open");
+        tb_decoder_close(d);
+        return s;
+    }
+    layout(d, d->arena);
+    memset(d->words, 0, 64);
+    for (int k = 0; k < 2; k++) {
+        const std::vector<float> f = rope_freq(k ? cfg->theta_global : cfg->theta_sliding, cfg->head_dim, k ? cfg->fraction_global : 1.0f);
+        e = cudaMemcpyAsync(d->freq[k], f.data(), f.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            const int s = cuda_fail(e, "tb_decoder_open: rope tables");
+            tb_decoder_close(d);
+            return s;
+        }
+    }
+    *out = d;
+    return OK;
+}
+
+void tb_decoder_close(tb_decoder* d) {
+    if (!d) return;
+    if (d->ctx && d->ctx->stream) cudaStreamSynchronize(d->ctx->stream);
+    for (int g = 0; g < 2; g++) {
+        if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]);
+        if (d->done[g]) cudaEventDestroy(d->done[g]);
+    }
+    if (d->arena) cudaFree(d->arena);
+    if (d->words) cudaFreeHost(d->words);
+    delete d;
+}
+
+int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t bytes) {
+    if (!d || !name || !data) return fail(OUT_OF_RANGE, "tb_decoder_load: null argument");
+    Named t;
+    if (!find_tensor(d, name, t)) return fail(NO_MODEL, std::string("tb_decoder_load: no tensor named ") + name);
+    if (bytes != t.bytes) return fail(FORMAT, std::string("tb_decoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
+    cudaStream_t s = d->ctx->stream;
+    if (t.kind == 3) {
+        memcpy(&d->layers[t.layer].layer_scalar, data, 4);
+        d->built = false;
+        return OK;
+    }
+    if (t.kind == 0) {
+        TB_CUDA(cudaMemcpyAsync(t.ptr, data, bytes, cudaMemcpyHostToDevice, s));
+        TB_CUDA(cudaStreamSynchronize(s));
+        return OK;
+    }
+    // gate_up: gate rows then up rows in the file; pairs (gate_j, up_j) on the device.
+    void* tmp = nullptr;
+    TB_CUDA(cudaMalloc(&tmp, bytes));
+    cudaError_t e = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, s);
+    int st = OK;
+    if (e == cudaSuccess) st = launch_interleave_rows(d->ctx, tmp, t.ptr, d->cfg.ffn, (uint32_t)(bytes / (2 * (size_t)d->cfg.ffn)));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(tmp);
+    if (e != cudaSuccess) return cuda_fail(e, "tb_decoder_load");
+    return st;
+}
+
+int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    const tb_config& c = d->cfg;
+    tb_context* ctx = d->ctx;
+    const float smul = 0.02f / 127.0f;
+    auto mat = [&](Mat& m, uint64_t id) -> int {
+        TB_TRY(launch_fill_codes(ctx, seed, id, m.w, m.code_bytes()));
+        return launch_fill_scales(ctx, seed, id + 1, m.s, m.scale_bytes() / 2, smul);
+    };
+    TB_TRY(mat(d->embed, 1ull << 20));
+    TB_TRY(launch_fill_uniform(ctx, seed, (1ull << 20) + 2, d->norm, c.hidden, 0.5f, 1.5f));
+    void *tw = nullptr, *ts = nullptr;
+    TB_CUDA(cudaMalloc(&tw, d->layers[0].gate_up.code_bytes()));
+    TB_CUDA(cudaMalloc(&ts, d->layers[0].gate_up.scale_bytes()));
+    int st = OK;
+    for (uint32_t i = 0; i < c.layers && st == OK; i++) {
+        Layer& L = d->layers[i];
+        const uint64_t b = 32ull * i;
+        st = mat(L.qkv, b);
+        if (st == OK) st = mat(L.o, b + 2);
+        if (st == OK) st = launch_fill_codes(ctx, seed, b + 4, static_cast<int8_t*>(tw), L.gate_up.code_bytes());
+        if (st == OK) st = launch_fill_scales(ctx, seed, b + 5, static_cast<__half*>(ts), L.gate_up.scale_bytes() / 2, smul);
+        if (st == OK) st = launch_interleave_rows(ctx, tw, L.gate_up.w, c.ffn, c.hidden);
+        if (st == OK) st = launch_interleave_rows(ctx, ts, L.gate_up.s, c.ffn, c.hidden / 32 * 2);
+        if (st == OK) st = mat(L.down, b + 6);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 8, L.q_norm, c.head_dim, 0.15f, 0.35f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 9, L.k_norm, c.head_dim, 0.15f, 0.35f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 10, L.input_ln, c.hidden, 0.5f, 1.5f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 11, L.post_attn, c.hidden, 0.5f, 1.5f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 12, L.pre_ffn, c.hidden, 0.5f, 1.5f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 13, L.post_ffn, c.hidden, 0.5f, 1.5f);
+        if (st == OK) {
+            // The scalar comes from the same generator, evaluated through a one-element device fill.
+            st = launch_fill_uniform(ctx, seed, b + 14, d->x[0], 1, 0.5f, 1.0f);
+            if (st == OK && cudaMemcpyAsync(d->words + 3, d->x[0], 4, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) st = fail(CUDA, "fill: copy");
+            if (st == OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = fail(CUDA, "fill: sync");
+            if (st == OK) memcpy(&L.layer_scalar, d->words + 3, 4);
+        }
+    }
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(tw);
+    cudaFree(ts);
+    if (st == OK) TB_CUDA(cudaMemsetAsync(d->x[0], 0, 4, ctx->stream));
+    d->built = false;
+    return st;
+}
+
+int tb_decoder_fill_cache(tb_decoder* d, uint64_t seed, uint32_t positions) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    if (positions > d->settings.context) return fail(TOO_LONG, "tb_decoder_fill_cache: more positions than the context");
+    const tb_config& c = d->cfg;
+    for (uint32_t i = 0; i < c.layers; i++) {
+        Layer& L = d->layers[i];
+        // Position p lives in slot p % cap; filling whole caches covers every slot a window can reach.
+        const size_t n = (size_t)c.kv_heads * L.cap * c.head_dim;
+        TB_TRY(launch_fill_gauss_f16(d->ctx, seed, (1ull << 21) + 2ull * i, L.kc, n, 1.0f));
+        TB_TRY(launch_fill_gauss_f16(d->ctx, seed, (1ull << 21) + 2ull * i + 1, L.vc, n, 1.0f));
+    }
+    return set_position(d, positions);
+}
+
+int tb_decoder_build(tb_decoder* d) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    cudaStream_t s = d->ctx->stream;
+    TB_CUDA(cudaStreamSynchronize(s));
+    for (int g = 0; g < 2; g++) {
+        if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]), d->graphs[g] = nullptr;
+        uint32_t* word = nullptr;
+        TB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&word), d->words + g, 0));
+        // One uncaptured pass first: it sets each kernel's attributes (not allowed while capturing) and surfaces
+        // descriptor errors plainly.  It runs on zeroed state and is followed by a reset.
+        if (g == 0) {
+            TB_TRY(step_ops(d, word));
+            TB_CUDA(cudaStreamSynchronize(s));
+        }
+        TB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        const int st = step_ops(d, word);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(s, &graph);
+        if (st != OK) {
+            if (graph) cudaGraphDestroy(graph);
+            return st;
+        }
+        if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+        const cudaError_t ei = cudaGraphInstantiate(&d->graphs[g], graph, 0);
+        cudaGraphDestroy(graph);
+        if (ei != cudaSuccess) return cuda_fail(ei, "cudaGraphInstantiate");
+    }
+    d->built = true;
+    d->running = false;
+    // The uncaptured pass advanced the position and wrote a cache slot; start clean.
+    return tb_decoder_reset(d);
+}
+
+int tb_decoder_reset(tb_decoder* d) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    if (d->running) TB_TRY(tb_decoder_stop(d));
+    TB_CUDA(cudaMemsetAsync(d->state, 0, 8, d->ctx->stream));
+    return set_position(d, 0);
+}
+
+int tb_decoder_step(tb_decoder* d, uint32_t token, uint32_t* next) {
+    TB_TRY(ready(d, 1));
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_step: a generation is running; stop it first");
+    TB_TRY(feed_token(d, token));
+    TB_TRY(queue(d, 0));
+    TB_CUDA(cudaEventSynchronize(d->done[0]));
+    if (next) *next = d->words[0];
+    return OK;
+}
+
+int tb_decoder_start(tb_decoder* d, uint32_t token) {
+    TB_TRY(ready(d, 1));
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_start: already running");
+    TB_TRY(feed_token(d, token));
+    d->at = 0;
+    TB_TRY(queue(d, 0));
+    d->running = true;
+    return OK;
+}
+
+int tb_decoder_next_token(tb_decoder* d, uint32_t* token) {
+    if (!d || !d->running) return fail(OUT_OF_RANGE, "tb_decoder_next_token: no generation running");
+    TB_TRY(ready(d, 1));
+    const int g = d->at;
+    TB_TRY(queue(d, 1 - g));  // the step on the token being waited for: the GPU never waits for the host
+    TB_CUDA(cudaEventSynchronize(d->done[g]));
+    d->at = 1 - g;
+    if (token) *token = d->words[g];
+    return OK;
+}
+
+int tb_decoder_stop(tb_decoder* d) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    if (!d->running) return OK;
+    TB_CUDA(cudaEventSynchronize(d->done[d->at]));
+    d->running = false;
+    return OK;
+}
+
+int tb_decoder_run(tb_decoder* d, uint32_t token, uint32_t steps, uint32_t* tokens_out) {
+    TB_TRY(ready(d, steps));
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_run: a generation is running; stop it first");
+    const uint32_t first = d->pos;
+    TB_TRY(feed_token(d, token));
+    for (uint32_t i = 0; i < steps; i++) TB_TRY(queue(d, (int)(i & 1)));
+    if (tokens_out) {
+        TB_CUDA(cudaMemcpyAsync(tokens_out, d->trace + first, (size_t)steps * 4, cudaMemcpyDeviceToHost, d->ctx->stream));
+        TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    }
+    return OK;
+}
+
+int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
+    TB_TRY(ready(d, n));
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_prefill: a generation is running; stop it first");
+    if (n && !tokens) return fail(OUT_OF_RANGE, "tb_decoder_prefill: null tokens");
+    for (uint32_t i = 0; i < n; i++) {
+        if (tokens[i] >= d->cfg.vocab) return fail(OUT_OF_RANGE, "decoder: token outside the vocabulary");
+        // Every prompt token through the decode step; its sample is dropped (the next token overwrites it).
+        TB_CUDA(cudaMemcpyAsync(d->state + 1, tokens + i, 4, cudaMemcpyHostToDevice, d->ctx->stream));
+        TB_TRY(queue(d, 0));
+    }
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    return OK;
+}
+
+int tb_decoder_logits(tb_decoder* d, float* host_out) {
+    if (!d || !host_out) return fail(OUT_OF_RANGE, "tb_decoder_logits: null argument");
+    if (!d->settings.keep_logits) return fail(UNSUPPORTED, "tb_decoder_logits: the decoder was opened without keep_logits");
+    TB_CUDA(cudaMemcpyAsync(host_out, d->logits, (size_t)d->cfg.vocab * 4, cudaMemcpyDeviceToHost, d->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    return OK;
+}
+
+int tb_decoder_position(tb_decoder* d, uint32_t* pos) {
+    if (!d || !pos) return fail(OUT_OF_RANGE, "tb_decoder_position: null argument");
+    TB_CUDA(cudaMemcpyAsync(d->words + 4, d->state, 4, cudaMemcpyDeviceToHost, d->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    *pos = d->words[4];
+    return OK;
+}
+
+int tb_decoder_step_bytes(tb_decoder* d, uint64_t* weight_bytes, uint64_t* cache_bytes) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    uint64_t w = d->embed.code_bytes() + d->embed.scale_bytes(), kv = 0;
+    for (const Layer& L : d->layers) {
+        for (const Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) w += m->code_bytes() + m->scale_bytes();
+        const uint64_t n = (uint64_t)d->pos + 1 < L.window ? (uint64_t)d->pos + 1 : L.window;
+        kv += 2ull * d->cfg.kv_heads * n * d->cfg.head_dim * 2;
+    }
+    if (weight_bytes) *weight_bytes = w;
+    if (cache_bytes) *cache_bytes = kv;
+    return OK;
+}
+
+int tb_decoder_step_launches(tb_decoder* d, uint32_t* launches) {
+    if (!d || !launches) return fail(OUT_OF_RANGE, "null argument");
+    *launches = 2 + 5 * d->cfg.layers;
+    return OK;
+}
+
+int tb_decoder_hidden(tb_decoder* d, float* host_out) {
+    if (!d || !host_out) return fail(OUT_OF_RANGE, "null argument");
+    TB_CUDA(cudaMemcpyAsync(host_out, d->x[d->final_x], (size_t)d->cfg.hidden * 4, cudaMemcpyDeviceToHost, d->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    return OK;
+}
+
+}  // extern "C"

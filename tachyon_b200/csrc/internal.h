@@ -1,0 +1,131 @@
+// Host-side declarations shared by the library's translation units: the context, launch descriptors of each
+// kernel family, and error plumbing.  Nothing here is part of the C ABI (see include/tachyon_b200.h).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+struct tb_context {
+    int gpu = 0;
+    int sms = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t* status = nullptr;       // device word: first kernel-side error (tb::ERR_*), 0 when fine
+    uint32_t* status_host = nullptr;  // pinned mirror used by tb_status
+    bool pdl = true;                  // launch kernels with programmatic stream serialization
+};
+
+namespace tb {
+
+// Status codes of the C ABI (mirrors the reference's error enum, crates/tachyon/src/error.rs:8-50).
+enum Status : int {
+    OK = 0,
+    NO_DRIVER = 1,
+    UNSUPPORTED_GPU = 2,
+    OUT_OF_RANGE = 3,
+    CUDA = 4,
+    FORMAT = 5,
+    TOO_LONG = 6,
+    OUT_OF_MEMORY = 7,
+    NO_MODEL = 8,
+    UNSUPPORTED = 9,
+    DEVICE_WAIT = 10,
+};
+
+int fail(int status, const std::string& what);
+int cuda_fail(cudaError_t e, const char* where);
+#define TB_CUDA(call)                                             \
+    do {                                                          \
+        cudaError_t e_ = (call);                                  \
+        if (e_ != cudaSuccess) return ::tb::cuda_fail(e_, #call); \
+    } while (0)
+#define TB_TRY(call)               \
+    do {                           \
+        int s_ = (call);           \
+        if (s_ != ::tb::OK) return s_; \
+    } while (0)
+
+// ---- GEMV ------------------------------------------------------------------------------------------------
+enum XMode : int { X_F16 = 0, X_F32 = 1, X_NORM = 2 };
+enum Epilogue : int { EPI_F32 = 0, EPI_F16 = 1, EPI_GEGLU = 2, EPI_ARGMAX = 3 };
+
+struct GemvParams {
+    const int8_t* w = nullptr;    // [rows, cols] codes
+    const __half* s = nullptr;    // [rows, cols/32] scales
+    uint32_t rows = 0, cols = 0;
+    int xmode = X_F16;
+    const void* x = nullptr;      // X_F16 / X_F32: the activation vector [cols]
+    // X_NORM: x = w2 * rmsnorm(h'), h' = (h + w1 * rmsnorm(y)) * hscale (y may be null: h' = h; w2 may be null: x = h')
+    const float* h = nullptr;
+    const float* yres = nullptr;
+    const float* w1 = nullptr;
+    const float* w2 = nullptr;
+    float eps = 1e-6f, hscale = 1.0f;
+    float* h_out = nullptr;       // receives h' (written by one block); may be null
+    int epi = EPI_F32;
+    void* y = nullptr;            // EPI_F32/F16: [rows]; EPI_GEGLU: f32 [rows/2]; EPI_ARGMAX: optional f32 logits [rows]
+    // EPI_ARGMAX: the pick is published through `best` (zero between launches) and `count` (zero between launches);
+    // the last block writes state[1] = token, state[0] += 1, *token_out (may be null), and clears both.
+    unsigned long long* best = nullptr;
+    uint32_t* count = nullptr;
+    uint32_t* state = nullptr;
+    uint32_t* token_out = nullptr;
+    uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
+    uint32_t trace_mask = 0;
+};
+
+int launch_gemv(tb_context* ctx, const GemvParams& p);
+size_t gemv_smem_bytes();
+
+// ---- decode attention ----------------------------------------------------------------------------------------
+struct AttendParams {
+    const float* qkv = nullptr;    // [(heads + 2*kv_heads) * 256] f32: queries, then new keys, then new values
+    const float* q_norm = nullptr; // [256] or null (plain mode: no norms)
+    const float* k_norm = nullptr;
+    const float* freq = nullptr;   // [128] RoPE frequencies or null (no rotation)
+    __half* kc = nullptr;          // [kv_heads][cap][256]
+    __half* vc = nullptr;
+    const uint32_t* pos = nullptr; // device word: position of the new token
+    uint32_t cap = 0, window = 0, fresh = 1, heads = 8, kv_heads = 2;
+    float scale = 1.0f, eps = 1e-6f;
+    float* partial = nullptr;      // scratch: kv_heads * splits * (2*group + group*256) floats
+    uint32_t* count = nullptr;     // kv_heads words, zero between launches
+    uint32_t splits = 1;           // blocks per kv head (upper bound on the split actually used)
+    void* out = nullptr;           // [heads*256] f32 or f16
+    int out_f16 = 0;
+};
+int launch_attend(tb_context* ctx, const AttendParams& p);
+size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
+
+// ---- small kernels ---------------------------------------------------------------------------------------------
+int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);
+int launch_norm(tb_context* ctx, const float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,
+                float* h_out, float* x_out);
+int launch_sample(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, const uint32_t* seen,
+                  const uint32_t* allowed, unsigned long long* best, uint32_t* count, uint32_t* state, uint32_t* seen_out, uint32_t* token_out);
+int launch_topk(tb_context* ctx, const float* logits, uint32_t vocab, uint32_t k, uint32_t* idx, float* val, unsigned long long* scratch);
+int launch_fill_codes(tb_context* ctx, uint64_t seed, uint64_t stream_id, int8_t* w, size_t n);
+int launch_fill_scales(tb_context* ctx, uint64_t seed, uint64_t stream_id, __half* s, size_t n, float mul);
+int launch_fill_gauss_f16(tb_context* ctx, uint64_t seed, uint64_t stream_id, __half* x, size_t n, float mul);
+int launch_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, float* x, size_t n, float lo, float hi);
+int launch_interleave_rows(tb_context* ctx, const void* src, void* dst, uint32_t half_rows, uint32_t row_bytes);
+
+// Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && ctx->pdl) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+}  // namespace tb

@@ -1,0 +1,64 @@
+"""The C-ABI library builds, loads without a GPU, and exports exactly what include/tachyon_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared():
+    text = open(os.path.join(ROOT, "include", "tachyon_b200.h")).read()
+    return sorted(set(re.findall(r"^TB_API [^;]*?\b(tb_\w+)\(", text, flags=re.M)))
+
+
+@pytest.fixture(scope="module")
+def lib_path():
+    from tachyon_b200 import build
+
+    return build.build()
+
+
+def test_header_declares_the_entry_points():
+    names = declared()
+    assert "tb_gemv_q8" in names and "tb_attend_decode" in names and "tb_decoder_step" in names
+    assert len(names) >= 45
+
+
+def test_library_exports_every_declared_symbol(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    missing = [n for n in declared() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_binding_covers_the_header(lib_path):
+    from tachyon_b200 import _lib
+
+    assert sorted(_lib.SIGNATURES) == declared()
+
+
+def test_library_needs_no_cuda_runtime_library(lib_path):
+    import subprocess
+
+    needed = subprocess.run(["readelf", "-d", lib_path], capture_output=True, text=True).stdout
+    assert "libcudart" not in needed, "the CUDA runtime must be linked statically"
+
+
+def test_no_gpu_is_reported_not_papered_over(lib_path):
+    import tachyon_b200 as tb
+
+    if os.path.exists("/dev/nvidiactl"):
+        pytest.skip("a GPU is present")
+    with pytest.raises(tb.Error) as e:
+        tb.Context(0)
+    assert e.value.status in (1, 3, 4)  # no driver / no such GPU / CUDA error: never a silent CPU path
+
+
+def test_bad_descriptors_are_rejected_before_launch(lib_path):
+    """Host-side validation needs no GPU for null contexts."""
+    lib = ctypes.CDLL(lib_path)
+    lib.tb_last_error.restype = ctypes.c_char_p
+    assert lib.tb_sync(None) == 3
+    assert b"null" in lib.tb_last_error()
+    assert lib.tb_attend_decode(None, None) == 3

@@ -1,0 +1,95 @@
+"""Decode attention on the GPU against the f64 oracle.  Cases follow crates/tachyon/tests/decode.rs:185-334 (short
+context, full sliding window, ring longer than the window, shared cache, 1/2/4 query heads per key-value head) at head
+size 256, plus the benchmark's plain configuration (scale 1/16, no norms, f16 output, 4096 positions)."""
+import numpy as np
+import pytest
+
+import oracle
+import tachyon_b200 as tb
+from util import f16, f16_to_f32, values_fast
+
+pytestmark = pytest.mark.gpu
+D = 256
+
+
+def run_case(ctx, *, cap, win, pos, splits, fresh, heads, kv, plain=False, out_f16=False, times=2, scale=1.0, seed=0):
+    rng_seed = seed + pos + cap
+    rows = heads + 2 * kv
+    qkv = values_fast(rows * D, rng_seed)
+    if plain:
+        qkv = np.random.default_rng(rng_seed).standard_normal(rows * D).astype(np.float32)
+    qn = (0.2 + 0.1 * values_fast(D, rng_seed + 1)).astype(np.float32)
+    kn = (0.2 + 0.1 * values_fast(D, rng_seed + 2)).astype(np.float32)
+    freq = oracle.rope_freq(10000.0, D, 1.0)
+    mul = 1.0 if plain else 0.3
+    kc = f16(mul * (np.random.default_rng(rng_seed + 3).standard_normal(kv * cap * D) if plain else values_fast(kv * cap * D, rng_seed + 3)))
+    vc = f16(mul * (np.random.default_rng(rng_seed + 4).standard_normal(kv * cap * D) if plain else values_fast(kv * cap * D, rng_seed + 4)))
+    kc0, vc0 = kc.copy(), vc.copy()
+    want = oracle.attend_decode(qkv, None if plain else qn, None if plain else kn, None if plain else freq, kc0, vc0, pos, cap, win, fresh, heads, kv, D, scale)
+
+    bufs = dict(qkv=ctx.upload(qkv), qn=ctx.upload(qn), kn=ctx.upload(kn), freq=ctx.upload(freq), k=ctx.upload(kc), v=ctx.upload(vc),
+                pos=ctx.upload(np.array([pos], np.uint32)), part=ctx.zeros(max(ctx.attend_scratch_bytes(heads, kv, splits), 16)),
+                count=ctx.zeros(4 * kv), out=ctx.zeros(heads * D * 4))
+    a = tb.Attend(qkv=bufs["qkv"].ptr, q_norm=None if plain else bufs["qn"].ptr, k_norm=None if plain else bufs["kn"].ptr,
+                  freq=None if plain else bufs["freq"].ptr, k_cache=bufs["k"].ptr, v_cache=bufs["v"].ptr, pos=bufs["pos"].ptr, cap=cap, window=win,
+                  fresh=int(fresh), heads=heads, kv_heads=kv, scale=scale, eps=1e-6, partial=bufs["part"].ptr, count=bufs["count"].ptr, splits=splits,
+                  out=bufs["out"].ptr, out_dtype=tb.F16 if out_f16 else tb.F32)
+    for _ in range(times):
+        ctx.attend_decode(a)
+    assert not bufs["count"].download(np.uint32, kv).any(), "the counters are left at zero"
+    got = f16_to_f32(bufs["out"].download(np.uint16, heads * D)) if out_f16 else bufs["out"].download(np.float32, heads * D)
+    tol = (2e-3 if out_f16 else 1e-3) * np.abs(want).max()
+    assert np.abs(got - want).max() <= tol, (np.abs(got - want).max(), tol)
+    # the caches: untouched when shared, the new token's slot rewritten when fresh
+    k_after, v_after = bufs["k"].download(np.uint16, kv * cap * D), bufs["v"].download(np.uint16, kv * cap * D)
+    if not fresh:
+        assert np.array_equal(k_after, kc) and np.array_equal(v_after, vc)
+    else:
+        slot = pos % cap
+        mask = np.ones(kv * cap * D, bool)
+        for g in range(kv):
+            mask[(g * cap + slot) * D:(g * cap + slot + 1) * D] = False
+        assert np.array_equal(k_after[mask], kc[mask]) and np.array_equal(v_after[mask], vc[mask]), "only the new slot changes"
+        for got_c, want_c in ((k_after, kc0), (v_after, vc0)):
+            g_, w_ = f16_to_f32(got_c[~mask]), f16_to_f32(want_c[~mask])
+            assert np.all(np.abs(g_ - w_) <= 1e-3 * np.abs(w_) + 1e-4)
+
+
+def test_attention_over_a_short_context(ctx):
+    run_case(ctx, cap=512, win=512, pos=0, splits=16, fresh=True, heads=8, kv=2)
+    run_case(ctx, cap=512, win=512, pos=100, splits=16, fresh=True, heads=8, kv=2)
+    run_case(ctx, cap=512, win=512, pos=100, splits=16, fresh=True, heads=4, kv=2)  # two query heads per kv head
+    run_case(ctx, cap=512, win=512, pos=100, splits=16, fresh=True, heads=2, kv=2)  # one
+    run_case(ctx, cap=512, win=512, pos=17, splits=1, fresh=True, heads=8, kv=2)    # a single block, no scratch used
+
+
+def test_attention_over_a_full_sliding_window(ctx):
+    run_case(ctx, cap=512, win=512, pos=700, splits=16, fresh=True, heads=8, kv=2)
+    run_case(ctx, cap=1024, win=512, pos=1700, splits=16, fresh=True, heads=8, kv=2)  # a ring longer than the window
+    run_case(ctx, cap=2048, win=1024, pos=3000, splits=32, fresh=True, heads=4, kv=2)
+    run_case(ctx, cap=600, win=512, pos=5999, splits=7, fresh=True, heads=8, kv=2)    # ragged spans, wrap inside a tile
+
+
+def test_global_attention_with_its_own_or_a_shared_cache(ctx):
+    run_case(ctx, cap=2048, win=2048, pos=1500, splits=32, fresh=True, heads=8, kv=2)
+    run_case(ctx, cap=2048, win=2048, pos=1500, splits=128, fresh=False, heads=8, kv=2)
+    run_case(ctx, cap=4096, win=4096, pos=4095, splits=4, fresh=True, heads=8, kv=2)  # several tiles per block
+
+
+def test_plain_configuration_of_the_benchmark(ctx):
+    """8 query heads, 2 kv heads, 4096 positions ~N(0,1), scale 1/sqrt(256), f16 out: global and sliding-512."""
+    run_case(ctx, cap=4096, win=4096, pos=4095, splits=64, fresh=False, heads=8, kv=2, plain=True, out_f16=True, scale=1 / 16.0)
+    run_case(ctx, cap=4096, win=512, pos=4095, splits=16, fresh=False, heads=8, kv=2, plain=True, out_f16=True, scale=1 / 16.0)
+    run_case(ctx, cap=4096, win=4096, pos=4095, splits=64, fresh=True, heads=8, kv=2, plain=True, out_f16=False, scale=1 / 16.0)
+
+
+def test_attention_rejects_bad_descriptors(ctx):
+    z = ctx.zeros(64)
+    a = tb.Attend(qkv=z.ptr, k_cache=z.ptr, v_cache=z.ptr, pos=z.ptr, cap=16, window=32, fresh=1, heads=8, kv_heads=2, scale=1.0, eps=1e-6,
+                  partial=z.ptr, count=z.ptr, splits=1, out=z.ptr, out_dtype=tb.F32)
+    with pytest.raises(tb.Error) as e:
+        ctx.attend_decode(a)  # window larger than the ring
+    assert e.value.status == 3
+    a.window, a.heads = 16, 6
+    with pytest.raises(tb.Error):
+        ctx.attend_decode(a)  # three query heads per kv head: no kernel

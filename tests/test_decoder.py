@@ -1,0 +1,148 @@
+"""The whole decode step on the GPU against the CPU forward pass (crates/tachyon/tests/model.rs:120-164): logits within
+tolerance, greedy tokens identical wherever the top-2 gap exceeds it, queued generation equal to single steps."""
+import numpy as np
+import pytest
+
+import oracle
+import tachyon_b200 as tb
+from oracle.model import OracleModel
+
+pytestmark = pytest.mark.gpu
+
+SEED = 1234
+
+
+def small_config(layers=3, ffn=2048, vocab=4096, window=16):
+    c = tb.gemma4_e4b_shape(layers=layers, ffn=ffn, vocab=vocab)
+    c.window, c.global_every = window, 3
+    return c
+
+
+def check_logits(got, want, gap, got_token, want_token):
+    scale = np.abs(want).max()
+    err = np.abs(got - want).max()
+    assert err <= 2e-3 * scale, (err, scale)
+    if gap > 4e-3 * scale:  # bit-exact pick once the top-2 gap clears the tolerance
+        assert got_token == want_token
+
+
+@pytest.fixture(scope="module")
+def models(ctx):
+    cfg = small_config()
+    dec = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True)
+    dec.fill_random(SEED)
+    dec.build()
+    ref = OracleModel(cfg, SEED, context=64, chunk=8)
+    yield cfg, dec, ref
+    dec.close()
+
+
+def test_steps_match_the_cpu_forward_through_a_ring_wrap(models):
+    cfg, dec, ref = models
+    dec.reset()
+    token = 17
+    for pos in range(40):  # window 16, ring 24: wraps; layer 2 is global
+        want_token, want_logits, want_hidden = ref.step(token, pos)
+        got_token = dec.step(token)
+        got_logits = dec.logits()
+        capped = cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap)
+        order = np.sort(capped)
+        check_logits(got_logits, want_logits, order[-1] - order[-2], got_token, want_token)
+        hid = dec.hidden()
+        assert np.abs(hid - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+        assert dec.position == pos + 1
+        token = (pos * 7919 + 13) % cfg.vocab  # a varied prompt: a tied random model would otherwise repeat itself
+
+
+def test_loaded_tensors_equal_the_device_fill(ctx, models):
+    cfg, dec, ref = models
+    other = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True)
+    for name, a in ref.tensors.items():
+        other.load(name, a)
+    other.build()
+    dec.reset()
+    for pos, token in enumerate([5, 99, 4000, 7]):
+        assert other.step(token) == dec.step(token)
+        assert np.array_equal(other.logits(), dec.logits()), "same bits from uploaded and generated weights"
+    with pytest.raises(tb.Error) as e:
+        other.load("3.qkv.w", np.zeros(4, np.int8))
+    assert e.value.status == 8  # no such tensor
+    with pytest.raises(tb.Error) as e:
+        other.load("0.qkv.w", np.zeros(4, np.int8))
+    assert e.value.status == 5  # wrong size
+    other.close()
+
+
+def test_queued_generation_equals_single_steps(models):
+    cfg, dec, ref = models
+    dec.reset()
+    single = []
+    token = 3
+    for _ in range(12):
+        token = dec.step(token)
+        single.append(token)
+    dec.reset()
+    dec.start(3)
+    queued = [dec.next_token() for _ in range(12)]
+    dec.stop()
+    assert queued == single
+    dec.reset()
+    chained = dec.run(3, 12)
+    assert list(chained) == single
+    # the decoder refuses to pass its context
+    dec.reset()
+    with pytest.raises(tb.Error) as e:
+        dec.run(3, 65)
+    assert e.value.status == 6
+
+
+def test_prefill_then_decode_equals_stepping(models):
+    cfg, dec, ref = models
+    prompt = [11, 22, 33, 44, 55, 66, 77, 88, 99]
+    dec.reset()
+    for t in prompt[:-1]:
+        dec.step(t)
+    a = dec.step(prompt[-1])
+    la = dec.logits()
+    dec.reset()
+    dec.prefill(prompt[:-1])
+    b = dec.step(prompt[-1])
+    assert a == b and np.array_equal(la, dec.logits())
+
+
+def test_overlap_off_gives_the_same_bits(ctx, models):
+    """Programmatic dependent launch only changes when kernels start, never what they compute."""
+    cfg, dec, ref = models
+    dec.reset()
+    want = list(dec.run(9, 10))
+    ctx.set_overlap(False)
+    try:
+        plain = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=False)
+        plain.fill_random(SEED)
+        plain.build()
+        assert list(plain.run(9, 10)) == want
+        plain.close()
+    finally:
+        ctx.set_overlap(True)
+
+
+def test_benchmark_width_ffn_and_a_prefilled_cache(ctx):
+    """One layer at the benchmark's FFN width (down projection over 16384 columns) on a synthetic 100-position cache."""
+    cfg = small_config(layers=2, ffn=16384, vocab=2048, window=512)
+    cfg.global_every = 2
+    dec = tb.Decoder(ctx, cfg, context=256, chunk=0, keep_logits=True)
+    dec.fill_random(77)
+    dec.build()
+    dec.fill_cache(5, 100)
+    ref = OracleModel(cfg, 77, context=256, chunk=0)
+    ref.fill_cache(5)
+    token = 1000
+    for pos in range(100, 104):
+        want_token, want_logits, _ = ref.step(token, pos)
+        got = dec.step(token)
+        capped = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+        check_logits(dec.logits(), want_logits, capped[-1] - capped[-2], got, want_token)
+        token = want_token
+    w, kv = dec.step_bytes()
+    assert w == sum(t.nbytes for n, t in ref.tensors.items() if n.endswith((".w", ".s")))
+    dec.close()
