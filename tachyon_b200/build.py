@@ -16,7 +16,7 @@ LIB = os.path.join(OUT_DIR, "libtachyon_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo",
+    "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "-cudart", "static",
 ]

@@ -59,6 +59,8 @@ int tb_context_new(int gpu, tb_context** out) {
     }
     const char* env = getenv("TACHYON_B200_NO_OVERLAP");
     ctx->pdl = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_NO_PREFETCH");
+    ctx->prefetch = !(env != nullptr && env[0] == '1');
     *out = ctx;
     return OK;
 }

@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, u
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // The hint is about weights no kernel writes: ask for them before waiting for the previous kernel.
+    if (tid == 0) prefetch_hint(p.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y);
     pdl_wait();
     pdl_launch_dependents();
 

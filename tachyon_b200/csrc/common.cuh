@@ -67,6 +67,27 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
 }
 
+// Issues the L2 prefetches of a hint (see Prefetch in internal.h) for the later kernel's blocks b = first, first +
+// step, ...  Called by one thread.
+template <typename P>
+__device__ __forceinline__ void prefetch_hint(const P& pf, uint32_t first, uint32_t step) {
+    if (pf.w == nullptr || pf.bytes == 0) return;
+    const uint32_t units = pf.rows / pf.unit;
+    for (uint32_t b = first; b < pf.grid; b += step) {
+        const uint32_t q0 = static_cast<uint32_t>((uint64_t)units * b / pf.grid) * pf.unit;
+        const uint32_t q1 = static_cast<uint32_t>((uint64_t)units * (b + 1) / pf.grid) * pf.unit;
+        const size_t total = (size_t)(q1 - q0) * pf.cols;
+        size_t lo = pf.skip < total ? pf.skip : total, hi = lo + pf.bytes < total ? lo + pf.bytes : total;
+        const char* base = reinterpret_cast<const char*>(pf.w) + (size_t)q0 * pf.cols;
+        for (size_t o = lo; o < hi; o += 16384) bulk_prefetch_l2(base + o, (uint32_t)(hi - o < 16384 ? hi - o : 16384));
+        const char* sb = reinterpret_cast<const char*>(pf.s) + (size_t)q0 * (pf.cols / 16);
+        lo = (lo / 16) & ~(size_t)15;
+        hi = ((hi / 16) + 15) & ~(size_t)15;
+        if (hi > total / 16) hi = total / 16;
+        for (size_t o = lo; o < hi; o += 16384) bulk_prefetch_l2(sb + o, (uint32_t)(hi - o < 16384 ? hi - o : 16384));
+    }
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its independent prologue / wait for the
 // kernels before this one to have finished and their writes to be visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -168,6 +168,16 @@ void layout(tb_decoder* d, char* base) {
     d->arena_bytes = t.end;
 }
 
+// Bytes of each block's range one hint covers.
+constexpr uint32_t PF = 192 * 1024;
+
+Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_t bytes) {
+    Prefetch pf;
+    if (!d->ctx->prefetch) return pf;
+    pf.w = m.w, pf.s = m.s, pf.rows = m.rows, pf.cols = m.cols, pf.unit = unit, pf.grid = (uint32_t)d->ctx->sms, pf.skip = skip, pf.bytes = bytes;
+    return pf;
+}
+
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols;
     d->launches++;
@@ -192,6 +202,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             cur = 1 - cur;
         }
         q.epi = EPI_F32, q.y = d->qkv;
+        q.pf = hint(d, L.o, 1, 0, PF);  // what follows attention
         TB_TRY(gemv(d, L.qkv, q));
 
         AttendParams a;
@@ -199,11 +210,13 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = 1;
         a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
+        a.pf = hint(d, L.gate_up, 2, 0, PF);
         TB_TRY(launch_attend(d->ctx, a));
         d->launches++;
 
         GemvParams o;
         o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
+        o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 
         GemvParams gu;
@@ -211,10 +224,12 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         gu.h_out = d->x[1 - cur];
         cur = 1 - cur;
         gu.epi = EPI_GEGLU, gu.y = d->g;
+        gu.pf = hint(d, L.down, 1, 0, PF);
         TB_TRY(gemv(d, L.gate_up, gu));
 
         GemvParams dn;
         dn.xmode = X_F32, dn.x = d->g, dn.epi = EPI_F32, dn.y = d->y;
+        dn.pf = i + 1 < c.layers ? hint(d, d->layers[i + 1].qkv, 1, 0, PF) : hint(d, d->embed, 1, 0, PF);
         TB_TRY(gemv(d, L.down, dn));
     }
     const Layer& P = d->layers[c.layers - 1];
@@ -224,6 +239,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
     h.epi = EPI_ARGMAX, h.y = d->settings.keep_logits ? d->logits : nullptr;
     h.best = d->best, h.count = reinterpret_cast<uint32_t*>(d->best + 1), h.state = d->state, h.token_out = token_word;
     h.trace = d->trace, h.trace_mask = TRACE - 1;
+    h.pf = hint(d, d->layers[0].qkv, 1, 0, PF);  // the next step's first matrix
     TB_TRY(gemv(d, d->embed, h));
     d->final_x = 1 - cur;
     return OK;

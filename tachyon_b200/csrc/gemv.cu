@@ -4,15 +4,17 @@
 // this kernel's prologue, GeGLU (geglu_q8, ptx/mod.rs:376-393) and the greedy pick (sample, ptx/sample.rs:387-417) as
 // its epilogues.
 //
-// Structure (one persistent block per SM, 8 consumer warps + 1 producer warp):
+// Structure (one persistent block per SM: 16 consumer warps + 1 producer warp):
 //  * every block owns a contiguous range of rows, so its weights are one contiguous byte range; the producer streams it
-//    through a ring of 16 KiB stages with one-dimensional bulk copies (cp.async.bulk) completing on mbarriers.  The
-//    weights do not depend on the previous kernel, so the producer starts before griddepcontrol.wait and the ring is
-//    full by the time the activations arrive;
-//  * the activation vector is split, per block of 32 values, into three byte planes of a 23-bit fixed-point number and a
-//    power-of-two multiplier; each consumer warp keeps the planes of its 2048-wide segment in registers, so a weight
-//    byte costs 3/4 of a dp4a and no conversion.  Block sums are exact integers, combined in f32 with the weight scale;
-//  * lanes reduce with shuffles; warps that share a row (cols > 2048) or a gate/up pair meet on a named barrier.
+//    through a ring of stages with one-dimensional bulk copies (cp.async.bulk) completing on mbarriers.  The weights do
+//    not depend on the previous kernel, so the producer starts before griddepcontrol.wait; when it has issued its last
+//    copy it asks the L2 to fetch the head of the next kernel's weights, so HBM keeps streaming across the boundary;
+//  * the activation vector is split once per block, per group of 32 values, into three byte planes of a 23-bit
+//    fixed-point number and a power-of-two multiplier, kept in shared memory and then in each warp's registers for
+//    its 2048-wide segment: a weight byte costs 3/4 of a dp4a and no conversion.  Block sums are exact integers,
+//    combined in f32 with the weight scale;
+//  * a warp takes one row (two when cols == 2048, which also puts a gate/up pair in one warp); lanes reduce with
+//    shuffles; warps that share a row (cols > 2048) meet on a named barrier.
 #include "common.cuh"
 #include "internal.h"
 
@@ -20,56 +22,53 @@ namespace tb {
 
 namespace {
 
-constexpr int STAGES = 6;
-constexpr int STAGE_W = 16384;  // weight bytes per stage
-constexpr int STAGE_S = 1024;   // scale bytes per stage (one f16 per 32 weights)
-constexpr int CONSUMERS = 8;    // consumer warps
-constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int CONSUMERS = 16;   // consumer warps
+constexpr int CTHREADS = CONSUMERS * 32;
+constexpr int THREADS = CTHREADS + 32;
 constexpr int SEG = 2048;       // columns one warp covers with its register-resident activation planes
+constexpr int SMEM_LIMIT = 230000;
 
-struct Smem {
-    uint8_t w[STAGES][STAGE_W];
-    uint8_t s[STAGES][STAGE_S];
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
-    float red[2][CONSUMERS];
-    float bestv[CONSUMERS];
-    uint32_t besti[CONSUMERS];
+// Rows a warp takes per stage: two when a row is one segment wide.
+constexpr int rows_per_warp(int wpr) { return wpr == 1 ? 2 : 1; }
+constexpr int stage_rows(int wpr) { return CONSUMERS / wpr * rows_per_warp(wpr); }
+constexpr int stage_w(int wpr) { return stage_rows(wpr) * wpr * SEG; }
+constexpr int stage_s(int wpr) { return stage_w(wpr) / 16; }
+constexpr int plane_bytes(int wpr) { return wpr * 64 * (96 + 4); }
+constexpr int tail_bytes() { return 16 * 8 + 2 * CONSUMERS * 4 + 2 * 2 * CONSUMERS * 4 + 4 * CONSUMERS * 4 + 64; }
+constexpr int stages(int wpr) {
+    const int n = (SMEM_LIMIT - plane_bytes(wpr) - tail_bytes()) / (stage_w(wpr) + stage_s(wpr));
+    return n > 8 ? 8 : n;
+}
+constexpr int smem_bytes(int wpr) { return stages(wpr) * (stage_w(wpr) + stage_s(wpr)) + plane_bytes(wpr) + tail_bytes(); }
+
+// Shared-memory carve-up, in this order: weight stages, scale stages, planes (hi, mid, lo words, multipliers),
+// barriers, reduction slots.
+template <int WPR>
+struct Layout {
+    static constexpr int NST = stages(WPR);
+    static constexpr int W = 0;
+    static constexpr int S = W + NST * stage_w(WPR);
+    static constexpr int HI = S + NST * stage_s(WPR);
+    static constexpr int MID = HI + WPR * 64 * 32;
+    static constexpr int LO = MID + WPR * 64 * 32;
+    static constexpr int MUL = LO + WPR * 64 * 32;
+    static constexpr int FULL = MUL + WPR * 64 * 4;
+    static constexpr int EMPTY = FULL + 8 * 8;
+    static constexpr int RED = EMPTY + 8 * 8;                 // float [2][CONSUMERS]
+    static constexpr int BESTV = RED + 2 * CONSUMERS * 4;      // float [2 * CONSUMERS]
+    static constexpr int BESTI = BESTV + 2 * CONSUMERS * 4;    // uint32 [2 * CONSUMERS]
+    static constexpr int SUMS = BESTI + 2 * CONSUMERS * 4;     // float [CONSUMERS][4]
 };
 
 // The three byte planes (signed high, unsigned middle and low) of 32 activations, and 2^(e-21): x ~ X * mul with
-// X = hi*65536 + mid*256 + lo, |X| <= 2^22.  Words 0..3 hold values 0..15, words 4..7 values 16..31.
+// X = hi*65536 + mid*256 + lo, |X| <= 2^22.
 struct Planes {
     uint32_t hi[8], mid[8], lo[8];
     float mul;
 };
 
-__device__ __forceinline__ void make_planes(const float (&v)[32], Planes& p, bool swap_halves) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(v[j]));
-    uint32_t eb = __float_as_uint(amax) >> 23;  // biased exponent of the largest magnitude
-    eb = min(eb, 254u);
-    const bool zero = eb < 22u;                 // below 2^-105: the block counts as zero
-    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);  // 2^(21 - e)
-    p.mul = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);           // 2^(e - 21)
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-        const int x0 = __float2int_rn(v[4 * k] * sc), x1 = __float2int_rn(v[4 * k + 1] * sc);
-        const int x2 = __float2int_rn(v[4 * k + 2] * sc), x3 = __float2int_rn(v[4 * k + 3] * sc);
-        p.hi[k] = __byte_perm(__byte_perm(x0, x1, 0x0062), __byte_perm(x2, x3, 0x0062), 0x5410);
-        p.mid[k] = __byte_perm(__byte_perm(x0, x1, 0x0051), __byte_perm(x2, x3, 0x0051), 0x5410);
-        p.lo[k] = __byte_perm(__byte_perm(x0, x1, 0x0040), __byte_perm(x2, x3, 0x0040), 0x5410);
-    }
-    if (swap_halves) {
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            uint32_t t;
-            t = p.hi[k], p.hi[k] = p.hi[k + 4], p.hi[k + 4] = t;
-            t = p.mid[k], p.mid[k] = p.mid[k + 4], p.mid[k + 4] = t;
-            t = p.lo[k], p.lo[k] = p.lo[k + 4], p.lo[k + 4] = t;
-        }
-    }
+__device__ __forceinline__ uint32_t pack_bytes(int x0, int x1, int x2, int x3, uint32_t sel) {
+    return __byte_perm(__byte_perm(x0, x1, sel), __byte_perm(x2, x3, sel), 0x5410);
 }
 
 // The dot product of 32 weights (two 16-byte chunks, in the order of the planes' words) with a block's planes, as a
@@ -85,6 +84,25 @@ __device__ __forceinline__ float block_dot(const uint4& a, const uint4& b, const
     h = dp4a_ss(b.z, p.hi[6], h), m = dp4a_su(b.z, p.mid[6], m), l = dp4a_su(b.z, p.lo[6], l);
     h = dp4a_ss(b.w, p.hi[7], h), m = dp4a_su(b.w, p.mid[7], m), l = dp4a_su(b.w, p.lo[7], l);
     return fmaf(static_cast<float>(h), 65536.0f, static_cast<float>(m * 256 + l));
+}
+
+// Used by the generic kernel: planes of 32 values held by one thread.
+__device__ __forceinline__ void make_planes(const float (&v)[32], Planes& p) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(v[j]));
+    uint32_t eb = min(__float_as_uint(amax) >> 23, 254u);  // biased exponent of the largest magnitude
+    const bool zero = eb < 22u;                            // below 2^-105: the block counts as zero
+    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);  // 2^(21 - e)
+    p.mul = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);           // 2^(e - 21)
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int x0 = __float2int_rn(v[4 * k] * sc), x1 = __float2int_rn(v[4 * k + 1] * sc);
+        const int x2 = __float2int_rn(v[4 * k + 2] * sc), x3 = __float2int_rn(v[4 * k + 3] * sc);
+        p.hi[k] = pack_bytes(x0, x1, x2, x3, 0x0062);
+        p.mid[k] = pack_bytes(x0, x1, x2, x3, 0x0051);
+        p.lo[k] = pack_bytes(x0, x1, x2, x3, 0x0040);
+    }
 }
 
 __device__ __forceinline__ void load32_f32(const float* base, float (&v)[32]) {
@@ -108,101 +126,134 @@ __device__ __forceinline__ void load32_f16(const __half* base, float (&v)[32]) {
     }
 }
 
-// The activation planes of blocks `b0` and `b0 + 32` of the input vector, for this lane.
-template <int XMODE>
-__device__ __forceinline__ void load_planes(const GemvParams& p, uint32_t b0, bool swap_halves, bool writer, Planes (&pl)[2]) {
-    float v[32];
+// The block-wide prologue: the 512 consumer threads turn the input vector into planes in shared memory.  Thread t
+// owns E = cols / 512 consecutive values; 32 / E consecutive lanes share a group of 32.
+template <int WPR, int XMODE>
+__device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t) {
+    using L = Layout<WPR>;
+    constexpr int E = 4 * WPR;
+    float v[E];
+    const size_t at = (size_t)t * E;
     if constexpr (XMODE == X_F16) {
+        const __half* x = static_cast<const __half*>(p.x) + at;
+        if constexpr (E == 4) {
+            const uint2 u = __ldcg(reinterpret_cast<const uint2*>(x));
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            load32_f16(static_cast<const __half*>(p.x) + (size_t)(b0 + 32 * i) * 32, v);
-            make_planes(v, pl[i], swap_halves);
+            for (int k = 0; k < E / 8; k++) {
+                const uint4 u = ld_cg_u4(x + 8 * k);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                    v[8 * k + 2 * j] = f.x, v[8 * k + 2 * j + 1] = f.y;
+                }
+            }
         }
     } else if constexpr (XMODE == X_F32) {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            load32_f32(static_cast<const float*>(p.x) + (size_t)(b0 + 32 * i) * 32, v);
-            make_planes(v, pl[i], swap_halves);
+        for (int k = 0; k < E / 4; k++) {
+            const float4 f = ld_cg_f4(static_cast<const float*>(p.x) + at + 4 * k);
+            v[4 * k] = f.x, v[4 * k + 1] = f.y, v[4 * k + 2] = f.z, v[4 * k + 3] = f.w;
         }
     } else {
-        // Residual step and RMS-norm over the whole vector (cols == 2048: the warp's lanes hold all of it).
-        // Sums in one pass, as the reference does (ptx/mod.rs:24-30): sum y^2, sum h^2, sum h*a, sum a^2 with a = y*w1;
-        // mean(h'^2) follows from them.
+        // Residual step and RMS-norm over the whole vector (cols == 2048, four values per thread).  One pass of sums, as
+        // the reference does (ptx/mod.rs:24-30): sum y^2, sum h^2, sum h*a, sum a^2 with a = y*w1; mean(h'^2) follows.
+        static_assert(XMODE != X_NORM || WPR == 1, "the norm prologue is built for 2048 columns");
+        const float4 h = ld_cg_f4(p.h + at);
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float sy = 0.0f;
+        if (p.yres != nullptr) {
+            const float4 y = ld_cg_f4(p.yres + at);
+            const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
+            a = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
+            sy = y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+        }
+        float4 w2 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (p.w2 != nullptr) w2 = __ldg(reinterpret_cast<const float4*>(p.w2 + at));
+        float sh = h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+        float sha = h.x * a.x + h.y * a.y + h.z * a.z + h.w * a.w;
+        float sa = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        sy = warp_sum(sy), sh = warp_sum(sh), sha = warp_sum(sha), sa = warp_sum(sa);
+        float4* sums = reinterpret_cast<float4*>(raw + L::SUMS);
+        if ((t & 31) == 0) sums[t >> 5] = make_float4(sy, sh, sha, sa);
+        named_bar_sync(1, CTHREADS);
+        sy = sh = sha = sa = 0.0f;
+#pragma unroll
+        for (int k = 0; k < CONSUMERS; k++) {
+            const float4 q = sums[k];
+            sy += q.x, sh += q.y, sha += q.z, sa += q.w;
+        }
         const float n = static_cast<float>(p.cols);
-        float ry = 0.0f, rh = 1.0f;
-        if (p.yres != nullptr || p.w2 != nullptr) {
-            float sy = 0.0f, sh = 0.0f, sha = 0.0f, sa = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const size_t at = (size_t)(b0 + 32 * i) * 32;
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const float4 h = ld_cg_f4(p.h + at + 4 * k);
-                    const float hv[4] = {h.x, h.y, h.z, h.w};
-                    float av[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (p.yres != nullptr) {
-                        const float4 y = ld_cg_f4(p.yres + at + 4 * k);
-                        const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at + 4 * k));
-                        av[0] = y.x * w.x, av[1] = y.y * w.y, av[2] = y.z * w.z, av[3] = y.w * w.w;
-                        sy += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) sh = fmaf(hv[j], hv[j], sh), sha = fmaf(hv[j], av[j], sha), sa = fmaf(av[j], av[j], sa);
-                }
-            }
-            sy = warp_sum(sy), sh = warp_sum(sh), sha = warp_sum(sha), sa = warp_sum(sa);
-            if (p.yres != nullptr) ry = rsqrtf(sy / n + p.eps);
-            const float hs = p.yres != nullptr ? p.hscale : 1.0f;  // without a residual the state passes through unscaled
-            const float sq = hs * hs * (sh + 2.0f * ry * sha + ry * ry * sa);
-            if (p.w2 != nullptr) rh = rsqrtf(fmaxf(sq, 0.0f) / n + p.eps);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const size_t at = (size_t)(b0 + 32 * i) * 32;
-            load32_f32(p.h + at, v);
-            if (p.yres != nullptr) {
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const float4 y = ld_cg_f4(p.yres + at + 4 * k);
-                    const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at + 4 * k));
-                    v[4 * k] = fmaf(y.x * ry, w.x, v[4 * k]) * p.hscale;
-                    v[4 * k + 1] = fmaf(y.y * ry, w.y, v[4 * k + 1]) * p.hscale;
-                    v[4 * k + 2] = fmaf(y.z * ry, w.z, v[4 * k + 2]) * p.hscale;
-                    v[4 * k + 3] = fmaf(y.w * ry, w.w, v[4 * k + 3]) * p.hscale;
-                }
-            }
-            if (writer && p.h_out != nullptr) {
-#pragma unroll
-                for (int k = 0; k < 8; k++) *reinterpret_cast<float4*>(p.h_out + at + 4 * k) = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
-            }
-            if (p.w2 != nullptr) {
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const float4 w = __ldg(reinterpret_cast<const float4*>(p.w2 + at + 4 * k));
-                    v[4 * k] *= rh * w.x, v[4 * k + 1] *= rh * w.y, v[4 * k + 2] *= rh * w.z, v[4 * k + 3] *= rh * w.w;
-                }
-            }
-            make_planes(v, pl[i], swap_halves);
-        }
+        const float ry = p.yres != nullptr ? rsqrtf(sy / n + p.eps) : 0.0f;
+        const float hs = p.yres != nullptr ? p.hscale : 1.0f;  // without a residual the state passes through unscaled
+        const float sq = hs * hs * (sh + 2.0f * ry * sha + ry * ry * sa);
+        const float rh = p.w2 != nullptr ? rsqrtf(fmaxf(sq, 0.0f) / n + p.eps) : 1.0f;
+        v[0] = fmaf(a.x, ry, h.x) * hs, v[1] = fmaf(a.y, ry, h.y) * hs, v[2] = fmaf(a.z, ry, h.z) * hs, v[3] = fmaf(a.w, ry, h.w) * hs;
+        if (blockIdx.x == 0 && p.h_out != nullptr) *reinterpret_cast<float4*>(p.h_out + at) = make_float4(v[0], v[1], v[2], v[3]);
+        v[0] *= rh * w2.x, v[1] *= rh * w2.y, v[2] *= rh * w2.z, v[3] *= rh * w2.w;
     }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < E; j++) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = 16 / E; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    uint32_t eb = min(__float_as_uint(amax) >> 23, 254u);
+    const bool zero = eb < 22u;
+    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);
+    const int block = t * E / 32, word = (t * E % 32) / 4;
+    uint32_t* hi = reinterpret_cast<uint32_t*>(raw + L::HI) + block * 8 + word;
+    uint32_t* mid = reinterpret_cast<uint32_t*>(raw + L::MID) + block * 8 + word;
+    uint32_t* lo = reinterpret_cast<uint32_t*>(raw + L::LO) + block * 8 + word;
+#pragma unroll
+    for (int k = 0; k < E / 4; k++) {
+        const int x0 = __float2int_rn(v[4 * k] * sc), x1 = __float2int_rn(v[4 * k + 1] * sc);
+        const int x2 = __float2int_rn(v[4 * k + 2] * sc), x3 = __float2int_rn(v[4 * k + 3] * sc);
+        hi[k] = pack_bytes(x0, x1, x2, x3, 0x0062);
+        mid[k] = pack_bytes(x0, x1, x2, x3, 0x0051);
+        lo[k] = pack_bytes(x0, x1, x2, x3, 0x0040);
+    }
+    if (word == 0) reinterpret_cast<float*>(raw + L::MUL)[block] = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);
+}
+
+// Planes of block `b` from shared memory; `first` picks which 16-byte half lands in words 0..3 (it matches the
+// order the lane loads the weights in, and spreads both loads over all banks).
+template <int WPR>
+__device__ __forceinline__ void fetch_planes(const uint8_t* raw, int b, int first, Planes& pl) {
+    using L = Layout<WPR>;
+    const uint4* hi = reinterpret_cast<const uint4*>(raw + L::HI) + b * 2;
+    const uint4* mid = reinterpret_cast<const uint4*>(raw + L::MID) + b * 2;
+    const uint4* lo = reinterpret_cast<const uint4*>(raw + L::LO) + b * 2;
+    const uint4 h0 = hi[first], h1 = hi[1 - first], m0 = mid[first], m1 = mid[1 - first], l0 = lo[first], l1 = lo[1 - first];
+    pl.hi[0] = h0.x, pl.hi[1] = h0.y, pl.hi[2] = h0.z, pl.hi[3] = h0.w, pl.hi[4] = h1.x, pl.hi[5] = h1.y, pl.hi[6] = h1.z, pl.hi[7] = h1.w;
+    pl.mid[0] = m0.x, pl.mid[1] = m0.y, pl.mid[2] = m0.z, pl.mid[3] = m0.w, pl.mid[4] = m1.x, pl.mid[5] = m1.y, pl.mid[6] = m1.z, pl.mid[7] = m1.w;
+    pl.lo[0] = l0.x, pl.lo[1] = l0.y, pl.lo[2] = l0.z, pl.lo[3] = l0.w, pl.lo[4] = l1.x, pl.lo[5] = l1.y, pl.lo[6] = l1.z, pl.lo[7] = l1.w;
+    pl.mul = reinterpret_cast<const float*>(raw + L::MUL)[b];
 }
 
 template <int WPR, int XMODE, int EPI>
-__global__ void __launch_bounds__(THREADS, 2) gemv_q8_kernel(const GemvParams p, uint32_t* status) {
+__global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p, uint32_t* status) {
     extern __shared__ __align__(128) uint8_t raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(raw);
-    constexpr int ROWS = CONSUMERS / WPR;                  // rows per stage
-    constexpr int UNIT = (EPI == EPI_GEGLU) ? 2 : 1;       // rows that stay in one block
-    constexpr int GROUP = (EPI == EPI_GEGLU) ? 2 : WPR;    // warps that produce one output together
+    using L = Layout<WPR>;
+    constexpr int NST = L::NST;
+    constexpr int RPW = rows_per_warp(WPR);
+    constexpr int ROWS = stage_rows(WPR);
+    constexpr int SW = stage_w(WPR), SS = stage_s(WPR);
+    constexpr int UNIT = (EPI == EPI_GEGLU) ? 2 : 1;  // rows that stay in one block
+    static_assert(EPI != EPI_GEGLU || RPW == 2, "a gate/up pair is the two rows of one warp");
     const uint32_t K = p.cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t units = p.rows / UNIT;
     const uint32_t r0 = static_cast<uint32_t>((uint64_t)units * blockIdx.x / gridDim.x) * UNIT;
     const uint32_t r1 = static_cast<uint32_t>((uint64_t)units * (blockIdx.x + 1) / gridDim.x) * UNIT;
     const uint32_t nst = (r1 - r0 + ROWS - 1) / ROWS;
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + L::FULL);
+    uint64_t* empty = reinterpret_cast<uint64_t*>(raw + L::EMPTY);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; i++) mbar_init(&sm.full[i], 1), mbar_init(&sm.empty[i], CONSUMERS);
+        for (int i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], CONSUMERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -211,88 +262,110 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q8_kernel(const GemvParams p,
     if (warp == CONSUMERS) {
         // Producer: one thread streams this block's rows.  Nothing it reads is written by another kernel.
         if (lane == 0) {
-            bool ok = true;
-            for (uint32_t i = 0; i < nst && ok; i++) {
-                const uint32_t s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&sm.empty[s], ((i / STAGES) - 1) & 1)) {
+            for (uint32_t i = 0; i < nst; i++) {
+                const uint32_t s = i % NST;
+                if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1)) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
-                    ok = false;
                     break;
                 }
                 const uint32_t row = r0 + i * ROWS, here = min((uint32_t)ROWS, r1 - row);
                 const uint32_t bw = here * K, bs = here * (K / 16);
-                mbar_expect_tx(&sm.full[s], bw + bs);
-                bulk_load(sm.w[s], p.w + (size_t)row * K, bw, &sm.full[s]);
-                bulk_load(sm.s[s], p.s + (size_t)row * (K / 32), bs, &sm.full[s]);
+                mbar_expect_tx(&full[s], bw + bs);
+                bulk_load(raw + L::W + s * SW, p.w + (size_t)row * K, bw, &full[s]);
+                bulk_load(raw + L::S + s * SS, p.s + (size_t)row * (K / 32), bs, &full[s]);
             }
             pdl_launch_dependents();
+            // Ask the L2 for what the next kernel's block with this index will stream first.
+            prefetch_hint(p.pf, blockIdx.x, gridDim.x);
         }
         return;
     }
 
     // Consumers.  Everything below may read what the previous kernel wrote.
     pdl_wait();
-    const int seg = warp % WPR, rin = warp / WPR;  // the warp's column segment, and its row within a stage
-    const bool sw = (lane >> 2) & 1;               // which 16-byte half of its blocks the lane loads first (bank spread)
+    build_planes<WPR, XMODE>(p, raw, threadIdx.x);
+    named_bar_sync(1, CTHREADS);
+    const int seg = warp % WPR, grp = warp / WPR;  // the warp's column segment, and its row group within a stage
+    const int first = (lane >> 2) & 1;             // which 16-byte half of its blocks the lane loads first (bank spread)
     Planes pl[2];
-    load_planes<XMODE>(p, (uint32_t)seg * 64 + lane, sw, blockIdx.x == 0 && warp == 0, pl);
+    fetch_planes<WPR>(raw, seg * 64 + lane, first, pl[0]);
+    fetch_planes<WPR>(raw, seg * 64 + lane + 32, first, pl[1]);
 
     float bestv = -INFINITY;
     uint32_t besti = 0xffffffffu;
     bool ok = true;
     for (uint32_t i = 0; i < nst; i++) {
-        const uint32_t s = i % STAGES;
-        if (ok && !mbar_wait(&sm.full[s], (i / STAGES) & 1)) {
+        const uint32_t s = i % NST;
+        if (ok && !mbar_wait(&full[s], (i / NST) & 1)) {
             atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
             ok = false;
         }
-        const uint32_t row = r0 + i * ROWS + rin;
-        float v = 0.0f;
-        if (ok && row < r1) {
-            const uint8_t* wr = sm.w[s] + (size_t)rin * K + seg * SEG;
-            const __half* sr = reinterpret_cast<const __half*>(sm.s[s]) + rin * (K / 32) + seg * 64;
-            const uint4 a0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + (sw ? 1 : 0)) * 16);
-            const uint4 b0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + (sw ? 0 : 1)) * 16);
-            const uint4 a1 = *reinterpret_cast<const uint4*>(wr + 1024 + (2 * lane + (sw ? 1 : 0)) * 16);
-            const uint4 b1 = *reinterpret_cast<const uint4*>(wr + 1024 + (2 * lane + (sw ? 0 : 1)) * 16);
-            const float s0 = __half2float(sr[lane]) * pl[0].mul, s1 = __half2float(sr[lane + 32]) * pl[1].mul;
-            v = block_dot(a0, b0, pl[0]) * s0;
-            v = fmaf(block_dot(a1, b1, pl[1]), s1, v);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.empty[s]);
-        v = warp_sum(v);
-        if constexpr (GROUP > 1) {
-            if (lane == 0) sm.red[i & 1][warp] = v;
-            named_bar_sync(1 + warp / GROUP, GROUP * 32);
-            if (warp % GROUP != 0) continue;
-            if constexpr (EPI == EPI_GEGLU) {
-                v = gelu_tanh(sm.red[i & 1][warp]) * sm.red[i & 1][warp + 1];
-            } else {
-                v = 0.0f;
+        const uint32_t row = r0 + i * ROWS + grp * RPW;  // the warp's first row of this stage
+        float v[RPW];
 #pragma unroll
-                for (int j = 0; j < GROUP; j++) v += sm.red[i & 1][warp + j];
+        for (int j = 0; j < RPW; j++) {
+            v[j] = 0.0f;
+            if (ok && row + j < r1) {
+                const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * K + seg * SEG;
+                const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 32) + seg * 64;
+                const uint4 a0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + first) * 16);
+                const uint4 b0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + 1 - first) * 16);
+                const uint4 a1 = *reinterpret_cast<const uint4*>(wr + 1024 + (2 * lane + first) * 16);
+                const uint4 b1 = *reinterpret_cast<const uint4*>(wr + 1024 + (2 * lane + 1 - first) * 16);
+                const float s0 = __half2float(sr[lane]) * pl[0].mul, s1 = __half2float(sr[lane + 32]) * pl[1].mul;
+                v[j] = fmaf(block_dot(a1, b1, pl[1]), s1, block_dot(a0, b0, pl[0]) * s0);
             }
         }
-        if (lane == 0 && row < r1) {
-            if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[row] = v;
-            if constexpr (EPI == EPI_F16) static_cast<__half*>(p.y)[row] = __float2half_rn(v);
-            if constexpr (EPI == EPI_GEGLU) static_cast<float*>(p.y)[row / 2] = v;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+        float r;           // row total: in lane 0 (and, with two rows, the second row's in lane 16)
+        uint32_t out_row;  // the row this lane would write
+        if constexpr (RPW == 2) {
+            // Both rows in five exchanges: the halves of the warp trade one value, then each half reduces its own.
+            const bool upper = lane & 16;
+            r = (upper ? v[1] : v[0]) + __shfl_xor_sync(0xffffffffu, upper ? v[0] : v[1], 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+            out_row = row + (upper ? 1 : 0);
+            if constexpr (EPI == EPI_GEGLU) {
+                const float up = __shfl_sync(0xffffffffu, r, 16);
+                r = gelu_tanh(r) * up;
+            }
+        } else {
+            r = warp_sum(v[0]);
+            out_row = row;
+        }
+        if constexpr (WPR > 1) {
+            float* red = reinterpret_cast<float*>(raw + L::RED) + (i & 1) * CONSUMERS;
+            if (lane == 0) red[warp] = r;
+            named_bar_sync(2 + grp, WPR * 32);
+            if (seg != 0) continue;
+            r = 0.0f;
+#pragma unroll
+            for (int j = 0; j < WPR; j++) r += red[warp + j];
+        }
+        const bool writer = (EPI == EPI_GEGLU || RPW == 1) ? lane == 0 : (lane & 15) == 0;
+        if (writer && out_row < r1) {
+            if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[out_row] = r;
+            if constexpr (EPI == EPI_F16) static_cast<__half*>(p.y)[out_row] = __float2half_rn(r);
+            if constexpr (EPI == EPI_GEGLU) static_cast<float*>(p.y)[out_row / 2] = r;
             if constexpr (EPI == EPI_ARGMAX) {
-                if (p.y != nullptr) static_cast<float*>(p.y)[row] = v;
-                if (v > bestv) bestv = v, besti = row;
+                if (p.y != nullptr) static_cast<float*>(p.y)[out_row] = r;
+                if (r > bestv) bestv = r, besti = out_row;
             }
         }
     }
 
     if constexpr (EPI == EPI_ARGMAX) {
         // Largest value, lowest row among equals (ptx/sample.rs:91-97): the key orders by value, then by inverted row.
-        if (lane == 0) sm.bestv[warp] = bestv, sm.besti[warp] = besti;
-        named_bar_sync(15, CONSUMERS * 32);
+        float* sbv = reinterpret_cast<float*>(raw + L::BESTV);
+        uint32_t* sbi = reinterpret_cast<uint32_t*>(raw + L::BESTI);
+        if ((lane & 15) == 0) sbv[2 * warp + (lane >> 4)] = bestv, sbi[2 * warp + (lane >> 4)] = besti;
+        named_bar_sync(1, CTHREADS);
         if (threadIdx.x == 0) {
             unsigned long long key = 0;
-            for (int j = 0; j < CONSUMERS; j++) {
-                const unsigned long long k = ((unsigned long long)float_key(sm.bestv[j]) << 32) | (0xffffffffu - sm.besti[j]);
+            for (int j = 0; j < 2 * CONSUMERS; j++) {
+                const unsigned long long k = ((unsigned long long)float_key(sbv[j]) << 32) | (0xffffffffu - sbi[j]);
                 key = k > key ? k : key;
             }
             atomicMax(p.best, key);
@@ -326,7 +399,7 @@ __global__ void __launch_bounds__(256) gemv_q8_generic(const GemvParams p) {
         if constexpr (XMODE == X_F16) load32_f16(static_cast<const __half*>(p.x) + (size_t)b * 32, v);
         else load32_f32(static_cast<const float*>(p.x) + (size_t)b * 32, v);
         Planes pl;
-        make_planes(v, pl, false);
+        make_planes(v, pl);
         // Rows of a matrix whose width is not a multiple of 16 bytes... cols % 32 == 0, so 16-byte loads stay aligned.
         const uint4* wp = reinterpret_cast<const uint4*>(p.w + (size_t)row * p.cols + (size_t)b * 32);
         const uint4 a = __ldg(wp), c = __ldg(wp + 1);
@@ -344,16 +417,15 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     auto kernel = gemv_q8_kernel<WPR, XMODE, EPI>;
     static bool configured[16] = {};  // per device ordinal
     if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(WPR)));
         configured[ctx->gpu & 15] = true;
     }
-    constexpr uint32_t ROWS = CONSUMERS / WPR;
+    constexpr uint32_t ROWS = stage_rows(WPR);
     constexpr uint32_t UNIT = (EPI == EPI_GEGLU) ? 2 : 1;
-    // The argmax epilogue counts blocks, so its grid must not depend on anything but the shape.
     uint32_t grid = (uint32_t)ctx->sms;
     const uint32_t most = (p.rows / UNIT * UNIT + ROWS - 1) / ROWS;
     if (grid > most) grid = most > 0 ? most : 1;
-    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), sizeof(Smem), true, p, ctx->status));
+    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR), true, p, ctx->status));
     return OK;
 }
 
@@ -381,7 +453,7 @@ int dispatch_staged(tb_context* ctx, const GemvParams& p) {
 
 }  // namespace
 
-size_t gemv_smem_bytes() { return sizeof(Smem); }
+size_t gemv_smem_bytes() { return smem_bytes(1); }
 
 int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if (p.rows == 0 || p.cols == 0 || p.cols % 32 != 0) return fail(OUT_OF_RANGE, "gemv: cols must be a positive multiple of 32");

@@ -15,6 +15,7 @@ struct tb_context {
     uint32_t* status = nullptr;       // device word: first kernel-side error (tb::ERR_*), 0 when fine
     uint32_t* status_host = nullptr;  // pinned mirror used by tb_status
     bool pdl = true;                  // launch kernels with programmatic stream serialization
+    bool prefetch = true;             // give kernels L2 hints about the next kernel's weights
 };
 
 namespace tb {
@@ -51,6 +52,15 @@ int cuda_fail(cudaError_t e, const char* where);
 enum XMode : int { X_F16 = 0, X_F32 = 1, X_NORM = 2 };
 enum Epilogue : int { EPI_F32 = 0, EPI_F16 = 1, EPI_GEGLU = 2, EPI_ARGMAX = 3 };
 
+// A hint about the matrix a later kernel will stream: that kernel runs `grid` blocks, block b owning the rows
+// [units*b/grid, units*(b+1)/grid) * unit with units = rows/unit.  A kernel given the hint asks the L2 for bytes
+// [skip, skip + bytes) of each block's range (weights, and the matching scales) once its own loads are issued.
+struct Prefetch {
+    const int8_t* w = nullptr;
+    const __half* s = nullptr;
+    uint32_t rows = 0, cols = 0, unit = 1, grid = 1, skip = 0, bytes = 0;
+};
+
 struct GemvParams {
     const int8_t* w = nullptr;    // [rows, cols] codes
     const __half* s = nullptr;    // [rows, cols/32] scales
@@ -74,6 +84,7 @@ struct GemvParams {
     uint32_t* token_out = nullptr;
     uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
     uint32_t trace_mask = 0;
+    Prefetch pf;                  // optional hint for the L2
 };
 
 int launch_gemv(tb_context* ctx, const GemvParams& p);
@@ -95,6 +106,7 @@ struct AttendParams {
     uint32_t splits = 1;           // blocks per kv head (upper bound on the split actually used)
     void* out = nullptr;           // [heads*256] f32 or f16
     int out_f16 = 0;
+    Prefetch pf;                   // optional hint for the L2
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
