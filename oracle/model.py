@@ -49,7 +49,7 @@ class OracleModel:
             vs = [vec(f"{i}.q_norm", b + 8, D, 0.15, 0.35), vec(f"{i}.k_norm", b + 9, D, 0.15, 0.35),
                   vec(f"{i}.input_layernorm", b + 10, H, 0.5, 1.5), vec(f"{i}.post_attention_layernorm", b + 11, H, 0.5, 1.5),
                   vec(f"{i}.pre_feedforward_layernorm", b + 12, H, 0.5, 1.5), vec(f"{i}.post_feedforward_layernorm", b + 13, H, 0.5, 1.5)]
-            scalar = vec(f"{i}.layer_scalar", b + 14, 1, 0.5, 1.0)
+            scalar = vec(f"{i}.layer_scalar", b + 14, 1, 0.95, 1.0)
             is_global = bool(cfg.global_every) and (i + 1) % cfg.global_every == 0
             cap = context if is_global else cfg.window + chunk
             kc, vc = np.zeros((cfg.kv_heads, cap, D), np.uint16), np.zeros((cfg.kv_heads, cap, D), np.uint16)

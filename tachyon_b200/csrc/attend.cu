@@ -187,13 +187,34 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, u
                     kv[2 * j] = f.x, kv[2 * j + 1] = f.y;
                 }
             }
+            float sc[G];
 #pragma unroll
             for (int h = 0; h < G; h++) {
-                float s = 0.0f;
+                sc[h] = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; i++) s = fmaf(qr[h][i], kv[i], s);
-                s = warp_sum(s);
-                if (lane == 0) sm.p[r][h] = ok ? s : 0.0f;
+                for (int i = 0; i < 8; i++) sc[h] = fmaf(qr[h][i], kv[i], sc[h]);
+            }
+            // Reduce the G sums together: the halves (then quarters) of the warp trade values, so head h ends up summed
+            // in the lanes whose top bits spell h.
+            float v;
+            if constexpr (G == 4) {
+                const bool b4 = lane & 16, b3 = lane & 8;
+                const float k0 = (b4 ? sc[2] : sc[0]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[0] : sc[2], 16);
+                const float k1 = (b4 ? sc[3] : sc[1]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[1] : sc[3], 16);
+                v = (b3 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b3 ? k0 : k1, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                if ((lane & 7) == 0) sm.p[r][lane >> 3] = ok ? v : 0.0f;
+            } else if constexpr (G == 2) {
+                const bool b4 = lane & 16;
+                v = (b4 ? sc[1] : sc[0]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[0] : sc[1], 16);
+#pragma unroll
+                for (int o2 = 8; o2 > 0; o2 >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o2);
+                if ((lane & 15) == 0) sm.p[r][lane >> 4] = ok ? v : 0.0f;
+            } else {
+                v = warp_sum(sc[0]);
+                if (lane == 0) sm.p[r][0] = ok ? v : 0.0f;
             }
         }
         __syncthreads();
@@ -249,27 +270,46 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, u
     __syncthreads();
     if (sm.last == 0) return;
     __threadfence();
-    // Combine (attend.rs:371-405): weights 2^(m_s - M) over the splits that ran.
+    // Combine (attend.rs:371-405): weights 2^(m_s - M) over the splits that ran.  Every load of a phase is issued
+    // before its first use, so the phases cost one trip to the L2 each, not one per split.
     const float* base = p.partial + (size_t)g * p.splits * stride;
-    float M[G], L[G], o[G];
-#pragma unroll
-    for (int h = 0; h < G; h++) M[h] = -INFINITY, L[h] = 0.0f, o[h] = 0.0f;
-    for (uint32_t s = 0; s < used; s++) {
-#pragma unroll
-        for (int h = 0; h < G; h++) M[h] = fmaxf(M[h], __ldcg(base + (size_t)s * stride + h));
-    }
-    for (uint32_t s = 0; s < used; s++) {
-        const float* ps = base + (size_t)s * stride;
-#pragma unroll
-        for (int h = 0; h < G; h++) {
-            const float wgt = exp2f(__ldcg(ps + h) - M[h]);
-            L[h] = fmaf(wgt, __ldcg(ps + G + h), L[h]);
-            o[h] = fmaf(wgt, __ldcg(ps + 2 * G + h * D + tid), o[h]);
+    float* wts = reinterpret_cast<float*>(&sm.k[0][0]);  // [used][G], the tile is no longer needed
+    for (uint32_t i = tid; i < used * G; i += THREADS) wts[i] = __ldcg(base + (size_t)(i / G) * stride + i % G);
+    __syncthreads();
+    if (warp < G) {
+        float M = -INFINITY, L = 0.0f;
+        for (uint32_t s2 = lane; s2 < used; s2 += 32) M = fmaxf(M, wts[s2 * G + warp]);
+        M = warp_max(M);
+        for (uint32_t s2 = lane; s2 < used; s2 += 32) {
+            const float wgt = exp2f(wts[s2 * G + warp] - M);
+            L = fmaf(wgt, __ldcg(base + (size_t)s2 * stride + G + warp), L);
+            wts[s2 * G + warp] = wgt;
         }
+        L = warp_sum(L);
+        if (lane == 0) sm.lrun[warp] = L;
     }
+    __syncthreads();
+    float o[G];
+#pragma unroll
+    for (int h = 0; h < G; h++) o[h] = 0.0f;
+    uint32_t s2 = 0;
+    for (; s2 + 4 <= used; s2 += 4) {
+        float t[4][G];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int h = 0; h < G; h++) t[u][h] = __ldcg(base + (size_t)(s2 + u) * stride + 2 * G + h * D + tid);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int h = 0; h < G; h++) o[h] = fmaf(wts[(s2 + u) * G + h], t[u][h], o[h]);
+    }
+    for (; s2 < used; s2++)
+#pragma unroll
+        for (int h = 0; h < G; h++) o[h] = fmaf(wts[s2 * G + h], __ldcg(base + (size_t)s2 * stride + 2 * G + h * D + tid), o[h]);
 #pragma unroll
     for (int h = 0; h < G; h++) {
-        const float r = o[h] / L[h];
+        const float r = o[h] / sm.lrun[h];
         const size_t at = (size_t)(g * G + h) * D + tid;
         if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(r);
         else static_cast<float*>(p.out)[at] = r;
@@ -289,7 +329,7 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
     const uint32_t group = p.heads / p.kv_heads;
     if (group != 1 && group != 2 && group != 4) return fail(UNSUPPORTED, "attend: 1, 2 or 4 query heads per key-value head");
     if (p.cap == 0 || p.window == 0 || p.window > p.cap) return fail(OUT_OF_RANGE, "attend: need 0 < window <= cap");
-    if (p.splits == 0 || p.splits > 65535) return fail(OUT_OF_RANGE, "attend: splits out of range");
+    if (p.splits == 0 || p.splits > 1024) return fail(OUT_OF_RANGE, "attend: splits out of range");
     if (!p.qkv || !p.kc || !p.vc || !p.pos || !p.out || !p.count || (p.splits > 1 && !p.partial)) return fail(OUT_OF_RANGE, "attend: null argument");
     if ((p.q_norm == nullptr) != (p.k_norm == nullptr)) return fail(OUT_OF_RANGE, "attend: q_norm and k_norm go together");
     if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.qkv)) & 15) return fail(OUT_OF_RANGE, "attend: buffers must be 16-byte aligned");

@@ -126,42 +126,48 @@ __device__ __forceinline__ void load32_f16(const __half* base, float (&v)[32]) {
     }
 }
 
-// The block-wide prologue: the 512 consumer threads turn the input vector into planes in shared memory.  Thread t
-// owns E = cols / 512 consecutive values; 32 / E consecutive lanes share a group of 32.
+// Four consecutive activations -> one word of each plane.  The eight lanes that share a group of 32 agree on its
+// exponent with three exchanges.
+template <int WPR>
+__device__ __forceinline__ void store_planes(uint8_t* raw, int idx, float v0, float v1, float v2, float v3) {
+    using L = Layout<WPR>;
+    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const uint32_t eb = min(__float_as_uint(amax) >> 23, 254u);  // biased exponent of the largest magnitude
+    const bool zero = eb < 22u;                                  // below 2^-105: the group counts as zero
+    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);  // 2^(21 - e)
+    const int x0 = __float2int_rn(v0 * sc), x1 = __float2int_rn(v1 * sc), x2 = __float2int_rn(v2 * sc), x3 = __float2int_rn(v3 * sc);
+    reinterpret_cast<uint32_t*>(raw + L::HI)[idx] = pack_bytes(x0, x1, x2, x3, 0x0062);
+    reinterpret_cast<uint32_t*>(raw + L::MID)[idx] = pack_bytes(x0, x1, x2, x3, 0x0051);
+    reinterpret_cast<uint32_t*>(raw + L::LO)[idx] = pack_bytes(x0, x1, x2, x3, 0x0040);
+    if ((idx & 7) == 0) reinterpret_cast<float*>(raw + L::MUL)[idx >> 3] = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);  // 2^(e - 21)
+}
+
+// The block-wide prologue: the 512 consumer threads turn the input vector into planes in shared memory, four
+// consecutive values per thread and pass (coalesced), cols / 2048 passes.
 template <int WPR, int XMODE>
 __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t) {
     using L = Layout<WPR>;
-    constexpr int E = 4 * WPR;
-    float v[E];
-    const size_t at = (size_t)t * E;
     if constexpr (XMODE == X_F16) {
-        const __half* x = static_cast<const __half*>(p.x) + at;
-        if constexpr (E == 4) {
-            const uint2 u = __ldcg(reinterpret_cast<const uint2*>(x));
+#pragma unroll
+        for (int j = 0; j < WPR; j++) {
+            const int idx = j * CTHREADS + t;
+            const uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(p.x) + (size_t)idx * 4));
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-            v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
-        } else {
-#pragma unroll
-            for (int k = 0; k < E / 8; k++) {
-                const uint4 u = ld_cg_u4(x + 8 * k);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                    v[8 * k + 2 * j] = f.x, v[8 * k + 2 * j + 1] = f.y;
-                }
-            }
+            store_planes<WPR>(raw, idx, a.x, a.y, b.x, b.y);
         }
     } else if constexpr (XMODE == X_F32) {
+        float4 f[WPR];
 #pragma unroll
-        for (int k = 0; k < E / 4; k++) {
-            const float4 f = ld_cg_f4(static_cast<const float*>(p.x) + at + 4 * k);
-            v[4 * k] = f.x, v[4 * k + 1] = f.y, v[4 * k + 2] = f.z, v[4 * k + 3] = f.w;
-        }
+        for (int j = 0; j < WPR; j++) f[j] = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)(j * CTHREADS + t) * 4);
+#pragma unroll
+        for (int j = 0; j < WPR; j++) store_planes<WPR>(raw, j * CTHREADS + t, f[j].x, f[j].y, f[j].z, f[j].w);
     } else {
         // Residual step and RMS-norm over the whole vector (cols == 2048, four values per thread).  One pass of sums, as
         // the reference does (ptx/mod.rs:24-30): sum y^2, sum h^2, sum h*a, sum a^2 with a = y*w1; mean(h'^2) follows.
         static_assert(XMODE != X_NORM || WPR == 1, "the norm prologue is built for 2048 columns");
+        const size_t at = (size_t)t * 4;
         const float4 h = ld_cg_f4(p.h + at);
         float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float sy = 0.0f;
@@ -191,31 +197,10 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         const float hs = p.yres != nullptr ? p.hscale : 1.0f;  // without a residual the state passes through unscaled
         const float sq = hs * hs * (sh + 2.0f * ry * sha + ry * ry * sa);
         const float rh = p.w2 != nullptr ? rsqrtf(fmaxf(sq, 0.0f) / n + p.eps) : 1.0f;
-        v[0] = fmaf(a.x, ry, h.x) * hs, v[1] = fmaf(a.y, ry, h.y) * hs, v[2] = fmaf(a.z, ry, h.z) * hs, v[3] = fmaf(a.w, ry, h.w) * hs;
-        if (blockIdx.x == 0 && p.h_out != nullptr) *reinterpret_cast<float4*>(p.h_out + at) = make_float4(v[0], v[1], v[2], v[3]);
-        v[0] *= rh * w2.x, v[1] *= rh * w2.y, v[2] *= rh * w2.z, v[3] *= rh * w2.w;
+        const float v0 = fmaf(a.x, ry, h.x) * hs, v1 = fmaf(a.y, ry, h.y) * hs, v2 = fmaf(a.z, ry, h.z) * hs, v3 = fmaf(a.w, ry, h.w) * hs;
+        if (blockIdx.x == 0 && p.h_out != nullptr) *reinterpret_cast<float4*>(p.h_out + at) = make_float4(v0, v1, v2, v3);
+        store_planes<WPR>(raw, t, v0 * rh * w2.x, v1 * rh * w2.y, v2 * rh * w2.z, v3 * rh * w2.w);
     }
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < E; j++) amax = fmaxf(amax, fabsf(v[j]));
-#pragma unroll
-    for (int o = 16 / E; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    uint32_t eb = min(__float_as_uint(amax) >> 23, 254u);
-    const bool zero = eb < 22u;
-    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);
-    const int block = t * E / 32, word = (t * E % 32) / 4;
-    uint32_t* hi = reinterpret_cast<uint32_t*>(raw + L::HI) + block * 8 + word;
-    uint32_t* mid = reinterpret_cast<uint32_t*>(raw + L::MID) + block * 8 + word;
-    uint32_t* lo = reinterpret_cast<uint32_t*>(raw + L::LO) + block * 8 + word;
-#pragma unroll
-    for (int k = 0; k < E / 4; k++) {
-        const int x0 = __float2int_rn(v[4 * k] * sc), x1 = __float2int_rn(v[4 * k + 1] * sc);
-        const int x2 = __float2int_rn(v[4 * k + 2] * sc), x3 = __float2int_rn(v[4 * k + 3] * sc);
-        hi[k] = pack_bytes(x0, x1, x2, x3, 0x0062);
-        mid[k] = pack_bytes(x0, x1, x2, x3, 0x0051);
-        lo[k] = pack_bytes(x0, x1, x2, x3, 0x0040);
-    }
-    if (word == 0) reinterpret_cast<float*>(raw + L::MUL)[block] = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);
 }
 
 // Planes of block `b` from shared memory; `first` picks which 16-byte half lands in words 0..3 (it matches the
@@ -423,8 +408,11 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     constexpr uint32_t ROWS = stage_rows(WPR);
     constexpr uint32_t UNIT = (EPI == EPI_GEGLU) ? 2 : 1;
     uint32_t grid = (uint32_t)ctx->sms;
-    const uint32_t most = (p.rows / UNIT * UNIT + ROWS - 1) / ROWS;
+    // Small matrices still spread over every SM (a block's stage is then partly empty): they are latency-bound.
+    constexpr uint32_t LEAST = UNIT > (uint32_t)rows_per_warp(WPR) ? UNIT : (uint32_t)rows_per_warp(WPR);
+    const uint32_t most = (p.rows + LEAST - 1) / LEAST;
     if (grid > most) grid = most > 0 ? most : 1;
+    (void)ROWS;
     TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR), true, p, ctx->status));
     return OK;
 }
