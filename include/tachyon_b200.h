@@ -140,6 +140,19 @@ typedef struct tb_attend {
 } tb_attend;
 TB_API size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits);
 TB_API int tb_attend_decode(tb_context* ctx, const tb_attend* args);
+/*
+ * tb_attend_decode for callers that cannot allocate device memory (no counterpart in the reference, which always carves
+ * this scratch out of its decoder's arena): an engine whose memory plan is fixed at start-up, or a loop that must not
+ * call cudaMalloc because it synchronises the device.  args->partial and args->count are ignored; the scratch is a
+ * fixed array inside the library (about 1.03 MiB held by every GPU that loads the library, until the process exits).
+ * Limits: kv_heads <= 4, splits <= 64, heads / kv_heads <= 4; anything larger returns TB_OUT_OF_RANGE and launches
+ * nothing.  The call itself makes no cudaMalloc, cudaFree or other allocating call.
+ * The first call on a GPU resolves the array's device address (once per device); make that first call before any
+ * stream capture begins.  All calls share the one array: calls that overlap on the GPU (two streams, two contexts on
+ * one GPU) race; serialise them.  The array keeps the last call's contents; the call clears the words that must be
+ * zero itself.
+ */
+TB_API int tb_attend_decode_static(tb_context* ctx, const tb_attend* args);
 
 /*
  * Greedy sampler over f32 logits with the reference's transform (soft cap, allowed mask, repetition penalty):

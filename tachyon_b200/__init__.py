@@ -138,6 +138,10 @@ class Context:
     def attend_decode(self, args: Attend) -> None:
         check(self.lib.tb_attend_decode(self.handle, C.byref(args)))
 
+    def attend_decode_static(self, args: Attend) -> None:
+        """tb_attend_decode_static: the scratch lives inside the library; nothing is allocated."""
+        check(self.lib.tb_attend_decode_static(self.handle, C.byref(args)))
+
     def attend_scratch_bytes(self, heads: int, kv_heads: int, splits: int) -> int:
         return self.lib.tb_attend_scratch_bytes(heads, kv_heads, splits)
 

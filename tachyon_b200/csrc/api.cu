@@ -243,6 +243,18 @@ int tb_attend_decode(tb_context* ctx, const tb_attend* a) {
     return launch_attend(ctx, p);
 }
 
+int tb_attend_decode_static(tb_context* ctx, const tb_attend* a) {
+    if (!ctx || !a) return fail(OUT_OF_RANGE, "tb_attend_decode_static: null argument");
+    if (!dtype_ok(a->out_dtype)) return fail(OUT_OF_RANGE, "tb_attend_decode_static: unknown dtype");
+    AttendParams p;
+    p.qkv = a->qkv, p.q_norm = a->q_norm, p.k_norm = a->k_norm, p.freq = a->freq;
+    p.kc = reinterpret_cast<__half*>(a->k_cache), p.vc = reinterpret_cast<__half*>(a->v_cache);
+    p.pos = a->pos, p.cap = a->cap, p.window = a->window, p.fresh = a->fresh, p.heads = a->heads, p.kv_heads = a->kv_heads;
+    p.scale = a->scale, p.eps = a->eps, p.splits = a->splits;
+    p.out = a->out, p.out_f16 = a->out_dtype == TB_F16;
+    return launch_attend_static(ctx, p);
+}
+
 int tb_sample_greedy(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, uint32_t* seen, const uint32_t* allowed,
                      void* scratch, uint32_t* state, uint32_t* token_out) {
     if (!ctx || !scratch || (reinterpret_cast<uintptr_t>(scratch) & 7)) return fail(OUT_OF_RANGE, "tb_sample_greedy: bad scratch");

@@ -14,6 +14,8 @@
 #include "common.cuh"
 #include "internal.h"
 
+#include <string>
+
 namespace tb {
 
 namespace {
@@ -345,6 +347,49 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
     else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(Smem), true, p, ctx->status));
     else TB_CUDA(launch_kernel(ctx, attend_kernel<1>, grid, block, sizeof(Smem), true, p, ctx->status));
     return OK;
+}
+
+// ---- the variant that allocates nothing ---------------------------------------------------------------------------
+//
+// tb_attend_decode needs scratch from its caller (the per-split partial results and the per-head counters).  Some
+// callers have no way to provide it: an engine whose device memory was carved up once at start-up and has nothing left
+// to hand out, or a latency-critical loop that may not call cudaMalloc because that call synchronises the whole device.
+// For them the scratch lives here, in the library's own image: a fixed array every GPU that loads the library holds
+// until the process exits.  Its size covers up to STATIC_KV_HEADS key-value heads with up to STATIC_SPLITS blocks each
+// and four query heads per key-value head (about 1.03 MiB); anything larger is refused.
+constexpr uint32_t STATIC_KV_HEADS = 4;
+constexpr uint32_t STATIC_SPLITS = 64;
+constexpr size_t STATIC_FLOATS = (size_t)STATIC_KV_HEADS * STATIC_SPLITS * (2 * MAXG + MAXG * D);
+constexpr size_t STATIC_COUNTERS = 64;  // words, after the partials
+
+namespace {
+static __device__ __align__(256) float g_attend_scratch[STATIC_FLOATS + STATIC_COUNTERS];
+// Device address of the array on each GPU ordinal, resolved on first use.  The name above is only a handle on the host:
+// it must go through cudaGetSymbolAddress before a kernel can be given it.
+float* g_attend_scratch_ptr[64] = {};
+}  // namespace
+
+int launch_attend_static(tb_context* ctx, AttendParams p) {
+    if (p.kv_heads == 0 || p.heads % p.kv_heads != 0 || p.heads / p.kv_heads > (uint32_t)MAXG)
+        return fail(OUT_OF_RANGE, "attend (static scratch): at most 4 query heads per key-value head");
+    if (p.kv_heads > STATIC_KV_HEADS || p.splits > STATIC_SPLITS)
+        return fail(OUT_OF_RANGE, "attend (static scratch): the built-in scratch holds at most 4 key-value heads x 64 splits; got " +
+                                      std::to_string(p.kv_heads) + " x " + std::to_string(p.splits) + " (use tb_attend_decode with caller scratch)");
+    if (ctx->gpu < 0 || ctx->gpu >= 64) return fail(OUT_OF_RANGE, "attend (static scratch): GPU ordinal out of range");
+    if (g_attend_scratch_ptr[ctx->gpu] == nullptr) {
+        // Once per device, with that device current.
+        TB_CUDA(cudaSetDevice(ctx->gpu));
+        void* ptr = nullptr;
+        TB_CUDA(cudaGetSymbolAddress(&ptr, g_attend_scratch));
+        g_attend_scratch_ptr[ctx->gpu] = static_cast<float*>(ptr);
+    }
+    float* base = g_attend_scratch_ptr[ctx->gpu];
+    p.partial = base;
+    p.count = reinterpret_cast<uint32_t*>(base + STATIC_FLOATS);
+    // The array keeps whatever the last call left.  The partials are overwritten before they are read; the counters must
+    // start at zero, so they are cleared on the stream ahead of the kernel.
+    TB_CUDA(cudaMemsetAsync(p.count, 0, STATIC_COUNTERS * sizeof(uint32_t), ctx->stream));
+    return launch_attend(ctx, p);
 }
 
 }  // namespace tb

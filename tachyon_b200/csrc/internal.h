@@ -110,6 +110,7 @@ struct AttendParams {
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
+int launch_attend_static(tb_context* ctx, AttendParams p);  // scratch inside the library; see attend.cu
 
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);
