@@ -186,6 +186,7 @@ typedef struct tb_settings {
     uint32_t context;      /* positions a global layer keeps */
     uint32_t chunk;        /* extra ring slots of sliding layers (the reference's prefill chunk) */
     uint32_t keep_logits;  /* != 0: every step also stores the f32 logits for tb_decoder_logits */
+    uint32_t fused;        /* != 0: the whole step as one persistent kernel with grid barriers instead of 2 + 5*layers launches */
 } tb_settings;
 
 /* Decoder::open without the file loader: allocates weights, caches and step buffers for `cfg`. */
@@ -225,6 +226,12 @@ TB_API int tb_decoder_position(tb_decoder* dec, uint32_t* pos);
 TB_API int tb_decoder_step_bytes(tb_decoder* dec, uint64_t* weight_bytes, uint64_t* cache_bytes);
 /* Kernels one step launches. */
 TB_API int tb_decoder_step_launches(tb_decoder* dec, uint32_t* launches);
+/*
+ * Decoder::timeline (decode.rs:424-436): runs one step on `token` outside the graphs and returns, for the first and
+ * for the last block of the fused step kernel, four %globaltimer stamps (ns) per phase: start, 0, end of work, after
+ * the barrier behind it.  host_out: 2 * phases * 4 words; call with host_out NULL to learn `phases`.
+ */
+TB_API int tb_decoder_timeline(tb_decoder* dec, uint32_t token, uint64_t* host_out, uint32_t* phases);
 /* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */
 TB_API int tb_decoder_hidden(tb_decoder* dec, float* host_out);
 

@@ -190,9 +190,9 @@ def gemma4_e4b_shape(layers: int = 35, ffn: int = 16384, vocab: int = 262144) ->
 class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
-    def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False):
+    def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False, fused: bool = False):
         self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
-        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits))
+        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused))
         h = C.c_void_p()
         check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
         self.handle = h.value
@@ -251,6 +251,14 @@ class Decoder:
     def hidden(self) -> np.ndarray:
         out = np.empty(self.cfg.hidden, np.float32)
         check(self.lib.tb_decoder_hidden(self.handle, out.ctypes.data))
+        return out
+
+    def timeline(self, token: int) -> np.ndarray:
+        """One step outside the graphs; returns ns stamps [2 blocks, phases, 4] (start, -, end of work, after barrier)."""
+        n = C.c_uint32(0)
+        check(self.lib.tb_decoder_timeline(self.handle, token, None, C.byref(n)))
+        out = np.zeros((2, n.value, 4), np.uint64)
+        check(self.lib.tb_decoder_timeline(self.handle, token, out.ctypes.data, C.byref(n)))
         return out
 
     @property

@@ -31,7 +31,7 @@ class Config(C.Structure):
 
 
 class Settings(C.Structure):
-    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32)]
+    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares.
@@ -87,6 +87,7 @@ SIGNATURES = {
     "tb_decoder_step_bytes": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
     "tb_decoder_step_launches": (i32, [vp, C.POINTER(u32)]),
     "tb_decoder_hidden": (i32, [vp, vp]),
+    "tb_decoder_timeline": (i32, [vp, u32, vp, C.POINTER(u32)]),
 }
 
 _lib = None

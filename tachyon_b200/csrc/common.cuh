@@ -9,7 +9,7 @@
 namespace tb {
 
 // Error words a kernel can leave in the context's device status word (0 = fine).
-enum : uint32_t { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_DRAIN = 3 };
+enum : uint32_t { ERR_NONE = 0, ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_DRAIN = 3, ERR_GRID = 4 };
 
 // Longest a thread polls one barrier before it gives up and reports: two seconds of %globaltimer.
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -32,6 +32,22 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// mbarrier.arrive counting for `count` arrivals at once.
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+// Adds to a counter with release semantics and without waiting for the old value.
+__device__ __forceinline__ void red_release_add(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
@@ -62,10 +78,27 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  : "memory");
 }
 
+// An L2 policy that marks what is fetched with it as the first to evict: for data that is streamed once.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+// bulk_load with an L2 cache policy.
+__device__ __forceinline__ void bulk_load_hint(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_addr(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+                 : "memory");
+}
+
 // Prefetch a range into L2 without a destination.
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
 }
+
+// One 128-byte line into the L2, through the load/store unit (it does not queue behind the bulk copies).
+__device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // Issues the L2 prefetches of a hint (see Prefetch in internal.h) for the later kernel's blocks b = first, first +
 // step, ...  Called by one thread.

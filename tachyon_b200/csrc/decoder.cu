@@ -75,6 +75,12 @@ struct tb_decoder {
     uint32_t pos = 0;  // host mirror of the position
     uint32_t launches = 0;
     int final_x = 0;  // which of x[0], x[1] holds the hidden state after the last layer
+    // The fused step: per graph, the phase table on the device; the grid barrier's counter.
+    StepPhase* phase_dev[2] = {nullptr, nullptr};
+    uint32_t phase_count = 0;
+    uint32_t* grid_counter = nullptr;
+    bool fused = false;
+    std::vector<StepPhase>* collect = nullptr;  // when set, step_ops records descriptors instead of launching
     float embed_scale = 1.0f;
 };
 
@@ -150,8 +156,8 @@ void layout(tb_decoder* d, char* base) {
         const size_t cache = (size_t)c.kv_heads * L.cap * c.head_dim * 2;
         L.kc = reinterpret_cast<__half*>(base + t.take(cache));
         L.vc = reinterpret_cast<__half*>(base + t.take(cache));
-        // Blocks per key-value head: spans of about 32 positions (sliding) or 64 (global), within the machine.
-        const uint32_t per = L.global ? 64 : 32;
+        // Blocks per key-value head: spans of about 32 positions (sliding) or 128 (global, two tiles), within the machine.
+        const uint32_t per = L.global ? 128 : 32;
         L.splits = (L.window + per - 1) / per;
         const uint32_t most = (uint32_t)(2 * d->ctx->sms) / c.kv_heads;
         if (L.splits > most) L.splits = most;
@@ -167,6 +173,7 @@ void layout(tb_decoder* d, char* base) {
     d->state = reinterpret_cast<uint32_t*>(base + t.take(8));
     d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
     d->trace = reinterpret_cast<uint32_t*>(base + t.take((size_t)TRACE * 4));
+    d->grid_counter = reinterpret_cast<uint32_t*>(base + t.take(4));
     d->arena_bytes = t.end;
 }
 
@@ -191,6 +198,13 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols;
     d->launches++;
+    if (d->collect) {
+        if (!step_supports(p)) return fail(UNSUPPORTED, "fused step: no code path for this product");
+        StepPhase ph;
+        ph.kind = PH_GEMV, ph.g = p;
+        d->collect->push_back(ph);
+        return OK;
+    }
     return launch_gemv(d->ctx, p);
 }
 
@@ -199,7 +213,14 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
     const tb_config& c = d->cfg;
     d->launches = 0;
     int cur = 0;
-    TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0]));
+    if (d->collect) {
+        StepPhase ph;
+        ph.kind = PH_EMBED;
+        ph.e.w = d->embed.w, ph.e.s = d->embed.s, ph.e.token = d->state + 1, ph.e.cols = c.hidden, ph.e.scale = d->embed_scale, ph.e.out = d->x[0];
+        d->collect->push_back(ph);
+    } else {
+        TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0]));
+    }
     d->launches++;
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
@@ -221,11 +242,22 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
         a.pf = hint(d, L.gate_up, 2, 0, PF);
-        TB_TRY(launch_attend(d->ctx, a));
+        if (d->collect) {
+            a.defer = 1;  // the o projection merges the splits in its prologue
+            StepPhase ph;
+            ph.kind = PH_ATTEND, ph.a = a;
+            d->collect->push_back(ph);
+        } else {
+            TB_TRY(launch_attend(d->ctx, a));
+        }
         d->launches++;
 
         GemvParams o;
         o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
+        if (d->collect) {
+            o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
+            o.att_heads = c.heads, o.att_kv = c.kv_heads;
+        }
         o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 
@@ -336,6 +368,10 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     TB_TRY(validate(*cfg, *settings));
     tb_decoder* d = new tb_decoder();
     d->ctx = ctx, d->cfg = *cfg, d->settings = *settings;
+    {
+        const char* env = getenv("TACHYON_B200_FUSED");
+        d->fused = settings->fused != 0 || (env != nullptr && env[0] == '1');
+    }
     d->global.resize(cfg->layers);
     for (uint32_t i = 0; i < cfg->layers; i++)
         d->global[i] = cfg->global ? cfg->global[i] : (cfg->global_every ? ((i + 1) % cfg->global_every == 0) : 0);
@@ -377,6 +413,8 @@ void tb_decoder_close(tb_decoder* d) {
         if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]);
         if (d->done[g]) cudaEventDestroy(d->done[g]);
     }
+    for (int g = 0; g < 2; g++)
+        if (d->phase_dev[g]) cudaFree(d->phase_dev[g]);
     if (d->arena) cudaFree(d->arena);
     if (d->words) cudaFreeHost(d->words);
     delete d;
@@ -479,14 +517,26 @@ int tb_decoder_build(tb_decoder* d) {
         if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]), d->graphs[g] = nullptr;
         uint32_t* word = nullptr;
         TB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&word), d->words + g, 0));
+        // The fused step reads its phases from a table on the device, one table per graph (the token word differs).
+        if (d->fused) {
+            std::vector<StepPhase> table;
+            d->collect = &table;
+            const int sc = step_ops(d, word);
+            d->collect = nullptr;
+            TB_TRY(sc);
+            d->phase_count = (uint32_t)table.size();
+            if (!d->phase_dev[g]) TB_CUDA(cudaMalloc(&d->phase_dev[g], table.size() * sizeof(StepPhase)));
+            TB_CUDA(cudaMemcpy(d->phase_dev[g], table.data(), table.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+        }
+        auto run = [&]() -> int { return d->fused ? launch_step(d->ctx, d->phase_dev[g], d->phase_count, d->grid_counter, d->state) : step_ops(d, word); };
         // One uncaptured pass first: it sets each kernel's attributes (not allowed while capturing) and surfaces
         // descriptor errors plainly.  It runs on zeroed state and is followed by a reset.
         if (g == 0) {
-            TB_TRY(step_ops(d, word));
+            TB_TRY(run());
             TB_CUDA(cudaStreamSynchronize(s));
         }
         TB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-        const int st = step_ops(d, word);
+        const int st = run();
         cudaGraph_t graph = nullptr;
         const cudaError_t e = cudaStreamEndCapture(s, &graph);
         if (st != OK) {
@@ -608,8 +658,29 @@ int tb_decoder_step_bytes(tb_decoder* d, uint64_t* weight_bytes, uint64_t* cache
 
 int tb_decoder_step_launches(tb_decoder* d, uint32_t* launches) {
     if (!d || !launches) return fail(OUT_OF_RANGE, "null argument");
-    *launches = 2 + 5 * d->cfg.layers;
+    *launches = d->fused ? 1 : 2 + 5 * d->cfg.layers;
     return OK;
+}
+
+int tb_decoder_timeline(tb_decoder* d, uint32_t token, uint64_t* host_out, uint32_t* phases) {
+    TB_TRY(ready(d, 1));
+    if (!d->fused) return fail(UNSUPPORTED, "tb_decoder_timeline: only the fused step records a timeline");
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_timeline: a generation is running; stop it first");
+    if (phases) *phases = d->phase_count;
+    if (!host_out) return OK;
+    const size_t bytes = (size_t)2 * d->phase_count * 4 * sizeof(unsigned long long);
+    unsigned long long* dev = nullptr;
+    TB_CUDA(cudaMalloc(&dev, bytes));
+    cudaError_t e = cudaMemsetAsync(dev, 0, bytes, d->ctx->stream);
+    int st = OK;
+    if (e == cudaSuccess) st = feed_token(d, token);
+    if (e == cudaSuccess && st == OK) st = launch_step(d->ctx, d->phase_dev[0], d->phase_count, d->grid_counter, d->state, dev);
+    if (e == cudaSuccess && st == OK) e = cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, d->ctx->stream);
+    if (e == cudaSuccess && st == OK) e = cudaStreamSynchronize(d->ctx->stream);
+    cudaFree(dev);
+    if (e != cudaSuccess) return cuda_fail(e, "tb_decoder_timeline");
+    if (st == OK) d->pos++;
+    return st;
 }
 
 int tb_decoder_hidden(tb_decoder* d, float* host_out) {

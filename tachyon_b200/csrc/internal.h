@@ -49,7 +49,7 @@ int cuda_fail(cudaError_t e, const char* where);
     } while (0)
 
 // ---- GEMV ------------------------------------------------------------------------------------------------
-enum XMode : int { X_F16 = 0, X_F32 = 1, X_NORM = 2 };
+enum XMode : int { X_F16 = 0, X_F32 = 1, X_NORM = 2, X_ATTN = 3 };
 enum Epilogue : int { EPI_F32 = 0, EPI_F16 = 1, EPI_GEGLU = 2, EPI_ARGMAX = 3 };
 
 // A hint about the matrix a later kernel will stream: that kernel runs `grid` blocks, block b owning the rows
@@ -85,6 +85,11 @@ struct GemvParams {
     uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
     uint32_t trace_mask = 0;
     Prefetch pf;                  // optional hint for the L2
+    // X_ATTN (fused step only): x is the attention output, merged here from the splits' partial results
+    // (layout of AttendParams::partial): x[h*256 + d] = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s.
+    const float* att_partial = nullptr;
+    const uint32_t* att_pos = nullptr;
+    uint32_t att_splits = 1, att_window = 1, att_heads = 8, att_kv = 2;
 };
 
 int launch_gemv(tb_context* ctx, const GemvParams& p);
@@ -107,10 +112,35 @@ struct AttendParams {
     void* out = nullptr;           // [heads*256] f32 or f16
     int out_f16 = 0;
     Prefetch pf;                   // optional hint for the L2
+    uint32_t defer = 0;            // != 0 (fused step): every split only stores its partial; the next product merges them
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
 int launch_attend_static(tb_context* ctx, AttendParams p);  // scratch inside the library; see attend.cu
+
+// ---- fused decode step ---------------------------------------------------------------------------------------
+struct EmbedParams {
+    const int8_t* w = nullptr;
+    const __half* s = nullptr;
+    const uint32_t* token = nullptr;
+    uint32_t cols = 0;
+    float scale = 1.0f;
+    float* out = nullptr;
+};
+enum PhaseKind : int { PH_EMBED = 0, PH_GEMV = 1, PH_ATTEND = 2 };
+// One phase of the fused step: the descriptor the stand-alone kernel of the same kind would be launched with.
+struct StepPhase {
+    int kind = PH_GEMV;
+    EmbedParams e;
+    GemvParams g;
+    AttendParams a;
+};
+// Whether the fused step has a code path for this product (shape and fusion).
+bool step_supports(const GemvParams& p);
+// Launches the fused step over `n` phases (device array); `counter` is a device word the call zeroes first.
+// `times` (optional): 2 * n * 4 device words for the first and last block's timeline.
+// `state`: the device word holding the step's position.
+int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* counter, const uint32_t* state, unsigned long long* times = nullptr);
 
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);

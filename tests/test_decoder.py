@@ -126,11 +126,34 @@ def test_overlap_off_gives_the_same_bits(ctx, models):
         ctx.set_overlap(True)
 
 
-def test_benchmark_width_ffn_and_a_prefilled_cache(ctx):
+def test_fused_step_equals_one_launch_per_phase(ctx, models):
+    """The persistent step kernel runs the same arithmetic as the 2 + 5*layers separate kernels."""
+    cfg, dec, ref = models
+    assert dec.step_launches == 2 + 5 * cfg.layers
+    plain = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True, fused=True)
+    plain.fill_random(SEED)
+    plain.build()
+    assert plain.step_launches == 1
+    dec.reset()
+    for pos in range(40):  # through the ring's wrap
+        token = (pos * 7919 + 13) % cfg.vocab
+        assert dec.step(token) == plain.step(token)
+        a, b = dec.logits(), plain.logits()
+        assert np.abs(a - b).max() <= 1e-4 * np.abs(b).max()  # the splits are merged in a different order
+    # Decoder::timeline: four stamps per phase for the first and the last block, in order
+    stamps = plain.timeline(7).astype(np.int64)
+    assert stamps.shape == (2, 2 + 5 * cfg.layers, 4)
+    starts = stamps[0, :, 0]
+    assert np.all(np.diff(starts) > 0) and np.all(stamps[0, :, 2] >= starts)
+    plain.close()
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_benchmark_width_ffn_and_a_prefilled_cache(ctx, fused):
     """One layer at the benchmark's FFN width (down projection over 16384 columns) on a synthetic 100-position cache."""
     cfg = small_config(layers=2, ffn=16384, vocab=2048, window=512)
     cfg.global_every = 2
-    dec = tb.Decoder(ctx, cfg, context=256, chunk=0, keep_logits=True)
+    dec = tb.Decoder(ctx, cfg, context=256, chunk=0, keep_logits=True, fused=fused)
     dec.fill_random(77)
     dec.build()
     dec.fill_cache(5, 100)
