@@ -107,6 +107,16 @@ TB_API int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* sca
 TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, float* logits, uint32_t rows, uint32_t cols,
                       void* scratch, uint32_t* state, uint32_t* token_out);
 
+/*
+ * Prefill product on the tensor cores: D[m, n] = A[m, k] x W[n, k]^T.  A: device f16 [m, k] row-major; W, scales: as
+ * tb_gemv_q8; f32 accumulation.  mode TB_GEMM_F32: out f32 [m, n]; TB_GEMM_F16: out f16 [m, n]; TB_GEMM_GEGLU: columns
+ * (2j, 2j+1) are (gate_j, up_j) and out is f16 [m, n/2] of gelu_tanh(gate) * up.  k a multiple of 64, n of 32.
+ * Stands in for gemm_q4 with its split-K slices and sum_slices (crates/tachyon/src/ptx/gemm.rs:18-23, 225-259,
+ * 287-325) and, in GeGLU mode, geglu_q8p (ptx/mod.rs:217-249).
+ */
+enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2 };
+TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
+
 /* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
 TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
             float* x_out);

@@ -1,0 +1,285 @@
+// Prefill GEMM on the fifth-generation tensor cores: D[M, N] = A[M, K] (f16 activations) x W[N, K]^T with W in the
+// decode path's Q8 layout (int8 codes + one f16 scale per 32 along K), f32 accumulation in tensor memory.
+// Stands in for the reference's gemm_q4 (crates/tachyon/src/ptx/gemm.rs:225-259: integer mma.sync on Q4 x Q8P) and its
+// split-K sum (gemm.rs:287-325), which the TMEM accumulator makes unnecessary: a block owns a 128 x 128 output tile
+// over the whole K.
+//
+// One block, six warps:
+//   warp 0      one thread issues the TMA loads of the activation tile (128 rows x 64 halves, 128-byte swizzle);
+//   warp 1      allocates tensor memory; one thread issues tcgen05.mma (M128 N128 K16, four per stage) and commits;
+//   warps 2-5   dequantise the weight tile: thread j reads row j's 64 codes and two scales, turns the codes into f16
+//               exactly (0x6400 | (code ^ 0x80) is 1024 + code + 128; minus 1152), multiplies by the scale and stores
+//               the row in the same swizzled K-major layout TMA would have produced; after the main loop the same
+//               warps read the accumulator back (tcgen05.ld) and write the output (f32, f16, or GeGLU of column pairs).
+// Stages hand over on mbarriers: full = TMA bytes + the four dequantising warps, empty = tcgen05.commit.
+// Operands are f16 rather than bf16: the code -> f16 step is exact and costs one instruction per two weights, the
+// tensor rate is the same, and the activations that reach this kernel are normalised.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;  // tile; BK halves = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256;
+
+// tcgen05.mma instruction descriptor, kind::f16: f32 accumulator, f16 A and B, both K-major, N = 128, M = 128.
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 1024 bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// 32 consecutive accumulator columns of this thread's row.
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+        "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Four codes (one word) -> four f16 of code * scale, as two half2.
+__device__ __forceinline__ void dequant4(uint32_t w, __half2 scale, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x = w ^ 0x80808080u;                 // code + 128 in every byte
+    uint32_t a = __byte_perm(x, 0x64646464u, 0x5140);  // {0x64, b1, 0x64, b0}: 1024 + b1, 1024 + b0
+    uint32_t b = __byte_perm(x, 0x64646464u, 0x7362);  // bytes 2 and 3
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+    const __half2 va = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&a), bias), scale);
+    const __half2 vb = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&b), bias), scale);
+    lo = *reinterpret_cast<const uint32_t*>(&va);
+    hi = *reinterpret_cast<const uint32_t*>(&vb);
+}
+
+struct GemmArgs {
+    const int8_t* w;
+    const __half* s;
+    void* out;
+    uint32_t M, N, K;
+    int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU of column pairs, f16 [M, N / 2]
+};
+
+__global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const GemmArgs g, uint32_t* status) {
+    extern __shared__ uint8_t raw_unaligned[];
+    uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
+    uint8_t* As = raw;
+    uint8_t* Bs = raw + STAGES * A_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, nk = g.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 5), mbar_init(&empty[i], 1);
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (uint32_t kt = 0; kt < nk && ok; kt++) {
+                const uint32_t s = kt % STAGES;
+                if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(&full[s], A_BYTES);
+                tma_load_2d(As + s * A_BYTES, &a_map, (int)(kt * BK), (int)m0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (uint32_t kt = 0; kt < nk && ok; kt++) {
+                const uint32_t s = kt % STAGES;
+                if (!mbar_wait(&full[s], (kt / STAGES) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a = smem_addr(As + s * A_BYTES), b = smem_addr(Bs + s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) mma_f16(tmem, smem_desc(a + k * 32), smem_desc(b + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                mma_commit(&empty[s]);
+            }
+            mma_commit(acc_full);  // arrives when every MMA above has finished (also after an early exit)
+        }
+    } else {
+        // Weight tile: thread j owns row n0 + j.
+        const int j = threadIdx.x - 64;
+        const uint32_t n = n0 + j;
+        const bool live = n < g.N;
+        const int8_t* wrow = g.w + (size_t)(live ? n : 0) * g.K;
+        const __half* srow = g.s + (size_t)(live ? n : 0) * (g.K / 32);
+        uint4 c[4];
+        __half s0, s1;
+        auto fetch = [&](uint32_t kt) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) c[q] = live ? __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)kt * BK) + q) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+            s0 = live ? srow[kt * 2] : __float2half(0.0f);
+            s1 = live ? srow[kt * 2 + 1] : __float2half(0.0f);
+        };
+        if (nk > 0) fetch(0);
+        for (uint32_t kt = 0; kt < nk; kt++) {
+            const uint32_t s = kt % STAGES;
+            uint32_t v[32];  // 64 halves
+            {
+                const __half2 sc0 = __half2half2(s0), sc1 = __half2half2(s1);
+                const uint32_t w[16] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w, c[2].x, c[2].y, c[2].z, c[2].w, c[3].x, c[3].y, c[3].z, c[3].w};
+#pragma unroll
+                for (int q = 0; q < 16; q++) dequant4(w[q], q < 8 ? sc0 : sc1, v[2 * q], v[2 * q + 1]);
+            }
+            if (kt + 1 < nk) fetch(kt + 1);  // the next tile's codes are on their way while this one is stored
+            if (ok && kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) {
+                atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                ok = false;
+            }
+            uint8_t* row = Bs + s * B_BYTES + j * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+                *reinterpret_cast<uint4*>(row + ((ch ^ (j & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+        // Epilogue: this warp's quarter of the accumulator rows.
+        if (!mbar_wait(acc_full, 0)) {
+            atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+            ok = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t q = warp & 3, rrow = 32 * q + lane, m = m0 + rrow;
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 32; cb++) {
+            uint32_t r[32];
+            tmem_load32(tmem + ((32 * q) << 16) + cb * 32, r);
+            if (m < g.M && ok) {
+                const uint32_t col = n0 + cb * 32;
+                if (g.mode == 0) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                } else if (g.mode == 1) {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const __half2 t = __floats2half2_rn(__uint_as_float(r[8 * i + 2 * e]), __uint_as_float(r[8 * i + 2 * e + 1]));
+                            h[e] = *reinterpret_cast<const uint32_t*>(&t);
+                        }
+                        if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                } else {
+                    // columns (2j, 2j+1) are (gate_j, up_j): gelu_tanh(gate) * up, 16 results per 32 columns
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * (g.N / 2) + col / 2);
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float a0 = gelu_tanh(__uint_as_float(r[16 * i + 4 * e])) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                            const float a1 = gelu_tanh(__uint_as_float(r[16 * i + 4 * e + 2])) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                            const __half2 t = __floats2half2_rn(a0, a1);
+                            h[e] = *reinterpret_cast<const uint32_t*>(&t);
+                        }
+                        if (col + 16 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode) {
+    if (!w || !s || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
+    if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
+    if (N % 32 != 0 || (mode == 2 && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
+    if (mode < 0 || mode > 2) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {K, M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {BK, BM}, elem[2] = {1, 1};
+    const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(a), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    static bool configured[16] = {};
+    if (!configured[ctx->gpu & 15]) {
+        TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[ctx->gpu & 15] = true;
+    }
+    GemmArgs g{w, s, out, M, N, K, mode};
+    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_q8_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(map, g, ctx->status);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+}  // namespace tb

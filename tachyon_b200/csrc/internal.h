@@ -142,6 +142,10 @@ bool step_supports(const GemvParams& p);
 // `state`: the device word holding the step's position.
 int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* counter, const uint32_t* state, unsigned long long* times = nullptr);
 
+// ---- prefill GEMM (tensor cores) ------------------------------------------------------------------------------
+// D[M, N] = A[M, K] (f16) x W[N, K]^T (Q8); mode 0: f32 out, 1: f16 out, 2: GeGLU of column pairs -> f16 [M, N/2].
+int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode);
+
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);
 int launch_norm(tb_context* ctx, const float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,

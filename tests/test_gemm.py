@@ -1,0 +1,66 @@
+"""Prefill GEMM (tcgen05, Q8 weights dequantised to f16 in the operand path) against f64 on the CPU.  Shapes follow
+crates/tachyon/tests/gemm.rs:17 in spirit (ragged token counts, one and several K tiles) at this build's widths."""
+import numpy as np
+import pytest
+
+import oracle
+import tachyon_b200 as tb
+from util import f16, f16_to_f32, q8_weights
+
+pytestmark = pytest.mark.gpu
+
+# (tokens, rows, cols)
+SHAPES = [(128, 128, 64), (128, 128, 256), (1, 128, 2048), (37, 256, 2048), (300, 3072, 2048), (512, 2048, 2048), (129, 2048, 16384), (256, 96, 128)]
+
+
+def reference(w, s, a):
+    deq = w.astype(np.float64) * np.repeat(f16_to_f32(s).astype(np.float64), 32, axis=1)
+    a64 = a.astype(np.float64)
+    return a64 @ deq.T, np.abs(a64) @ np.abs(deq).T
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_matches_f64(ctx, m, n, k):
+    w, s = q8_weights(n, k, 7 + n + k)
+    a = f16_to_f32(f16(np.random.default_rng(m + k).standard_normal((m, k)).astype(np.float32)))
+    want, bound = reference(w, s, a)
+    wd, sd, ad = ctx.upload(w), ctx.upload(s), ctx.upload(f16(a))
+    out = ctx.alloc((m + 3) * n * 4)
+    canary = np.full((m + 3) * n, 12345.0, np.float32)
+    out.upload(canary)
+    ctx.gemm_q8(wd, sd, ad, m, n, k, out, 0)
+    got = out.download(np.float32, (m + 3) * n)
+    assert np.all(got[m * n:] == 12345.0), "rows past the tokens were written"
+    got = got[: m * n].reshape(m, n)
+    # weights are rounded to f16 after scaling (2^-11 relative each); the accumulation is f32
+    assert np.all(np.abs(got - want) <= 1e-3 * bound + 1e-6), float(np.abs(got - want).max())
+    # f16 output
+    out16 = ctx.zeros(m * n * 2)
+    ctx.gemm_q8(wd, sd, ad, m, n, k, out16, 1)
+    got16 = f16_to_f32(out16.download(np.uint16, m * n)).reshape(m, n)
+    assert np.all(np.abs(got16 - want) <= 2.0**-10 * np.abs(want) + 1e-3 * bound + 1e-6)
+    assert ctx.status() == 0
+
+
+def test_gemm_geglu_epilogue(ctx):
+    m, n, k = 200, 1024, 2048
+    w, s = q8_weights(n, k, 3)
+    a = f16_to_f32(f16(np.random.default_rng(5).standard_normal((m, k)).astype(np.float32)))
+    want, bound = reference(w, s, a)
+    gate, up = want[:, 0::2], want[:, 1::2]
+    gelu = np.vectorize(lambda v: oracle.lib().tbo_gelu_tanh(float(v)))
+    ref = gelu(gate) * up
+    out = ctx.zeros(m * n)
+    ctx.gemm_q8(ctx.upload(w), ctx.upload(s), ctx.upload(f16(a)), m, n, k, out, 2)
+    got = f16_to_f32(out.download(np.uint16, m * n // 2)).reshape(m, n // 2)
+    tol = 2.0**-9 * np.abs(ref) + 2e-3 * (bound[:, 0::2] * (1 + np.abs(up)) + bound[:, 1::2] * (1 + np.abs(gate))) * 0.05 + 1e-4
+    assert np.all(np.abs(got - ref) <= tol), float(np.abs(got - ref).max())
+
+
+def test_gemm_rejects_bad_shapes(ctx):
+    z = ctx.zeros(4096)
+    with pytest.raises(tb.Error) as e:
+        ctx.gemm_q8(z, z, z, 4, 32, 48, z, 0)  # K not a multiple of 64
+    assert e.value.status == 3
+    with pytest.raises(tb.Error):
+        ctx.gemm_q8(z, z, z, 4, 32, 64, z, 9)
