@@ -75,6 +75,10 @@ struct tb_decoder {
     uint32_t pos = 0;  // host mirror of the position
     uint32_t launches = 0;
     int final_x = 0;  // which of x[0], x[1] holds the hidden state after the last layer
+    // Prefill chunk buffers (settings.chunk tokens): ids, residual stream, f16 GEMM inputs, projections.
+    uint32_t* pf_tokens = nullptr;
+    float *pf_h = nullptr, *pf_qkv = nullptr, *pf_y = nullptr;
+    __half *pf_x = nullptr, *pf_q = nullptr, *pf_att = nullptr, *pf_g = nullptr;
     // The fused step: per graph, the phase table on the device; the grid barrier's counter.
     StepPhase* phase_dev[2] = {nullptr, nullptr};
     uint32_t phase_count = 0;
@@ -174,6 +178,13 @@ void layout(tb_decoder* d, char* base) {
     d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
     d->trace = reinterpret_cast<uint32_t*>(base + t.take((size_t)TRACE * 4));
     d->grid_counter = reinterpret_cast<uint32_t*>(base + t.take(4));
+    if (d->settings.chunk > 0) {
+        const size_t T = d->settings.chunk;
+        auto half = [&](__half*& v, size_t n) { v = reinterpret_cast<__half*>(base + t.take(n * 2)); };
+        d->pf_tokens = reinterpret_cast<uint32_t*>(base + t.take(T * 4));
+        vec(d->pf_h, T * c.hidden), vec(d->pf_qkv, T * (nq(c) + 2 * nkv(c))), vec(d->pf_y, T * c.hidden);
+        half(d->pf_x, T * c.hidden), half(d->pf_q, T * nq(c)), half(d->pf_att, T * nq(c)), half(d->pf_g, T * c.ffn);
+    }
     d->arena_bytes = t.end;
 }
 
@@ -613,17 +624,59 @@ int tb_decoder_run(tb_decoder* d, uint32_t token, uint32_t steps, uint32_t* toke
     return OK;
 }
 
+// One chunk of prompt tokens through every layer (crates/tachyon/src/model/prefill.rs:124-196): tensor-core GEMMs over
+// the chunk, flash attention over the cache ring.  Only what later tokens need is computed: the caches of every layer,
+// so the last layer stops after its attention inputs are stored.
+static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint32_t pos0) {
+    const tb_config& c = d->cfg;
+    tb_context* ctx = d->ctx;
+    const uint32_t H = c.hidden, NQ = nq(c), NQKV = nq(c) + 2 * nkv(c);
+    TB_CUDA(cudaMemcpyAsync(d->pf_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h));
+    for (uint32_t i = 0; i < c.layers; i++) {
+        Layer& L = d->layers[i];
+        if (i == 0) {
+            TB_TRY(launch_prefill_norm(ctx, d->pf_h, nullptr, nullptr, L.input_ln, n, H, c.eps, 1.0f, d->pf_x));
+        } else {
+            const Layer& P = d->layers[i - 1];
+            TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
+        }
+        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, NQKV, H, d->pf_qkv, 0));
+        TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads, c.kv_heads,
+                                  c.eps, c.attn_scale));
+        if (i + 1 == c.layers) break;
+        TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, c.kv_heads));
+        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, NQ, d->pf_y, 0));
+        TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_attn, L.pre_ffn, n, H, c.eps, 1.0f, d->pf_x));
+        TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2));
+        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0));
+    }
+    return OK;
+}
+
 int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
     TB_TRY(ready(d, n));
     if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_prefill: a generation is running; stop it first");
     if (n && !tokens) return fail(OUT_OF_RANGE, "tb_decoder_prefill: null tokens");
-    for (uint32_t i = 0; i < n; i++) {
+    for (uint32_t i = 0; i < n; i++)
         if (tokens[i] >= d->cfg.vocab) return fail(OUT_OF_RANGE, "decoder: token outside the vocabulary");
-        // Every prompt token through the decode step; its sample is dropped (the next token overwrites it).
-        TB_CUDA(cudaMemcpyAsync(d->state + 1, tokens + i, 4, cudaMemcpyHostToDevice, d->ctx->stream));
-        TB_TRY(queue(d, 0));
+    const char* env = getenv("TACHYON_B200_PREFILL_BY_STEPS");
+    const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || (env != nullptr && env[0] == '1');
+    if (by_steps) {
+        // Without chunk buffers: every prompt token through the decode step; its sample is dropped.
+        for (uint32_t i = 0; i < n; i++) {
+            TB_CUDA(cudaMemcpyAsync(d->state + 1, tokens + i, 4, cudaMemcpyHostToDevice, d->ctx->stream));
+            TB_TRY(queue(d, 0));
+        }
+        TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+        return OK;
     }
-    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    for (uint32_t at = 0; at < n; at += d->settings.chunk) {
+        const uint32_t m = n - at < d->settings.chunk ? n - at : d->settings.chunk;
+        TB_TRY(prefill_chunk(d, tokens + at, m, d->pos));
+        TB_CUDA(cudaStreamSynchronize(d->ctx->stream));  // as the reference: one synchronisation per chunk (decode.rs:346-364)
+        TB_TRY(set_position(d, d->pos + m));
+    }
     return OK;
 }
 

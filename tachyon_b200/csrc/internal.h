@@ -146,6 +146,15 @@ int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* 
 // D[M, N] = A[M, K] (f16) x W[N, K]^T (Q8); mode 0: f32 out, 1: f16 out, 2: GeGLU of column pairs -> f16 [M, N/2].
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode);
 
+// ---- prefill kernels around the GEMMs (prefill.cu) ---------------------------------------------------------------------
+int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out);
+int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
+                        __half* x);
+int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
+                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale);
+int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                         uint32_t window, uint32_t heads, uint32_t kv_heads);
+
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);
 int launch_norm(tb_context* ctx, const float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,

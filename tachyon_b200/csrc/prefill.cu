@@ -1,0 +1,302 @@
+// The kernels around the prefill GEMMs, one chunk of prompt tokens at a time: embedding rows, the residual/RMS-norm
+// step per token (quant_q8p / norm_q8p's place, crates/tachyon/src/ptx/mod.rs:253-287, 491-511), query and key/value
+// preparation (query_256 and kv_256, ptx/attend.rs:472-556) and causal / sliding-window flash attention over the cache
+// ring (flash_256, ptx/flash.rs:326-374).  Attention is 2 % of a prefill's arithmetic; it runs on mma.sync with f16
+// operands and f32 softmax and accumulators, the GEMMs (98 %) on tcgen05 (gemm.cu).
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int D = 256;
+
+// ---- embedding rows ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prefill_embed_kernel(const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t cols, float scale, float* out) {
+    const size_t row = (size_t)tokens[blockIdx.x] * cols;
+    float* o = out + (size_t)blockIdx.x * cols;
+    for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) o[i] = (float)w[row + i] * __half2float(s[(row + i) / 32]) * scale;
+}
+
+// ---- residual + norm, one block per token, 2048 values (8 per thread) -----------------------------------------------
+// h' = (h + w1 * rmsnorm(y)) * hscale when y is given (h updated in place), x = w2 * rmsnorm(h') as f16.
+__global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,
+                                                           __half* x) {
+    __shared__ float sh[8];
+    const size_t base = (size_t)blockIdx.x * n;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto block_sum = [&](float v) {
+        v = warp_sum(v);
+        __syncthreads();
+        if (lane == 0) sh[warp] = v;
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) t += sh[i];
+        return t;
+    };
+    float v[8];
+    const float4 a = *reinterpret_cast<const float4*>(h + base + tid * 8), b = *reinterpret_cast<const float4*>(h + base + tid * 8 + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    if (y != nullptr) {
+        float yy[8];
+        const float4 c = *reinterpret_cast<const float4*>(y + base + tid * 8), d = *reinterpret_cast<const float4*>(y + base + tid * 8 + 4);
+        yy[0] = c.x, yy[1] = c.y, yy[2] = c.z, yy[3] = c.w, yy[4] = d.x, yy[5] = d.y, yy[6] = d.z, yy[7] = d.w;
+        float sy = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) sy = fmaf(yy[i], yy[i], sy);
+        const float ry = rsqrtf(block_sum(sy) / (float)n + eps);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = fmaf(yy[i] * ry, __ldg(w1 + tid * 8 + i), v[i]) * hscale;
+        *reinterpret_cast<float4*>(h + base + tid * 8) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(h + base + tid * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) sq = fmaf(v[i], v[i], sq);
+    const float rh = rsqrtf(block_sum(sq) / (float)n + eps);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half2 t = __floats2half2_rn(v[2 * i] * rh * __ldg(w2 + tid * 8 + 2 * i), v[2 * i + 1] * rh * __ldg(w2 + tid * 8 + 2 * i + 1));
+        o[i] = *reinterpret_cast<const uint32_t*>(&t);
+    }
+    *reinterpret_cast<uint4*>(x + base + tid * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ---- q / k / v preparation: one warp per (token, head) -----------------------------------------------------------------
+// Queries: norm (weights) + RoPE, times scale*log2(e), f16 [token][head][256].  Keys: norm (weights) + RoPE -> cache
+// slot (pos0 + token) % cap; values: norm without weights -> cache.  A lane holds dims 4l..4l+3 and 128+4l..128+4l+3.
+__global__ void __launch_bounds__(128) prefill_qkv_kernel(const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out,
+                                                          __half* kc, __half* vc, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps,
+                                                          float qscale) {
+    const uint32_t rows = heads + 2 * kv_heads;
+    const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows, r = item % rows;
+    const int lane = threadIdx.x & 31;
+    const float* src = qkv + ((size_t)token * rows + r) * D;
+    const float4 a = *reinterpret_cast<const float4*>(src + 4 * lane), b = *reinterpret_cast<const float4*>(src + 128 + 4 * lane);
+    float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) ss = fmaf(x[i], x[i], ss);
+    const float rn = rsqrtf(warp_sum(ss) / (float)D + eps);
+    const bool is_q = r < heads, is_k = !is_q && r < heads + kv_heads;
+    const float* w = is_q ? q_norm : (is_k ? k_norm : nullptr);
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] *= rn * (w ? __ldg(w + (i < 4 ? 4 * lane + i : 128 + 4 * lane + i - 4)) : 1.0f);
+    const uint32_t pos = pos0 + token;
+    if (is_q || is_k) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float sn, cs;
+            sincosf((float)pos * __ldg(freq + 4 * lane + i), &sn, &cs);
+            const float p = x[i], q = x[i + 4];
+            x[i] = p * cs - q * sn;
+            x[i + 4] = q * cs + p * sn;
+        }
+    }
+    __half* dst;
+    if (is_q) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] *= qscale;
+        dst = q_out + ((size_t)token * heads + r) * D;
+    } else {
+        const uint32_t g = is_k ? r - heads : r - heads - kv_heads;
+        dst = (is_k ? kc : vc) + ((size_t)g * cap + pos % cap) * D;
+    }
+    const __half2 h0 = __floats2half2_rn(x[0], x[1]), h1 = __floats2half2_rn(x[2], x[3]), h2 = __floats2half2_rn(x[4], x[5]), h3 = __floats2half2_rn(x[6], x[7]);
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+    *reinterpret_cast<uint2*>(dst + 128 + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+}
+
+// ---- flash attention --------------------------------------------------------------------------------------------------
+// A block: 16 tokens x the 4 (or `group`) query heads of one key-value head; warp w owns head g*group + w (16 rows).
+// Keys are visited in tiles of 32 positions that start at multiples of 32, so a token's sums do not depend on how the
+// prompt was cut into chunks (ptx/flash.rs:9-17).  Token at position p sees positions p - window < j <= p.
+constexpr int FT = 16, FK = 32, LDS = D + 8;  // tokens per block, keys per tile, padded row length in halves
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) prefill_flash_kernel(const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0,
+                                                            uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads) {
+    extern __shared__ __align__(16) uint8_t raw[];
+    __half* Qs = reinterpret_cast<__half*>(raw);   // [group * FT][LDS]
+    const uint32_t group = heads / kv_heads;
+    __half* Ks = Qs + group * FT * LDS;            // [FK][LDS]
+    __half* Vs = Ks + FK * LDS;                    // [FK][LDS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t t0 = blockIdx.x * FT, g = blockIdx.y;
+    const uint32_t nthreads = group * 32;
+
+    // Queries of this block: row w*16 + i is (head g*group + w, token t0 + i).
+    for (uint32_t c = tid; c < group * FT * (D / 8); c += nthreads) {
+        const uint32_t row = c / (D / 8), ch = c % (D / 8), w = row / FT, i = row % FT, t = t0 + i;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < tokens) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * heads + g * group + w) * D + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + row * LDS + ch * 8) = v;
+    }
+    const uint32_t p_first = pos0 + t0, p_last = pos0 + min(t0 + FT, tokens) - 1;
+    const uint32_t lo = p_first + 1 > window ? p_first + 1 - window : 0;  // oldest position any token of the block sees
+    const uint32_t tile0 = lo / FK * FK;
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const uint32_t row_a = lane >> 2, row_b = row_a + 8;                   // the two rows this lane holds
+    const uint32_t pa = pos0 + t0 + row_a, pb = pos0 + t0 + row_b;        // their positions
+
+    for (uint32_t j0 = tile0; j0 <= p_last; j0 += FK) {
+        __syncthreads();  // the previous tile is no longer read (and, first time, Qs is written)
+        for (uint32_t c = tid; c < FK * (D / 8); c += nthreads) {
+            const uint32_t r = c / (D / 8), ch = c % (D / 8), j = j0 + r;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (j <= p_last) {
+                const size_t at = ((size_t)g * cap + j % cap) * D + ch * 8;
+                kv = __ldg(reinterpret_cast<const uint4*>(kc + at));
+                vv = __ldg(reinterpret_cast<const uint4*>(vc + at));
+            }
+            *reinterpret_cast<uint4*>(Ks + r * LDS + ch * 8) = kv;
+            *reinterpret_cast<uint4*>(Vs + r * LDS + ch * 8) = vv;
+        }
+        __syncthreads();
+        // Scores S = Q K^T for this warp's 16 rows and the tile's 32 keys.
+        float sc[FK / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < FK / 8; nb++) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f;
+#pragma unroll 4
+        for (int ks = 0; ks < D / 16; ks++) {
+            uint32_t a[4];
+            ldmatrix_x4(a, Qs + (warp * FT + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < FK / 8; nb++) {
+                uint32_t b[2];
+                ldmatrix_x2(b, Ks + (nb * 8 + (lane & 7)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_16816(sc[nb], a, b);
+            }
+        }
+        // Mask, running maximum and sums (scores are already in base 2: the queries carry scale*log2(e)).
+        float mt[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < FK / 8; nb++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), p = (e < 2) ? pa : pb;
+                const bool seen = j <= p && j + window > p && p <= p_last;
+                sc[nb][e] = seen ? sc[nb][e] : -INFINITY;
+                mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 1));
+            mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 2));
+            const float mn = fmaxf(m_run[h], mt[h]);
+            corr[h] = (mn == -INFINITY) ? 1.0f : exp2f(m_run[h] - mn);  // a row that has seen nothing yet keeps its zeros
+            m_run[h] = mn;
+        }
+        float lt[2] = {0.0f, 0.0f};
+        uint32_t pfrag[FK / 16][4];
+#pragma unroll
+        for (int nb = 0; nb < FK / 8; nb++) {
+            float e0 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][0] - m_run[0]), e1 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][1] - m_run[0]);
+            float e2 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][2] - m_run[1]), e3 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][3] - m_run[1]);
+            const __half2 h01 = __floats2half2_rn(e0, e1), h23 = __floats2half2_rn(e2, e3);
+            // the sums use the rounded probabilities, the ones the values are weighted with
+            lt[0] += __low2float(h01) + __high2float(h01);
+            lt[1] += __low2float(h23) + __high2float(h23);
+            pfrag[nb / 2][(nb & 1) * 2] = *reinterpret_cast<const uint32_t*>(&h01);
+            pfrag[nb / 2][(nb & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            lt[h] += __shfl_xor_sync(0xffffffffu, lt[h], 1);
+            lt[h] += __shfl_xor_sync(0xffffffffu, lt[h], 2);
+            l_run[h] = l_run[h] * corr[h] + lt[h];
+        }
+        // O = O * corr + P V.
+#pragma unroll
+        for (int nb = 0; nb < D / 8; nb++) {
+            o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+#pragma unroll
+            for (int kk = 0; kk < FK / 16; kk++) {
+                uint32_t b[2];
+                ldmatrix_x2_trans(b, Vs + (kk * 16 + (lane & 15)) * LDS + nb * 8);
+                mma_16816(o[nb], pfrag[kk], b);
+            }
+        }
+    }
+    // Normalise and store f16 [token][heads * 256].
+    const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
+    const uint32_t head = g * group + warp;
+#pragma unroll
+    for (int nb = 0; nb < D / 8; nb++) {
+        const uint32_t col = head * D + nb * 8 + 2 * (lane & 3);
+        if (t0 + row_a < tokens) {
+            const __half2 v = __floats2half2_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_a) * heads * D + col) = v;
+        }
+        if (t0 + row_b < tokens) {
+            const __half2 v = __floats2half2_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
+            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_b) * heads * D + col) = v;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out) {
+    prefill_embed_kernel<<<n, 256, 0, ctx->stream>>>(w, s, tokens, cols, scale, out);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
+                        __half* x) {
+    if (n != 2048) return fail(UNSUPPORTED, "prefill norm: rows of 2048 values");
+    prefill_norm_kernel<<<tokens, 256, 0, ctx->stream>>>(h, y, w1, w2, n, eps, hscale, x);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
+                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale) {
+    const uint32_t items = tokens * (heads + 2 * kv_heads);
+    if (items % 4 != 0) return fail(UNSUPPORTED, "prefill qkv: heads + 2*kv_heads must be a multiple of 4");
+    prefill_qkv_kernel<<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps,
+                                                            scale * 1.4426950408889634f);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                         uint32_t window, uint32_t heads, uint32_t kv_heads) {
+    const uint32_t group = heads / kv_heads;
+    if (group < 1 || group > 4) return fail(UNSUPPORTED, "prefill attention: 1 to 4 query heads per key-value head");
+    const size_t smem = (size_t)(group * FT + 2 * FK) * LDS * 2;
+    static bool configured[16] = {};
+    if (!configured[ctx->gpu & 15]) {
+        TB_CUDA(cudaFuncSetAttribute(prefill_flash_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((4 * FT + 2 * FK) * LDS * 2)));
+        configured[ctx->gpu & 15] = true;
+    }
+    prefill_flash_kernel<<<dim3((tokens + FT - 1) / FT, kv_heads), group * 32, smem, ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+}  // namespace tb
