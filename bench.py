@@ -370,6 +370,89 @@ def bench_attend(args, ranks: Ranks):
             "roofline": {"bound": "hbm", "achieved": g["achieved_gbs"], "peak": peak, "unit": "GB/s", "frac": g["achieved_gbs"] / peak, "peak_source": how, "traffic": None}}
 
 
+def measured_peak_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+        return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def bench_gemm(args, ranks: Ranks):
+    """configs[3]'s GEMM shapes alone: M tokens x K -> N with Q8 weights dequantised in the operand path (tcgen05)."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    m, n, k = args.tokens, args.rows, args.cols
+    lib = ctx.lib
+    w, s = ctx.alloc(n * k), ctx.alloc(n * (k // 32) * 2)
+    tb.check(lib.tb_fill_codes(ctx.handle, 3, 1, w.ptr, n * k))
+    tb.check(lib.tb_fill_scales(ctx.handle, 3, 2, s.ptr, n * (k // 32), 0.02 / 127))
+    a = ctx.upload(np.random.default_rng(0).standard_normal((m, k)).astype(np.float16))
+    out = ctx.zeros(m * n * 4)
+    for _ in range(args.warmup):
+        ctx.gemm_q8(w, s, a, m, n, k, out, 0)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(args.steps):
+        ctx.gemm_q8(w, s, a, m, n, k, out, 0)
+    e1.record()
+    e1.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / args.steps
+    tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
+    burst, sustained, how = measured_peak_tflops()
+    return {"metric": "gemm_q8_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
+            "higher_is_better": True, "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05)", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3] GEMM: M={m} K={k} N={n}"}, "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "peak_source": how, "traffic": None,
+                         "flops_per_launch": 2.0 * m * n * k, "us_per_launch": us}}
+
+
+def bench_prefill(args, ranks: Ranks):
+    """configs[3]: one prompt of 2048 token ids through the 35-layer model; the last token goes through the decode step."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    cfg = tb.gemma4_e4b_shape()
+    T = args.tokens
+    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=args.chunk, keep_logits=False)
+    dec.fill_random(SEED)
+    dec.build()
+    prompt = np.array([(i * 7919 + 13) % cfg.vocab for i in range(T)], np.uint32)  # the reference's prompt (benches/generate.rs:47)
+    times, first = [], None
+    for it in range(args.warmup + args.steps):
+        dec.reset()
+        ctx.sync()
+        ranks.barrier()
+        t0 = time.perf_counter()
+        dec.prefill(prompt[:-1])
+        tok = dec.step(int(prompt[-1]))
+        dt = time.perf_counter() - t0
+        first = tok if first is None else first
+        assert tok == first, "prefill is deterministic"
+        if it >= args.warmup:
+            times.append(dt)
+    ms = statistics.median(times) * 1e3
+    ms_max = ranks.max(ms)
+    # arithmetic of the prompt (the last layer stops after its cache writes; its query/key/value product still runs)
+    per_layer = (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden + cfg.hidden * cfg.heads * cfg.head_dim + 3 * cfg.ffn * cfg.hidden
+    flops = 2.0 * (T - 1) * (per_layer * (cfg.layers - 1) + (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden)
+    burst, sustained, how = measured_peak_tflops()
+    tf = flops / (ms_max * 1e-3) / 1e12
+    dec.close()
+    n = ranks.world
+    return {"metric": "prefill_tokens_per_second", "value": n * T / (ms_max / 1e3), "unit": "tok/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape Q8, chunks of {args.chunk}, last token through the decode step",
+                       "timing": "host wall clock around tb_decoder_prefill + tb_decoder_step (token ids cross from host memory)"},
+            "gpu_launches": None, "first_token": int(first),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained, "peak_source": how + " (sustained)",
+                         "traffic": None, "gemm_flops": flops}}
+
+
 def reference_arm(args, ranks: Ranks):
     """The reference's implementation of the path, on the host cores.  The reference (Rust + generated PTX) cannot be
     built in this environment, so this arm times the CPU oracle's restatement of its decode step on the same model."""
@@ -393,7 +476,9 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "attend"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "attend", "gemm", "prefill"])
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--chunk", type=int, default=512)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
@@ -409,6 +494,10 @@ def main():
             line = bench_gemv(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "attend":
             line = bench_attend(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "gemm":
+            line = bench_gemm(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "prefill":
+            line = bench_prefill(args, ranks)
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu:

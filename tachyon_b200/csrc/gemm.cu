@@ -1,17 +1,18 @@
 // Prefill GEMM on the fifth-generation tensor cores: D[M, N] = A[M, K] (f16 activations) x W[N, K]^T with W in the
 // decode path's Q8 layout (int8 codes + one f16 scale per 32 along K), f32 accumulation in tensor memory.
 // Stands in for the reference's gemm_q4 (crates/tachyon/src/ptx/gemm.rs:225-259: integer mma.sync on Q4 x Q8P) and its
-// split-K sum (gemm.rs:287-325), which the TMEM accumulator makes unnecessary: a block owns a 128 x 128 output tile
-// over the whole K.
+// split-K sum (gemm.rs:287-325), which the TMEM accumulator makes unnecessary: a block owns one output tile
+// over the whole K (128 or 256 tokens x 256 outputs).
 //
-// One block, six warps:
+// One block, ten warps:
 //   warp 0      one thread issues the TMA loads of the activation tile (128 rows x 64 halves, 128-byte swizzle);
-//   warp 1      allocates tensor memory; one thread issues tcgen05.mma (M128 N128 K16, four per stage) and commits;
-//   warps 2-5   dequantise the weight tile: thread j reads row j's 64 codes and two scales, turns the codes into f16
+//   warp 1      allocates tensor memory; one thread issues tcgen05.mma (M128 N256 K16: the widest shape, so that the
+//               operand reads from shared memory stay below the tensor core's rate) and commits;
+//   warps 2-9   dequantise the weight tile: thread j reads row j's 64 codes and two scales, turns the codes into f16
 //               exactly (0x6400 | (code ^ 0x80) is 1024 + code + 128; minus 1152), multiplies by the scale and stores
 //               the row in the same swizzled K-major layout TMA would have produced; after the main loop the same
 //               warps read the accumulator back (tcgen05.ld) and write the output (f32, f16, or GeGLU of column pairs).
-// Stages hand over on mbarriers: full = TMA bytes + the four dequantising warps, empty = tcgen05.commit.
+// Stages hand over on mbarriers: full = TMA bytes + the eight dequantising warps, empty = tcgen05.commit.
 // Operands are f16 rather than bf16: the code -> f16 step is exact and costs one instruction per two weights, the
 // tensor rate is the same, and the activations that reach this kernel are normalised.
 #include <cuda.h>
@@ -23,11 +24,11 @@ namespace tb {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;  // tile; BK halves = one 128-byte swizzle row
-constexpr int STAGES = 4;
-constexpr int THREADS = 192;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256;
+constexpr int BM = 128, BN = 256, BK = 64;  // MMA shape M128 N256; BK halves = one 128-byte swizzle row
+constexpr int stages(int mt) { return mt == 2 ? 3 : 4; }
+constexpr int THREADS = 64 + 256;  // TMA warp, MMA warp, eight dequantising / epilogue warps
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;  // per 128-row sub-tile of activations, per weight tile
+constexpr int smem_bytes(int mt) { return 1024 + stages(mt) * (mt * A_BYTES + B_BYTES) + 256; }
 
 // tcgen05.mma instruction descriptor, kind::f16: f32 accumulator, f16 A and B, both K-major, N = 128, M = 128.
 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -89,26 +90,31 @@ struct GemmArgs {
     int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU of column pairs, f16 [M, N / 2]
 };
 
+// MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
+// dequantisation is shared by twice the tensor-core work.
+template <int MT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const GemmArgs g, uint32_t* status) {
+    constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
     extern __shared__ uint8_t raw_unaligned[];
     uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
     uint8_t* As = raw;
-    uint8_t* Bs = raw + STAGES * A_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(raw + STAGES * (A_BYTES + B_BYTES));
+    uint8_t* Bs = raw + STAGES * AS;
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + STAGES * (AS + B_BYTES));
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, nk = g.K / BK;
+    // Consecutive blocks share a weight tile (their reads of it meet in the L2) and differ in the token tile.
+    const uint32_t m0 = blockIdx.x * (MT * BM), n0 = blockIdx.y * BN, nk = g.K / BK;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 5), mbar_init(&empty[i], 1);
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 9), mbar_init(&empty[i], 1);
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)(MT * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -126,8 +132,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                     ok = false;
                     break;
                 }
-                mbar_expect_tx(&full[s], A_BYTES);
-                tma_load_2d(As + s * A_BYTES, &a_map, (int)(kt * BK), (int)m0, &full[s]);
+                mbar_expect_tx(&full[s], AS);
+                tma_load_2d(As + s * AS, &a_map, (int)(kt * BK), (int)m0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -140,47 +146,74 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a = smem_addr(As + s * A_BYTES), b = smem_addr(Bs + s * B_BYTES);
+                const uint32_t a = smem_addr(As + s * AS), b = smem_addr(Bs + s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) mma_f16(tmem, smem_desc(a + k * 32), smem_desc(b + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)
+                        mma_f16(tmem + mt * BN, smem_desc(a + mt * A_BYTES + k * 32), smem_desc(b + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
                 mma_commit(&empty[s]);
             }
             mma_commit(acc_full);  // arrives when every MMA above has finished (also after an early exit)
         }
     } else {
-        // Weight tile: thread j owns row n0 + j.
-        const int j = threadIdx.x - 64;
-        const uint32_t n = n0 + j;
-        const bool live = n < g.N;
-        const int8_t* wrow = g.w + (size_t)(live ? n : 0) * g.K;
-        const __half* srow = g.s + (size_t)(live ? n : 0) * (g.K / 32);
+        // Weight tile: 256 rows x 64 codes = 1024 pieces of 16 codes; thread j takes pieces j, j + 256, j + 512, j + 768
+        // (piece p: row p / 4, quarter p % 4), so a warp's load covers eight rows' whole 64-byte segments instead of
+        // thirty-two separate lines.  A row's scales for four tiles come in one 16-byte load every fourth tile.  The
+        // next tile's codes are fetched before this one's are stored.
+        const int j = threadIdx.x - 64, qtr = j & 3;
         uint4 c[4];
-        __half s0, s1;
+        uint4 sc8[4];  // per piece: the row's eight scales covering tiles kt & ~3 ... + 3
         auto fetch = [&](uint32_t kt) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) c[q] = live ? __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)kt * BK) + q) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
-            s0 = live ? srow[kt * 2] : __float2half(0.0f);
-            s1 = live ? srow[kt * 2 + 1] : __float2half(0.0f);
+            for (int it = 0; it < 4; it++) {
+                const uint32_t row = it * 64 + (j >> 2), n = n0 + row;
+                const bool live = n < g.N;
+                c[it] = live ? __ldg(reinterpret_cast<const uint4*>(g.w + (size_t)n * g.K + (size_t)kt * BK + qtr * 16))
+                             : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+                if ((kt & 3) == 0) {
+                    // K is a multiple of 64: the last group of four tiles may be short, a 16-byte load still stays
+                    // inside the row when K is a multiple of 256; otherwise fall back to single scales.
+                    const __half* sp = g.s + (size_t)n * (g.K / 32) + kt * 2;
+                    if (live && kt * 2 + 8 <= g.K / 32 && (g.K / 32) % 8 == 0) {
+                        sc8[it] = __ldg(reinterpret_cast<const uint4*>(sp));
+                    } else {
+                        __half t[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) t[e] = (live && kt * 2 + e < g.K / 32) ? sp[e] : __float2half(0.0f);
+                        sc8[it] = *reinterpret_cast<const uint4*>(t);
+                    }
+                }
+            }
         };
         if (nk > 0) fetch(0);
         for (uint32_t kt = 0; kt < nk; kt++) {
             const uint32_t s = kt % STAGES;
-            uint32_t v[32];  // 64 halves
-            {
-                const __half2 sc0 = __half2half2(s0), sc1 = __half2half2(s1);
-                const uint32_t w[16] = {c[0].x, c[0].y, c[0].z, c[0].w, c[1].x, c[1].y, c[1].z, c[1].w, c[2].x, c[2].y, c[2].z, c[2].w, c[3].x, c[3].y, c[3].z, c[3].w};
+            uint32_t v[4][8];  // per piece 16 halves
 #pragma unroll
-                for (int q = 0; q < 16; q++) dequant4(w[q], q < 8 ? sc0 : sc1, v[2 * q], v[2 * q + 1]);
+            for (int it = 0; it < 4; it++) {
+                // scale of this piece's group of 32: tile kt's two scales are halves 2*(kt&3) and 2*(kt&3)+1
+                const uint32_t words[4] = {sc8[it].x, sc8[it].y, sc8[it].z, sc8[it].w};
+                const uint32_t pair = words[kt & 3];
+                const __half sh = __ushort_as_half((unsigned short)((qtr & 2) ? (pair >> 16) : (pair & 0xffffu)));
+                const __half2 s2 = __half2half2(sh);
+                dequant4(c[it].x, s2, v[it][0], v[it][1]);
+                dequant4(c[it].y, s2, v[it][2], v[it][3]);
+                dequant4(c[it].z, s2, v[it][4], v[it][5]);
+                dequant4(c[it].w, s2, v[it][6], v[it][7]);
             }
-            if (kt + 1 < nk) fetch(kt + 1);  // the next tile's codes are on their way while this one is stored
+            if (kt + 1 < nk) fetch(kt + 1);
             if (ok && kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) {
                 atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                 ok = false;
             }
-            uint8_t* row = Bs + s * B_BYTES + j * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *reinterpret_cast<uint4*>(row + ((ch ^ (j & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+            for (int it = 0; it < 4; it++) {
+                const uint32_t row = it * 64 + (j >> 2);
+                uint8_t* base = Bs + s * B_BYTES + row * 128;
+                *reinterpret_cast<uint4*>(base + (((2 * qtr) ^ (row & 7)) << 4)) = make_uint4(v[it][0], v[it][1], v[it][2], v[it][3]);
+                *reinterpret_cast<uint4*>(base + (((2 * qtr + 1) ^ (row & 7)) << 4)) = make_uint4(v[it][4], v[it][5], v[it][6], v[it][7]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
@@ -191,11 +224,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             ok = false;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t q = warp & 3, rrow = 32 * q + lane, m = m0 + rrow;
+        // Two warps share each quarter of the accumulator's lanes and take alternate column blocks.
+        const uint32_t q = warp & 3, rrow = 32 * q + lane;
 #pragma unroll 1
-        for (int cb = 0; cb < BN / 32; cb++) {
+        for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += 2) {
+            const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
+            const uint32_t m = m0 + mt * BM + rrow;
             uint32_t r[32];
-            tmem_load32(tmem + ((32 * q) << 16) + cb * 32, r);
+            tmem_load32(tmem + ((32 * q) << 16) + mt * BN + cb * 32, r);
             if (m < g.M && ok) {
                 const uint32_t col = n0 + cb * 32;
                 if (g.mode == 0) {
@@ -236,7 +272,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(MT * BN)) : "memory");
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -266,18 +302,22 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     CUtensorMap map;
     const cuuint64_t dims[2] = {K, M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {BK, BM}, elem[2] = {1, 1};
+    // Two token sub-tiles share a dequantised weight tile when that still leaves enough blocks for the machine.
+    const int mt = (M > (uint32_t)BM && (uint64_t)((M + 255) / 256) * ((N + BN - 1) / BN) >= (uint64_t)ctx->sms * 3 / 4) ? 2 : 1;
+    const cuuint32_t box[2] = {BK, (cuuint32_t)(mt * BM)}, elem[2] = {1, 1};
     const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(a), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
     static bool configured[16] = {};
     if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
+        TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
     GemmArgs g{w, s, out, M, N, K, mode};
-    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_q8_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(map, g, ctx->status);
+    const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
+    if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
+    else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
