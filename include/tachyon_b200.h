@@ -111,10 +111,12 @@ TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* s
  * Prefill product on the tensor cores: D[m, n] = A[m, k] x W[n, k]^T.  A: device f16 [m, k] row-major; W, scales: as
  * tb_gemv_q8; f32 accumulation.  mode TB_GEMM_F32: out f32 [m, n]; TB_GEMM_F16: out f16 [m, n]; TB_GEMM_GEGLU: columns
  * (2j, 2j+1) are (gate_j, up_j) and out is f16 [m, n/2] of gelu_tanh(gate) * up.  k a multiple of 64, n of 32.
+ * TB_GEMM_ADD: out f32 [m, n] += D (residual); TB_GEMM_GEGLU_ERF / TB_GEMM_GELU_ERF: the encoder's exact-form GELU, gated on
+ * column pairs (f16 [m, n/2]) or plain (f16 [m, n]) -- the store modes of gemm_q8 / gemm_f16 (ptx/encoder.rs:418-492).
  * Stands in for gemm_q4 with its split-K slices and sum_slices (crates/tachyon/src/ptx/gemm.rs:18-23, 225-259,
  * 287-325) and, in GeGLU mode, geglu_q8p (ptx/mod.rs:217-249).
  */
-enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2 };
+enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2, TB_GEMM_ADD = 3, TB_GEMM_GEGLU_ERF = 4, TB_GEMM_GELU_ERF = 5 };
 TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
 
 /* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
@@ -244,6 +246,37 @@ TB_API int tb_decoder_step_launches(tb_decoder* dec, uint32_t* launches);
 TB_API int tb_decoder_timeline(tb_decoder* dec, uint32_t token, uint64_t* host_out, uint32_t* phases);
 /* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */
 TB_API int tb_decoder_hidden(tb_decoder* dec, float* host_out);
+
+/* ---- encoder: crates/tachyon/src/encoder/{mod,run}.rs (Config, Encoder) ---- */
+
+typedef struct tb_encoder tb_encoder;
+
+/* encoder::Config (encoder/mod.rs:36-90) plus the benchmark's variants. */
+typedef struct tb_encoder_config {
+    uint32_t hidden, heads, inter, vocab, layers;
+    uint32_t window;        /* a sliding layer sees |i - j| <= window (Config::window = local_attention / 2) */
+    const uint8_t* global;  /* [layers] != 0 where a layer attends globally; NULL: every global_every-th from layer 0 */
+    uint32_t global_every;  /* with global == NULL (0 means 3, as the reference's default) */
+    float theta_global, theta_local, eps;
+    uint32_t gated;         /* != 0: Wi is [2*inter, hidden], MLP = gelu(first half) * second half (the reference); 0: plain GELU */
+    uint32_t mean_pool;     /* != 0: mean over a sequence's tokens; 0: its first token (the reference, run.rs:160-173) */
+    uint32_t dims;          /* leading dimensions kept (Matryoshka, encoder/text.rs:56-63); hidden keeps all */
+} tb_encoder_config;
+
+/* Encoder::open without the file loader: room for `tokens` packed tokens and `sequences` sequences a batch
+ * (encoder::Settings::tokens, encoder/mod.rs:23-33). */
+TB_API int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, tb_encoder** out);
+TB_API void tb_encoder_close(tb_encoder* enc);
+/* Tensors by converted-model name (encoder/convert.rs:79-105): embed (f16 [vocab, hidden]), embed_norm, final_norm,
+ * {l}.attn_norm (layer 0's is unused), {l}.mlp_norm (f32 [hidden]); matrices {l}.qkv, {l}.o, {l}.up, {l}.down as
+ * <name>.w (int8 codes) and <name>.s (f16 scale per 32 along a row). */
+TB_API int tb_encoder_load(tb_encoder* enc, const char* name, const void* data, size_t bytes);
+TB_API int tb_encoder_fill_random(tb_encoder* enc, uint64_t seed);
+/* Encoder::embeddings (run.rs:161-175): ids packed back to back, lens[s] tokens each; out_host: dims f32 per sequence,
+ * L2-normalised. */
+TB_API int tb_encoder_embed(tb_encoder* enc, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host);
+/* The last batch's final hidden states, f32 [tokens, hidden] (for parity checks). */
+TB_API int tb_encoder_hidden(tb_encoder* enc, float* out_host);
 
 #ifdef __cplusplus
 }

@@ -52,6 +52,15 @@ class Model(C.Structure):
     _fields_ = [("cfg", Config), ("embed", C.c_void_p), ("embed_s", C.c_void_p), ("norm", C.c_void_p), ("layers", C.POINTER(Layer))]
 
 
+class EncConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "heads", "inter", "vocab", "layers", "window", "gated")] + [
+        (n, C.c_float) for n in ("theta_global", "theta_local", "eps")] + [("global_", C.c_void_p)]
+
+
+class EncLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "qkv", "o", "mlp_norm", "up", "down")]
+
+
 def _declare(l: C.CDLL) -> None:
     vp, sz, u32, u64, i32, f32, f64 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_double
     sig = {
@@ -77,6 +86,8 @@ def _declare(l: C.CDLL) -> None:
         "tbo_fill_gauss_f16": (None, [u64, u64, vp, sz, f32]),
         "tbo_fill_gauss_f32": (None, [u64, u64, vp, sz, f32]),
         "tbo_decoder_step": (C.c_int32, [C.POINTER(Model), u32, u32, vp, i32, vp]),
+        "tbo_encoder_forward": (None, [C.POINTER(EncConfig), vp, vp, C.POINTER(EncLayer), vp, vp, sz, vp]),
+        "tbo_erf_as": (f32, [f32]),
         "tbo_threads": (i32, []),
         "tbo_set_threads": (None, [i32]),
     }
@@ -211,3 +222,24 @@ def fill_gauss_f32(seed, stream, n, mul=1.0):
     x = np.zeros(n, np.float32)
     lib().tbo_fill_gauss_f32(seed, stream, ptr(x), n, mul)
     return x
+
+
+def encoder_forward(cfg: dict, weights: dict, ids) -> np.ndarray:
+    """Last hidden states [n, hidden] of one sequence.  cfg: hidden, heads, inter, vocab, window, gated, theta_global,
+    theta_local, eps, global (list of bool).  weights: f32 arrays named embed, embed_norm, {l}.attn_norm (absent in
+    layer 0), {l}.qkv, {l}.o, {l}.mlp_norm, {l}.up, {l}.down, final_norm."""
+    layers = len(cfg["global"])
+    keep = {k: np.ascontiguousarray(v, np.float32) for k, v in weights.items()}
+    glob = np.array([1 if g else 0 for g in cfg["global"]], np.uint8)
+    c = EncConfig(hidden=cfg["hidden"], heads=cfg["heads"], inter=cfg["inter"], vocab=cfg["vocab"], layers=layers, window=cfg["window"],
+                  gated=int(cfg.get("gated", 1)), theta_global=cfg["theta_global"], theta_local=cfg["theta_local"], eps=cfg["eps"], global_=glob.ctypes.data)
+    arr = (EncLayer * layers)()
+    for l in range(layers):
+        arr[l].attn_norm = keep[f"{l}.attn_norm"].ctypes.data if f"{l}.attn_norm" in keep else None
+        for name in ("qkv", "o", "mlp_norm", "up", "down"):
+            setattr(arr[l], name, keep[f"{l}.{name}"].ctypes.data)
+    ids = np.ascontiguousarray(ids, np.uint32)
+    out = np.zeros((ids.size, cfg["hidden"]), np.float32)
+    lib().tbo_encoder_forward(C.byref(c), ptr(keep["embed"]), ptr(keep["embed_norm"]), C.cast(arr, C.POINTER(EncLayer)), ptr(keep["final_norm"]),
+                              ptr(ids), ids.size, ptr(out))
+    return out

@@ -588,3 +588,119 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
 TBO_API int tbo_threads(void) { return threads_now(); }
 
 TBO_API void tbo_set_threads(int n) { g_threads = n > 256 ? 256 : n; }
+
+/* ------------------------------------------------------------------------------------------------ */
+/* The ModernBERT-style encoder forward, f32, one sequence.  crates/tachyon/tests/encoder.rs:29-123    */
+/* (linear, norm, erf to 1.5e-7 by Abramowitz-Stegun 7.1.26, gelu, attend with RoPE and window, encode). */
+/* Pinned by the reference's tiny-encoder fixture (PyTorch hidden states), see tests/golden.           */
+/* ------------------------------------------------------------------------------------------------ */
+
+typedef struct {
+    int32_t hidden, heads, inter, vocab, layers, window, gated;
+    float theta_global, theta_local, eps;
+    const uint8_t *global; /* [layers] */
+} tbo_enc_config;
+
+typedef struct {
+    const float *attn_norm; /* NULL in layer 0 */
+    const float *qkv, *o, *mlp_norm, *up, *down;
+} tbo_enc_layer;
+
+/* encoder.rs:29-35 (no bias) */
+static void enc_linear(const float *x, const float *w, size_t n, size_t cols, size_t out, float *y) {
+    for (size_t r = 0; r < n; r++)
+        for (size_t o = 0; o < out; o++) {
+            float s = 0.0f;
+            for (size_t c = 0; c < cols; c++) s += x[r * cols + c] * w[o * cols + c];
+            y[r * out + o] = s;
+        }
+}
+
+/* encoder.rs:38-48 */
+static void enc_norm(const float *x, const float *w, size_t n, size_t h, float eps, float *y) {
+    for (size_t r = 0; r < n; r++) {
+        float mean = 0.0f, var = 0.0f;
+        for (size_t i = 0; i < h; i++) mean += x[r * h + i];
+        mean /= (float)h;
+        for (size_t i = 0; i < h; i++) var += (x[r * h + i] - mean) * (x[r * h + i] - mean);
+        var /= (float)h;
+        float rs = 1.0f / sqrtf(var + eps);
+        for (size_t i = 0; i < h; i++) y[r * h + i] = (x[r * h + i] - mean) * rs * w[i];
+    }
+}
+
+/* encoder.rs:51-59 */
+TBO_API float tbo_erf_as(float x) {
+    float t = 1.0f / (1.0f + 0.3275911f * fabsf(x));
+    float p = t * (0.2548296f + t * (-0.28449674f + t * (1.4214137f + t * (-1.4531521f + t * 1.0614054f))));
+    return copysignf(1.0f - p * expf(-x * x), x);
+}
+static float enc_gelu(float x) { return 0.5f * x * (1.0f + tbo_erf_as(x / 1.41421356237f)); }
+
+/* encoder.rs:67-101: RoPE by row index, window |i - j| <= w or none (w < 0), scale 1/sqrt(d). */
+static void enc_attend(const float *qkv, size_t n, size_t heads, size_t d, long window, float theta, float *out) {
+    size_t h = heads * d;
+    float *q = (float *)malloc(n * h * 4), *k = (float *)malloc(n * h * 4), *sc = (float *)malloc(n * 4);
+    for (size_t r = 0; r < n; r++)
+        for (int part = 0; part < 2; part++) {
+            float *dst = (part ? k : q) + r * h;
+            memcpy(dst, qkv + r * 3 * h + (size_t)part * h, h * 4);
+            for (size_t hd = 0; hd < heads; hd++)
+                for (size_t j = 0; j < d / 2; j++) {
+                    float ang = (float)r * powf(theta, -2.0f * (float)j / (float)d), c = cosf(ang), s = sinf(ang);
+                    float a = dst[hd * d + j], b = dst[hd * d + j + d / 2];
+                    dst[hd * d + j] = a * c - b * s;
+                    dst[hd * d + j + d / 2] = b * c + a * s;
+                }
+        }
+    memset(out, 0, n * h * 4);
+    for (size_t i = 0; i < n; i++)
+        for (size_t hd = 0; hd < heads; hd++) {
+            float top = -INFINITY, sum = 0.0f;
+            for (size_t j = 0; j < n; j++) {
+                long dist = (long)i - (long)j;
+                if (window >= 0 && (dist > window || -dist > window)) { sc[j] = -INFINITY; continue; }
+                float s = 0.0f;
+                for (size_t t = 0; t < d; t++) s += q[i * h + hd * d + t] * k[j * h + hd * d + t];
+                sc[j] = s / sqrtf((float)d);
+                if (sc[j] > top) top = sc[j];
+            }
+            for (size_t j = 0; j < n; j++) { sc[j] = sc[j] == -INFINITY ? 0.0f : expf(sc[j] - top); sum += sc[j]; }
+            for (size_t j = 0; j < n; j++) {
+                if (sc[j] == 0.0f) continue;
+                float p = sc[j] / sum;
+                for (size_t t = 0; t < d; t++) out[i * h + hd * d + t] += p * qkv[j * 3 * h + 2 * h + hd * d + t];
+            }
+        }
+    free(q); free(k); free(sc);
+}
+
+/* encoder.rs:104-123.  gated: Wi is [2*inter, h] and the MLP is gelu(first half) * second half; otherwise Wi is
+ * [inter, h] and the MLP is gelu(Wi x) (the benchmark's plain GeLU FFN).  hidden_out: [n, hidden]. */
+TBO_API void tbo_encoder_forward(const tbo_enc_config *c, const float *embed, const float *embed_norm, const tbo_enc_layer *layers,
+                                 const float *final_norm, const uint32_t *ids, size_t n, float *hidden_out) {
+    size_t h = (size_t)c->hidden, inter = (size_t)c->inter, d = h / (size_t)c->heads, up_rows = c->gated ? 2 * inter : inter;
+    float *x = (float *)malloc(n * h * 4), *a = (float *)malloc(n * h * 4), *qkv = (float *)malloc(n * 3 * h * 4);
+    float *att = (float *)malloc(n * h * 4), *up = (float *)malloc(n * up_rows * 4), *g = (float *)malloc(n * inter * 4);
+    for (size_t r = 0; r < n; r++) memcpy(a + r * h, embed + (size_t)ids[r] * h, h * 4);
+    enc_norm(a, embed_norm, n, h, c->eps, x);
+    for (int l = 0; l < c->layers; l++) {
+        const tbo_enc_layer *L = &layers[l];
+        if (L->attn_norm) enc_norm(x, L->attn_norm, n, h, c->eps, a);
+        else memcpy(a, x, n * h * 4);
+        enc_linear(a, L->qkv, n, h, 3 * h, qkv);
+        int global = c->global[l] != 0;
+        enc_attend(qkv, n, (size_t)c->heads, d, global ? -1 : (long)c->window, global ? c->theta_global : c->theta_local, att);
+        enc_linear(att, L->o, n, h, h, a);
+        for (size_t i = 0; i < n * h; i++) x[i] += a[i];
+        enc_norm(x, L->mlp_norm, n, h, c->eps, a);
+        enc_linear(a, L->up, n, h, up_rows, up);
+        for (size_t r = 0; r < n; r++)
+            for (size_t i = 0; i < inter; i++)
+                g[r * inter + i] = c->gated ? enc_gelu(up[r * up_rows + i]) * up[r * up_rows + inter + i] : enc_gelu(up[r * up_rows + i]);
+        enc_linear(g, L->down, n, inter, h, a);
+        for (size_t i = 0; i < n * h; i++) x[i] += a[i];
+    }
+    enc_norm(x, final_norm, n, h, c->eps, hidden_out);
+    free(x); free(a); free(qkv); free(att); free(up); free(g);
+}

@@ -12,7 +12,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import Attend, Config, Settings
+from ._lib import Attend, Config, EncoderConfig, Settings
 
 F32, F16 = 0, 1
 
@@ -281,3 +281,46 @@ class Decoder:
         n = C.c_uint32(0)
         check(self.lib.tb_decoder_step_launches(self.handle, C.byref(n)))
         return n.value
+
+
+def granite_311m_shape(layers: int = 22, vocab: int = 50368) -> EncoderConfig:
+    """The benchmark's Granite-embedding-311m-shaped encoder: 22 layers, width 768, 12 heads of 64, plain GELU FFN of 3072,
+    every third layer global and the others within 64 positions either way, mean-pooled, 256 dimensions kept."""
+    return EncoderConfig(hidden=768, heads=12, inter=3072, vocab=vocab, layers=layers, window=64, global_=None, global_every=3, theta_global=160000.0,
+                         theta_local=10000.0, eps=1e-5, gated=0, mean_pool=1, dims=256)
+
+
+class Encoder:
+    """encoder::Encoder (crates/tachyon/src/encoder/run.rs:68-90): open, load or fill, then embed packed batches."""
+
+    def __init__(self, ctx: Context, cfg: EncoderConfig, tokens: int = 4096, sequences: int = 64):
+        self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
+        h = C.c_void_p()
+        check(self.lib.tb_encoder_open(ctx.handle, C.byref(cfg), tokens, sequences, C.byref(h)))
+        self.handle = h.value
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_encoder_close(self.handle)
+            self.handle = None
+
+    def load(self, name: str, a: np.ndarray) -> None:
+        a = np.ascontiguousarray(a)
+        check(self.lib.tb_encoder_load(self.handle, name.encode(), a.ctypes.data, a.nbytes))
+
+    def fill_random(self, seed: int) -> None:
+        check(self.lib.tb_encoder_fill_random(self.handle, seed))
+
+    def embed(self, sequences) -> np.ndarray:
+        """Embeddings [len(sequences), dims] of lists of token ids, packed into one batch."""
+        lens = np.array([len(q) for q in sequences], np.uint32)
+        ids = np.concatenate([np.asarray(q, np.uint32) for q in sequences])
+        out = np.zeros((len(sequences), self.cfg.dims), np.float32)
+        check(self.lib.tb_encoder_embed(self.handle, ids.ctypes.data, lens.ctypes.data, len(sequences), out.ctypes.data))
+        self._tokens = int(lens.sum())
+        return out
+
+    def hidden(self) -> np.ndarray:
+        out = np.zeros((self._tokens, self.cfg.hidden), np.float32)
+        check(self.lib.tb_encoder_hidden(self.handle, out.ctypes.data))
+        return out

@@ -30,6 +30,11 @@ class Config(C.Structure):
     ]
 
 
+class EncoderConfig(C.Structure):
+    _fields_ = [("hidden", u32), ("heads", u32), ("inter", u32), ("vocab", u32), ("layers", u32), ("window", u32), ("global_", vp), ("global_every", u32),
+                ("theta_global", f32), ("theta_local", f32), ("eps", f32), ("gated", u32), ("mean_pool", u32), ("dims", u32)]
+
+
 class Settings(C.Structure):
     _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32)]
 
@@ -88,6 +93,12 @@ SIGNATURES = {
     "tb_decoder_step_bytes": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
     "tb_decoder_step_launches": (i32, [vp, C.POINTER(u32)]),
     "tb_decoder_hidden": (i32, [vp, vp]),
+    "tb_encoder_open": (i32, [vp, C.POINTER(EncoderConfig), u32, u32, pp]),
+    "tb_encoder_close": (None, [vp]),
+    "tb_encoder_load": (i32, [vp, cp, vp, sz]),
+    "tb_encoder_fill_random": (i32, [vp, u64]),
+    "tb_encoder_embed": (i32, [vp, vp, vp, u32, vp]),
+    "tb_encoder_hidden": (i32, [vp, vp]),
     "tb_decoder_timeline": (i32, [vp, u32, vp, C.POINTER(u32)]),
 }
 

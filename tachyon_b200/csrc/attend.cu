@@ -33,6 +33,10 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, u
     }
     // The hint is about weights no kernel writes: ask for them before waiting for the previous kernel.
     if (tid == 0) prefetch_hint(p.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y);
+    // The norm weights and the RoPE table are model constants (2.5 KiB): ask the L2 for them ahead of the wait.
+    if (tid < 8 && p.q_norm != nullptr) prefetch_line_l2(p.q_norm + tid * 32);
+    else if (tid >= 8 && tid < 16 && p.k_norm != nullptr) prefetch_line_l2(p.k_norm + (tid - 8) * 32);
+    else if (tid >= 16 && tid < 20 && p.freq != nullptr) prefetch_line_l2(p.freq + (tid - 16) * 32);
     pdl_wait();
     pdl_launch_dependents();
     __syncthreads();

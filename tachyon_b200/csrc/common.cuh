@@ -167,6 +167,15 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return x / (1.0f + exp2f(-2.0f * 0.7978845608028654f * 1.4426950408889634f * u));
 }
 
+// erf to 1.5e-7 (Abramowitz and Stegun 7.1.26) and the exact-form GELU built on it, as the reference's encoder
+// computes them (crates/tachyon/src/ptx/encoder.rs:807-841).
+__device__ __forceinline__ float erf_as(float x) {
+    const float t = 1.0f / (1.0f + 0.3275911f * fabsf(x));
+    const float p = t * (0.2548296f + t * (-0.28449674f + t * (1.4214137f + t * (-1.4531521f + t * 1.0614054f))));
+    return copysignf(1.0f - p * __expf(-x * x), x);
+}
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erf_as(x * 0.70710678118f)); }
+
 // A float's bits as an unsigned key with the same order (for atomicMax on values).
 __device__ __forceinline__ uint32_t float_key(float v) {
     const uint32_t b = __float_as_uint(v);

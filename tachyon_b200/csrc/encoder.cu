@@ -1,0 +1,541 @@
+// The packed variable-length encoder (ModernBERT shape): kernels and host object.  Counterpart of
+// crates/tachyon/src/encoder/run.rs (layers 413-447, batches/tiles 207-221 and 354-373, embeddings 161-175) and of the
+// kernels in crates/tachyon/src/ptx/encoder.rs: embed_f16 + norm_f16 (582-668, 761-805), rope_f16 (893-959),
+// attend_f16 (961-1215), with the products on the tcgen05 GEMM (gemm.cu; its store modes replace ptx/encoder.rs:418-492).
+//
+// Sequences are packed back to back without padding: activations are [tokens, width]; attention works per sequence
+// through a list of 64-query tiles.  Weights are Q8 (int8 codes + f16 scale per 32), the embedding table f16.
+#include "../../include/tachyon_b200.h"
+#include "common.cuh"
+#include "internal.h"
+
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+namespace tb {
+
+namespace {
+
+// ---- layer norm without bias, one block per token -----------------------------------------------------------------------
+// y = (x - mean) / sqrt(var + eps) * w.  `ids` given: x is row ids[token] of the f16 table (embedding + its norm).
+// Outputs: f32 (optional) and f16 (optional).
+__global__ void __launch_bounds__(256) enc_norm_kernel(const float* x, const __half* table, const uint32_t* ids, const float* w, uint32_t h, float eps,
+                                                       float* out32, __half* out16) {
+    __shared__ float sh[8];
+    const uint32_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto block_sum = [&](float v) {
+        v = warp_sum(v);
+        __syncthreads();
+        if (lane == 0) sh[warp] = v;
+        __syncthreads();
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += sh[i];
+        return s;
+    };
+    float v[8];  // h <= 2048
+    int cnt = 0;
+    float sum = 0.0f;
+    for (uint32_t i = tid; i < h; i += 256, cnt++) {
+        v[cnt] = ids ? __half2float(table[(size_t)ids[t] * h + i]) : x[(size_t)t * h + i];
+        sum += v[cnt];
+    }
+    const float mean = block_sum(sum) / (float)h;
+    float var = 0.0f;
+    for (int c = 0; c < cnt; c++) var = fmaf(v[c] - mean, v[c] - mean, var);
+    const float rs = rsqrtf(block_sum(var) / (float)h + eps);
+    cnt = 0;
+    for (uint32_t i = tid; i < h; i += 256, cnt++) {
+        const float y = (v[cnt] - mean) * rs * __ldg(w + i);
+        if (out32) out32[(size_t)t * h + i] = y;
+        if (out16) out16[(size_t)t * h + i] = __float2half_rn(y);
+    }
+}
+
+// ---- RoPE in place on the q and k parts of f16 [tokens, 3h]: pairs (j, j + d/2) of every head turn by pos * freq[j] -------
+__global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32_t* pos, const float* freq, uint32_t h, uint32_t d) {
+    const uint32_t t = blockIdx.x, half_d = d / 2, pairs = h / 2;  // pairs per part
+    const float p = (float)pos[t];
+    for (uint32_t i = threadIdx.x; i < 2 * pairs; i += blockDim.x) {
+        const uint32_t part = i / pairs, r = i % pairs, head = r / half_d, j = r % half_d;
+        __half* base = qkv + (size_t)t * 3 * h + part * h + head * d;
+        float sn, cs;
+        sincosf(p * __ldg(freq + j), &sn, &cs);
+        const float a = __half2float(base[j]), b = __half2float(base[j + half_d]);
+        base[j] = __float2half_rn(a * cs - b * sn);
+        base[j + half_d] = __float2half_rn(b * cs + a * sn);
+    }
+}
+
+// ---- bidirectional attention over packed sequences -----------------------------------------------------------------------
+// A block: one tile of up to 64 queries of one sequence, one head; 4 warps x 16 query rows; keys in tiles of 64.
+// Query i sees key j of its sequence when |i - j| <= window (window < 0: all).  Scores scale by 1/sqrt(d).
+constexpr int QT = 64, KT = 64;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, int window) {
+    constexpr int LD = D + 8;
+    __shared__ __align__(16) __half Qs[QT * LD];
+    __shared__ __align__(16) __half Ks[KT * LD];
+    __shared__ __align__(16) __half Vs[KT * LD];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t start = tiles[blockIdx.x * 3], len = tiles[blockIdx.x * 3 + 1], q0 = tiles[blockIdx.x * 3 + 2], head = blockIdx.y;
+    const uint32_t nq = min((uint32_t)QT, len - q0);
+    const size_t row = (size_t)3 * h;
+    for (uint32_t c = tid; c < QT * (D / 8); c += 128) {
+        const uint32_t r = c / (D / 8), ch = c % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nq) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(start + q0 + r) * row + head * D + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * LD + ch * 8) = v;
+    }
+    const uint32_t lo = window < 0 ? 0u : (q0 > (uint32_t)window ? q0 - (uint32_t)window : 0u);
+    const uint32_t hi = window < 0 ? len : min(len, q0 + nq + (uint32_t)window);  // exclusive
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const uint32_t ia = q0 + warp * 16 + (lane >> 2), ib = ia + 8;  // the two query positions this lane holds
+    const float scale = 1.4426950408889634f * rsqrtf((float)D);
+
+    for (uint32_t j0 = lo; j0 < hi; j0 += KT) {
+        __syncthreads();
+        for (uint32_t c = tid; c < KT * (D / 8); c += 128) {
+            const uint32_t r = c / (D / 8), ch = c % (D / 8), j = j0 + r;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (j < hi) {
+                const __half* src = qkv + (size_t)(start + j) * row + head * D + ch * 8;
+                kv = *reinterpret_cast<const uint4*>(src + h);
+                vv = *reinterpret_cast<const uint4*>(src + 2 * h);
+            }
+            *reinterpret_cast<uint4*>(Ks + r * LD + ch * 8) = kv;
+            *reinterpret_cast<uint4*>(Vs + r * LD + ch * 8) = vv;
+        }
+        __syncthreads();
+        float sc[KT / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < KT / 8; nb++) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+            uint32_t a[4];
+            ldsm_x4(a, Qs + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < KT / 8; nb++) {
+                uint32_t b[2];
+                ldsm_x2(b, Ks + (nb * 8 + (lane & 7)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(sc[nb], a, b);
+            }
+        }
+        float mt[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < KT / 8; nb++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), i = (e < 2) ? ia : ib;
+                const bool seen = j < hi && i < len && (window < 0 || (j <= i + (uint32_t)window && i <= j + (uint32_t)window));
+                sc[nb][e] = seen ? sc[nb][e] * scale : -INFINITY;
+                mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 1));
+            mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 2));
+            const float mn = fmaxf(m_run[r], mt[r]);
+            corr[r] = (mn == -INFINITY) ? 1.0f : exp2f(m_run[r] - mn);
+            m_run[r] = mn;
+        }
+        float lt[2] = {0.0f, 0.0f};
+        uint32_t pf[KT / 16][4];
+#pragma unroll
+        for (int nb = 0; nb < KT / 8; nb++) {
+            const float e0 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][0] - m_run[0]), e1 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][1] - m_run[0]);
+            const float e2 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][2] - m_run[1]), e3 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][3] - m_run[1]);
+            const __half2 h01 = __floats2half2_rn(e0, e1), h23 = __floats2half2_rn(e2, e3);
+            lt[0] += __low2float(h01) + __high2float(h01);
+            lt[1] += __low2float(h23) + __high2float(h23);
+            pf[nb / 2][(nb & 1) * 2] = *reinterpret_cast<const uint32_t*>(&h01);
+            pf[nb / 2][(nb & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            lt[r] += __shfl_xor_sync(0xffffffffu, lt[r], 1);
+            lt[r] += __shfl_xor_sync(0xffffffffu, lt[r], 2);
+            l_run[r] = l_run[r] * corr[r] + lt[r];
+        }
+#pragma unroll
+        for (int nb = 0; nb < D / 8; nb++) {
+            o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+#pragma unroll
+            for (int kk = 0; kk < KT / 16; kk++) {
+                uint32_t b[2];
+                ldsm_x2_trans(b, Vs + (kk * 16 + (lane & 15)) * LD + nb * 8);
+                mma16816(o[nb], pf[kk], b);
+            }
+        }
+    }
+    const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
+#pragma unroll
+    for (int nb = 0; nb < D / 8; nb++) {
+        const uint32_t col = head * D + nb * 8 + 2 * (lane & 3);
+        if (ia < len) *reinterpret_cast<__half2*>(out + (size_t)(start + ia) * h + col) = __floats2half2_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+        if (ib < len) *reinterpret_cast<__half2*>(out + (size_t)(start + ib) * h + col) = __floats2half2_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
+    }
+}
+
+// ---- pooling: one block per sequence ---------------------------------------------------------------------------------------
+// The sequence's vector (first token, or the mean over its tokens) L2-normalised (max(len, 1e-12), as
+// encoder/run.rs:160-173), truncated to `dims` and normalised again when truncated (encoder/text.rs:56-63).
+__global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, const uint32_t* starts, const uint32_t* lens, uint32_t h, uint32_t dims, int mean,
+                                                       float* out) {
+    __shared__ float sh[8];
+    __shared__ float vec[2048];
+    const uint32_t s = blockIdx.x, start = starts[s], len = lens[s];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto block_sum = [&](float v) {
+        v = warp_sum(v);
+        __syncthreads();
+        if (lane == 0) sh[warp] = v;
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) t += sh[i];
+        return t;
+    };
+    float sq = 0.0f;
+    for (uint32_t i = tid; i < h; i += 256) {
+        float v = 0.0f;
+        if (mean) {
+            for (uint32_t t = 0; t < len; t++) v += hidden[(size_t)(start + t) * h + i];
+            v /= (float)len;
+        } else {
+            v = hidden[(size_t)start * h + i];
+        }
+        vec[i] = v;
+        sq = fmaf(v, v, sq);
+    }
+    const float n1 = fmaxf(sqrtf(block_sum(sq)), 1e-12f);
+    float sq2 = 0.0f;
+    for (uint32_t i = tid; i < dims; i += 256) {
+        const float v = vec[i] / n1;
+        vec[i] = v;
+        sq2 = fmaf(v, v, sq2);
+    }
+    const float n2 = dims < h ? fmaxf(sqrtf(block_sum(sq2)), 1e-12f) : 1.0f;
+    for (uint32_t i = tid; i < dims; i += 256) out[(size_t)s * dims + i] = vec[i] / n2;
+}
+
+struct EMat {
+    int8_t* w = nullptr;
+    __half* s = nullptr;
+    uint32_t rows = 0, cols = 0;
+    size_t code_bytes() const { return (size_t)rows * cols; }
+    size_t scale_bytes() const { return (size_t)rows * (cols / 32) * 2; }
+};
+
+struct ELayer {
+    EMat qkv, o, up, down;
+    float *attn_norm = nullptr, *mlp_norm = nullptr;
+    bool global = false;
+};
+
+}  // namespace
+}  // namespace tb
+
+using namespace tb;
+
+struct tb_encoder {
+    tb_context* ctx = nullptr;
+    tb_encoder_config cfg = {};
+    std::vector<uint8_t> global;
+    std::vector<ELayer> layers;
+    uint32_t cap_tokens = 0, cap_seqs = 0, tokens = 0;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    __half* embed = nullptr;
+    float *embed_norm = nullptr, *final_norm = nullptr, *freq[2] = {nullptr, nullptr};
+    float *x = nullptr, *hidden = nullptr, *pooled = nullptr;
+    __half *a16 = nullptr, *qkv16 = nullptr, *att16 = nullptr, *g16 = nullptr;
+    uint32_t *ids = nullptr, *pos = nullptr, *tiles = nullptr, *starts = nullptr, *lens = nullptr;
+};
+
+namespace {
+
+size_t enc_layout(tb_encoder* e, char* base) {
+    const tb_encoder_config& c = e->cfg;
+    size_t end = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = end;
+        end += (bytes + 255) / 256 * 256;
+        return base + at;
+    };
+    auto mat = [&](EMat& m, uint32_t rows, uint32_t cols) {
+        m.rows = rows, m.cols = cols;
+        m.w = reinterpret_cast<int8_t*>(take(m.code_bytes()));
+        m.s = reinterpret_cast<__half*>(take(m.scale_bytes()));
+    };
+    const uint32_t h = c.hidden, up_rows = c.gated ? 2 * c.inter : c.inter, T = e->cap_tokens, S = e->cap_seqs;
+    e->embed = reinterpret_cast<__half*>(take((size_t)c.vocab * h * 2));
+    e->embed_norm = reinterpret_cast<float*>(take(h * 4));
+    e->final_norm = reinterpret_cast<float*>(take(h * 4));
+    for (int k = 0; k < 2; k++) e->freq[k] = reinterpret_cast<float*>(take(h / c.heads / 2 * 4));
+    for (uint32_t l = 0; l < c.layers; l++) {
+        ELayer& L = e->layers[l];
+        L.global = e->global[l] != 0;
+        L.attn_norm = reinterpret_cast<float*>(take(h * 4));
+        L.mlp_norm = reinterpret_cast<float*>(take(h * 4));
+        mat(L.qkv, 3 * h, h), mat(L.o, h, h), mat(L.up, up_rows, h), mat(L.down, h, c.inter);
+    }
+    e->x = reinterpret_cast<float*>(take((size_t)T * h * 4));
+    e->hidden = reinterpret_cast<float*>(take((size_t)T * h * 4));
+    e->pooled = reinterpret_cast<float*>(take((size_t)S * h * 4));
+    e->a16 = reinterpret_cast<__half*>(take((size_t)T * h * 2));
+    e->qkv16 = reinterpret_cast<__half*>(take((size_t)T * 3 * h * 2));
+    e->att16 = reinterpret_cast<__half*>(take((size_t)T * h * 2));
+    e->g16 = reinterpret_cast<__half*>(take((size_t)T * c.inter * 2));
+    e->ids = reinterpret_cast<uint32_t*>(take((size_t)T * 4));
+    e->pos = reinterpret_cast<uint32_t*>(take((size_t)T * 4));
+    e->tiles = reinterpret_cast<uint32_t*>(take(((size_t)T / QT + S) * 3 * 4));
+    e->starts = reinterpret_cast<uint32_t*>(take((size_t)S * 4));
+    e->lens = reinterpret_cast<uint32_t*>(take((size_t)S * 4));
+    return end;
+}
+
+int enc_validate(const tb_encoder_config& c) {
+    if (c.hidden == 0 || c.heads == 0 || c.hidden % c.heads != 0) return fail(FORMAT, "encoder: an inconsistent shape");
+    const uint32_t d = c.hidden / c.heads;
+    if (d != 32 && d != 64) return fail(UNSUPPORTED, "encoder: head size 32 or 64");
+    if (c.hidden % 64 != 0 || c.inter % 64 != 0 || c.hidden > 2048) return fail(UNSUPPORTED, "encoder: widths must be multiples of 64, hidden at most 2048");
+    if (c.layers == 0 || c.vocab == 0 || c.inter == 0) return fail(OUT_OF_RANGE, "encoder: empty model");
+    if (c.dims == 0 || c.dims > c.hidden) return fail(OUT_OF_RANGE, "encoder: dims must be in 1..hidden");
+    return OK;
+}
+
+struct ENamed {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int kind = 0;  // 0 plain, 1 gated up codes, 2 gated up scales
+};
+
+bool enc_find(tb_encoder* e, const std::string& name, ENamed& out) {
+    const tb_encoder_config& c = e->cfg;
+    const size_t hb = (size_t)c.hidden * 4;
+    if (name == "embed") return out = {e->embed, (size_t)c.vocab * c.hidden * 2, 0}, true;
+    if (name == "embed_norm") return out = {e->embed_norm, hb, 0}, true;
+    if (name == "final_norm") return out = {e->final_norm, hb, 0}, true;
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos || dot == 0) return false;
+    uint32_t l = 0;
+    for (size_t k = 0; k < dot; k++) {
+        if (name[k] < '0' || name[k] > '9') return false;
+        l = l * 10 + (uint32_t)(name[k] - '0');
+    }
+    if (l >= c.layers) return false;
+    ELayer& L = e->layers[l];
+    const std::string rest = name.substr(dot + 1);
+    if (rest == "attn_norm") return out = {L.attn_norm, hb, 0}, true;
+    if (rest == "mlp_norm") return out = {L.mlp_norm, hb, 0}, true;
+    auto mat = [&](EMat& m, const std::string& suffix, bool gated_up) {
+        if (suffix == ".w") out = {m.w, m.code_bytes(), gated_up ? 1 : 0};
+        else if (suffix == ".s") out = {m.s, m.scale_bytes(), gated_up ? 2 : 0};
+        else return false;
+        return true;
+    };
+    if (rest.rfind("qkv", 0) == 0) return mat(L.qkv, rest.substr(3), false);
+    if (rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), false);
+    if (rest.rfind("up", 0) == 0) return mat(L.up, rest.substr(2), c.gated != 0);
+    if (rest.rfind("down", 0) == 0) return mat(L.down, rest.substr(4), false);
+    return false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, tb_encoder** out) {
+    if (!ctx || !cfg || !out || tokens == 0 || sequences == 0) return fail(OUT_OF_RANGE, "tb_encoder_open: null or empty argument");
+    *out = nullptr;
+    TB_TRY(enc_validate(*cfg));
+    tb_encoder* e = new tb_encoder();
+    e->ctx = ctx, e->cfg = *cfg, e->cap_tokens = tokens, e->cap_seqs = sequences;
+    e->global.resize(cfg->layers);
+    for (uint32_t l = 0; l < cfg->layers; l++) e->global[l] = cfg->global ? cfg->global[l] : (l % (cfg->global_every ? cfg->global_every : 3) == 0);
+    e->cfg.global = nullptr;
+    e->layers.resize(cfg->layers);
+    e->arena_bytes = enc_layout(e, nullptr);
+    cudaError_t err = cudaSetDevice(ctx->gpu);
+    if (err == cudaSuccess) err = cudaMalloc(&e->arena, e->arena_bytes);
+    if (err == cudaSuccess) err = cudaMemsetAsync(e->arena, 0, e->arena_bytes, ctx->stream);
+    if (err != cudaSuccess) {
+        delete e;
+        return cuda_fail(err, "tb_encoder_open");
+    }
+    enc_layout(e, e->arena);
+    // RoPE frequencies theta^(-2j/d): global layers', sliding layers' (encoder/run.rs:525-537 builds tables of these).
+    const uint32_t d = cfg->hidden / cfg->heads;
+    for (int k = 0; k < 2; k++) {
+        std::vector<float> f(d / 2);
+        for (uint32_t j = 0; j < d / 2; j++) f[j] = powf(k ? cfg->theta_local : cfg->theta_global, -2.0f * (float)j / (float)d);
+        err = cudaMemcpyAsync(e->freq[k], f.data(), f.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+        if (err != cudaSuccess) {
+            tb_encoder_close(e);
+            return cuda_fail(err, "tb_encoder_open: rope tables");
+        }
+    }
+    *out = e;
+    return OK;
+}
+
+void tb_encoder_close(tb_encoder* e) {
+    if (!e) return;
+    if (e->ctx && e->ctx->stream) cudaStreamSynchronize(e->ctx->stream);
+    if (e->arena) cudaFree(e->arena);
+    delete e;
+}
+
+int tb_encoder_load(tb_encoder* e, const char* name, const void* data, size_t bytes) {
+    if (!e || !name || !data) return fail(OUT_OF_RANGE, "tb_encoder_load: null argument");
+    ENamed t;
+    if (!enc_find(e, name, t)) return fail(NO_MODEL, std::string("tb_encoder_load: no tensor named ") + name);
+    if (bytes != t.bytes) return fail(FORMAT, std::string("tb_encoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
+    cudaStream_t s = e->ctx->stream;
+    if (t.kind == 0) {
+        TB_CUDA(cudaMemcpyAsync(t.ptr, data, bytes, cudaMemcpyHostToDevice, s));
+        TB_CUDA(cudaStreamSynchronize(s));
+        return OK;
+    }
+    // The gated MLP's Wi: activation rows, then gate rows in the file; pairs side by side on the device, so that a GEMM
+    // tile holds both (encoder/run.rs:449-466).
+    void* tmp = nullptr;
+    TB_CUDA(cudaMalloc(&tmp, bytes));
+    cudaError_t err = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, s);
+    int st = OK;
+    if (err == cudaSuccess) st = launch_interleave_rows(e->ctx, tmp, t.ptr, e->cfg.inter, (uint32_t)(bytes / (2 * (size_t)e->cfg.inter)));
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    cudaFree(tmp);
+    if (err != cudaSuccess) return cuda_fail(err, "tb_encoder_load");
+    return st;
+}
+
+int tb_encoder_fill_random(tb_encoder* e, uint64_t seed) {
+    if (!e) return fail(OUT_OF_RANGE, "null encoder");
+    const tb_encoder_config& c = e->cfg;
+    tb_context* ctx = e->ctx;
+    // Streams: 0 embed (f16 N(0,1)*0.02... as values), 1 embed_norm, 2 final_norm; layer l: 16*(l+1) + {0 qkv.w, 1 qkv.s, 2 o.w, 3 o.s,
+    // 4 up.w, 5 up.s, 6 down.w, 7 down.s, 8 attn_norm, 9 mlp_norm}.
+    TB_TRY(launch_fill_gauss_f16(ctx, seed, 0, e->embed, (size_t)c.vocab * c.hidden, 1.0f));
+    TB_TRY(launch_fill_uniform(ctx, seed, 1, e->embed_norm, c.hidden, 0.5f, 1.5f));
+    TB_TRY(launch_fill_uniform(ctx, seed, 2, e->final_norm, c.hidden, 0.5f, 1.5f));
+    const float smul = 0.02f / 127.0f;
+    void *tw = nullptr, *ts = nullptr;
+    if (c.gated) {
+        TB_CUDA(cudaMalloc(&tw, e->layers[0].up.code_bytes()));
+        TB_CUDA(cudaMalloc(&ts, e->layers[0].up.scale_bytes()));
+    }
+    int st = OK;
+    for (uint32_t l = 0; l < c.layers && st == OK; l++) {
+        ELayer& L = e->layers[l];
+        const uint64_t b = 16ull * (l + 1);
+        auto mat = [&](EMat& m, uint64_t id) -> int {
+            TB_TRY(launch_fill_codes(ctx, seed, id, m.w, m.code_bytes()));
+            return launch_fill_scales(ctx, seed, id + 1, m.s, m.scale_bytes() / 2, smul);
+        };
+        st = mat(L.qkv, b);
+        if (st == OK) st = mat(L.o, b + 2);
+        if (st == OK && c.gated) {
+            st = launch_fill_codes(ctx, seed, b + 4, static_cast<int8_t*>(tw), L.up.code_bytes());
+            if (st == OK) st = launch_fill_scales(ctx, seed, b + 5, static_cast<__half*>(ts), L.up.scale_bytes() / 2, smul);
+            if (st == OK) st = launch_interleave_rows(ctx, tw, L.up.w, c.inter, c.hidden);
+            if (st == OK) st = launch_interleave_rows(ctx, ts, L.up.s, c.inter, c.hidden / 32 * 2);
+        } else if (st == OK) {
+            st = mat(L.up, b + 4);
+        }
+        if (st == OK) st = mat(L.down, b + 6);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 8, L.attn_norm, c.hidden, 0.5f, 1.5f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 9, L.mlp_norm, c.hidden, 0.5f, 1.5f);
+    }
+    cudaStreamSynchronize(ctx->stream);
+    if (tw) cudaFree(tw);
+    if (ts) cudaFree(ts);
+    return st;
+}
+
+// Encoder::embeddings (encoder/run.rs:161-175): `ids` packed back to back, `lens[s]` tokens per sequence; out (host)
+// receives dims floats per sequence.
+int tb_encoder_embed(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host) {
+    if (!e || !ids || !lens || sequences == 0) return fail(OUT_OF_RANGE, "tb_encoder_embed: null or empty argument");
+    if (sequences > e->cap_seqs) return fail(TOO_LONG, "tb_encoder_embed: more sequences than the encoder was opened for");
+    const tb_encoder_config& c = e->cfg;
+    tb_context* ctx = e->ctx;
+    cudaStream_t s = ctx->stream;
+    const uint32_t h = c.hidden, d = h / c.heads;
+    // Host side of a batch: positions within each sequence, the 64-query tile list [start, len, first query] (run.rs:354-373).
+    std::vector<uint32_t> pos, tiles, starts(sequences);
+    uint32_t T = 0;
+    for (uint32_t q = 0; q < sequences; q++) {
+        if (lens[q] == 0) return fail(OUT_OF_RANGE, "tb_encoder_embed: an empty sequence");
+        starts[q] = T;
+        for (uint32_t i = 0; i < lens[q]; i++) pos.push_back(i);
+        for (uint32_t q0 = 0; q0 < lens[q]; q0 += QT) tiles.insert(tiles.end(), {T, lens[q], q0});
+        T += lens[q];
+        if (T > e->cap_tokens) return fail(TOO_LONG, "tb_encoder_embed: more tokens than the encoder was opened for");
+    }
+    for (uint32_t i = 0; i < T; i++)
+        if (ids[i] >= c.vocab) return fail(OUT_OF_RANGE, "tb_encoder_embed: token outside the vocabulary");
+    e->tokens = T;
+    const uint32_t ntiles = (uint32_t)tiles.size() / 3;
+    TB_CUDA(cudaMemcpyAsync(e->ids, ids, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    TB_CUDA(cudaMemcpyAsync(e->pos, pos.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    TB_CUDA(cudaMemcpyAsync(e->tiles, tiles.data(), tiles.size() * 4, cudaMemcpyHostToDevice, s));
+    TB_CUDA(cudaMemcpyAsync(e->starts, starts.data(), (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
+    TB_CUDA(cudaMemcpyAsync(e->lens, lens, (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
+    // embeddings -> norm: x (f32 residual stream) and, since layer 0 has no attention norm, its f16 GEMM input
+    enc_norm_kernel<<<T, 256, 0, s>>>(nullptr, e->embed, e->ids, e->embed_norm, h, c.eps, e->x, e->a16);
+    for (uint32_t l = 0; l < c.layers; l++) {
+        ELayer& L = e->layers[l];
+        if (l > 0) enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
+        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, e->a16, T, 3 * h, h, e->qkv16, 1));
+        enc_rope_kernel<<<T, 256, 0, s>>>(e->qkv16, e->pos, e->freq[L.global ? 0 : 1], h, d);
+        const int window = L.global ? -1 : (int)c.window;
+        if (d == 64) enc_attend_kernel<64><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
+        else enc_attend_kernel<32><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
+        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, e->att16, T, h, h, e->x, 3));
+        enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
+        TB_TRY(launch_gemm_q8(ctx, L.up.w, L.up.s, e->a16, T, L.up.rows, h, e->g16, c.gated ? 4 : 5));
+        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, e->g16, T, h, c.inter, e->x, 3));
+    }
+    enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
+    enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
+    TB_CUDA(cudaGetLastError());
+    if (out_host) TB_CUDA(cudaMemcpyAsync(out_host, e->pooled, (size_t)sequences * c.dims * 4, cudaMemcpyDeviceToHost, s));
+    TB_CUDA(cudaStreamSynchronize(s));
+    return OK;
+}
+
+int tb_encoder_hidden(tb_encoder* e, float* out_host) {
+    if (!e || !out_host) return fail(OUT_OF_RANGE, "tb_encoder_hidden: null argument");
+    TB_CUDA(cudaMemcpyAsync(out_host, e->hidden, (size_t)e->tokens * e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(e->ctx->stream));
+    return OK;
+}
+
+}  // extern "C"

@@ -87,7 +87,8 @@ struct GemmArgs {
     const __half* s;
     void* out;
     uint32_t M, N, K;
-    int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU of column pairs, f16 [M, N / 2]
+    int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU (tanh) of column pairs, f16 [M, N / 2]; 3: f32 [M, N] += D;
+               // 4: GeGLU (erf) of column pairs, f16 [M, N / 2]; 5: GELU (erf), f16 [M, N]
 };
 
 // MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
@@ -234,19 +235,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             tmem_load32(tmem + ((32 * q) << 16) + mt * BN + cb * 32, r);
             if (m < g.M && ok) {
                 const uint32_t col = n0 + cb * 32;
-                if (g.mode == 0) {
+                if (g.mode == 3) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        if (col + 4 * i < g.N) {
+                            float4 t = dst[i];
+                            t.x += __uint_as_float(r[4 * i]), t.y += __uint_as_float(r[4 * i + 1]), t.z += __uint_as_float(r[4 * i + 2]), t.w += __uint_as_float(r[4 * i + 3]);
+                            dst[i] = t;
+                        }
+                } else if (g.mode == 0) {
                     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
 #pragma unroll
                     for (int i = 0; i < 8; i++)
                         if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                } else if (g.mode == 1) {
+                } else if (g.mode == 1 || g.mode == 5) {
                     uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         uint32_t h[4];
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
-                            const __half2 t = __floats2half2_rn(__uint_as_float(r[8 * i + 2 * e]), __uint_as_float(r[8 * i + 2 * e + 1]));
+                            float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
+                            if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                            const __half2 t = __floats2half2_rn(f0, f1);
                             h[e] = *reinterpret_cast<const uint32_t*>(&t);
                         }
                         if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
@@ -259,8 +271,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                         uint32_t h[4];
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
-                            const float a0 = gelu_tanh(__uint_as_float(r[16 * i + 4 * e])) * __uint_as_float(r[16 * i + 4 * e + 1]);
-                            const float a1 = gelu_tanh(__uint_as_float(r[16 * i + 4 * e + 2])) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                            const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
+                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
                             const __half2 t = __floats2half2_rn(a0, a1);
                             h[e] = *reinterpret_cast<const uint32_t*>(&t);
                         }
@@ -293,8 +306,8 @@ EncodeTiled encode_tiled() {
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode) {
     if (!w || !s || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
     if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
-    if (N % 32 != 0 || (mode == 2 && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
-    if (mode < 0 || mode > 2) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if (N % 32 != 0 || ((mode == 2 || mode == 4) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
+    if (mode < 0 || mode > 5) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
     EncodeTiled enc = encode_tiled();

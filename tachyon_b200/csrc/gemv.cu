@@ -80,7 +80,7 @@ __device__ __forceinline__ void store_planes(uint8_t* raw, int idx, float v0, fl
 // The block-wide prologue: the 512 consumer threads turn the input vector into planes in shared memory, four
 // consecutive values per thread and pass (coalesced), cols / 2048 passes.
 template <int WPR, int XMODE>
-__device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t) {
+__device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t, const float4& nw1, const float4& nw2) {
     using L = Layout<WPR>;
     if constexpr (XMODE == X_F16) {
 #pragma unroll
@@ -106,12 +106,11 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         float sy = 0.0f;
         if (p.yres != nullptr) {
             const float4 y = ld_cg_f4(p.yres + at);
-            const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
+            const float4 w = nw1;
             a = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
             sy = y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
         }
-        float4 w2 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        if (p.w2 != nullptr) w2 = __ldg(reinterpret_cast<const float4*>(p.w2 + at));
+        const float4 w2 = nw2;
         float sh = h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
         float sha = h.x * a.x + h.y * a.y + h.z * a.z + h.w * a.w;
         float sa = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
@@ -200,8 +199,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
     }
 
     // Consumers.  Everything below may read what the previous kernel wrote.
+    // The norm weights are model constants: fetch them (often from HBM, once a step) before waiting for the previous
+    // kernel rather than after.
+    float4 nw1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), nw2 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if constexpr (XMODE == X_NORM) {
+        if (p.yres != nullptr) nw1 = __ldg(reinterpret_cast<const float4*>(p.w1 + (size_t)threadIdx.x * 4));
+        if (p.w2 != nullptr) nw2 = __ldg(reinterpret_cast<const float4*>(p.w2 + (size_t)threadIdx.x * 4));
+    }
     pdl_wait();
-    build_planes<WPR, XMODE>(p, raw, threadIdx.x);
+    build_planes<WPR, XMODE>(p, raw, threadIdx.x, nw1, nw2);
     named_bar_sync(1, CTHREADS);
     const int seg = warp % WPR, grp = warp / WPR;  // the warp's column segment, and its row group within a stage
     const int first = (lane >> 2) & 1;             // which 16-byte half of its blocks the lane loads first (bank spread)

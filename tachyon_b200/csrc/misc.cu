@@ -170,7 +170,8 @@ __global__ void fill_uniform_kernel(unsigned long long base, float* x, size_t n,
 
 // dst row 2j = src row j, dst row 2j+1 = src row half_rows + j: gate and up rows side by side, so that one block of the
 // matrix-vector kernel holds both halves of a GeGLU output.
-__global__ void interleave_rows_kernel(const uint4* src, uint4* dst, uint32_t half_rows, uint32_t row_vecs) {
+template <typename V>
+__global__ void interleave_rows_kernel(const V* src, V* dst, uint32_t half_rows, uint32_t row_vecs) {
     const size_t total = (size_t)2 * half_rows * row_vecs;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t drow = i / row_vecs, col = i % row_vecs;
@@ -243,9 +244,15 @@ int launch_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, floa
     return OK;
 }
 int launch_interleave_rows(tb_context* ctx, const void* src, void* dst, uint32_t half_rows, uint32_t row_bytes) {
-    if (row_bytes % 16 != 0) return fail(OUT_OF_RANGE, "interleave: rows must be a multiple of 16 bytes");
-    const size_t n = (size_t)2 * half_rows * (row_bytes / 16);
-    interleave_rows_kernel<<<fill_grid(ctx, n), 256, 0, ctx->stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), half_rows, row_bytes / 16);
+    if (row_bytes % 2 != 0) return fail(OUT_OF_RANGE, "interleave: rows must be a multiple of 2 bytes");
+    if (row_bytes % 16 == 0) {
+        const size_t n = (size_t)2 * half_rows * (row_bytes / 16);
+        interleave_rows_kernel<uint4><<<fill_grid(ctx, n), 256, 0, ctx->stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), half_rows, row_bytes / 16);
+    } else {
+        const size_t n = (size_t)2 * half_rows * (row_bytes / 2);
+        interleave_rows_kernel<unsigned short><<<fill_grid(ctx, n), 256, 0, ctx->stream>>>(static_cast<const unsigned short*>(src), static_cast<unsigned short*>(dst),
+                                                                                        half_rows, row_bytes / 2);
+    }
     TB_CUDA(cudaGetLastError());
     return OK;
 }

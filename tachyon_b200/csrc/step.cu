@@ -94,7 +94,7 @@ __device__ __forceinline__ void fetch_planes(const PlanePtr& pp, int b, int firs
 
 // The activation vector of a product -> planes, by the 512 consumer threads (same arithmetic as gemv.cu's prologue).
 template <int WPR, int XMODE>
-__device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t, uint32_t pos) {
+__device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t, uint32_t pos, const float4& nw1, const float4& nw2) {
     const PlanePtr pp = plane_ptr<WPR>(raw);
     if constexpr (XMODE == X_F32) {
         float4 f[WPR];
@@ -134,12 +134,11 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         float sy = 0.0f;
         if (p.yres != nullptr) {
             const float4 y = ld_cg_f4(p.yres + at);
-            const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
+            const float4 w = nw1;
             a = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
             sy = y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
         }
-        float4 w2 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        if (p.w2 != nullptr) w2 = __ldg(reinterpret_cast<const float4*>(p.w2 + at));
+        const float4 w2 = nw2;
         float sh = h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
         float sha = h.x * a.x + h.y * a.y + h.z * a.z + h.w * a.w;
         float sa = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
@@ -182,7 +181,8 @@ struct Best {
 // cols == 2048: a stage holds 16 rows, taken by one half of the warps (two rows a warp) while the other half takes the
 // next stage; longer rows: WPR warps share a row and all warps work on every stage.
 template <int WPR, int XMODE, int EPI>
-__device__ __forceinline__ void gemv_phase(const GemvParams& p, uint8_t* raw, uint32_t& gi, bool& ok, uint32_t* status, Best& best, uint32_t pos, unsigned long long* st) {
+__device__ __forceinline__ void gemv_phase(const GemvParams& p, uint8_t* raw, uint32_t& gi, bool& ok, uint32_t* status, Best& best, uint32_t pos, unsigned long long* st,
+                                           const float4& nw1, const float4& nw2) {
     constexpr int RPW = WPR == 1 ? 2 : 1;
     constexpr int ROWS = STAGE_W / (WPR * SEG);
     const uint32_t K = p.cols;
@@ -192,7 +192,7 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& p, uint8_t* raw, ui
     uint64_t* full = reinterpret_cast<uint64_t*>(raw + OFF_FULL);
     uint64_t* empty = reinterpret_cast<uint64_t*>(raw + OFF_EMPTY);
 
-    build_planes<WPR, XMODE>(p, raw, threadIdx.x, pos);
+    build_planes<WPR, XMODE>(p, raw, threadIdx.x, pos, nw1, nw2);
     named_bar_sync(1, CTHREADS);
     const int half = WPR == 1 ? warp >> 3 : 0;              // which stages this warp takes when cols == 2048
     const int seg = WPR == 1 ? 0 : warp % WPR;              // the warp's column segment
@@ -296,19 +296,19 @@ __device__ __forceinline__ void gemv_phase(const GemvParams& p, uint8_t* raw, ui
 }
 
 __device__ __forceinline__ void run_gemv(const GemvParams& p, uint8_t* raw, uint32_t& gi, bool& ok, uint32_t* status, Best& best, uint32_t pos,
-                                         unsigned long long* st) {
+                                         unsigned long long* st, const float4& nw1, const float4& nw2) {
     if (p.cols == 2048) {
-        if (p.xmode == X_NORM && p.epi == EPI_F32) gemv_phase<1, X_NORM, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
-        else if (p.xmode == X_NORM && p.epi == EPI_GEGLU) gemv_phase<1, X_NORM, EPI_GEGLU>(p, raw, gi, ok, status, best, pos, st);
-        else if (p.xmode == X_NORM && p.epi == EPI_ARGMAX) gemv_phase<1, X_NORM, EPI_ARGMAX>(p, raw, gi, ok, status, best, pos, st);
-        else if (p.xmode == X_ATTN) gemv_phase<1, X_ATTN, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
-        else gemv_phase<1, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
+        if (p.xmode == X_NORM && p.epi == EPI_F32) gemv_phase<1, X_NORM, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
+        else if (p.xmode == X_NORM && p.epi == EPI_GEGLU) gemv_phase<1, X_NORM, EPI_GEGLU>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
+        else if (p.xmode == X_NORM && p.epi == EPI_ARGMAX) gemv_phase<1, X_NORM, EPI_ARGMAX>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
+        else if (p.xmode == X_ATTN) gemv_phase<1, X_ATTN, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
+        else gemv_phase<1, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
     } else if (p.cols == 4096) {
-        gemv_phase<2, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
+        gemv_phase<2, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
     } else if (p.cols == 8192) {
-        gemv_phase<4, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
+        gemv_phase<4, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
     } else {
-        gemv_phase<8, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st);
+        gemv_phase<8, X_F32, EPI_F32>(p, raw, gi, ok, status, best, pos, st, nw1, nw2);
     }
 }
 
@@ -444,6 +444,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
     uint32_t gi = 0, aphase = 0;
     bool ok = true;
     Best best;
+    // Norm weights of the phase about to run: fetched before the barrier in front of it (they are model constants and
+    // usually come from HBM), used after it.
+    float4 nw1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), nw2 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
     // Optional timeline (the reference's Decoder::timeline, decode.rs:424-436): the first and the last block stamp
     // %globaltimer at each phase's start, after its planes, at its end and after the barrier behind it.
     const bool stamp = times != nullptr && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1);
@@ -468,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
                 if (blockIdx.x < an.kv_heads * an.splits) sent = attend::issue_first_tile(an, asm_, abar, blockIdx.x % an.kv_heads, blockIdx.x / an.kv_heads, pos);
                 flags[1] = sent ? 1u : 0u;
             }
-            run_gemv(cur.g, raw, gi, ok, status, best, pos, stamp ? mine + ph * 4 : nullptr);
+            run_gemv(cur.g, raw, gi, ok, status, best, pos, stamp ? mine + ph * 4 : nullptr, nw1, nw2);
         } else {
             const AttendParams& a = cur.a;
             const uint32_t items = a.kv_heads * a.splits, group = a.heads / a.kv_heads;
@@ -484,6 +487,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
         }
         if (stamp) mine[ph * 4 + 2] = global_ns();
         if (ph + 1 == nphases) break;
+        if (nxt.kind == PH_GEMV && nxt.g.xmode == X_NORM) {
+            nw1 = nxt.g.yres != nullptr ? __ldg(reinterpret_cast<const float4*>(nxt.g.w1 + (size_t)threadIdx.x * 4)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            nw2 = nxt.g.w2 != nullptr ? __ldg(reinterpret_cast<const float4*>(nxt.g.w2 + (size_t)threadIdx.x * 4)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        }
         // While waiting, the descriptor after the next one replaces this phase's.
         if (!grid_barrier(counter, (ph + 1) * gridDim.x, status, ph + 2 < nphases ? phases + ph + 2 : nullptr, raw + OFF_PHASE + (ph & 1) * PHASE_BYTES, raw)) break;
         if (stamp) mine[ph * 4 + 3] = global_ns();

@@ -1,0 +1,147 @@
+"""The packed variable-length encoder.  CPU: the oracle's forward against PyTorch's hidden states on the reference's tiny
+encoder (crates/tachyon/tests/encoder.rs:162-181, bound 1e-4).  GPU: the kernels against the oracle on the same
+fixture with Q8 weights (tests/encoder.rs:384-441: f16 path within 2e-2), packing invariance, and the benchmark's
+variant (plain GELU FFN, mean pooling, truncated embeddings)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_encoder.npz")
+
+
+def fixture():
+    z = np.load(GOLDEN)
+    cfg = json.loads(bytes(z["config_json"]).decode())
+    weights = {k: z[k].astype(np.float32) for k in z.files if not k.startswith("case") and k not in ("config_json", "cases")}
+    cases = [(z[f"case{i}.ids"], z[f"case{i}.hidden"]) for i in range(int(z["cases"][0]))]
+    return cfg, weights, cases
+
+
+def test_the_oracle_encoder_matches_pytorch():
+    cfg, weights, cases = fixture()
+    assert (cfg["global"], cfg["window"], int(cfg["theta_global"]), int(cfg["theta_local"])) == ([True, False, False], 8, 160000, 10000)
+    for ids, hidden in cases:
+        got = oracle.encoder_forward(cfg, weights, ids)
+        assert np.abs(got.ravel() - hidden).max() < 1e-4
+
+
+def quantize(w: np.ndarray):
+    """Q8 as this build stores it: per 32 along a row an f16 scale amax/127 and int8 codes; returns codes, scale bits and
+    the dequantised matrix (what the GPU multiplies with, up to its f16 rounding of code*scale)."""
+    rows, cols = w.shape
+    blocks = w.reshape(rows, cols // 32, 32)
+    scale = (np.abs(blocks).max(axis=2) / 127.0).astype(np.float16)
+    sf = scale.astype(np.float32)
+    codes = np.where(sf[..., None] > 0, np.rint(blocks / np.where(sf[..., None] > 0, sf[..., None], 1.0)), 0).clip(-127, 127).astype(np.int8)
+    deq = (codes.astype(np.float32) * sf[..., None]).reshape(rows, cols)
+    return codes.reshape(rows, cols), scale.view(np.uint16), deq
+
+
+def build(ctx, cfg, weights, tokens=1024, sequences=16, mean_pool=0, dims=None):
+    import tachyon_b200 as tb
+
+    glob = np.array([1 if g else 0 for g in cfg["global"]], np.uint8)
+    ec = tb.EncoderConfig(hidden=cfg["hidden"], heads=cfg["heads"], inter=cfg["inter"], vocab=cfg["vocab"], layers=len(cfg["global"]), window=cfg["window"],
+                          global_=glob.ctypes.data, global_every=0, theta_global=cfg["theta_global"], theta_local=cfg["theta_local"], eps=cfg["eps"],
+                          gated=int(cfg.get("gated", 1)), mean_pool=mean_pool, dims=dims or cfg["hidden"])
+    enc = tb.Encoder(ctx, ec, tokens=tokens, sequences=sequences)
+    deq = dict(weights)
+    for name, w in weights.items():
+        if w.ndim == 2 and name != "embed":
+            codes, scales, d = quantize(w)
+            enc.load(name + ".w", codes)
+            enc.load(name + ".s", scales)
+            deq[name] = d
+        elif name == "embed":
+            enc.load(name, w.astype(np.float16))
+            deq[name] = w.astype(np.float16).astype(np.float32)
+        else:
+            enc.load(name, w.astype(np.float32))
+    enc._glob = glob
+    return enc, deq
+
+
+@pytest.mark.gpu
+def test_gpu_encoder_matches_the_oracle_on_the_reference_fixture(ctx):
+    cfg, weights, cases = fixture()
+    enc, deq = build(ctx, cfg, weights)
+    for ids, hidden in cases:
+        emb = enc.embed([ids])
+        got = enc.hidden()
+        want = oracle.encoder_forward(cfg, deq, ids)
+        assert np.abs(got - want).max() < 2e-2, float(np.abs(got - want).max())
+        # and, through the 8-bit weights, still PyTorch's states
+        ref = hidden.reshape(len(ids), -1)
+        cos = (got * ref).sum(1) / (np.linalg.norm(got, axis=1) * np.linalg.norm(ref, axis=1))
+        assert cos.min() > 0.999
+        # the embedding is the first token's state, normalised
+        first = got[0] / max(np.linalg.norm(got[0]), 1e-12)
+        assert np.allclose(emb[0], first, atol=1e-6)
+    enc.close()
+
+
+@pytest.mark.gpu
+def test_packing_does_not_change_a_sequence(ctx):
+    """Packed with others or alone, a sequence's embedding has the same bits (rows past the tokens are never mixed in)."""
+    cfg, weights, _ = fixture()
+    enc, _ = build(ctx, cfg, weights)
+    rng = np.random.default_rng(3)
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (1, 16, 64, 65, 130, 7, 200)]
+    packed = enc.embed(seqs)
+    for i, q in enumerate(seqs):
+        alone = enc.embed([q])
+        assert np.array_equal(alone[0], packed[i]), i
+    assert np.allclose(np.linalg.norm(packed, axis=1), 1.0, atol=1e-5)
+    enc.close()
+
+
+@pytest.mark.gpu
+def test_benchmark_variant_plain_ffn_mean_pool_truncated(ctx):
+    """Plain GELU FFN, head size 64, every third layer global, mean pooling, 64 of 256 dimensions kept."""
+    rng = np.random.default_rng(11)
+    cfg = {"hidden": 256, "heads": 4, "inter": 512, "vocab": 500, "window": 8, "gated": 0, "theta_global": 160000.0, "theta_local": 10000.0, "eps": 1e-5,
+           "global": [True, False, False, True]}
+    h, inter = cfg["hidden"], cfg["inter"]
+    weights = {"embed": rng.standard_normal((cfg["vocab"], h)).astype(np.float32), "embed_norm": rng.uniform(0.5, 1.5, h).astype(np.float32),
+               "final_norm": rng.uniform(0.5, 1.5, h).astype(np.float32)}
+    for l in range(4):
+        if l > 0:
+            weights[f"{l}.attn_norm"] = rng.uniform(0.5, 1.5, h).astype(np.float32)
+        weights[f"{l}.mlp_norm"] = rng.uniform(0.5, 1.5, h).astype(np.float32)
+        for name, shape in (("qkv", (3 * h, h)), ("o", (h, h)), ("up", (inter, h)), ("down", (h, inter))):
+            weights[f"{l}.{name}"] = (rng.standard_normal(shape) * 0.05).astype(np.float32)
+    enc, deq = build(ctx, cfg, weights, mean_pool=1, dims=64)
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (40, 100, 17)]
+    got = enc.embed(seqs)
+    hidden = enc.hidden()
+    at = 0
+    for i, q in enumerate(seqs):
+        want_h = oracle.encoder_forward(cfg, deq, q)
+        assert np.abs(hidden[at:at + len(q)] - want_h).max() < 3e-2, float(np.abs(hidden[at:at + len(q)] - want_h).max())
+        v = want_h.mean(0)
+        v = v / max(np.linalg.norm(v), 1e-12)
+        v = v[:64] / max(np.linalg.norm(v[:64]), 1e-12)
+        assert np.abs(got[i] - v).max() < 5e-3
+        at += len(q)
+    enc.close()
+
+
+@pytest.mark.gpu
+def test_encoder_refuses_what_it_cannot_hold(ctx):
+    import tachyon_b200 as tb
+
+    cfg, weights, _ = fixture()
+    enc, _ = build(ctx, cfg, weights, tokens=64, sequences=2)
+    with pytest.raises(tb.Error) as e:
+        enc.embed([[1] * 40, [2] * 40])
+    assert e.value.status == 6
+    with pytest.raises(tb.Error) as e:
+        enc.embed([[1], [2], [3]])
+    assert e.value.status == 6
+    with pytest.raises(tb.Error):
+        enc.embed([[cfg["vocab"]]])
+    enc.close()
