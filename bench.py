@@ -453,6 +453,49 @@ def bench_prefill(args, ranks: Ranks):
                          "traffic": None, "gemm_flops": flops}}
 
 
+def encoder_batch(cfg_vocab: int, sequences: int = 64, seed: int = 5):
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(16, 513, sequences)
+    return [rng.integers(0, cfg_vocab, int(n)).astype(np.uint32) for n in lens]
+
+
+def bench_encoder(args, ranks: Ranks):
+    """configs[4]: 64 sequences of 16..512 tokens, packed without padding, through the Granite-311m-shaped encoder."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    cfg = tb.granite_311m_shape()
+    seqs = encoder_batch(cfg.vocab, 64, 5 + ranks.rank)  # disjoint batches per replica
+    tokens = int(sum(len(q) for q in seqs))
+    enc = tb.Encoder(ctx, cfg, tokens=32768, sequences=64)
+    enc.fill_random(SEED)
+    for _ in range(args.warmup):
+        out = enc.embed(seqs)
+    ranks.barrier()
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        out = enc.embed(seqs)  # ids cross from host memory, embeddings come back to it
+        times.append(time.perf_counter() - t0)
+    ms = statistics.median(times) * 1e3
+    ms_max = ranks.max(ms)
+    assert np.allclose(np.linalg.norm(out, axis=1), 1.0, atol=1e-4)
+    h, inter, L = cfg.hidden, cfg.inter, cfg.layers
+    flops = 2.0 * tokens * L * (3 * h * h + h * h + 2 * h * inter)
+    burst, sustained, how = measured_peak_tflops()
+    tf = flops / (ms_max * 1e-3) / 1e12
+    n = ranks.world
+    enc.close()
+    return {"metric": "encoder_sequences_per_second", "value": n * 64 / (ms_max / 1e3), "unit": "seq/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 attention", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[4]: 64 sequences of 16..512 tokens ({tokens} tokens packed), Granite-311m shape, plain GELU FFN 3072, mean pooling, 256 dims",
+                       "parallelism": f"{n} independent replicas on disjoint batches", "timing": "host wall clock around tb_encoder_embed (host ids in, host embeddings out)"},
+            "e2e": {"value": n * 64 / (ms_max / 1e3), "unit": "seq/s", "h2d_bytes_per_step": tokens * 8 + 64 * 8, "d2h_bytes_per_step": 64 * 256 * 4},
+            "gpu_launches": args.steps * (2 + L * 9),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "peak_source": how, "traffic": None, "gemm_flops": flops}}
+
+
 def reference_arm(args, ranks: Ranks):
     """The reference's implementation of the path, on the host cores.  The reference (Rust + generated PTX) cannot be
     built in this environment, so this arm times the CPU oracle's restatement of its decode step on the same model."""
@@ -476,9 +519,9 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "attend", "gemm", "prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "attend", "gemm", "prefill", "encoder"])
     ap.add_argument("--tokens", type=int, default=2048)
-    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
@@ -498,6 +541,8 @@ def main():
             line = bench_gemm(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "prefill":
             line = bench_prefill(args, ranks)
+        elif args.workload == "encoder":
+            line = bench_encoder(args, ranks)
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu:
