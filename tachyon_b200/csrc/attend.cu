@@ -37,11 +37,20 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, u
     if (tid < 8 && p.q_norm != nullptr) prefetch_line_l2(p.q_norm + tid * 32);
     else if (tid >= 8 && tid < 16 && p.k_norm != nullptr) prefetch_line_l2(p.k_norm + (tid - 8) * 32);
     else if (tid >= 16 && tid < 20 && p.freq != nullptr) prefetch_line_l2(p.freq + (tid - 16) * 32);
+    // The decoder's caches and position do not depend on the kernel right before this one: fetch the first tile now.
+    __shared__ uint32_t early_sent;
+    uint32_t pos = 0;
+    if (p.early) {
+        pos = ld_cg_u(p.pos);
+        __syncthreads();  // the barrier is initialised
+        if (tid == 0) early_sent = issue_first_tile(p, sm, &sm.bar, blockIdx.x, blockIdx.y, pos) ? 1u : 0u;
+    }
     pdl_wait();
     pdl_launch_dependents();
     __syncthreads();
+    if (!p.early) pos = ld_cg_u(p.pos);
     uint32_t phase = 0;
-    attend_body<G, false>(p, sm, &sm.bar, tid, blockIdx.x, blockIdx.y, ld_cg_u(p.pos), false, status, phase);
+    attend_body<G, false>(p, sm, &sm.bar, tid, blockIdx.x, blockIdx.y, pos, p.early != 0 && early_sent != 0, status, phase);
 }
 
 }  // namespace
@@ -57,7 +66,7 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
     if (group != 1 && group != 2 && group != 4) return fail(UNSUPPORTED, "attend: 1, 2 or 4 query heads per key-value head");
     if (p.cap == 0 || p.window == 0 || p.window > p.cap) return fail(OUT_OF_RANGE, "attend: need 0 < window <= cap");
     if (p.splits == 0 || p.splits > 1024) return fail(OUT_OF_RANGE, "attend: splits out of range");
-    if (!p.qkv || !p.kc || !p.vc || !p.pos || !p.out || !p.count || (p.splits > 1 && !p.partial)) return fail(OUT_OF_RANGE, "attend: null argument");
+    if (!p.qkv || !p.kc || !p.vc || !p.pos || (!p.defer && (!p.out || !p.count)) || ((p.splits > 1 || p.defer) && !p.partial)) return fail(OUT_OF_RANGE, "attend: null argument");
     if ((p.q_norm == nullptr) != (p.k_norm == nullptr)) return fail(OUT_OF_RANGE, "attend: q_norm and k_norm go together");
     if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.qkv)) & 15) return fail(OUT_OF_RANGE, "attend: buffers must be 16-byte aligned");
     const dim3 grid(p.kv_heads, p.splits), block(THREADS);

@@ -253,8 +253,9 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
         a.pf = hint(d, L.gate_up, 2, 0, PF);
+        a.defer = 1;  // the o projection merges the splits in its prologue
+        a.early = 1;  // caches and position are final long before the kernel in front of this one
         if (d->collect) {
-            a.defer = 1;  // the o projection merges the splits in its prologue
             StepPhase ph;
             ph.kind = PH_ATTEND, ph.a = a;
             d->collect->push_back(ph);
@@ -265,10 +266,8 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
 
         GemvParams o;
         o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
-        if (d->collect) {
-            o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
-            o.att_heads = c.heads, o.att_kv = c.kv_heads;
-        }
+        o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
+        o.att_heads = c.heads, o.att_kv = c.kv_heads;
         o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 

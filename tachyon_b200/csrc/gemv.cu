@@ -96,6 +96,32 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         for (int j = 0; j < WPR; j++) f[j] = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)(j * CTHREADS + t) * 4);
 #pragma unroll
         for (int j = 0; j < WPR; j++) store_planes<WPR>(raw, j * CTHREADS + t, f[j].x, f[j].y, f[j].z, f[j].w);
+    } else if constexpr (XMODE == X_ATTN) {
+        // The vector is attention's output, still split over the blocks that computed it: merge the splits' (maximum,
+        // sum, unnormalised output) here, four dimensions per thread, with running-maximum rescaling
+        // (crates/tachyon/src/ptx/attend.rs:371-405 does this in the attention kernel's last block).
+        static_assert(XMODE != X_ATTN || WPR == 1, "the attention merge is built for 2048 columns");
+        const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
+        const uint32_t head = (uint32_t)t / 64, g = head / G, hh = head % G, d0 = ((uint32_t)t * 4) % 256;
+        const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
+        uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
+        if (span > 64u) span = (span + 63u) / 64u * 64u;
+        const uint32_t used = (n + span - 1) / span;
+        const float* base = p.att_partial + (size_t)g * p.att_splits * stride;
+        float M = -INFINITY, Lsum = 0.0f;
+        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+        for (uint32_t s2 = 0; s2 < used; s2++) {
+            const float* ps = base + (size_t)s2 * stride;
+            const float m = ld_cg_f(ps + hh), l = ld_cg_f(ps + G + hh);
+            const float4 a = ld_cg_f4(ps + 2 * G + hh * 256 + d0);
+            const float Mn = fmaxf(M, m), c = exp2f(M - Mn), w = exp2f(m - Mn);
+            Lsum = fmaf(Lsum, c, w * l);
+            o.x = fmaf(o.x, c, w * a.x), o.y = fmaf(o.y, c, w * a.y), o.z = fmaf(o.z, c, w * a.z), o.w = fmaf(o.w, c, w * a.w);
+            M = Mn;
+        }
+        const float inv = 1.0f / Lsum;
+        store_planes<WPR>(raw, t, o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     } else {
         // Residual step and RMS-norm over the whole vector (cols == 2048, four values per thread).  One pass of sums, as
         // the reference does (ptx/mod.rs:24-30): sum y^2, sum h^2, sum h*a, sum a^2 with a = y*w1; mean(h'^2) follows.
@@ -358,12 +384,13 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
 
 template <int WPR>
 int dispatch_staged(tb_context* ctx, const GemvParams& p) {
-    if (p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX || p.xmode == X_NORM) {
+    if (p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX || p.xmode == X_NORM || p.xmode == X_ATTN) {
         if constexpr (WPR == 1) {
             if (p.xmode == X_NORM && p.epi == EPI_F32) return launch_staged<1, X_NORM, EPI_F32>(ctx, p);
             if (p.xmode == X_NORM && p.epi == EPI_F16) return launch_staged<1, X_NORM, EPI_F16>(ctx, p);
             if (p.xmode == X_NORM && p.epi == EPI_GEGLU) return launch_staged<1, X_NORM, EPI_GEGLU>(ctx, p);
             if (p.xmode == X_NORM && p.epi == EPI_ARGMAX) return launch_staged<1, X_NORM, EPI_ARGMAX>(ctx, p);
+            if (p.xmode == X_ATTN && p.epi == EPI_F32) return launch_staged<1, X_ATTN, EPI_F32>(ctx, p);
             if (p.xmode == X_F32 && p.epi == EPI_GEGLU) return launch_staged<1, X_F32, EPI_GEGLU>(ctx, p);
             if (p.xmode == X_F32 && p.epi == EPI_ARGMAX) return launch_staged<1, X_F32, EPI_ARGMAX>(ctx, p);
             if (p.xmode == X_F16 && p.epi == EPI_GEGLU) return launch_staged<1, X_F16, EPI_GEGLU>(ctx, p);
@@ -388,6 +415,9 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if ((reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.s)) & 15) return fail(OUT_OF_RANGE, "gemv: weights and scales must be 16-byte aligned");
     if (p.xmode == X_NORM) {
         if (p.h == nullptr || (p.yres != nullptr && p.w1 == nullptr)) return fail(OUT_OF_RANGE, "gemv: the norm prologue needs h, and w1 with y");
+    } else if (p.xmode == X_ATTN) {
+        if (p.att_partial == nullptr || p.att_pos == nullptr || p.att_kv == 0 || p.att_heads % p.att_kv != 0 || p.att_heads * 256 != p.cols)
+            return fail(OUT_OF_RANGE, "gemv: the attention-merge prologue needs partials, a position and heads * 256 == cols");
     } else if (p.x == nullptr || (reinterpret_cast<uintptr_t>(p.x) & 15)) {
         return fail(OUT_OF_RANGE, "gemv: the input vector must be present and 16-byte aligned");
     }
@@ -401,7 +431,7 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
         case 16384: return dispatch_staged<8>(ctx, p);
         default: break;
     }
-    if (p.xmode == X_NORM || p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX) return fail(UNSUPPORTED, "gemv: fused prologue/epilogues need cols of 2048");
+    if (p.xmode == X_NORM || p.xmode == X_ATTN || p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX) return fail(UNSUPPORTED, "gemv: fused prologue/epilogues need cols of 2048");
     const dim3 grid((p.rows + 7) / 8), block(256);
     if (p.xmode == X_F16 && p.epi == EPI_F32) TB_CUDA(launch_kernel(ctx, gemv_q8_generic<X_F16, EPI_F32>, grid, block, 0, true, p));
     else if (p.xmode == X_F16 && p.epi == EPI_F16) TB_CUDA(launch_kernel(ctx, gemv_q8_generic<X_F16, EPI_F16>, grid, block, 0, true, p));

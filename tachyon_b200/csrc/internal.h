@@ -85,7 +85,7 @@ struct GemvParams {
     uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
     uint32_t trace_mask = 0;
     Prefetch pf;                  // optional hint for the L2
-    // X_ATTN (fused step only): x is the attention output, merged here from the splits' partial results
+    // X_ATTN: x is the attention output, merged here from the splits' partial results
     // (layout of AttendParams::partial): x[h*256 + d] = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s.
     const float* att_partial = nullptr;
     const uint32_t* att_pos = nullptr;
@@ -112,7 +112,9 @@ struct AttendParams {
     void* out = nullptr;           // [heads*256] f32 or f16
     int out_f16 = 0;
     Prefetch pf;                   // optional hint for the L2
-    uint32_t defer = 0;            // != 0 (fused step): every split only stores its partial; the next product merges them
+    uint32_t defer = 0;            // != 0: every split only stores its partial; the product that follows merges them (X_ATTN)
+    uint32_t early = 0;            // != 0: the position and the older cache rows are final before the previous kernel in the
+                                   // stream started, so the first tile may be fetched ahead of griddepcontrol.wait
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
