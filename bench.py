@@ -364,7 +364,7 @@ def bench_attend(args, ranks: Ranks):
     peak, how = measured_peak_gbs()
     g = results["global_4096"]
     return {"metric": "attend_decode_us", "value": g["us_per_launch"], "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": g["us_per_launch"] / 1e3, "higher_is_better": False, "dtype": "f16 cache, f32 math", "data": "synthetic", "impl": "ours",
+            "ms_per_step": g["us_per_launch"] / 1e3, "higher_is_better": False, "dtype": "f16 cache; f32 queries and probabilities as two f16 parts on mma.sync, f32 accumulate", "data": "synthetic", "impl": "ours",
             "config": {"workload": f"configs[1]: decode attention 8q/2kv x 256 over 4096 positions, {copies} cache copies cycled", "variants": results},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "achieved": g["achieved_gbs"], "peak": peak, "unit": "GB/s", "frac": g["achieved_gbs"] / peak, "peak_source": how, "traffic": None}}

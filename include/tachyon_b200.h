@@ -239,9 +239,12 @@ TB_API int tb_decoder_step_bytes(tb_decoder* dec, uint64_t* weight_bytes, uint64
 /* Kernels one step launches. */
 TB_API int tb_decoder_step_launches(tb_decoder* dec, uint32_t* launches);
 /*
- * Decoder::timeline (decode.rs:424-436): runs one step on `token` outside the graphs and returns, for the first and
- * for the last block of the fused step kernel, four %globaltimer stamps (ns) per phase: start, 0, end of work, after
- * the barrier behind it.  host_out: 2 * phases * 4 words; call with host_out NULL to learn `phases`.
+ * Decoder::timeline (decode.rs:424-436): runs one step on `token` outside the two step graphs and returns, for the
+ * first and for the last block of every phase (embedding, per layer qkv / attention / o / gate_up / down, head),
+ * four %globaltimer stamps in ns.  One launch per phase: kernel entry, after the wait for the previous kernel, after
+ * the prologue (0 for attention and the embedding, which has no stamps at all), end of the block's work.  Fused
+ * step: start, after the prologue, end of work, after the barrier behind it.
+ * host_out: [2 blocks][phases][4] words; call with host_out NULL to learn `phases`.
  */
 TB_API int tb_decoder_timeline(tb_decoder* dec, uint32_t token, uint64_t* host_out, uint32_t* phases);
 /* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */

@@ -3,8 +3,8 @@
 // (crates/tachyon/src/ptx/attend.rs:423-466; setup 281-330, step 213-225, partial 334-367, combine 371-405).
 //
 // Per key-value head there are `splits` blocks; each takes a span of the newest min(pos + 1, window) positions,
-// brings their keys and values into shared memory with bulk copies (a span of ring slots is at most two contiguous
-// byte ranges), and keeps running softmax statistics for the query heads of its group.  Optional per-head RMS-norms and
+// brings their keys and values into shared memory with asynchronous 16-byte copies (into padded rows, so that the
+// tensor-core fragment loads meet no bank conflicts), and keeps running softmax statistics for the query heads of its group.  Optional per-head RMS-norms and
 // RoPE on the new query/key/value (the reference's Gemma-4 semantics) and a plain mode (no norms, no rotation, caller's
 // scale) are parameters.  The new token's key/value are written to slot pos % cap by the first block of each group and
 // used from f32, as the reference does.
@@ -22,35 +22,41 @@ using namespace attend;
 namespace {
 
 template <int G>
-__global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p, uint32_t* status) {
+__global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p) {
     extern __shared__ __align__(128) uint8_t raw[];
     Smem& sm = *reinterpret_cast<Smem*>(raw);
     const int tid = threadIdx.x;
-    if (tid == 0) {
-        mbar_init(&sm.bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
     // The hint is about weights no kernel writes: ask for them before waiting for the previous kernel.
     if (tid == 0) prefetch_hint(p.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y);
     // The norm weights and the RoPE table are model constants (2.5 KiB): ask the L2 for them ahead of the wait.
     if (tid < 8 && p.q_norm != nullptr) prefetch_line_l2(p.q_norm + tid * 32);
     else if (tid >= 8 && tid < 16 && p.k_norm != nullptr) prefetch_line_l2(p.k_norm + (tid - 8) * 32);
     else if (tid >= 16 && tid < 20 && p.freq != nullptr) prefetch_line_l2(p.freq + (tid - 16) * 32);
-    // The decoder's caches and position do not depend on the kernel right before this one: fetch the first tile now.
-    __shared__ uint32_t early_sent;
+    // The decoder's caches and position do not depend on the kernel right before this one: ask for the first tile now,
+    // and have the rotation's cosines and sines ready.
     uint32_t pos = 0;
+    bool sent = false;
+    Trig trig;
     if (p.early) {
         pos = ld_cg_u(p.pos);
-        __syncthreads();  // the barrier is initialised
-        if (tid == 0) early_sent = issue_first_tile(p, sm, &sm.bar, blockIdx.x, blockIdx.y, pos) ? 1u : 0u;
+        sent = load_first_tile(p, sm, blockIdx.x, blockIdx.y, pos, tid);
+        trig = rope_trig(p.freq, pos, tid & 31);
     }
+    unsigned long long* stamp = nullptr;
+    if (p.stamps != nullptr && tid == 0) {
+        const uint32_t b = blockIdx.y * gridDim.x + blockIdx.x;
+        if (b == 0 || b == gridDim.x * gridDim.y - 1) stamp = p.stamps + (b == 0 ? 0 : 4);
+    }
+    if (stamp) stamp[0] = global_ns();
     pdl_wait();
     pdl_launch_dependents();
-    __syncthreads();
-    if (!p.early) pos = ld_cg_u(p.pos);
-    uint32_t phase = 0;
-    attend_body<G, false>(p, sm, &sm.bar, tid, blockIdx.x, blockIdx.y, pos, p.early != 0 && early_sent != 0, status, phase);
+    if (stamp) stamp[1] = global_ns();
+    if (!p.early) {
+        pos = ld_cg_u(p.pos);
+        trig = rope_trig(p.freq, pos, tid & 31);
+    }
+    attend_body<G, false>(p, sm, tid, blockIdx.x, blockIdx.y, pos, sent, trig);
+    if (stamp) stamp[3] = global_ns();
 }
 
 }  // namespace
@@ -77,9 +83,9 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
         TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
         configured[ctx->gpu & 15] = true;
     }
-    if (group == 4) TB_CUDA(launch_kernel(ctx, attend_kernel<4>, grid, block, sizeof(Smem), true, p, ctx->status));
-    else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(Smem), true, p, ctx->status));
-    else TB_CUDA(launch_kernel(ctx, attend_kernel<1>, grid, block, sizeof(Smem), true, p, ctx->status));
+    if (group == 4) TB_CUDA(launch_kernel(ctx, attend_kernel<4>, grid, block, sizeof(Smem), true, p));
+    else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(Smem), true, p));
+    else TB_CUDA(launch_kernel(ctx, attend_kernel<1>, grid, block, sizeof(Smem), true, p));
     return OK;
 }
 

@@ -15,19 +15,42 @@ constexpr int MAXG = 4;       // query heads per key-value head this kernel is b
 constexpr int THREADS = 256;
 constexpr int MIN_SPAN = 16;  // fewest positions worth a block of their own
 
+constexpr int ROW = D + 8;    // halves between rows of a tile: 16 bytes of padding put eight neighbouring rows on different banks
+constexpr int PROW = TILE + 8;  // the same for the transposed probabilities
+
 struct Smem {
-    __half k[TILE][D];
-    __half v[TILE][D];
-    float q[MAXG][D];
+    __half k[TILE][ROW];
+    __half v[TILE][ROW];
+    float q[MAXG][D];            // the queries, scaled; after the last tile the outputs on their way to the old layout
     float kf[D], vf[D];          // the new token's key and value
-    float p[TILE][MAXG];         // scores, then probabilities
+    float s[2][TILE][8];         // raw scores: [half of the dimensions][row][column]; column h is head h's high part, G + h its low part
+    __half pt[8][PROW];          // probabilities, transposed: row h the f16 value of head h's, row G + h what the f16 leaves of it
+    float pnew[MAXG];            // probability of the new token's row
     float corr[MAXG], mrun[MAXG], lrun[MAXG];
-    uint64_t bar;
     uint32_t last;
 };
 
+// cos and sin of the position's angle for the four dimension pairs a lane rotates: (4l + i, 128 + 4l + i).  They depend
+// on the position alone, so a kernel can have them ready before its input arrives.
+struct Trig {
+    float c[4], s[4];
+};
+__device__ __forceinline__ Trig rope_trig(const float* freq, uint32_t pos, int lane) {
+    Trig t;
+    if (freq == nullptr) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) t.c[i] = 1.0f, t.s[i] = 0.0f;
+        return t;
+    }
+    const float4 f = __ldg(reinterpret_cast<const float4*>(freq + 4 * lane));
+    const float fr[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) sincosf((float)pos * fr[i], &t.s[i], &t.c[i]);
+    return t;
+}
+
 // RMS-norm (optional weights), RoPE (optional) of one head held as 8 values per lane: dims 4l..4l+3 and 128+4l..128+4l+3.
-__device__ __forceinline__ void norm_rope(float (&x)[8], bool norm, const float* w, const float* freq, uint32_t pos, float eps, int lane) {
+__device__ __forceinline__ void norm_rope(float (&x)[8], bool norm, const float* w, const Trig* trig, float eps, int lane) {
     if (norm) {
         float s = 0.0f;
 #pragma unroll
@@ -40,16 +63,12 @@ __device__ __forceinline__ void norm_rope(float (&x)[8], bool norm, const float*
             x[0] *= a.x, x[1] *= a.y, x[2] *= a.z, x[3] *= a.w, x[4] *= b.x, x[5] *= b.y, x[6] *= b.z, x[7] *= b.w;
         }
     }
-    if (freq != nullptr) {
-        const float4 f = __ldg(reinterpret_cast<const float4*>(freq + 4 * lane));
-        const float fr[4] = {f.x, f.y, f.z, f.w};
+    if (trig != nullptr) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            float s, c;
-            sincosf((float)pos * fr[i], &s, &c);
             const float a = x[i], b = x[i + 4];
-            x[i] = a * c - b * s;
-            x[i + 4] = b * c + a * s;
+            x[i] = a * trig->c[i] - b * trig->s[i];
+            x[i + 4] = b * trig->c[i] + a * trig->s[i];
         }
     }
 }
@@ -82,8 +101,6 @@ __device__ __forceinline__ void block_sync() {
     else __syncthreads();
 }
 
-// One work item: key-value head `g`, split `sp`.  `phase` is the parity of sm.bar's next completion; the caller keeps
-// it across calls that reuse the barrier.  Every return is taken by all 256 threads together.
 // How the newest n positions are split over at most `splits` blocks: positions per block.  Spans longer than a tile are
 // whole tiles, so that no block is left with a sliver of a second tile.
 __device__ __forceinline__ uint32_t split_span(uint32_t n, uint32_t splits) {
@@ -92,44 +109,78 @@ __device__ __forceinline__ uint32_t split_span(uint32_t n, uint32_t splits) {
     return span;
 }
 
-// Thread 0's part of loading a tile: rows of ages [a0, a0 + cnt) of key-value head `g` (without the new token's row
-// when `has_new`), as one or two contiguous ranges of ring slots, completing on `bar`.
-__device__ __forceinline__ void issue_tile(const AttendParams& p, Smem& sm, uint64_t* bar, uint32_t g, uint32_t cur, uint32_t a0, uint32_t cnt,
-                                           bool has_new) {
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// x = hi + lo with both f16: the tensor cores then multiply x to nearly f32 precision in two columns (or rows).
+__device__ __forceinline__ void split_f16(float x, __half& hi, __half& lo) {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+}
+
+// The 256 threads' part of loading a tile: rows of ages [a0, a0 + cnt) of key-value head `g` (without the new token's
+// row when `has_new`), in 16-byte asynchronous copies into the padded rows.  Rows of the value tile that stay unused
+// are cleared: the tensor cores multiply them by zero, which must not meet a NaN left by an earlier tile.
+// The caller commits the copies.
+__device__ __forceinline__ void load_tile(const AttendParams& p, Smem& sm, uint32_t g, uint32_t cur, uint32_t a0, uint32_t cnt, bool has_new, int tid) {
     const uint32_t loaded = has_new ? cnt - 1 : cnt;
-    if (loaded == 0) return;
     const uint32_t first = (cur + p.cap - (a0 + cnt - 1)) % p.cap;  // slot of row 0
-    const uint32_t head_rows = min(loaded, p.cap - first), tail_rows = loaded - head_rows;
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier accesses to the tile's memory precede its refill
-    mbar_expect_tx(bar, loaded * D * 2 * 2);
     const __half* kb = p.kc + (size_t)g * p.cap * D;
     const __half* vb = p.vc + (size_t)g * p.cap * D;
-    bulk_load(&sm.k[0][0], kb + (size_t)first * D, head_rows * D * 2, bar);
-    bulk_load(&sm.v[0][0], vb + (size_t)first * D, head_rows * D * 2, bar);
-    if (tail_rows > 0) {
-        bulk_load(&sm.k[head_rows][0], kb, tail_rows * D * 2, bar);
-        bulk_load(&sm.v[head_rows][0], vb, tail_rows * D * 2, bar);
+#pragma unroll 4
+    for (uint32_t i = (uint32_t)tid; i < TILE * 64; i += THREADS) {
+        const uint32_t r = i / 64, j = i % 64;  // row; 16-byte piece: 0..31 of the key, 32..63 of the value
+        if (r < loaded) {
+            uint32_t slot = first + r;
+            if (slot >= p.cap) slot -= p.cap;
+            if (j < 32) cp_async_16(&sm.k[r][j * 8], kb + (size_t)slot * D + j * 8);
+            else cp_async_16(&sm.v[r][(j - 32) * 8], vb + (size_t)slot * D + (j - 32) * 8);
+        } else if (j >= 32) {
+            *reinterpret_cast<uint4*>(&sm.v[r][(j - 32) * 8]) = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
 }
 
-// The first tile of work item (g, sp) at position `pos`: issues its loads (thread 0 calls this; the body is then told
-// the tile is already on its way).  Returns false when the item has nothing to load.
-__device__ __forceinline__ bool issue_first_tile(const AttendParams& p, Smem& sm, uint64_t* bar, uint32_t g, uint32_t sp, uint32_t pos) {
+// The first tile of work item (g, sp) at position `pos`, asked for before the rest of the body runs (all 256 threads
+// call this and commit; the body is then told the tile is on its way).  Returns false when the item has no tile.
+__device__ __forceinline__ bool load_first_tile(const AttendParams& p, Smem& sm, uint32_t g, uint32_t sp, uint32_t pos, int tid) {
     const uint32_t n = min(pos + 1, p.window), cur = pos % p.cap;
     const uint32_t span = split_span(n, p.splits);
     const uint32_t used = (n + span - 1) / span;
     if (sp >= used) return false;
     const uint32_t a_begin = sp * span, a_end = min(n, a_begin + span);
     const uint32_t cnt = min((uint32_t)TILE, a_end - a_begin);
-    const bool has_new = p.fresh != 0 && sp == 0;
-    if ((has_new ? cnt - 1 : cnt) == 0) return false;
-    issue_tile(p, sm, bar, g, cur, a_begin, cnt, has_new);
+    load_tile(p, sm, g, cur, a_begin, cnt, p.fresh != 0 && sp == 0, tid);
+    cp_async_commit();
     return true;
 }
 
+// One work item: key-value head `g`, split `sp`.  Every return is taken by all 256 threads together.
+//
+// The two products run on the tensor cores (mma.sync m16n8k16, f16 operands, f32 accumulation): a 64-row tile is far
+// too little work to be worth anything else, and what matters is how few dependent instructions stand between the
+// arrival of the query and the partial result.  The f32 query is split into two f16 numbers (columns h and G + h of
+// the scores' B operand), and so are the probabilities (rows h and G + h of the second product's A operand), so
+// the only rounding beyond the f32 path's is the accumulation order.  The cache is f16 as it is.
+//   scores[row][col] = K[row][:] . q[col][:]      M = 64 rows (four 16-row tiles), N = 8, K = 256: warp w takes
+//                                                 row tile w % 4 and dimensions 128 (w / 4) .. + 127
+//   out[m][dim]      = P[m][:] . V[:][dim]        M = 16 (2G rows used), N = 256 (warp w: 32 w .. + 31), K = 64 rows
 template <int G, bool FUSED>
-__device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, uint64_t* bar, const int tid, const uint32_t g, const uint32_t sp,
-                                            const uint32_t pos, const bool preloaded, uint32_t* status, uint32_t& phase) {
+__device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, const int tid, const uint32_t g, const uint32_t sp, const uint32_t pos,
+                                            const bool preloaded, const Trig& trig) {
     const int warp = tid >> 5, lane = tid & 31;
     const uint32_t n = min(pos + 1, p.window), cur = pos % p.cap;
     const uint32_t span = split_span(n, p.splits);
@@ -138,113 +189,126 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, uin
     const uint32_t a_begin = sp * span, a_end = min(n, a_begin + span);  // ages: 0 is the new token
     const bool fresh_here = p.fresh != 0 && sp == 0;
     const bool norms = p.q_norm != nullptr;
+    const Trig* rot = p.freq != nullptr ? &trig : nullptr;
     const float qscale = p.scale * 1.4426950408889634f;  // scores in base 2
 
     // Queries of the group (warps 0..G-1), the new key (warp G) and value (warp G+1).
     if (warp < G) {
         float x[8];
         load_head(p.qkv + (size_t)(g * G + warp) * D, x, lane);
-        norm_rope(x, norms, p.q_norm, p.freq, pos, p.eps, lane);
+        norm_rope(x, norms, p.q_norm, rot, p.eps, lane);
 #pragma unroll
         for (int i = 0; i < 8; i++) x[i] *= qscale;
         store_head(sm.q[warp], x, lane);
     } else if (fresh_here && warp == G) {
         float x[8];
         load_head(p.qkv + (size_t)(p.heads + g) * D, x, lane);
-        norm_rope(x, norms, p.k_norm, p.freq, pos, p.eps, lane);
+        norm_rope(x, norms, p.k_norm, rot, p.eps, lane);
         store_head(sm.kf, x, lane);
         store_head_f16(p.kc + ((size_t)g * p.cap + cur) * D, x, lane);
     } else if (fresh_here && warp == G + 1) {
         float x[8];
         load_head(p.qkv + (size_t)(p.heads + p.kv_heads + g) * D, x, lane);
-        norm_rope(x, norms, nullptr, nullptr, pos, p.eps, lane);
+        norm_rope(x, norms, nullptr, nullptr, p.eps, lane);
         store_head(sm.vf, x, lane);
         store_head_f16(p.vc + ((size_t)g * p.cap + cur) * D, x, lane);
     }
     if (tid < G) sm.mrun[tid] = -INFINITY, sm.lrun[tid] = 0.0f;
+    // Rows 2G..7 of the transposed probabilities are never written: they are the unused rows of the A operand.
+    for (int i = tid; i < 8 * PROW / 2; i += THREADS) reinterpret_cast<uint32_t*>(&sm.pt[0][0])[i] = 0u;
+    block_sync<FUSED>();  // q, kf, vf are written
 
-    float acc[G];
+    // The scores' B operand for this warp's half of the dimensions: column c = lane / 4 is the high part of head c
+    // (c < G), the low part of head c - G (c < 2G), or nothing; a thread holds dimensions 16 ks + 2 (lane % 4) + {0, 1, 8, 9}.
+    const int khalf = warp >> 2, mtile = warp & 3;
+    uint32_t qb[8][2];
+    {
+        const int c = lane >> 2;
+        const bool use = c < 2 * G, low = c >= G;
+        const float* qh = sm.q[use ? (low ? c - G : c) : 0];
 #pragma unroll
-    for (int h = 0; h < G; h++) acc[h] = 0.0f;
-    bool ok = true;
+        for (int ks = 0; ks < 8; ks++) {
+            const int d = khalf * 128 + ks * 16 + 2 * (lane & 3);
+            const float2 x0 = *reinterpret_cast<const float2*>(qh + d), x1 = *reinterpret_cast<const float2*>(qh + d + 8);
+            __half h0, l0, h1, l1, h2, l2, h3, l3;
+            split_f16(x0.x, h0, l0), split_f16(x0.y, h1, l1), split_f16(x1.x, h2, l2), split_f16(x1.y, h3, l3);
+            const __half2 b0 = low ? __halves2half2(l0, l1) : __halves2half2(h0, h1), b1 = low ? __halves2half2(l2, l3) : __halves2half2(h2, h3);
+            qb[ks][0] = use ? *reinterpret_cast<const uint32_t*>(&b0) : 0u;
+            qb[ks][1] = use ? *reinterpret_cast<const uint32_t*>(&b1) : 0u;
+        }
+    }
+
+    // Outputs: this warp's four 8-dimension tiles; element 0, 1 of each is row lane / 4, dimensions 2 (lane % 4) + {0, 1}.
+    float acc[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; t++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[t][i] = 0.0f;
+    const int orow = lane >> 2;       // row of the second product this thread holds
+    const int ohead = orow % G;      // its head (rows >= 2G hold zeros)
+
     for (uint32_t a0 = a_begin; a0 < a_end; a0 += TILE) {
         const uint32_t cnt = min((uint32_t)TILE, a_end - a0);
         // Rows of the tile: row r holds age a0 + cnt - 1 - r, so rows are ascending ring slots.  The new token (age 0)
         // would be the last row of the first tile; it is taken from kf / vf instead and not loaded.
         const bool has_new = fresh_here && a0 == 0;
         const uint32_t loaded = has_new ? cnt - 1 : cnt;
-        block_sync<FUSED>();  // the previous tile is no longer read; q, kf, vf, mrun are written
-        if (tid == 0 && !(preloaded && a0 == a_begin)) issue_tile(p, sm, bar, g, cur, a0, cnt, has_new);
-        if (loaded > 0) {
-            if (ok && !mbar_wait(bar, phase)) {
-                atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
-                ok = false;
-            }
-            phase ^= 1;
+        if (!(preloaded && a0 == a_begin)) {
+            if (a0 != a_begin) block_sync<FUSED>();  // the previous tile is no longer read
+            load_tile(p, sm, g, cur, a0, cnt, has_new, tid);
+            cp_async_commit();
         }
-        // Scores: one warp per row, a lane holds eight dimensions of the key and of each query.
-        float qr[G][8];
+        cp_async_wait_all();
+        block_sync<FUSED>();
+
+        // Scores of 16 rows over 128 dimensions, in two chains of four products.
+        {
+            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const __half* base = &sm.k[mtile * 16 + (lane & 15)][khalf * 128 + (lane >> 4) * 8];
 #pragma unroll
-        for (int h = 0; h < G; h++) {
-            const float4 a = *reinterpret_cast<const float4*>(&sm.q[h][8 * lane]), b = *reinterpret_cast<const float4*>(&sm.q[h][8 * lane + 4]);
-            qr[h][0] = a.x, qr[h][1] = a.y, qr[h][2] = a.z, qr[h][3] = a.w, qr[h][4] = b.x, qr[h][5] = b.y, qr[h][6] = b.z, qr[h][7] = b.w;
-        }
-        for (uint32_t r = warp; r < cnt; r += THREADS / 32) {
-            float kv[8];
-            if (has_new && r == cnt - 1) {
-                const float4 a = *reinterpret_cast<const float4*>(&sm.kf[8 * lane]), b = *reinterpret_cast<const float4*>(&sm.kf[8 * lane + 4]);
-                kv[0] = a.x, kv[1] = a.y, kv[2] = a.z, kv[3] = a.w, kv[4] = b.x, kv[5] = b.y, kv[6] = b.z, kv[7] = b.w;
-            } else {
-                const uint4 t = *reinterpret_cast<const uint4*>(&sm.k[r][8 * lane]);
-                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                    kv[2 * j] = f.x, kv[2 * j + 1] = f.y;
-                }
+            for (int ks = 0; ks < 8; ks += 2) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, base + ks * 16);
+                ldmatrix_x4(b, base + ks * 16 + 16);
+                mma_16816(c0, a[0], a[1], a[2], a[3], qb[ks][0], qb[ks][1]);
+                mma_16816(c1, b[0], b[1], b[2], b[3], qb[ks + 1][0], qb[ks + 1][1]);
             }
-            float sc[G];
-#pragma unroll
-            for (int h = 0; h < G; h++) {
-                sc[h] = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) sc[h] = fmaf(qr[h][i], kv[i], sc[h]);
-            }
-            // Reduce the G sums together: the halves (then quarters) of the warp trade values, so head h ends up summed
-            // in the lanes whose top bits spell h.
-            float v;
-            if constexpr (G == 4) {
-                const bool b4 = lane & 16, b3 = lane & 8;
-                const float k0 = (b4 ? sc[2] : sc[0]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[0] : sc[2], 16);
-                const float k1 = (b4 ? sc[3] : sc[1]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[1] : sc[3], 16);
-                v = (b3 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b3 ? k0 : k1, 8);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                if ((lane & 7) == 0) sm.p[r][lane >> 3] = ok ? v : 0.0f;
-            } else if constexpr (G == 2) {
-                const bool b4 = lane & 16;
-                v = (b4 ? sc[1] : sc[0]) + __shfl_xor_sync(0xffffffffu, b4 ? sc[0] : sc[1], 16);
-#pragma unroll
-                for (int o2 = 8; o2 > 0; o2 >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o2);
-                if ((lane & 15) == 0) sm.p[r][lane >> 4] = ok ? v : 0.0f;
-            } else {
-                v = warp_sum(sc[0]);
-                if (lane == 0) sm.p[r][0] = ok ? v : 0.0f;
-            }
+            float* out = &sm.s[khalf][mtile * 16 + (lane >> 2)][2 * (lane & 3)];
+            *reinterpret_cast<float2*>(out) = make_float2(c0[0] + c1[0], c0[1] + c1[1]);
+            *reinterpret_cast<float2*>(out + 8 * 8) = make_float2(c0[2] + c1[2], c0[3] + c1[3]);
         }
         block_sync<FUSED>();
-        // Softmax statistics: warp h owns query head h.
+        // Softmax statistics: warp h owns query head h; a lane takes rows lane and lane + 32.
         if (warp < G) {
+            float fresh_score = 0.0f;
+            if (has_new) {  // the new token's key is still f32
+                const float4 ka = *reinterpret_cast<const float4*>(&sm.kf[8 * lane]), kb = *reinterpret_cast<const float4*>(&sm.kf[8 * lane + 4]);
+                const float4 qa = *reinterpret_cast<const float4*>(&sm.q[warp][8 * lane]), qc = *reinterpret_cast<const float4*>(&sm.q[warp][8 * lane + 4]);
+                fresh_score = warp_sum(ka.x * qa.x + ka.y * qa.y + ka.z * qa.z + ka.w * qa.w + kb.x * qc.x + kb.y * qc.y + kb.z * qc.z + kb.w * qc.w);
+            }
+            float sc[TILE / 32];
             float m = -INFINITY;
-            for (uint32_t r = lane; r < cnt; r += 32) m = fmaxf(m, sm.p[r][warp]);
+#pragma unroll
+            for (int u = 0; u < TILE / 32; u++) {
+                const uint32_t r = lane + 32 * u;
+                float v = -INFINITY;
+                if (r < loaded) v = (sm.s[0][r][warp] + sm.s[1][r][warp]) + (sm.s[0][r][G + warp] + sm.s[1][r][G + warp]);
+                else if (r < cnt) v = fresh_score;
+                sc[u] = v;
+                m = fmaxf(m, v);
+            }
             m = warp_max(m);
             const float mold = sm.mrun[warp], mnew = fmaxf(mold, m);
             float l = 0.0f;
-            for (uint32_t r = lane; r < cnt; r += 32) {
-                const float e = exp2f(sm.p[r][warp] - mnew);
-                sm.p[r][warp] = e;
+#pragma unroll
+            for (int u = 0; u < TILE / 32; u++) {
+                const uint32_t r = lane + 32 * u;
+                const float e = r < cnt ? exp2f(sc[u] - mnew) : 0.0f;
                 l += e;
+                __half hi, lo;
+                split_f16(r < loaded ? e : 0.0f, hi, lo);  // the new token's row goes through vf, not through the tile
+                sm.pt[warp][r] = hi, sm.pt[G + warp][r] = lo;
+                if (has_new && r == cnt - 1) sm.pnew[warp] = e;
             }
             l = warp_sum(l);
             if (lane == 0) {
@@ -255,15 +319,45 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, uin
             }
         }
         block_sync<FUSED>();
-        // Values: one thread per dimension, all heads of the group.
+        // Values.
+        {
+            const float c = sm.corr[ohead];
 #pragma unroll
-        for (int h = 0; h < G; h++) acc[h] *= sm.corr[h];
-        for (uint32_t r = 0; r < cnt; r++) {
-            const float vv = (has_new && r == cnt - 1) ? sm.vf[tid] : __half2float(sm.v[r][tid]);
+            for (int t = 0; t < 4; t++) acc[t][0] *= c, acc[t][1] *= c;
 #pragma unroll
-            for (int h = 0; h < G; h++) acc[h] = fmaf(sm.p[r][h], vv, acc[h]);
+            for (int ks = 0; ks < TILE / 16; ks++) {
+                const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&sm.pt[orow][ks * 16 + 2 * (lane & 3)]);
+                const uint32_t pa2 = *reinterpret_cast<const uint32_t*>(&sm.pt[orow][ks * 16 + 8 + 2 * (lane & 3)]);
+#pragma unroll
+                for (int t = 0; t < 4; t += 2) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, &sm.v[ks * 16 + (lane & 15)][warp * 32 + t * 8 + (lane >> 4) * 8]);
+                    mma_16816(acc[t], pa0, 0u, pa2, 0u, b[0], b[1]);
+                    mma_16816(acc[t + 1], pa0, 0u, pa2, 0u, b[2], b[3]);
+                }
+            }
+            if (has_new && orow < G) {
+                const float pn = sm.pnew[orow];
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const float2 vf = *reinterpret_cast<const float2*>(&sm.vf[warp * 32 + t * 8 + 2 * (lane & 3)]);
+                    acc[t][0] = fmaf(pn, vf.x, acc[t][0]), acc[t][1] = fmaf(pn, vf.y, acc[t][1]);
+                }
+            }
         }
     }
+    // High and low rows together, then through shared memory to one thread per dimension with all heads of the group.
+    block_sync<FUSED>();  // the queries are no longer read
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const float v0 = acc[t][0] + __shfl_xor_sync(0xffffffffu, acc[t][0], 4 * G);
+        const float v1 = acc[t][1] + __shfl_xor_sync(0xffffffffu, acc[t][1], 4 * G);
+        if (orow < G) *reinterpret_cast<float2*>(&sm.q[orow][warp * 32 + t * 8 + 2 * (lane & 3)]) = make_float2(v0, v1);
+    }
+    block_sync<FUSED>();
+    float out[G];
+#pragma unroll
+    for (int h = 0; h < G; h++) out[h] = sm.q[h][tid];
 
     const uint32_t stride = 2 * G + G * D;  // floats per partial: maxima, sums, outputs
     if (p.defer) {
@@ -271,13 +365,13 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, uin
         float* mine = p.partial + (size_t)(g * p.splits + sp) * stride;
         if (tid < G) mine[tid] = sm.mrun[tid], mine[G + tid] = sm.lrun[tid];
 #pragma unroll
-        for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = acc[h];
+        for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = out[h];
         return;
     }
     if (used == 1) {
 #pragma unroll
         for (int h = 0; h < G; h++) {
-            const float o = acc[h] / sm.lrun[h];
+            const float o = out[h] / sm.lrun[h];
             const size_t at = (size_t)(g * G + h) * D + tid;
             if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(o);
             else static_cast<float*>(p.out)[at] = o;
@@ -287,7 +381,7 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, uin
     float* mine = p.partial + (size_t)(g * p.splits + sp) * stride;
     if (tid < G) mine[tid] = sm.mrun[tid], mine[G + tid] = sm.lrun[tid];
 #pragma unroll
-    for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = acc[h];
+    for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = out[h];
     __threadfence();
     block_sync<FUSED>();
     if (tid == 0) sm.last = (atomicAdd(p.count + g, 1u) == used - 1) ? 1u : 0u;

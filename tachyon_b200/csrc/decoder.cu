@@ -85,6 +85,7 @@ struct tb_decoder {
     uint32_t* grid_counter = nullptr;
     bool fused = false;
     std::vector<StepPhase>* collect = nullptr;  // when set, step_ops records descriptors instead of launching
+    unsigned long long* stamps = nullptr;       // when set, launch number i of step_ops stamps its timeline at stamps + 8 * i
     float embed_scale = 1.0f;
 };
 
@@ -161,7 +162,9 @@ void layout(tb_decoder* d, char* base) {
         L.kc = reinterpret_cast<__half*>(base + t.take(cache));
         L.vc = reinterpret_cast<__half*>(base + t.take(cache));
         // Blocks per key-value head: spans of about 32 positions (sliding) or 128 (global, two tiles), within the machine.
-        const uint32_t per = L.global ? 128 : 32;
+        static const uint32_t span_global = getenv("TACHYON_B200_SPAN_GLOBAL") ? (uint32_t)atoi(getenv("TACHYON_B200_SPAN_GLOBAL")) : 128u;
+        static const uint32_t span_sliding = getenv("TACHYON_B200_SPAN_SLIDING") ? (uint32_t)atoi(getenv("TACHYON_B200_SPAN_SLIDING")) : 64u;
+        const uint32_t per = std::max(16u, L.global ? span_global : span_sliding);
         L.splits = (L.window + per - 1) / per;
         const uint32_t most = (uint32_t)(2 * d->ctx->sms) / c.kv_heads;
         if (L.splits > most) L.splits = most;
@@ -208,6 +211,7 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
 
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols;
+    if (d->stamps) p.stamps = d->stamps + 8 * (size_t)d->launches;
     d->launches++;
     if (d->collect) {
         if (!step_supports(p)) return fail(UNSUPPORTED, "fused step: no code path for this product");
@@ -260,6 +264,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             ph.kind = PH_ATTEND, ph.a = a;
             d->collect->push_back(ph);
         } else {
+            if (d->stamps) a.stamps = d->stamps + 8 * (size_t)d->launches;
             TB_TRY(launch_attend(d->ctx, a));
         }
         d->launches++;
@@ -716,19 +721,48 @@ int tb_decoder_step_launches(tb_decoder* d, uint32_t* launches) {
 
 int tb_decoder_timeline(tb_decoder* d, uint32_t token, uint64_t* host_out, uint32_t* phases) {
     TB_TRY(ready(d, 1));
-    if (!d->fused) return fail(UNSUPPORTED, "tb_decoder_timeline: only the fused step records a timeline");
     if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_timeline: a generation is running; stop it first");
-    if (phases) *phases = d->phase_count;
+    const uint32_t count = d->fused ? d->phase_count : 2 + 5 * d->cfg.layers;
+    if (phases) *phases = count;
     if (!host_out) return OK;
-    const size_t bytes = (size_t)2 * d->phase_count * 4 * sizeof(unsigned long long);
+    const size_t bytes = (size_t)2 * count * 4 * sizeof(unsigned long long);
+    cudaStream_t s = d->ctx->stream;
     unsigned long long* dev = nullptr;
     TB_CUDA(cudaMalloc(&dev, bytes));
-    cudaError_t e = cudaMemsetAsync(dev, 0, bytes, d->ctx->stream);
+    cudaError_t e = cudaMemsetAsync(dev, 0, bytes, s);
     int st = OK;
     if (e == cudaSuccess) st = feed_token(d, token);
-    if (e == cudaSuccess && st == OK) st = launch_step(d->ctx, d->phase_dev[0], d->phase_count, d->grid_counter, d->state, dev);
-    if (e == cudaSuccess && st == OK) e = cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, d->ctx->stream);
-    if (e == cudaSuccess && st == OK) e = cudaStreamSynchronize(d->ctx->stream);
+    if (d->fused) {
+        if (e == cudaSuccess && st == OK) st = launch_step(d->ctx, d->phase_dev[0], d->phase_count, d->grid_counter, d->state, dev);
+        if (e == cudaSuccess && st == OK) e = cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, s);
+    } else if (e == cudaSuccess && st == OK) {
+        // One launch per phase: the step is captured once more with every kernel told where to leave its stamps, and
+        // replayed as a graph so that the host's launch cost stays out of the picture.  Kernel i's eight words are the
+        // first block's four stamps, then the last block's; they are reordered to [block][phase][4] on the way out.
+        uint32_t* word = nullptr;
+        e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&word), d->words, 0);
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        if (e == cudaSuccess) e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            d->stamps = dev;
+            st = step_ops(d, word);
+            d->stamps = nullptr;
+            e = cudaStreamEndCapture(s, &graph);
+        }
+        if (e == cudaSuccess && st == OK) e = cudaGraphInstantiate(&exec, graph, 0);
+        if (e == cudaSuccess && st == OK) e = cudaGraphLaunch(exec, s);
+        std::vector<unsigned long long> raw((size_t)count * 8);
+        if (e == cudaSuccess && st == OK) e = cudaMemcpyAsync(raw.data(), dev, bytes, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess && st == OK) e = cudaStreamSynchronize(s);
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+        if (e == cudaSuccess && st == OK)
+            for (uint32_t i = 0; i < count; i++)
+                for (int b = 0; b < 2; b++)
+                    for (int k = 0; k < 4; k++) host_out[((size_t)b * count + i) * 4 + k] = raw[(size_t)i * 8 + b * 4 + k];
+    }
+    if (e == cudaSuccess && st == OK) e = cudaStreamSynchronize(s);
     cudaFree(dev);
     if (e != cudaSuccess) return cuda_fail(e, "tb_decoder_timeline");
     if (st == OK) d->pos++;

@@ -108,17 +108,40 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         if (span > 64u) span = (span + 63u) / 64u * 64u;
         const uint32_t used = (n + span - 1) / span;
         const float* base = p.att_partial + (size_t)g * p.att_splits * stride;
+        // A warp's threads share a head.  Lane k fetches split k's maximum and sum, so the statistics of up to 32 splits
+        // cost one trip to the L2; the outputs are fetched eight splits at a time, asked for before the statistics so
+        // that both are in flight together.  The weights 2^(m_s - M) then go from lane to lane.
+        const uint32_t lane = (uint32_t)t & 31u;
         float M = -INFINITY, Lsum = 0.0f;
         float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 4
-        for (uint32_t s2 = 0; s2 < used; s2++) {
-            const float* ps = base + (size_t)s2 * stride;
-            const float m = ld_cg_f(ps + hh), l = ld_cg_f(ps + G + hh);
-            const float4 a = ld_cg_f4(ps + 2 * G + hh * 256 + d0);
-            const float Mn = fmaxf(M, m), c = exp2f(M - Mn), w = exp2f(m - Mn);
-            Lsum = fmaf(Lsum, c, w * l);
-            o.x = fmaf(o.x, c, w * a.x), o.y = fmaf(o.y, c, w * a.y), o.z = fmaf(o.z, c, w * a.z), o.w = fmaf(o.w, c, w * a.w);
-            M = Mn;
+        for (uint32_t s0 = 0; s0 < used; s0 += 32) {
+            const uint32_t nch = min(32u, used - s0);
+            float wl = 0.0f;
+            for (uint32_t b0 = 0; b0 < nch; b0 += 8) {
+                float4 a[8];
+#pragma unroll
+                for (uint32_t k = 0; k < 8; k++)
+                    if (b0 + k < nch) a[k] = ld_cg_f4(base + (size_t)(s0 + b0 + k) * stride + 2 * G + hh * 256 + d0);
+                if (b0 == 0) {
+                    float ml = -INFINITY, ll = 0.0f;
+                    if (lane < nch) {
+                        const float* ps = base + (size_t)(s0 + lane) * stride;
+                        ml = ld_cg_f(ps + hh), ll = ld_cg_f(ps + G + hh);
+                    }
+                    const float Mn = fmaxf(M, warp_max(ml)), c = exp2f(M - Mn);
+                    wl = lane < nch ? exp2f(ml - Mn) : 0.0f;
+                    Lsum = fmaf(Lsum, c, warp_sum(wl * ll));
+                    o.x *= c, o.y *= c, o.z *= c, o.w *= c;
+                    M = Mn;
+                }
+#pragma unroll
+                for (uint32_t k = 0; k < 8; k++) {
+                    if (b0 + k < nch) {
+                        const float wt = __shfl_sync(0xffffffffu, wl, b0 + k);
+                        o.x = fmaf(wt, a[k].x, o.x), o.y = fmaf(wt, a[k].y, o.y), o.z = fmaf(wt, a[k].z, o.z), o.w = fmaf(wt, a[k].w, o.w);
+                    }
+                }
+            }
         }
         const float inv = 1.0f / Lsum;
         store_planes<WPR>(raw, t, o.x * inv, o.y * inv, o.z * inv, o.w * inv);
@@ -232,9 +255,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
         if (p.yres != nullptr) nw1 = __ldg(reinterpret_cast<const float4*>(p.w1 + (size_t)threadIdx.x * 4));
         if (p.w2 != nullptr) nw2 = __ldg(reinterpret_cast<const float4*>(p.w2 + (size_t)threadIdx.x * 4));
     }
+    unsigned long long* stamp = nullptr;
+    if (p.stamps != nullptr && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) stamp = p.stamps + (blockIdx.x == 0 ? 0 : 4);
+    if (stamp) stamp[0] = global_ns();
     pdl_wait();
+    if (stamp) stamp[1] = global_ns();
     build_planes<WPR, XMODE>(p, raw, threadIdx.x, nw1, nw2);
     named_bar_sync(1, CTHREADS);
+    if (stamp) stamp[2] = global_ns();
     const int seg = warp % WPR, grp = warp / WPR;  // the warp's column segment, and its row group within a stage
     const int first = (lane >> 2) & 1;             // which 16-byte half of its blocks the lane loads first (bank spread)
     Planes pl[2];
@@ -306,6 +334,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
         }
     }
 
+    if (stamp) stamp[3] = global_ns();
     if constexpr (EPI == EPI_ARGMAX) {
         // Largest value, lowest row among equals (ptx/sample.rs:91-97): the key orders by value, then by inverted row.
         float* sbv = reinterpret_cast<float*>(raw + L::BESTV);

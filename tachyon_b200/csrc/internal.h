@@ -85,6 +85,9 @@ struct GemvParams {
     uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
     uint32_t trace_mask = 0;
     Prefetch pf;                  // optional hint for the L2
+    // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for
+    // the previous kernel, after the prologue and at the end.
+    unsigned long long* stamps = nullptr;
     // X_ATTN: x is the attention output, merged here from the splits' partial results
     // (layout of AttendParams::partial): x[h*256 + d] = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s.
     const float* att_partial = nullptr;
@@ -112,6 +115,7 @@ struct AttendParams {
     void* out = nullptr;           // [heads*256] f32 or f16
     int out_f16 = 0;
     Prefetch pf;                   // optional hint for the L2
+    unsigned long long* stamps = nullptr;  // optional timeline, as in GemvParams (the third stamp stays zero)
     uint32_t defer = 0;            // != 0: every split only stores its partial; the product that follows merges them (X_ATTN)
     uint32_t early = 0;            // != 0: the position and the older cache rows are final before the previous kernel in the
                                    // stream started, so the first tile may be fetched ahead of griddepcontrol.wait

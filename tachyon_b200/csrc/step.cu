@@ -24,7 +24,7 @@ constexpr int SEG = 2048;
 constexpr int NST = 4;              // ring stages
 constexpr int STAGE_W = 32768;      // weight bytes per stage: 16 rows of 2048, 2 rows of 16384
 constexpr int STAGE_S = STAGE_W / 16;
-constexpr int AREA = 73728;         // attention's tiles, or the planes of a vector longer than 2048
+constexpr int AREA = 81920;         // attention's tiles, or the planes of a vector longer than 2048
 
 // Shared memory, in this order.
 constexpr int OFF_W = 0;
@@ -40,8 +40,7 @@ constexpr int OFF_RED = OFF_EMPTY + NST * 8;          // float [2][CONSUMERS]
 constexpr int OFF_BESTV = OFF_RED + 2 * CONSUMERS * 4;  // float [2 * CONSUMERS]
 constexpr int OFF_BESTI = OFF_BESTV + 2 * CONSUMERS * 4;
 constexpr int OFF_SUMS = OFF_BESTI + 2 * CONSUMERS * 4;  // float4 [CONSUMERS]
-constexpr int OFF_FLAGS = OFF_SUMS + CONSUMERS * 16;     // uint32: [0] abort, [1] attention's first tile is on its way; then attention's mbarrier
-constexpr int OFF_ABAR = OFF_FLAGS + 8;
+constexpr int OFF_FLAGS = OFF_SUMS + CONSUMERS * 16;     // uint32: [0] abort, [1] attention's first tile is on its way
 constexpr int OFF_PHASE = OFF_FLAGS + 16;                // two descriptors: phase ph lives in slot ph % 2, the next one beside it
 constexpr int PHASE_BYTES = ((int)sizeof(StepPhase) + 15) / 16 * 16;
 constexpr int SMEM_BYTES = OFF_PHASE + 2 * PHASE_BYTES;
@@ -383,7 +382,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
     uint64_t* empty = reinterpret_cast<uint64_t*>(raw + OFF_EMPTY);
     if (threadIdx.x == 0) {
         for (int i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], CONSUMERS);
-        mbar_init(reinterpret_cast<uint64_t*>(raw + OFF_ABAR), 1);
         reinterpret_cast<uint32_t*>(raw + OFF_FLAGS)[0] = 0;
         reinterpret_cast<uint32_t*>(raw + OFF_FLAGS)[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -438,10 +436,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
 
     // Consumers.
     attend::Smem& asm_ = *reinterpret_cast<attend::Smem*>(raw + OFF_AREA);
-    uint64_t* abar = reinterpret_cast<uint64_t*>(raw + OFF_ABAR);
     uint32_t* flags = reinterpret_cast<uint32_t*>(raw + OFF_FLAGS);
     const uint32_t pos = ld_cg_u(state);  // the step's position: only the last phase changes it
-    uint32_t gi = 0, aphase = 0;
+    uint32_t gi = 0;
     bool ok = true;
     Best best;
     // Norm weights of the phase about to run: fetched before the barrier in front of it (they are model constants and
@@ -465,23 +462,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
         } else if (cur.kind == PH_GEMV) {
             // When attention comes next, its first tile of keys and values (written by earlier steps) can already be
             // on its way while this product runs: the area it lands in is idle during a 2048-column product.
-            if (threadIdx.x == 0 && ph + 1 < nphases && cur.g.cols == 2048 && nxt.kind == PH_ATTEND) {
+            if (threadIdx.x < attend::THREADS && ph + 1 < nphases && cur.g.cols == 2048 && nxt.kind == PH_ATTEND) {
                 const AttendParams& an = nxt.a;
                 bool sent = false;
-                if (blockIdx.x < an.kv_heads * an.splits) sent = attend::issue_first_tile(an, asm_, abar, blockIdx.x % an.kv_heads, blockIdx.x / an.kv_heads, pos);
-                flags[1] = sent ? 1u : 0u;
+                if (blockIdx.x < an.kv_heads * an.splits)
+                    sent = attend::load_first_tile(an, asm_, blockIdx.x % an.kv_heads, blockIdx.x / an.kv_heads, pos, (int)threadIdx.x);
+                if (threadIdx.x == 0) flags[1] = sent ? 1u : 0u;
             }
             run_gemv(cur.g, raw, gi, ok, status, best, pos, stamp ? mine + ph * 4 : nullptr, nw1, nw2);
         } else {
             const AttendParams& a = cur.a;
             const uint32_t items = a.kv_heads * a.splits, group = a.heads / a.kv_heads;
             if (threadIdx.x < attend::THREADS) {
+                const attend::Trig trig = attend::rope_trig(a.freq, pos, lane);
                 for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
                     const bool pre = item == blockIdx.x && flags[1] != 0;
                     attend::block_sync<true>();
-                    if (group == 4) attend::attend_body<4, true>(a, asm_, abar, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, status, aphase);
-                    else if (group == 2) attend::attend_body<2, true>(a, asm_, abar, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, status, aphase);
-                    else attend::attend_body<1, true>(a, asm_, abar, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, status, aphase);
+                    if (group == 4) attend::attend_body<4, true>(a, asm_, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, trig);
+                    else if (group == 2) attend::attend_body<2, true>(a, asm_, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, trig);
+                    else attend::attend_body<1, true>(a, asm_, threadIdx.x, item % a.kv_heads, item / a.kv_heads, pos, pre, trig);
                 }
             }
         }
