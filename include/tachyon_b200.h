@@ -119,6 +119,18 @@ TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* s
 enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2, TB_GEMM_ADD = 3, TB_GEMM_GEGLU_ERF = 4, TB_GEMM_GELU_ERF = 5 };
 TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
 
+/*
+ * The reference's own decode formats, for callers that hold a model converted by the reference (quant.rs:47-130):
+ * Q4 weights, two per byte in the order of quant.rs:60-66 with one f16 scale per 64, and Q8 activations, i8 codes with
+ * a pair [s, s * sum q] per 32.  Both kernels repeat the reference kernels' f32 operations one by one (round to
+ * nearest throughout, the same order of sums), so the outputs are the reference's bit for bit.
+ *   tb_quant_q8 = quant_q8 (ptx/mod.rs:191-212, 393-399): x f32 [n] -> q i8 [n], pairs f32 [n / 32][2]; n % 32 == 0.
+ *   tb_gemv_q4  = gemv_q4 (ptx/gemv.rs:156-195): y f32 [rows] = W (packed [rows][cols / 2], scales f16 [rows][cols / 64])
+ *                 times (q, pairs); cols a multiple of 64 (powers of two from 512 to 16384 stream through shared memory).
+ */
+TB_API int tb_quant_q8(tb_context* ctx, const float* x, uint32_t n, int8_t* q, float* pairs);
+TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const int8_t* q, const float* pairs, float* y, uint32_t rows, uint32_t cols);
+
 /* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
 TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
             float* x_out);

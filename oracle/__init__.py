@@ -70,6 +70,7 @@ def _declare(l: C.CDLL) -> None:
         "tbo_q8_blocks": (None, [vp, sz, i32, vp, vp]),
         "tbo_q8p_pairs": (None, [vp, sz]),
         "tbo_product_q4": (None, [vp, vp, vp, sz, sz, vp, vp]),
+        "tbo_gemv_q4": (None, [vp, vp, vp, vp, sz, sz, vp]),
         "tbo_gemv_q8": (None, [vp, vp, vp, sz, sz, vp, vp, vp]),
         "tbo_normalize": (None, [vp, sz, vp, f64]),
         "tbo_rotate": (None, [vp, sz, vp, u32]),
@@ -141,6 +142,15 @@ def product_q4(packed, scales, x, rows):
     s, b = np.zeros(rows, np.float64), np.zeros(rows, np.float64)
     lib().tbo_product_q4(ptr(packed), ptr(scales), ptr(x), rows, x.size, ptr(s), ptr(b))
     return s, b
+
+
+def gemv_q4(packed, scales, q, pairs, rows: int):
+    """The reference's gemv_q4 kernel, bit for bit: f32 y [rows] from Q4 weights and Q8 activations (codes, pairs)."""
+    q = np.ascontiguousarray(q, np.int8)
+    pairs = np.ascontiguousarray(pairs, np.float32)
+    y = np.zeros(rows, np.float32)
+    lib().tbo_gemv_q4(ptr(packed), ptr(scales), ptr(q), ptr(pairs), rows, q.size, ptr(y))
+    return y
 
 
 def gemv_q8(w: np.ndarray, scales: np.ndarray, x: np.ndarray):

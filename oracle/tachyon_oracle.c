@@ -172,6 +172,40 @@ TBO_API void tbo_product_q4(const uint8_t *packed, const uint16_t *scales, const
     free(s);
 }
 
+/* crates/tachyon/src/ptx/gemv.rs:88-110, 156-195: gemv_q4 as the GPU computes it, operation by operation.  One warp per
+ * row; lane l takes the chunks of 32 weights l, l + 32, ... in rising order; a chunk adds
+ * fma(fma(ss, -8, f32(sum n*q) * sx), f32(scale), sum) to the lane's f32 sum (mul.f32, fma.rn.f32, fma.rn.f32); the 32
+ * sums then meet in a butterfly (shfl.bfly 16, 8, 4, 2, 1; add.f32) and lane 0 stores.  All of it is IEEE
+ * round-to-nearest, so this C gives the kernel's bits. */
+TBO_API void tbo_gemv_q4(const uint8_t *packed, const uint16_t *scales, const int8_t *q, const float *pairs, size_t rows,
+                         size_t cols, float *y) {
+    size_t nch = cols / 32;
+    for (size_t r = 0; r < rows; r++) {
+        float lane[32];
+        for (size_t l = 0; l < 32; l++) {
+            float sum = 0.0f;
+            for (size_t c = l; c < nch; c += 32) {
+                int32_t acc = 0;
+                for (size_t j = 0; j < 32; j++) {
+                    size_t col = c * 32 + j, g = (r * cols + col) / 64, k = col % 64;
+                    int nib = (packed[g * 32 + k / 8 * 4 + k % 4] >> (k % 8 / 4 * 4)) & 15;
+                    acc += nib * (int32_t)q[col];
+                }
+                float f = (float)acc * pairs[2 * c];
+                f = fmaf(pairs[2 * c + 1], -8.0f, f);
+                sum = fmaf(f, tbo_f16_value(scales[(r * cols + c * 32) / 64]), sum);
+            }
+            lane[l] = sum;
+        }
+        for (size_t k = 16; k > 0; k /= 2) {
+            float next[32];
+            for (size_t l = 0; l < 32; l++) next[l] = lane[l] + lane[l ^ k];
+            memcpy(lane, next, sizeof lane);
+        }
+        y[r] = lane[0];
+    }
+}
+
 /* ------------------------------------------------------------------------------------------------ */
 /* The benchmark's own weight format: int8 codes, one f16 scale per 32 along K; activation in f16 or  */
 /* f32; f32 accumulation.  Follows the shape of crates/tachyon/tests/common/mod.rs:95-112 (block sums */

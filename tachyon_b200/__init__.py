@@ -120,6 +120,14 @@ class Context:
     def gemv_q8(self, w: DevBuf, s: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, y_dtype: int, rows: int, cols: int) -> None:
         check(self.lib.tb_gemv_q8(self.handle, w.ptr, s.ptr, x.ptr, x_dtype, y.ptr, y_dtype, rows, cols))
 
+    def quant_q8(self, x: DevBuf, n: int, q: DevBuf, pairs: DevBuf) -> None:
+        """tb_quant_q8 (the reference's quant_q8): f32 x [n] -> i8 codes [n] and f32 pairs [n / 32][2]."""
+        check(self.lib.tb_quant_q8(self.handle, x.ptr, n, q.ptr, pairs.ptr))
+
+    def gemv_q4(self, packed: DevBuf, scales: DevBuf, q: DevBuf, pairs: DevBuf, y: DevBuf, rows: int, cols: int) -> None:
+        """tb_gemv_q4 (the reference's gemv_q4): Q4 weights x Q8 activations -> f32 y [rows]."""
+        check(self.lib.tb_gemv_q4(self.handle, packed.ptr, scales.ptr, q.ptr, pairs.ptr, y.ptr, rows, cols))
+
     def gemv_q8_norm(self, w, s, h, y_res, w1, w2, eps, hscale, h_out, y, rows, cols, geglu=False) -> None:
         p = lambda b: None if b is None else b.ptr
         check(self.lib.tb_gemv_q8_norm(self.handle, w.ptr, s.ptr, h.ptr, p(y_res), p(w1), p(w2), eps, hscale, p(h_out), y.ptr, rows, cols, int(geglu)))

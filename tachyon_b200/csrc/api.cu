@@ -192,6 +192,16 @@ int tb_gemv_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const v
     return launch_gemv(ctx, p);
 }
 
+int tb_quant_q8(tb_context* ctx, const float* x, uint32_t n, int8_t* q, float* pairs) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_quant_q8(ctx, x, q, pairs, n);
+}
+
+int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const int8_t* q, const float* pairs, float* y, uint32_t rows, uint32_t cols) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_gemv_q4(ctx, packed, scales, q, pairs, y, rows, cols);
+}
+
 int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, const float* h, const float* y_res, const float* w1, const float* w2, float eps,
                     float hscale, float* h_out, float* y, uint32_t rows, uint32_t cols, int geglu) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");

@@ -174,6 +174,10 @@ int launch_fill_gauss_f16(tb_context* ctx, uint64_t seed, uint64_t stream_id, __
 int launch_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, float* x, size_t n, float lo, float hi);
 int launch_interleave_rows(tb_context* ctx, const void* src, void* dst, uint32_t half_rows, uint32_t row_bytes);
 
+// The reference's own formats (q4.cu): f32 -> Q8 codes and [s, s * sum q] pairs; Q4 weights x Q8 activations.
+int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t n);
+int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols);
+
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {

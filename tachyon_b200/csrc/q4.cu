@@ -1,0 +1,218 @@
+// The reference's own decode formats: Q4 weights (two per byte, an f16 scale per group of 64, crates/tachyon/src/quant.rs:47-82)
+// times Q8 activations (i8 codes and [s, s * sum q] per block of 32, quant.rs:93-130), f32 out.
+//
+//   quant_q8_kernel  = quant_q8   (ptx/mod.rs:191-212, 393-399)
+//   gemv_q4_kernel   = gemv_q4    (ptx/gemv.rs:156-195)
+//
+// Both follow the reference kernels' arithmetic operation by operation, all of it IEEE f32 with round-to-nearest
+// (div.rn, mul.rn, fma.rn, cvt.rni) or exact integer sums, so the results are the reference's bit for bit:
+//   * a block of 32 activations: d = amax / 127, q = rni(x * (127 / amax)), pair [d, f32(sum q) * d];
+//   * a row: lane l of one warp takes the chunks of 32 weights l, l + 32, ... in rising order, each adding
+//     fma(fma(ss, -8, f32(sum n q) * sx), f32(scale), sum) to the lane's sum, and the lanes' sums meet in a butterfly
+//     with partners 16, 8, 4, 2, 1.
+// What differs is how the bytes travel: a producer warp streams each block's rows through a ring of shared-memory
+// stages with bulk copies, ahead of the wait for the previous kernel, as the Q8 kernel of gemv.cu does.
+#include "common.cuh"
+#include "internal.h"
+
+#include <algorithm>
+
+namespace tb {
+
+namespace {
+
+constexpr int CONSUMERS = 16;
+constexpr int CTHREADS = CONSUMERS * 32;
+constexpr int THREADS = CTHREADS + 32;
+constexpr int STAGE_W = 32768;            // bytes of packed weights per stage
+constexpr int STAGE_S = STAGE_W / 16;     // their scales: 2 bytes per 32 bytes of weights
+constexpr int NST = 6;
+
+struct Layout {
+    static constexpr int W = 0;
+    static constexpr int S = W + NST * STAGE_W;
+    static constexpr int FULL = S + NST * STAGE_S;
+    static constexpr int EMPTY = FULL + NST * 8;
+    static constexpr int X = EMPTY + NST * 8 + 32;  // the activations: first and second 16 bytes of every chunk, then the pairs
+};
+static size_t smem_bytes(uint32_t cols) { return (size_t)Layout::X + cols + cols / 4; }
+
+// One warp per 32 values, as the reference's q8 (ptx/mod.rs:191-212).
+__global__ void __launch_bounds__(256) quant_q8_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float2* __restrict__ s, uint32_t n) {
+    pdl_wait();
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;  // n is a multiple of 32: whole warps leave together
+    const float v = x[i];
+    const float amax = warp_max(fabsf(v));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    const int code = __float2int_rn(__fmul_rn(v, inv));
+    q[i] = static_cast<int8_t>(code);
+    int sum = code;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((i & 31u) == 0) s[i >> 5] = make_float2(d, __fmul_rn(static_cast<float>(sum), d));
+}
+
+struct Q4Params {
+    const uint8_t* w;      // [rows][cols / 2]
+    const __half* ws;      // [rows][cols / 64]
+    const int8_t* q;       // [cols]
+    const float2* s;       // [cols / 32]
+    float* y;              // [rows]
+    uint32_t rows, cols;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, uint32_t* status) {
+    extern __shared__ __align__(128) uint8_t raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rb = p.cols / 2;            // bytes per row
+    const uint32_t rps = STAGE_W / rb;         // rows per stage: 32 at 2048 columns, 4 at 16384
+    const uint32_t r0 = static_cast<uint32_t>((uint64_t)p.rows * blockIdx.x / gridDim.x);
+    const uint32_t r1 = static_cast<uint32_t>((uint64_t)p.rows * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t nst = (r1 - r0 + rps - 1) / rps;
+    // Warps per stage: all sixteen when a stage holds at least sixteen rows, else one per row, the stages going round
+    // the groups of warps.
+    const uint32_t wps = min(rps, (uint32_t)CONSUMERS), groups = CONSUMERS / wps;
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + Layout::FULL);
+    uint64_t* empty = reinterpret_cast<uint64_t*>(raw + Layout::EMPTY);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], wps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == CONSUMERS) {
+        // Producer: nothing it reads is written by another kernel.
+        if (lane == 0) {
+            for (uint32_t i = 0; i < nst; i++) {
+                const uint32_t slot = i % NST;
+                if (i >= NST && !mbar_wait(&empty[slot], ((i / NST) - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
+                }
+                const uint32_t row = r0 + i * rps, here = min(rps, r1 - row);
+                const uint32_t bw = here * rb, bs = here * (p.cols / 32);
+                mbar_expect_tx(&full[slot], bw + bs);
+                bulk_load(raw + Layout::W + slot * STAGE_W, p.w + (size_t)row * rb, bw, &full[slot]);
+                bulk_load(raw + Layout::S + slot * STAGE_S, p.ws + (size_t)row * (p.cols / 64), bs, &full[slot]);
+            }
+            pdl_launch_dependents();
+        }
+        return;
+    }
+
+    // Consumers.  The activations come from the kernel before this one.
+    pdl_wait();
+    uint4* xlo = reinterpret_cast<uint4*>(raw + Layout::X);
+    uint4* xhi = xlo + p.cols / 32;
+    float2* xs = reinterpret_cast<float2*>(xhi + p.cols / 32);
+    const uint32_t nch = p.cols / 32;
+    for (uint32_t i = threadIdx.x; i < nch * 2; i += CTHREADS) {
+        const uint4 v = ld_cg_u4(reinterpret_cast<const uint4*>(p.q) + i);
+        if (i & 1) xhi[i >> 1] = v;
+        else xlo[i >> 1] = v;
+    }
+    for (uint32_t i = threadIdx.x; i < nch; i += CTHREADS) xs[i] = __ldcg(p.s + i);
+    named_bar_sync(1, CTHREADS);
+
+    bool ok = true;
+    const uint32_t grp = (uint32_t)warp / wps, wl = (uint32_t)warp % wps;
+    for (uint32_t i = grp; i < nst; i += groups) {
+        const uint32_t slot = i % NST;
+        if (ok && !mbar_wait(&full[slot], (i / NST) & 1)) {
+            atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+            ok = false;
+        }
+        for (uint32_t k = wl; k < rps; k += wps) {
+            const uint32_t row = r0 + i * rps + k;
+            if (!ok || row >= r1) break;
+            const uint4* wr = reinterpret_cast<const uint4*>(raw + Layout::W + slot * STAGE_W + (size_t)k * rb);
+            const __half* sr = reinterpret_cast<const __half*>(raw + Layout::S + slot * STAGE_S) + (size_t)k * (p.cols / 64);
+            float sum = 0.0f;
+#pragma unroll 2
+            for (uint32_t c = lane; c < nch; c += 32) {
+                const uint4 w = wr[c], a = xlo[c], b = xhi[c];
+                const float2 sc = xs[c];
+                int acc = 0;
+                acc = dp4a_su(a.x, w.x & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.y, (w.x >> 4) & 0x0F0F0F0Fu, acc);
+                acc = dp4a_su(a.z, w.y & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.w, (w.y >> 4) & 0x0F0F0F0Fu, acc);
+                acc = dp4a_su(b.x, w.z & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.y, (w.z >> 4) & 0x0F0F0F0Fu, acc);
+                acc = dp4a_su(b.z, w.w & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.w, (w.w >> 4) & 0x0F0F0F0Fu, acc);
+                float f = __fmul_rn(static_cast<float>(acc), sc.x);
+                f = __fmaf_rn(sc.y, -8.0f, f);
+                sum = __fmaf_rn(f, __half2float(sr[c >> 1]), sum);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+            if (lane == 0) p.y[row] = sum;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+    }
+}
+
+// Any other column count (a multiple of 64): one warp per row straight from global memory, the same arithmetic in
+// the same order.  The reference's other decode widths (2560, 10240) and its edge shapes take this path.
+__global__ void __launch_bounds__(128) gemv_q4_generic(const Q4Params p) {
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5), nch = p.cols / 32;
+    if (row >= p.rows) return;
+    const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)row * (p.cols / 2));
+    const __half* sr = p.ws + (size_t)row * (p.cols / 64);
+    const uint4* xq = reinterpret_cast<const uint4*>(p.q);
+    float sum = 0.0f;
+    for (uint32_t c = lane; c < nch; c += 32) {
+        const uint4 w = __ldcs(wr + c), a = ld_cg_u4(xq + 2 * c), b = ld_cg_u4(xq + 2 * c + 1);
+        const float2 sc = __ldcg(p.s + c);
+        int acc = 0;
+        acc = dp4a_su(a.x, w.x & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.y, (w.x >> 4) & 0x0F0F0F0Fu, acc);
+        acc = dp4a_su(a.z, w.y & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.w, (w.y >> 4) & 0x0F0F0F0Fu, acc);
+        acc = dp4a_su(b.x, w.z & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.y, (w.z >> 4) & 0x0F0F0F0Fu, acc);
+        acc = dp4a_su(b.z, w.w & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.w, (w.w >> 4) & 0x0F0F0F0Fu, acc);
+        float f = __fmul_rn(static_cast<float>(acc), sc.x);
+        f = __fmaf_rn(sc.y, -8.0f, f);
+        sum = __fmaf_rn(f, __half2float(sr[c >> 1]), sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+    if (lane == 0) p.y[row] = sum;
+}
+
+}  // namespace
+
+int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t n) {
+    if (!x || !q || !s) return fail(OUT_OF_RANGE, "quant_q8: null argument");
+    if (n == 0 || n % 32 != 0) return fail(OUT_OF_RANGE, "quant_q8: the length must be a positive multiple of 32");
+    if (reinterpret_cast<uintptr_t>(s) & 7) return fail(OUT_OF_RANGE, "quant_q8: the pairs must be 8-byte aligned");
+    TB_CUDA(launch_kernel(ctx, quant_q8_kernel, dim3((n + 255) / 256), dim3(256), 0, true, x, q, reinterpret_cast<float2*>(s), n));
+    return OK;
+}
+
+int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols) {
+    if (!w || !scales || !q || !s || !y) return fail(OUT_OF_RANGE, "gemv_q4: null argument");
+    if (rows == 0 || cols == 0 || cols % 64 != 0) return fail(OUT_OF_RANGE, "gemv_q4: columns must be a positive multiple of 64");
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(q)) & 15)
+        return fail(OUT_OF_RANGE, "gemv_q4: weights, scales and codes must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(s) & 7) return fail(OUT_OF_RANGE, "gemv_q4: the pairs must be 8-byte aligned");
+    Q4Params p{w, reinterpret_cast<const __half*>(scales), q, reinterpret_cast<const float2*>(s), y, rows, cols};
+    // The staged kernel wants whole rows in a stage, stages going round whole groups of warps, and a row's scales
+    // (cols / 32 bytes) copied in 16-byte units: a power of two from 512 to 16384 columns.
+    if (cols < 512 || cols > 16384 || STAGE_W % (cols / 2) != 0) {
+        TB_CUDA(launch_kernel(ctx, gemv_q4_generic, dim3((rows + 3) / 4), dim3(128), 0, true, p));
+        return OK;
+    }
+    const size_t smem = smem_bytes(cols);
+    static size_t configured[16] = {};
+    if (configured[ctx->gpu & 15] < smem) {
+        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
+        configured[ctx->gpu & 15] = smem_bytes(16384);
+    }
+    const uint32_t rps = STAGE_W / (cols / 2);
+    const uint32_t grid = std::min<uint32_t>((uint32_t)ctx->sms, (rows + rps - 1) / rps);
+    TB_CUDA(launch_kernel(ctx, gemv_q4_kernel, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
+    return OK;
+}
+
+}  // namespace tb
