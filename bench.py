@@ -330,6 +330,45 @@ def bench_gemv(args, ranks: Ranks):
                          "peak_source": how, "traffic": None, "bytes_per_launch": alg, "us_per_launch": us}}
 
 
+def bench_gemv_q4(args, ranks: Ranks):
+    """The reference's own GEMV on its own formats (benches/gemv.rs): Q4 W [16384, 2048] x Q8 x -> f32; 64 weight copies."""
+    import ctypes as C
+
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    rows, cols, copies = args.rows, args.cols, args.copies
+    lib = ctx.lib
+    wb, sb = rows * cols // 2, rows * (cols // 64) * 2
+    w, s = ctx.alloc(copies * wb), ctx.alloc(copies * sb)
+    tb.check(lib.tb_fill_codes(ctx.handle, 3, 1, w.ptr, copies * wb))  # any byte is two valid nibbles
+    tb.check(lib.tb_fill_scales(ctx.handle, 3, 2, s.ptr, copies * sb // 2, 0.02 / 8))
+    x = ctx.upload(np.random.default_rng(0).standard_normal(cols).astype(np.float32))
+    q, pairs, y = ctx.zeros(cols), ctx.zeros(cols // 32 * 8), ctx.zeros(rows * 4)
+    ctx.quant_q8(x, cols, q, pairs)
+
+    def launch(i):
+        tb.check(lib.tb_gemv_q4(ctx.handle, C.c_void_p(w.ptr + (i % copies) * wb), C.c_void_p(s.ptr + (i % copies) * sb), q.ptr, pairs.ptr, y.ptr, rows, cols))
+
+    for i in range(args.warmup):
+        launch(i)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for i in range(args.steps):
+        launch(i)
+    e1.record()
+    e1.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / args.steps
+    alg = wb + sb + cols + cols // 32 * 8 + rows * 4
+    peak, how = measured_peak_gbs()
+    return {"metric": "gemv_q4_gbs", "value": alg / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
+            "higher_is_better": True, "dtype": "int4 x int8 -> f32 (dp4a, f32 scale steps)", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"the reference's gemv_q4 {rows}x{cols} (Q4 weights, Q8 activations), {copies} weight copies cycled"}, "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak, "unit": "GB/s", "frac": alg / us / 1e3 / peak, "frac_of_8tbs": alg / us / 1e3 / HBM_SPEC_GBS,
+                         "peak_source": how, "traffic": None, "bytes_per_launch": alg, "us_per_launch": us}}
+
+
 def bench_attend(args, ranks: Ranks):
     """configs[1]: decode attention, 8 query / 2 kv heads of 256 over an f16 cache of 4096; global and sliding-512."""
     import tachyon_b200 as tb
@@ -519,7 +558,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "attend", "gemm", "prefill", "encoder"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "attend", "gemm", "prefill", "encoder"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -535,6 +574,8 @@ def main():
             line = reference_arm(args, ranks)
         elif args.workload == "gemv":
             line = bench_gemv(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "gemv_q4":
+            line = bench_gemv_q4(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "attend":
             line = bench_attend(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "gemm":

@@ -63,6 +63,25 @@ struct Q4Params {
     uint32_t rows, cols;
 };
 
+// The sum of 32 nibbles times 32 codes: weight word j holds nibbles 8j..8j+3 low and 8j+4..8j+7 high (quant.rs:60-66).
+__device__ __forceinline__ int chunk_dot(const uint4& w, const uint4& a, const uint4& b) {
+    int acc = 0;
+    acc = dp4a_su(a.x, w.x & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.y, (w.x >> 4) & 0x0F0F0F0Fu, acc);
+    acc = dp4a_su(a.z, w.y & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.w, (w.y >> 4) & 0x0F0F0F0Fu, acc);
+    acc = dp4a_su(b.x, w.z & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.y, (w.z >> 4) & 0x0F0F0F0Fu, acc);
+    acc = dp4a_su(b.z, w.w & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.w, (w.w >> 4) & 0x0F0F0F0Fu, acc);
+    return acc;
+}
+// One chunk's step of a lane's sum (gemv.rs:100-110).
+__device__ __forceinline__ float chunk_step(int acc, const float2& sc, float scale, float sum) {
+    float f = __fmul_rn(static_cast<float>(acc), sc.x);
+    f = __fmaf_rn(sc.y, -8.0f, f);
+    return __fmaf_rn(f, scale, sum);
+}
+
+// NCH > 0: a lane's NCH chunks of the activations stay in registers (rows of up to 4096 columns); NCH == 0: they are
+// read from shared memory chunk by chunk.
+template <int NCH>
 __global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, uint32_t* status) {
     extern __shared__ __align__(128) uint8_t raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,6 +135,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, u
     }
     for (uint32_t i = threadIdx.x; i < nch; i += CTHREADS) xs[i] = __ldcg(p.s + i);
     named_bar_sync(1, CTHREADS);
+    uint4 ra[NCH > 0 ? NCH : 1], rbb[NCH > 0 ? NCH : 1];
+    float2 rs[NCH > 0 ? NCH : 1];
+    if constexpr (NCH > 0) {
+#pragma unroll
+        for (int j = 0; j < NCH; j++) {
+            const uint32_t c = lane + 32 * j;
+            if (c < nch) ra[j] = xlo[c], rbb[j] = xhi[c], rs[j] = xs[c];
+        }
+    }
 
     bool ok = true;
     const uint32_t grp = (uint32_t)warp / wps, wl = (uint32_t)warp % wps;
@@ -131,18 +159,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, u
             const uint4* wr = reinterpret_cast<const uint4*>(raw + Layout::W + slot * STAGE_W + (size_t)k * rb);
             const __half* sr = reinterpret_cast<const __half*>(raw + Layout::S + slot * STAGE_S) + (size_t)k * (p.cols / 64);
             float sum = 0.0f;
+            if constexpr (NCH > 0) {
+#pragma unroll
+                for (int j = 0; j < NCH; j++) {
+                    const uint32_t c = lane + 32 * j;
+                    if (c < nch) sum = chunk_step(chunk_dot(wr[c], ra[j], rbb[j]), rs[j], __half2float(sr[c >> 1]), sum);
+                }
+            } else {
 #pragma unroll 2
-            for (uint32_t c = lane; c < nch; c += 32) {
-                const uint4 w = wr[c], a = xlo[c], b = xhi[c];
-                const float2 sc = xs[c];
-                int acc = 0;
-                acc = dp4a_su(a.x, w.x & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.y, (w.x >> 4) & 0x0F0F0F0Fu, acc);
-                acc = dp4a_su(a.z, w.y & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.w, (w.y >> 4) & 0x0F0F0F0Fu, acc);
-                acc = dp4a_su(b.x, w.z & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.y, (w.z >> 4) & 0x0F0F0F0Fu, acc);
-                acc = dp4a_su(b.z, w.w & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.w, (w.w >> 4) & 0x0F0F0F0Fu, acc);
-                float f = __fmul_rn(static_cast<float>(acc), sc.x);
-                f = __fmaf_rn(sc.y, -8.0f, f);
-                sum = __fmaf_rn(f, __half2float(sr[c >> 1]), sum);
+                for (uint32_t c = lane; c < nch; c += 32) sum = chunk_step(chunk_dot(wr[c], xlo[c], xhi[c]), xs[c], __half2float(sr[c >> 1]), sum);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
@@ -166,14 +191,7 @@ __global__ void __launch_bounds__(128) gemv_q4_generic(const Q4Params p) {
     for (uint32_t c = lane; c < nch; c += 32) {
         const uint4 w = __ldcs(wr + c), a = ld_cg_u4(xq + 2 * c), b = ld_cg_u4(xq + 2 * c + 1);
         const float2 sc = __ldcg(p.s + c);
-        int acc = 0;
-        acc = dp4a_su(a.x, w.x & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.y, (w.x >> 4) & 0x0F0F0F0Fu, acc);
-        acc = dp4a_su(a.z, w.y & 0x0F0F0F0Fu, acc), acc = dp4a_su(a.w, (w.y >> 4) & 0x0F0F0F0Fu, acc);
-        acc = dp4a_su(b.x, w.z & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.y, (w.z >> 4) & 0x0F0F0F0Fu, acc);
-        acc = dp4a_su(b.z, w.w & 0x0F0F0F0Fu, acc), acc = dp4a_su(b.w, (w.w >> 4) & 0x0F0F0F0Fu, acc);
-        float f = __fmul_rn(static_cast<float>(acc), sc.x);
-        f = __fmaf_rn(sc.y, -8.0f, f);
-        sum = __fmaf_rn(f, __half2float(sr[c >> 1]), sum);
+        sum = chunk_step(chunk_dot(w, a, b), sc, __half2float(sr[c >> 1]), sum);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
@@ -206,12 +224,18 @@ int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, co
     const size_t smem = smem_bytes(cols);
     static size_t configured[16] = {};
     if (configured[ctx->gpu & 15] < smem) {
-        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
+        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
+        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
+        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
+        TB_CUDA(cudaFuncSetAttribute(gemv_q4_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(16384)));
         configured[ctx->gpu & 15] = smem_bytes(16384);
     }
     const uint32_t rps = STAGE_W / (cols / 2);
     const uint32_t grid = std::min<uint32_t>((uint32_t)ctx->sms, (rows + rps - 1) / rps);
-    TB_CUDA(launch_kernel(ctx, gemv_q4_kernel, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
+    if (cols <= 1024) TB_CUDA(launch_kernel(ctx, gemv_q4_kernel<1>, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
+    else if (cols == 2048) TB_CUDA(launch_kernel(ctx, gemv_q4_kernel<2>, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
+    else if (cols == 4096) TB_CUDA(launch_kernel(ctx, gemv_q4_kernel<4>, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
+    else TB_CUDA(launch_kernel(ctx, gemv_q4_kernel<0>, dim3(grid), dim3(THREADS), smem, true, p, ctx->status));
     return OK;
 }
 
