@@ -130,6 +130,12 @@ TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, 
  */
 TB_API int tb_quant_q8(tb_context* ctx, const float* x, uint32_t n, int8_t* q, float* pairs);
 TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const int8_t* q, const float* pairs, float* y, uint32_t rows, uint32_t cols);
+/*
+ * The same Q4 weights, read as they are by this build's decode product: the activation (f16 or f32, device) is not
+ * rounded to Q8 but split into the exact fixed-point planes tb_gemv_q8 uses, so y = sum_g d_g sum_k (n_k - 8) x_k to
+ * f32 accuracy.  This is the product a decoder opened with TB_WEIGHTS_Q4 runs.  cols: 2048, 4096, 8192 or 16384.
+ */
+TB_API int tb_gemv_q4x(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const void* x, int x_dtype, float* y, uint32_t rows, uint32_t cols);
 
 /* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
 TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,

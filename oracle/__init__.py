@@ -71,6 +71,7 @@ def _declare(l: C.CDLL) -> None:
         "tbo_q8p_pairs": (None, [vp, sz]),
         "tbo_product_q4": (None, [vp, vp, vp, sz, sz, vp, vp]),
         "tbo_gemv_q4": (None, [vp, vp, vp, vp, sz, sz, vp]),
+        "tbo_gemv_q4x": (None, [vp, vp, vp, sz, sz, vp, vp]),
         "tbo_gemv_q8": (None, [vp, vp, vp, sz, sz, vp, vp, vp]),
         "tbo_normalize": (None, [vp, sz, vp, f64]),
         "tbo_rotate": (None, [vp, sz, vp, u32]),
@@ -151,6 +152,14 @@ def gemv_q4(packed, scales, q, pairs, rows: int):
     y = np.zeros(rows, np.float32)
     lib().tbo_gemv_q4(ptr(packed), ptr(scales), ptr(q), ptr(pairs), rows, q.size, ptr(y))
     return y
+
+
+def gemv_q4x(packed, scales, x, rows: int):
+    """(f64 y, bound) of Q4 weights times an f32 vector that is not rounded to Q8."""
+    x = np.ascontiguousarray(x, np.float32)
+    y, b = np.zeros(rows, np.float64), np.zeros(rows, np.float64)
+    lib().tbo_gemv_q4x(ptr(packed), ptr(scales), ptr(x), rows, x.size, ptr(y), ptr(b))
+    return y, b
 
 
 def gemv_q8(w: np.ndarray, scales: np.ndarray, x: np.ndarray):

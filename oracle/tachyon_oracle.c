@@ -206,6 +206,29 @@ TBO_API void tbo_gemv_q4(const uint8_t *packed, const uint16_t *scales, const in
     }
 }
 
+/* Q4 weights (quant.rs:47-82) times an f32 vector that is NOT rounded to Q8 first: y[r] = sum_g d_g sum_k (n_k - 8) x_k,
+ * in f64, with the sum of the terms' magnitudes as the error scale.  This is the product this build's decode path
+ * computes when it is given the reference's converted weights. */
+TBO_API void tbo_gemv_q4x(const uint8_t *packed, const uint16_t *scales, const float *x, size_t rows, size_t cols, double *y,
+                          double *bound) {
+    for (size_t r = 0; r < rows; r++) {
+        double sum = 0.0, mag = 0.0;
+        for (size_t g = r * cols / 64; g < (r + 1) * cols / 64; g++) {
+            double d = (double)tbo_f16_value(scales[g]), t = 0.0, a = 0.0;
+            for (size_t k = 0; k < 64; k++) {
+                int nib = (packed[g * 32 + k / 8 * 4 + k % 4] >> (k % 8 / 4 * 4)) & 15;
+                double term = (double)(nib - 8) * (double)x[g * 64 - r * cols + k];
+                t += term;
+                a += fabs(term);
+            }
+            sum += d * t;
+            mag += fabs(d) * a;
+        }
+        y[r] = sum;
+        bound[r] = mag;
+    }
+}
+
 /* ------------------------------------------------------------------------------------------------ */
 /* The benchmark's own weight format: int8 codes, one f16 scale per 32 along K; activation in f16 or  */
 /* f32; f32 accumulation.  Follows the shape of crates/tachyon/tests/common/mod.rs:95-112 (block sums */

@@ -128,6 +128,10 @@ class Context:
         """tb_gemv_q4 (the reference's gemv_q4): Q4 weights x Q8 activations -> f32 y [rows]."""
         check(self.lib.tb_gemv_q4(self.handle, packed.ptr, scales.ptr, q.ptr, pairs.ptr, y.ptr, rows, cols))
 
+    def gemv_q4x(self, packed: DevBuf, scales: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, rows: int, cols: int) -> None:
+        """tb_gemv_q4x: Q4 weights x an f16/f32 activation that is not rounded to Q8 -> f32 y [rows]."""
+        check(self.lib.tb_gemv_q4x(self.handle, packed.ptr, scales.ptr, x.ptr, x_dtype, y.ptr, rows, cols))
+
     def gemv_q8_norm(self, w, s, h, y_res, w1, w2, eps, hscale, h_out, y, rows, cols, geglu=False) -> None:
         p = lambda b: None if b is None else b.ptr
         check(self.lib.tb_gemv_q8_norm(self.handle, w.ptr, s.ptr, h.ptr, p(y_res), p(w1), p(w2), eps, hscale, p(h_out), y.ptr, rows, cols, int(geglu)))

@@ -202,6 +202,16 @@ int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, c
     return launch_gemv_q4(ctx, packed, scales, q, pairs, y, rows, cols);
 }
 
+int tb_gemv_q4x(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const void* x, int x_dtype, float* y, uint32_t rows, uint32_t cols) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (!dtype_ok(x_dtype)) return fail(OUT_OF_RANGE, "tb_gemv_q4x: unknown dtype");
+    GemvParams p;
+    p.w = reinterpret_cast<const int8_t*>(packed), p.s = reinterpret_cast<const __half*>(scales), p.rows = rows, p.cols = cols, p.wbits = 4;
+    p.xmode = x_dtype == TB_F16 ? X_F16 : X_F32, p.x = x;
+    p.epi = EPI_F32, p.y = y;
+    return launch_gemv(ctx, p);
+}
+
 int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, const float* h, const float* y_res, const float* w1, const float* w2, float eps,
                     float hscale, float* h_out, float* y, uint32_t rows, uint32_t cols, int geglu) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");

@@ -30,24 +30,25 @@ constexpr int SMEM_LIMIT = 230000;
 // Rows a warp takes per stage: two when a row is one segment wide.
 constexpr int rows_per_warp(int wpr) { return wpr == 1 ? 2 : 1; }
 constexpr int stage_rows(int wpr) { return CONSUMERS / wpr * rows_per_warp(wpr); }
-constexpr int stage_w(int wpr) { return stage_rows(wpr) * wpr * SEG; }
-constexpr int stage_s(int wpr) { return stage_w(wpr) / 16; }
+// wb: bits per weight, 8 (one f16 scale per 32) or 4 (the reference's Q4: two weights per byte, one scale per 64).
+constexpr int stage_w(int wpr, int wb = 8) { return stage_rows(wpr) * wpr * SEG * wb / 8; }
+constexpr int stage_s(int wpr, int wb = 8) { return stage_w(wpr, wb) / 16; }
 constexpr int plane_bytes(int wpr) { return wpr * 64 * (96 + 4); }
 constexpr int tail_bytes() { return 16 * 8 + 2 * CONSUMERS * 4 + 2 * 2 * CONSUMERS * 4 + 4 * CONSUMERS * 4 + 64; }
-constexpr int stages(int wpr) {
-    const int n = (SMEM_LIMIT - plane_bytes(wpr) - tail_bytes()) / (stage_w(wpr) + stage_s(wpr));
+constexpr int stages(int wpr, int wb = 8) {
+    const int n = (SMEM_LIMIT - plane_bytes(wpr) - tail_bytes()) / (stage_w(wpr, wb) + stage_s(wpr, wb));
     return n > 8 ? 8 : n;
 }
-constexpr int smem_bytes(int wpr) { return stages(wpr) * (stage_w(wpr) + stage_s(wpr)) + plane_bytes(wpr) + tail_bytes(); }
+constexpr int smem_bytes(int wpr, int wb = 8) { return stages(wpr, wb) * (stage_w(wpr, wb) + stage_s(wpr, wb)) + plane_bytes(wpr) + tail_bytes(); }
 
 // Shared-memory carve-up, in this order: weight stages, scale stages, planes (hi, mid, lo words, multipliers),
 // barriers, reduction slots.
-template <int WPR>
+template <int WPR, int WB = 8>
 struct Layout {
-    static constexpr int NST = stages(WPR);
+    static constexpr int NST = stages(WPR, WB);
     static constexpr int W = 0;
-    static constexpr int S = W + NST * stage_w(WPR);
-    static constexpr int HI = S + NST * stage_s(WPR);
+    static constexpr int S = W + NST * stage_w(WPR, WB);
+    static constexpr int HI = S + NST * stage_s(WPR, WB);
     static constexpr int MID = HI + WPR * 64 * 32;
     static constexpr int LO = MID + WPR * 64 * 32;
     static constexpr int MUL = LO + WPR * 64 * 32;
@@ -61,9 +62,9 @@ struct Layout {
 
 // Four consecutive activations -> one word of each plane.  The eight lanes that share a group of 32 agree on its
 // exponent with three exchanges.
-template <int WPR>
+template <int WPR, int WB>
 __device__ __forceinline__ void store_planes(uint8_t* raw, int idx, float v0, float v1, float v2, float v3) {
-    using L = Layout<WPR>;
+    using L = Layout<WPR, WB>;
     float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -79,23 +80,23 @@ __device__ __forceinline__ void store_planes(uint8_t* raw, int idx, float v0, fl
 
 // The block-wide prologue: the 512 consumer threads turn the input vector into planes in shared memory, four
 // consecutive values per thread and pass (coalesced), cols / 2048 passes.
-template <int WPR, int XMODE>
+template <int WPR, int XMODE, int WB>
 __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, int t, const float4& nw1, const float4& nw2) {
-    using L = Layout<WPR>;
+    using L = Layout<WPR, WB>;
     if constexpr (XMODE == X_F16) {
 #pragma unroll
         for (int j = 0; j < WPR; j++) {
             const int idx = j * CTHREADS + t;
             const uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(p.x) + (size_t)idx * 4));
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-            store_planes<WPR>(raw, idx, a.x, a.y, b.x, b.y);
+            store_planes<WPR, WB>(raw, idx, a.x, a.y, b.x, b.y);
         }
     } else if constexpr (XMODE == X_F32) {
         float4 f[WPR];
 #pragma unroll
         for (int j = 0; j < WPR; j++) f[j] = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)(j * CTHREADS + t) * 4);
 #pragma unroll
-        for (int j = 0; j < WPR; j++) store_planes<WPR>(raw, j * CTHREADS + t, f[j].x, f[j].y, f[j].z, f[j].w);
+        for (int j = 0; j < WPR; j++) store_planes<WPR, WB>(raw, j * CTHREADS + t, f[j].x, f[j].y, f[j].z, f[j].w);
     } else if constexpr (XMODE == X_ATTN) {
         // The vector is attention's output, still split over the blocks that computed it: merge the splits' (maximum,
         // sum, unnormalised output) here, four dimensions per thread, with running-maximum rescaling
@@ -144,7 +145,7 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
             }
         }
         const float inv = 1.0f / Lsum;
-        store_planes<WPR>(raw, t, o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        store_planes<WPR, WB>(raw, t, o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     } else {
         // Residual step and RMS-norm over the whole vector (cols == 2048, four values per thread).  One pass of sums, as
         // the reference does (ptx/mod.rs:24-30): sum y^2, sum h^2, sum h*a, sum a^2 with a = y*w1; mean(h'^2) follows.
@@ -180,15 +181,15 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         const float rh = p.w2 != nullptr ? rsqrtf(fmaxf(sq, 0.0f) / n + p.eps) : 1.0f;
         const float v0 = fmaf(a.x, ry, h.x) * hs, v1 = fmaf(a.y, ry, h.y) * hs, v2 = fmaf(a.z, ry, h.z) * hs, v3 = fmaf(a.w, ry, h.w) * hs;
         if (blockIdx.x == 0 && p.h_out != nullptr) *reinterpret_cast<float4*>(p.h_out + at) = make_float4(v0, v1, v2, v3);
-        store_planes<WPR>(raw, t, v0 * rh * w2.x, v1 * rh * w2.y, v2 * rh * w2.z, v3 * rh * w2.w);
+        store_planes<WPR, WB>(raw, t, v0 * rh * w2.x, v1 * rh * w2.y, v2 * rh * w2.z, v3 * rh * w2.w);
     }
 }
 
 // Planes of block `b` from shared memory; `first` picks which 16-byte half lands in words 0..3 (it matches the
 // order the lane loads the weights in, and spreads both loads over all banks).
-template <int WPR>
+template <int WPR, int WB>
 __device__ __forceinline__ void fetch_planes(const uint8_t* raw, int b, int first, Planes& pl) {
-    using L = Layout<WPR>;
+    using L = Layout<WPR, WB>;
     const uint4* hi = reinterpret_cast<const uint4*>(raw + L::HI) + b * 2;
     const uint4* mid = reinterpret_cast<const uint4*>(raw + L::MID) + b * 2;
     const uint4* lo = reinterpret_cast<const uint4*>(raw + L::LO) + b * 2;
@@ -199,14 +200,15 @@ __device__ __forceinline__ void fetch_planes(const uint8_t* raw, int b, int firs
     pl.mul = reinterpret_cast<const float*>(raw + L::MUL)[b];
 }
 
-template <int WPR, int XMODE, int EPI>
+template <int WPR, int XMODE, int EPI, int WB = 8>
 __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p, uint32_t* status) {
     extern __shared__ __align__(128) uint8_t raw[];
-    using L = Layout<WPR>;
+    using L = Layout<WPR, WB>;
     constexpr int NST = L::NST;
     constexpr int RPW = rows_per_warp(WPR);
     constexpr int ROWS = stage_rows(WPR);
-    constexpr int SW = stage_w(WPR), SS = stage_s(WPR);
+    constexpr int SW = stage_w(WPR, WB), SS = stage_s(WPR, WB);
+    constexpr int GROUP = WB == 8 ? 32 : 64;  // weights per scale
     constexpr int UNIT = (EPI == EPI_GEGLU) ? 2 : 1;  // rows that stay in one block
     static_assert(EPI != EPI_GEGLU || RPW == 2, "a gate/up pair is the two rows of one warp");
     const uint32_t K = p.cols;
@@ -235,10 +237,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
                     break;
                 }
                 const uint32_t row = r0 + i * ROWS, here = min((uint32_t)ROWS, r1 - row);
-                const uint32_t bw = here * K, bs = here * (K / 16);
+                const uint32_t bw = here * (K * WB / 8), bs = here * (K / GROUP * 2);
                 mbar_expect_tx(&full[s], bw + bs);
-                bulk_load(raw + L::W + s * SW, p.w + (size_t)row * K, bw, &full[s]);
-                bulk_load(raw + L::S + s * SS, p.s + (size_t)row * (K / 32), bs, &full[s]);
+                bulk_load(raw + L::W + s * SW, p.w + (size_t)row * (K * WB / 8), bw, &full[s]);
+                bulk_load(raw + L::S + s * SS, p.s + (size_t)row * (K / GROUP), bs, &full[s]);
             }
             pdl_launch_dependents();
             // Ask the L2 for what the next kernel's block with this index will stream first.
@@ -260,14 +262,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
     if (stamp) stamp[0] = global_ns();
     pdl_wait();
     if (stamp) stamp[1] = global_ns();
-    build_planes<WPR, XMODE>(p, raw, threadIdx.x, nw1, nw2);
+    build_planes<WPR, XMODE, WB>(p, raw, threadIdx.x, nw1, nw2);
     named_bar_sync(1, CTHREADS);
     if (stamp) stamp[2] = global_ns();
     const int seg = warp % WPR, grp = warp / WPR;  // the warp's column segment, and its row group within a stage
-    const int first = (lane >> 2) & 1;             // which 16-byte half of its blocks the lane loads first (bank spread)
+    // Which 16-byte half of its blocks the lane loads first (bank spread); four-bit weights are read in their order.
+    const int first = WB == 8 ? (lane >> 2) & 1 : 0;
     Planes pl[2];
-    fetch_planes<WPR>(raw, seg * 64 + lane, first, pl[0]);
-    fetch_planes<WPR>(raw, seg * 64 + lane + 32, first, pl[1]);
+    fetch_planes<WPR, WB>(raw, seg * 64 + lane, first, pl[0]);
+    fetch_planes<WPR, WB>(raw, seg * 64 + lane + 32, first, pl[1]);
+    float sx[2] = {0.0f, 0.0f};  // four-bit weights are n - 8: the blocks' activation sums, taken eight times off
+    if constexpr (WB == 4) sx[0] = plane_sum(pl[0]), sx[1] = plane_sum(pl[1]);
 
     float bestv = -INFINITY;
     uint32_t besti = 0xffffffffu;
@@ -283,7 +288,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
 #pragma unroll
         for (int j = 0; j < RPW; j++) {
             v[j] = 0.0f;
-            if (ok && row + j < r1) {
+            if constexpr (WB == 4) {
+                if (ok && row + j < r1) {
+                    // The lane's two blocks of 32 columns are 16 bytes each: 32 lane and 1024 + 32 lane of the segment.
+                    const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * (K / 2) + seg * (SEG / 2);
+                    const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 64) + seg * 32;
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(wr + lane * 16), w1 = *reinterpret_cast<const uint4*>(wr + 512 + lane * 16);
+                    const float s0 = __half2float(sr[lane >> 1]) * pl[0].mul, s1 = __half2float(sr[16 + (lane >> 1)]) * pl[1].mul;
+                    v[j] = fmaf(block_dot_q4(w1, pl[1], sx[1]), s1, block_dot_q4(w0, pl[0], sx[0]) * s0);
+                }
+            } else if (ok && row + j < r1) {
                 const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * K + seg * SEG;
                 const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 32) + seg * 64;
                 const uint4 a0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + first) * 16);
@@ -391,12 +405,12 @@ __global__ void __launch_bounds__(256) gemv_q8_generic(const GemvParams p) {
     }
 }
 
-template <int WPR, int XMODE, int EPI>
+template <int WPR, int XMODE, int EPI, int WB = 8>
 int launch_staged(tb_context* ctx, const GemvParams& p) {
-    auto kernel = gemv_q8_kernel<WPR, XMODE, EPI>;
+    auto kernel = gemv_q8_kernel<WPR, XMODE, EPI, WB>;
     static bool configured[16] = {};  // per device ordinal
     if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(WPR)));
+        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(WPR, WB)));
         configured[ctx->gpu & 15] = true;
     }
     constexpr uint32_t ROWS = stage_rows(WPR);
@@ -407,8 +421,22 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     const uint32_t most = (p.rows + LEAST - 1) / LEAST;
     if (grid > most) grid = most > 0 ? most : 1;
     (void)ROWS;
-    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR), true, p, ctx->status));
+    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR, WB), true, p, ctx->status));
     return OK;
+}
+
+// Four-bit weights: the combinations a decode step and the plain product use.
+template <int WPR>
+int dispatch_staged_q4(tb_context* ctx, const GemvParams& p) {
+    if constexpr (WPR == 1) {
+        if (p.xmode == X_NORM && p.epi == EPI_F32) return launch_staged<1, X_NORM, EPI_F32, 4>(ctx, p);
+        if (p.xmode == X_NORM && p.epi == EPI_GEGLU) return launch_staged<1, X_NORM, EPI_GEGLU, 4>(ctx, p);
+        if (p.xmode == X_NORM && p.epi == EPI_ARGMAX) return launch_staged<1, X_NORM, EPI_ARGMAX, 4>(ctx, p);
+        if (p.xmode == X_ATTN && p.epi == EPI_F32) return launch_staged<1, X_ATTN, EPI_F32, 4>(ctx, p);
+    }
+    if (p.xmode == X_F32 && p.epi == EPI_F32) return launch_staged<WPR, X_F32, EPI_F32, 4>(ctx, p);
+    if (p.xmode == X_F16 && p.epi == EPI_F32) return launch_staged<WPR, X_F16, EPI_F32, 4>(ctx, p);
+    return fail(UNSUPPORTED, "gemv: no code path for this prologue and epilogue with four-bit weights");
 }
 
 template <int WPR>
@@ -453,6 +481,16 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if (p.epi == EPI_GEGLU && p.rows % 2 != 0) return fail(OUT_OF_RANGE, "gemv: GeGLU needs an even number of rows");
     if (p.epi == EPI_ARGMAX && (p.best == nullptr || p.count == nullptr || p.state == nullptr)) return fail(OUT_OF_RANGE, "gemv: argmax needs best, count and state");
     if (p.epi != EPI_ARGMAX && p.y == nullptr) return fail(OUT_OF_RANGE, "gemv: null output");
+    if (p.wbits != 8 && p.wbits != 4) return fail(OUT_OF_RANGE, "gemv: weights are 8 or 4 bits");
+    if (p.wbits == 4) {
+        switch (p.cols) {
+            case 2048: return dispatch_staged_q4<1>(ctx, p);
+            case 4096: return dispatch_staged_q4<2>(ctx, p);
+            case 8192: return dispatch_staged_q4<4>(ctx, p);
+            case 16384: return dispatch_staged_q4<8>(ctx, p);
+            default: return fail(UNSUPPORTED, "gemv: four-bit weights need 2048, 4096, 8192 or 16384 columns");
+        }
+    }
     switch (p.cols) {
         case 2048: return dispatch_staged<1>(ctx, p);
         case 4096: return dispatch_staged<2>(ctx, p);

@@ -84,6 +84,7 @@ struct GemvParams {
     uint32_t* token_out = nullptr;
     uint32_t* trace = nullptr;    // optional: trace[position & trace_mask] = token
     uint32_t trace_mask = 0;
+    uint32_t wbits = 8;           // 8: int8 codes, an f16 scale per 32; 4: the reference's Q4, two per byte, a scale per 64
     Prefetch pf;                  // optional hint for the L2
     // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for
     // the previous kernel, after the prologue and at the end.

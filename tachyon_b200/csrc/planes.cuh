@@ -32,6 +32,30 @@ __device__ __forceinline__ float block_dot(const uint4& a, const uint4& b, const
     return fmaf(static_cast<float>(h), 65536.0f, static_cast<float>(m * 256 + l));
 }
 
+// The same for 32 four-bit weights n - 8 (crates/tachyon/src/quant.rs:60-66: word j holds columns 8j..8j+3 in its low
+// nibbles and 8j+4..8j+7 in its high ones): sum n X - 8 sum X, with `sx` the block's sum of X.
+__device__ __forceinline__ float block_dot_q4(const uint4& w, const Planes& p, float sx) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    int h = 0;
+    uint32_t m = 0, l = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t lo = ww[j] & 0x0F0F0F0Fu, hi = (ww[j] >> 4) & 0x0F0F0F0Fu;
+        h = dp4a_su(p.hi[2 * j], lo, h), m = dp4a_uu(p.mid[2 * j], lo, m), l = dp4a_uu(p.lo[2 * j], lo, l);
+        h = dp4a_su(p.hi[2 * j + 1], hi, h), m = dp4a_uu(p.mid[2 * j + 1], hi, m), l = dp4a_uu(p.lo[2 * j + 1], hi, l);
+    }
+    return fmaf(-8.0f, sx, fmaf(static_cast<float>(h), 65536.0f, static_cast<float>(m * 256u + l)));
+}
+
+// Sum of a block's 32 fixed-point activations, as a float.
+__device__ __forceinline__ float plane_sum(const Planes& p) {
+    int h = 0;
+    uint32_t m = 0, l = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) h = dp4a_ss(p.hi[k], 0x01010101, h), m = dp4a_uu(p.mid[k], 0x01010101u, m), l = dp4a_uu(p.lo[k], 0x01010101u, l);
+    return fmaf(static_cast<float>(h), 65536.0f, static_cast<float>(m * 256u + l));
+}
+
 // Used by the generic kernel: planes of 32 values held by one thread.
 __device__ __forceinline__ void make_planes(const float (&v)[32], Planes& p) {
     float amax = 0.0f;

@@ -38,6 +38,22 @@ def test_binding_covers_the_header(lib_path):
     assert sorted(_lib.SIGNATURES) == declared()
 
 
+def test_binding_passes_as_many_arguments_as_the_header_takes():
+    """A missing entry in a ctypes signature shifts every later argument: a pointer then travels as 32 bits."""
+    from tachyon_b200 import _lib
+
+    text = open(os.path.join(ROOT, "include", "tachyon_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    for name, args in re.findall(r"^TB_API [^;(]*?\b(tb_\w+)\(([^;]*?)\);", text, flags=re.M | re.S):
+        args = args.strip()
+        count = 0 if args in ("", "void") else args.count(",") + 1
+        assert len(_lib.SIGNATURES[name][1]) == count, f"{name}: the header takes {count} arguments"
+        # pointers must be declared as pointers
+        for i, a in enumerate(args.split(",") if count else []):
+            if "*" in a:
+                assert _lib.SIGNATURES[name][1][i] in (ctypes.c_void_p, ctypes.c_char_p) or hasattr(_lib.SIGNATURES[name][1][i], "contents"), f"{name}: argument {i} is a pointer"
+
+
 def test_library_needs_no_cuda_runtime_library(lib_path):
     import subprocess
 

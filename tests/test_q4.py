@@ -84,3 +84,18 @@ def test_gemv_q4_rejects_what_it_cannot_run(ctx):
         ctx.gemv_q4(d, d, d, d, d, 4, 96)  # not whole groups of 64
     with pytest.raises(tb.Error):
         ctx.quant_q8(d, 48, d, d)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(3072, 2048), (37, 2048), (1, 2048), (300, 4096), (64, 8192), (2048, 16384), (37, 16384)])
+def test_gemv_q4x_reads_q4_weights_with_an_unrounded_activation(ctx, rows, cols):
+    """The decode product on the reference's converted weights: f32 accuracy against the f64 product."""
+    wf, x = values_fast(rows * cols, 21 + rows), np.random.default_rng(cols + rows).standard_normal(cols).astype(np.float32)
+    x[64:96] = 0.0
+    x[100] = 1e-30
+    packed, scales = oracle.q4(wf.reshape(rows, cols))
+    want, bound = oracle.gemv_q4x(packed, scales, x, rows)
+    wd, sd, xd, yd = ctx.upload(packed), ctx.upload(scales), ctx.upload(x), ctx.zeros(rows * 4)
+    ctx.gemv_q4x(wd, sd, xd, tb.F32, yd, rows, cols)
+    got = yd.download(np.float32, rows)
+    assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-5 * bound + 1e-6), np.abs(got - want).max()
