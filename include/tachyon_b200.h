@@ -217,14 +217,17 @@ typedef struct tb_settings {
     uint32_t chunk;        /* extra ring slots of sliding layers (the reference's prefill chunk) */
     uint32_t keep_logits;  /* != 0: every step also stores the f32 logits for tb_decoder_logits */
     uint32_t fused;        /* != 0: the whole step as one persistent kernel with grid barriers instead of 2 + 5*layers launches */
+    uint32_t weight_bits;  /* 0 or 8: int8 codes with an f16 scale per 32 (TB_WEIGHTS_Q8); 4: the reference's converted Q4
+                              matrices as they are in weights.wpk, u8 [rows, cols/2] and f16 [rows, cols/64] (TB_WEIGHTS_Q4) */
 } tb_settings;
+enum { TB_WEIGHTS_Q8 = 8, TB_WEIGHTS_Q4 = 4 };
 
 /* Decoder::open without the file loader: allocates weights, caches and step buffers for `cfg`. */
 TB_API int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, tb_decoder** out);
 TB_API void tb_decoder_close(tb_decoder* dec);
 /*
- * Uploads one tensor by its converted-model name (model/mod.rs:178-286): matrices as `<name>.w` (int8 codes) and
- * `<name>.s` (f16 scales, one per 32 along a row) for embed, {i}.qkv, {i}.o, {i}.gate_up (gate rows, then up rows),
+ * Uploads one tensor by its converted-model name (model/mod.rs:178-286): matrices as `<name>.w` (int8 codes; with
+ * TB_WEIGHTS_Q4 the reference's packed nibbles) and `<name>.s` (f16 scales, one per 32 along a row; per 64 with Q4) for embed, {i}.qkv, {i}.o, {i}.gate_up (gate rows, then up rows),
  * {i}.down; f32 vectors {i}.q_norm, {i}.k_norm, {i}.input_layernorm, {i}.post_attention_layernorm,
  * {i}.pre_feedforward_layernorm, {i}.post_feedforward_layernorm, {i}.layer_scalar, norm.
  */

@@ -16,17 +16,19 @@ def bf16_round(v: float) -> float:
 class OracleModel:
     """Weights (numpy, kept alive here), caches and the ctypes structs of oracle.tbo_decoder_step."""
 
-    def __init__(self, cfg, seed: int, context: int, chunk: int = 0, layers: int | None = None):
+    def __init__(self, cfg, seed: int, context: int, chunk: int = 0, layers: int | None = None, weight_bits: int = 8):
         self.cfg, self.keep = cfg, []
         H, F, D = cfg.hidden, cfg.ffn, cfg.head_dim
         nq, nkv = cfg.heads * D, cfg.kv_heads * D
         L = cfg.layers if layers is None else layers
-        smul = 0.02 / 127
+        smul = 0.02 / 8 if weight_bits == 4 else 0.02 / 127
+        group = 64 if weight_bits == 4 else 32
         self.tensors = {}
 
         def mat(name, stream, rows, cols):
-            w = oracle.fill_codes(seed, stream, rows * cols).reshape(rows, cols)
-            s = oracle.fill_scales(seed, stream + 1, rows * cols // 32, smul).reshape(rows, cols // 32)
+            # Four-bit matrices: the same seeded bytes, each holding two weights (tb_decoder_fill_random does the same).
+            w = oracle.fill_codes(seed, stream, rows * cols * weight_bits // 8).reshape(rows, cols * weight_bits // 8)
+            s = oracle.fill_scales(seed, stream + 1, rows * cols // group, smul).reshape(rows, cols // group)
             self.tensors[name + ".w"], self.tensors[name + ".s"] = w, s
             return w, s
 
@@ -61,7 +63,8 @@ class OracleModel:
             ly.layer_scalar, ly.global_, ly.kc, ly.vc, ly.cap = float(scalar[0]), int(is_global), kc.ctypes.data, vc.ctypes.data, cap
         oc = oracle.Config(hidden=H, ffn=F, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=D, vocab=cfg.vocab, layers=L, window=cfg.window,
                            context=context, theta_sliding=cfg.theta_sliding, theta_global=cfg.theta_global, fraction_global=cfg.fraction_global,
-                           eps=cfg.eps, softcap=cfg.softcap, attn_scale=cfg.attn_scale, embed_scale=bf16_round(float(np.sqrt(np.float32(H)))))
+                           eps=cfg.eps, softcap=cfg.softcap, attn_scale=cfg.attn_scale, embed_scale=bf16_round(float(np.sqrt(np.float32(H)))),
+                           weight_bits=weight_bits)
         self.model = oracle.Model(cfg=oc, embed=self.embed.ctypes.data, embed_s=self.embed_s.ctypes.data, norm=self.norm.ctypes.data,
                                   layers=C.cast(self.layers, C.POINTER(oracle.Layer)))
 

@@ -513,6 +513,7 @@ TBO_API void tbo_fill_gauss_f32(uint64_t seed, uint64_t stream, float *x, size_t
 typedef struct {
     int32_t hidden, ffn, heads, kv_heads, head_dim, vocab, layers, window, context;
     float theta_sliding, theta_global, fraction_global, eps, softcap, attn_scale, embed_scale;
+    int32_t weight_bits; /* 0 or 8: int8 codes, a scale per 32; 4: the reference's Q4 (quant.rs:47-82), a scale per 64 */
 } tbo_config;
 
 typedef struct {
@@ -533,8 +534,27 @@ typedef struct {
     tbo_layer *layers;
 } tbo_model;
 
-static void matvec_q8(const int8_t *w, const uint16_t *s, const float *x, size_t rows, size_t cols, float *y) {
-    tbo_gemv_q8(w, s, x, rows, cols, y, NULL, NULL);
+static int nibble(const uint8_t *packed, size_t at) { /* weight `at` of a row-major Q4 matrix, 0..15 (quant.rs:60-66) */
+    size_t g = at / 64, k = at % 64;
+    return (packed[g * 32 + k / 8 * 4 + k % 4] >> (k % 8 / 4 * 4)) & 15;
+}
+
+/* y = W x for the model's weight format, accumulated in f32 group by group. */
+static void matvec(const tbo_config *c, const int8_t *w, const uint16_t *s, const float *x, size_t rows, size_t cols, float *y) {
+    if (c->weight_bits != 4) {
+        tbo_gemv_q8(w, s, x, rows, cols, y, NULL, NULL);
+        return;
+    }
+    const uint8_t *packed = (const uint8_t *)w;
+    for (size_t r = 0; r < rows; r++) {
+        float sum = 0.0f;
+        for (size_t g = 0; g < cols / 64; g++) {
+            float t = 0.0f;
+            for (size_t k = 0; k < 64; k++) t += (float)(nibble(packed, r * cols + g * 64 + k) - 8) * x[g * 64 + k];
+            sum += tbo_f16_value(s[r * cols / 64 + g]) * t;
+        }
+        y[r] = sum;
+    }
 }
 
 /* tiny.rs:364-367: x / sqrt(mean(x^2) + eps), times w when given, in f32. */
@@ -570,14 +590,17 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
     float *freq = (float *)malloc(D / 2 * 4), *tmp = (float *)malloc(D * 4);
     /* tiny.rs:233: the embedding row times sqrt(hidden) (model/decode.rs:571 rounds that factor to bfloat16; the caller
      * passes the factor it wants in embed_scale). */
-    for (size_t i = 0; i < H; i++)
-        x[i] = (float)m->embed[(size_t)token * H + i] * tbo_f16_value(m->embed_s[((size_t)token * H + i) / 32]) * c->embed_scale;
+    for (size_t i = 0; i < H; i++) {
+        size_t at = (size_t)token * H + i;
+        if (c->weight_bits == 4) x[i] = (float)(nibble((const uint8_t *)m->embed, at) - 8) * tbo_f16_value(m->embed_s[at / 64]) * c->embed_scale;
+        else x[i] = (float)m->embed[at] * tbo_f16_value(m->embed_s[at / 32]) * c->embed_scale;
+    }
     int nl = stop_layer > 0 ? stop_layer : c->layers;
     for (int li = 0; li < nl; li++) {
         tbo_layer *L = &m->layers[li];
         tbo_rope_freq(L->global ? c->theta_global : c->theta_sliding, (int)D, L->global ? c->fraction_global : 1.0f, freq);
         rms_f32(x, L->input_ln, H, c->eps, h);                                  /* tiny.rs:278 */
-        matvec_q8(L->qkv, L->qkv_s, h, nq + 2 * nkv, H, qkv);                    /* :279, 286-287 (fused q, k, v) */
+        matvec(c, L->qkv, L->qkv_s, h, nq + 2 * nkv, H, qkv);                    /* :279, 286-287 (fused q, k, v) */
         for (int hd = 0; hd < c->heads; hd++) {                                 /* :280-283 */
             rms_f32(qkv + (size_t)hd * D, L->q_norm, D, c->eps, tmp);
             rotate_f32(tmp, D, freq, pos);
@@ -619,13 +642,13 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
             }
             free(sc);
         }
-        matvec_q8(L->o, L->o_s, att, H, nq, y);                                  /* :294 */
+        matvec(c, L->o, L->o_s, att, H, nq, y);                                  /* :294 */
         rms_f32(y, L->post_attn_ln, H, c->eps, h);
         for (size_t i = 0; i < H; i++) x[i] += h[i];
         rms_f32(x, L->pre_ffn_ln, H, c->eps, h);                                 /* :312 */
-        matvec_q8(L->gate_up, L->gate_up_s, h, 2 * F, H, gu);
+        matvec(c, L->gate_up, L->gate_up_s, h, 2 * F, H, gu);
         for (size_t i = 0; i < F; i++) a[i] = gelu_f32(gu[i]) * gu[F + i];       /* :309 */
-        matvec_q8(L->down, L->down_s, a, H, F, y);
+        matvec(c, L->down, L->down_s, a, H, F, y);
         rms_f32(y, L->post_ffn_ln, H, c->eps, h);                                /* :314 */
         for (size_t i = 0; i < H; i++) x[i] = (x[i] + h[i]) * L->layer_scalar;   /* :296-297 */
     }
@@ -634,7 +657,7 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
     if (stop_layer <= 0) {
         float *lg = logits ? logits : (float *)malloc((size_t)c->vocab * 4);
         rms_f32(x, m->norm, H, c->eps, h);                                       /* :238 */
-        matvec_q8(m->embed, m->embed_s, h, (size_t)c->vocab, H, lg);
+        matvec(c, m->embed, m->embed_s, h, (size_t)c->vocab, H, lg);
         pick = (int32_t)tbo_sample_greedy(lg, (size_t)c->vocab, c->softcap, 1.0f, NULL, NULL, NULL);
         if (!logits) free(lg);
     }

@@ -206,9 +206,10 @@ def gemma4_e4b_shape(layers: int = 35, ffn: int = 16384, vocab: int = 262144) ->
 class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
-    def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False, fused: bool = False):
+    def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False, fused: bool = False,
+                 weight_bits: int = 8):
         self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
-        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused))
+        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused), weight_bits=weight_bits)
         h = C.c_void_p()
         check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
         self.handle = h.value

@@ -36,7 +36,7 @@ class EncoderConfig(C.Structure):
 
 
 class Settings(C.Structure):
-    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32)]
+    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares.

@@ -35,8 +35,9 @@ struct Mat {
     int8_t* w = nullptr;
     __half* s = nullptr;
     uint32_t rows = 0, cols = 0;
-    size_t code_bytes() const { return (size_t)rows * cols; }
-    size_t scale_bytes() const { return (size_t)rows * (cols / 32) * 2; }
+    uint32_t bits = 8;  // 8: int8 codes, an f16 scale per 32; 4: the reference's Q4 (quant.rs:47-82), a scale per 64
+    size_t code_bytes() const { return (size_t)rows * cols * bits / 8; }
+    size_t scale_bytes() const { return (size_t)rows * (cols / (bits == 4 ? 64 : 32)) * 2; }
 };
 
 struct Layer {
@@ -121,6 +122,13 @@ int validate(const tb_config& c, const tb_settings& s) {
     if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
     if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
     if (s.context == 0 || s.context > TRACE) return fail(OUT_OF_RANGE, "decoder: context must be in 1..65536");
+    if (s.weight_bits != 0 && s.weight_bits != 8 && s.weight_bits != 4) return fail(OUT_OF_RANGE, "decoder: weights are 8 or 4 bits");
+    if (s.weight_bits == 4) {
+        const uint32_t qc = c.heads * c.head_dim;
+        if ((qc != 2048 && qc != 4096 && qc != 8192 && qc != 16384) || (c.ffn != 2048 && c.ffn != 4096 && c.ffn != 8192 && c.ffn != 16384))
+            return fail(UNSUPPORTED, "decoder: four-bit weights need heads*head_dim and ffn of 2048, 4096, 8192 or 16384");
+        if (s.fused) return fail(UNSUPPORTED, "decoder: the fused step reads eight-bit weights only");
+    }
     return OK;
 }
 
@@ -138,7 +146,7 @@ void layout(tb_decoder* d, char* base) {
     const tb_config& c = d->cfg;
     Taker t;
     auto mat = [&](Mat& m, uint32_t rows, uint32_t cols) {
-        m.rows = rows, m.cols = cols;
+        m.rows = rows, m.cols = cols, m.bits = d->settings.weight_bits == 4 ? 4 : 8;
         m.w = reinterpret_cast<int8_t*>(base + t.take(m.code_bytes()));
         m.s = reinterpret_cast<__half*>(base + t.take(m.scale_bytes()));
     };
@@ -210,7 +218,7 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
 }
 
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
-    p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols;
+    p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols, p.wbits = m.bits;
     if (d->stamps) p.stamps = d->stamps + 8 * (size_t)d->launches;
     d->launches++;
     if (d->collect) {
@@ -234,7 +242,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         ph.e.w = d->embed.w, ph.e.s = d->embed.s, ph.e.token = d->state + 1, ph.e.cols = c.hidden, ph.e.scale = d->embed_scale, ph.e.out = d->x[0];
         d->collect->push_back(ph);
     } else {
-        TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0]));
+        TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0], d->embed.bits));
     }
     d->launches++;
     for (uint32_t i = 0; i < c.layers; i++) {
@@ -385,7 +393,7 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     d->ctx = ctx, d->cfg = *cfg, d->settings = *settings;
     {
         const char* env = getenv("TACHYON_B200_FUSED");
-        d->fused = settings->fused != 0 || (env != nullptr && env[0] == '1');
+        d->fused = settings->fused != 0 || (env != nullptr && env[0] == '1' && settings->weight_bits != 4);
     }
     d->global.resize(cfg->layers);
     for (uint32_t i = 0; i < cfg->layers; i++)
@@ -467,7 +475,8 @@ int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
     if (!d) return fail(OUT_OF_RANGE, "null decoder");
     const tb_config& c = d->cfg;
     tb_context* ctx = d->ctx;
-    const float smul = 0.02f / 127.0f;
+    const uint32_t bits = d->embed.bits;
+    const float smul = bits == 4 ? 0.02f / 8.0f : 0.02f / 127.0f;  // either way weights of magnitude ~0.02
     auto mat = [&](Mat& m, uint64_t id) -> int {
         TB_TRY(launch_fill_codes(ctx, seed, id, m.w, m.code_bytes()));
         return launch_fill_scales(ctx, seed, id + 1, m.s, m.scale_bytes() / 2, smul);
@@ -485,8 +494,8 @@ int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
         if (st == OK) st = mat(L.o, b + 2);
         if (st == OK) st = launch_fill_codes(ctx, seed, b + 4, static_cast<int8_t*>(tw), L.gate_up.code_bytes());
         if (st == OK) st = launch_fill_scales(ctx, seed, b + 5, static_cast<__half*>(ts), L.gate_up.scale_bytes() / 2, smul);
-        if (st == OK) st = launch_interleave_rows(ctx, tw, L.gate_up.w, c.ffn, c.hidden);
-        if (st == OK) st = launch_interleave_rows(ctx, ts, L.gate_up.s, c.ffn, c.hidden / 32 * 2);
+        if (st == OK) st = launch_interleave_rows(ctx, tw, L.gate_up.w, c.ffn, c.hidden * bits / 8);
+        if (st == OK) st = launch_interleave_rows(ctx, ts, L.gate_up.s, c.ffn, c.hidden / (bits == 4 ? 64 : 32) * 2);
         if (st == OK) st = mat(L.down, b + 6);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 8, L.q_norm, c.head_dim, 0.15f, 0.35f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 9, L.k_norm, c.head_dim, 0.15f, 0.35f);
@@ -665,7 +674,8 @@ int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
     for (uint32_t i = 0; i < n; i++)
         if (tokens[i] >= d->cfg.vocab) return fail(OUT_OF_RANGE, "decoder: token outside the vocabulary");
     const char* env = getenv("TACHYON_B200_PREFILL_BY_STEPS");
-    const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || (env != nullptr && env[0] == '1');
+    // Four-bit weights have no tensor-core product yet: their prompts go through the decode step.
+    const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || d->embed.bits == 4 || (env != nullptr && env[0] == '1');
     if (by_steps) {
         // Without chunk buffers: every prompt token through the decode step; its sample is dropped.
         for (uint32_t i = 0; i < n; i++) {

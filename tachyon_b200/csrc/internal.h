@@ -163,7 +163,7 @@ int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, con
                          uint32_t window, uint32_t heads, uint32_t kv_heads);
 
 // ---- small kernels ---------------------------------------------------------------------------------------------
-int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out);
+int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out, uint32_t wbits = 8);
 int launch_norm(tb_context* ctx, const float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,
                 float* h_out, float* x_out);
 int launch_sample(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, const uint32_t* seen,

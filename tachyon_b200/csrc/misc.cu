@@ -18,6 +18,18 @@ __global__ void __launch_bounds__(256) embed_q8_kernel(const int8_t* w, const __
         out[i] = (float)w[row + i] * __half2float(s[(row + i) / 32]) * scale;
 }
 
+// The reference's embed_q4 itself (ptx/mod.rs:531-598): weight k of a group of 64 is nibble k % 8 / 4 of byte
+// k / 8 * 4 + k % 4 (quant.rs:60-66), minus 8, times the group's scale.
+__global__ void __launch_bounds__(256) embed_q4_kernel(const uint8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out) {
+    pdl_wait();
+    const size_t row = (size_t)ld_cg_u(token) * cols;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < cols; i += gridDim.x * blockDim.x) {
+        const size_t at = row + i, g = at / 64, k = at % 64;
+        const int n = (w[g * 32 + k / 8 * 4 + k % 4] >> (k % 8 / 4 * 4)) & 15;
+        out[i] = (float)(n - 8) * __half2float(s[g]) * scale;
+    }
+}
+
 __device__ __forceinline__ float block_sum(float v, float* sh) {
     v = warp_sum(v);
     __syncthreads();
@@ -194,9 +206,10 @@ uint32_t fill_grid(tb_context* ctx, size_t n) {
 
 }  // namespace
 
-int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out) {
-    if (!w || !s || !token || !out || cols == 0 || cols % 32 != 0) return fail(OUT_OF_RANGE, "embed: bad arguments");
-    TB_CUDA(launch_kernel(ctx, embed_q8_kernel, dim3((cols + 255) / 256), dim3(256), 0, true, w, s, token, cols, scale, out));
+int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out, uint32_t wbits) {
+    if (!w || !s || !token || !out || cols == 0 || cols % 32 != 0 || (wbits == 4 && cols % 64 != 0)) return fail(OUT_OF_RANGE, "embed: bad arguments");
+    if (wbits == 4) TB_CUDA(launch_kernel(ctx, embed_q4_kernel, dim3((cols + 255) / 256), dim3(256), 0, true, reinterpret_cast<const uint8_t*>(w), s, token, cols, scale, out));
+    else TB_CUDA(launch_kernel(ctx, embed_q8_kernel, dim3((cols + 255) / 256), dim3(256), 0, true, w, s, token, cols, scale, out));
     return OK;
 }
 

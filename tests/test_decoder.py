@@ -219,3 +219,46 @@ def test_prefill_at_the_benchmark_width(ctx):
     if top[-1] - top[-2] > 2e-2 * scale:
         assert got_token == want_token
     dec.close()
+
+
+def test_q4_weights_step_matches_the_cpu_forward_and_loads_converted_tensors(ctx):
+    """TB_WEIGHTS_Q4: the reference's converted matrices (u8 [rows, cols/2] nibbles, f16 [rows, cols/64] scales) as
+    they come out of weights.wpk; the same checks as for eight-bit weights, and a prompt through tb_decoder_prefill."""
+    cfg = small_config()
+    dec = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True, weight_bits=4)
+    dec.fill_random(SEED + 4)
+    dec.build()
+    ref = OracleModel(cfg, SEED + 4, context=64, chunk=8, weight_bits=4)
+    token = 17
+    for pos in range(28):
+        want_token, want_logits, want_hidden = ref.step(token, pos)
+        got_token = dec.step(token)
+        capped = cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap)
+        order = np.sort(capped)
+        check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+        assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+        token = (pos * 7919 + 13) % cfg.vocab
+    # the same tensors uploaded by name give the same bits as the device fill
+    other = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True, weight_bits=4)
+    for name, a in ref.tensors.items():
+        other.load(name, a)
+    other.build()
+    dec.reset()
+    for token in [5, 99, 4000, 7]:
+        assert other.step(token) == dec.step(token)
+        assert np.array_equal(other.logits(), dec.logits())
+    with pytest.raises(tb.Error) as e:
+        other.load("0.qkv.w", np.zeros(3072 * 2048, np.int8))  # the eight-bit size
+    assert e.value.status == 5
+    # a prompt (token by token inside the library for this format) equals stepping
+    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(20)]
+    dec.reset()
+    for t in prompt[:-1]:
+        dec.step(t)
+    a, la = dec.step(prompt[-1]), dec.logits()
+    dec.reset()
+    dec.prefill(prompt[:-1])
+    assert dec.step(prompt[-1]) == a and np.array_equal(dec.logits(), la)
+    with pytest.raises(tb.Error):
+        tb.Decoder(ctx, cfg, context=64, fused=True, weight_bits=4)
+    dec.close(), other.close()
