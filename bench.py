@@ -135,14 +135,14 @@ class Clocks:
 # CPU oracle legs
 # ---------------------------------------------------------------------------------------------------------------------
 
-def cpu_decode(cfg, steps_wanted: int, budget_s: float, gpu_tokens=None):
+def cpu_decode(cfg, steps_wanted: int, budget_s: float, gpu_tokens=None, weight_bits: int = 8):
     """The CPU oracle's decode step on the same seeded model and pre-filled cache; returns tokens/s and what ran."""
     import oracle
     from oracle.model import OracleModel
 
     cores = oracle.lib().tbo_threads()
     t0 = time.time()
-    model = OracleModel(cfg, SEED, context=CONTEXT, chunk=0)
+    model = OracleModel(cfg, SEED, context=CONTEXT, chunk=0, weight_bits=weight_bits)
     model.fill_cache(SEED + 1)
     build_s = time.time() - t0
     token, times, tokens, gaps = 1, [], [], []
@@ -177,7 +177,8 @@ def bench_decode(args, ranks: Ranks):
 
     ctx = tb.Context(ranks.local)
     cfg = tb.gemma4_e4b_shape()
-    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=0, keep_logits=False, fused=args.fused)
+    bits = 4 if args.weights == "q4" else 8
+    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=0, keep_logits=False, fused=args.fused, weight_bits=bits)
     dec.fill_random(SEED)
     dec.build()
     K, W = args.steps, args.warmup
@@ -234,12 +235,14 @@ def bench_decode(args, ranks: Ranks):
     peak, how = measured_peak_gbs()
     line = {
         "metric": "decode_tokens_per_second", "value": value, "unit": "tok/s", "n_gpus": n, "steps": K, "warmup": W,
-        "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights x f32 activations, f32 accumulate",
+        "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": ("int4 (the reference's Q4)" if bits == 4 else "int8") + " weights x f32 activations, f32 accumulate",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape Q8, batch 1, context pre-filled to 2048, greedy, CUDA graph",
+        "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape " + ("Q4 (the reference's converted format; not the configuration the metric is quoted on)" if bits == 4 else "Q8")
+                   + ", batch 1, context pre-filled to 2048, greedy, CUDA graph",
                    "step": "one persistent kernel per step" if args.fused else "one launch per phase, programmatic dependent launch",
                    "layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "parallelism": f"{n} independent replicas",
-                   "l2": "inputs exceed L2: 4.70 GB of weights streamed per step"},
+                   "l2": f"inputs exceed L2: {weight_bytes / 1e9:.2f} GB of weights streamed per step"},
         "e2e": {"value": n * K / (e2e_ms_max / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
                 "api": "tb_decoder_step: host token in, graph replay, sampled token read from pinned memory"},
         "gpu_launches": K * launches_per_step,
@@ -565,6 +568,7 @@ def main():
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--weights", default="q8", choices=["q8", "q4"], help="decode workload: the benchmark's Q8 matrices, or the reference's converted Q4 format")
     ap.add_argument("--fused", action="store_true", help="decode with the single persistent step kernel instead of one launch per phase")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -587,7 +591,7 @@ def main():
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu:
-                line["cpu_baseline"], _ = cpu_decode(cfg, 4, 30.0, gpu_tokens)
+                line["cpu_baseline"], _ = cpu_decode(cfg, 4, 30.0, gpu_tokens, 4 if args.weights == "q4" else 8)
             elif ranks.rank == 0:
                 line["cpu_baseline"] = None
         if ranks.rank == 0 and line is not None:

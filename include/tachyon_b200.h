@@ -36,7 +36,8 @@ enum {
     TB_OUT_OF_MEMORY = 7,   /* Error::OutOfMemory */
     TB_NO_MODEL = 8,        /* Error::NoModel: a tensor is missing */
     TB_UNSUPPORTED = 9,     /* Error::Unsupported: a shape this build has no kernel for */
-    TB_DEVICE_WAIT = 10     /* a kernel gave up a bounded wait; see tb_status */
+    TB_DEVICE_WAIT = 10,    /* a kernel gave up a bounded wait; see tb_status */
+    TB_IO = 11              /* Error::Io(errno): a file could not be opened or read; tb_last_error() has the errno text */
 };
 
 typedef struct tb_context tb_context;
@@ -268,6 +269,36 @@ TB_API int tb_decoder_step_launches(tb_decoder* dec, uint32_t* launches);
  * host_out: [2 blocks][phases][4] words; call with host_out NULL to learn `phases`.
  */
 TB_API int tb_decoder_timeline(tb_decoder* dec, uint32_t token, uint64_t* host_out, uint32_t* phases);
+/* ---- weights.wpk: crates/tachyon/src/wpk/mod.rs (Wpk::open, tensors, verify) ---- */
+
+typedef struct tb_wpk tb_wpk;
+/* wpk::Tensor (wpk/mod.rs:74-89).  dtype: 0 F32, 1 F16, 2 BF16, 3 F8E4M3, 4 I8, 5 U8 (wpk/mod.rs:44-62). */
+typedef struct tb_wpk_info {
+    const char* name;      /* owned by the file handle */
+    uint32_t dtype, rank;
+    uint64_t shape[8];
+    uint64_t offset;       /* in the data region, which starts at byte 4096 of the file */
+    uint64_t bytes;
+    uint32_t crc32c;
+} tb_wpk_info;
+/* CRC32C (Castagnoli) of `bytes` bytes continuing from `crc` (wpk/mod.rs:105-123); tb_crc32c(0, "123456789", 9) is 0xE3069283. */
+TB_API uint32_t tb_crc32c(uint32_t crc, const void* data, size_t bytes);
+/* Wpk::open (wpk/mod.rs:190-213): checks the header, the table's checksum and every table entry; TB_FORMAT with the
+ * reference's message when a check fails, TB_IO when the file cannot be read. */
+TB_API int tb_wpk_open(const char* path, tb_wpk** out);
+TB_API void tb_wpk_close(tb_wpk* wpk);
+TB_API uint32_t tb_wpk_count(const tb_wpk* wpk);
+TB_API int tb_wpk_tensor(const tb_wpk* wpk, uint32_t index, tb_wpk_info* out);
+/* Reads tensor `index` into `host` (`bytes` must be its size); verify != 0 also checks its CRC32C (Wpk::verify). */
+TB_API int tb_wpk_read(const tb_wpk* wpk, uint32_t index, void* host, size_t bytes, int verify);
+/*
+ * Decoder::open's loading step (decode.rs:225-247) for a converted model's weights.wpk: every tensor of the file goes
+ * to tb_decoder_load under its own name.  The decoder must have been opened with the file's format (TB_WEIGHTS_Q4 for
+ * a model converted by the reference).  A tensor the decoder has no place for (per-layer inputs, experts) ends the
+ * load with TB_NO_MODEL; a size that does not fit with TB_FORMAT.
+ */
+TB_API int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify);
+
 /* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */
 TB_API int tb_decoder_hidden(tb_decoder* dec, float* host_out);
 

@@ -8,6 +8,7 @@ nothing falls back when the library or a GPU is missing.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -203,6 +204,42 @@ def gemma4_e4b_shape(layers: int = 35, ffn: int = 16384, vocab: int = 262144) ->
                   theta_sliding=1e4, theta_global=1e6, fraction_global=0.25, eps=1e-6, softcap=30.0, attn_scale=1.0)
 
 
+class Wpk:
+    """wpk::Wpk (crates/tachyon/src/wpk/mod.rs): an open weights.wpk, its table checked; no GPU involved."""
+
+    DTYPES = {0: np.float32, 1: np.float16, 2: np.uint16, 3: np.uint8, 4: np.int8, 5: np.uint8}  # bf16 and f8 as raw bits
+
+    def __init__(self, path: str):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        check(self.lib.tb_wpk_open(os.fsencode(path), C.byref(h)))
+        self.handle = h.value
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_wpk_close(self.handle)
+            self.handle = None
+
+    def tensors(self):
+        out = []
+        for i in range(self.lib.tb_wpk_count(self.handle)):
+            info = _lib.WpkInfo()
+            check(self.lib.tb_wpk_tensor(self.handle, i, C.byref(info)))
+            out.append((info.name.decode(), info.dtype, tuple(info.shape[: info.rank]), info.offset, info.bytes, info.crc32c))
+        return out
+
+    def read(self, index: int, verify: bool = True) -> np.ndarray:
+        name, dtype, shape, _, nbytes, _ = self.tensors()[index]
+        raw = np.zeros(nbytes, np.uint8)
+        check(self.lib.tb_wpk_read(self.handle, index, raw.ctypes.data, nbytes, int(verify)))
+        return raw.view(self.DTYPES[dtype]).reshape(shape)
+
+
+def crc32c(data: bytes, crc: int = 0) -> int:
+    buf = np.frombuffer(data, np.uint8)
+    return int(_lib.load().tb_crc32c(crc, buf.ctypes.data if buf.size else None, buf.size))
+
+
 class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
@@ -222,6 +259,10 @@ class Decoder:
     def load(self, name: str, a: np.ndarray) -> None:
         a = np.ascontiguousarray(a)
         check(self.lib.tb_decoder_load(self.handle, name.encode(), a.ctypes.data, a.nbytes))
+
+    def load_wpk(self, path: str, verify: bool = True) -> None:
+        """tb_decoder_load_wpk: every tensor of a converted model's weights.wpk, by its name."""
+        check(self.lib.tb_decoder_load_wpk(self.handle, os.fsencode(path), int(verify)))
 
     def fill_random(self, seed: int) -> None:
         check(self.lib.tb_decoder_fill_random(self.handle, seed))

@@ -35,6 +35,10 @@ class EncoderConfig(C.Structure):
                 ("theta_global", f32), ("theta_local", f32), ("eps", f32), ("gated", u32), ("mean_pool", u32), ("dims", u32)]
 
 
+class WpkInfo(C.Structure):
+    _fields_ = [("name", cp), ("dtype", u32), ("rank", u32), ("shape", u64 * 8), ("offset", u64), ("bytes", u64), ("crc32c", u32)]
+
+
 class Settings(C.Structure):
     _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32)]
 
@@ -96,6 +100,13 @@ SIGNATURES = {
     "tb_decoder_step_bytes": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
     "tb_decoder_step_launches": (i32, [vp, C.POINTER(u32)]),
     "tb_decoder_hidden": (i32, [vp, vp]),
+    "tb_crc32c": (u32, [u32, vp, sz]),
+    "tb_wpk_open": (i32, [cp, pp]),
+    "tb_wpk_close": (None, [vp]),
+    "tb_wpk_count": (u32, [vp]),
+    "tb_wpk_tensor": (i32, [vp, u32, vp]),
+    "tb_wpk_read": (i32, [vp, u32, vp, sz, i32]),
+    "tb_decoder_load_wpk": (i32, [vp, cp, i32]),
     "tb_encoder_open": (i32, [vp, C.POINTER(EncoderConfig), u32, u32, pp]),
     "tb_encoder_close": (None, [vp]),
     "tb_encoder_load": (i32, [vp, cp, vp, sz]),

@@ -33,6 +33,7 @@ enum Status : int {
     NO_MODEL = 8,
     UNSUPPORTED = 9,
     DEVICE_WAIT = 10,
+    IO = 11,
 };
 
 int fail(int status, const std::string& what);

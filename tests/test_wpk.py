@@ -1,0 +1,138 @@
+"""The `.wpk` reader against files written as the reference writes them; the cases of crates/tachyon/src/wpk/mod.rs:379-470
+(check value of CRC32C, round trip, damaged files, bit rot, misaligned tensors).  No GPU: host code only."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import tachyon_b200 as tb
+import wpk_writer as ww
+
+
+def sample(tmp_path, name):
+    raw = bytes((i * 7 % 251) & 255 for i in range(10_000))  # wpk/mod.rs:357-365
+    path = str(tmp_path / f"{name}.wpk")
+    ww.write(path, [("embed", "bf16", (50, 100), raw), ("norm", "f32", (3,), raw[:12]), ("packed", "u8", (10, 2, 5), raw[:100])])
+    return path, raw
+
+
+def rejection(path):
+    with pytest.raises(tb.Error) as e:
+        tb.Wpk(path)
+    assert e.value.status == 5, e.value  # TB_FORMAT
+    return str(e.value)
+
+
+def patch(path, at, data):
+    with open(path, "r+b") as f:
+        f.seek(at)
+        f.write(data)
+
+
+def test_crc32c_matches_the_standard_check_value():
+    assert tb.crc32c(b"123456789") == 0xE3069283 == ww.crc32c(b"123456789")
+    long = bytes(i & 255 for i in range(1000))
+    assert tb.crc32c(long[333:], tb.crc32c(long[:333])) == ww.crc32c(long) == tb.crc32c(long)
+    assert tb.crc32c(b"") == 0
+
+
+def test_written_tensors_read_back_aligned(tmp_path):
+    path, raw = sample(tmp_path, "roundtrip")
+    w = tb.Wpk(path)
+    t = w.tensors()
+    assert [x[0] for x in t] == ["embed", "norm", "packed"]
+    assert all(x[3] % 4096 == 0 for x in t)
+    assert t[1][2] == (3,) and t[2][2] == (10, 2, 5)
+    assert os.path.getsize(path) == 4096 + 12288 + 2 * 4096 + len(ww.encode([(n, d, s, o, b, c) for n, d, s, o, b, c in t]))
+    assert w.read(0).tobytes() == raw and w.read(1).tobytes() == raw[:12] and w.read(2).tobytes() == raw[:100]
+    w.close()
+
+
+def test_damaged_files_are_rejected(tmp_path):
+    path, _ = sample(tmp_path, "damaged")
+    size = os.path.getsize(path)
+    patch(path, size - 1, b"\xff")
+    assert "the tensor table is corrupt" in rejection(path)
+    patch(path, 9, b"\xff")
+    assert "the header is corrupt" in rejection(path)
+    os.truncate(path, size - 1)
+    why = rejection(path)
+    assert "truncated" in why or "corrupt" in why
+    patch(path, 0, b"NOTAWPK!")
+    assert "not a .wpk file" in rejection(path)
+    with open(path, "wb") as f:
+        f.write(b"tiny")
+    assert "the file ends early" in rejection(path)
+    with pytest.raises(tb.Error) as e:
+        tb.Wpk(str(tmp_path / "absent.wpk"))
+    assert e.value.status == 11  # TB_IO
+
+
+def test_corrupted_data_fails_verification(tmp_path):
+    path, _ = sample(tmp_path, "bitrot")
+    patch(path, 4096 + 5000, b"\xff")
+    w = tb.Wpk(path)
+    with pytest.raises(tb.Error) as e:
+        w.read(0)
+    assert e.value.status == 5 and '"embed"' in str(e.value)
+    assert w.read(0, verify=False).nbytes == 10_000  # loading never touches the bytes with the CPU
+    w.read(1)
+    w.close()
+
+
+def test_misaligned_and_mismatched_tensors_are_rejected(tmp_path):
+    path = str(tmp_path / "misaligned.wpk")
+    table = ww.encode([("w", 5, (8,), 100, 8, 0)])
+    with open(path, "wb") as f:
+        f.write(ww.header(1, 4096, table) + b"\0" * 4096 + table)
+    assert 'tensor "w": not 4 KiB aligned' in rejection(path)
+    table = ww.encode([("x", 1, (3,), 0, 5, 0)])  # three f16 are six bytes
+    with open(path, "wb") as f:
+        f.write(ww.header(1, 4096, table) + b"\0" * 4096 + table)
+    assert "its length does not match its shape" in rejection(path)
+    table = ww.encode([("y", 5, (8192,), 0, 8192, 0)])
+    with open(path, "wb") as f:
+        f.write(ww.header(1, 4096, table) + b"\0" * 4096 + table)
+    assert "it lies outside the data region" in rejection(path)
+    table = ww.encode([("z", 9, (8,), 0, 8, 0)])
+    with open(path, "wb") as f:
+        f.write(ww.header(1, 4096, table) + b"\0" * 4096 + table)
+    assert "unknown element type" in rejection(path)
+
+
+@pytest.mark.gpu
+def test_a_converted_q4_model_loads_from_its_wpk(ctx, tmp_path):
+    """weights.wpk as model::convert writes it (model/mod.rs:178-286): `<name>.w` u8 [rows, cols/2], `<name>.s` f16
+    [rows, cols/64], vectors f32; the decoder that read the file gives the bits of the one filled on the device."""
+    from oracle.model import OracleModel
+
+    cfg = tb.gemma4_e4b_shape(layers=2, ffn=2048, vocab=2048)
+    cfg.window, cfg.global_every = 16, 2
+    ref = OracleModel(cfg, 31, context=64, chunk=0, weight_bits=4)
+    tensors = []
+    for name, a in ref.tensors.items():
+        kind = "u8" if name.endswith(".w") else "f16" if name.endswith(".s") else "f32"
+        a = np.ascontiguousarray(a)
+        tensors.append((name, kind, a.shape, a.view(np.uint8).tobytes() if kind != "u8" else a.astype(np.uint8, copy=False).view(np.uint8).tobytes()))
+    path = str(tmp_path / "weights.wpk")
+    ww.write(path, tensors, crc=ww.fast_crc32c)
+    a = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4)
+    a.load_wpk(path)
+    a.build()
+    b = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4)
+    b.fill_random(31)
+    b.build()
+    for token in [5, 99, 2000, 7]:
+        assert a.step(token) == b.step(token)
+        assert np.array_equal(a.logits(), b.logits())
+    # the wrong format is refused by size, an unknown tensor by name
+    c = tb.Decoder(ctx, cfg, context=64, weight_bits=8)
+    with pytest.raises(tb.Error) as e:
+        c.load_wpk(path)
+    assert e.value.status == 5
+    ww.write(path, [("per_layer_proj.w", "u8", (4,), b"abcd")])
+    with pytest.raises(tb.Error) as e:
+        a.load_wpk(path)
+    assert e.value.status == 8
+    a.close(), b.close(), c.close()
