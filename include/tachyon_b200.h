@@ -119,6 +119,9 @@ TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* s
  */
 enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2, TB_GEMM_ADD = 3, TB_GEMM_GEGLU_ERF = 4, TB_GEMM_GELU_ERF = 5 };
 TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
+/* The same product on the reference's Q4 weights (packed u8 [n, k/2], scales f16 [n, k/64], quant.rs:47-82): the nibbles
+ * become f16 (n - 8) * scale in the operand path; stands in for gemm_q4 (ptx/gemm.rs:225-259) on a converted model. */
+TB_API int tb_gemm_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
 
 /*
  * The reference's own decode formats, for callers that hold a model converted by the reference (quant.rs:47-130):

@@ -645,7 +645,7 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
     tb_context* ctx = d->ctx;
     const uint32_t H = c.hidden, NQ = nq(c), NQKV = nq(c) + 2 * nkv(c);
     TB_CUDA(cudaMemcpyAsync(d->pf_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
-    TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h));
+    TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h, d->embed.bits));
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
         if (i == 0) {
@@ -654,15 +654,15 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
             const Layer& P = d->layers[i - 1];
             TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
         }
-        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, NQKV, H, d->pf_qkv, 0));
+        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, NQKV, H, d->pf_qkv, 0, L.qkv.bits));
         TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads, c.kv_heads,
                                   c.eps, c.attn_scale));
         if (i + 1 == c.layers) break;
         TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, c.kv_heads));
-        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, NQ, d->pf_y, 0));
+        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, NQ, d->pf_y, 0, L.o.bits));
         TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_attn, L.pre_ffn, n, H, c.eps, 1.0f, d->pf_x));
-        TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2));
-        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0));
+        TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2, L.gate_up.bits));
+        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0, L.down.bits));
     }
     return OK;
 }
@@ -674,8 +674,7 @@ int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
     for (uint32_t i = 0; i < n; i++)
         if (tokens[i] >= d->cfg.vocab) return fail(OUT_OF_RANGE, "decoder: token outside the vocabulary");
     const char* env = getenv("TACHYON_B200_PREFILL_BY_STEPS");
-    // Four-bit weights have no tensor-core product yet: their prompts go through the decode step.
-    const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || d->embed.bits == 4 || (env != nullptr && env[0] == '1');
+    const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || (env != nullptr && env[0] == '1');
     if (by_steps) {
         // Without chunk buffers: every prompt token through the decode step; its sample is dropped.
         for (uint32_t i = 0; i < n; i++) {

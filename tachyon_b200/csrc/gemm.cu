@@ -82,6 +82,20 @@ __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale, uint32_t& lo
     hi = *reinterpret_cast<const uint32_t*>(&vb);
 }
 
+// Eight four-bit weights (one word of the reference's Q4: bytes' low nibbles are weights 0..3, high nibbles 4..7,
+// crates/tachyon/src/quant.rs:60-66) -> eight f16 of (n - 8) * scale, in order, as four half2.
+__device__ __forceinline__ void dequant8_q4(uint32_t w, __half2 scale, uint32_t (&out)[4]) {
+    const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+    const __half2 bias = __floats2half2_rn(1032.0f, 1032.0f);  // 0x6400 | n is 1024 + n
+    uint32_t p[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342), __byte_perm(hi, 0x64646464u, 0x4140),
+                     __byte_perm(hi, 0x64646464u, 0x4342)};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p[i]), bias), scale);
+        out[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
 struct GemmArgs {
     const int8_t* w;
     const __half* s;
@@ -93,7 +107,8 @@ struct GemmArgs {
 
 // MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
 // dequantisation is shared by twice the tensor-core work.
-template <int MT>
+// WB: bits per weight, 8 (codes, an f16 scale per 32) or 4 (the reference's Q4, a scale per 64 = one per row and K tile).
+template <int MT, int WB = 8>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const GemmArgs g, uint32_t* status) {
     constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
     extern __shared__ uint8_t raw_unaligned[];
@@ -170,6 +185,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             for (int it = 0; it < 4; it++) {
                 const uint32_t row = it * 64 + (j >> 2), n = n0 + row;
                 const bool live = n < g.N;
+                if constexpr (WB == 4) {
+                    // A piece is 16 weights = 8 bytes; a row's tile 32 bytes; its one scale per tile comes eight tiles at a time.
+                    const uint2 t = live ? __ldg(reinterpret_cast<const uint2*>(g.w + (size_t)n * (g.K / 2) + (size_t)kt * (BK / 2) + qtr * 8))
+                                         : make_uint2(0x88888888u, 0x88888888u);
+                    c[it] = make_uint4(t.x, t.y, 0u, 0u);
+                    if ((kt & 7) == 0) {
+                        const __half* sp = g.s + (size_t)n * (g.K / 64) + kt;
+                        if (live && kt + 8 <= g.K / 64 && (g.K / 64) % 8 == 0) {
+                            sc8[it] = __ldg(reinterpret_cast<const uint4*>(sp));
+                        } else {
+                            __half t8[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) t8[e] = (live && kt + e < g.K / 64) ? sp[e] : __float2half(0.0f);
+                            sc8[it] = *reinterpret_cast<const uint4*>(t8);
+                        }
+                    }
+                    continue;
+                }
                 c[it] = live ? __ldg(reinterpret_cast<const uint4*>(g.w + (size_t)n * g.K + (size_t)kt * BK + qtr * 16))
                              : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
                 if ((kt & 3) == 0) {
@@ -195,6 +228,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             for (int it = 0; it < 4; it++) {
                 // scale of this piece's group of 32: tile kt's two scales are halves 2*(kt&3) and 2*(kt&3)+1
                 const uint32_t words[4] = {sc8[it].x, sc8[it].y, sc8[it].z, sc8[it].w};
+                if constexpr (WB == 4) {
+                    const uint32_t pair = words[(kt & 7) >> 1];
+                    const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)((kt & 1) ? (pair >> 16) : (pair & 0xffffu))));
+                    uint32_t a[4], b[4];
+                    dequant8_q4(c[it].x, s2, a), dequant8_q4(c[it].y, s2, b);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) v[it][e] = a[e], v[it][4 + e] = b[e];
+                    continue;
+                }
                 const uint32_t pair = words[kt & 3];
                 const __half sh = __ushort_as_half((unsigned short)((qtr & 2) ? (pair >> 16) : (pair & 0xffffu)));
                 const __half2 s2 = __half2half2(sh);
@@ -303,11 +345,13 @@ EncodeTiled encode_tiled() {
 
 }  // namespace
 
-int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode) {
+int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
+                   uint32_t wbits) {
     if (!w || !s || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
     if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
     if (N % 32 != 0 || ((mode == 2 || mode == 4) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
     if (mode < 0 || mode > 5) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
     EncodeTiled enc = encode_tiled();
@@ -325,11 +369,15 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     if (!configured[ctx->gpu & 15]) {
         TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
         TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<1, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
     GemmArgs g{w, s, out, M, N, K, mode};
     const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
-    if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
+    if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
+    else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
+    else if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
     else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
     TB_CUDA(cudaGetLastError());
     return OK;

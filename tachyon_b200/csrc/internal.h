@@ -152,10 +152,12 @@ int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* 
 
 // ---- prefill GEMM (tensor cores) ------------------------------------------------------------------------------
 // D[M, N] = A[M, K] (f16) x W[N, K]^T (Q8); mode 0: f32 out, 1: f16 out, 2: GeGLU of column pairs -> f16 [M, N/2].
-int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode);
+int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
+                   uint32_t wbits = 8);
 
 // ---- prefill kernels around the GEMMs (prefill.cu) ---------------------------------------------------------------------
-int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out);
+int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out,
+                         uint32_t wbits = 8);
 int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
                         __half* x);
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,

@@ -13,9 +13,19 @@ namespace {
 constexpr int D = 256;
 
 // ---- embedding rows ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) prefill_embed_kernel(const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t cols, float scale, float* out) {
+__global__ void __launch_bounds__(256) prefill_embed_kernel(const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t cols, float scale, float* out,
+                                                            uint32_t wbits) {
     const size_t row = (size_t)tokens[blockIdx.x] * cols;
     float* o = out + (size_t)blockIdx.x * cols;
+    if (wbits == 4) {  // the reference's Q4 table (quant.rs:60-66)
+        const uint8_t* packed = reinterpret_cast<const uint8_t*>(w);
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            const size_t at = row + i, g = at / 64, k = at % 64;
+            const int n = (packed[g * 32 + k / 8 * 4 + k % 4] >> (k % 8 / 4 * 4)) & 15;
+            o[i] = (float)(n - 8) * __half2float(s[g]) * scale;
+        }
+        return;
+    }
     for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) o[i] = (float)w[row + i] * __half2float(s[(row + i) / 32]) * scale;
 }
 
@@ -260,8 +270,9 @@ __global__ void __launch_bounds__(128) prefill_flash_kernel(const __half* q, con
 
 }  // namespace
 
-int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out) {
-    prefill_embed_kernel<<<n, 256, 0, ctx->stream>>>(w, s, tokens, cols, scale, out);
+int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out,
+                         uint32_t wbits) {
+    prefill_embed_kernel<<<n, 256, 0, ctx->stream>>>(w, s, tokens, cols, scale, out, wbits);
     TB_CUDA(cudaGetLastError());
     return OK;
 }

@@ -250,15 +250,20 @@ def test_q4_weights_step_matches_the_cpu_forward_and_loads_converted_tensors(ctx
     with pytest.raises(tb.Error) as e:
         other.load("0.qkv.w", np.zeros(3072 * 2048, np.int8))  # the eight-bit size
     assert e.value.status == 5
-    # a prompt (token by token inside the library for this format) equals stepping
-    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(20)]
+    # a prompt through the chunked tensor-core prefill (nibbles dequantised in the operand path) against stepping
+    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(30)]
     dec.reset()
     for t in prompt[:-1]:
         dec.step(t)
     a, la = dec.step(prompt[-1]), dec.logits()
     dec.reset()
     dec.prefill(prompt[:-1])
-    assert dec.step(prompt[-1]) == a and np.array_equal(dec.logits(), la)
+    b, lb = dec.step(prompt[-1]), dec.logits()
+    scale = np.abs(la).max()
+    assert np.abs(la - lb).max() <= 4e-3 * scale
+    order = np.sort(cfg.softcap * np.tanh(la.astype(np.float64) / cfg.softcap))
+    if order[-1] - order[-2] > 8e-3 * scale:
+        assert a == b
     with pytest.raises(tb.Error):
         tb.Decoder(ctx, cfg, context=64, fused=True, weight_bits=4)
     dec.close(), other.close()

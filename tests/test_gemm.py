@@ -64,3 +64,26 @@ def test_gemm_rejects_bad_shapes(ctx):
     assert e.value.status == 3
     with pytest.raises(tb.Error):
         ctx.gemm_q8(z, z, z, 4, 32, 64, z, 9)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (37, 256, 2048), (300, 3072, 2048), (129, 2048, 16384), (256, 96, 128), (64, 64, 576)])
+def test_gemm_q4_matches_f64(ctx, m, n, k):
+    """The reference's Q4 weights (quant.rs:47-82) through the same tensor-core product: (n - 8) * scale as f16 operands."""
+    wf = np.random.default_rng(n + k).uniform(-1, 1, (n, k)).astype(np.float32)
+    packed, scales = oracle.q4(wf)
+    nib = np.zeros((n * k // 64, 64), np.float64)
+    pk = packed.reshape(-1, 32)
+    for j in range(64):  # weight j of a group: nibble j % 8 / 4 of byte j / 8 * 4 + j % 4
+        nib[:, j] = (pk[:, j // 8 * 4 + j % 4] >> (j % 8 // 4 * 4)) & 15
+    deq = ((nib - 8) * f16_to_f32(scales).astype(np.float64)[:, None]).reshape(n, k)
+    a = f16_to_f32(f16(np.random.default_rng(m + k).standard_normal((m, k)).astype(np.float32)))
+    a64 = a.astype(np.float64)
+    want, bound = a64 @ deq.T, np.abs(a64) @ np.abs(deq).T
+    out = ctx.alloc((m + 1) * n * 4)
+    out.upload(np.full((m + 1) * n, 12345.0, np.float32))
+    ctx.gemm_q4(ctx.upload(packed), ctx.upload(scales), ctx.upload(f16(a)), m, n, k, out, 0)
+    got = out.download(np.float32, (m + 1) * n)
+    assert np.all(got[m * n:] == 12345.0)
+    got = got[: m * n].reshape(m, n)
+    assert np.all(np.abs(got - want) <= 1e-3 * bound + 1e-6), float(np.abs(got - want).max())
+    assert ctx.status() == 0
