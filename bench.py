@@ -459,7 +459,7 @@ def bench_prefill(args, ranks: Ranks):
     ctx = tb.Context(ranks.local)
     cfg = tb.gemma4_e4b_shape()
     T = args.tokens
-    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=args.chunk, keep_logits=False)
+    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=args.chunk, keep_logits=False, weight_bits=4 if args.weights == "q4" else 8)
     dec.fill_random(SEED)
     dec.build()
     prompt = np.array([(i * 7919 + 13) % cfg.vocab for i in range(T)], np.uint32)  # the reference's prompt (benches/generate.rs:47)
@@ -487,8 +487,8 @@ def bench_prefill(args, ranks: Ranks):
     n = ranks.world
     return {"metric": "prefill_tokens_per_second", "value": n * T / (ms_max / 1e3), "unit": "tok/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
-            "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape Q8, chunks of {args.chunk}, last token through the decode step",
+            "dtype": ("int4" if args.weights == "q4" else "int8") + " weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape {args.weights.upper()}, chunks of {args.chunk}, last token through the decode step",
                        "timing": "host wall clock around tb_decoder_prefill + tb_decoder_step (token ids cross from host memory)"},
             "gpu_launches": None, "first_token": int(first),
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained, "peak_source": how + " (sustained)",
