@@ -195,6 +195,29 @@ TB_API int tb_attend_decode_static(tb_context* ctx, const tb_attend* args);
  */
 TB_API int tb_sample_greedy(tb_context* ctx, const float* logits, uint32_t vocab, float softcap, float penalty, uint32_t* seen, const uint32_t* allowed,
                      void* scratch, uint32_t* state, uint32_t* token_out);
+/*
+ * Sampling (ptx/sample.rs:38-78), laid out as the kernel reads it from DEVICE memory, so that one recorded decode step
+ * serves every setting: soft cap (0: none), temperature (0: the most likely token), nucleus size (1: no limit), least
+ * probability relative to the most likely token (0: no limit), repetition penalty (1: none), most tokens kept (0: no
+ * limit), device address of a bitmap of allowed tokens (0: all), seed of the draws.
+ */
+typedef struct tb_sampling {
+    float softcap, temperature, top_p, min_p, penalty;
+    uint32_t top_k;
+    uint64_t allowed;
+    uint64_t seed;
+} tb_sampling;
+/*
+ * sample (ptx/sample.rs:1-27), argument for argument: logits f32 [vocab] (left unchanged), work f32 [vocab], cfg (device),
+ * state = [step, token] (the kernel writes the token and advances the step, which seeds the next draw), seen (bitmap of
+ * vocab bits; the token's bit is set), out (NULL or a word that also receives the token, e.g. mapped pinned memory),
+ * partial (8 words per block), count (zero before the first launch, left zero).  vocab is a multiple of 4.  The draw
+ * is exact under top_k / top_p / min_p: Gumbel-max over the tokens, the candidate checked against the filters by the
+ * last block and redrawn among the tokens above it when it fails (32 rounds at most, then the largest).
+ * blocks: 0, or the most blocks to launch (the reference's tests use 7 so that a block walks several shares).
+ */
+TB_API int tb_sample(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const tb_sampling* cfg, uint32_t* state, uint32_t* seen,
+                     uint32_t* out, void* partial, uint32_t* count, uint32_t blocks);
 /* The k largest logits, largest first, lowest index first among equals. idx, val: device [k]. */
 TB_API int tb_topk(tb_context* ctx, const float* logits, uint32_t vocab, uint32_t k, uint32_t* idx, float* val);
 

@@ -70,6 +70,7 @@ def _declare(l: C.CDLL) -> None:
         "tbo_q8_blocks": (None, [vp, sz, i32, vp, vp]),
         "tbo_q8p_pairs": (None, [vp, sz]),
         "tbo_product_q4": (None, [vp, vp, vp, sz, sz, vp, vp]),
+        "tbo_sample_draw": (C.c_uint32, [vp, sz, vp, C.c_uint32, vp, vp, vp]),
         "tbo_gemv_q4": (None, [vp, vp, vp, vp, sz, sz, vp]),
         "tbo_gemv_q4x": (None, [vp, vp, vp, sz, sz, vp, vp]),
         "tbo_gemv_q8": (None, [vp, vp, vp, sz, sz, vp, vp, vp]),
@@ -204,6 +205,25 @@ def sample_greedy(logits, softcap=0.0, penalty=1.0, seen=None, allowed=None):
     gap = C.c_double(0)
     t = lib().tbo_sample_greedy(ptr(logits), logits.size, softcap, penalty, ptr(seen), ptr(allowed), C.byref(gap))
     return int(t), gap.value
+
+
+class Sampling(C.Structure):
+    """ptx/sample.rs:38-78: the 40 bytes the sampler reads."""
+    _fields_ = [("softcap", C.c_float), ("temperature", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("penalty", C.c_float),
+                ("top_k", C.c_uint32), ("allowed", C.c_uint64), ("seed", C.c_uint64)]
+
+
+def sampling(softcap=0.0, temperature=0.0, top_p=1.0, min_p=0.0, penalty=1.0, top_k=0, allowed=0, seed=0) -> Sampling:
+    """Sampling::default (sample.rs:58-63) with overrides."""
+    return Sampling(softcap, temperature, top_p, min_p, penalty, top_k, allowed, seed)
+
+
+def sample_draw(logits, cfg: Sampling, step: int, seen=None, allowed=None):
+    """(token, failed draws) of one draw at `step`, hash and filters as the reference's kernel, transcendental steps in double."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    rounds = C.c_int(0)
+    t = lib().tbo_sample_draw(ptr(logits), logits.size, C.byref(cfg), step, ptr(seen), ptr(allowed), C.byref(rounds))
+    return int(t), rounds.value
 
 
 def sample_topk(logits, k):

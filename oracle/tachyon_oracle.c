@@ -442,6 +442,73 @@ TBO_API void tbo_sample_topk(const float *logits, size_t vocab, int k, uint32_t 
 }
 
 /* ------------------------------------------------------------------------------------------------ */
+/* Sampler, drawing part: ptx/sample.rs:81-88 (hash), 113-121 (Gumbel noise), 318-352 (filter check    */
+/* and redraw), with the transcendental steps in double instead of the GPU's approximate instructions. */
+/* ------------------------------------------------------------------------------------------------ */
+
+typedef struct {   /* ptx/sample.rs:38-78, the 40 bytes the kernel reads */
+    float softcap, temperature, top_p, min_p, penalty;
+    uint32_t top_k;
+    uint64_t allowed, seed;
+} tbo_sampling;
+
+static uint32_t fmix32(uint32_t h) { h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16; return h; }
+static uint32_t noise_base(uint32_t step, uint32_t round, uint64_t seed) {
+    uint32_t h = step * 0x9E3779B9u + (uint32_t)(seed >> 32);
+    h = round * 0x85EBCA77u + h;
+    return fmix32(fmix32(h) ^ (uint32_t)seed);
+}
+static double gumbel_noise(uint32_t i, uint32_t base) {
+    uint32_t h = fmix32((i * 0x9E3779B9u) ^ base) >> 9;
+    double u = ((double)h + 0.5) * 0x1p-23;
+    return -log(-log(u));
+}
+
+/* One draw at step `step` (the kernel's state[0]); `allowed`, `seen`: bitmaps or NULL.  `rounds` receives the number of
+ * failed draws. */
+TBO_API uint32_t tbo_sample_draw(const float *logits, size_t vocab, const tbo_sampling *c, uint32_t step, const uint32_t *seen,
+                                 const uint32_t *allowed, int *rounds) {
+    double *x = (double *)malloc(vocab * sizeof(double));
+    double m = -INFINITY, z = 0.0;
+    size_t amax = 0;
+    for (size_t i = 0; i < vocab; i++) {
+        x[i] = tbo_sample_transform(logits[i], i, c->softcap, c->penalty, c->temperature, seen, allowed);
+        if (i == 0 || x[i] > m) { m = x[i]; amax = i; }
+    }
+    uint32_t token = (uint32_t)amax;
+    int round = 0;
+    if (c->temperature > 0.0f) {
+        for (size_t i = 0; i < vocab; i++) z += exp(x[i] - m);
+        int filter = c->top_k != 0 || c->top_p < 1.0f || c->min_p > 0.0f;
+        double thr = -INFINITY;
+        for (;;) {
+            uint32_t base = noise_base(step, (uint32_t)round, c->seed);
+            double kv = -INFINITY;
+            size_t ki = amax;
+            for (size_t i = 0; i < vocab; i++) {
+                if (!(x[i] > thr)) continue;
+                double k = x[i] + gumbel_noise((uint32_t)i, base);
+                if (k > kv) { kv = k; ki = i; }
+            }
+            token = (uint32_t)ki;
+            if (!filter) break;
+            double cnt = 0.0, mass = 0.0, lj = x[ki];
+            for (size_t i = 0; i < vocab; i++) if (x[i] > lj) { cnt += 1.0; mass += exp(x[i] - m); }
+            int ok = (c->top_k == 0 || cnt < (double)c->top_k) && (c->top_p >= 1.0f || mass < (double)c->top_p * z || mass == 0.0) &&
+                     lj - m >= log((double)c->min_p);
+            if (ok) break;
+            thr = lj;
+            round++;
+            token = (uint32_t)amax;
+            if (round >= 32) break;
+        }
+    }
+    if (rounds) *rounds = round;
+    free(x);
+    return token;
+}
+
+/* ------------------------------------------------------------------------------------------------ */
 /* Seeded synthetic tensors.  The reference's benches use synthetic weights too (benches/gemv.rs:8-9); */
 /* these generators are this build's own and use only exactly-rounded operations, so a GPU fill kernel */
 /* written with the same steps produces identical bits.                                               */

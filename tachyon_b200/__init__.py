@@ -149,6 +149,11 @@ class Context:
         """tb_gemm_q4: the same product on the reference's Q4 weights."""
         check(self.lib.tb_gemm_q4(self.handle, packed.ptr, s.ptr, a.ptr, m, n, k, out.ptr, mode))
 
+    def sample(self, logits, work, vocab, cfg, state, seen, out, partial, count, blocks=0) -> None:
+        """tb_sample: the reference's sampler; cfg is a device buffer holding the 40-byte Sampling."""
+        check(self.lib.tb_sample(self.handle, logits.ptr, work.ptr, vocab, cfg.ptr, state.ptr, seen.ptr, None if out is None else out.ptr, partial.ptr,
+                                 count.ptr, blocks))
+
     def norm(self, h, y_res, w1, w2, n, eps, hscale, h_out, x_out) -> None:
         p = lambda b: None if b is None else b.ptr
         check(self.lib.tb_norm(self.handle, h.ptr, p(y_res), p(w1), p(w2), n, eps, hscale, p(h_out), p(x_out)))

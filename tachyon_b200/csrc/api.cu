@@ -212,6 +212,12 @@ int tb_gemv_q4x(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, 
     return launch_gemv(ctx, p);
 }
 
+int tb_sample(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const tb_sampling* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
+              void* partial, uint32_t* count, uint32_t blocks) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_sample_draw(ctx, logits, work, vocab, cfg, state, seen, out, static_cast<float*>(partial), count, blocks);
+}
+
 int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, const float* h, const float* y_res, const float* w1, const float* w2, float eps,
                     float hscale, float* h_out, float* y, uint32_t rows, uint32_t cols, int geglu) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");

@@ -182,6 +182,10 @@ int launch_interleave_rows(tb_context* ctx, const void* src, void* dst, uint32_t
 int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t n);
 int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols);
 
+// The reference's sampler with draws (sample.cu); cfg: 40 bytes of device memory in the reference's Sampling layout.
+int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const void* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
+                       float* partial, uint32_t* count, uint32_t blocks);
+
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {
