@@ -282,6 +282,15 @@ TB_API int tb_decoder_prefill(tb_decoder* dec, const uint32_t* tokens, uint32_t 
 TB_API int tb_decoder_logits(tb_decoder* dec, float* host_out);
 /* Current position. */
 TB_API int tb_decoder_position(tb_decoder* dec, uint32_t* pos);
+/*
+ * How the next steps pick their token (the engine's Request -> Sampling, sample.rs:38-78; NULL: Sampling::default, the
+ * largest logit).  While the settings ask for no more than the largest logit (temperature 0, penalty 1, no mask) the
+ * step's LM head picks it itself; otherwise the step ends in the head's logits and tb_sample's kernel, recorded once:
+ * the settings live in device memory, so changing them records nothing.  `allowed` is a device address the caller keeps
+ * alive.  The bitmap of seen tokens starts empty at tb_decoder_reset and gains every generated token.  Draws are a
+ * function of (seed, position).  Not with the fused step.
+ */
+TB_API int tb_decoder_set_sampling(tb_decoder* dec, const tb_sampling* sampling);
 /* Bytes of weights and of key/value cache one step reads at the current position (the roofline's numerator). */
 TB_API int tb_decoder_step_bytes(tb_decoder* dec, uint64_t* weight_bytes, uint64_t* cache_bytes);
 /* Kernels one step launches. */

@@ -269,6 +269,14 @@ class Decoder:
         a = np.ascontiguousarray(a)
         check(self.lib.tb_decoder_load(self.handle, name.encode(), a.ctypes.data, a.nbytes))
 
+    def set_sampling(self, softcap=0.0, temperature=0.0, top_p=1.0, min_p=0.0, penalty=1.0, top_k=0, allowed: int = 0, seed=0) -> None:
+        """tb_decoder_set_sampling with the reference's Sampling fields (defaults: the largest logit)."""
+        raw = np.zeros(40, np.uint8)
+        raw[:20].view(np.float32)[:] = [softcap, temperature, top_p, min_p, penalty]
+        raw[20:24].view(np.uint32)[0] = top_k
+        raw[24:40].view(np.uint64)[:] = [allowed, seed]
+        check(self.lib.tb_decoder_set_sampling(self.handle, raw.ctypes.data))
+
     def load_wpk(self, path: str, verify: bool = True) -> None:
         """tb_decoder_load_wpk: every tensor of a converted model's weights.wpk, by its name."""
         check(self.lib.tb_decoder_load_wpk(self.handle, os.fsencode(path), int(verify)))

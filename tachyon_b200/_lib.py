@@ -102,6 +102,7 @@ SIGNATURES = {
     "tb_decoder_step_bytes": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
     "tb_decoder_step_launches": (i32, [vp, C.POINTER(u32)]),
     "tb_decoder_hidden": (i32, [vp, vp]),
+    "tb_decoder_set_sampling": (i32, [vp, vp]),
     "tb_crc32c": (u32, [u32, vp, sz]),
     "tb_wpk_open": (i32, [cp, pp]),
     "tb_wpk_close": (None, [vp]),

@@ -70,6 +70,16 @@ struct tb_decoder {
     unsigned long long* best = nullptr;
     uint32_t* words = nullptr;  // pinned host: [0], [1] the tokens the two graphs write; [2] staging for the token fed in
     cudaGraphExec_t graphs[2] = {nullptr, nullptr};
+    // The same step ending in logits + the sampler kernel instead of the fused greedy pick; used while the settings ask
+    // for more than the plain largest logit.  The sampler reads its settings from `sampling` on the device.
+    cudaGraphExec_t graphs_sampled[2] = {nullptr, nullptr};
+    bool sampled = false;       // which pair the next step replays
+    bool capture_sampled = false;  // which op list step_ops is recording
+    void* sampling = nullptr;   // 40 bytes, ptx/sample.rs:38-78
+    float* work = nullptr;      // the sampler's transformed logits
+    uint32_t* seen = nullptr;   // bitmap of the tokens generated since the last reset
+    float* sample_partial = nullptr;
+    uint32_t* sample_count = nullptr;
     cudaEvent_t done[2] = {nullptr, nullptr};
     int at = 0;
     bool running = false, built = false;
@@ -181,7 +191,12 @@ void layout(tb_decoder* d, char* base) {
     }
     vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
     vec(d->qkv, nq(c) + 2 * nkv(c)), vec(d->att, nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
-    vec(d->logits, d->settings.keep_logits ? c.vocab : 1);
+    vec(d->logits, c.vocab);
+    vec(d->work, c.vocab);
+    d->seen = reinterpret_cast<uint32_t*>(base + t.take(((size_t)c.vocab + 31) / 32 * 4));
+    d->sampling = base + t.take(64);
+    vec(d->sample_partial, (size_t)8 * 1024);
+    d->sample_count = reinterpret_cast<uint32_t*>(base + t.take(4));
     vec(d->partial, attend_partial_floats(c.heads, c.kv_heads, max_splits));
     vec(d->freq[0], c.head_dim / 2), vec(d->freq[1], c.head_dim / 2);
     d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.kv_heads * 4));
@@ -305,7 +320,16 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
     h.best = d->best, h.count = reinterpret_cast<uint32_t*>(d->best + 1), h.state = d->state, h.token_out = token_word;
     h.trace = d->trace, h.trace_mask = TRACE - 1;
     h.pf = hint(d, d->layers[0].qkv, 1, 0, PF);  // the next step's first matrix
-    TB_TRY(gemv(d, d->embed, h));
+    if (d->capture_sampled) {
+        // decode.rs:588-591: the head's logits, then the sampler, which writes the token and advances the position.
+        h.epi = EPI_F32, h.y = d->logits;
+        TB_TRY(gemv(d, d->embed, h));
+        TB_TRY(launch_sample_draw(d->ctx, d->logits, d->work, c.vocab, d->sampling, d->state, d->seen, token_word, d->sample_partial, d->sample_count, 0,
+                                  d->trace, TRACE - 1));
+        d->launches++;
+    } else {
+        TB_TRY(gemv(d, d->embed, h));
+    }
     d->final_x = 1 - cur;
     return OK;
 }
@@ -361,7 +385,7 @@ int set_position(tb_decoder* d, uint32_t pos) {
 }
 
 int queue(tb_decoder* d, int g) {
-    TB_CUDA(cudaGraphLaunch(d->graphs[g], d->ctx->stream));
+    TB_CUDA(cudaGraphLaunch(d->sampled ? d->graphs_sampled[g] : d->graphs[g], d->ctx->stream));
     TB_CUDA(cudaEventRecord(d->done[g], d->ctx->stream));
     d->pos++;
     return OK;
@@ -434,6 +458,7 @@ void tb_decoder_close(tb_decoder* d) {
     if (d->ctx && d->ctx->stream) cudaStreamSynchronize(d->ctx->stream);
     for (int g = 0; g < 2; g++) {
         if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]);
+        if (d->graphs_sampled[g]) cudaGraphExecDestroy(d->graphs_sampled[g]);
         if (d->done[g]) cudaEventDestroy(d->done[g]);
     }
     for (int g = 0; g < 2; g++)
@@ -537,10 +562,13 @@ int tb_decoder_build(tb_decoder* d) {
     if (!d) return fail(OUT_OF_RANGE, "null decoder");
     cudaStream_t s = d->ctx->stream;
     TB_CUDA(cudaStreamSynchronize(s));
-    for (int g = 0; g < 2; g++) {
-        if (d->graphs[g]) cudaGraphExecDestroy(d->graphs[g]), d->graphs[g] = nullptr;
+    for (int g = 0; g < (d->fused ? 2 : 4); g++) {
+        // Graphs 2 and 3 are the pair that ends in the sampler kernel (one launch per phase only).
+        cudaGraphExec_t& slot = g < 2 ? d->graphs[g] : d->graphs_sampled[g - 2];
+        d->capture_sampled = g >= 2;
+        if (slot) cudaGraphExecDestroy(slot), slot = nullptr;
         uint32_t* word = nullptr;
-        TB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&word), d->words + g, 0));
+        TB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&word), d->words + (g & 1), 0));
         // The fused step reads its phases from a table on the device, one table per graph (the token word differs).
         if (d->fused) {
             std::vector<StepPhase> table;
@@ -555,20 +583,22 @@ int tb_decoder_build(tb_decoder* d) {
         auto run = [&]() -> int { return d->fused ? launch_step(d->ctx, d->phase_dev[g], d->phase_count, d->grid_counter, d->state) : step_ops(d, word); };
         // One uncaptured pass first: it sets each kernel's attributes (not allowed while capturing) and surfaces
         // descriptor errors plainly.  It runs on zeroed state and is followed by a reset.
-        if (g == 0) {
-            TB_TRY(run());
+        if (g == 0 || g == 2) {
+            const int first = run();
+            if (first != OK) return d->capture_sampled = false, first;
             TB_CUDA(cudaStreamSynchronize(s));
         }
         TB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         const int st = run();
         cudaGraph_t graph = nullptr;
         const cudaError_t e = cudaStreamEndCapture(s, &graph);
+        d->capture_sampled = false;
         if (st != OK) {
             if (graph) cudaGraphDestroy(graph);
             return st;
         }
         if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
-        const cudaError_t ei = cudaGraphInstantiate(&d->graphs[g], graph, 0);
+        const cudaError_t ei = cudaGraphInstantiate(&slot, graph, 0);
         cudaGraphDestroy(graph);
         if (ei != cudaSuccess) return cuda_fail(ei, "cudaGraphInstantiate");
     }
@@ -582,7 +612,24 @@ int tb_decoder_reset(tb_decoder* d) {
     if (!d) return fail(OUT_OF_RANGE, "null decoder");
     if (d->running) TB_TRY(tb_decoder_stop(d));
     TB_CUDA(cudaMemsetAsync(d->state, 0, 8, d->ctx->stream));
+    TB_CUDA(cudaMemsetAsync(d->seen, 0, ((size_t)d->cfg.vocab + 31) / 32 * 4, d->ctx->stream));  // a new sequence has seen nothing
     return set_position(d, 0);
+}
+
+int tb_decoder_set_sampling(tb_decoder* d, const tb_sampling* s) {
+    if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_set_sampling: a generation is running; stop it first");
+    tb_sampling v = {0.0f, 0.0f, 1.0f, 0.0f, 1.0f, 0u, 0ull, 0ull};  // Sampling::default (sample.rs:58-63)
+    if (s) v = *s;
+    if (!(v.penalty > 0.0f) || v.temperature < 0.0f || v.softcap < 0.0f) return fail(OUT_OF_RANGE, "tb_decoder_set_sampling: negative temperature or soft cap, or penalty <= 0");
+    // The plain largest logit needs no sampler kernel: the LM head picks it (the soft cap is monotonic).
+    const bool plain = v.temperature == 0.0f && v.penalty == 1.0f && v.allowed == 0;
+    if (!plain && d->fused) return fail(UNSUPPORTED, "tb_decoder_set_sampling: the fused step only picks the largest logit");
+    if (!plain && d->cfg.vocab % 4 != 0) return fail(UNSUPPORTED, "tb_decoder_set_sampling: the sampler needs a vocabulary that is a multiple of 4");
+    TB_CUDA(cudaMemcpyAsync(d->sampling, &v, sizeof v, cudaMemcpyHostToDevice, d->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(d->ctx->stream));  // `v` is on this stack
+    d->sampled = !plain;
+    return OK;
 }
 
 int tb_decoder_step(tb_decoder* d, uint32_t token, uint32_t* next) {

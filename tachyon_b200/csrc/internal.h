@@ -184,7 +184,7 @@ int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, co
 
 // The reference's sampler with draws (sample.cu); cfg: 40 bytes of device memory in the reference's Sampling layout.
 int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const void* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
-                       float* partial, uint32_t* count, uint32_t blocks);
+                       float* partial, uint32_t* count, uint32_t blocks, uint32_t* trace = nullptr, uint32_t trace_mask = 0);
 
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>

@@ -94,8 +94,9 @@ static_assert(sizeof(Sampling) == 40, "the reference's layout");
 
 constexpr float LOG2E = 1.44269502162933349609375f;  // 0f3FB8AA3B
 
+// trace (optional, not in the reference's list): trace[step & trace_mask] = token, for the decoder's chained runs.
 __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, float* work, uint32_t vocab, const Sampling* cfg, uint32_t* state,
-                                                         uint32_t* seen, uint32_t* out, float* partial, uint32_t* count) {
+                                                         uint32_t* seen, uint32_t* out, float* partial, uint32_t* count, uint32_t* trace, uint32_t trace_mask) {
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
     __shared__ uint32_t flag;
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         }
     }
     if (th == 0) {
+        if (trace != nullptr) trace[step & trace_mask] = token;
         state[1] = token;
         state[0] = step + 1;
         atomicOr(seen + (token >> 5), 1u << (token & 31));
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
 }  // namespace
 
 int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const void* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
-                       float* partial, uint32_t* count, uint32_t blocks) {
+                       float* partial, uint32_t* count, uint32_t blocks, uint32_t* trace, uint32_t trace_mask) {
     if (!logits || !work || !cfg || !state || !seen || !partial || !count) return fail(OUT_OF_RANGE, "sample: null argument");
     if (vocab == 0 || vocab % 4 != 0) return fail(OUT_OF_RANGE, "sample: the vocabulary must be a positive multiple of 4");
     if ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(work)) & 15) return fail(OUT_OF_RANGE, "sample: logits and work must be 16-byte aligned");
@@ -222,7 +224,7 @@ int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32
     if (grid > most) grid = most;
     if (grid > 1024) grid = 1024;
     TB_CUDA(launch_kernel(ctx, sample_kernel, dim3(grid), dim3(THREADS), 0, true, logits, work, vocab, static_cast<const Sampling*>(cfg), state, seen, out, partial,
-                          count));
+                          count, trace, trace_mask));
     return OK;
 }
 
