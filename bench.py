@@ -35,6 +35,7 @@ SEED = 20251
 CONTEXT_FILLED = 2048
 CONTEXT = 4096
 HBM_SPEC_GBS = 8000.0  # the denominator the benchmark definition fixes
+GATEUP_TRAFFIC = 72_201_216  # bytes per launch of the gate/up kernel under ncu (dram read + write), profiles/gemv_q8_kernel__gate_up_32768x2048.md
 
 
 def measured_peak_gbs():
@@ -254,11 +255,11 @@ def bench_decode(args, ranks: Ranks):
     return line, cfg, gpu_tokens
 
 
-def kernel_roofline(ctx, cfg, warmup: int, steps: int):
+def kernel_roofline(ctx, cfg, warmup: int, steps: int, matrices: int = 0):
     """Times the gate/up projection kernel (norm prologue, GeGLU epilogue) back to back over `layers` distinct matrices."""
     import tachyon_b200 as tb
 
-    rows, cols, layers = 2 * cfg.ffn, cfg.hidden, cfg.layers
+    rows, cols, layers = 2 * cfg.ffn, cfg.hidden, matrices or cfg.layers
     lib = ctx.lib
     w = ctx.alloc(layers * rows * cols)
     s = ctx.alloc(layers * rows * (cols // 32) * 2)
@@ -273,8 +274,8 @@ def kernel_roofline(ctx, cfg, warmup: int, steps: int):
         si = C.c_void_p(s.ptr + (i % layers) * rows * (cols // 32) * 2)
         tb.check(lib.tb_gemv_q8_norm(ctx.handle, wi, si, h.ptr, y.ptr, w1.ptr, w2.ptr, 1e-6, 1.0, hout.ptr, out.ptr, rows, cols, 1))
 
-    n = max(steps, 64)
-    for i in range(max(warmup, 3) * 4):
+    n = steps if matrices else max(steps, 64)
+    for i in range(max(warmup, 3) * (1 if matrices else 4)):
         launch(i)
     ctx.sync()
     e0, e1 = ctx.event(), ctx.event()
@@ -290,9 +291,22 @@ def kernel_roofline(ctx, cfg, warmup: int, steps: int):
     for b in (w, s):
         b.free()
     return {"kernel": "gemv_q8_kernel<1, X_NORM, EPI_GEGLU> (gate/up projection)", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "frac_of_8tbs": achieved / HBM_SPEC_GBS, "peak_source": how, "traffic": None,
+            "frac": achieved / peak, "frac_of_8tbs": achieved / HBM_SPEC_GBS, "peak_source": how, "traffic": GATEUP_TRAFFIC,
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of this kernel and shape under ncu (profiles/gemv_q8_kernel__gate_up_32768x2048.md)",
             "bytes_per_launch": alg, "us_per_launch": us, "launches_timed": n,
-            "how": "back-to-back launches cycling over 35 distinct matrices (2.5 GB), CUDA events on the launching stream"}
+            "how": f"back-to-back launches cycling over {layers} distinct matrices ({layers * rows * cols / 1e9:.1f} GB), CUDA events on the launching stream"}
+
+
+def bench_gateup(args, ranks: Ranks):
+    """The dominant kernel alone on few matrices (default 4 x 71 MB, larger than L2): the case small enough to capture."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    roof = kernel_roofline(ctx, tb.gemma4_e4b_shape(), args.warmup, args.steps, matrices=min(args.copies, 35))
+    return {"metric": "gate_up_gemv_gbs", "value": roof["achieved"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": roof["us_per_launch"] / 1e3, "higher_is_better": True, "dtype": "int8 weights x f32 activations, f32 accumulate", "data": "synthetic",
+            "impl": "ours", "config": {"workload": "gate/up projection of configs[2] alone: norm prologue, 32768 x 2048 Q8, GeGLU epilogue"},
+            "gpu_launches": args.steps, "roofline": roof}
 
 
 def bench_gemv(args, ranks: Ranks):
@@ -561,7 +575,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "attend", "gemm", "prefill", "encoder"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "prefill", "encoder"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -578,6 +592,8 @@ def main():
             line = reference_arm(args, ranks)
         elif args.workload == "gemv":
             line = bench_gemv(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "gateup":
+            line = bench_gateup(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "gemv_q4":
             line = bench_gemv_q4(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "attend":

@@ -21,7 +21,7 @@ constexpr int PROW = TILE + 8;  // the same for the transposed probabilities
 struct Smem {
     __half k[TILE][ROW];
     __half v[TILE][ROW];
-    float q[MAXG][D];            // the queries, scaled; after the last tile the outputs on their way to the old layout
+    float q[MAXG][D + 8];        // the queries, scaled (rows padded: the fragment build reads four rows at once); after the last tile the outputs on their way to the old layout
     float kf[D], vf[D];          // the new token's key and value
     float s[2][TILE][8];         // raw scores: [half of the dimensions][row][column]; column h is head h's high part, G + h its low part
     __half pt[8][PROW];          // probabilities, transposed: row h the f16 value of head h's, row G + h what the f16 leaves of it
