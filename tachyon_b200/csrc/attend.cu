@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p) {
     if (p.early) {
         pos = ld_cg_u(p.pos);
         sent = load_first_tile(p, sm, blockIdx.x, blockIdx.y, pos, tid);
-        trig = rope_trig(p.freq, pos, tid & 31);
+        trig = rope_trig(p.freq, pos, tid & 31, p.trig);
     }
     unsigned long long* stamp = nullptr;
     if (p.stamps != nullptr && tid == 0) {
@@ -53,13 +53,31 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p) {
     if (stamp) stamp[1] = global_ns();
     if (!p.early) {
         pos = ld_cg_u(p.pos);
-        trig = rope_trig(p.freq, pos, tid & 31);
+        trig = rope_trig(p.freq, pos, tid & 31, p.trig);
     }
     attend_body<G, false>(p, sm, tid, blockIdx.x, blockIdx.y, pos, sent, trig);
     if (stamp) stamp[3] = global_ns();
 }
 
+// table[pos][i] = cos(pos * freq[i]), table[pos][128 + i] = sin(pos * freq[i]): sincosf of the f32 product, as rope_trig.
+__global__ void rope_table_kernel(const float* freq, uint32_t positions, float* table) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= positions * (D / 2)) return;
+    const uint32_t pos = i / (D / 2), k = i % (D / 2);
+    float s, c;
+    sincosf((float)pos * freq[k], &s, &c);
+    table[(size_t)pos * D + k] = c, table[(size_t)pos * D + D / 2 + k] = s;
+}
+
 }  // namespace
+
+int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, float* table) {
+    if (!freq || !table || positions == 0) return fail(OUT_OF_RANGE, "rope table: bad arguments");
+    const uint32_t n = positions * (D / 2);
+    rope_table_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(freq, positions, table);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
 
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits) {
     const uint32_t group = heads / kv_heads;

@@ -35,8 +35,14 @@ struct Smem {
 struct Trig {
     float c[4], s[4];
 };
-__device__ __forceinline__ Trig rope_trig(const float* freq, uint32_t pos, int lane) {
+__device__ __forceinline__ Trig rope_trig(const float* freq, uint32_t pos, int lane, const float* table = nullptr) {
     Trig t;
+    if (table != nullptr) {  // the same values, computed once per position when the table was filled
+        const float4 c = __ldg(reinterpret_cast<const float4*>(table + (size_t)pos * D + 4 * lane));
+        const float4 s = __ldg(reinterpret_cast<const float4*>(table + (size_t)pos * D + D / 2 + 4 * lane));
+        t.c[0] = c.x, t.c[1] = c.y, t.c[2] = c.z, t.c[3] = c.w, t.s[0] = s.x, t.s[1] = s.y, t.s[2] = s.z, t.s[3] = s.w;
+        return t;
+    }
     if (freq == nullptr) {
 #pragma unroll
         for (int i = 0; i < 4; i++) t.c[i] = 1.0f, t.s[i] = 0.0f;
@@ -140,17 +146,18 @@ __device__ __forceinline__ void load_tile(const AttendParams& p, Smem& sm, uint3
     const uint32_t first = (cur + p.cap - (a0 + cnt - 1)) % p.cap;  // slot of row 0
     const __half* kb = p.kc + (size_t)g * p.cap * D;
     const __half* vb = p.vc + (size_t)g * p.cap * D;
+    // Thread t takes 16-byte piece t % 64 (0..31 of the key, 32..63 of the value) of rows t / 64, t / 64 + 4, ...
+    const uint32_t j = (uint32_t)tid % 64, piece = (j & 31) * 8;
+    const __half* src = (j < 32 ? kb : vb) + piece;
+    __half* dst = (j < 32 ? &sm.k[0][0] : &sm.v[0][0]) + piece;
+    uint32_t slot = first + (uint32_t)tid / 64;
+    if (slot >= p.cap) slot -= p.cap;
 #pragma unroll 4
-    for (uint32_t i = (uint32_t)tid; i < TILE * 64; i += THREADS) {
-        const uint32_t r = i / 64, j = i % 64;  // row; 16-byte piece: 0..31 of the key, 32..63 of the value
-        if (r < loaded) {
-            uint32_t slot = first + r;
-            if (slot >= p.cap) slot -= p.cap;
-            if (j < 32) cp_async_16(&sm.k[r][j * 8], kb + (size_t)slot * D + j * 8);
-            else cp_async_16(&sm.v[r][(j - 32) * 8], vb + (size_t)slot * D + (j - 32) * 8);
-        } else if (j >= 32) {
-            *reinterpret_cast<uint4*>(&sm.v[r][(j - 32) * 8]) = make_uint4(0u, 0u, 0u, 0u);
-        }
+    for (uint32_t r = (uint32_t)tid / 64; r < TILE; r += THREADS / 64) {
+        if (r < loaded) cp_async_16(dst + r * ROW, src + (size_t)slot * D);
+        else if (j >= 32) *reinterpret_cast<uint4*>(dst + r * ROW) = make_uint4(0u, 0u, 0u, 0u);
+        slot += THREADS / 64;
+        if (slot >= p.cap) slot -= p.cap;
     }
 }
 

@@ -66,6 +66,7 @@ struct tb_decoder {
     // step buffers
     float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *y = nullptr, *g = nullptr, *logits = nullptr, *partial = nullptr;
     float* freq[2] = {nullptr, nullptr};
+    float* trig[2] = {nullptr, nullptr};  // cos/sin of every position for the two frequency sets: [context][256]
     uint32_t *count = nullptr, *state = nullptr, *trace = nullptr;
     unsigned long long* best = nullptr;
     uint32_t* words = nullptr;  // pinned host: [0], [1] the tokens the two graphs write; [2] staging for the token fed in
@@ -199,6 +200,7 @@ void layout(tb_decoder* d, char* base) {
     d->sample_count = reinterpret_cast<uint32_t*>(base + t.take(4));
     vec(d->partial, attend_partial_floats(c.heads, c.kv_heads, max_splits));
     vec(d->freq[0], c.head_dim / 2), vec(d->freq[1], c.head_dim / 2);
+    vec(d->trig[0], (size_t)d->settings.context * c.head_dim), vec(d->trig[1], (size_t)d->settings.context * c.head_dim);
     d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.kv_heads * 4));
     d->state = reinterpret_cast<uint32_t*>(base + t.take(8));
     d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
@@ -275,7 +277,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         TB_TRY(gemv(d, L.qkv, q));
 
         AttendParams a;
-        a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0];
+        a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0], a.trig = d->trig[L.global ? 1 : 0];
         a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = 1;
         a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
@@ -443,6 +445,7 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
         const std::vector<float> f = rope_freq(k ? cfg->theta_global : cfg->theta_sliding, cfg->head_dim, k ? cfg->fraction_global : 1.0f);
         e = cudaMemcpyAsync(d->freq[k], f.data(), f.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess && launch_rope_table(ctx, d->freq[k], d->settings.context, d->trig[k]) != OK) e = cudaErrorUnknown;
         if (e != cudaSuccess) {
             const int s = cuda_fail(e, "tb_decoder_open: rope tables");
             tb_decoder_close(d);

@@ -106,6 +106,8 @@ struct AttendParams {
     const float* q_norm = nullptr; // [256] or null (plain mode: no norms)
     const float* k_norm = nullptr;
     const float* freq = nullptr;   // [128] RoPE frequencies or null (no rotation)
+    const float* trig = nullptr;   // optional: [positions][256] = cos(pos * freq[0..127]) then sin(...), filled by launch_rope_table
+                                   // with the arithmetic the kernel would use; saves the kernel four sincosf per lane
     __half* kc = nullptr;          // [kv_heads][cap][256]
     __half* vc = nullptr;
     const uint32_t* pos = nullptr; // device word: position of the new token
@@ -185,6 +187,9 @@ int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, co
 // The reference's sampler with draws (sample.cu); cfg: 40 bytes of device memory in the reference's Sampling layout.
 int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const void* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
                        float* partial, uint32_t* count, uint32_t blocks, uint32_t* trace = nullptr, uint32_t trace_mask = 0);
+
+// cos/sin of every (position, frequency): table [positions][256] for AttendParams::trig.
+int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, float* table);
 
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>

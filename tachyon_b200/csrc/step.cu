@@ -474,7 +474,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
             const AttendParams& a = cur.a;
             const uint32_t items = a.kv_heads * a.splits, group = a.heads / a.kv_heads;
             if (threadIdx.x < attend::THREADS) {
-                const attend::Trig trig = attend::rope_trig(a.freq, pos, lane);
+                const attend::Trig trig = attend::rope_trig(a.freq, pos, lane, a.trig);
                 for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
                     const bool pre = item == blockIdx.x && flags[1] != 0;
                     attend::block_sync<true>();
