@@ -135,6 +135,25 @@ TB_API int tb_gemm_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* sc
 TB_API int tb_quant_q8(tb_context* ctx, const float* x, uint32_t n, int8_t* q, float* pairs);
 TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const int8_t* q, const float* pairs, float* y, uint32_t rows, uint32_t cols);
 /*
+ * The rest of the reference's small decode kernels, in its formats and with its arithmetic (the approximate instructions
+ * too: ex2.approx, rsqrt.approx):
+ *   tb_geglu_q8 = geglu_q8 (ptx/mod.rs:376-393): q, pairs <- Q8 of gelu_tanh(a[i]) * b[i]; n % 32 == 0.
+ *   tb_norm_q8  = norm_q8 (ptx/mod.rs:404-511): per chunk of `len` values (a multiple of 256 up to 6144): when y is not
+ *                 NULL, h_out <- (h + w1 * rmsnorm(y)) * scale; then, when q is not NULL, Q8 of w2 * rmsnorm(h') (of h'
+ *                 itself when w2 is NULL).  h is left alone; w1, w2 hold one chunk.
+ *   tb_embed_q4 = embed_q4 (ptx/mod.rs:531-598): out[r][i] = (nibble - 8) * scale_f16 * scale for row tokens[r] of the table.
+ * tb_launch is Stream::launch by kernel name (cuda/mod.rs:417-425): the names "quant_q8", "geglu_q8", "norm_q8",
+ * "embed_q4", "gemv_q4" and "sample" with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16 and sample.rs:21-27;
+ * args[i] points at argument i's value (a u64 device address, u32 or f32), as the driver's kernelParams do.  Grid and block
+ * are checked against the kernel's documented launch shape where it has a meaning here (chunks, rows and block counts
+ * are taken from the grid).  An unknown name is TB_NO_MODEL.
+ */
+TB_API int tb_geglu_q8(tb_context* ctx, const float* a, const float* b, uint32_t n, int8_t* q, float* pairs);
+TB_API int tb_norm_q8(tb_context* ctx, const float* h, float* h_out, const float* y, const float* w1, const float* w2, int8_t* q, float* pairs, uint32_t len,
+                      uint32_t chunks, float eps, float scale);
+TB_API int tb_embed_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const uint32_t* tokens, uint32_t rows, float* out, uint32_t cols, float scale);
+TB_API int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_bytes, void* const* args, size_t nargs);
+/*
  * The same Q4 weights, read as they are by this build's decode product: the activation (f16 or f32, device) is not
  * rounded to Q8 but split into the exact fixed-point planes tb_gemv_q8 uses, so y = sum_g d_g sum_k (n_k - 8) x_k to
  * f32 accuracy.  This is the product a decoder opened with TB_WEIGHTS_Q4 runs.  cols: 2048, 4096, 8192 or 16384.

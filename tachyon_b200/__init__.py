@@ -129,6 +129,23 @@ class Context:
         """tb_gemv_q4 (the reference's gemv_q4): Q4 weights x Q8 activations -> f32 y [rows]."""
         check(self.lib.tb_gemv_q4(self.handle, packed.ptr, scales.ptr, q.ptr, pairs.ptr, y.ptr, rows, cols))
 
+    def geglu_q8(self, a, b, n, q, pairs) -> None:
+        check(self.lib.tb_geglu_q8(self.handle, a.ptr, b.ptr, n, q.ptr, pairs.ptr))
+
+    def norm_q8(self, h, h_out, y, w1, w2, q, pairs, length, chunks, eps, scale) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_norm_q8(self.handle, h.ptr, p(h_out), p(y), p(w1), p(w2), p(q), p(pairs), length, chunks, eps, scale))
+
+    def embed_q4(self, packed, scales, tokens, rows, out, cols, scale) -> None:
+        check(self.lib.tb_embed_q4(self.handle, packed.ptr, scales.ptr, tokens.ptr, rows, out.ptr, cols, scale))
+
+    def launch(self, kernel: str, grid, block, shared_bytes, args) -> None:
+        """tb_launch: the reference's Stream::launch by kernel name; args: ("p", address) | ("u", int) | ("f", float)."""
+        slots = [C.c_uint64(v or 0) if k == "p" else C.c_uint32(v) if k == "u" else C.c_float(v) for k, v in args]
+        table = (C.c_void_p * len(slots))(*[C.addressof(s) for s in slots])
+        g, b = (C.c_uint32 * 3)(*grid), (C.c_uint32 * 3)(*block)
+        check(self.lib.tb_launch(self.handle, kernel.encode(), g, b, shared_bytes, table, len(slots)))
+
     def gemv_q4x(self, packed: DevBuf, scales: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, rows: int, cols: int) -> None:
         """tb_gemv_q4x: Q4 weights x an f16/f32 activation that is not rounded to Q8 -> f32 y [rows]."""
         check(self.lib.tb_gemv_q4x(self.handle, packed.ptr, scales.ptr, x.ptr, x_dtype, y.ptr, rows, cols))

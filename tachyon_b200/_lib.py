@@ -67,6 +67,10 @@ SIGNATURES = {
     "tb_gemv_q8": (i32, [vp, vp, vp, vp, i32, vp, i32, u32, u32]),
     "tb_quant_q8": (i32, [vp, vp, u32, vp, vp]),
     "tb_gemv_q4": (i32, [vp, vp, vp, vp, vp, vp, u32, u32]),
+    "tb_geglu_q8": (i32, [vp, vp, vp, u32, vp, vp]),
+    "tb_norm_q8": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, f32, f32]),
+    "tb_embed_q4": (i32, [vp, vp, vp, vp, u32, vp, u32, f32]),
+    "tb_launch": (i32, [vp, cp, vp, vp, u32, vp, sz]),
     "tb_gemv_q4x": (i32, [vp, vp, vp, vp, i32, vp, u32, u32]),
     "tb_sample": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, vp, u32]),
     "tb_gemv_q8_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, f32, f32, vp, vp, u32, u32, i32]),

@@ -202,6 +202,70 @@ int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, c
     return launch_gemv_q4(ctx, packed, scales, q, pairs, y, rows, cols);
 }
 
+int tb_geglu_q8(tb_context* ctx, const float* a, const float* b, uint32_t n, int8_t* q, float* pairs) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_geglu_q8(ctx, a, b, q, pairs, n);
+}
+
+int tb_norm_q8(tb_context* ctx, const float* h, float* h_out, const float* y, const float* w1, const float* w2, int8_t* q, float* pairs, uint32_t len,
+               uint32_t chunks, float eps, float scale) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_norm_q8(ctx, h, h_out, y, w1, w2, q, pairs, len, chunks, eps, scale);
+}
+
+int tb_embed_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const uint32_t* tokens, uint32_t rows, float* out, uint32_t cols, float scale) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_embed_q4_rows(ctx, packed, scales, tokens, rows, out, cols, scale);
+}
+
+// Stream::launch by kernel name (cuda/mod.rs:417-425, ptx/mod.rs:7-41): args[i] points at argument i's value, as the
+// reference's `arg(&x)` and the driver's kernelParams do.
+int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_bytes, void* const* args, size_t nargs) {
+    if (!ctx || !kernel || !grid || !block || (nargs && !args)) return fail(OUT_OF_RANGE, "tb_launch: null argument");
+    const std::string name(kernel);
+    auto ptr = [&](size_t i) { return reinterpret_cast<void*>(*static_cast<const uintptr_t*>(args[i])); };
+    auto u32 = [&](size_t i) { return *static_cast<const uint32_t*>(args[i]); };
+    auto f32 = [&](size_t i) { return *static_cast<const float*>(args[i]); };
+    auto shape = [&](size_t want, uint32_t threads) -> int {
+        if (nargs != want) return fail(OUT_OF_RANGE, "tb_launch: " + name + " takes " + std::to_string(want) + " arguments");
+        if (block[0] != threads || block[1] != 1 || block[2] != 1) return fail(OUT_OF_RANGE, "tb_launch: " + name + " runs blocks of " + std::to_string(threads));
+        if (shared_bytes != 0) return fail(OUT_OF_RANGE, "tb_launch: " + name + " takes no dynamic shared memory");
+        return OK;
+    };
+    for (size_t i = 0; i < nargs; i++)
+        if (!args[i]) return fail(OUT_OF_RANGE, "tb_launch: null argument slot");
+    if (name == "quant_q8") {  // x, q, s, len
+        TB_TRY(shape(4, 256));
+        return launch_quant_q8(ctx, static_cast<const float*>(ptr(0)), static_cast<int8_t*>(ptr(1)), static_cast<float*>(ptr(2)), u32(3));
+    }
+    if (name == "geglu_q8") {  // a, b, q, s, len
+        TB_TRY(shape(5, 256));
+        return launch_geglu_q8(ctx, static_cast<const float*>(ptr(0)), static_cast<const float*>(ptr(1)), static_cast<int8_t*>(ptr(2)), static_cast<float*>(ptr(3)), u32(4));
+    }
+    if (name == "norm_q8") {  // h, h_out, y, w1, w2, q, s, len, eps, scale; grid (len / 256, chunks)
+        TB_TRY(shape(10, 256));
+        if (grid[0] != u32(7) / 256) return fail(OUT_OF_RANGE, "tb_launch: norm_q8 runs len / 256 blocks per chunk");
+        return launch_norm_q8(ctx, static_cast<const float*>(ptr(0)), static_cast<float*>(ptr(1)), static_cast<const float*>(ptr(2)), static_cast<const float*>(ptr(3)),
+                              static_cast<const float*>(ptr(4)), static_cast<int8_t*>(ptr(5)), static_cast<float*>(ptr(6)), u32(7), grid[1], f32(8), f32(9));
+    }
+    if (name == "embed_q4") {  // packed, scales, token, out, cols, scale; grid (cols / 256, rows)
+        TB_TRY(shape(6, 256));
+        return launch_embed_q4_rows(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const uint32_t*>(ptr(2)), grid[1],
+                                    static_cast<float*>(ptr(3)), u32(4), f32(5));
+    }
+    if (name == "gemv_q4") {  // w, ws, q, s, y, rows, cols; this build chooses its own grid
+        if (nargs != 7) return fail(OUT_OF_RANGE, "tb_launch: gemv_q4 takes 7 arguments");
+        return launch_gemv_q4(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const int8_t*>(ptr(2)),
+                              static_cast<const float*>(ptr(3)), static_cast<float*>(ptr(4)), u32(5), u32(6));
+    }
+    if (name == "sample") {  // logits, work, vocab, cfg, state, seen, out, partial, count; grid[0] blocks of 1024
+        TB_TRY(shape(9, 1024));
+        return launch_sample_draw(ctx, static_cast<const float*>(ptr(0)), static_cast<float*>(ptr(1)), u32(2), ptr(3), static_cast<uint32_t*>(ptr(4)),
+                                  static_cast<uint32_t*>(ptr(5)), static_cast<uint32_t*>(ptr(6)), static_cast<float*>(ptr(7)), static_cast<uint32_t*>(ptr(8)), grid[0]);
+    }
+    return fail(NO_MODEL, "tb_launch: no kernel named " + name);
+}
+
 int tb_gemv_q4x(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const void* x, int x_dtype, float* y, uint32_t rows, uint32_t cols) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     if (!dtype_ok(x_dtype)) return fail(OUT_OF_RANGE, "tb_gemv_q4x: unknown dtype");

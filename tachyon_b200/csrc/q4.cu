@@ -2,6 +2,9 @@
 // times Q8 activations (i8 codes and [s, s * sum q] per block of 32, quant.rs:93-130), f32 out.
 //
 //   quant_q8_kernel  = quant_q8   (ptx/mod.rs:191-212, 393-399)
+//   geglu_q8_kernel  = geglu_q8   (ptx/mod.rs:376-393): gelu(a) * b in its tanh form, then Q8
+//   norm_q8_kernel   = norm_q8    (ptx/mod.rs:404-511): residual step, RMS norms, Q8 of the next input
+//   embed_q4_rows    = embed_q4   (ptx/mod.rs:531-598): rows of a Q4 table, one per token
 //   gemv_q4_kernel   = gemv_q4    (ptx/gemv.rs:156-195)
 //
 // Both follow the reference kernels' arithmetic operation by operation, all of it IEEE f32 with round-to-nearest
@@ -52,6 +55,136 @@ __global__ void __launch_bounds__(256) quant_q8_kernel(const float* __restrict__
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     if ((i & 31u) == 0) s[i >> 5] = make_float2(d, __fmul_rn(static_cast<float>(sum), d));
+}
+
+// Value x of element i -> Q8 (ptx/mod.rs:191-212): every thread of the warp calls this with the warp's 32 consecutive values.
+__device__ __forceinline__ void store_q8(float x, uint32_t i, int8_t* q, float2* s) {
+    const float amax = warp_max(fabsf(x));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    const int code = __float2int_rn(__fmul_rn(x, inv));
+    q[i] = static_cast<int8_t>(code);
+    int sum = code;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((i & 31u) == 0) s[i >> 5] = make_float2(d, __fmul_rn(static_cast<float>(sum), d));
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+    float y;
+    asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ptx/mod.rs:376-393: x / (1 + e^(-2u)) * b, u = sqrt(2/pi) (x + 0.044715 x^3), operation by operation.
+__global__ void __launch_bounds__(256) geglu_q8_kernel(const float* __restrict__ a, const float* __restrict__ b, int8_t* __restrict__ q, float2* __restrict__ s,
+                                                       uint32_t n) {
+    pdl_wait();
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float x = a[i];
+    float t = __fmul_rn(x, x);
+    t = __fmaf_rn(t, 0.044714998453855514526f, 1.0f);          // 0f3D372713
+    t = __fmul_rn(t, x);
+    t = __fmul_rn(t, -2.3022081851959228516f);                 // 0fC0135761 = -2 sqrt(2/pi) log2(e)
+    t = __fadd_rn(ex2_approx(t), 1.0f);
+    x = __fmul_rn(__fdiv_rn(x, t), b[i]);
+    store_q8(x, i, q, s);
+}
+
+// Sums of up to four values over a block of eight warps, in every thread, in the order of the reference's block()
+// (ptx/mod.rs:153-170): warp butterflies, one slot per warp, lanes 0..7 read the slots, butterflies again.
+__device__ __forceinline__ void block_sums4(float (&v)[4], float* red) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v[k] = __fadd_rn(v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+    if (lane == 0)
+#pragma unroll
+        for (int k = 0; k < 4; k++) red[32 * k + warp] = v[k];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; k++) v[k] = lane < 8 ? red[32 * k + lane] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v[k] = __fadd_rn(v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+    __syncthreads();
+}
+
+// ptx/mod.rs:404-511.  Grid (len / 256, chunks) x 256 threads; every block reads its whole chunk (thread t takes values
+// t, t + 256, ...: up to 24), reduces sum y^2, sum h^2, sum h a, sum a^2 (a = w1 y) at once, and writes its own slice
+// of the new h and of the Q8 output.
+constexpr int NORM_PER_THREAD = 24;
+__global__ void __launch_bounds__(256) norm_q8_kernel(const float* __restrict__ h, float* h_out, const float* __restrict__ y, const float* __restrict__ w1,
+                                                      const float* __restrict__ w2, int8_t* q, float2* s, uint32_t len, float eps, float scale) {
+    __shared__ float red[128];
+    pdl_wait();
+    const uint32_t th = threadIdx.x, slice = blockIdx.x, base = blockIdx.y * len, own = slice * 256 + th;
+    const float n = static_cast<float>(len);
+    float hv[NORM_PER_THREAD], yv[NORM_PER_THREAD], av[NORM_PER_THREAD];
+#pragma unroll
+    for (int k = 0; k < NORM_PER_THREAD; k++) {
+        const uint32_t i = th + 256 * k;
+        const bool in = i < len;
+        hv[k] = in ? h[base + i] : 0.0f;
+        yv[k] = (in && y != nullptr) ? y[base + i] : 0.0f;
+        av[k] = (in && y != nullptr) ? w1[i] : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < NORM_PER_THREAD; k++) av[k] = __fmul_rn(av[k], yv[k]);
+    float v[4] = {__fmul_rn(yv[0], yv[0]), __fmul_rn(hv[0], hv[0]), __fmul_rn(hv[0], av[0]), __fmul_rn(av[0], av[0])};
+#pragma unroll
+    for (int k = 1; k < NORM_PER_THREAD; k++) v[0] = __fmaf_rn(yv[k], yv[k], v[0]);
+#pragma unroll
+    for (int k = 1; k < NORM_PER_THREAD; k++) v[1] = __fmaf_rn(hv[k], hv[k], v[1]);
+#pragma unroll
+    for (int k = 1; k < NORM_PER_THREAD; k++) v[2] = __fmaf_rn(hv[k], av[k], v[2]);
+#pragma unroll
+    for (int k = 1; k < NORM_PER_THREAD; k++) v[3] = __fmaf_rn(av[k], av[k], v[3]);
+    block_sums4(v, red);
+    float ss = v[0], sh = v[1], su = v[2], uu = v[3];
+    float r = rsqrt_approx(__fadd_rn(__fdiv_rn(ss, n), eps));
+    if (y != nullptr) {
+#pragma unroll
+        for (int k = 0; k < NORM_PER_THREAD; k++) {
+            hv[k] = __fmul_rn(__fmaf_rn(av[k], r, hv[k]), scale);
+            if (slice == (uint32_t)k && th + 256 * k < len) h_out[base + th + 256 * k] = hv[k];
+        }
+        su = __fadd_rn(su, su);
+        su = __fmaf_rn(r, uu, su);
+        sh = __fmaf_rn(r, su, sh);
+        sh = __fmul_rn(__fmul_rn(sh, scale), scale);
+    }
+    if (q == nullptr) return;
+    r = rsqrt_approx(__fadd_rn(__fdiv_rn(sh, n), eps));
+    if (w2 == nullptr) r = 1.0f;
+    float x = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NORM_PER_THREAD; k++)
+        if (slice == (uint32_t)k) x = hv[k];
+    x = __fmul_rn(x, r);
+    x = __fmul_rn(x, w2 != nullptr ? w2[own] : 1.0f);
+    store_q8(x, base + own, q, s);
+}
+
+// ptx/mod.rs:531-598: thread i decodes weight i of row token[blockIdx.y] into row blockIdx.y of the output.
+__global__ void __launch_bounds__(256) embed_q4_rows(const uint8_t* __restrict__ w, const __half* __restrict__ s, const uint32_t* __restrict__ token, float* out,
+                                                     uint32_t cols, float scale) {
+    pdl_wait();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= cols) return;
+    const uint32_t tok = token[blockIdx.y], g = i >> 6, k = i & 63;
+    const float d = __half2float(s[(size_t)tok * (cols >> 6) + g]);
+    const uint32_t byte = w[(size_t)tok * (cols >> 1) + (g << 5) + ((k >> 3) << 2) + (k & 3)];
+    const int nib = static_cast<int>((byte >> (((k >> 2) & 1) << 2)) & 15u) - 8;
+    out[(size_t)blockIdx.y * cols + i] = __fmul_rn(__fmul_rn(static_cast<float>(nib), d), scale);
 }
 
 struct Q4Params {
@@ -205,6 +338,33 @@ int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32
     if (n == 0 || n % 32 != 0) return fail(OUT_OF_RANGE, "quant_q8: the length must be a positive multiple of 32");
     if (reinterpret_cast<uintptr_t>(s) & 7) return fail(OUT_OF_RANGE, "quant_q8: the pairs must be 8-byte aligned");
     TB_CUDA(launch_kernel(ctx, quant_q8_kernel, dim3((n + 255) / 256), dim3(256), 0, true, x, q, reinterpret_cast<float2*>(s), n));
+    return OK;
+}
+
+int launch_geglu_q8(tb_context* ctx, const float* a, const float* b, int8_t* q, float* s, uint32_t n) {
+    if (!a || !b || !q || !s) return fail(OUT_OF_RANGE, "geglu_q8: null argument");
+    if (n == 0 || n % 32 != 0) return fail(OUT_OF_RANGE, "geglu_q8: the length must be a positive multiple of 32");
+    if (reinterpret_cast<uintptr_t>(s) & 7) return fail(OUT_OF_RANGE, "geglu_q8: the pairs must be 8-byte aligned");
+    TB_CUDA(launch_kernel(ctx, geglu_q8_kernel, dim3((n + 255) / 256), dim3(256), 0, true, a, b, q, reinterpret_cast<float2*>(s), n));
+    return OK;
+}
+
+int launch_norm_q8(tb_context* ctx, const float* h, float* h_out, const float* y, const float* w1, const float* w2, int8_t* q, float* s, uint32_t len,
+                   uint32_t chunks, float eps, float scale) {
+    if (!h || chunks == 0) return fail(OUT_OF_RANGE, "norm_q8: null or empty input");
+    if (len == 0 || len % 256 != 0 || len > 256 * NORM_PER_THREAD) return fail(OUT_OF_RANGE, "norm_q8: the length must be a multiple of 256 up to 6144");
+    if (y && (!w1 || !h_out)) return fail(OUT_OF_RANGE, "norm_q8: a residual needs w1 and h_out");
+    if ((q == nullptr) != (s == nullptr) || (reinterpret_cast<uintptr_t>(s) & 7)) return fail(OUT_OF_RANGE, "norm_q8: q and s go together; s 8-byte aligned");
+    TB_CUDA(launch_kernel(ctx, norm_q8_kernel, dim3(len / 256, chunks), dim3(256), 0, true, h, h_out, y, w1, w2, q, reinterpret_cast<float2*>(s), len, eps,
+                          scale));
+    return OK;
+}
+
+int launch_embed_q4_rows(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const uint32_t* tokens, uint32_t rows, float* out, uint32_t cols, float scale) {
+    if (!w || !scales || !tokens || !out || rows == 0) return fail(OUT_OF_RANGE, "embed_q4: null or empty argument");
+    if (cols == 0 || cols % 64 != 0) return fail(OUT_OF_RANGE, "embed_q4: columns must be a positive multiple of 64");
+    TB_CUDA(launch_kernel(ctx, embed_q4_rows, dim3((cols + 255) / 256, rows), dim3(256), 0, true, w, reinterpret_cast<const __half*>(scales), tokens, out, cols,
+                          scale));
     return OK;
 }
 
