@@ -143,7 +143,8 @@ TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* sc
  *                 itself when w2 is NULL).  h is left alone; w1, w2 hold one chunk.
  *   tb_embed_q4 = embed_q4 (ptx/mod.rs:531-598): out[r][i] = (nibble - 8) * scale_f16 * scale for row tokens[r] of the table.
  * tb_launch is Stream::launch by kernel name (cuda/mod.rs:417-425): the names "quant_q8", "geglu_q8", "norm_q8",
- * "embed_q4", "gemv_q4" and "sample" with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16 and sample.rs:21-27;
+ * "embed_q4", "gemv_q4", "sample", and "attend_256" / "attend_256_2" (one block per key-value head: group 1; Q8 out)
+ * with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16, sample.rs:21-27 and attend.rs:21-32;
  * args[i] points at argument i's value (a u64 device address, u32 or f32), as the driver's kernelParams do.  Grid and block
  * are checked against the kernel's documented launch shape where it has a meaning here (chunks, rows and block counts
  * are taken from the grid).  An unknown name is TB_NO_MODEL.

@@ -263,6 +263,22 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         return launch_sample_draw(ctx, static_cast<const float*>(ptr(0)), static_cast<float*>(ptr(1)), u32(2), ptr(3), static_cast<uint32_t*>(ptr(4)),
                                   static_cast<uint32_t*>(ptr(5)), static_cast<uint32_t*>(ptr(6)), static_cast<float*>(ptr(7)), static_cast<uint32_t*>(ptr(8)), grid[0]);
     }
+    if (name == "attend_256" || name == "attend_256_2") {
+        // attend.rs:21-32: qkv, qn, kn, freq, k_cache, v_cache, pos, cap, window, fresh, group, partial, count, Q8 out (q, s);
+        // grid (H / per, S) blocks of 256, per = 4 query heads a block (2 for attend_256_2), `group` blocks per key-value head.
+        TB_TRY(shape(15, 256));
+        const uint32_t per = name == "attend_256" ? 4u : 2u, group = u32(10);
+        if (group != 1) return fail(UNSUPPORTED, "tb_launch: " + name + " with more than one block per key-value head (8 query heads to one) has no kernel here");
+        AttendParams a;
+        a.qkv = static_cast<const float*>(ptr(0)), a.q_norm = static_cast<const float*>(ptr(1)), a.k_norm = static_cast<const float*>(ptr(2));
+        a.freq = static_cast<const float*>(ptr(3)), a.kc = static_cast<__half*>(ptr(4)), a.vc = static_cast<__half*>(ptr(5));
+        a.pos = static_cast<const uint32_t*>(ptr(6)), a.cap = u32(7), a.window = u32(8), a.fresh = u32(9);
+        a.kv_heads = grid[0], a.heads = per * grid[0], a.splits = grid[1], a.scale = 1.0f, a.eps = 1e-6f;
+        a.partial = static_cast<float*>(ptr(11)), a.count = static_cast<uint32_t*>(ptr(12));
+        a.out = ptr(13), a.out_pairs = static_cast<float*>(ptr(14)), a.out_f16 = 2;
+        if (!a.q_norm || !a.k_norm || !a.out || !a.out_pairs) return fail(OUT_OF_RANGE, "tb_launch: " + name + " needs its norm weights and its Q8 output");
+        return launch_attend(ctx, a);
+    }
     return fail(NO_MODEL, "tb_launch: no kernel named " + name);
 }
 

@@ -380,7 +380,8 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
         for (int h = 0; h < G; h++) {
             const float o = out[h] / sm.lrun[h];
             const size_t at = (size_t)(g * G + h) * D + tid;
-            if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(o);
+            if (p.out_f16 == 2) q8_store(o, (uint32_t)at, static_cast<int8_t*>(p.out), reinterpret_cast<float2*>(p.out_pairs));
+            else if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(o);
             else static_cast<float*>(p.out)[at] = o;
         }
         return;
@@ -436,7 +437,8 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
     for (int h = 0; h < G; h++) {
         const float r = o[h] / sm.lrun[h];
         const size_t at = (size_t)(g * G + h) * D + tid;
-        if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(r);
+        if (p.out_f16 == 2) q8_store(r, (uint32_t)at, static_cast<int8_t*>(p.out), reinterpret_cast<float2*>(p.out_pairs));
+        else if (p.out_f16) static_cast<__half*>(p.out)[at] = __float2half_rn(r);
         else static_cast<float*>(p.out)[at] = r;
     }
     if (tid == 0) p.count[g] = 0;

@@ -167,6 +167,22 @@ __device__ __forceinline__ uint32_t ld_cg_u(const uint32_t* p) { return __ldcg(p
 
 // tanh-form GELU, as the reference's decoder computes it (crates/tachyon/src/ptx/mod.rs:376-390):
 // x / (1 + 2^(-2*sqrt(2/pi)*log2(e)*(x + 0.044715 x^3))).
+// Value x of element i -> the reference's Q8 (crates/tachyon/src/ptx/mod.rs:191-212): the 32 lanes of a warp hold 32
+// consecutive values, one block; scale amax / 127, codes rounded to nearest even, the pair [s, s * sum q] from lane 0.
+__device__ __forceinline__ void q8_store(float x, uint32_t i, int8_t* q, float2* s) {
+    float amax = fabsf(x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    const int code = __float2int_rn(__fmul_rn(x, inv));
+    q[i] = static_cast<int8_t>(code);
+    int sum = code;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((i & 31u) == 0) s[i >> 5] = make_float2(d, __fmul_rn(static_cast<float>(sum), d));
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float u = x + 0.044715f * x * x * x;
     return x / (1.0f + exp2f(-2.0f * 0.7978845608028654f * 1.4426950408889634f * u));

@@ -117,7 +117,8 @@ struct AttendParams {
     uint32_t* count = nullptr;     // kv_heads words, zero between launches
     uint32_t splits = 1;           // blocks per kv head (upper bound on the split actually used)
     void* out = nullptr;           // [heads*256] f32 or f16
-    int out_f16 = 0;
+    int out_f16 = 0;               // 0: f32, 1: f16, 2: the reference's Q8 (out = i8 codes, out_pairs = [s, s * sum q] per 32)
+    float* out_pairs = nullptr;
     Prefetch pf;                   // optional hint for the L2
     unsigned long long* stamps = nullptr;  // optional timeline, as in GemvParams (the third stamp stays zero)
     uint32_t defer = 0;            // != 0: every split only stores its partial; the product that follows merges them (X_ATTN)
