@@ -26,7 +26,9 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;  // MMA shape M128 N256; BK halves = one 128-byte swizzle row
 constexpr int stages(int mt) { return mt == 2 ? 3 : 4; }
-constexpr int THREADS = 64 + 256;  // TMA warp, MMA warp, eight dequantising / epilogue warps
+constexpr int DW = 16;                  // dequantising / epilogue warps: with two per scheduler the loads' latency showed
+constexpr int DT = DW * 32, PIECES = 1024 / DT;  // a weight tile is 1024 pieces of 16 codes
+constexpr int THREADS = 64 + DT;        // TMA warp, MMA warp, the dequantising / epilogue warps
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;  // per 128-row sub-tile of activations, per weight tile
 constexpr int smem_bytes(int mt) { return 1024 + stages(mt) * (mt * A_BYTES + B_BYTES) + 256; }
 
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
     const uint32_t m0 = blockIdx.x * (MT * BM), n0 = blockIdx.y * BN, nk = g.K / BK;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 9), mbar_init(&empty[i], 1);
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], DW + 1), mbar_init(&empty[i], 1);
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,17 +175,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             mma_commit(acc_full);  // arrives when every MMA above has finished (also after an early exit)
         }
     } else {
-        // Weight tile: 256 rows x 64 codes = 1024 pieces of 16 codes; thread j takes pieces j, j + 256, j + 512, j + 768
+        // Weight tile: 256 rows x 64 codes = 1024 pieces of 16 codes; thread j takes pieces j, j + 512 (with sixteen warps)
         // (piece p: row p / 4, quarter p % 4), so a warp's load covers eight rows' whole 64-byte segments instead of
         // thirty-two separate lines.  A row's scales for four tiles come in one 16-byte load every fourth tile.  The
         // next tile's codes are fetched before this one's are stored.
         const int j = threadIdx.x - 64, qtr = j & 3;
-        uint4 c[4];
-        uint4 sc8[4];  // per piece: the row's eight scales covering tiles kt & ~3 ... + 3
+        uint4 c[PIECES];
+        uint4 sc8[PIECES];  // per piece: the row's eight scales covering tiles kt & ~3 ... + 3
         auto fetch = [&](uint32_t kt) {
 #pragma unroll
-            for (int it = 0; it < 4; it++) {
-                const uint32_t row = it * 64 + (j >> 2), n = n0 + row;
+            for (int it = 0; it < PIECES; it++) {
+                const uint32_t row = it * (DT / 4) + (j >> 2), n = n0 + row;
                 const bool live = n < g.N;
                 if constexpr (WB == 4) {
                     // A piece is 16 weights = 8 bytes; a row's tile 32 bytes; its one scale per tile comes eight tiles at a time.
@@ -223,9 +225,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
         if (nk > 0) fetch(0);
         for (uint32_t kt = 0; kt < nk; kt++) {
             const uint32_t s = kt % STAGES;
-            uint32_t v[4][8];  // per piece 16 halves
+            uint32_t v[PIECES][8];  // per piece 16 halves
 #pragma unroll
-            for (int it = 0; it < 4; it++) {
+            for (int it = 0; it < PIECES; it++) {
                 // scale of this piece's group of 32: tile kt's two scales are halves 2*(kt&3) and 2*(kt&3)+1
                 const uint32_t words[4] = {sc8[it].x, sc8[it].y, sc8[it].z, sc8[it].w};
                 if constexpr (WB == 4) {
@@ -251,8 +253,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                 ok = false;
             }
 #pragma unroll
-            for (int it = 0; it < 4; it++) {
-                const uint32_t row = it * 64 + (j >> 2);
+            for (int it = 0; it < PIECES; it++) {
+                const uint32_t row = it * (DT / 4) + (j >> 2);
                 uint8_t* base = Bs + s * B_BYTES + row * 128;
                 *reinterpret_cast<uint4*>(base + (((2 * qtr) ^ (row & 7)) << 4)) = make_uint4(v[it][0], v[it][1], v[it][2], v[it][3]);
                 *reinterpret_cast<uint4*>(base + (((2 * qtr + 1) ^ (row & 7)) << 4)) = make_uint4(v[it][4], v[it][5], v[it][6], v[it][7]);
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
         // Two warps share each quarter of the accumulator's lanes and take alternate column blocks.
         const uint32_t q = warp & 3, rrow = 32 * q + lane;
 #pragma unroll 1
-        for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += 2) {
+        for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += DW / 4) {
             const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
             const uint32_t m = m0 + mt * BM + rrow;
             uint32_t r[32];
