@@ -256,6 +256,9 @@ typedef struct tb_config {
     float theta_sliding, theta_global, fraction_global; /* Config::theta, Config::fraction */
     float eps, softcap;
     float attn_scale;       /* softmax scale; Gemma 4 uses 1 */
+    uint32_t shared;        /* Config::shared: the last `shared` layers project no keys or values and attend over the cache of the
+                               last earlier layer of their kind (Config::source, model/mod.rs:138-143); their qkv matrix holds
+                               the query rows only */
 } tb_config;
 
 /* model::Settings (decode.rs:64-76) plus what this build adds. */

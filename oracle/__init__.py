@@ -44,7 +44,7 @@ class Layer(C.Structure):
     _fields_ = (
         [(n, C.c_void_p) for n in ("qkv", "o", "gate_up", "down", "qkv_s", "o_s", "gate_up_s", "down_s")]
         + [(n, C.c_void_p) for n in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")]
-        + [("layer_scalar", C.c_float), ("global_", C.c_int32), ("kc", C.c_void_p), ("vc", C.c_void_p), ("cap", C.c_int32)]
+        + [("layer_scalar", C.c_float), ("global_", C.c_int32), ("kc", C.c_void_p), ("vc", C.c_void_p), ("cap", C.c_int32), ("shared", C.c_int32)]
     )
 
 

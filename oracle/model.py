@@ -44,7 +44,13 @@ class OracleModel:
         for i in range(L):
             b = 32 * i
             ly = self.layers[i]
-            qkv, qkv_s = mat(f"{i}.qkv", b, nq + 2 * nkv, H)
+            is_global = bool(cfg.global_every) and (i + 1) % cfg.global_every == 0
+            # Config::source (model/mod.rs:138-143): the last `shared` layers reuse the cache of the last earlier layer of their kind
+            first_shared = L - getattr(cfg, "shared", 0)
+            source = i
+            if i >= first_shared:
+                source = next(j for j in range(first_shared - 1, -1, -1) if (bool(cfg.global_every) and (j + 1) % cfg.global_every == 0) == is_global)
+            qkv, qkv_s = mat(f"{i}.qkv", b, nq + (2 * nkv if source == i else 0), H)
             o, o_s = mat(f"{i}.o", b + 2, H, nq)
             gu, gu_s = mat(f"{i}.gate_up", b + 4, 2 * F, H)
             dn, dn_s = mat(f"{i}.down", b + 6, H, F)
@@ -52,15 +58,18 @@ class OracleModel:
                   vec(f"{i}.input_layernorm", b + 10, H, 0.5, 1.5), vec(f"{i}.post_attention_layernorm", b + 11, H, 0.5, 1.5),
                   vec(f"{i}.pre_feedforward_layernorm", b + 12, H, 0.5, 1.5), vec(f"{i}.post_feedforward_layernorm", b + 13, H, 0.5, 1.5)]
             scalar = vec(f"{i}.layer_scalar", b + 14, 1, 0.95, 1.0)
-            is_global = bool(cfg.global_every) and (i + 1) % cfg.global_every == 0
             cap = context if is_global else cfg.window + chunk
-            kc, vc = np.zeros((cfg.kv_heads, cap, D), np.uint16), np.zeros((cfg.kv_heads, cap, D), np.uint16)
+            if source == i:
+                kc, vc = np.zeros((cfg.kv_heads, cap, D), np.uint16), np.zeros((cfg.kv_heads, cap, D), np.uint16)
+            else:
+                kc, vc = self.caches[source]
             self.caches.append((kc, vc))
             for name, a in zip(("qkv", "o", "gate_up", "down", "qkv_s", "o_s", "gate_up_s", "down_s"), (qkv, o, gu, dn, qkv_s, o_s, gu_s, dn_s)):
                 setattr(ly, name, a.ctypes.data)
             for name, a in zip(("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln"), vs):
                 setattr(ly, name, a.ctypes.data)
             ly.layer_scalar, ly.global_, ly.kc, ly.vc, ly.cap = float(scalar[0]), int(is_global), kc.ctypes.data, vc.ctypes.data, cap
+            ly.shared = int(source != i)
         oc = oracle.Config(hidden=H, ffn=F, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=D, vocab=cfg.vocab, layers=L, window=cfg.window,
                            context=context, theta_sliding=cfg.theta_sliding, theta_global=cfg.theta_global, fraction_global=cfg.fraction_global,
                            eps=cfg.eps, softcap=cfg.softcap, attn_scale=cfg.attn_scale, embed_scale=bf16_round(float(np.sqrt(np.float32(H)))),
@@ -71,6 +80,8 @@ class OracleModel:
     def fill_cache(self, seed: int):
         """The same seeded N(0,1) cache contents tb_decoder_fill_cache writes."""
         for i, (kc, vc) in enumerate(self.caches):
+            if self.layers[i].shared:
+                continue  # the source layer's arrays
             kc[...] = oracle.fill_gauss_f16(seed, (1 << 21) + 2 * i, kc.size, 1.0).reshape(kc.shape)
             vc[...] = oracle.fill_gauss_f16(seed, (1 << 21) + 2 * i + 1, vc.size, 1.0).reshape(vc.shape)
 

@@ -591,6 +591,7 @@ typedef struct {
     int32_t global;
     uint16_t *kc, *vc;                                /* f16 caches [kv_heads][cap][head_dim]; cap = context (global) or ring */
     int32_t cap;
+    int32_t shared;                                   /* != 0: no key/value rows in qkv; kc, vc are another layer's (tiny.rs: Config::source) */
 } tbo_layer;
 
 typedef struct {
@@ -667,14 +668,14 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
         tbo_layer *L = &m->layers[li];
         tbo_rope_freq(L->global ? c->theta_global : c->theta_sliding, (int)D, L->global ? c->fraction_global : 1.0f, freq);
         rms_f32(x, L->input_ln, H, c->eps, h);                                  /* tiny.rs:278 */
-        matvec(c, L->qkv, L->qkv_s, h, nq + 2 * nkv, H, qkv);                    /* :279, 286-287 (fused q, k, v) */
+        matvec(c, L->qkv, L->qkv_s, h, nq + (L->shared ? 0 : 2 * nkv), H, qkv);  /* :279, 286-287 (fused q, k, v) */
         for (int hd = 0; hd < c->heads; hd++) {                                 /* :280-283 */
             rms_f32(qkv + (size_t)hd * D, L->q_norm, D, c->eps, tmp);
             rotate_f32(tmp, D, freq, pos);
             memcpy(qkv + (size_t)hd * D, tmp, D * 4);
         }
         uint32_t cap = (uint32_t)L->cap, slot = pos % cap;
-        for (int g = 0; g < c->kv_heads; g++) {                                 /* :288-289: k-norm + RoPE, v-norm without weights */
+        for (int g = 0; g < (L->shared ? 0 : c->kv_heads); g++) {               /* :288-289: k-norm + RoPE, v-norm without weights */
             rms_f32(qkv + nq + (size_t)g * D, L->k_norm, D, c->eps, tmp);
             rotate_f32(tmp, D, freq, pos);
             for (size_t i = 0; i < D; i++) L->kc[((size_t)g * cap + slot) * D + i] = tbo_f16_bits(tmp[i]);

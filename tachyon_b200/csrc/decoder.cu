@@ -45,6 +45,7 @@ struct Layer {
     float *q_norm = nullptr, *k_norm = nullptr, *input_ln = nullptr, *post_attn = nullptr, *pre_ffn = nullptr, *post_ffn = nullptr;
     float layer_scalar = 1.0f;
     bool global = false;
+    int source = -1;  // >= 0: this layer projects no keys or values and attends over that layer's cache
     __half *kc = nullptr, *vc = nullptr;
     uint32_t cap = 0, window = 0, splits = 1;
 };
@@ -133,6 +134,7 @@ int validate(const tb_config& c, const tb_settings& s) {
     if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
     if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
     if (s.context == 0 || s.context > TRACE) return fail(OUT_OF_RANGE, "decoder: context must be in 1..65536");
+    if (c.shared >= c.layers) return fail(OUT_OF_RANGE, "decoder: at least one layer must own its cache");
     if (s.weight_bits != 0 && s.weight_bits != 8 && s.weight_bits != 4) return fail(OUT_OF_RANGE, "decoder: weights are 8 or 4 bits");
     if (s.weight_bits == 4) {
         const uint32_t qc = c.heads * c.head_dim;
@@ -168,7 +170,16 @@ void layout(tb_decoder* d, char* base) {
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
         L.global = d->global[i] != 0;
-        mat(L.qkv, nq(c) + 2 * nkv(c), c.hidden);
+        // Config::source (model/mod.rs:138-143): a shared layer reuses the last unshared layer of its kind.
+        L.source = -1;
+        const uint32_t first_shared = c.layers - c.shared;
+        if (i >= first_shared)
+            for (int j = (int)first_shared - 1; j >= 0; j--)
+                if ((d->global[j] != 0) == L.global) {
+                    L.source = j;
+                    break;
+                }
+        mat(L.qkv, nq(c) + (L.source < 0 ? 2 * nkv(c) : 0), c.hidden);
         mat(L.o, c.hidden, nq(c));
         mat(L.gate_up, 2 * c.ffn, c.hidden);
         mat(L.down, c.hidden, c.ffn);
@@ -178,8 +189,12 @@ void layout(tb_decoder* d, char* base) {
         L.window = L.global ? d->settings.context : c.window;
         L.cap = L.global ? d->settings.context : c.window + d->settings.chunk;
         const size_t cache = (size_t)c.kv_heads * L.cap * c.head_dim * 2;
-        L.kc = reinterpret_cast<__half*>(base + t.take(cache));
-        L.vc = reinterpret_cast<__half*>(base + t.take(cache));
+        if (L.source >= 0) {
+            L.kc = d->layers[L.source].kc, L.vc = d->layers[L.source].vc;
+        } else {
+            L.kc = reinterpret_cast<__half*>(base + t.take(cache));
+            L.vc = reinterpret_cast<__half*>(base + t.take(cache));
+        }
         // Blocks per key-value head: spans of about 32 positions (sliding) or 128 (global, two tiles), within the machine.
         static const uint32_t span_global = getenv("TACHYON_B200_SPAN_GLOBAL") ? (uint32_t)atoi(getenv("TACHYON_B200_SPAN_GLOBAL")) : 128u;
         static const uint32_t span_sliding = getenv("TACHYON_B200_SPAN_SLIDING") ? (uint32_t)atoi(getenv("TACHYON_B200_SPAN_SLIDING")) : 64u;
@@ -278,7 +293,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
 
         AttendParams a;
         a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0], a.trig = d->trig[L.global ? 1 : 0];
-        a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = 1;
+        a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = L.source < 0 ? 1 : 0;
         a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
         a.pf = hint(d, L.gate_up, 2, 0, PF);
@@ -553,6 +568,7 @@ int tb_decoder_fill_cache(tb_decoder* d, uint64_t seed, uint32_t positions) {
     const tb_config& c = d->cfg;
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
+        if (L.source >= 0) continue;  // a shared layer has no cache of its own
         // Position p lives in slot p % cap; filling whole caches covers every slot a window can reach.
         const size_t n = (size_t)c.kv_heads * L.cap * c.head_dim;
         TB_TRY(launch_fill_gauss_f16(d->ctx, seed, (1ull << 21) + 2ull * i, L.kc, n, 1.0f));
@@ -693,7 +709,7 @@ int tb_decoder_run(tb_decoder* d, uint32_t token, uint32_t steps, uint32_t* toke
 static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint32_t pos0) {
     const tb_config& c = d->cfg;
     tb_context* ctx = d->ctx;
-    const uint32_t H = c.hidden, NQ = nq(c), NQKV = nq(c) + 2 * nkv(c);
+    const uint32_t H = c.hidden, NQ = nq(c);
     TB_CUDA(cudaMemcpyAsync(d->pf_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
     TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h, d->embed.bits));
     for (uint32_t i = 0; i < c.layers; i++) {
@@ -704,9 +720,10 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
             const Layer& P = d->layers[i - 1];
             TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
         }
-        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, NQKV, H, d->pf_qkv, 0, L.qkv.bits));
-        TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads, c.kv_heads,
-                                  c.eps, c.attn_scale));
+        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, L.qkv.rows, H, d->pf_qkv, 0, L.qkv.bits));
+        // A shared layer has query rows only: nothing to append to the cache it reads.
+        TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads,
+                                  L.source < 0 ? c.kv_heads : 0, c.eps, c.attn_scale));
         if (i + 1 == c.layers) break;
         TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, c.kv_heads));
         TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, NQ, d->pf_y, 0, L.o.bits));

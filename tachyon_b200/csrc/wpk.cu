@@ -34,19 +34,22 @@ constexpr size_t HEADER = 48;      // wpk/mod.rs:40
 const uint64_t DTYPE_SIZE[6] = {4, 2, 2, 1, 1, 1};  // F32, F16, BF16, F8E4M3, I8, U8 (wpk/mod.rs:62-72)
 
 // CRC32C (Castagnoli, reflected 0x82F63B78), continuing from `crc`: wpk/mod.rs:105-123.
-uint32_t crc32c(uint32_t crc, const uint8_t* p, size_t n) {
-    static uint32_t table[8][256];
-    static bool ready = false;
-    if (!ready) {
+struct CrcTable {
+    uint32_t t[8][256];
+    CrcTable() {
         for (uint32_t i = 0; i < 256; i++) {
             uint32_t c = i;
             for (int k = 0; k < 8; k++) c = (c >> 1) ^ (0x82F63B78u & (0u - (c & 1u)));
-            table[0][i] = c;
+            t[0][i] = c;
         }
         for (uint32_t i = 0; i < 256; i++)
-            for (int t = 1; t < 8; t++) table[t][i] = (table[t - 1][i] >> 8) ^ table[0][table[t - 1][i] & 255u];
-        ready = true;
+            for (int k = 1; k < 8; k++) t[k][i] = (t[k - 1][i] >> 8) ^ t[0][t[k - 1][i] & 255u];
     }
+};
+
+uint32_t crc32c(uint32_t crc, const uint8_t* p, size_t n) {
+    static const CrcTable tables;  // built once, by whichever thread comes first
+    const uint32_t (*table)[256] = tables.t;
     uint32_t c = ~crc;
     while (n >= 8) {  // eight bytes a turn
         uint32_t lo, hi;

@@ -297,3 +297,39 @@ def test_decoder_draws_with_the_reference_sampler(models):
     dec.set_sampling()
     dec.reset()
     assert [int(t) for t in dec.run(3, 6)] == greedy
+
+
+def test_shared_key_value_layers_attend_over_their_source_layers_cache(ctx):
+    """Config::shared (model/mod.rs:64, 138-143): the last layers have query rows only and read the cache of the last
+    earlier layer of their kind; stepping, the chunked prefill and the Q4 format all follow the CPU forward."""
+    cfg = small_config(layers=6)
+    cfg.global_every, cfg.shared = 3, 3  # layers 3, 4 (sliding) share layer 1's cache, layer 5 (global) layer 2's
+    for bits in (8, 4):
+        dec = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True, weight_bits=bits)
+        dec.fill_random(SEED + bits)
+        dec.build()
+        ref = OracleModel(cfg, SEED + bits, context=64, chunk=8, weight_bits=bits)
+        assert ref.tensors["4.qkv.w"].shape[0] == cfg.heads * cfg.head_dim and ref.tensors["1.qkv.w"].shape[0] == (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim
+        token = 17
+        for pos in range(30):
+            want_token, want_logits, want_hidden = ref.step(token, pos)
+            got_token = dec.step(token)
+            order = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+            check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+            assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+            token = (pos * 7919 + 13) % cfg.vocab
+        prompt = [(i * 7919 + 13) % cfg.vocab for i in range(30)]
+        dec.reset()
+        for t in prompt[:-1]:
+            dec.step(t)
+        a, la = dec.step(prompt[-1]), dec.logits()
+        dec.reset()
+        dec.prefill(prompt[:-1])
+        b, lb = dec.step(prompt[-1]), dec.logits()
+        scale = np.abs(la).max()
+        assert np.abs(la - lb).max() <= 4e-3 * scale
+        dec.close()
+    with pytest.raises(tb.Error):
+        bad = small_config(layers=3)
+        bad.shared = 3
+        tb.Decoder(ctx, bad, context=64)
