@@ -356,6 +356,14 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
+    {
+        // TACHYON_B200_GEMM=2: the persistent schedule of gemm2.cu.
+        static const int which = [] {
+            const char* e = getenv("TACHYON_B200_GEMM");
+            return e ? atoi(e) : 1;
+        }();
+        if (which == 2 && gemm_persistent_supports(N, K, wbits)) return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits);
+    }
     EncodeTiled enc = encode_tiled();
     if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
     CUtensorMap map;

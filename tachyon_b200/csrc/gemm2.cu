@@ -1,0 +1,384 @@
+// The prefill / encoder product as a persistent kernel: D[M, N] = A[M, K] (f16) x W[N, K]^T with W quantised (int8 codes
+// and an f16 scale per 32, or the reference's Q4 nibbles and a scale per 64), f32 accumulation in tensor memory.
+// Stands in for the reference's gemm_q4 (crates/tachyon/src/ptx/gemm.rs:225-259) and gemm_q8* (ptx/encoder.rs:315-375);
+// same results as gemm.cu's kernel, different schedule, built on what measuring that kernel showed: its tensor pipe
+// waits for the dequantised weight tile (the codes' trip from the L2, the conversion, the swizzled stores), and
+// between tiles for the epilogue.  Here
+//   * one block per SM walks the output tiles (256 tokens x 128 weight rows), tiles that share weight rows running at
+//     the same time on neighbouring SMs so that their code reads meet in the L2;
+//   * the codes come through their own ring of eight bulk tensor copies, far enough ahead that no warp waits for the L2;
+//   * sixteen warps turn a stage's codes into f16 in the K-major swizzled layout the tensor core reads;
+//   * the accumulator is double-buffered (2 x 256 columns of tensor memory): four epilogue warps drain one tile while
+//     the products of the next are issued.
+// Warps: 0 activation copies, 1 code copies, 2 MMA issue, 3..18 dequantisation, 19..22 epilogue.  Every wait is
+// bounded; a warp that gives up records it in the context's status word and leaves its loops.
+#include <cuda.h>
+
+#include <string>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, MT = 2;   // MMA M128 N128; two token sub-tiles share a weight tile
+constexpr int ST = 3;                                // stages of f16 operands
+constexpr int CS = 8;                                // stages of codes
+constexpr int DW = 16, EW = 4;                       // dequantising and epilogue warps
+constexpr int FIRST_DW = 3, FIRST_EW = FIRST_DW + DW;
+constexpr int THREADS = 32 * (FIRST_EW + EW);
+constexpr int A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, C_BYTES = BN * BK;  // per stage; codes at 8 bits
+constexpr int OFF_A = 0, OFF_B = OFF_A + ST * A_BYTES, OFF_C = OFF_B + ST * B_BYTES, OFF_BAR = OFF_C + CS * C_BYTES;
+constexpr int SMEM_BYTES = 1024 + OFF_BAR + 512;
+static_assert(SMEM_BYTES <= 232448, "over the 227 KiB a block may use");
+
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // kind::f16, f32 accumulator, K-major A and B
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {  // K-major, 128-byte rows, SWIZZLE_128B, 1024 bytes between 8-row groups
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+        "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Four int8 codes (one word) -> four f16 of code * scale: 0x6400 | (code ^ 0x80) is the f16 1024 + code + 128.
+__device__ __forceinline__ void dequant4(uint32_t w, __half2 scale, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x = w ^ 0x80808080u;
+    uint32_t a = __byte_perm(x, 0x64646464u, 0x5140), b = __byte_perm(x, 0x64646464u, 0x7362);
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+    const __half2 va = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&a), bias), scale), vb = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&b), bias), scale);
+    lo = *reinterpret_cast<const uint32_t*>(&va), hi = *reinterpret_cast<const uint32_t*>(&vb);
+}
+// Eight four-bit weights (quant.rs:60-66: low nibbles are weights 0..3, high nibbles 4..7) -> eight f16 of (n - 8) * scale.
+__device__ __forceinline__ void dequant8_q4(uint32_t w, __half2 scale, uint32_t (&out)[4]) {
+    const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+    const __half2 bias = __floats2half2_rn(1032.0f, 1032.0f);
+    uint32_t p[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342), __byte_perm(hi, 0x64646464u, 0x4140),
+                     __byte_perm(hi, 0x64646464u, 0x4342)};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p[i]), bias), scale);
+        out[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
+struct Args {
+    const __half* s;   // scales [N][K / 32] (8-bit codes) or [N][K / 64] (4-bit)
+    void* out;
+    uint32_t M, N, K;
+    int mode;          // as gemm.cu: 0 f32, 1 f16, 2 GeGLU(tanh) pairs, 3 f32 +=, 4 GeGLU(erf) pairs, 5 GELU(erf) f16
+};
+
+struct Bars {
+    uint64_t full[ST], empty[ST], c_full[CS], c_empty[CS], acc_full[2], acc_empty[2];
+    uint32_t tmem;
+};
+
+template <int WB>
+__global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map, const Args g,
+                                                                     uint32_t* status) {
+    extern __shared__ uint8_t raw_unaligned[];
+    uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
+    uint8_t *As = raw + OFF_A, *Bs = raw + OFF_B, *Cs = raw + OFF_C;
+    Bars& bar = *reinterpret_cast<Bars*>(raw + OFF_BAR);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nk = g.K / BK, tiles_m = (g.M + MT * BM - 1) / (MT * BM), tiles_n = (g.N + BN - 1) / BN, tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], DW + 1), mbar_init(&bar.empty[i], 1);
+        for (int i = 0; i < CS; i++) mbar_init(&bar.c_full[i], 1), mbar_init(&bar.c_empty[i], DW);
+        for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], EW);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&bar.tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bar.tmem;
+
+    // Tile t: token tile t % tiles_m, weight tile t / tiles_m: blocks that run together share weight rows.
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+                const uint32_t m0 = (t % tiles_m) * (MT * BM);
+                for (uint32_t kt = 0; kt < nk; kt++, it++) {
+                    const uint32_t s = it % ST;
+                    if (it >= ST && !mbar_wait(&bar.empty[s], ((it / ST) - 1) & 1)) {
+                        atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                        t = tiles;
+                        break;
+                    }
+                    mbar_expect_tx(&bar.full[s], A_BYTES);
+                    tma_load_2d(As + s * A_BYTES, &a_map, (int)(kt * BK), (int)m0, &bar.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t ic = 0;
+            for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+                const uint32_t n0 = (t / tiles_m) * BN;
+                for (uint32_t kt = 0; kt < nk; kt++, ic++) {
+                    const uint32_t c = ic % CS;
+                    if (ic >= CS && !mbar_wait(&bar.c_empty[c], ((ic / CS) - 1) & 1)) {
+                        atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                        t = tiles;
+                        break;
+                    }
+                    mbar_expect_tx(&bar.c_full[c], C_BYTES * WB / 8);
+                    tma_load_2d(Cs + c * C_BYTES, &w_map, (int)(kt * BK * WB / 8), (int)n0, &bar.c_full[c]);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {
+            uint32_t it = 0, ti = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ti++) {
+                const uint32_t b = ti & 1;
+                if (ti >= 2 && !mbar_wait(&bar.acc_empty[b], ((ti >> 1) - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (uint32_t kt = 0; kt < nk; kt++, it++) {
+                    const uint32_t s = it % ST;
+                    if (!mbar_wait(&bar.full[s], (it / ST) & 1)) {
+                        atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a = smem_addr(As + s * A_BYTES), bb = smem_addr(Bs + s * B_BYTES);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                        for (int k = 0; k < BK / 16; k++)
+                            mma_f16(tmem + b * (MT * BN) + mt * BN, smem_desc(a + mt * (BM * BK * 2) + k * 32), smem_desc(bb + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&bar.empty[s]);
+                }
+                mma_commit(&bar.acc_full[b]);  // arrives when the tile's products have finished
+            }
+        }
+    } else if (warp < FIRST_EW) {
+        // Dequantisation: thread j takes the 16 codes of piece (row j / 4, quarter j % 4) of every stage.
+        const int j = threadIdx.x - 32 * FIRST_DW, row = j >> 2, qtr = j & 3;
+        constexpr uint32_t GS = WB == 4 ? 8 : 4;               // k tiles one 16-byte load of scales covers
+        const uint32_t spr = g.K / (WB == 4 ? 64 : 32);        // scales per row
+        uint32_t it = 0, ic = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            const uint32_t n = (t / tiles_m) * BN + row;
+            const bool live = n < g.N;
+            const __half* srow = g.s + (size_t)n * spr;
+            auto scales_from = [&](uint32_t kt) -> uint4 {  // the row's eight scales from k tile `kt` on
+                const uint32_t at = kt * (WB == 4 ? 1 : 2);
+                if (live && at + 8 <= spr && spr % 8 == 0) return __ldg(reinterpret_cast<const uint4*>(srow + at));
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (uint32_t e = 0; e < 8; e++)
+                    if (live && at + e < spr) w[e >> 1] |= (uint32_t)__half_as_ushort(srow[at + e]) << (16 * (e & 1));
+                return make_uint4(w[0], w[1], w[2], w[3]);
+            };
+            uint4 sc = scales_from(0), sc_next = sc;
+            for (uint32_t kt = 0; kt < nk; kt++, it++, ic++) {
+                if (kt % GS == 0) {
+                    if (kt > 0) sc = sc_next;
+                    if (kt + GS < nk) sc_next = scales_from(kt + GS);  // one group ahead
+                }
+                const uint32_t c = ic % CS, s = it % ST;
+                if (!mbar_wait(&bar.c_full[c], (ic / CS) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                    ok = false;
+                    break;
+                }
+                uint32_t v[8];
+                const uint32_t h = WB == 4 ? (kt & 7u) : 2u * (kt & 3u) + (uint32_t)(qtr >> 1);  // which of the eight scales
+                const uint32_t word = (h >> 1) == 0 ? sc.x : (h >> 1) == 1 ? sc.y : (h >> 1) == 2 ? sc.z : sc.w;
+                const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)((h & 1u) ? (word >> 16) : (word & 0xffffu))));
+                if constexpr (WB == 4) {
+                    const uint2 cw = *reinterpret_cast<const uint2*>(Cs + c * C_BYTES + row * (BK / 2) + qtr * 8);
+                    uint32_t a[4], b[4];
+                    dequant8_q4(cw.x, s2, a), dequant8_q4(cw.y, s2, b);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) v[e] = a[e], v[4 + e] = b[e];
+                } else {
+                    const uint4 cw = *reinterpret_cast<const uint4*>(Cs + c * C_BYTES + row * BK + qtr * 16);
+                    dequant4(cw.x, s2, v[0], v[1]), dequant4(cw.y, s2, v[2], v[3]), dequant4(cw.z, s2, v[4], v[5]), dequant4(cw.w, s2, v[6], v[7]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar.c_empty[c]);  // the codes are in registers
+                if (it >= ST && !mbar_wait(&bar.empty[s], ((it / ST) - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    ok = false;
+                    break;
+                }
+                uint8_t* base = Bs + s * B_BYTES + row * 128;
+                *reinterpret_cast<uint4*>(base + (((2 * qtr) ^ (row & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<uint4*>(base + (((2 * qtr + 1) ^ (row & 7)) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar.full[s]);
+            }
+        }
+    } else {
+        // Epilogue: warp q of the four reads lanes 32 q .. 32 q + 31 of the accumulator (token rows), 32 columns at a time.
+        const uint32_t q = warp & 3;
+        uint32_t ti = 0;
+        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ti++) {
+            const uint32_t b = ti & 1, m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
+            if (!mbar_wait(&bar.acc_full[b], (ti >> 1) & 1)) {
+                atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int cbi = 0; cbi < MT * (BN / 32); cbi++) {
+                const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
+                const uint32_t m = m0 + mt * BM + 32 * q + lane;
+                uint32_t r[32];
+                tmem_load32(tmem + ((32 * q) << 16) + b * (MT * BN) + mt * BN + cb * 32, r);
+                if (m >= g.M) continue;
+                const uint32_t col = n0 + cb * 32;
+                if (g.mode == 3) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        if (col + 4 * i < g.N) {
+                            float4 x = dst[i];
+                            x.x += __uint_as_float(r[4 * i]), x.y += __uint_as_float(r[4 * i + 1]), x.z += __uint_as_float(r[4 * i + 2]), x.w += __uint_as_float(r[4 * i + 3]);
+                            dst[i] = x;
+                        }
+                } else if (g.mode == 0) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                } else if (g.mode == 1 || g.mode == 5) {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
+                            if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                            const __half2 x = __floats2half2_rn(f0, f1);
+                            h[e] = *reinterpret_cast<const uint32_t*>(&x);
+                        }
+                        if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                } else {
+                    // columns (2j, 2j + 1) are (gate_j, up_j): gelu(gate) * up, 16 results per 32 columns
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * (g.N / 2) + col / 2);
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
+                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                            const __half2 x = __floats2half2_rn(a0, a1);
+                            h[e] = *reinterpret_cast<const uint32_t*>(&x);
+                        }
+                        if (col + 16 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar.acc_empty[b]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+// The shapes this schedule takes: everything gemm.cu's kernel takes with whole 16-byte rows of codes.
+bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K % BK == 0 && (K * wbits / 8) % 16 == 0 && N > 0; }
+
+int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
+                           uint32_t wbits) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
+    CUtensorMap amap, wmap;
+    {
+        const cuuint64_t dims[2] = {K, M};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        const cuuint32_t box[2] = {BK, MT * BM}, elem[2] = {1, 1};
+        const CUresult r = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(a), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (activations) failed (" + std::to_string((int)r) + ")");
+    }
+    {
+        const cuuint64_t row = (cuuint64_t)K * wbits / 8;  // bytes of codes per weight row
+        const cuuint64_t dims[2] = {row, N};
+        const cuuint64_t strides[1] = {row};
+        const cuuint32_t box[2] = {(cuuint32_t)(BK * wbits / 8), BN}, elem[2] = {1, 1};
+        const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (codes) failed (" + std::to_string((int)r) + ")");
+    }
+    static bool configured[16] = {};
+    if (!configured[ctx->gpu & 15]) {
+        TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[ctx->gpu & 15] = true;
+    }
+    const uint32_t tiles = ((M + MT * BM - 1) / (MT * BM)) * ((N + BN - 1) / BN);
+    const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
+    const Args g{s, out, M, N, K, mode};
+    if (wbits == 4) gemm_persistent_kernel<4><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
+    else gemm_persistent_kernel<8><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+}  // namespace tb

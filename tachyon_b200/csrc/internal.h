@@ -196,6 +196,11 @@ int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32
 // cos/sin of every (position, frequency): table [positions][256] for AttendParams::trig.
 int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, float* table);
 
+// The same product as a persistent kernel (gemm2.cu); launch_gemm_q8 validates and dispatches.
+bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits);
+int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
+                           uint32_t wbits);
+
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {

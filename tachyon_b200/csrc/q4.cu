@@ -286,9 +286,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, u
             atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
             ok = false;
         }
-        for (uint32_t k = wl; k < rps; k += wps) {
-            const uint32_t row = r0 + i * rps + k;
-            if (!ok || row >= r1) break;
+        // Two of the warp's rows at a time: each row's sum keeps the reference's order, the two butterflies interleave.
+        auto row_sum = [&](uint32_t k) -> float {
             const uint4* wr = reinterpret_cast<const uint4*>(raw + Layout::W + slot * STAGE_W + (size_t)k * rb);
             const __half* sr = reinterpret_cast<const __half*>(raw + Layout::S + slot * STAGE_S) + (size_t)k * (p.cols / 64);
             float sum = 0.0f;
@@ -302,9 +301,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q4_kernel(const Q4Params p, u
 #pragma unroll 2
                 for (uint32_t c = lane; c < nch; c += 32) sum = chunk_step(chunk_dot(wr[c], xlo[c], xhi[c]), xs[c], __half2float(sr[c >> 1]), sum);
             }
+            return sum;
+        };
+        for (uint32_t k = wl; k < rps && ok; k += 2 * wps) {
+            const uint32_t row = r0 + i * rps + k, k2 = k + wps;
+            if (row >= r1) break;
+            const bool two = k2 < rps && row + wps < r1;
+            float s0 = row_sum(k), s1 = two ? row_sum(k2) : 0.0f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
-            if (lane == 0) p.y[row] = sum;
+            for (int o = 16; o > 0; o >>= 1) {
+                s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o));
+                s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o));
+            }
+            if (lane == 0) {
+                p.y[row] = s0;
+                if (two) p.y[row + wps] = s1;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);
