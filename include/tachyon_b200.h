@@ -170,7 +170,8 @@ TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales,
 
 /*
  * Decode attention for one new token; argument meaning follows attend_256 (crates/tachyon/src/ptx/attend.rs:21-32).
- * head size 256; heads / kv_heads in {1, 2, 4}.
+ * head size 256; heads / kv_heads in {1, 2, 4}, or 8 (E2B: two blocks of four query heads share a key-value head, the
+ * reference's `group` 2; a simpler, slower kernel serves it).
  */
 typedef struct tb_attend {
     const float* qkv;      /* device f32 [(heads + 2*kv_heads) * 256]: queries, new keys, new values */
@@ -187,13 +188,21 @@ typedef struct tb_attend {
     float scale;           /* softmax scale (1 in Gemma 4, 1/sqrt(256) in the plain configuration) */
     float eps;
     float* partial;        /* device scratch, tb_attend_scratch_bytes(...) bytes; NULL allowed when splits == 1 */
-    uint32_t* count;       /* device, kv_heads words, zero before the first launch, left zero */
+    uint32_t* count;       /* device, kv_heads words (heads / 4 when heads = 8 kv_heads), zero before the first launch, left zero */
     uint32_t splits;       /* blocks per kv head */
     void* out;             /* device [heads * 256], f32 or f16 */
     int out_dtype;
 } tb_attend;
 TB_API size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits);
 TB_API int tb_attend_decode(tb_context* ctx, const tb_attend* args);
+/*
+ * The same for heads of 512: attend_512 (crates/tachyon/src/ptx/attend.rs:1-32, 37-38), Gemma 4's global layers.  The
+ * struct's 256s read 512 (freq: f32 [256]); heads / kv_heads in {1, 2, 4, 8}.  A block takes up to four query heads, so
+ * with 8 to a key-value head two blocks share it (the reference's `group` 2).  count: heads / min(heads / kv_heads, 4)
+ * words; partial: tb_attend_512_scratch_bytes(heads, splits) bytes.
+ */
+TB_API size_t tb_attend_512_scratch_bytes(uint32_t heads, uint32_t splits);
+TB_API int tb_attend_decode_512(tb_context* ctx, const tb_attend* args);
 /*
  * tb_attend_decode for callers that cannot allocate device memory (no counterpart in the reference, which always carves
  * this scratch out of its decoder's arena): an engine whose memory plan is fixed at start-up, or a loop that must not

@@ -181,6 +181,13 @@ class Context:
     def attend_decode(self, args: Attend) -> None:
         check(self.lib.tb_attend_decode(self.handle, C.byref(args)))
 
+    def attend_decode_512(self, args: Attend) -> None:
+        """tb_attend_decode_512: heads of 512 (the reference's attend_512)."""
+        check(self.lib.tb_attend_decode_512(self.handle, C.byref(args)))
+
+    def attend_512_scratch_bytes(self, heads: int, splits: int) -> int:
+        return self.lib.tb_attend_512_scratch_bytes(heads, splits)
+
     def attend_decode_static(self, args: Attend) -> None:
         """tb_attend_decode_static: the scratch lives inside the library; nothing is allocated."""
         check(self.lib.tb_attend_decode_static(self.handle, C.byref(args)))

@@ -83,6 +83,8 @@ SIGNATURES = {
     "tb_attend_scratch_bytes": (sz, [u32, u32, u32]),
     "tb_attend_decode": (i32, [vp, C.POINTER(Attend)]),
     "tb_attend_decode_static": (i32, [vp, C.POINTER(Attend)]),
+    "tb_attend_decode_512": (i32, [vp, C.POINTER(Attend)]),
+    "tb_attend_512_scratch_bytes": (C.c_size_t, [u32, u32]),
     "tb_sample_greedy": (i32, [vp, vp, u32, f32, f32, vp, vp, vp, vp, vp]),
     "tb_topk": (i32, [vp, vp, u32, u32, vp, vp]),
     "tb_fill_codes": (i32, [vp, u64, u64, vp, sz]),

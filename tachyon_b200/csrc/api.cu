@@ -268,16 +268,33 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         // grid (H / per, S) blocks of 256, per = 4 query heads a block (2 for attend_256_2), `group` blocks per key-value head.
         TB_TRY(shape(15, 256));
         const uint32_t per = name == "attend_256" ? 4u : 2u, group = u32(10);
-        if (group != 1) return fail(UNSUPPORTED, "tb_launch: " + name + " with more than one block per key-value head (8 query heads to one) has no kernel here");
+        if (group != 1 && !(group == 2 && per == 4)) return fail(UNSUPPORTED, "tb_launch: " + name + " with that many blocks per key-value head has no kernel here");
+        if (grid[0] % group != 0) return fail(OUT_OF_RANGE, "tb_launch: " + name + " runs `group` blocks per key-value head");
         AttendParams a;
         a.qkv = static_cast<const float*>(ptr(0)), a.q_norm = static_cast<const float*>(ptr(1)), a.k_norm = static_cast<const float*>(ptr(2));
         a.freq = static_cast<const float*>(ptr(3)), a.kc = static_cast<__half*>(ptr(4)), a.vc = static_cast<__half*>(ptr(5));
         a.pos = static_cast<const uint32_t*>(ptr(6)), a.cap = u32(7), a.window = u32(8), a.fresh = u32(9);
-        a.kv_heads = grid[0], a.heads = per * grid[0], a.splits = grid[1], a.scale = 1.0f, a.eps = 1e-6f;
+        a.kv_heads = grid[0] / group, a.heads = per * grid[0], a.splits = grid[1], a.scale = 1.0f, a.eps = 1e-6f;
         a.partial = static_cast<float*>(ptr(11)), a.count = static_cast<uint32_t*>(ptr(12));
         a.out = ptr(13), a.out_pairs = static_cast<float*>(ptr(14)), a.out_f16 = 2;
         if (!a.q_norm || !a.k_norm || !a.out || !a.out_pairs) return fail(OUT_OF_RANGE, "tb_launch: " + name + " needs its norm weights and its Q8 output");
-        return launch_attend(ctx, a);
+        return group == 2 ? launch_attend_256_shared(ctx, a) : launch_attend(ctx, a);  // eight query heads to a key-value head: E2B
+    }
+    if (name == "attend_512") {
+        // attend.rs:21-32 at head size 512: grid (H / 4, S), four query heads a block, `group` blocks per key-value head.
+        TB_TRY(shape(15, 256));
+        const uint32_t group = u32(10);
+        if (group != 1 && group != 2) return fail(UNSUPPORTED, "tb_launch: attend_512 with more than two blocks per key-value head has no kernel here");
+        if (grid[0] % group != 0) return fail(OUT_OF_RANGE, "tb_launch: attend_512 runs `group` blocks per key-value head");
+        AttendParams a;
+        a.qkv = static_cast<const float*>(ptr(0)), a.q_norm = static_cast<const float*>(ptr(1)), a.k_norm = static_cast<const float*>(ptr(2));
+        a.freq = static_cast<const float*>(ptr(3)), a.kc = static_cast<__half*>(ptr(4)), a.vc = static_cast<__half*>(ptr(5));
+        a.pos = static_cast<const uint32_t*>(ptr(6)), a.cap = u32(7), a.window = u32(8), a.fresh = u32(9);
+        a.kv_heads = grid[0] / group, a.heads = 4 * grid[0], a.splits = grid[1], a.scale = 1.0f, a.eps = 1e-6f;
+        a.partial = static_cast<float*>(ptr(11)), a.count = static_cast<uint32_t*>(ptr(12));
+        a.out = ptr(13), a.out_pairs = static_cast<float*>(ptr(14)), a.out_f16 = 2;
+        if (!a.q_norm || !a.k_norm || !a.out || !a.out_pairs) return fail(OUT_OF_RANGE, "tb_launch: attend_512 needs its norm weights and its Q8 output");
+        return launch_attend_512(ctx, a);
     }
     return fail(NO_MODEL, "tb_launch: no kernel named " + name);
 }
@@ -356,7 +373,22 @@ int tb_attend_decode(tb_context* ctx, const tb_attend* a) {
     p.pos = a->pos, p.cap = a->cap, p.window = a->window, p.fresh = a->fresh, p.heads = a->heads, p.kv_heads = a->kv_heads;
     p.scale = a->scale, p.eps = a->eps, p.partial = a->partial, p.count = a->count, p.splits = a->splits;
     p.out = a->out, p.out_f16 = a->out_dtype == TB_F16;
+    if (a->kv_heads != 0 && a->heads == 8 * a->kv_heads) return launch_attend_256_shared(ctx, p);  // two blocks of four heads per key-value head
     return launch_attend(ctx, p);
+}
+
+size_t tb_attend_512_scratch_bytes(uint32_t heads, uint32_t splits) { return (size_t)heads * splits * (2 + 512) * sizeof(float); }
+
+int tb_attend_decode_512(tb_context* ctx, const tb_attend* a) {
+    if (!ctx || !a) return fail(OUT_OF_RANGE, "tb_attend_decode_512: null argument");
+    if (!dtype_ok(a->out_dtype)) return fail(OUT_OF_RANGE, "tb_attend_decode_512: unknown dtype");
+    AttendParams p;
+    p.qkv = a->qkv, p.q_norm = a->q_norm, p.k_norm = a->k_norm, p.freq = a->freq;
+    p.kc = reinterpret_cast<__half*>(a->k_cache), p.vc = reinterpret_cast<__half*>(a->v_cache);
+    p.pos = a->pos, p.cap = a->cap, p.window = a->window, p.fresh = a->fresh, p.heads = a->heads, p.kv_heads = a->kv_heads;
+    p.scale = a->scale, p.eps = a->eps, p.partial = a->partial, p.count = a->count, p.splits = a->splits;
+    p.out = a->out, p.out_f16 = a->out_dtype == TB_F16;
+    return launch_attend_512(ctx, p);
 }
 
 int tb_attend_decode_static(tb_context* ctx, const tb_attend* a) {

@@ -26,7 +26,7 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 64, MT = 2;   // MMA M128 N128; two token sub-tiles share a weight tile
 constexpr int ST = 3;                                // stages of f16 operands
 constexpr int CS = 8;                                // stages of codes
-constexpr int DW = 16, EW = 4;                       // dequantising and epilogue warps
+constexpr int DW = 16, EW = 8;                       // dequantising and epilogue warps (a multiple of four: TMEM lane quarters)
 constexpr int FIRST_DW = 3, FIRST_EW = FIRST_DW + DW;
 constexpr int THREADS = 32 * (FIRST_EW + EW);
 constexpr int A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, C_BYTES = BN * BK;  // per stage; codes at 8 bits
@@ -253,8 +253,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
             }
         }
     } else {
-        // Epilogue: warp q of the four reads lanes 32 q .. 32 q + 31 of the accumulator (token rows), 32 columns at a time.
-        const uint32_t q = warp & 3;
+        // Epilogue: a warp reads the accumulator lanes (token rows) of its quarter q = warp % 4, 32 columns at a time;
+        // the EW / 4 warps of a quarter take alternate column blocks.
+        const uint32_t q = warp & 3, part = (warp - FIRST_EW) >> 2;
         uint32_t ti = 0;
         for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ti++) {
             const uint32_t b = ti & 1, m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int cbi = 0; cbi < MT * (BN / 32); cbi++) {
+            for (int cbi = part; cbi < MT * (BN / 32); cbi += EW / 4) {
                 const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
                 const uint32_t m = m0 + mt * BM + 32 * q + lane;
                 uint32_t r[32];

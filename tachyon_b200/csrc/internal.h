@@ -127,6 +127,8 @@ struct AttendParams {
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
+int launch_attend_512(tb_context* ctx, const AttendParams& p);  // heads of 512; up to 8 query heads per key-value head (attend512.cu)
+int launch_attend_256_shared(tb_context* ctx, const AttendParams& p);  // heads of 256, the same simple kernel: 8 query heads per key-value head
 int launch_attend_static(tb_context* ctx, AttendParams p);  // scratch inside the library; see attend.cu
 
 // ---- fused decode step ---------------------------------------------------------------------------------------

@@ -1,6 +1,7 @@
 """Decode attention on the GPU against the f64 oracle.  Cases follow crates/tachyon/tests/decode.rs:185-334 (short
 context, full sliding window, ring longer than the window, shared cache, 1/2/4 query heads per key-value head) at head
-size 256, plus the benchmark's plain configuration (scale 1/16, no norms, f16 output, 4096 positions)."""
+size 256, plus the benchmark's plain configuration (scale 1/16, no norms, f16 output, 4096 positions); head size 512
+(rope(1e6, 512, 0.25), decode.rs:212, 329-334) and eight query heads to a key-value head (decode.rs:313-314)."""
 import numpy as np
 import pytest
 
@@ -12,7 +13,8 @@ pytestmark = pytest.mark.gpu
 D = 256
 
 
-def run_case(ctx, *, cap, win, pos, splits, fresh, heads, kv, plain=False, out_f16=False, times=2, scale=1.0, seed=0):
+def run_case(ctx, *, cap, win, pos, splits, fresh, heads, kv, plain=False, out_f16=False, times=2, scale=1.0, seed=0, D=256):
+    blocks = heads // min(heads // kv, 4)  # blocks per split: the counters
     rng_seed = seed + pos + cap
     rows = heads + 2 * kv
     qkv = values_fast(rows * D, rng_seed)
@@ -20,7 +22,7 @@ def run_case(ctx, *, cap, win, pos, splits, fresh, heads, kv, plain=False, out_f
         qkv = np.random.default_rng(rng_seed).standard_normal(rows * D).astype(np.float32)
     qn = (0.2 + 0.1 * values_fast(D, rng_seed + 1)).astype(np.float32)
     kn = (0.2 + 0.1 * values_fast(D, rng_seed + 2)).astype(np.float32)
-    freq = oracle.rope_freq(10000.0, D, 1.0)
+    freq = oracle.rope_freq(10000.0, D, 1.0) if D == 256 else oracle.rope_freq(1e6, D, 0.25)
     mul = 1.0 if plain else 0.3
     kc = f16(mul * (np.random.default_rng(rng_seed + 3).standard_normal(kv * cap * D) if plain else values_fast(kv * cap * D, rng_seed + 3)))
     vc = f16(mul * (np.random.default_rng(rng_seed + 4).standard_normal(kv * cap * D) if plain else values_fast(kv * cap * D, rng_seed + 4)))
@@ -28,15 +30,15 @@ def run_case(ctx, *, cap, win, pos, splits, fresh, heads, kv, plain=False, out_f
     want = oracle.attend_decode(qkv, None if plain else qn, None if plain else kn, None if plain else freq, kc0, vc0, pos, cap, win, fresh, heads, kv, D, scale)
 
     bufs = dict(qkv=ctx.upload(qkv), qn=ctx.upload(qn), kn=ctx.upload(kn), freq=ctx.upload(freq), k=ctx.upload(kc), v=ctx.upload(vc),
-                pos=ctx.upload(np.array([pos], np.uint32)), part=ctx.zeros(max(ctx.attend_scratch_bytes(heads, kv, splits), 16)),
-                count=ctx.zeros(4 * kv), out=ctx.zeros(heads * D * 4))
+                pos=ctx.upload(np.array([pos], np.uint32)), part=ctx.zeros(max(ctx.attend_scratch_bytes(heads, kv, splits) * (D // 256), 16)),
+                count=ctx.zeros(4 * blocks), out=ctx.zeros(heads * D * 4))
     a = tb.Attend(qkv=bufs["qkv"].ptr, q_norm=None if plain else bufs["qn"].ptr, k_norm=None if plain else bufs["kn"].ptr,
                   freq=None if plain else bufs["freq"].ptr, k_cache=bufs["k"].ptr, v_cache=bufs["v"].ptr, pos=bufs["pos"].ptr, cap=cap, window=win,
                   fresh=int(fresh), heads=heads, kv_heads=kv, scale=scale, eps=1e-6, partial=bufs["part"].ptr, count=bufs["count"].ptr, splits=splits,
                   out=bufs["out"].ptr, out_dtype=tb.F16 if out_f16 else tb.F32)
     for _ in range(times):
-        ctx.attend_decode(a)
-    assert not bufs["count"].download(np.uint32, kv).any(), "the counters are left at zero"
+        ctx.attend_decode(a) if D == 256 else ctx.attend_decode_512(a)
+    assert not bufs["count"].download(np.uint32, blocks).any(), "the counters are left at zero"
     got = f16_to_f32(bufs["out"].download(np.uint16, heads * D)) if out_f16 else bufs["out"].download(np.float32, heads * D)
     tol = (2e-3 if out_f16 else 1e-3) * np.abs(want).max()
     assert np.abs(got - want).max() <= tol, (np.abs(got - want).max(), tol)
@@ -74,6 +76,24 @@ def test_global_attention_with_its_own_or_a_shared_cache(ctx):
     run_case(ctx, cap=2048, win=2048, pos=1500, splits=32, fresh=True, heads=8, kv=2)
     run_case(ctx, cap=2048, win=2048, pos=1500, splits=128, fresh=False, heads=8, kv=2)
     run_case(ctx, cap=4096, win=4096, pos=4095, splits=4, fresh=True, heads=8, kv=2)  # several tiles per block
+
+
+def test_heads_of_512(ctx):
+    """decode.rs:329-334: global layers' heads of 512, their own cache or a shared one, four or eight query heads to a key-value head."""
+    assert ctx.attend_512_scratch_bytes(8, 32) == 8 * 32 * 514 * 4
+    run_case(ctx, D=512, cap=2048, win=2048, pos=1500, splits=32, fresh=True, heads=8, kv=2)
+    run_case(ctx, D=512, cap=2048, win=2048, pos=1500, splits=256, fresh=False, heads=8, kv=2)
+    run_case(ctx, D=512, cap=2048, win=2048, pos=1500, splits=32, fresh=True, heads=16, kv=2)
+    run_case(ctx, D=512, cap=512, win=512, pos=0, splits=8, fresh=True, heads=4, kv=2)
+    run_case(ctx, D=512, cap=600, win=512, pos=5999, splits=7, fresh=True, heads=2, kv=2, out_f16=True)
+    run_case(ctx, D=512, cap=512, win=512, pos=17, splits=1, fresh=True, heads=8, kv=2)
+
+
+def test_eight_query_heads_to_a_key_value_head(ctx):
+    """decode.rs:313-314 (E2B): two blocks share each key-value head and the first stores the new key and value."""
+    run_case(ctx, cap=512, win=512, pos=100, splits=16, fresh=True, heads=16, kv=2)
+    run_case(ctx, cap=1024, win=512, pos=1700, splits=16, fresh=True, heads=8, kv=1)
+    run_case(ctx, cap=2048, win=2048, pos=1500, splits=64, fresh=False, heads=16, kv=2)
 
 
 def test_plain_configuration_of_the_benchmark(ctx):

@@ -13,6 +13,13 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(128, 128, 64), (128, 128, 256), (1, 128, 2048), (37, 256, 2048), (300, 3072, 2048), (512, 2048, 2048), (129, 2048, 16384), (256, 96, 128)]
 
 
+@pytest.fixture(params=["one tile per block", "persistent"])
+def schedule(request, monkeypatch):
+    """Both schedules of the GEMM (the library reads the variable at every launch); left to itself it picks by shape."""
+    monkeypatch.setenv("TACHYON_B200_GEMM", "1" if request.param == "one tile per block" else "2")
+    return request.param
+
+
 def reference(w, s, a):
     deq = w.astype(np.float64) * np.repeat(f16_to_f32(s).astype(np.float64), 32, axis=1)
     a64 = a.astype(np.float64)
@@ -20,7 +27,7 @@ def reference(w, s, a):
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
-def test_gemm_matches_f64(ctx, m, n, k):
+def test_gemm_matches_f64(ctx, schedule, m, n, k):
     w, s = q8_weights(n, k, 7 + n + k)
     a = f16_to_f32(f16(np.random.default_rng(m + k).standard_normal((m, k)).astype(np.float32)))
     want, bound = reference(w, s, a)
@@ -42,7 +49,7 @@ def test_gemm_matches_f64(ctx, m, n, k):
     assert ctx.status() == 0
 
 
-def test_gemm_geglu_epilogue(ctx):
+def test_gemm_geglu_epilogue(ctx, schedule):
     m, n, k = 200, 1024, 2048
     w, s = q8_weights(n, k, 3)
     a = f16_to_f32(f16(np.random.default_rng(5).standard_normal((m, k)).astype(np.float32)))
@@ -67,7 +74,7 @@ def test_gemm_rejects_bad_shapes(ctx):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (37, 256, 2048), (300, 3072, 2048), (129, 2048, 16384), (256, 96, 128), (64, 64, 576)])
-def test_gemm_q4_matches_f64(ctx, m, n, k):
+def test_gemm_q4_matches_f64(ctx, schedule, m, n, k):
     """The reference's Q4 weights (quant.rs:47-82) through the same tensor-core product: (n - 8) * scale as f16 operands."""
     wf = np.random.default_rng(n + k).uniform(-1, 1, (n, k)).astype(np.float32)
     packed, scales = oracle.q4(wf)

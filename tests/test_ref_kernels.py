@@ -135,30 +135,31 @@ def test_gemv_and_sampler_launch_by_name_and_bad_launches_are_refused(ctx):
         ctx.launch("geglu_q8", (1, 1, 1), (256, 1, 1), 0, [("p", ld.ptr)])
 
 
-@pytest.mark.parametrize("name,per,cap,win,pos,splits,fresh", [
+@pytest.mark.parametrize("name,per,cap,win,pos,splits,fresh,group", [(n, p, c, w, at, s, f, 1) for n, p, c, w, at, s, f in [
     ("attend_256", 4, 512, 512, 0, 16, True), ("attend_256", 4, 512, 512, 100, 16, True), ("attend_256_2", 2, 512, 512, 100, 16, True),
     ("attend_256", 4, 512, 512, 700, 16, True), ("attend_256", 4, 1024, 512, 1700, 16, True), ("attend_256_2", 2, 2048, 1024, 3000, 32, True),
-    ("attend_256", 4, 2048, 2048, 1500, 64, False)])
-def test_attention_by_name_writes_q8(ctx, name, per, cap, win, pos, splits, fresh):
-    """tests/decode.rs:185-334 at head size 256 through the launch seam: fifteen arguments, Q8 out, counters left at zero."""
+    ("attend_256", 4, 2048, 2048, 1500, 64, False), ("attend_512", 4, 2048, 2048, 1500, 32, True), ("attend_512", 4, 2048, 2048, 1500, 256, False)]] + [
+    ("attend_256", 4, 512, 512, 100, 16, True, 2), ("attend_512", 4, 2048, 2048, 1500, 32, True, 2)])
+def test_attention_by_name_writes_q8(ctx, name, per, cap, win, pos, splits, fresh, group):
+    """tests/decode.rs:185-334 through the launch seam: fifteen arguments, Q8 out, counters left at zero; `group` blocks per key-value head."""
     from util import f16, values_fast
 
-    D, kv = 256, 2
-    heads, seed = per * kv, pos + 256
+    D, kv = 512 if name == "attend_512" else 256, 2
+    heads, seed, blocks = per * group * kv, pos + 256, group * kv
     qkv = values_fast((heads + 2 * kv) * D, seed)
     qn, kn = (0.2 + 0.1 * values_fast(D, seed + 1)).astype(np.float32), (0.2 + 0.1 * values_fast(D, seed + 2)).astype(np.float32)
-    freq = oracle.rope_freq(10000.0, D, 1.0)
+    freq = oracle.rope_freq(10000.0, D, 1.0) if D == 256 else oracle.rope_freq(1e6, D, 0.25)
     kc, vc = f16(0.3 * values_fast(kv * cap * D, seed + 3)), f16(0.3 * values_fast(kv * cap * D, seed + 4))
     want = oracle.attend_decode(qkv, qn, kn, freq, kc.copy(), vc.copy(), pos, cap, win, fresh, heads, kv, D, 1.0).astype(np.float64)
     b = [ctx.upload(a) for a in (qkv, qn, kn, freq, kc, vc, np.array([pos], np.uint32))]
-    part, count, (q, s) = ctx.zeros(kv * splits * (8 + per * D) * 4), ctx.zeros(4 * kv), q8_out(ctx, heads * D)
-    args = [("p", x.ptr) for x in b] + [("u", cap), ("u", win), ("u", int(fresh)), ("u", 1), ("p", part.ptr), ("p", count.ptr), ("p", q.ptr), ("p", s.ptr)]
+    part, count, (q, s) = ctx.zeros(blocks * splits * (8 + per * D) * 4), ctx.zeros(4 * blocks), q8_out(ctx, heads * D)
+    args = [("p", x.ptr) for x in b] + [("u", cap), ("u", win), ("u", int(fresh)), ("u", group), ("p", part.ptr), ("p", count.ptr), ("p", q.ptr), ("p", s.ptr)]
     for _ in range(2):
-        ctx.launch(name, (kv, splits, 1), (256, 1, 1), 0, args)
-    assert not count.download(np.uint32, kv).any(), "the counters are left at zero"
+        ctx.launch(name, (blocks, splits, 1), (256, 1, 1), 0, args)
+    assert not count.download(np.uint32, blocks).any(), "the counters are left at zero"
     assert_q8(*q8_read(q, s, heads * D), want, 1e-3 * np.abs(want).max())
     if not fresh:
         assert np.array_equal(b[4].download(np.uint16, kc.size), kc) and np.array_equal(b[5].download(np.uint16, vc.size), vc)
     with pytest.raises(tb.Error) as e:
-        ctx.launch(name, (kv, splits, 1), (256, 1, 1), 0, args[:10] + [("u", 2)] + args[11:])
-    assert e.value.status == 9  # eight query heads to one key-value head: no kernel here
+        ctx.launch(name, (4 * blocks, splits, 1), (256, 1, 1), 0, args[:10] + [("u", 4)] + args[11:])
+    assert e.value.status == 9  # sixteen query heads to one key-value head: no kernel here
