@@ -169,6 +169,27 @@ TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const fl
 TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint32_t* token, uint32_t cols, float scale, float* out);
 
 /*
+ * Prefill attention on tensor cores: flash_256 / flash_512 (crates/tachyon/src/ptx/flash.rs:1-23).  Token t of the chunk,
+ * at position pos0 + t, attends positions p - window < j <= p of the cache (f16 [kv_heads][cap][head_dim], position j in
+ * slot j % cap, the chunk's own keys and values already stored).  q: device f16 [tokens][heads][head_dim] as the query
+ * kernel leaves them, already multiplied by scale * log2(e); out: device f16 [tokens][heads * head_dim].
+ * head_dim 256 or 512; heads / kv_heads in {1, 2, 4}.  Key tiles start at multiples of 32 positions, so a token's sums
+ * do not depend on how the prompt was cut into chunks.
+ */
+TB_API int tb_prefill_attend(tb_context* ctx, const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out, uint32_t tokens,
+                             uint32_t pos0, uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim);
+/*
+ * What prefill does to a chunk's projected rows before that: kv_256 / kv_512 and query_256 / query_512 (ptx/attend.rs:
+ * 472-556) in one launch.  qkv: device f32 [tokens][(heads + 2 kv_heads) * head_dim]; queries are normalised (q_norm),
+ * rotated at pos0 + t, multiplied by scale * log2(e) and stored as f16 [tokens][heads][head_dim]; keys normalised
+ * (k_norm) and rotated, values normalised without weights, both stored as f16 in cache slot (pos0 + t) % cap.
+ * kv_heads 0: a layer that shares another layer's cache projects queries only.  freq: f32 [head_dim / 2].
+ */
+TB_API int tb_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, uint16_t* q_out, uint16_t* k_cache,
+                          uint16_t* v_cache, uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale,
+                          uint32_t head_dim);
+
+/*
  * Decode attention for one new token; argument meaning follows attend_256 (crates/tachyon/src/ptx/attend.rs:21-32).
  * head size 256; heads / kv_heads in {1, 2, 4}, or 8 (E2B: two blocks of four query heads share a key-value head, the
  * reference's `group` 2; a simpler, slower kernel serves it).

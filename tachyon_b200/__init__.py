@@ -178,6 +178,16 @@ class Context:
     def embed_q8(self, w, s, token, cols, scale, out) -> None:
         check(self.lib.tb_embed_q8(self.handle, w.ptr, s.ptr, token.ptr, cols, scale, out.ptr))
 
+    def prefill_attend(self, q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads, head_dim=256) -> None:
+        """tb_prefill_attend: a chunk's tokens over their windows of the cache (the reference's flash_256 / flash_512)."""
+        check(self.lib.tb_prefill_attend(self.handle, q.ptr, kc.ptr, vc.ptr, out.ptr, tokens, pos0, cap, window, heads, kv_heads, head_dim))
+
+    def prefill_qkv(self, qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, scale, head_dim=256) -> None:
+        """tb_prefill_qkv: norms, RoPE, cache append and f16 queries for a chunk (kv_256/512 and query_256/512 in one launch)."""
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_prefill_qkv(self.handle, qkv.ptr, q_norm.ptr, p(k_norm), freq.ptr, q_out.ptr, p(kc), p(vc), tokens, pos0, cap, heads, kv_heads, eps, scale,
+                                      head_dim))
+
     def attend_decode(self, args: Attend) -> None:
         check(self.lib.tb_attend_decode(self.handle, C.byref(args)))
 

@@ -80,6 +80,8 @@ SIGNATURES = {
     "tb_gemm_q4": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_norm": (i32, [vp, vp, vp, vp, vp, u32, f32, f32, vp, vp]),
     "tb_embed_q8": (i32, [vp, vp, vp, vp, u32, f32, vp]),
+    "tb_prefill_attend": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32]),
+    "tb_prefill_qkv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, u32]),
     "tb_attend_scratch_bytes": (sz, [u32, u32, u32]),
     "tb_attend_decode": (i32, [vp, C.POINTER(Attend)]),
     "tb_attend_decode_static": (i32, [vp, C.POINTER(Attend)]),

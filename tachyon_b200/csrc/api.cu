@@ -359,6 +359,25 @@ int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const 
     return launch_embed_q8(ctx, w, reinterpret_cast<const __half*>(scales), token, cols, scale, out);
 }
 
+int tb_prefill_attend(tb_context* ctx, const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out, uint32_t tokens, uint32_t pos0,
+                      uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
+    if (!ctx || !q || !k_cache || !v_cache || !out) return fail(OUT_OF_RANGE, "tb_prefill_attend: null argument");
+    if (tokens == 0 || cap == 0 || window == 0 || kv_heads == 0 || heads % kv_heads != 0) return fail(OUT_OF_RANGE, "tb_prefill_attend: empty or ragged shape");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(OUT_OF_RANGE, "tb_prefill_attend: buffers must be 16-byte aligned");
+    return launch_prefill_flash(ctx, reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache),
+                                reinterpret_cast<__half*>(out), tokens, pos0, cap, window, heads, kv_heads, head_dim);
+}
+
+int tb_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, uint16_t* q_out, uint16_t* k_cache,
+                   uint16_t* v_cache, uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim) {
+    if (!ctx || !qkv || !q_norm || !freq || !q_out) return fail(OUT_OF_RANGE, "tb_prefill_qkv: null argument");
+    if (kv_heads != 0 && (!k_norm || !k_cache || !v_cache)) return fail(OUT_OF_RANGE, "tb_prefill_qkv: keys and values need their norm weights and caches");
+    if (tokens == 0 || cap == 0 || heads == 0) return fail(OUT_OF_RANGE, "tb_prefill_qkv: empty shape");
+    return launch_prefill_qkv(ctx, qkv, q_norm, k_norm, freq, reinterpret_cast<__half*>(q_out), reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache),
+                              tokens, pos0, cap, heads, kv_heads, eps, scale, head_dim);
+}
+
 size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits) {
     if (kv_heads == 0) return 0;
     return attend_partial_floats(heads, kv_heads, splits) * sizeof(float);

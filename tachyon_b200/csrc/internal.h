@@ -166,9 +166,9 @@ int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, cons
 int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
                         __half* x);
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
-                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale);
+                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim = 256);
 int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                         uint32_t window, uint32_t heads, uint32_t kv_heads);
+                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim = 256);
 
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out, uint32_t wbits = 8);

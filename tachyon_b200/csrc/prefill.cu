@@ -76,127 +76,159 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float
 }
 
 // ---- q / k / v preparation: one warp per (token, head) -----------------------------------------------------------------
-// Queries: norm (weights) + RoPE, times scale*log2(e), f16 [token][head][256].  Keys: norm (weights) + RoPE -> cache
-// slot (pos0 + token) % cap; values: norm without weights -> cache.  A lane holds dims 4l..4l+3 and 128+4l..128+4l+3.
+// Queries: norm (weights) + RoPE, times scale*log2(e), f16 [token][head][DH].  Keys: norm (weights) + RoPE -> cache
+// slot (pos0 + token) % cap; values: norm without weights -> cache.  The reference's kv_256 / kv_512 and query_256 /
+// query_512 (crates/tachyon/src/ptx/attend.rs:472-556) in one launch.  A lane holds dims (DH/64) l .. and their RoPE
+// partners DH/2 + (DH/64) l ..
+template <int DH>
 __global__ void __launch_bounds__(128) prefill_qkv_kernel(const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out,
                                                           __half* kc, __half* vc, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps,
                                                           float qscale) {
+    constexpr int H2 = DH / 64, NV = 2 * H2;  // values a lane holds of each half, and in all
     const uint32_t rows = heads + 2 * kv_heads;
     const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows, r = item % rows;
     const int lane = threadIdx.x & 31;
-    const float* src = qkv + ((size_t)token * rows + r) * D;
-    const float4 a = *reinterpret_cast<const float4*>(src + 4 * lane), b = *reinterpret_cast<const float4*>(src + 128 + 4 * lane);
-    float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const float* src = qkv + ((size_t)token * rows + r) * DH;
+    float x[NV];
+#pragma unroll
+    for (int half = 0; half < 2; half++)
+#pragma unroll
+        for (int v = 0; v < H2 / 4; v++) {
+            const float4 t = *reinterpret_cast<const float4*>(src + half * (DH / 2) + H2 * lane + 4 * v);
+            x[half * H2 + 4 * v] = t.x, x[half * H2 + 4 * v + 1] = t.y, x[half * H2 + 4 * v + 2] = t.z, x[half * H2 + 4 * v + 3] = t.w;
+        }
     float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) ss = fmaf(x[i], x[i], ss);
-    const float rn = rsqrtf(warp_sum(ss) / (float)D + eps);
+    for (int i = 0; i < NV; i++) ss = fmaf(x[i], x[i], ss);
+    const float rn = rsqrtf(warp_sum(ss) / (float)DH + eps);
     const bool is_q = r < heads, is_k = !is_q && r < heads + kv_heads;
     const float* w = is_q ? q_norm : (is_k ? k_norm : nullptr);
 #pragma unroll
-    for (int i = 0; i < 8; i++) x[i] *= rn * (w ? __ldg(w + (i < 4 ? 4 * lane + i : 128 + 4 * lane + i - 4)) : 1.0f);
+    for (int i = 0; i < NV; i++) x[i] *= rn * (w ? __ldg(w + (i < H2 ? H2 * lane + i : DH / 2 + H2 * lane + i - H2)) : 1.0f);
     const uint32_t pos = pos0 + token;
     if (is_q || is_k) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
+        for (int i = 0; i < H2; i++) {
             float sn, cs;
-            sincosf((float)pos * __ldg(freq + 4 * lane + i), &sn, &cs);
-            const float p = x[i], q = x[i + 4];
+            sincosf((float)pos * __ldg(freq + H2 * lane + i), &sn, &cs);
+            const float p = x[i], q = x[i + H2];
             x[i] = p * cs - q * sn;
-            x[i + 4] = q * cs + p * sn;
+            x[i + H2] = q * cs + p * sn;
         }
     }
     __half* dst;
     if (is_q) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) x[i] *= qscale;
-        dst = q_out + ((size_t)token * heads + r) * D;
+        for (int i = 0; i < NV; i++) x[i] *= qscale;
+        dst = q_out + ((size_t)token * heads + r) * DH;
     } else {
         const uint32_t g = is_k ? r - heads : r - heads - kv_heads;
-        dst = (is_k ? kc : vc) + ((size_t)g * cap + pos % cap) * D;
+        dst = (is_k ? kc : vc) + ((size_t)g * cap + pos % cap) * DH;
     }
-    const __half2 h0 = __floats2half2_rn(x[0], x[1]), h1 = __floats2half2_rn(x[2], x[3]), h2 = __floats2half2_rn(x[4], x[5]), h3 = __floats2half2_rn(x[6], x[7]);
-    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-    *reinterpret_cast<uint2*>(dst + 128 + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+#pragma unroll
+    for (int half = 0; half < 2; half++)
+#pragma unroll
+        for (int v = 0; v < H2 / 4; v++) {
+            const __half2 h0 = __floats2half2_rn(x[half * H2 + 4 * v], x[half * H2 + 4 * v + 1]), h1 = __floats2half2_rn(x[half * H2 + 4 * v + 2], x[half * H2 + 4 * v + 3]);
+            *reinterpret_cast<uint2*>(dst + half * (DH / 2) + H2 * lane + 4 * v) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+        }
 }
 
 // ---- flash attention --------------------------------------------------------------------------------------------------
-// A block: 16 tokens x the 4 (or `group`) query heads of one key-value head; warp w owns head g*group + w (16 rows).
-// Keys are visited in tiles of 32 positions that start at multiples of 32, so a token's sums do not depend on how the
-// prompt was cut into chunks (ptx/flash.rs:9-17).  Token at position p sees positions p - window < j <= p.
-constexpr int FT = 16, FK = 32, LDS = D + 8;  // tokens per block, keys per tile, padded row length in halves
+// The reference's flash_256 / flash_512 (crates/tachyon/src/ptx/flash.rs:1-23).  A block: 16 tokens x the `group` (up
+// to 4) query heads of one key-value head.  SPLIT warps share the 16 rows of a head: each scores all the tile's keys
+// and sums its 1/SPLIT of the head's width, which keeps a thread's sums in registers at heads of 512 (SPLIT 2; heads
+// of 256 run SPLIT 1).  Keys are visited in tiles of 32 positions that start at multiples of 32, so a token's sums do
+// not depend on how the prompt was cut into chunks (flash.rs:9-12).  Token at position p sees p - window < j <= p.
+constexpr int FT = 16, FK = 32;  // tokens per block, keys per tile
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
 }
-__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
 }
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+// 16 bytes global -> shared without passing through registers; `bytes` 0 fills the 16 bytes with zeros instead.
+__device__ __forceinline__ void cp_async_16_zfill(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(128) prefill_flash_kernel(const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0,
-                                                            uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads) {
+template <int DH, int SPLIT>
+__global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens,
+                                                                    uint32_t pos0, uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads) {
+    constexpr int LDS = DH + 8;        // padded row length in halves
+    constexpr int DW = DH / SPLIT;     // dimensions a warp sums
     extern __shared__ __align__(16) uint8_t raw[];
     __half* Qs = reinterpret_cast<__half*>(raw);   // [group * FT][LDS]
     const uint32_t group = heads / kv_heads;
-    __half* Ks = Qs + group * FT * LDS;            // [FK][LDS]
-    __half* Vs = Ks + FK * LDS;                    // [FK][LDS]
+    __half* KV = Qs + group * FT * LDS;            // two stages of keys [FK][LDS] then values [FK][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hw = warp / SPLIT, part = warp % SPLIT;  // the head (of the group) this warp serves, and its share of the width
     const uint32_t t0 = blockIdx.x * FT, g = blockIdx.y;
-    const uint32_t nthreads = group * 32;
+    const uint32_t nthreads = group * SPLIT * 32;
 
     // Queries of this block: row w*16 + i is (head g*group + w, token t0 + i).
-    for (uint32_t c = tid; c < group * FT * (D / 8); c += nthreads) {
-        const uint32_t row = c / (D / 8), ch = c % (D / 8), w = row / FT, i = row % FT, t = t0 + i;
+    for (uint32_t c = tid; c < group * FT * (DH / 8); c += nthreads) {
+        const uint32_t row = c / (DH / 8), ch = c % (DH / 8), w = row / FT, i = row % FT, t = t0 + i;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < tokens) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * heads + g * group + w) * D + ch * 8);
+        if (t < tokens) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * heads + g * group + w) * DH + ch * 8);
         *reinterpret_cast<uint4*>(Qs + row * LDS + ch * 8) = v;
     }
     const uint32_t p_first = pos0 + t0, p_last = pos0 + min(t0 + FT, tokens) - 1;
     const uint32_t lo = p_first + 1 > window ? p_first + 1 - window : 0;  // oldest position any token of the block sees
     const uint32_t tile0 = lo / FK * FK;
 
-    float o[D / 8][4];
+    float o[DW / 8][4];
 #pragma unroll
-    for (int nb = 0; nb < D / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+    for (int nb = 0; nb < DW / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const uint32_t row_a = lane >> 2, row_b = row_a + 8;                   // the two rows this lane holds
     const uint32_t pa = pos0 + t0 + row_a, pb = pos0 + t0 + row_b;        // their positions
 
-    for (uint32_t j0 = tile0; j0 <= p_last; j0 += FK) {
-        __syncthreads();  // the previous tile is no longer read (and, first time, Qs is written)
-        for (uint32_t c = tid; c < FK * (D / 8); c += nthreads) {
-            const uint32_t r = c / (D / 8), ch = c % (D / 8), j = j0 + r;
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-            if (j <= p_last) {
-                const size_t at = ((size_t)g * cap + j % cap) * D + ch * 8;
-                kv = __ldg(reinterpret_cast<const uint4*>(kc + at));
-                vv = __ldg(reinterpret_cast<const uint4*>(vc + at));
-            }
-            *reinterpret_cast<uint4*>(Ks + r * LDS + ch * 8) = kv;
-            *reinterpret_cast<uint4*>(Vs + r * LDS + ch * 8) = vv;
+    // Tiles arrive through cp.async, one tile ahead of the products: the copy of tile i + 1 is in flight while tile i is
+    // multiplied.  Rows past the block's last position are filled with zeros (stale cache rows could hold anything).
+    auto fetch = [&](uint32_t j0, uint32_t stage) {
+        __half* Kd = KV + stage * (2 * FK * LDS);
+        __half* Vd = Kd + FK * LDS;
+        for (uint32_t c = tid; c < FK * (DH / 8); c += nthreads) {
+            const uint32_t r = c / (DH / 8), ch = c % (DH / 8), j = j0 + r;
+            const uint32_t bytes = j <= p_last ? 16u : 0u;
+            const size_t at = ((size_t)g * cap + (j <= p_last ? j % cap : 0u)) * DH + ch * 8;
+            cp_async_16_zfill(Kd + r * LDS + ch * 8, kc + at, bytes);
+            cp_async_16_zfill(Vd + r * LDS + ch * 8, vc + at, bytes);
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    fetch(tile0, 0);
+    uint32_t stage = 0;
+    for (uint32_t j0 = tile0; j0 <= p_last; j0 += FK, stage ^= 1u) {
+        cp_async_wait_all();
+        __syncthreads();  // this tile is visible to all; the other stage is no longer read (and, first time, Qs is written)
+        if (j0 + FK <= p_last) fetch(j0 + FK, stage ^ 1u);
+        const __half* Ks = KV + stage * (2 * FK * LDS);
+        const __half* Vs = Ks + FK * LDS;
         // Scores S = Q K^T for this warp's 16 rows and the tile's 32 keys.
         float sc[FK / 8][4];
 #pragma unroll
         for (int nb = 0; nb < FK / 8; nb++) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f;
 #pragma unroll 4
-        for (int ks = 0; ks < D / 16; ks++) {
+        for (int ks = 0; ks < DH / 16; ks++) {
             uint32_t a[4];
-            ldmatrix_x4(a, Qs + (warp * FT + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+            ldmatrix_x4(a, Qs + (hw * FT + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-            for (int nb = 0; nb < FK / 8; nb++) {
-                uint32_t b[2];
-                ldmatrix_x2(b, Ks + (nb * 8 + (lane & 7)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
-                mma_16816(sc[nb], a, b);
+            for (int nb = 0; nb < FK / 8; nb += 2) {  // two blocks of eight keys per load
+                uint32_t b[4];
+                ldmatrix_x4(b, Ks + (nb * 8 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma_16816(sc[nb], a, b0);
+                mma_16816(sc[nb + 1], a, b1);
             }
         }
         // Mask, running maximum and sums (scores are already in base 2: the queries carry scale*log2(e)).
@@ -239,31 +271,38 @@ __global__ void __launch_bounds__(128) prefill_flash_kernel(const __half* q, con
             lt[h] += __shfl_xor_sync(0xffffffffu, lt[h], 2);
             l_run[h] = l_run[h] * corr[h] + lt[h];
         }
-        // O = O * corr + P V.
+        // O = O * corr + P V over this warp's share of the width; a tile that moved no maximum of the warp skips the scaling.
+        const bool moved = __any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f);
+        const __half* Vw = Vs + part * DW;
 #pragma unroll
-        for (int nb = 0; nb < D / 8; nb++) {
-            o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+        for (int nb = 0; nb < DW / 8; nb += 2) {  // two blocks of eight dimensions per load
+            if (moved) {
+                o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+                o[nb + 1][0] *= corr[0], o[nb + 1][1] *= corr[0], o[nb + 1][2] *= corr[1], o[nb + 1][3] *= corr[1];
+            }
 #pragma unroll
             for (int kk = 0; kk < FK / 16; kk++) {
-                uint32_t b[2];
-                ldmatrix_x2_trans(b, Vs + (kk * 16 + (lane & 15)) * LDS + nb * 8);
-                mma_16816(o[nb], pfrag[kk], b);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, Vw + (kk * 16 + (lane & 15)) * LDS + (nb + (lane >> 4)) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma_16816(o[nb], pfrag[kk], b0);
+                mma_16816(o[nb + 1], pfrag[kk], b1);
             }
         }
     }
-    // Normalise and store f16 [token][heads * 256].
+    // Normalise and store f16 [token][heads * DH].
     const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
-    const uint32_t head = g * group + warp;
+    const uint32_t head = g * group + hw;
 #pragma unroll
-    for (int nb = 0; nb < D / 8; nb++) {
-        const uint32_t col = head * D + nb * 8 + 2 * (lane & 3);
+    for (int nb = 0; nb < DW / 8; nb++) {
+        const uint32_t col = head * DH + part * DW + nb * 8 + 2 * (lane & 3);
         if (t0 + row_a < tokens) {
             const __half2 v = __floats2half2_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
-            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_a) * heads * D + col) = v;
+            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_a) * heads * DH + col) = v;
         }
         if (t0 + row_b < tokens) {
             const __half2 v = __floats2half2_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
-            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_b) * heads * D + col) = v;
+            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_b) * heads * DH + col) = v;
         }
     }
 }
@@ -286,26 +325,33 @@ int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* 
 }
 
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
-                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale) {
+                       uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim) {
     const uint32_t items = tokens * (heads + 2 * kv_heads);
     if (items % 4 != 0) return fail(UNSUPPORTED, "prefill qkv: heads + 2*kv_heads must be a multiple of 4");
-    prefill_qkv_kernel<<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps,
-                                                            scale * 1.4426950408889634f);
+    if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill qkv: heads of 256 or 512");
+    const float qscale = scale * 1.4426950408889634f;
+    if (head_dim == 512) prefill_qkv_kernel<512><<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps, qscale);
+    else prefill_qkv_kernel<256><<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps, qscale);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
 
 int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                         uint32_t window, uint32_t heads, uint32_t kv_heads) {
+                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
     const uint32_t group = heads / kv_heads;
-    if (group < 1 || group > 4) return fail(UNSUPPORTED, "prefill attention: 1 to 4 query heads per key-value head");
-    const size_t smem = (size_t)(group * FT + 2 * FK) * LDS * 2;
+    if (group < 1 || group > 4 || heads % kv_heads != 0) return fail(UNSUPPORTED, "prefill attention: 1 to 4 query heads per key-value head");
+    if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill attention: heads of 256 or 512");
+    // queries, two stages of keys and values; rows padded by 8 halves
+    auto bytes = [&](uint32_t grp) { return (size_t)(grp * FT + 4 * FK) * (head_dim + 8) * 2; };
     static bool configured[16] = {};
     if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(prefill_flash_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((4 * FT + 2 * FK) * LDS * 2)));
+        TB_CUDA(cudaFuncSetAttribute(prefill_flash_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((4 * FT + 4 * FK) * (256 + 8) * 2)));
+        TB_CUDA(cudaFuncSetAttribute(prefill_flash_kernel<512, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((4 * FT + 4 * FK) * (512 + 8) * 2)));
         configured[ctx->gpu & 15] = true;
     }
-    prefill_flash_kernel<<<dim3((tokens + FT - 1) / FT, kv_heads), group * 32, smem, ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
+    const dim3 grid((tokens + FT - 1) / FT, kv_heads);
+    if (head_dim == 512) prefill_flash_kernel<512, 2><<<grid, group * 64, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
+    else prefill_flash_kernel<256, 1><<<grid, group * 32, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
