@@ -173,7 +173,7 @@ TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales,
  * at position pos0 + t, attends positions p - window < j <= p of the cache (f16 [kv_heads][cap][head_dim], position j in
  * slot j % cap, the chunk's own keys and values already stored).  q: device f16 [tokens][heads][head_dim] as the query
  * kernel leaves them, already multiplied by scale * log2(e); out: device f16 [tokens][heads * head_dim].
- * head_dim 256 or 512; heads / kv_heads in {1, 2, 4}.  Key tiles start at multiples of 32 positions, so a token's sums
+ * head_dim 256 or 512; heads / kv_heads in {1, 2, 4, 8}.  Key tiles start at multiples of 32 positions, so a token's sums
  * do not depend on how the prompt was cut into chunks.
  */
 TB_API int tb_prefill_attend(tb_context* ctx, const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out, uint32_t tokens,
@@ -289,6 +289,8 @@ typedef struct tb_config {
     uint32_t shared;        /* Config::shared: the last `shared` layers project no keys or values and attend over the cache of the
                                last earlier layer of their kind (Config::source, model/mod.rs:138-143); their qkv matrix holds
                                the query rows only */
+    uint32_t global_head_dim; /* Config::head_dim[1]: head size of global layers, 256 or 512; 0 = head_dim */
+    uint32_t global_kv_heads; /* Config::kv_heads[1]: key-value heads of global layers; 0 = kv_heads */
 } tb_config;
 
 /* model::Settings (decode.rs:64-76) plus what this build adds. */

@@ -37,7 +37,7 @@ def lib() -> C.CDLL:
 class Config(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("hidden", "ffn", "heads", "kv_heads", "head_dim", "vocab", "layers", "window", "context")] + [
         (n, C.c_float) for n in ("theta_sliding", "theta_global", "fraction_global", "eps", "softcap", "attn_scale", "embed_scale")
-    ] + [("weight_bits", C.c_int32)]
+    ] + [("weight_bits", C.c_int32), ("global_head_dim", C.c_int32), ("global_kv_heads", C.c_int32)]
 
 
 class Layer(C.Structure):

@@ -18,8 +18,10 @@ class OracleModel:
 
     def __init__(self, cfg, seed: int, context: int, chunk: int = 0, layers: int | None = None, weight_bits: int = 8):
         self.cfg, self.keep = cfg, []
-        H, F, D = cfg.hidden, cfg.ffn, cfg.head_dim
-        nq, nkv = cfg.heads * D, cfg.kv_heads * D
+        H, F = cfg.hidden, cfg.ffn
+        # Config::head_dim / Config::kv_heads of the two kinds of layer (model/mod.rs:34-37); 0 = as the sliding layers
+        dims = (cfg.head_dim, getattr(cfg, "global_head_dim", 0) or cfg.head_dim)
+        kvs = (cfg.kv_heads, getattr(cfg, "global_kv_heads", 0) or cfg.kv_heads)
         L = cfg.layers if layers is None else layers
         smul = 0.02 / 8 if weight_bits == 4 else 0.02 / 127
         group = 64 if weight_bits == 4 else 32
@@ -45,6 +47,8 @@ class OracleModel:
             b = 32 * i
             ly = self.layers[i]
             is_global = bool(cfg.global_every) and (i + 1) % cfg.global_every == 0
+            D, kvh = dims[int(is_global)], kvs[int(is_global)]
+            nq, nkv = cfg.heads * D, kvh * D
             # Config::source (model/mod.rs:138-143): the last `shared` layers reuse the cache of the last earlier layer of their kind
             first_shared = L - getattr(cfg, "shared", 0)
             source = i
@@ -60,7 +64,7 @@ class OracleModel:
             scalar = vec(f"{i}.layer_scalar", b + 14, 1, 0.95, 1.0)
             cap = context if is_global else cfg.window + chunk
             if source == i:
-                kc, vc = np.zeros((cfg.kv_heads, cap, D), np.uint16), np.zeros((cfg.kv_heads, cap, D), np.uint16)
+                kc, vc = np.zeros((kvh, cap, D), np.uint16), np.zeros((kvh, cap, D), np.uint16)
             else:
                 kc, vc = self.caches[source]
             self.caches.append((kc, vc))
@@ -70,10 +74,10 @@ class OracleModel:
                 setattr(ly, name, a.ctypes.data)
             ly.layer_scalar, ly.global_, ly.kc, ly.vc, ly.cap = float(scalar[0]), int(is_global), kc.ctypes.data, vc.ctypes.data, cap
             ly.shared = int(source != i)
-        oc = oracle.Config(hidden=H, ffn=F, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=D, vocab=cfg.vocab, layers=L, window=cfg.window,
+        oc = oracle.Config(hidden=H, ffn=F, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, vocab=cfg.vocab, layers=L, window=cfg.window,
                            context=context, theta_sliding=cfg.theta_sliding, theta_global=cfg.theta_global, fraction_global=cfg.fraction_global,
                            eps=cfg.eps, softcap=cfg.softcap, attn_scale=cfg.attn_scale, embed_scale=bf16_round(float(np.sqrt(np.float32(H)))),
-                           weight_bits=weight_bits)
+                           weight_bits=weight_bits, global_head_dim=dims[1], global_kv_heads=kvs[1])
         self.model = oracle.Model(cfg=oc, embed=self.embed.ctypes.data, embed_s=self.embed_s.ctypes.data, norm=self.norm.ctypes.data,
                                   layers=C.cast(self.layers, C.POINTER(oracle.Layer)))
 

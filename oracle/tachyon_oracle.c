@@ -581,6 +581,7 @@ typedef struct {
     int32_t hidden, ffn, heads, kv_heads, head_dim, vocab, layers, window, context;
     float theta_sliding, theta_global, fraction_global, eps, softcap, attn_scale, embed_scale;
     int32_t weight_bits; /* 0 or 8: int8 codes, a scale per 32; 4: the reference's Q4 (quant.rs:47-82), a scale per 64 */
+    int32_t global_head_dim, global_kv_heads; /* Config::head_dim[1], Config::kv_heads[1] (model/mod.rs:34-37); 0 = as the sliding layers */
 } tbo_config;
 
 typedef struct {
@@ -651,11 +652,13 @@ static float gelu_f32(float x) { return 0.5f * x * (1.0f + tanhf(sqrtf(2.0f / (f
  * layers and skips the head (for timing a bounded sample); hidden state is left in `h_out` when given. */
 TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, float *logits, int stop_layer, float *h_out) {
     const tbo_config *c = &m->cfg;
-    size_t H = (size_t)c->hidden, D = (size_t)c->head_dim, F = (size_t)c->ffn;
-    size_t nq = (size_t)c->heads * D, nkv = (size_t)c->kv_heads * D;
-    float *x = (float *)malloc(H * 4), *h = (float *)malloc(H * 4), *qkv = (float *)malloc((nq + 2 * nkv) * 4);
-    float *att = (float *)malloc(nq * 4), *y = (float *)malloc(H * 4), *gu = (float *)malloc(2 * F * 4), *a = (float *)malloc(F * 4);
-    float *freq = (float *)malloc(D / 2 * 4), *tmp = (float *)malloc(D * 4);
+    size_t H = (size_t)c->hidden, F = (size_t)c->ffn;
+    size_t Dg = (size_t)(c->global_head_dim ? c->global_head_dim : c->head_dim), KVg = (size_t)(c->global_kv_heads ? c->global_kv_heads : c->kv_heads);
+    size_t Dmax = Dg > (size_t)c->head_dim ? Dg : (size_t)c->head_dim;
+    size_t nq_max = (size_t)c->heads * Dmax, nkv_max = (KVg * Dg > (size_t)c->kv_heads * (size_t)c->head_dim) ? KVg * Dg : (size_t)c->kv_heads * (size_t)c->head_dim;
+    float *x = (float *)malloc(H * 4), *h = (float *)malloc(H * 4), *qkv = (float *)malloc((nq_max + 2 * nkv_max) * 4);
+    float *att = (float *)malloc(nq_max * 4), *y = (float *)malloc(H * 4), *gu = (float *)malloc(2 * F * 4), *a = (float *)malloc(F * 4);
+    float *freq = (float *)malloc(Dmax / 2 * 4), *tmp = (float *)malloc(Dmax * 4);
     /* tiny.rs:233: the embedding row times sqrt(hidden) (model/decode.rs:571 rounds that factor to bfloat16; the caller
      * passes the factor it wants in embed_scale). */
     for (size_t i = 0; i < H; i++) {
@@ -666,6 +669,8 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
     int nl = stop_layer > 0 ? stop_layer : c->layers;
     for (int li = 0; li < nl; li++) {
         tbo_layer *L = &m->layers[li];
+        size_t D = L->global ? Dg : (size_t)c->head_dim, kvh = L->global ? KVg : (size_t)c->kv_heads; /* this kind's head size and key-value heads */
+        size_t nq = (size_t)c->heads * D, nkv = kvh * D;
         tbo_rope_freq(L->global ? c->theta_global : c->theta_sliding, (int)D, L->global ? c->fraction_global : 1.0f, freq);
         rms_f32(x, L->input_ln, H, c->eps, h);                                  /* tiny.rs:278 */
         matvec(c, L->qkv, L->qkv_s, h, nq + (L->shared ? 0 : 2 * nkv), H, qkv);  /* :279, 286-287 (fused q, k, v) */
@@ -675,7 +680,7 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
             memcpy(qkv + (size_t)hd * D, tmp, D * 4);
         }
         uint32_t cap = (uint32_t)L->cap, slot = pos % cap;
-        for (int g = 0; g < (L->shared ? 0 : c->kv_heads); g++) {               /* :288-289: k-norm + RoPE, v-norm without weights */
+        for (int g = 0; g < (L->shared ? 0 : (int)kvh); g++) {                  /* :288-289: k-norm + RoPE, v-norm without weights */
             rms_f32(qkv + nq + (size_t)g * D, L->k_norm, D, c->eps, tmp);
             rotate_f32(tmp, D, freq, pos);
             for (size_t i = 0; i < D; i++) L->kc[((size_t)g * cap + slot) * D + i] = tbo_f16_bits(tmp[i]);
@@ -686,7 +691,7 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
          * holds f16 (model/decode.rs keeps it so); the reference's f32 test model keeps f32. */
         uint32_t win = L->global ? (uint32_t)c->context : (uint32_t)c->window;
         size_t n = (pos + 1 < win) ? pos + 1 : win;
-        int group = c->heads / c->kv_heads;
+        int group = c->heads / (int)kvh;
         for (int hd = 0; hd < c->heads; hd++) {
             int g = hd / group;
             float *sc = (float *)malloc(n * 4), mx = -INFINITY, sum = 0.0f;

@@ -48,6 +48,8 @@ struct Layer {
     int source = -1;  // >= 0: this layer projects no keys or values and attends over that layer's cache
     __half *kc = nullptr, *vc = nullptr;
     uint32_t cap = 0, window = 0, splits = 1;
+    uint32_t dim = 256, kvh = 0;  // head size and key-value heads of this layer's kind (Config::head_dim, Config::kv_heads)
+    uint32_t nq = 0, nkv = 0;      // heads * dim, kvh * dim
 };
 
 constexpr uint32_t TRACE = 1u << 16;  // tokens remembered by position (a power of two)
@@ -104,8 +106,11 @@ struct tb_decoder {
 
 namespace {
 
-uint32_t nq(const tb_config& c) { return c.heads * c.head_dim; }
-uint32_t nkv(const tb_config& c) { return c.kv_heads * c.head_dim; }
+// Head size and key-value heads of the two kinds of layer (0 sliding, 1 global): Config::head_dim, Config::kv_heads.
+uint32_t dim_of(const tb_config& c, int kind) { return kind && c.global_head_dim ? c.global_head_dim : c.head_dim; }
+uint32_t kvh_of(const tb_config& c, int kind) { return kind && c.global_kv_heads ? c.global_kv_heads : c.kv_heads; }
+uint32_t max_nq(const tb_config& c) { return c.heads * std::max(dim_of(c, 0), dim_of(c, 1)); }
+uint32_t max_nkv(const tb_config& c) { return std::max(kvh_of(c, 0) * dim_of(c, 0), kvh_of(c, 1) * dim_of(c, 1)); }
 
 float bf16_round(float v) {
     uint32_t b;
@@ -126,11 +131,21 @@ std::vector<float> rope_freq(float theta, uint32_t d, float fraction) {
 int validate(const tb_config& c, const tb_settings& s) {
     if (c.hidden != 2048) return fail(UNSUPPORTED, "decoder: hidden must be 2048 (the width the fused norm prologue is built for)");
     if (c.head_dim != 256) return fail(UNSUPPORTED, "decoder: head_dim must be 256");
-    if (c.heads == 0 || c.kv_heads == 0 || c.heads % c.kv_heads != 0) return fail(UNSUPPORTED, "decoder: heads must be a multiple of kv_heads");
-    const uint32_t group = c.heads / c.kv_heads;
-    if (group != 1 && group != 2 && group != 4) return fail(UNSUPPORTED, "decoder: 1, 2 or 4 query heads per key-value head");
+    if (c.global_head_dim != 0 && c.global_head_dim != 256 && c.global_head_dim != 512) return fail(UNSUPPORTED, "decoder: global_head_dim must be 256 or 512");
+    if (c.global_head_dim == 512 && s.fused) return fail(UNSUPPORTED, "decoder: the single-kernel step has no attention for heads of 512");
+    for (int kind = 0; kind < 2; kind++) {
+        const uint32_t kvh = kvh_of(c, kind);
+        if (c.heads == 0 || kvh == 0 || c.heads % kvh != 0) return fail(UNSUPPORTED, "decoder: heads must be a multiple of kv_heads");
+        const uint32_t group = c.heads / kvh;
+        if (group != 1 && group != 2 && group != 4 && group != 8) return fail(UNSUPPORTED, "decoder: 1, 2, 4 or 8 query heads per key-value head");
+        if (group == 8 && s.fused) return fail(UNSUPPORTED, "decoder: the single-kernel step has no attention for eight query heads to a key-value head");
+    }
     const uint32_t qcols = c.heads * c.head_dim;
     if (qcols != 2048 && qcols != 4096 && qcols != 8192 && qcols != 16384 && qcols % 32 != 0) return fail(UNSUPPORTED, "decoder: heads*head_dim must be a multiple of 32");
+    if (c.global_head_dim == 512) {
+        const uint32_t wide = c.heads * 512;
+        if (wide != 2048 && wide != 4096 && wide != 8192 && wide != 16384) return fail(UNSUPPORTED, "decoder: heads*512 must be 2048, 4096, 8192 or 16384");
+    }
     if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
     if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
     if (s.context == 0 || s.context > TRACE) return fail(OUT_OF_RANGE, "decoder: context must be in 1..65536");
@@ -179,16 +194,17 @@ void layout(tb_decoder* d, char* base) {
                     L.source = j;
                     break;
                 }
-        mat(L.qkv, nq(c) + (L.source < 0 ? 2 * nkv(c) : 0), c.hidden);
-        mat(L.o, c.hidden, nq(c));
+        L.dim = dim_of(c, L.global), L.kvh = kvh_of(c, L.global), L.nq = c.heads * L.dim, L.nkv = L.kvh * L.dim;
+        mat(L.qkv, L.nq + (L.source < 0 ? 2 * L.nkv : 0), c.hidden);
+        mat(L.o, c.hidden, L.nq);
         mat(L.gate_up, 2 * c.ffn, c.hidden);
         mat(L.down, c.hidden, c.ffn);
-        vec(L.q_norm, c.head_dim), vec(L.k_norm, c.head_dim);
+        vec(L.q_norm, L.dim), vec(L.k_norm, L.dim);
         vec(L.input_ln, c.hidden), vec(L.post_attn, c.hidden), vec(L.pre_ffn, c.hidden), vec(L.post_ffn, c.hidden);
         // Caches: a global layer keeps `context` positions, a sliding one a ring of window + chunk (decode.rs:152).
         L.window = L.global ? d->settings.context : c.window;
         L.cap = L.global ? d->settings.context : c.window + d->settings.chunk;
-        const size_t cache = (size_t)c.kv_heads * L.cap * c.head_dim * 2;
+        const size_t cache = (size_t)L.kvh * L.cap * L.dim * 2;
         if (L.source >= 0) {
             L.kc = d->layers[L.source].kc, L.vc = d->layers[L.source].vc;
         } else {
@@ -200,23 +216,24 @@ void layout(tb_decoder* d, char* base) {
         static const uint32_t span_sliding = getenv("TACHYON_B200_SPAN_SLIDING") ? (uint32_t)atoi(getenv("TACHYON_B200_SPAN_SLIDING")) : 64u;
         const uint32_t per = std::max(16u, L.global ? span_global : span_sliding);
         L.splits = (L.window + per - 1) / per;
-        const uint32_t most = (uint32_t)(2 * d->ctx->sms) / c.kv_heads;
+        const uint32_t most = (uint32_t)(2 * d->ctx->sms) / L.kvh;
         if (L.splits > most) L.splits = most;
         if (L.splits == 0) L.splits = 1;
         if (L.splits > max_splits) max_splits = L.splits;
     }
     vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
-    vec(d->qkv, nq(c) + 2 * nkv(c)), vec(d->att, nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
+    vec(d->qkv, max_nq(c) + 2 * max_nkv(c)), vec(d->att, max_nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
     vec(d->logits, c.vocab);
     vec(d->work, c.vocab);
     d->seen = reinterpret_cast<uint32_t*>(base + t.take(((size_t)c.vocab + 31) / 32 * 4));
     d->sampling = base + t.take(64);
     vec(d->sample_partial, (size_t)8 * 1024);
     d->sample_count = reinterpret_cast<uint32_t*>(base + t.take(4));
-    vec(d->partial, attend_partial_floats(c.heads, c.kv_heads, max_splits));
-    vec(d->freq[0], c.head_dim / 2), vec(d->freq[1], c.head_dim / 2);
-    vec(d->trig[0], (size_t)d->settings.context * c.head_dim), vec(d->trig[1], (size_t)d->settings.context * c.head_dim);
-    d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.kv_heads * 4));
+    // Attention scratch for the larger kind: per key-value head and split the maxima, sums and outputs of its query heads.
+    vec(d->partial, (size_t)c.heads * max_splits * (2 + std::max(dim_of(c, 0), dim_of(c, 1))));
+    vec(d->freq[0], dim_of(c, 0) / 2), vec(d->freq[1], dim_of(c, 1) / 2);
+    vec(d->trig[0], (size_t)d->settings.context * 256), vec(d->trig[1], (size_t)d->settings.context * 256);  // heads of 256 only
+    d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.heads * 4));
     d->state = reinterpret_cast<uint32_t*>(base + t.take(8));
     d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
     d->trace = reinterpret_cast<uint32_t*>(base + t.take((size_t)TRACE * 4));
@@ -225,8 +242,8 @@ void layout(tb_decoder* d, char* base) {
         const size_t T = d->settings.chunk;
         auto half = [&](__half*& v, size_t n) { v = reinterpret_cast<__half*>(base + t.take(n * 2)); };
         d->pf_tokens = reinterpret_cast<uint32_t*>(base + t.take(T * 4));
-        vec(d->pf_h, T * c.hidden), vec(d->pf_qkv, T * (nq(c) + 2 * nkv(c))), vec(d->pf_y, T * c.hidden);
-        half(d->pf_x, T * c.hidden), half(d->pf_q, T * nq(c)), half(d->pf_att, T * nq(c)), half(d->pf_g, T * c.ffn);
+        vec(d->pf_h, T * c.hidden), vec(d->pf_qkv, T * (max_nq(c) + 2 * max_nkv(c))), vec(d->pf_y, T * c.hidden);
+        half(d->pf_x, T * c.hidden), half(d->pf_q, T * max_nq(c)), half(d->pf_att, T * max_nq(c)), half(d->pf_g, T * c.ffn);
     }
     d->arena_bytes = t.end;
 }
@@ -294,12 +311,17 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         AttendParams a;
         a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0], a.trig = d->trig[L.global ? 1 : 0];
         a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = L.source < 0 ? 1 : 0;
-        a.heads = c.heads, a.kv_heads = c.kv_heads, a.scale = c.attn_scale, a.eps = c.eps;
+        a.heads = c.heads, a.kv_heads = L.kvh, a.scale = c.attn_scale, a.eps = c.eps;
         a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
         a.pf = hint(d, L.gate_up, 2, 0, PF);
-        a.defer = 1;  // the o projection merges the splits in its prologue
-        a.early = 1;  // caches and position are final long before the kernel in front of this one
-        if (d->collect) {
+        // Heads of 512, or eight query heads to a key-value head: attend512.cu's kernel, which merges its own splits and writes f32 heads.
+        const bool wide = L.dim == 512 || c.heads == 8 * L.kvh;
+        a.defer = wide ? 0 : 1;  // the o projection merges the splits in its prologue
+        a.early = wide ? 0 : 1;  // caches and position are final long before the kernel in front of this one
+        if (wide) {
+            if (d->collect) return fail(UNSUPPORTED, "fused step: no attention for this layer's heads");
+            TB_TRY(L.dim == 512 ? launch_attend_512(d->ctx, a) : launch_attend_256_shared(d->ctx, a));
+        } else if (d->collect) {
             StepPhase ph;
             ph.kind = PH_ATTEND, ph.a = a;
             d->collect->push_back(ph);
@@ -311,8 +333,10 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
 
         GemvParams o;
         o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
-        o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
-        o.att_heads = c.heads, o.att_kv = c.kv_heads;
+        if (!wide) {
+            o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
+            o.att_heads = c.heads, o.att_kv = L.kvh;
+        }
         o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 
@@ -382,7 +406,7 @@ bool find_tensor(tb_decoder* d, const std::string& name, Named& out) {
     if (rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), 0);
     if (rest.rfind("gate_up", 0) == 0) return mat(L.gate_up, rest.substr(7), 1);
     if (rest.rfind("down", 0) == 0) return mat(L.down, rest.substr(4), 0);
-    const size_t hb = (size_t)c.hidden * 4, db = (size_t)c.head_dim * 4;
+    const size_t hb = (size_t)c.hidden * 4, db = (size_t)L.dim * 4;
     if (rest == "q_norm") return out = {L.q_norm, db, 0, i}, true;
     if (rest == "k_norm") return out = {L.k_norm, db, 0, i}, true;
     if (rest == "input_layernorm") return out = {L.input_ln, hb, 0, i}, true;
@@ -457,10 +481,11 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     layout(d, d->arena);
     memset(d->words, 0, 64);
     for (int k = 0; k < 2; k++) {
-        const std::vector<float> f = rope_freq(k ? cfg->theta_global : cfg->theta_sliding, cfg->head_dim, k ? cfg->fraction_global : 1.0f);
+        const std::vector<float> f = rope_freq(k ? cfg->theta_global : cfg->theta_sliding, dim_of(*cfg, k), k ? cfg->fraction_global : 1.0f);
         e = cudaMemcpyAsync(d->freq[k], f.data(), f.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-        if (e == cudaSuccess && launch_rope_table(ctx, d->freq[k], d->settings.context, d->trig[k]) != OK) e = cudaErrorUnknown;
+        // The table of cosines and sines by position serves attend.cu's kernel (heads of 256) only.
+        if (e == cudaSuccess && dim_of(*cfg, k) == 256 && launch_rope_table(ctx, d->freq[k], d->settings.context, d->trig[k]) != OK) e = cudaErrorUnknown;
         if (e != cudaSuccess) {
             const int s = cuda_fail(e, "tb_decoder_open: rope tables");
             tb_decoder_close(d);
@@ -540,8 +565,8 @@ int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
         if (st == OK) st = launch_interleave_rows(ctx, tw, L.gate_up.w, c.ffn, c.hidden * bits / 8);
         if (st == OK) st = launch_interleave_rows(ctx, ts, L.gate_up.s, c.ffn, c.hidden / (bits == 4 ? 64 : 32) * 2);
         if (st == OK) st = mat(L.down, b + 6);
-        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 8, L.q_norm, c.head_dim, 0.15f, 0.35f);
-        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 9, L.k_norm, c.head_dim, 0.15f, 0.35f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 8, L.q_norm, L.dim, 0.15f, 0.35f);
+        if (st == OK) st = launch_fill_uniform(ctx, seed, b + 9, L.k_norm, L.dim, 0.15f, 0.35f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 10, L.input_ln, c.hidden, 0.5f, 1.5f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 11, L.post_attn, c.hidden, 0.5f, 1.5f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 12, L.pre_ffn, c.hidden, 0.5f, 1.5f);
@@ -570,7 +595,7 @@ int tb_decoder_fill_cache(tb_decoder* d, uint64_t seed, uint32_t positions) {
         Layer& L = d->layers[i];
         if (L.source >= 0) continue;  // a shared layer has no cache of its own
         // Position p lives in slot p % cap; filling whole caches covers every slot a window can reach.
-        const size_t n = (size_t)c.kv_heads * L.cap * c.head_dim;
+        const size_t n = (size_t)L.kvh * L.cap * L.dim;
         TB_TRY(launch_fill_gauss_f16(d->ctx, seed, (1ull << 21) + 2ull * i, L.kc, n, 1.0f));
         TB_TRY(launch_fill_gauss_f16(d->ctx, seed, (1ull << 21) + 2ull * i + 1, L.vc, n, 1.0f));
     }
@@ -709,7 +734,7 @@ int tb_decoder_run(tb_decoder* d, uint32_t token, uint32_t steps, uint32_t* toke
 static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint32_t pos0) {
     const tb_config& c = d->cfg;
     tb_context* ctx = d->ctx;
-    const uint32_t H = c.hidden, NQ = nq(c);
+    const uint32_t H = c.hidden;
     TB_CUDA(cudaMemcpyAsync(d->pf_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
     TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h, d->embed.bits));
     for (uint32_t i = 0; i < c.layers; i++) {
@@ -723,10 +748,10 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
         TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, L.qkv.rows, H, d->pf_qkv, 0, L.qkv.bits));
         // A shared layer has query rows only: nothing to append to the cache it reads.
         TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads,
-                                  L.source < 0 ? c.kv_heads : 0, c.eps, c.attn_scale));
+                                  L.source < 0 ? L.kvh : 0, c.eps, c.attn_scale, L.dim));
         if (i + 1 == c.layers) break;
-        TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, c.kv_heads));
-        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, NQ, d->pf_y, 0, L.o.bits));
+        TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, L.kvh, L.dim));
+        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, L.nq, d->pf_y, 0, L.o.bits));
         TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_attn, L.pre_ffn, n, H, c.eps, 1.0f, d->pf_x));
         TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2, L.gate_up.bits));
         TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0, L.down.bits));
@@ -782,7 +807,7 @@ int tb_decoder_step_bytes(tb_decoder* d, uint64_t* weight_bytes, uint64_t* cache
     for (const Layer& L : d->layers) {
         for (const Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) w += m->code_bytes() + m->scale_bytes();
         const uint64_t n = (uint64_t)d->pos + 1 < L.window ? (uint64_t)d->pos + 1 : L.window;
-        kv += 2ull * d->cfg.kv_heads * n * d->cfg.head_dim * 2;
+        kv += 2ull * L.kvh * n * L.dim * 2;
     }
     if (weight_bytes) *weight_bytes = w;
     if (cache_bytes) *cache_bytes = kv;

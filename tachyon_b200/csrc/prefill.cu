@@ -82,11 +82,12 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float
 // partners DH/2 + (DH/64) l ..
 template <int DH>
 __global__ void __launch_bounds__(128) prefill_qkv_kernel(const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out,
-                                                          __half* kc, __half* vc, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps,
-                                                          float qscale) {
+                                                          __half* kc, __half* vc, uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads,
+                                                          float eps, float qscale) {
     constexpr int H2 = DH / 64, NV = 2 * H2;  // values a lane holds of each half, and in all
     const uint32_t rows = heads + 2 * kv_heads;
     const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows, r = item % rows;
+    if (token >= tokens) return;  // the last block's spare warps (nothing below synchronises the block)
     const int lane = threadIdx.x & 31;
     const float* src = qkv + ((size_t)token * rows + r) * DH;
     float x[NV];
@@ -167,18 +168,20 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
     constexpr int DW = DH / SPLIT;     // dimensions a warp sums
     extern __shared__ __align__(16) uint8_t raw[];
     __half* Qs = reinterpret_cast<__half*>(raw);   // [group * FT][LDS]
-    const uint32_t group = heads / kv_heads;
+    // Block row blockIdx.y takes `group` query heads, all of one key-value head: every head of it, or four of its eight
+    // (flash.rs:5-6: block row ctaid.y serves key-value head ctaid.y / group).
+    const uint32_t ratio = heads / kv_heads, group = ratio < 4 ? ratio : 4;
     __half* KV = Qs + group * FT * LDS;            // two stages of keys [FK][LDS] then values [FK][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hw = warp / SPLIT, part = warp % SPLIT;  // the head (of the group) this warp serves, and its share of the width
-    const uint32_t t0 = blockIdx.x * FT, g = blockIdx.y;
+    const uint32_t t0 = blockIdx.x * FT, head0 = blockIdx.y * group, g = head0 / ratio;
     const uint32_t nthreads = group * SPLIT * 32;
 
-    // Queries of this block: row w*16 + i is (head g*group + w, token t0 + i).
+    // Queries of this block: row w*16 + i is (head head0 + w, token t0 + i).
     for (uint32_t c = tid; c < group * FT * (DH / 8); c += nthreads) {
         const uint32_t row = c / (DH / 8), ch = c % (DH / 8), w = row / FT, i = row % FT, t = t0 + i;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < tokens) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * heads + g * group + w) * DH + ch * 8);
+        if (t < tokens) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * heads + head0 + w) * DH + ch * 8);
         *reinterpret_cast<uint4*>(Qs + row * LDS + ch * 8) = v;
     }
     const uint32_t p_first = pos0 + t0, p_last = pos0 + min(t0 + FT, tokens) - 1;
@@ -292,7 +295,7 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
     }
     // Normalise and store f16 [token][heads * DH].
     const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
-    const uint32_t head = g * group + hw;
+    const uint32_t head = head0 + hw;
 #pragma unroll
     for (int nb = 0; nb < DW / 8; nb++) {
         const uint32_t col = head * DH + part * DW + nb * 8 + 2 * (lane & 3);
@@ -326,20 +329,20 @@ int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* 
 
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
                        uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim) {
-    const uint32_t items = tokens * (heads + 2 * kv_heads);
-    if (items % 4 != 0) return fail(UNSUPPORTED, "prefill qkv: heads + 2*kv_heads must be a multiple of 4");
+    const uint32_t items = tokens * (heads + 2 * kv_heads), blocks = (items + 3) / 4;
     if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill qkv: heads of 256 or 512");
     const float qscale = scale * 1.4426950408889634f;
-    if (head_dim == 512) prefill_qkv_kernel<512><<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps, qscale);
-    else prefill_qkv_kernel<256><<<items / 4, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, pos0, cap, heads, kv_heads, eps, qscale);
+    if (head_dim == 512) prefill_qkv_kernel<512><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale);
+    else prefill_qkv_kernel<256><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
 
 int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
                          uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
-    const uint32_t group = heads / kv_heads;
-    if (group < 1 || group > 4 || heads % kv_heads != 0) return fail(UNSUPPORTED, "prefill attention: 1 to 4 query heads per key-value head");
+    if (kv_heads == 0 || heads % kv_heads != 0) return fail(UNSUPPORTED, "prefill attention: heads must be a multiple of kv_heads");
+    const uint32_t ratio = heads / kv_heads, group = ratio < 4 ? ratio : 4;  // query heads a block takes
+    if (ratio != 1 && ratio != 2 && ratio != 4 && ratio != 8) return fail(UNSUPPORTED, "prefill attention: 1, 2, 4 or 8 query heads per key-value head");
     if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill attention: heads of 256 or 512");
     // queries, two stages of keys and values; rows padded by 8 halves
     auto bytes = [&](uint32_t grp) { return (size_t)(grp * FT + 4 * FK) * (head_dim + 8) * 2; };
@@ -349,7 +352,7 @@ int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, con
         TB_CUDA(cudaFuncSetAttribute(prefill_flash_kernel<512, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((4 * FT + 4 * FK) * (512 + 8) * 2)));
         configured[ctx->gpu & 15] = true;
     }
-    const dim3 grid((tokens + FT - 1) / FT, kv_heads);
+    const dim3 grid((tokens + FT - 1) / FT, heads / group);
     if (head_dim == 512) prefill_flash_kernel<512, 2><<<grid, group * 64, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
     else prefill_flash_kernel<256, 1><<<grid, group * 32, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
     TB_CUDA(cudaGetLastError());

@@ -333,3 +333,46 @@ def test_shared_key_value_layers_attend_over_their_source_layers_cache(ctx):
         bad = small_config(layers=3)
         bad.shared = 3
         tb.Decoder(ctx, bad, context=64)
+
+
+@pytest.mark.parametrize("kv,global_dim,global_kv", [(2, 512, 0), (2, 512, 1), (1, 0, 0), (1, 512, 2)])
+def test_global_layers_with_heads_of_512(ctx, kv, global_dim, global_kv):
+    """Config::head_dim = [256, 512] and Config::kv_heads = [2, 1] (model/mod.rs:34-37, Gemma 4's global layers): wider
+    query/key/value and output matrices, a cache of heads of 512, RoPE over a quarter of the head; and eight query heads
+    to a key-value head in either kind of layer (E2B).  Stepping, the chunked prefill, the Q4 format and a shared global
+    layer follow the CPU forward."""
+    cfg = small_config(layers=6)
+    cfg.kv_heads = kv
+    cfg.global_every, cfg.global_head_dim, cfg.global_kv_heads, cfg.shared = 3, global_dim, global_kv, 2  # layer 5 (global) shares layer 2's cache
+    gd = global_dim or 256
+    for bits in (8, 4):
+        dec = tb.Decoder(ctx, cfg, context=96, chunk=40, keep_logits=True, weight_bits=bits)
+        dec.fill_random(SEED + bits)
+        dec.build()
+        ref = OracleModel(cfg, SEED + bits, context=96, chunk=40, weight_bits=bits)
+        kvg = global_kv or cfg.kv_heads
+        assert ref.tensors["2.qkv.w"].shape[0] == (cfg.heads + 2 * kvg) * gd and ref.tensors["5.qkv.w"].shape[0] == cfg.heads * gd
+        assert ref.tensors["2.q_norm"].size == gd and ref.tensors["1.q_norm"].size == 256
+        token = 17
+        for pos in range(40):
+            want_token, want_logits, want_hidden = ref.step(token, pos)
+            got_token = dec.step(token)
+            order = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+            check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+            assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+            token = (pos * 7919 + 13) % cfg.vocab
+        prompt = [(i * 7919 + 13) % cfg.vocab for i in range(70)]
+        dec.reset()
+        for t in prompt[:-1]:
+            dec.step(t)
+        a, la = dec.step(prompt[-1]), dec.logits()
+        dec.reset()
+        dec.prefill(prompt[:-1])  # two chunks: 40 tokens, then 29
+        b, lb = dec.step(prompt[-1]), dec.logits()
+        assert np.abs(la - lb).max() <= 4e-3 * np.abs(la).max()
+        dec.close()
+    with pytest.raises(tb.Error) as e:
+        bad = small_config(layers=3)
+        bad.global_head_dim = 128
+        tb.Decoder(ctx, bad, context=64)
+    assert e.value.status == 9

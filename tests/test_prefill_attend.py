@@ -31,7 +31,7 @@ def reference(q, kc, vc, tokens, pos0, cap, window, heads, D):
 @pytest.mark.parametrize("D,ratio,cap,window,pos0,tokens", [(256, 4, 1024, 512, 600, 100), (256, 2, 1024, 512, 600, 100), (256, 4, 700, 700, 600, 100),
                                                             (256, 1, 256, 64, 0, 37), (256, 4, 2048, 512, 0, 300), (256, 4, 640, 512, 1900, 129),
                                                             (512, 4, 700, 700, 600, 100), (512, 2, 1024, 512, 600, 70), (512, 1, 256, 64, 0, 37),
-                                                            (512, 4, 2048, 2048, 0, 200)])
+                                                            (512, 4, 2048, 2048, 0, 200), (256, 8, 1024, 512, 600, 50), (512, 8, 700, 700, 600, 50)])
 def test_prefill_attention_matches_f64(ctx, D, ratio, cap, window, pos0, tokens):
     heads, seed = ratio * KV, cap + pos0 + tokens
     q = f16(0.25 * values_fast(tokens * heads * D, seed))
@@ -65,10 +65,10 @@ def test_prefill_attention_does_not_depend_on_the_chunking(ctx, D):
     assert np.array_equal(whole.download(np.uint16, tokens * heads * D), parts)
 
 
-@pytest.mark.parametrize("D,heads,kv,theta,fraction", [(256, 8, 2, 1e4, 1.0), (512, 8, 2, 1e6, 0.25), (256, 8, 0, 1e4, 1.0), (512, 2, 1, 1e6, 0.25)])
+@pytest.mark.parametrize("D,heads,kv,theta,fraction", [(256, 8, 2, 1e4, 1.0), (512, 8, 2, 1e6, 0.25), (256, 8, 0, 1e4, 1.0), (512, 2, 1, 1e6, 0.25), (512, 8, 1, 1e6, 0.25)])
 def test_prefill_qkv_stores_keys_values_and_queries(ctx, D, heads, kv, theta, fraction):
     """kv_256 / kv_512 and query_256 / query_512 (ptx/attend.rs:472-556): norms, RoPE at pos0 + t, ring slot (pos0 + t) % cap."""
-    tokens, pos0, cap, eps, scale = 52, 990, 64, 1e-6, 0.5
+    tokens, pos0, cap, eps, scale = 53, 990, 64, 1e-6, 0.5  # 53 x 10 rows: the last block is not full
     rows = heads + 2 * kv
     qkv = values_fast(tokens * rows * D, 11 + D).reshape(tokens, rows, D)
     qn, kn = (0.2 + 0.1 * values_fast(D, 12)).astype(np.float32), (0.2 + 0.1 * values_fast(D, 13)).astype(np.float32)
@@ -118,6 +118,6 @@ def test_prefill_attention_rejects_bad_shapes(ctx):
         ctx.prefill_attend(z, z, z, z, 4, 0, 16, 16, 6, 4, 256)
     assert e.value.status == 3
     with pytest.raises(tb.Error):
-        ctx.prefill_attend(z, z, z, z, 4, 0, 16, 16, 16, 2, 256)  # eight query heads to a key-value head: no kernel
+        ctx.prefill_attend(z, z, z, z, 4, 0, 16, 16, 32, 2, 256)  # sixteen query heads to a key-value head: no kernel
     with pytest.raises(tb.Error):
         ctx.prefill_attend(z, z, z, z, 4, 0, 16, 16, 8, 2, 128)  # heads of 128: no kernel
