@@ -291,6 +291,11 @@ typedef struct tb_config {
                                the query rows only */
     uint32_t global_head_dim; /* Config::head_dim[1]: head size of global layers, 256 or 512; 0 = head_dim */
     uint32_t global_kv_heads; /* Config::kv_heads[1]: key-value heads of global layers; 0 = kv_heads */
+    uint32_t per_layer;       /* Config::per_layer: width of each layer's per-layer input (256 in Gemma 4's E models); 0 = none.
+                                 Tensors: embed_per_layer [vocab, layers * per_layer], per_layer_proj [layers * per_layer, hidden],
+                                 per_layer_norm [per_layer], {i}.per_layer_gate [per_layer, hidden], {i}.per_layer_proj [hidden,
+                                 per_layer], {i}.post_per_layer_input_norm [hidden] (model/mod.rs:180-186, 199-201, 228-236).  Eight-bit weights only;
+                                 the table lives in device memory (the reference keeps it in pinned host memory) */
 } tb_config;
 
 /* model::Settings (decode.rs:64-76) plus what this build adds. */

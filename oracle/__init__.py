@@ -37,7 +37,7 @@ def lib() -> C.CDLL:
 class Config(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("hidden", "ffn", "heads", "kv_heads", "head_dim", "vocab", "layers", "window", "context")] + [
         (n, C.c_float) for n in ("theta_sliding", "theta_global", "fraction_global", "eps", "softcap", "attn_scale", "embed_scale")
-    ] + [("weight_bits", C.c_int32), ("global_head_dim", C.c_int32), ("global_kv_heads", C.c_int32)]
+    ] + [("weight_bits", C.c_int32), ("global_head_dim", C.c_int32), ("global_kv_heads", C.c_int32), ("per_layer", C.c_int32)]
 
 
 class Layer(C.Structure):
@@ -45,11 +45,13 @@ class Layer(C.Structure):
         [(n, C.c_void_p) for n in ("qkv", "o", "gate_up", "down", "qkv_s", "o_s", "gate_up_s", "down_s")]
         + [(n, C.c_void_p) for n in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")]
         + [("layer_scalar", C.c_float), ("global_", C.c_int32), ("kc", C.c_void_p), ("vc", C.c_void_p), ("cap", C.c_int32), ("shared", C.c_int32)]
+        + [(n, C.c_void_p) for n in ("pl_gate", "pl_proj", "pl_gate_s", "pl_proj_s", "post_pl_ln")]
     )
 
 
 class Model(C.Structure):
-    _fields_ = [("cfg", Config), ("embed", C.c_void_p), ("embed_s", C.c_void_p), ("norm", C.c_void_p), ("layers", C.POINTER(Layer))]
+    _fields_ = [("cfg", Config), ("embed", C.c_void_p), ("embed_s", C.c_void_p), ("norm", C.c_void_p), ("layers", C.POINTER(Layer))] + [
+        (n, C.c_void_p) for n in ("embed_pl", "pl_model_proj", "embed_pl_s", "pl_model_proj_s", "pl_norm")]
 
 
 class EncConfig(C.Structure):

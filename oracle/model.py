@@ -41,6 +41,12 @@ class OracleModel:
 
         self.embed, self.embed_s = mat("embed", 1 << 20, cfg.vocab, H)
         self.norm = vec("norm", (1 << 20) + 2, H, 0.5, 1.5)
+        pl = getattr(cfg, "per_layer", 0)
+        if pl:  # per-layer inputs: the table, the projection of the embedding, the norm (streams 2^20 + 4 .. 8)
+            full = L  # the table holds one input per layer
+            self.embed_pl, self.embed_pl_s = mat("embed_per_layer", (1 << 20) + 4, cfg.vocab, pl * full)
+            self.pl_model_proj, self.pl_model_proj_s = mat("per_layer_proj", (1 << 20) + 6, pl * full, H)
+            self.pl_norm = vec("per_layer_norm", (1 << 20) + 8, pl, 0.5, 1.5)
         self.layers = (oracle.Layer * L)()
         self.caches = []
         for i in range(L):
@@ -62,6 +68,11 @@ class OracleModel:
                   vec(f"{i}.input_layernorm", b + 10, H, 0.5, 1.5), vec(f"{i}.post_attention_layernorm", b + 11, H, 0.5, 1.5),
                   vec(f"{i}.pre_feedforward_layernorm", b + 12, H, 0.5, 1.5), vec(f"{i}.post_feedforward_layernorm", b + 13, H, 0.5, 1.5)]
             scalar = vec(f"{i}.layer_scalar", b + 14, 1, 0.95, 1.0)
+            if pl:
+                g, g_s = mat(f"{i}.per_layer_gate", b + 16, pl, H)
+                pj, pj_s = mat(f"{i}.per_layer_proj", b + 18, H, pl)
+                post = vec(f"{i}.post_per_layer_input_norm", b + 20, H, 0.5, 1.5)
+                ly.pl_gate, ly.pl_gate_s, ly.pl_proj, ly.pl_proj_s, ly.post_pl_ln = (a.ctypes.data for a in (g, g_s, pj, pj_s, post))
             cap = context if is_global else cfg.window + chunk
             if source == i:
                 kc, vc = np.zeros((kvh, cap, D), np.uint16), np.zeros((kvh, cap, D), np.uint16)
@@ -77,9 +88,13 @@ class OracleModel:
         oc = oracle.Config(hidden=H, ffn=F, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, vocab=cfg.vocab, layers=L, window=cfg.window,
                            context=context, theta_sliding=cfg.theta_sliding, theta_global=cfg.theta_global, fraction_global=cfg.fraction_global,
                            eps=cfg.eps, softcap=cfg.softcap, attn_scale=cfg.attn_scale, embed_scale=bf16_round(float(np.sqrt(np.float32(H)))),
-                           weight_bits=weight_bits, global_head_dim=dims[1], global_kv_heads=kvs[1])
+                           weight_bits=weight_bits, global_head_dim=dims[1], global_kv_heads=kvs[1], per_layer=pl)
         self.model = oracle.Model(cfg=oc, embed=self.embed.ctypes.data, embed_s=self.embed_s.ctypes.data, norm=self.norm.ctypes.data,
                                   layers=C.cast(self.layers, C.POINTER(oracle.Layer)))
+        if pl:
+            self.model.embed_pl, self.model.embed_pl_s = self.embed_pl.ctypes.data, self.embed_pl_s.ctypes.data
+            self.model.pl_model_proj, self.model.pl_model_proj_s = self.pl_model_proj.ctypes.data, self.pl_model_proj_s.ctypes.data
+            self.model.pl_norm = self.pl_norm.ctypes.data
 
     def fill_cache(self, seed: int):
         """The same seeded N(0,1) cache contents tb_decoder_fill_cache writes."""

@@ -582,6 +582,7 @@ typedef struct {
     float theta_sliding, theta_global, fraction_global, eps, softcap, attn_scale, embed_scale;
     int32_t weight_bits; /* 0 or 8: int8 codes, a scale per 32; 4: the reference's Q4 (quant.rs:47-82), a scale per 64 */
     int32_t global_head_dim, global_kv_heads; /* Config::head_dim[1], Config::kv_heads[1] (model/mod.rs:34-37); 0 = as the sliding layers */
+    int32_t per_layer;                        /* Config::per_layer: width of each layer's per-layer input; 0 = none */
 } tbo_config;
 
 typedef struct {
@@ -593,6 +594,9 @@ typedef struct {
     uint16_t *kc, *vc;                                /* f16 caches [kv_heads][cap][head_dim]; cap = context (global) or ring */
     int32_t cap;
     int32_t shared;                                   /* != 0: no key/value rows in qkv; kc, vc are another layer's (tiny.rs: Config::source) */
+    const int8_t *pl_gate, *pl_proj;                  /* per-layer input: gate [per_layer, hidden], projection [hidden, per_layer] */
+    const uint16_t *pl_gate_s, *pl_proj_s;
+    const float *post_pl_ln;                          /* post_per_layer_input_norm [hidden] */
 } tbo_layer;
 
 typedef struct {
@@ -601,6 +605,9 @@ typedef struct {
     const uint16_t *embed_s;
     const float *norm;        /* [hidden] */
     tbo_layer *layers;
+    const int8_t *embed_pl, *pl_model_proj; /* per-layer table [vocab, layers*per_layer]; projection of the embedding [layers*per_layer, hidden] */
+    const uint16_t *embed_pl_s, *pl_model_proj_s;
+    const float *pl_norm;                   /* per_layer_projection_norm [per_layer] */
 } tbo_model;
 
 static int nibble(const uint8_t *packed, size_t at) { /* weight `at` of a row-major Q4 matrix, 0..15 (quant.rs:60-66) */
@@ -666,6 +673,24 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
         if (c->weight_bits == 4) x[i] = (float)(nibble((const uint8_t *)m->embed, at) - 8) * tbo_f16_value(m->embed_s[at / 64]) * c->embed_scale;
         else x[i] = (float)m->embed[at] * tbo_f16_value(m->embed_s[at / 32]) * c->embed_scale;
     }
+    /* tiny.rs:239-252: every layer's input (rmsnorm(projection of the embedding / sqrt(hidden)) + table row * sqrt(per_layer)) / sqrt(2). */
+    size_t PL = (size_t)c->per_layer, PLW = PL * (size_t)c->layers;
+    float *pli = NULL;
+    if (PL) {
+        float *proj = (float *)malloc(PLW * 4);
+        pli = (float *)malloc(PLW * 4);
+        matvec(c, m->pl_model_proj, m->pl_model_proj_s, x, PLW, H, proj);
+        for (size_t i = 0; i < PLW; i++) proj[i] /= sqrtf((float)H);
+        for (size_t l = 0; l < (size_t)c->layers; l++) {
+            rms_f32(proj + l * PL, m->pl_norm, PL, c->eps, pli + l * PL);
+            for (size_t i = 0; i < PL; i++) {
+                size_t at = (size_t)token * PLW + l * PL + i;
+                float e = (float)m->embed_pl[at] * tbo_f16_value(m->embed_pl_s[at / 32]) * sqrtf((float)PL);
+                pli[l * PL + i] = (pli[l * PL + i] + e) * 0.70710678118654752f;
+            }
+        }
+        free(proj);
+    }
     int nl = stop_layer > 0 ? stop_layer : c->layers;
     for (int li = 0; li < nl; li++) {
         tbo_layer *L = &m->layers[li];
@@ -723,7 +748,16 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
         for (size_t i = 0; i < F; i++) a[i] = gelu_f32(gu[i]) * gu[F + i];       /* :309 */
         matvec(c, L->down, L->down_s, a, H, F, y);
         rms_f32(y, L->post_ffn_ln, H, c->eps, h);                                /* :314 */
-        for (size_t i = 0; i < H; i++) x[i] = (x[i] + h[i]) * L->layer_scalar;   /* :296-297 */
+        if (PL) {                                                                /* :298-300: gelu(gate x) * input, projected back, normed, added */
+            for (size_t i = 0; i < H; i++) x[i] += h[i];
+            float *g = (float *)malloc(PL * 4);
+            matvec(c, L->pl_gate, L->pl_gate_s, x, PL, H, g);
+            for (size_t i = 0; i < PL; i++) g[i] = gelu_f32(g[i]) * pli[(size_t)li * PL + i];
+            matvec(c, L->pl_proj, L->pl_proj_s, g, H, PL, y);
+            free(g);
+            rms_f32(y, L->post_pl_ln, H, c->eps, h);
+        }
+        for (size_t i = 0; i < H; i++) x[i] = (x[i] + h[i]) * L->layer_scalar;   /* :296-297, 301 */
     }
     int32_t pick = -1;
     if (h_out) memcpy(h_out, x, H * 4);
@@ -734,7 +768,7 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
         pick = (int32_t)tbo_sample_greedy(lg, (size_t)c->vocab, c->softcap, 1.0f, NULL, NULL, NULL);
         if (!logits) free(lg);
     }
-    free(x); free(h); free(qkv); free(att); free(y); free(gu); free(a); free(freq); free(tmp);
+    free(x); free(h); free(qkv); free(att); free(y); free(gu); free(a); free(freq); free(tmp); free(pli);
     return pick;
 }
 

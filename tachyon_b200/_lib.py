@@ -27,7 +27,7 @@ class Config(C.Structure):
         ("hidden", u32), ("ffn", u32), ("heads", u32), ("kv_heads", u32), ("head_dim", u32), ("vocab", u32), ("layers", u32), ("window", u32),
         ("global_", vp), ("global_every", u32),
         ("theta_sliding", f32), ("theta_global", f32), ("fraction_global", f32), ("eps", f32), ("softcap", f32), ("attn_scale", f32),
-        ("shared", u32), ("global_head_dim", u32), ("global_kv_heads", u32),
+        ("shared", u32), ("global_head_dim", u32), ("global_kv_heads", u32), ("per_layer", u32),
     ]
 
 

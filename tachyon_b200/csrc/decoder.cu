@@ -1,11 +1,14 @@
 // The decoder: buffers, the op list of one decode step, its capture into CUDA graphs and the calls that replay it.
 // Host-side counterpart of crates/tachyon/src/model/decode.rs (layout 151-181, control 190-204, step 569-592,
-// attention 603-618, mlp 631-662, record 525-528, step/start/next_token/stop 305-345) for a model without per-layer
-// inputs, shared caches or experts, with this build's Q8 weights.
+// attention 603-618, mlp 631-662, record 525-528, step/start/next_token/stop 305-345) for a model without experts, with
+// this build's Q8 weights or the reference's Q4.
 //
 // One step is 2 + 5 * layers launches:
 //   embed -> per layer { qkv (norm prologue) -> attention -> o -> gate_up (residual + norm prologue, GeGLU epilogue) ->
 //   down } -> LM head (residual + final norm prologue, greedy pick epilogue).
+// With per-layer inputs (Config::per_layer, decode.rs:572-579, 650-660) three more launches open the step (the token's
+// row of the per-layer table, the projection of the embedding, their normalised sum for every layer) and two close
+// each layer (the gate: residual prologue, GELU times the layer's input; the projection back to the stream).
 // The residual additions and every RMS-norm run inside the prologue of the product that consumes them; the token and
 // the position live on the device (state = [position, token]) and are advanced by the last kernel, so steps chain
 // without the host.
@@ -13,7 +16,9 @@
 // Seeded synthetic models (tb_decoder_fill_random): tensor k of layer i uses generator stream 32*i + k with k =
 // 0 qkv.w, 1 qkv.s, 2 o.w, 3 o.s, 4 gate_up.w, 5 gate_up.s (gate rows then up rows), 6 down.w, 7 down.s, 8 q_norm,
 // 9 k_norm, 10 input_layernorm, 11 post_attention_layernorm, 12 pre_feedforward_layernorm,
-// 13 post_feedforward_layernorm, 14 layer_scalar; 2^20 embed.w, 2^20+1 embed.s, 2^20+2 norm; caches 2^21 + 2*i (+1).
+// 13 post_feedforward_layernorm, 14 layer_scalar, 16 per_layer_gate.w, 17 .s, 18 per_layer_proj.w, 19 .s,
+// 20 post_per_layer_input_norm; 2^20 embed.w, 2^20+1 embed.s, 2^20+2 norm, 2^20+4 embed_per_layer.w, +5 .s,
+// 2^20+6 per_layer_proj.w, +7 .s, 2^20+8 per_layer_norm; caches 2^21 + 2*i (+1).
 // Codes are uniform in [-127, 127], scales |N(0,1)|*0.02/127, norm weights uniform in [0.5, 1.5), q/k norm weights in
 // [0.15, 0.35), layer scalars in [0.95, 1): a random network with smaller scalars forgets its residual stream within a
 // few layers and amplifies rounding differences by five orders of magnitude over 35 layers, which would make any
@@ -42,6 +47,8 @@ struct Mat {
 
 struct Layer {
     Mat qkv, o, gate_up, down;
+    Mat pl_gate, pl_proj;          // per-layer input: gate [per_layer, hidden], projection [hidden, per_layer]
+    float* post_pl = nullptr;      // post_per_layer_input_norm
     float *q_norm = nullptr, *k_norm = nullptr, *input_ln = nullptr, *post_attn = nullptr, *pre_ffn = nullptr, *post_ffn = nullptr;
     float layer_scalar = 1.0f;
     bool global = false;
@@ -64,6 +71,12 @@ struct tb_decoder {
     std::vector<Layer> layers;
     Mat embed;
     float* norm = nullptr;
+    // Per-layer inputs (Config::per_layer > 0): the table [vocab, layers * per_layer], the projection of the embedding
+    // [layers * per_layer, hidden], the norm weights [per_layer]; and the step's buffers for them.
+    Mat embed_pl, pl_model_proj;
+    float *pl_norm = nullptr, *ple = nullptr, *proj = nullptr, *pli = nullptr, *g2 = nullptr;
+    float *pf_ple = nullptr, *pf_proj = nullptr, *pf_pli = nullptr;  // prefill: [chunk][layers * per_layer]: table rows, projections, inputs
+    __half* pf_g2 = nullptr;                      // prefill: [chunk][per_layer]
     char* arena = nullptr;
     size_t arena_bytes = 0;
     // step buffers
@@ -147,6 +160,11 @@ int validate(const tb_config& c, const tb_settings& s) {
         if (wide != 2048 && wide != 4096 && wide != 8192 && wide != 16384) return fail(UNSUPPORTED, "decoder: heads*512 must be 2048, 4096, 8192 or 16384");
     }
     if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
+    if (c.per_layer != 0) {
+        if (c.per_layer % 256 != 0 || c.per_layer > 6144) return fail(UNSUPPORTED, "decoder: per_layer must be a multiple of 256 up to 6144");
+        if (s.weight_bits == 4) return fail(UNSUPPORTED, "decoder: per-layer inputs with four-bit weights (matrices 256 wide) have no product here");
+        if (s.fused) return fail(UNSUPPORTED, "decoder: the single-kernel step has no per-layer inputs");
+    }
     if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
     if (s.context == 0 || s.context > TRACE) return fail(OUT_OF_RANGE, "decoder: context must be in 1..65536");
     if (c.shared >= c.layers) return fail(OUT_OF_RANGE, "decoder: at least one layer must own its cache");
@@ -181,6 +199,8 @@ void layout(tb_decoder* d, char* base) {
     auto vec = [&](float*& v, size_t n) { v = reinterpret_cast<float*>(base + t.take(n * 4)); };
     mat(d->embed, c.vocab, c.hidden);
     vec(d->norm, c.hidden);
+    const uint32_t pl = c.per_layer, plw = c.per_layer * c.layers;
+    if (pl) mat(d->embed_pl, c.vocab, plw), mat(d->pl_model_proj, plw, c.hidden), vec(d->pl_norm, pl);
     uint32_t max_splits = 1;
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
@@ -201,6 +221,7 @@ void layout(tb_decoder* d, char* base) {
         mat(L.down, c.hidden, c.ffn);
         vec(L.q_norm, L.dim), vec(L.k_norm, L.dim);
         vec(L.input_ln, c.hidden), vec(L.post_attn, c.hidden), vec(L.pre_ffn, c.hidden), vec(L.post_ffn, c.hidden);
+        if (pl) mat(L.pl_gate, pl, c.hidden), mat(L.pl_proj, c.hidden, pl), vec(L.post_pl, c.hidden);
         // Caches: a global layer keeps `context` positions, a sliding one a ring of window + chunk (decode.rs:152).
         L.window = L.global ? d->settings.context : c.window;
         L.cap = L.global ? d->settings.context : c.window + d->settings.chunk;
@@ -224,6 +245,7 @@ void layout(tb_decoder* d, char* base) {
     vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
     vec(d->qkv, max_nq(c) + 2 * max_nkv(c)), vec(d->att, max_nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
     vec(d->logits, c.vocab);
+    if (pl) vec(d->ple, plw), vec(d->proj, plw), vec(d->pli, plw), vec(d->g2, pl);
     vec(d->work, c.vocab);
     d->seen = reinterpret_cast<uint32_t*>(base + t.take(((size_t)c.vocab + 31) / 32 * 4));
     d->sampling = base + t.take(64);
@@ -244,6 +266,7 @@ void layout(tb_decoder* d, char* base) {
         d->pf_tokens = reinterpret_cast<uint32_t*>(base + t.take(T * 4));
         vec(d->pf_h, T * c.hidden), vec(d->pf_qkv, T * (max_nq(c) + 2 * max_nkv(c))), vec(d->pf_y, T * c.hidden);
         half(d->pf_x, T * c.hidden), half(d->pf_q, T * max_nq(c)), half(d->pf_att, T * max_nq(c)), half(d->pf_g, T * c.ffn);
+        if (pl) vec(d->pf_ple, T * plw), vec(d->pf_proj, T * plw), vec(d->pf_pli, T * plw), half(d->pf_g2, T * pl);
     }
     d->arena_bytes = t.end;
 }
@@ -294,6 +317,20 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         TB_TRY(launch_embed_q8(d->ctx, d->embed.w, d->embed.s, d->state + 1, c.hidden, d->embed_scale, d->x[0], d->embed.bits));
     }
     d->launches++;
+    const uint32_t pl = c.per_layer;
+    if (pl) {
+        // decode.rs:572-579: the token's row of the per-layer table times sqrt(per_layer); the embedding through the
+        // per-layer projection; then for every layer (row + w * rmsnorm(projection)) / sqrt(2), the projection's
+        // 1 / sqrt(hidden) folded into eps (rmsnorm(c y) is rmsnorm(y) with eps / c^2).
+        if (d->collect) return fail(UNSUPPORTED, "fused step: no per-layer inputs");
+        TB_TRY(launch_embed_q8(d->ctx, d->embed_pl.w, d->embed_pl.s, d->state + 1, pl * c.layers, sqrtf((float)pl), d->ple, d->embed_pl.bits));
+        d->launches++;
+        GemvParams pp;
+        pp.xmode = X_F32, pp.x = d->x[0], pp.epi = EPI_F32, pp.y = d->proj;
+        TB_TRY(gemv(d, d->pl_model_proj, pp));
+        TB_TRY(launch_norm_q8(d->ctx, d->ple, d->pli, d->proj, d->pl_norm, nullptr, nullptr, nullptr, pl, c.layers, c.eps * (float)c.hidden, 0.70710678118654752f));
+        d->launches++;
+    }
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
         GemvParams q;
@@ -301,7 +338,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         if (i > 0) {
             // The previous layer's closing residual: x = (x + post_ffn_norm(down)) * layer_scalar (decode.rs:631-662).
             const Layer& P = d->layers[i - 1];
-            q.yres = d->y, q.w1 = P.post_ffn, q.hscale = P.layer_scalar, q.h_out = d->x[1 - cur];
+            q.yres = d->y, q.w1 = pl ? P.post_pl : P.post_ffn, q.hscale = P.layer_scalar, q.h_out = d->x[1 - cur];
             cur = 1 - cur;
         }
         q.epi = EPI_F32, q.y = d->qkv;
@@ -352,10 +389,24 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         dn.xmode = X_F32, dn.x = d->g, dn.epi = EPI_F32, dn.y = d->y;
         dn.pf = i + 1 < c.layers ? hint(d, d->layers[i + 1].qkv, 1, 0, PF) : hint(d, d->embed, 1, 0, PF);
         TB_TRY(gemv(d, L.down, dn));
+
+        if (pl) {
+            // decode.rs:654-658: x += post_ffn_norm(down), unscaled, feeds the gate; gelu(gate) times the layer's input,
+            // projected back; the next product's prologue adds post_per_layer_input_norm of it and applies the scalar.
+            GemvParams pg;
+            pg.xmode = X_NORM, pg.h = d->x[cur], pg.yres = d->y, pg.w1 = L.post_ffn, pg.hscale = 1.0f, pg.w2 = nullptr, pg.eps = c.eps;
+            pg.h_out = d->x[1 - cur];
+            cur = 1 - cur;
+            pg.epi = EPI_F32, pg.y = d->g2, pg.gelu_mul = d->pli + (size_t)i * pl;
+            TB_TRY(gemv(d, L.pl_gate, pg));
+            GemvParams pj;
+            pj.xmode = X_F32, pj.x = d->g2, pj.epi = EPI_F32, pj.y = d->y;
+            TB_TRY(gemv(d, L.pl_proj, pj));
+        }
     }
     const Layer& P = d->layers[c.layers - 1];
     GemvParams h;
-    h.xmode = X_NORM, h.h = d->x[cur], h.yres = d->y, h.w1 = P.post_ffn, h.hscale = P.layer_scalar, h.w2 = d->norm, h.eps = c.eps;
+    h.xmode = X_NORM, h.h = d->x[cur], h.yres = d->y, h.w1 = pl ? P.post_pl : P.post_ffn, h.hscale = P.layer_scalar, h.w2 = d->norm, h.eps = c.eps;
     h.h_out = d->x[1 - cur];
     h.epi = EPI_ARGMAX, h.y = d->settings.keep_logits ? d->logits : nullptr;
     h.best = d->best, h.count = reinterpret_cast<uint32_t*>(d->best + 1), h.state = d->state, h.token_out = token_word;
@@ -390,6 +441,9 @@ bool find_tensor(tb_decoder* d, const std::string& name, Named& out) {
         else return false;
         return true;
     };
+    if (c.per_layer && name.rfind("embed_per_layer", 0) == 0) return mat(d->embed_pl, name.substr(15), 0);
+    if (c.per_layer && name.rfind("per_layer_proj", 0) == 0) return mat(d->pl_model_proj, name.substr(14), 0);
+    if (c.per_layer && name == "per_layer_norm") return out = {d->pl_norm, (size_t)c.per_layer * 4, 0, 0}, true;
     if (name.rfind("embed", 0) == 0) return mat(d->embed, name.substr(5), 0);
     if (name == "norm") return out = {d->norm, (size_t)c.hidden * 4, 0, 0}, true;
     const size_t dot = name.find('.');
@@ -402,6 +456,9 @@ bool find_tensor(tb_decoder* d, const std::string& name, Named& out) {
     if (i >= c.layers) return false;
     Layer& L = d->layers[i];
     const std::string rest = name.substr(dot + 1);
+    if (c.per_layer && rest.rfind("per_layer_gate", 0) == 0) return mat(L.pl_gate, rest.substr(14), 0);
+    if (c.per_layer && rest.rfind("per_layer_proj", 0) == 0) return mat(L.pl_proj, rest.substr(14), 0);
+    if (c.per_layer && rest == "post_per_layer_input_norm") return out = {L.post_pl, (size_t)c.hidden * 4, 0, i}, true;
     if (rest.rfind("qkv", 0) == 0) return mat(L.qkv, rest.substr(3), 0);
     if (rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), 0);
     if (rest.rfind("gate_up", 0) == 0) return mat(L.gate_up, rest.substr(7), 1);
@@ -551,6 +608,11 @@ int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
     };
     TB_TRY(mat(d->embed, 1ull << 20));
     TB_TRY(launch_fill_uniform(ctx, seed, (1ull << 20) + 2, d->norm, c.hidden, 0.5f, 1.5f));
+    if (c.per_layer) {
+        TB_TRY(mat(d->embed_pl, (1ull << 20) + 4));
+        TB_TRY(mat(d->pl_model_proj, (1ull << 20) + 6));
+        TB_TRY(launch_fill_uniform(ctx, seed, (1ull << 20) + 8, d->pl_norm, c.per_layer, 0.5f, 1.5f));
+    }
     void *tw = nullptr, *ts = nullptr;
     TB_CUDA(cudaMalloc(&tw, d->layers[0].gate_up.code_bytes()));
     TB_CUDA(cudaMalloc(&ts, d->layers[0].gate_up.scale_bytes()));
@@ -571,6 +633,9 @@ int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 11, L.post_attn, c.hidden, 0.5f, 1.5f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 12, L.pre_ffn, c.hidden, 0.5f, 1.5f);
         if (st == OK) st = launch_fill_uniform(ctx, seed, b + 13, L.post_ffn, c.hidden, 0.5f, 1.5f);
+        if (st == OK && c.per_layer) st = mat(L.pl_gate, b + 16);
+        if (st == OK && c.per_layer) st = mat(L.pl_proj, b + 18);
+        if (st == OK && c.per_layer) st = launch_fill_uniform(ctx, seed, b + 20, L.post_pl, c.hidden, 0.5f, 1.5f);
         if (st == OK) {
             // The scalar comes from the same generator, evaluated through a one-element device fill.
             st = launch_fill_uniform(ctx, seed, b + 14, d->x[0], 1, 0.95f, 1.0f);
@@ -737,13 +802,27 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
     const uint32_t H = c.hidden;
     TB_CUDA(cudaMemcpyAsync(d->pf_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
     TB_TRY(launch_prefill_embed(ctx, d->embed.w, d->embed.s, d->pf_tokens, n, H, d->embed_scale, d->pf_h, d->embed.bits));
+    const uint32_t pl = c.per_layer, plw = pl * c.layers;
+    if (pl) {
+        // Every token's per-layer inputs (decode.rs:572-579 for a chunk): table rows times sqrt(per_layer), the embeddings
+        // through the per-layer projection, and (row + w * rmsnorm(projection)) / sqrt(2) per token and layer.
+        TB_TRY(launch_prefill_embed(ctx, d->embed_pl.w, d->embed_pl.s, d->pf_tokens, n, plw, sqrtf((float)pl), d->pf_ple, d->embed_pl.bits));
+        TB_TRY(launch_prefill_norm(ctx, d->pf_h, nullptr, nullptr, nullptr, n, H, c.eps, 1.0f, d->pf_x));  // the embeddings as f16
+        TB_TRY(launch_gemm_q8(ctx, d->pl_model_proj.w, d->pl_model_proj.s, d->pf_x, n, plw, H, d->pf_proj, 0, d->pl_model_proj.bits));
+        const uint32_t chunks = n * c.layers;
+        for (uint32_t at = 0; at < chunks; at += 32768) {  // the grid's second dimension holds 65535 blocks
+            const uint32_t now = std::min(32768u, chunks - at);
+            const size_t off = (size_t)at * pl;
+            TB_TRY(launch_norm_q8(ctx, d->pf_ple + off, d->pf_pli + off, d->pf_proj + off, d->pl_norm, nullptr, nullptr, nullptr, pl, now, c.eps * (float)H, 0.70710678118654752f));
+        }
+    }
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
         if (i == 0) {
             TB_TRY(launch_prefill_norm(ctx, d->pf_h, nullptr, nullptr, L.input_ln, n, H, c.eps, 1.0f, d->pf_x));
         } else {
             const Layer& P = d->layers[i - 1];
-            TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
+            TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, pl ? P.post_pl : P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
         }
         TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, L.qkv.rows, H, d->pf_qkv, 0, L.qkv.bits));
         // A shared layer has query rows only: nothing to append to the cache it reads.
@@ -755,6 +834,13 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
         TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_attn, L.pre_ffn, n, H, c.eps, 1.0f, d->pf_x));
         TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2, L.gate_up.bits));
         TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0, L.down.bits));
+        if (pl) {
+            // decode.rs:654-658 for a chunk: the stream plus the MLP's normed output, unscaled, through the gate; GELU times
+            // each token's input of this layer; projected back.  The next layer's norm step adds it.
+            TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_ffn, nullptr, n, H, c.eps, 1.0f, d->pf_x));
+            TB_TRY(launch_gemm_q8(ctx, L.pl_gate.w, L.pl_gate.s, d->pf_x, n, pl, H, d->pf_g2, 6, L.pl_gate.bits, d->pf_pli + (size_t)i * pl, plw));
+            TB_TRY(launch_gemm_q8(ctx, L.pl_proj.w, L.pl_proj.s, d->pf_g2, n, H, pl, d->pf_y, 0, L.pl_proj.bits));
+        }
     }
     return OK;
 }
@@ -806,6 +892,7 @@ int tb_decoder_step_bytes(tb_decoder* d, uint64_t* weight_bytes, uint64_t* cache
     uint64_t w = d->embed.code_bytes() + d->embed.scale_bytes(), kv = 0;
     for (const Layer& L : d->layers) {
         for (const Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) w += m->code_bytes() + m->scale_bytes();
+        if (d->cfg.per_layer) w += L.pl_gate.code_bytes() + L.pl_gate.scale_bytes() + L.pl_proj.code_bytes() + L.pl_proj.scale_bytes();
         const uint64_t n = (uint64_t)d->pos + 1 < L.window ? (uint64_t)d->pos + 1 : L.window;
         kv += 2ull * L.kvh * n * L.dim * 2;
     }

@@ -348,11 +348,19 @@ EncodeTiled encode_tiled() {
 }  // namespace
 
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                   uint32_t wbits) {
+                   uint32_t wbits, const float* mul, uint32_t mul_stride) {
     if (!w || !s || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
     if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
     if (N % 32 != 0 || ((mode == 2 || mode == 4) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
-    if (mode < 0 || mode > 5) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if (mode < 0 || mode > 6) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if (mode == 6) {  // only the persistent schedule has this epilogue
+        if (!mul || mul_stride < N || (reinterpret_cast<uintptr_t>(mul) & 15) || mul_stride % 4 != 0) return fail(OUT_OF_RANGE, "gemm: the multiplier must be present, 16-byte aligned and at least N wide");
+        if (!gemm_persistent_supports(N, K, wbits)) return fail(UNSUPPORTED, "gemm: no kernel for this shape with a multiplier");
+        if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
+        if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
+            return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
+        return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits, mul, mul_stride);
+    }
     if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");

@@ -92,7 +92,9 @@ struct Args {
     const __half* s;   // scales [N][K / 32] (8-bit codes) or [N][K / 64] (4-bit)
     void* out;
     uint32_t M, N, K;
-    int mode;          // as gemm.cu: 0 f32, 1 f16, 2 GeGLU(tanh) pairs, 3 f32 +=, 4 GeGLU(erf) pairs, 5 GELU(erf) f16
+    int mode;          // as gemm.cu: 0 f32, 1 f16, 2 GeGLU(tanh) pairs, 3 f32 +=, 4 GeGLU(erf) pairs, 5 GELU(erf) f16, 6 GELU(tanh) * mul f16
+    const float* mul;  // mode 6: f32 [M][mul_stride], the factor of output (m, n) at m * mul_stride + n
+    uint32_t mul_stride;
 };
 
 struct Bars {
@@ -286,8 +288,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
 #pragma unroll
                     for (int i = 0; i < 8; i++)
                         if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                } else if (g.mode == 1 || g.mode == 5) {
+                } else if (g.mode == 1 || g.mode == 5 || g.mode == 6) {
                     uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
+                    const float* mrow = g.mode == 6 ? g.mul + (size_t)m * g.mul_stride + col : nullptr;
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         uint32_t h[4];
@@ -295,6 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         for (int e = 0; e < 4; e++) {
                             float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
                             if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                            if (g.mode == 6 && col + 8 * i < g.N) f0 = gelu_tanh(f0) * __ldg(mrow + 8 * i + 2 * e), f1 = gelu_tanh(f1) * __ldg(mrow + 8 * i + 2 * e + 1);
                             const __half2 x = __floats2half2_rn(f0, f1);
                             h[e] = *reinterpret_cast<const uint32_t*>(&x);
                         }
@@ -346,7 +350,7 @@ EncodeTiled encode_tiled() {
 bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K % BK == 0 && (K * wbits / 8) % 16 == 0 && N > 0; }
 
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                           uint32_t wbits) {
+                           uint32_t wbits, const float* mul, uint32_t mul_stride) {
     EncodeTiled enc = encode_tiled();
     if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
     CUtensorMap amap, wmap;
@@ -375,7 +379,7 @@ int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, co
     }
     const uint32_t tiles = ((M + MT * BM - 1) / (MT * BM)) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
-    const Args g{s, out, M, N, K, mode};
+    const Args g{s, out, M, N, K, mode, mul, mul_stride};
     if (wbits == 4) gemm_persistent_kernel<4><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
     else gemm_persistent_kernel<8><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
     TB_CUDA(cudaGetLastError());

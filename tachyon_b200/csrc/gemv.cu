@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
         }
         const bool writer = (EPI == EPI_GEGLU || RPW == 1) ? lane == 0 : (lane & 15) == 0;
         if (writer && out_row < r1) {
-            if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[out_row] = r;
+            if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[out_row] = p.gelu_mul ? gelu_tanh(r) * __ldg(p.gelu_mul + out_row) : r;
             if constexpr (EPI == EPI_F16) static_cast<__half*>(p.y)[out_row] = __float2half_rn(r);
             if constexpr (EPI == EPI_GEGLU) static_cast<float*>(p.y)[out_row / 2] = r;
             if constexpr (EPI == EPI_ARGMAX) {
@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(256) gemv_q8_generic(const GemvParams p) {
     }
     sum = warp_sum(sum);
     if (lane == 0) {
-        if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[row] = sum;
+        if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[row] = p.gelu_mul ? gelu_tanh(sum) * __ldg(p.gelu_mul + row) : sum;
         else static_cast<__half*>(p.y)[row] = __float2half_rn(sum);
     }
 }
@@ -481,6 +481,7 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if (p.epi == EPI_GEGLU && p.rows % 2 != 0) return fail(OUT_OF_RANGE, "gemv: GeGLU needs an even number of rows");
     if (p.epi == EPI_ARGMAX && (p.best == nullptr || p.count == nullptr || p.state == nullptr)) return fail(OUT_OF_RANGE, "gemv: argmax needs best, count and state");
     if (p.epi != EPI_ARGMAX && p.y == nullptr) return fail(OUT_OF_RANGE, "gemv: null output");
+    if (p.gelu_mul != nullptr && p.epi != EPI_F32) return fail(OUT_OF_RANGE, "gemv: the GELU-times-vector output is f32");
     if (p.wbits != 8 && p.wbits != 4) return fail(OUT_OF_RANGE, "gemv: weights are 8 or 4 bits");
     if (p.wbits == 4) {
         switch (p.cols) {

@@ -77,6 +77,7 @@ struct GemvParams {
     float* h_out = nullptr;       // receives h' (written by one block); may be null
     int epi = EPI_F32;
     void* y = nullptr;            // EPI_F32/F16: [rows]; EPI_GEGLU: f32 [rows/2]; EPI_ARGMAX: optional f32 logits [rows]
+    const float* gelu_mul = nullptr;  // EPI_F32 only: y[r] = gelu_tanh(sum) * gelu_mul[r] (the per-layer input's gate, decode.rs:654-655)
     // EPI_ARGMAX: the pick is published through `best` (zero between launches) and `count` (zero between launches);
     // the last block writes state[1] = token, state[0] += 1, *token_out (may be null), and clears both.
     unsigned long long* best = nullptr;
@@ -157,8 +158,9 @@ int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* 
 
 // ---- prefill GEMM (tensor cores) ------------------------------------------------------------------------------
 // D[M, N] = A[M, K] (f16) x W[N, K]^T (Q8); mode 0: f32 out, 1: f16 out, 2: GeGLU of column pairs -> f16 [M, N/2].
+// mode 6 (the per-layer input's gate in prefill): out f16 [M, N] = gelu_tanh(product) * mul[m * mul_stride + n].
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                   uint32_t wbits = 8);
+                   uint32_t wbits = 8, const float* mul = nullptr, uint32_t mul_stride = 0);
 
 // ---- prefill kernels around the GEMMs (prefill.cu) ---------------------------------------------------------------------
 int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out,
@@ -201,7 +203,7 @@ int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, fl
 // The same product as a persistent kernel (gemm2.cu); launch_gemm_q8 validates and dispatches.
 bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits);
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                           uint32_t wbits);
+                           uint32_t wbits, const float* mul = nullptr, uint32_t mul_stride = 0);
 
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>

@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(256) prefill_embed_kernel(const int8_t* w, con
 }
 
 // ---- residual + norm, one block per token, 2048 values (8 per thread) -----------------------------------------------
-// h' = (h + w1 * rmsnorm(y)) * hscale when y is given (h updated in place), x = w2 * rmsnorm(h') as f16.
+// h' = (h + w1 * rmsnorm(y)) * hscale when y is given (h updated in place), x = w2 * rmsnorm(h') as f16, or h' itself
+// without w2 (what the per-layer input's gate reads).
 __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,
                                                            __half* x) {
     __shared__ float sh[8];
@@ -65,11 +66,12 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float
     float sq = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) sq = fmaf(v[i], v[i], sq);
-    const float rh = rsqrtf(block_sum(sq) / (float)n + eps);
+    const float rh = w2 != nullptr ? rsqrtf(block_sum(sq) / (float)n + eps) : 1.0f;
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const __half2 t = __floats2half2_rn(v[2 * i] * rh * __ldg(w2 + tid * 8 + 2 * i), v[2 * i + 1] * rh * __ldg(w2 + tid * 8 + 2 * i + 1));
+        const float w_a = w2 != nullptr ? __ldg(w2 + tid * 8 + 2 * i) : 1.0f, w_b = w2 != nullptr ? __ldg(w2 + tid * 8 + 2 * i + 1) : 1.0f;
+        const __half2 t = __floats2half2_rn(v[2 * i] * rh * w_a, v[2 * i + 1] * rh * w_b);
         o[i] = *reinterpret_cast<const uint32_t*>(&t);
     }
     *reinterpret_cast<uint4*>(x + base + tid * 8) = make_uint4(o[0], o[1], o[2], o[3]);

@@ -499,6 +499,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const StepPhase
 }  // namespace
 
 bool step_supports(const GemvParams& p) {
+    if (p.gelu_mul != nullptr) return false;  // the per-layer input's gate: not in the single-kernel step
     if (p.cols == 2048)
         return (p.xmode == X_NORM && (p.epi == EPI_F32 || p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX)) || ((p.xmode == X_F32 || p.xmode == X_ATTN) && p.epi == EPI_F32);
     return (p.cols == 4096 || p.cols == 8192 || p.cols == 16384) && p.xmode == X_F32 && p.epi == EPI_F32;

@@ -376,3 +376,42 @@ def test_global_layers_with_heads_of_512(ctx, kv, global_dim, global_kv):
         bad.global_head_dim = 128
         tb.Decoder(ctx, bad, context=64)
     assert e.value.status == 9
+
+
+def test_per_layer_inputs(ctx):
+    """Config::per_layer (model/mod.rs:38-39; decode.rs:572-579, 650-660): every layer adds a gated projection of its own
+    input, built from the token's row of a second table and a projection of the embedding.  Stepping and the chunked
+    prefill follow the CPU forward (tests/common/tiny.rs:239-252, 298-301), also with heads of 512 and a shared layer."""
+    cfg = small_config(layers=5)
+    cfg.per_layer, cfg.global_every, cfg.global_head_dim, cfg.shared = 256, 3, 512, 1
+    dec = tb.Decoder(ctx, cfg, context=96, chunk=40, keep_logits=True)
+    dec.fill_random(SEED)
+    dec.build()
+    ref = OracleModel(cfg, SEED, context=96, chunk=40)
+    assert ref.tensors["embed_per_layer.w"].shape == (cfg.vocab, 5 * 256) and ref.tensors["3.per_layer_proj.w"].shape == (cfg.hidden, 256)
+    token = 17
+    for pos in range(30):
+        want_token, want_logits, want_hidden = ref.step(token, pos)
+        got_token = dec.step(token)
+        order = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+        check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+        assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+        token = (pos * 7919 + 13) % cfg.vocab
+    # the inputs matter: without them the same weights give another hidden state
+    plain = small_config(layers=5)
+    plain.global_every, plain.global_head_dim, plain.shared = 3, 512, 1
+    other = OracleModel(plain, SEED, context=96, chunk=40)
+    assert np.abs(other.step(17, 0)[2] - ref.step(17, 0)[2]).max() > 0.05 * np.abs(want_hidden).max()
+    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(70)]
+    dec.reset()
+    for t in prompt[:-1]:
+        dec.step(t)
+    a, la = dec.step(prompt[-1]), dec.logits()
+    dec.reset()
+    dec.prefill(prompt[:-1])  # two chunks
+    b, lb = dec.step(prompt[-1]), dec.logits()
+    assert np.abs(la - lb).max() <= 4e-3 * np.abs(la).max()
+    dec.close()
+    with pytest.raises(tb.Error) as e:
+        tb.Decoder(ctx, cfg, context=96, weight_bits=4)
+    assert e.value.status == 9
