@@ -466,6 +466,43 @@ def bench_gemm(args, ranks: Ranks):
                          "flops_per_launch": 2.0 * m * n * k, "us_per_launch": us}}
 
 
+def bench_flash(args, ranks: Ranks):
+    """configs[3]'s attention alone: 2048 tokens x 8 query / 2 kv heads of 256 over the cache ring, sliding 512 and global."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    heads, kv, d, T, cap = 8, 2, 256, args.tokens, 4096
+    lib = ctx.lib
+    kc, vc, q = ctx.alloc(kv * cap * d * 2), ctx.alloc(kv * cap * d * 2), ctx.alloc(T * heads * d * 2)
+    tb.check(lib.tb_fill_gauss_f16(ctx.handle, 1, 1, kc.ptr, kv * cap * d, 1.0))
+    tb.check(lib.tb_fill_gauss_f16(ctx.handle, 1, 2, vc.ptr, kv * cap * d, 1.0))
+    tb.check(lib.tb_fill_gauss_f16(ctx.handle, 1, 3, q.ptr, T * heads * d, 0.09))  # scale * log2(e) folded in: scores ~N(0, 1.4)
+    out = ctx.zeros(T * heads * d * 2)
+    results = {}
+    for name, window in (("sliding_512", 512), ("global", cap)):
+        for _ in range(args.warmup):
+            ctx.prefill_attend(q, kc, vc, out, T, 0, cap, window, heads, kv, d)
+        ctx.sync()
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record()
+        for _ in range(args.steps):
+            ctx.prefill_attend(q, kc, vc, out, T, 0, cap, window, heads, kv, d)
+        e1.record()
+        e1.sync()
+        us = e0.elapsed_ms(e1) * 1e3 / args.steps
+        keys = sum(min(t + 1, window) for t in range(T))  # keys each token's heads see
+        flops = 4.0 * keys * heads * d
+        results[name] = {"us_per_launch": us, "flops_per_launch": flops, "achieved_tflops": flops / us / 1e6}
+    burst, sustained, how = measured_peak_tflops()
+    g = results["sliding_512"]
+    return {"metric": "prefill_attention_us", "value": g["us_per_launch"], "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": g["us_per_launch"] / 1e3, "higher_is_better": False, "dtype": "f16 mma.sync, f32 softmax and sums", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3] prefill attention: {T} tokens, 8 query / 2 kv heads of 256, sliding window 512 (and global)"},
+            "gpu_launches": args.steps, "cases": results,
+            "roofline": {"bound": "tensor", "achieved": g["achieved_tflops"], "peak": burst, "unit": "TFLOP/s", "frac": g["achieved_tflops"] / burst,
+                         "peak_source": how, "traffic": None, "flops_per_launch": g["flops_per_launch"], "us_per_launch": g["us_per_launch"]}}
+
+
 def bench_prefill(args, ranks: Ranks):
     """configs[3]: one prompt of 2048 token ids through the 35-layer model; the last token goes through the decode step."""
     import tachyon_b200 as tb
@@ -575,7 +612,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "prefill", "encoder"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -598,6 +635,8 @@ def main():
             line = bench_gemv_q4(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "attend":
             line = bench_attend(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "flash":
+            line = bench_flash(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "gemm":
             line = bench_gemm(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "prefill":

@@ -157,6 +157,12 @@ __device__ __forceinline__ void cp_async_16_zfill(void* dst, const void* src, ui
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// 2^x by the hardware's approximation; 2^-inf is 0.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -199,18 +205,27 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
 
     // Tiles arrive through cp.async, one tile ahead of the products: the copy of tile i + 1 is in flight while tile i is
     // multiplied.  Rows past the block's last position are filled with zeros (stale cache rows could hold anything).
+    // A thread copies the same 16 bytes of every (nthreads / (DH / 8))-th row (the block's threads are a multiple of a row's pieces).
+    const uint32_t piece = tid % (DH / 8), row0 = tid / (DH / 8), row_step = nthreads / (DH / 8);
+    const __half* kbase = kc + (size_t)g * cap * DH + piece * 8;
+    const __half* vbase = vc + (size_t)g * cap * DH + piece * 8;
     auto fetch = [&](uint32_t j0, uint32_t stage) {
-        __half* Kd = KV + stage * (2 * FK * LDS);
+        __half* Kd = KV + stage * (2 * FK * LDS) + piece * 8;
         __half* Vd = Kd + FK * LDS;
-        for (uint32_t c = tid; c < FK * (DH / 8); c += nthreads) {
-            const uint32_t r = c / (DH / 8), ch = c % (DH / 8), j = j0 + r;
-            const uint32_t bytes = j <= p_last ? 16u : 0u;
-            const size_t at = ((size_t)g * cap + (j <= p_last ? j % cap : 0u)) * DH + ch * 8;
-            cp_async_16_zfill(Kd + r * LDS + ch * 8, kc + at, bytes);
-            cp_async_16_zfill(Vd + r * LDS + ch * 8, vc + at, bytes);
+        const uint32_t slot0 = j0 % cap;
+        for (uint32_t r = row0; r < FK; r += row_step) {
+            const bool live = j0 + r <= p_last;
+            uint32_t slot = slot0 + r;
+            slot = slot >= cap ? slot % cap : slot;
+            const size_t at = live ? (size_t)slot * DH : 0;
+            cp_async_16_zfill(Kd + r * LDS, kbase + at, live ? 16u : 0u);
+            cp_async_16_zfill(Vd + r * LDS, vbase + at, live ? 16u : 0u);
         }
         cp_async_commit();
     };
+    // Tiles every row of the block sees whole need no mask: all keys at or before the first row's position and inside the
+    // last row's window.  (A block with rows past the chunk's end always masks.)
+    const bool whole_rows = t0 + FT <= tokens;
     fetch(tile0, 0);
     uint32_t stage = 0;
     for (uint32_t j0 = tile0; j0 <= p_last; j0 += FK, stage ^= 1u) {
@@ -238,31 +253,39 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
         }
         // Mask, running maximum and sums (scores are already in base 2: the queries carry scale*log2(e)).
         float mt[2] = {-INFINITY, -INFINITY};
+        if (whole_rows && j0 + FK - 1 <= p_first && j0 + window > p_first + FT - 1) {
 #pragma unroll
-        for (int nb = 0; nb < FK / 8; nb++) {
+            for (int nb = 0; nb < FK / 8; nb++) {
+                mt[0] = fmaxf(mt[0], fmaxf(sc[nb][0], sc[nb][1]));
+                mt[1] = fmaxf(mt[1], fmaxf(sc[nb][2], sc[nb][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), p = (e < 2) ? pa : pb;
-                const bool seen = j <= p && j + window > p && p <= p_last;
-                sc[nb][e] = seen ? sc[nb][e] : -INFINITY;
-                mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+            for (int nb = 0; nb < FK / 8; nb++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), p = (e < 2) ? pa : pb;
+                    const bool seen = j <= p && j + window > p && p <= p_last;
+                    sc[nb][e] = seen ? sc[nb][e] : -INFINITY;
+                    mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+                }
             }
         }
-        float corr[2];
+        float corr[2], base[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 1));
             mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 2));
             const float mn = fmaxf(m_run[h], mt[h]);
-            corr[h] = (mn == -INFINITY) ? 1.0f : exp2f(m_run[h] - mn);  // a row that has seen nothing yet keeps its zeros
+            base[h] = fmaxf(mn, -1e30f);        // finite, so a row that has seen nothing yet gets 2^-inf = 0 and no NaN
+            corr[h] = ex2(m_run[h] - base[h]);  // 1 when the maximum stays; 0 for a row's first keys (its sums are zeros)
             m_run[h] = mn;
         }
         float lt[2] = {0.0f, 0.0f};
         uint32_t pfrag[FK / 16][4];
 #pragma unroll
         for (int nb = 0; nb < FK / 8; nb++) {
-            float e0 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][0] - m_run[0]), e1 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][1] - m_run[0]);
-            float e2 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][2] - m_run[1]), e3 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][3] - m_run[1]);
+            const float e0 = ex2(sc[nb][0] - base[0]), e1 = ex2(sc[nb][1] - base[0]), e2 = ex2(sc[nb][2] - base[1]), e3 = ex2(sc[nb][3] - base[1]);
             const __half2 h01 = __floats2half2_rn(e0, e1), h23 = __floats2half2_rn(e2, e3);
             // the sums use the rounded probabilities, the ones the values are weighted with
             lt[0] += __low2float(h01) + __high2float(h01);
