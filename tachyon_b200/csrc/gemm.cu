@@ -372,6 +372,8 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         // (Read at every launch, so a test can run both.)  Up to 128 tokens the persistent tile of 256 would be half empty.
         const char* e = getenv("TACHYON_B200_GEMM");
         const int which = e ? atoi(e) : 0;
+        // 3 and 4: the pair schedule of gemm3.cu with tiles of 256 and 128 weight rows.
+        if ((which == 3 || which == 4) && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
         const bool stores_only = (mode == 0 || mode == 1 || mode == 3) && M > 128;
         if ((which == 2 || (which == 0 && stores_only)) && gemm_persistent_supports(N, K, wbits)) return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits);
     }

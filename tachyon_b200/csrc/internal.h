@@ -200,6 +200,10 @@ int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32
 // cos/sin of every (position, frequency): table [positions][256] for AttendParams::trig.
 int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, float* table);
 
+// The same product on pairs of SMs (gemm3.cu, tcgen05 cta_group::2).
+bool gemm_pair_supports(uint32_t N, uint32_t K, uint32_t wbits, int mode);
+int launch_gemm_pair(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
+                     uint32_t wbits, bool narrow);
 // The same product as a persistent kernel (gemm2.cu); launch_gemm_q8 validates and dispatches.
 bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits);
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,

@@ -13,10 +13,13 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(128, 128, 64), (128, 128, 256), (1, 128, 2048), (37, 256, 2048), (300, 3072, 2048), (512, 2048, 2048), (129, 2048, 16384), (256, 96, 128)]
 
 
-@pytest.fixture(params=["one tile per block", "persistent"])
+SCHEDULES = {"one tile per block": "1", "persistent": "2", "pairs of SMs, tiles of 256 weight rows": "3", "pairs of SMs, tiles of 128 weight rows": "4"}
+
+
+@pytest.fixture(params=list(SCHEDULES))
 def schedule(request, monkeypatch):
-    """Both schedules of the GEMM (the library reads the variable at every launch); left to itself it picks by shape."""
-    monkeypatch.setenv("TACHYON_B200_GEMM", "1" if request.param == "one tile per block" else "2")
+    """Every schedule of the GEMM (the library reads the variable at every launch); left to itself it picks by shape."""
+    monkeypatch.setenv("TACHYON_B200_GEMM", SCHEDULES[request.param])
     return request.param
 
 
