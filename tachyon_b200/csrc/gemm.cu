@@ -365,16 +365,16 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
     {
-        // Two schedules: this file's one tile per block, and gemm2.cu's persistent blocks whose epilogue overlaps the next
-        // tile's products.  Measured on the benchmark's shapes the persistent one wins where the epilogue only stores
-        // (f32, f16, residual add: +3..25 %), and loses where it computes a GELU per output (its epilogue warps share
-        // the issue slots with the dequantising warps).  TACHYON_B200_GEMM=1 or 2 forces one of them.
+        // Schedules: this file's one tile per block; gemm2.cu's persistent blocks, whose epilogue overlaps the next tile's
+        // products and whose MMAs read less shared memory per FLOP; gemm3.cu's pairs of SMs.  Measured on the benchmark's
+        // shapes the persistent one wins where the epilogue stores f32 (plain or added to the output: 1.2 to 1.7 times
+        // the rate), and loses where it stores f16 or computes a GELU per output.  TACHYON_B200_GEMM=1..4 forces one.
         // (Read at every launch, so a test can run both.)  Up to 128 tokens the persistent tile of 256 would be half empty.
         const char* e = getenv("TACHYON_B200_GEMM");
         const int which = e ? atoi(e) : 0;
         // 3 and 4: the pair schedule of gemm3.cu with tiles of 256 and 128 weight rows.
         if ((which == 3 || which == 4) && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
-        const bool stores_only = (mode == 0 || mode == 1 || mode == 3) && M > 128;
+        const bool stores_only = (mode == 0 || mode == 3) && M > 128;
         if ((which == 2 || (which == 0 && stores_only)) && gemm_persistent_supports(N, K, wbits)) return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits);
     }
     EncodeTiled enc = encode_tiled();

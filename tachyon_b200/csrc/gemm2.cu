@@ -34,7 +34,10 @@ constexpr int OFF_A = 0, OFF_B = OFF_A + ST * A_BYTES, OFF_C = OFF_B + ST * B_BY
 constexpr int SMEM_BYTES = 1024 + OFF_BAR + 512;
 static_assert(SMEM_BYTES <= 232448, "over the 227 KiB a block may use");
 
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // kind::f16, f32 accumulator, K-major A and B
+// kind::f16, f32 accumulator, K-major operands.  The weight tile is the MMA's A operand (M = 128 weight rows) and the token
+// tile its B operand (N = 256 tokens): one M128 N256 product reads 12 KiB of shared memory per 16 of K where two M128 N128
+// products with the roles the other way round read 16, and shared-memory bandwidth is what the tensor pipe waits for.
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)((MT * BM) >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {  // K-major, 128-byte rows, SWIZZLE_128B, 1024 bytes between 8-row groups
     const uint32_t lo = ((addr & 0x3ffffu) >> 4) | (1u << 16);
@@ -184,10 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a = smem_addr(As + s * A_BYTES), bb = smem_addr(Bs + s * B_BYTES);
 #pragma unroll
-                    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-                        for (int k = 0; k < BK / 16; k++)
-                            mma_f16(tmem + b * (MT * BN) + mt * BN, smem_desc(a + mt * (BM * BK * 2) + k * 32), smem_desc(bb + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; k++) mma_f16(tmem + b * (MT * BM), smem_desc(bb + k * 32), smem_desc(a + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
                     mma_commit(&bar.empty[s]);
                 }
                 mma_commit(&bar.acc_full[b]);  // arrives when the tile's products have finished
@@ -255,70 +255,68 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
             }
         }
     } else {
-        // Epilogue: a warp reads the accumulator lanes (token rows) of its quarter q = warp % 4, 32 columns at a time;
-        // the EW / 4 warps of a quarter take alternate column blocks.
+        // Epilogue: the accumulator's lanes are weight rows, its columns tokens.  A warp reads the lanes of its quarter
+        // q = warp % 4, 32 tokens at a time (the EW / 4 warps of a quarter take alternate blocks of tokens); for each token
+        // its 32 lanes then hold 32 consecutive outputs of that token's row, which go out as one 128-byte (f32) store.
         const uint32_t q = warp & 3, part = (warp - FIRST_EW) >> 2;
         uint32_t ti = 0;
         for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ti++) {
-            const uint32_t b = ti & 1, m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
+            const uint32_t b = ti & 1, m0 = (t % tiles_m) * (MT * BM), n = (t / tiles_m) * BN + 32 * q + lane;
             if (!mbar_wait(&bar.acc_full[b], (ti >> 1) & 1)) {
                 atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool row_ok = n < g.N;  // the same for the whole warp: N is a multiple of 32
 #pragma unroll 1
-            for (int cbi = part; cbi < MT * (BN / 32); cbi += EW / 4) {
-                const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
-                const uint32_t m = m0 + mt * BM + 32 * q + lane;
+            for (int cb = part; cb < MT * BM / 32; cb += EW / 4) {
                 uint32_t r[32];
-                tmem_load32(tmem + ((32 * q) << 16) + b * (MT * BN) + mt * BN + cb * 32, r);
-                if (m >= g.M) continue;
-                const uint32_t col = n0 + cb * 32;
-                if (g.mode == 3) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+                tmem_load32(tmem + ((32 * q) << 16) + b * (MT * BM) + cb * 32, r);
+                if (!row_ok) continue;
+                const uint32_t mb = m0 + cb * 32;
+                if (g.mode == 0) {
+                    float* dst = static_cast<float*>(g.out) + (size_t)mb * g.N + n;
 #pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        if (col + 4 * i < g.N) {
-                            float4 x = dst[i];
-                            x.x += __uint_as_float(r[4 * i]), x.y += __uint_as_float(r[4 * i + 1]), x.z += __uint_as_float(r[4 * i + 2]), x.w += __uint_as_float(r[4 * i + 3]);
-                            dst[i] = x;
-                        }
-                } else if (g.mode == 0) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+                    for (int i = 0; i < 32; i++)
+                        if (mb + i < g.M) dst[(size_t)i * g.N] = __uint_as_float(r[i]);
+                } else if (g.mode == 3) {
+                    // The old values first, sixteen loads in flight, then the sums (a load after a store to the same array
+                    // would wait for it).
+                    float* dst = static_cast<float*>(g.out) + (size_t)mb * g.N + n;
 #pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    for (int half = 0; half < 2; half++) {
+                        float old[16];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) old[i] = mb + 16 * half + i < g.M ? __ldcg(dst + (size_t)(16 * half + i) * g.N) : 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            if (mb + 16 * half + i < g.M) dst[(size_t)(16 * half + i) * g.N] = old[i] + __uint_as_float(r[16 * half + i]);
+                    }
                 } else if (g.mode == 1 || g.mode == 5 || g.mode == 6) {
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
-                    const float* mrow = g.mode == 6 ? g.mul + (size_t)m * g.mul_stride + col : nullptr;
+                    // Two lanes (weight rows n, n + 1) trade values so that each writes a pair of halves: the even lane
+                    // the even tokens of a pair of tokens, the odd lane the odd ones.
+                    const uint32_t odd = lane & 1u;
+                    __half* dst = static_cast<__half*>(g.out) + (size_t)(mb + odd) * g.N + (n - odd);
+                    const float* mrow = g.mode == 6 ? g.mul + (size_t)mb * g.mul_stride + n : nullptr;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
-                            if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
-                            if (g.mode == 6 && col + 8 * i < g.N) f0 = gelu_tanh(f0) * __ldg(mrow + 8 * i + 2 * e), f1 = gelu_tanh(f1) * __ldg(mrow + 8 * i + 2 * e + 1);
-                            const __half2 x = __floats2half2_rn(f0, f1);
-                            h[e] = *reinterpret_cast<const uint32_t*>(&x);
+                    for (int k = 0; k < 16; k++) {
+                        float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
+                        if (g.mode == 5) v0 = gelu_erf(v0), v1 = gelu_erf(v1);
+                        if (g.mode == 6) {
+                            v0 = mb + 2 * k < g.M ? gelu_tanh(v0) * __ldg(mrow + (size_t)(2 * k) * g.mul_stride) : 0.0f;
+                            v1 = mb + 2 * k + 1 < g.M ? gelu_tanh(v1) * __ldg(mrow + (size_t)(2 * k + 1) * g.mul_stride) : 0.0f;
                         }
-                        if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);  // the neighbour's value for my token
+                        const __half2 pair = odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
+                        if (mb + 2 * k + odd < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * g.N) = pair;
                     }
                 } else {
-                    // columns (2j, 2j + 1) are (gate_j, up_j): gelu(gate) * up, 16 results per 32 columns
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * (g.N / 2) + col / 2);
+                    // weight rows (2j, 2j + 1) are (gate_j, up_j): the even lane takes its neighbour's value and writes gelu(gate) * up
+                    __half* dst = static_cast<__half*>(g.out) + (size_t)mb * (g.N / 2) + n / 2;
 #pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
-                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
-                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
-                            const __half2 x = __floats2half2_rn(a0, a1);
-                            h[e] = *reinterpret_cast<const uint32_t*>(&x);
-                        }
-                        if (col + 16 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                    for (int i = 0; i < 32; i++) {
+                        const float gate = __uint_as_float(r[i]), up = __shfl_down_sync(0xffffffffu, gate, 1);
+                        if ((lane & 1) == 0 && mb + i < g.M) dst[(size_t)i * (g.N / 2)] = __float2half_rn((g.mode == 2 ? gelu_tanh(gate) : gelu_erf(gate)) * up);
                     }
                 }
             }

@@ -8,13 +8,12 @@
 //
 // Warps of each block: 0 activation copies, 1 code copies, 2 MMA issue (leading block) or relay (the other block: tells
 // the leader when a stage of its shared memory is full), then the dequantising warps, then eight epilogue warps.
-// Barriers between the blocks: both blocks' dequantising warps and the relay arrive on the leader's `full`; the leader's
-// commits arrive on both blocks' `empty` and `acc_full`; both blocks' epilogue warps arrive on the leader's `acc_empty`.  Every wait is
+// Barriers between the blocks: the relay arrives on the leader's `peer_full`; the leader's commits arrive on both
+// blocks' `empty` and `acc_full`; both blocks' epilogue warps arrive on the leader's `acc_empty`.  Every wait is
 // bounded; a warp that gives up records it in the context's status word and leaves its loops; the blocks meet at a
 // cluster barrier before either exits, so neither reads the other's shared memory after it is gone.
 #include <cuda.h>
 
-#include <cstdio>
 #include <string>
 
 #include "common.cuh"
@@ -25,9 +24,11 @@ namespace tb {
 namespace {
 
 constexpr int BM = 128, BK = 64;  // token rows per block, K per stage
-constexpr int ST = 4;             // stages of f16 operands
-constexpr int CS = 8;             // stages of codes
+constexpr int ST = 6;             // stages of f16 operands
+constexpr int CS = 4;             // stages of codes (at least PER)
 constexpr int EW = 8;             // epilogue warps (two per quarter of the accumulator's lanes)
+constexpr int PER = 3;            // k tiles a dequantising warp converts per turn
+constexpr int RELAYS = 4;         // lanes of the second block's relay warp (fewer than ST)
 constexpr int FIRST_DW = 3;
 
 // BN: weight rows of a pair's tile (accumulator columns); each block dequantises BN / 2 of them.
@@ -47,7 +48,6 @@ struct Shape {
     static_assert(COLS == 256 || COLS == 512, "tensor memory is allocated in powers of two");
 };
 
-__device__ unsigned long long g_pair_dbg[8];  // DEBUG: ns waited by pair 0: [0] leader on full, [1] leader total, [2] dequant on empty, [3] dequant on codes, [4] dequant total
 enum : uint32_t { ERR_PAIR_TMEM = 5 };  // the two blocks of a pair were given different tensor memory
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {  // K-major, 128-byte rows, SWIZZLE_128B, 1024 bytes between 8-row groups
@@ -151,7 +151,7 @@ struct Args {
 };
 
 struct Bars {
-    uint64_t full[ST], a_full[ST], empty[ST], c_full[CS], c_empty[CS], acc_full[2], acc_empty[2];
+    uint64_t full[ST], peer_full[ST], empty[ST], c_full[CS], c_empty[CS], acc_full[2], acc_empty[2];
     uint32_t tmem;
 };
 
@@ -168,9 +168,8 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
     const uint32_t nk = g.K / BK, tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + BN - 1) / BN, tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
-        // full (the leader's is the one in use): its own activation copy, the other block's (through the relay), and the
-        // dequantising warps of both blocks.  a_full: the other block's activation copy, which its relay waits for.
-        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], 2 * S::DW + 2), mbar_init(&bar.a_full[i], 1), mbar_init(&bar.empty[i], 1);
+        // full: this block's activation copy and its dequantising warps.  peer_full (the leader's): the other block's relay.
+        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], S::DW + 1), mbar_init(&bar.peer_full[i], 1), mbar_init(&bar.empty[i], 1);
         for (int i = 0; i < CS; i++) mbar_init(&bar.c_full[i], 1), mbar_init(&bar.c_empty[i], S::DW);
         for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], 2 * EW);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -204,9 +203,8 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                         t = tiles;
                         break;
                     }
-                    uint64_t* landed = rank == 0 ? &bar.full[s] : &bar.a_full[s];
-                    mbar_expect_tx(landed, S::A_BYTES);
-                    tma_load_2d(As + s * S::A_BYTES, &a_map, (int)(kt * BK), (int)m0, landed);
+                    mbar_expect_tx(&bar.full[s], S::A_BYTES);
+                    tma_load_2d(As + s * S::A_BYTES, &a_map, (int)(kt * BK), (int)m0, &bar.full[s]);
                 }
             }
         }
@@ -232,7 +230,6 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
             // The leader: one MMA of M 256 per 16 of K, reading both blocks' stages.
             uint32_t it = 0, ti = 0;
             bool ok = true;
-            unsigned long long w_full = 0, t_begin = global_ns();
             for (uint32_t t = pair; t < tiles && ok; t += pairs, ti++) {
                 const uint32_t b = ti & 1;
                 if (ti >= 2 && !mbar_wait_cluster(&bar.acc_empty[b], ((ti >> 1) - 1) & 1)) {
@@ -242,13 +239,11 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (uint32_t kt = 0; kt < nk; kt++, it++) {
                     const uint32_t s = it % ST;
-                    const unsigned long long w0 = global_ns();
-                    if (!mbar_wait_cluster(&bar.full[s], (it / ST) & 1)) {
+                    if (!mbar_wait(&bar.full[s], (it / ST) & 1) || !mbar_wait_cluster(&bar.peer_full[s], (it / ST) & 1)) {
                         atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
                         ok = false;
                         break;
                     }
-                    w_full += global_ns() - w0;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a = smem_addr(As + s * S::A_BYTES), bb = smem_addr(Bs + s * S::B_BYTES);
 #pragma unroll
@@ -259,21 +254,20 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                     mma_commit_both(smem_addr(&bar.acc_full[b]));  // arrive when the tile's products have finished, in both blocks
                 }
             }
-            if (pair == 0) g_pair_dbg[0] = w_full, g_pair_dbg[1] = global_ns() - t_begin;
-        } else if (lane == 0) {
-            // The relay: tells the leader when this block's activation rows of stage s have landed (the dequantising warps
-            // arrive on the leader's barrier themselves).
-            uint32_t it = 0;
-            for (uint32_t t = pair; t < tiles; t += pairs) {
-                for (uint32_t kt = 0; kt < nk; kt++, it++) {
-                    const uint32_t s = it % ST;
-                    if (!mbar_wait(&bar.a_full[s], (it / ST) & 1)) {
-                        atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
-                        t = tiles;
-                        break;
-                    }
-                    mbar_arrive_cluster(in_cta(smem_addr(&bar.full[s]), 0));
+        } else if (rank == 1 && lane < RELAYS) {
+            // The relay: tells the leader when stage s of this block (activation rows and dequantised weights) is full.  The
+            // dequantising warps arrive on their own block's barrier: a release at cluster scope in their loop measured
+            // twice the time per turn.  An arrival at the other SM takes the issuing thread most of a microsecond, more
+            // than the products of a k tile, so RELAYS lanes take the k tiles in turn (fewer than ST: when a lane moves on
+            // to k tile it + RELAYS, the stage's barrier has long finished the phase before the one it waits for).
+            const uint32_t mine = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;  // tiles this pair takes
+            for (uint32_t it = lane; it < mine * nk; it += RELAYS) {
+                const uint32_t s = it % ST;
+                if (!mbar_wait(&bar.full[s], (it / ST) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                    break;
                 }
+                mbar_arrive_cluster(in_cta(smem_addr(&bar.peer_full[s]), 0));
             }
         }
     } else if (warp < S::FIRST_EW) {
@@ -281,10 +275,8 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
         const int j = threadIdx.x - 32 * FIRST_DW, row = j >> 2, qtr = j & 3;
         constexpr uint32_t GS = WB == 4 ? 8 : 4;               // k tiles one 16-byte load of scales covers
         const uint32_t spr = g.K / (WB == 4 ? 64 : 32);        // scales per row
-        const uint32_t full_at_leader = in_cta(smem_addr(&bar.full[0]), 0);  // barriers are 8 bytes apart
         uint32_t it = 0, ic = 0;
         bool ok = true;
-        unsigned long long w_empty = 0, w_codes = 0, t_begin = global_ns();
         for (uint32_t t = pair; t < tiles && ok; t += pairs) {
             const uint32_t n = (t / tiles_m) * BN + rank * S::BH + row;
             const bool live = n < g.N;
@@ -299,20 +291,12 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                 return make_uint4(w[0], w[1], w[2], w[3]);
             };
             uint4 sc = scales_from(0), sc_next = sc;
-            for (uint32_t kt = 0; kt < nk; kt++, it++, ic++) {
+            // The codes of k tile `kt` (code stage c) as eight f16 pairs of code * scale.
+            auto convert = [&](uint32_t kt, uint32_t c, uint32_t (&v)[8]) {
                 if (kt % GS == 0) {
                     if (kt > 0) sc = sc_next;
                     if (kt + GS < nk) sc_next = scales_from(kt + GS);  // one group ahead
                 }
-                const uint32_t c = ic % CS, s = it % ST;
-                const unsigned long long w0 = global_ns();
-                if (!mbar_wait(&bar.c_full[c], (ic / CS) & 1)) {
-                    atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
-                    ok = false;
-                    break;
-                }
-                w_codes += global_ns() - w0;
-                uint32_t v[8];
                 const uint32_t h = WB == 4 ? (kt & 7u) : 2u * (kt & 3u) + (uint32_t)(qtr >> 1);  // which of the eight scales
                 const uint32_t word = (h >> 1) == 0 ? sc.x : (h >> 1) == 1 ? sc.y : (h >> 1) == 2 ? sc.z : sc.w;
                 const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)((h & 1u) ? (word >> 16) : (word & 0xffffu))));
@@ -326,27 +310,55 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                     const uint4 cw = *reinterpret_cast<const uint4*>(Cs + c * S::C_BYTES + row * BK + qtr * 16);
                     dequant4(cw.x, s2, v[0], v[1]), dequant4(cw.y, s2, v[2], v[3]), dequant4(cw.z, s2, v[4], v[5]), dequant4(cw.w, s2, v[6], v[7]);
                 }
+            };
+            auto store = [&](uint32_t stage, const uint32_t (&v)[8]) {
+                uint8_t* base = Bs + stage * S::B_BYTES + row * 128;
+                *reinterpret_cast<uint4*>(base + (((2 * qtr) ^ (row & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<uint4*>(base + (((2 * qtr + 1) ^ (row & 7)) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
+            };
+            // PER k tiles a turn: a turn's fixed costs (the waits, the proxy fence, the arrivals) are paid once per PER stages.
+            for (uint32_t kt = 0; kt < nk; kt += PER) {
+                const uint32_t cnt = min((uint32_t)PER, nk - kt);
+                bool got = true;
+#pragma unroll
+                for (uint32_t i = 0; i < PER; i++)
+                    if (i < cnt) got = got && mbar_wait(&bar.c_full[(ic + i) % CS], ((ic + i) / CS) & 1);
+                if (!got) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                    ok = false;
+                    break;
+                }
+                uint32_t v[PER][8];
+#pragma unroll
+                for (uint32_t i = 0; i < PER; i++)
+                    if (i < cnt) convert(kt + i, (ic + i) % CS, v[i]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar.c_empty[c]);  // the codes are in registers
-                const unsigned long long w1 = global_ns();
-                if (it >= ST && !mbar_wait_cluster(&bar.empty[s], ((it / ST) - 1) & 1)) {
+                if (lane == 0) {  // the codes are in registers
+#pragma unroll
+                    for (uint32_t i = 0; i < PER; i++)
+                        if (i < cnt) mbar_arrive(&bar.c_empty[(ic + i) % CS]);
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < PER; i++)
+                    if (i < cnt && it + i >= ST) got = got && mbar_wait_cluster(&bar.empty[(it + i) % ST], (((it + i) / ST) - 1) & 1);
+                if (!got) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                     ok = false;
                     break;
                 }
-                w_empty += global_ns() - w1;
-                uint8_t* base = Bs + s * S::B_BYTES + row * 128;
-                *reinterpret_cast<uint4*>(base + (((2 * qtr) ^ (row & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<uint4*>(base + (((2 * qtr + 1) ^ (row & 7)) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+                for (uint32_t i = 0; i < PER; i++)
+                    if (i < cnt) store((it + i) % ST, v[i]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read through the async proxy
                 __syncwarp();
                 if (lane == 0) {
-                    if (rank == 0) mbar_arrive(&bar.full[s]);
-                    else mbar_arrive_cluster(full_at_leader + s * 8);
+#pragma unroll
+                    for (uint32_t i = 0; i < PER; i++)
+                        if (i < cnt) mbar_arrive(&bar.full[(it + i) % ST]);
                 }
+                it += cnt, ic += cnt;
             }
         }
-        if (pair == 0 && j == 0) g_pair_dbg[2 + 3 * rank] = w_empty, g_pair_dbg[3 + 3 * rank] = w_codes, g_pair_dbg[4 + 3 * rank] = global_ns() - t_begin;
     } else {
         // Epilogue: a warp reads the accumulator lanes (this block's token rows) of its quarter q = warp % 4, 32 columns at
         // a time; the two warps of a quarter take alternate column blocks.
@@ -451,16 +463,6 @@ int launch_pair(tb_context* ctx, const CUtensorMap& amap, const CUtensorMap& wma
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr, cfg.numAttrs = 1;
-    if (getenv("TACHYON_B200_PAIR_INFO")) {
-        unsigned long long d[8];
-        cudaDeviceSynchronize();
-        cudaMemcpyFromSymbol(d, g_pair_dbg, sizeof(d));
-        fprintf(stderr, "previous launch, pair 0 (us): leader waited on full %.1f of %.1f; dequant r0 waited empty %.1f codes %.1f of %.1f; r1 empty %.1f codes %.1f of %.1f\n",
-                d[0] / 1e3, d[1] / 1e3, d[2] / 1e3, d[3] / 1e3, d[4] / 1e3, d[5] / 1e3, d[6] / 1e3, d[7] / 1e3);
-        int n = -1;
-        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<WB, BN>, &cfg);
-        fprintf(stderr, "pair kernel: %u pairs launched, max active clusters %d (%s)\n", pairs, n, cudaGetErrorString(e));
-    }
     TB_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<WB, BN>, amap, wmap, g, ctx->status));
     return OK;
 }
