@@ -311,12 +311,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         if (mb + 2 * k + odd < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * g.N) = pair;
                     }
                 } else {
-                    // weight rows (2j, 2j + 1) are (gate_j, up_j): the even lane takes its neighbour's value and writes gelu(gate) * up
-                    __half* dst = static_cast<__half*>(g.out) + (size_t)mb * (g.N / 2) + n / 2;
+                    // Weight rows (2j, 2j + 1) are (gate_j, up_j): lanes 4c .. 4c + 3 hold gate, up, gate, up of outputs n / 2 and
+                    // n / 2 + 1.  The even lanes take their neighbour's `up` and compute gelu(gate) * up for two tokens; then
+                    // lane 4c writes the pair of outputs of the even token and lane 4c + 2 that of the odd token.
+                    const bool even = (lane & 1u) == 0, second = (lane & 2u) != 0;
+                    __half* dst = static_cast<__half*>(g.out) + (size_t)(mb + (second ? 1 : 0)) * (g.N / 2) + (n - (second ? 2 : 0)) / 2;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const float gate = __uint_as_float(r[i]), up = __shfl_down_sync(0xffffffffu, gate, 1);
-                        if ((lane & 1) == 0 && mb + i < g.M) dst[(size_t)i * (g.N / 2)] = __float2half_rn((g.mode == 2 ? gelu_tanh(gate) : gelu_erf(gate)) * up);
+                    for (int k = 0; k < 16; k++) {
+                        const float g0 = __uint_as_float(r[2 * k]), g1 = __uint_as_float(r[2 * k + 1]);
+                        const float u0 = __shfl_down_sync(0xffffffffu, g0, 1), u1 = __shfl_down_sync(0xffffffffu, g1, 1);
+                        float a0 = 0.0f, a1 = 0.0f;
+                        if (even) {
+                            a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * u0;
+                            a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * u1;
+                        }
+                        const float got = __shfl_xor_sync(0xffffffffu, second ? a0 : a1, 2);  // the other pair's output for my token
+                        const __half2 pair = second ? __floats2half2_rn(got, a1) : __floats2half2_rn(a0, got);
+                        if (even && mb + 2 * k + (second ? 1 : 0) < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * (g.N / 2)) = pair;
                     }
                 }
             }
