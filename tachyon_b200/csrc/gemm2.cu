@@ -2,15 +2,17 @@
 // and an f16 scale per 32, or the reference's Q4 nibbles and a scale per 64), f32 accumulation in tensor memory.
 // Stands in for the reference's gemm_q4 (crates/tachyon/src/ptx/gemm.rs:225-259) and gemm_q8* (ptx/encoder.rs:315-375);
 // same results as gemm.cu's kernel, different schedule, built on what measuring that kernel showed: its tensor pipe
-// waits for the dequantised weight tile (the codes' trip from the L2, the conversion, the swizzled stores), and
-// between tiles for the epilogue.  Here
+// waits for operands (the codes' trip from the L2, the conversion, the swizzled stores, and shared-memory bandwidth
+// itself), and between tiles for the epilogue.  Here
 //   * one block per SM walks the output tiles (256 tokens x 128 weight rows), tiles that share weight rows running at
 //     the same time on neighbouring SMs so that their code reads meet in the L2;
 //   * the codes come through their own ring of eight bulk tensor copies, far enough ahead that no warp waits for the L2;
 //   * sixteen warps turn a stage's codes into f16 in the K-major swizzled layout the tensor core reads;
-//   * the accumulator is double-buffered (2 x 256 columns of tensor memory): four epilogue warps drain one tile while
-//     the products of the next are issued.
-// Warps: 0 activation copies, 1 code copies, 2 MMA issue, 3..18 dequantisation, 19..22 epilogue.  Every wait is
+//   * the weight tile is the MMA's M operand and the 256 tokens its N operand, so a product of M128 N256 K16 reads
+//     12 KiB of shared memory where two of M128 N128 read 16;
+//   * the accumulator (lanes: weight rows, columns: tokens) is double-buffered (2 x 256 columns of tensor memory): eight
+//     epilogue warps drain one tile, writing whole 128-byte segments of output rows, while the next is multiplied.
+// Warps: 0 activation copies, 1 code copies, 2 MMA issue, 3..18 dequantisation, 19..26 epilogue.  Every wait is
 // bounded; a warp that gives up records it in the context's status word and leaves its loops.
 #include <cuda.h>
 

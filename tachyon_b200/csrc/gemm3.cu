@@ -12,6 +12,14 @@
 // blocks' `empty` and `acc_full`; both blocks' epilogue warps arrive on the leader's `acc_empty`.  Every wait is
 // bounded; a warp that gives up records it in the context's status word and leaves its loops; the blocks meet at a
 // cluster barrier before either exits, so neither reads the other's shared memory after it is gone.
+//
+// State: results equal the other schedules' on every test shape (tests/test_gemm.py runs both tile widths).  Speed: 660
+// to 790 TFLOP/s on the benchmark's long shapes against 990 to 1,000 for gemm2.cu, so launch_gemm_q8 does not pick it
+// (TACHYON_B200_GEMM=3 or 4 does).  What the measurements showed on the way: an arrival on the other SM's barrier keeps
+// the issuing thread for most of a microsecond (hence several relay lanes, and no such arrival in the dequantising
+// loop); a dequantising turn has about half a microsecond of fixed cost (hence several k tiles per turn); more stages
+// (4 -> 6) changed nothing.  Not yet understood: the remaining 0.8 us per 64 of K with the leader still waiting for
+// full stages.
 #include <cuda.h>
 
 #include <string>
