@@ -4,7 +4,7 @@ sequences, made by the reference's scripts/encoders.py).  The npz holds the enco
 names (float16, as the fixture stores them), its config and the cases' ids and hidden states, so that the oracle's encoder forward
 stays pinned where the reference tree is absent.
 
-Run from the repository root with the reference mounted: python tests/golden/make_encoder_golden.py [reference root]
+Run from the repository root with the reference's tree at hand: python tests/golden/make_encoder_golden.py <reference root>
 """
 import json
 import os
@@ -14,7 +14,9 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit(__doc__)
+REF = sys.argv[1]
 DIR = os.path.join(REF, "crates/tachyon/tests/fixtures/tiny-encoder")
 
 raw = open(os.path.join(DIR, "model.safetensors"), "rb").read()
