@@ -143,7 +143,9 @@ TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* sc
  *                 itself when w2 is NULL).  h is left alone; w1, w2 hold one chunk.
  *   tb_embed_q4 = embed_q4 (ptx/mod.rs:531-598): out[r][i] = (nibble - 8) * scale_f16 * scale for row tokens[r] of the table.
  * tb_launch is Stream::launch by kernel name (cuda/mod.rs:417-425): the names "quant_q8", "geglu_q8", "norm_q8",
- * "embed_q4", "gemv_q4", "sample", and "attend_256" / "attend_256_2" (one block per key-value head: group 1; Q8 out)
+ * "embed_q4", "gemv_q4", "sample", "attend_256" / "attend_256_2" / "attend_512" (group 1, or 2 for attend_256 and
+ * attend_512; Q8 out), and prefill's "kv_256" / "kv_512", "query_256" / "query_512" (attend.rs:472-556) and "flash_256" /
+ * "flash_256_2" / "flash_512" (flash.rs:19-22: f32 out; tiles, block and shared memory are this build's own),
  * with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16, sample.rs:21-27 and attend.rs:21-32;
  * args[i] points at argument i's value (a u64 device address, u32 or f32), as the driver's kernelParams do.  Grid and block
  * are checked against the kernel's documented launch shape where it has a meaning here (chunks, rows and block counts

@@ -296,6 +296,40 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         if (!a.q_norm || !a.k_norm || !a.out || !a.out_pairs) return fail(OUT_OF_RANGE, "tb_launch: attend_512 needs its norm weights and its Q8 output");
         return launch_attend_512(ctx, a);
     }
+    const bool wide = name.size() > 4 && name.compare(name.size() - 4, 4, "_512") == 0;  // heads of 512
+    if (name == "kv_256" || name == "kv_512") {
+        // attend.rs:472-511: qkv, kn, freq, k_cache, v_cache, pos, cap, ratio; grid (Hkv, tokens) blocks of 32.
+        TB_TRY(shape(8, 32));
+        const uint32_t kv = grid[0], tokens = grid[1], ratio = u32(7), d = wide ? 512u : 256u;
+        PrefillRows rows;
+        rows.first = ratio * kv, rows.count = 2 * kv, rows.stride = (ratio + 2) * kv * d, rows.pos = static_cast<const uint32_t*>(ptr(5));
+        if (!ptr(0) || !ptr(1) || !ptr(2) || !ptr(3) || !ptr(4) || !rows.pos || kv == 0 || tokens == 0 || ratio == 0 || u32(6) == 0)
+            return fail(OUT_OF_RANGE, "tb_launch: " + name + ": null or empty argument");
+        return launch_prefill_rows(ctx, static_cast<const float*>(ptr(0)), nullptr, static_cast<const float*>(ptr(1)), static_cast<const float*>(ptr(2)), nullptr,
+                                   static_cast<__half*>(ptr(3)), static_cast<__half*>(ptr(4)), tokens, 0, u32(6), ratio * kv, kv, 1e-6f, 1.0f, d, rows);
+    }
+    if (name == "query_256" || name == "query_512") {
+        // attend.rs:514-556: qkv, qn, freq, out, pos, row (floats per token of qkv); grid (H, tokens) blocks of 32.
+        TB_TRY(shape(6, 32));
+        const uint32_t heads = grid[0], tokens = grid[1], d = wide ? 512u : 256u;
+        PrefillRows rows;
+        rows.first = 0, rows.count = heads, rows.stride = u32(5), rows.pos = static_cast<const uint32_t*>(ptr(4));
+        if (!ptr(0) || !ptr(1) || !ptr(2) || !ptr(3) || !rows.pos || heads == 0 || tokens == 0 || rows.stride < heads * d)
+            return fail(OUT_OF_RANGE, "tb_launch: " + name + ": null, empty or short argument");
+        // kv_heads 0: no row is a key or a value; cap 1 is not used.  The queries are stored as they are (scale 1, no log2 e).
+        return launch_prefill_rows(ctx, static_cast<const float*>(ptr(0)), static_cast<const float*>(ptr(1)), nullptr, static_cast<const float*>(ptr(2)),
+                                   static_cast<__half*>(ptr(3)), nullptr, nullptr, tokens, 0, 1, heads, 0, 1e-6f, 1.0f, d, rows);
+    }
+    if (name == "flash_256" || name == "flash_256_2" || name == "flash_512") {
+        // flash.rs:19-22: q, k_cache, v_cache, pos, cap, window, group, tokens, y (f32); grid (tiles of tokens, H / P).  This build
+        // chooses its own tiles, block and shared memory: grid[0], block and shared_bytes are not used.
+        if (nargs != 9) return fail(OUT_OF_RANGE, "tb_launch: " + name + " takes 9 arguments");
+        const uint32_t per = name == "flash_256_2" ? 2u : 4u, group = u32(6), heads = per * grid[1], tokens = u32(7), d = wide ? 512u : 256u;
+        if (!ptr(0) || !ptr(1) || !ptr(2) || !ptr(3) || !ptr(8) || group == 0 || grid[1] % group != 0 || tokens == 0 || u32(4) == 0 || u32(5) == 0)
+            return fail(OUT_OF_RANGE, "tb_launch: " + name + ": null, empty or ragged argument");
+        return launch_prefill_flash(ctx, static_cast<const __half*>(ptr(0)), static_cast<const __half*>(ptr(1)), static_cast<const __half*>(ptr(2)), ptr(8), tokens, 0,
+                                    u32(4), u32(5), heads, grid[1] / group, d, static_cast<const uint32_t*>(ptr(3)), 1.4426950408889634f, 1);
+    }
     return fail(NO_MODEL, "tb_launch: no kernel named " + name);
 }
 

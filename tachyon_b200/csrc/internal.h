@@ -169,8 +169,20 @@ int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* 
                         __half* x);
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
                        uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim = 256);
-int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim = 256);
+// The same kernel over some of a token's rows (kv_256 / kv_512: the key and value rows; query_256 / query_512: the query
+// rows), `stride` floats from token to token, the first position optionally from device memory; qscale multiplies the queries.
+struct PrefillRows {
+    uint32_t first = 0, count = 0, stride = 0;
+    const uint32_t* pos = nullptr;
+};
+int launch_prefill_rows(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
+                        uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float qscale, uint32_t head_dim,
+                        const PrefillRows& rows);
+// out: f16 (or f32 with out_f32) [tokens][heads * head_dim].  pos_dev: the first position from device memory instead of pos0;
+// sscale: factor of the scores (1 when the queries already carry scale * log2(e)).
+int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim = 256, const uint32_t* pos_dev = nullptr, float sscale = 1.0f,
+                         int out_f32 = 0);
 
 // ---- small kernels ---------------------------------------------------------------------------------------------
 int launch_embed_q8(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* token, uint32_t cols, float scale, float* out, uint32_t wbits = 8);

@@ -29,52 +29,46 @@ __global__ void __launch_bounds__(256) prefill_embed_kernel(const int8_t* w, con
     for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) o[i] = (float)w[row + i] * __half2float(s[(row + i) / 32]) * scale;
 }
 
-// ---- residual + norm, one block per token, 2048 values (8 per thread) -----------------------------------------------
+// ---- residual + norm, one warp per token, 2048 values (64 per lane) ---------------------------------------------------
 // h' = (h + w1 * rmsnorm(y)) * hscale when y is given (h updated in place), x = w2 * rmsnorm(h') as f16, or h' itself
-// without w2 (what the per-layer input's gate reads).
-__global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float* y, const float* w1, const float* w2, uint32_t n, float eps, float hscale,
+// without w2 (what the per-layer input's gate reads).  A warp keeps its token in registers: sixteen 16-byte loads of h
+// and of y in flight per lane and two shuffle reductions, no block barrier.
+constexpr int NORM_N = 2048, NORM_V = NORM_N / 128;  // float4 per lane
+__global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, float eps, float hscale,
                                                            __half* x) {
-    __shared__ float sh[8];
-    const size_t base = (size_t)blockIdx.x * n;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    auto block_sum = [&](float v) {
-        v = warp_sum(v);
-        __syncthreads();
-        if (lane == 0) sh[warp] = v;
-        __syncthreads();
-        float t = 0.0f;
+    const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (token >= tokens) return;
+    const size_t base = (size_t)token * NORM_N;
+    float4 v[NORM_V];
 #pragma unroll
-        for (int i = 0; i < 8; i++) t += sh[i];
-        return t;
-    };
-    float v[8];
-    const float4 a = *reinterpret_cast<const float4*>(h + base + tid * 8), b = *reinterpret_cast<const float4*>(h + base + tid * 8 + 4);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    for (int i = 0; i < NORM_V; i++) v[i] = *reinterpret_cast<const float4*>(h + base + (i * 32 + lane) * 4);
     if (y != nullptr) {
-        float yy[8];
-        const float4 c = *reinterpret_cast<const float4*>(y + base + tid * 8), d = *reinterpret_cast<const float4*>(y + base + tid * 8 + 4);
-        yy[0] = c.x, yy[1] = c.y, yy[2] = c.z, yy[3] = c.w, yy[4] = d.x, yy[5] = d.y, yy[6] = d.z, yy[7] = d.w;
+        float4 yy[NORM_V];
+#pragma unroll
+        for (int i = 0; i < NORM_V; i++) yy[i] = __ldcs(reinterpret_cast<const float4*>(y + base + (i * 32 + lane) * 4));
         float sy = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) sy = fmaf(yy[i], yy[i], sy);
-        const float ry = rsqrtf(block_sum(sy) / (float)n + eps);
+        for (int i = 0; i < NORM_V; i++) sy = fmaf(yy[i].x, yy[i].x, fmaf(yy[i].y, yy[i].y, fmaf(yy[i].z, yy[i].z, fmaf(yy[i].w, yy[i].w, sy))));
+        const float ry = rsqrtf(warp_sum(sy) / (float)NORM_N + eps);
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = fmaf(yy[i] * ry, __ldg(w1 + tid * 8 + i), v[i]) * hscale;
-        *reinterpret_cast<float4*>(h + base + tid * 8) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(h + base + tid * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        for (int i = 0; i < NORM_V; i++) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(w1 + (i * 32 + lane) * 4));
+            v[i].x = fmaf(yy[i].x * ry, w.x, v[i].x) * hscale, v[i].y = fmaf(yy[i].y * ry, w.y, v[i].y) * hscale;
+            v[i].z = fmaf(yy[i].z * ry, w.z, v[i].z) * hscale, v[i].w = fmaf(yy[i].w * ry, w.w, v[i].w) * hscale;
+            *reinterpret_cast<float4*>(h + base + (i * 32 + lane) * 4) = v[i];
+        }
     }
     float sq = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) sq = fmaf(v[i], v[i], sq);
-    const float rh = w2 != nullptr ? rsqrtf(block_sum(sq) / (float)n + eps) : 1.0f;
-    uint32_t o[4];
+    for (int i = 0; i < NORM_V; i++) sq = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, sq))));
+    const float rh = w2 != nullptr ? rsqrtf(warp_sum(sq) / (float)NORM_N + eps) : 1.0f;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float w_a = w2 != nullptr ? __ldg(w2 + tid * 8 + 2 * i) : 1.0f, w_b = w2 != nullptr ? __ldg(w2 + tid * 8 + 2 * i + 1) : 1.0f;
-        const __half2 t = __floats2half2_rn(v[2 * i] * rh * w_a, v[2 * i + 1] * rh * w_b);
-        o[i] = *reinterpret_cast<const uint32_t*>(&t);
+    for (int i = 0; i < NORM_V; i++) {
+        const float4 w = w2 != nullptr ? __ldg(reinterpret_cast<const float4*>(w2 + (i * 32 + lane) * 4)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        const __half2 a = __floats2half2_rn(v[i].x * rh * w.x, v[i].y * rh * w.y), b2 = __floats2half2_rn(v[i].z * rh * w.z, v[i].w * rh * w.w);
+        *reinterpret_cast<uint2*>(x + base + (i * 32 + lane) * 4) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b2));
     }
-    *reinterpret_cast<uint4*>(x + base + tid * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // ---- q / k / v preparation: one warp per (token, head) -----------------------------------------------------------------
@@ -82,16 +76,24 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float
 // slot (pos0 + token) % cap; values: norm without weights -> cache.  The reference's kv_256 / kv_512 and query_256 /
 // query_512 (crates/tachyon/src/ptx/attend.rs:472-556) in one launch.  A lane holds dims (DH/64) l .. and their RoPE
 // partners DH/2 + (DH/64) l ..
+// Which rows of a token's projected vector a launch prepares (the whole of it in the decoder; the key and value rows for
+// kv_256 / kv_512 and the query rows for query_256 / query_512 when they are launched by name), the floats from one
+// token's vector to the next, and, for the launches by name, the chunk's first position in device memory.
+struct QkvRows {
+    uint32_t first, count, stride;
+    const uint32_t* pos;
+};
+
 template <int DH>
 __global__ void __launch_bounds__(128) prefill_qkv_kernel(const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out,
                                                           __half* kc, __half* vc, uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads,
-                                                          float eps, float qscale) {
+                                                          float eps, float qscale, QkvRows rows_of) {
     constexpr int H2 = DH / 64, NV = 2 * H2;  // values a lane holds of each half, and in all
-    const uint32_t rows = heads + 2 * kv_heads;
-    const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows, r = item % rows;
+    const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows_of.count, r = rows_of.first + item % rows_of.count;
     if (token >= tokens) return;  // the last block's spare warps (nothing below synchronises the block)
+    if (rows_of.pos != nullptr) pos0 = __ldg(rows_of.pos);
     const int lane = threadIdx.x & 31;
-    const float* src = qkv + ((size_t)token * rows + r) * DH;
+    const float* src = qkv + (size_t)token * rows_of.stride + (size_t)r * DH;
     float x[NV];
 #pragma unroll
     for (int half = 0; half < 2; half++)
@@ -169,9 +171,19 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// What a launch by the reference's kernel name changes (flash.rs:19-22): the chunk's first position comes from device
+// memory, the queries carry no log2(e) (the scores are multiplied by `sscale` instead), the output is f32.
+struct FlashByName {
+    const uint32_t* pos;
+    float sscale;  // 1 when the queries are already in base 2
+    int out_f32;
+};
+
 template <int DH, int SPLIT>
-__global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens,
-                                                                    uint32_t pos0, uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads) {
+__global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens,
+                                                                    uint32_t pos0, uint32_t cap, uint32_t window, uint32_t heads, uint32_t kv_heads,
+                                                                    FlashByName named) {
+    if (named.pos != nullptr) pos0 = __ldg(named.pos);
     constexpr int LDS = DH + 8;        // padded row length in halves
     constexpr int DW = DH / SPLIT;     // dimensions a warp sums
     extern __shared__ __align__(16) uint8_t raw[];
@@ -253,6 +265,10 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
         }
         // Mask, running maximum and sums (scores are already in base 2: the queries carry scale*log2(e)).
         float mt[2] = {-INFINITY, -INFINITY};
+        if (named.sscale != 1.0f) {
+#pragma unroll
+            for (int nb = 0; nb < FK / 8; nb++) sc[nb][0] *= named.sscale, sc[nb][1] *= named.sscale, sc[nb][2] *= named.sscale, sc[nb][3] *= named.sscale;
+        }
         if (whole_rows && j0 + FK - 1 <= p_first && j0 + window > p_first + FT - 1) {
 #pragma unroll
             for (int nb = 0; nb < FK / 8; nb++) {
@@ -324,13 +340,13 @@ __global__ void __launch_bounds__(128 * SPLIT) prefill_flash_kernel(const __half
 #pragma unroll
     for (int nb = 0; nb < DW / 8; nb++) {
         const uint32_t col = head * DH + part * DW + nb * 8 + 2 * (lane & 3);
-        if (t0 + row_a < tokens) {
-            const __half2 v = __floats2half2_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
-            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_a) * heads * DH + col) = v;
-        }
-        if (t0 + row_b < tokens) {
-            const __half2 v = __floats2half2_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
-            *reinterpret_cast<__half2*>(out + (size_t)(t0 + row_b) * heads * DH + col) = v;
+        const size_t at_a = (size_t)(t0 + row_a) * heads * DH + col, at_b = (size_t)(t0 + row_b) * heads * DH + col;
+        if (named.out_f32) {
+            if (t0 + row_a < tokens) *reinterpret_cast<float2*>(static_cast<float*>(out) + at_a) = make_float2(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+            if (t0 + row_b < tokens) *reinterpret_cast<float2*>(static_cast<float*>(out) + at_b) = make_float2(o[nb][2] * inv[1], o[nb][3] * inv[1]);
+        } else {
+            if (t0 + row_a < tokens) *reinterpret_cast<__half2*>(static_cast<__half*>(out) + at_a) = __floats2half2_rn(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+            if (t0 + row_b < tokens) *reinterpret_cast<__half2*>(static_cast<__half*>(out) + at_b) = __floats2half2_rn(o[nb][2] * inv[1], o[nb][3] * inv[1]);
         }
     }
 }
@@ -347,24 +363,33 @@ int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, cons
 int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
                         __half* x) {
     if (n != 2048) return fail(UNSUPPORTED, "prefill norm: rows of 2048 values");
-    prefill_norm_kernel<<<tokens, 256, 0, ctx->stream>>>(h, y, w1, w2, n, eps, hscale, x);
+    prefill_norm_kernel<<<(tokens + 7) / 8, 256, 0, ctx->stream>>>(h, y, w1, w2, tokens, eps, hscale, x);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
 
 int launch_prefill_qkv(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
                        uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float scale, uint32_t head_dim) {
-    const uint32_t items = tokens * (heads + 2 * kv_heads), blocks = (items + 3) / 4;
+    PrefillRows rows;
+    rows.count = heads + 2 * kv_heads, rows.stride = rows.count * head_dim;
+    return launch_prefill_rows(ctx, qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, scale * 1.4426950408889634f, head_dim, rows);
+}
+
+int launch_prefill_rows(tb_context* ctx, const float* qkv, const float* q_norm, const float* k_norm, const float* freq, __half* q_out, __half* kc, __half* vc,
+                        uint32_t tokens, uint32_t pos0, uint32_t cap, uint32_t heads, uint32_t kv_heads, float eps, float qscale, uint32_t head_dim,
+                        const PrefillRows& rows) {
+    const uint32_t items = tokens * rows.count, blocks = (items + 3) / 4;
     if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill qkv: heads of 256 or 512");
-    const float qscale = scale * 1.4426950408889634f;
-    if (head_dim == 512) prefill_qkv_kernel<512><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale);
-    else prefill_qkv_kernel<256><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale);
+    if (items == 0) return fail(OUT_OF_RANGE, "prefill qkv: nothing to prepare");
+    const QkvRows r{rows.first, rows.count, rows.stride, rows.pos};
+    if (head_dim == 512) prefill_qkv_kernel<512><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
+    else prefill_qkv_kernel<256><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
 
-int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, __half* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
+int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                         uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, const uint32_t* pos_dev, float sscale, int out_f32) {
     if (kv_heads == 0 || heads % kv_heads != 0) return fail(UNSUPPORTED, "prefill attention: heads must be a multiple of kv_heads");
     const uint32_t ratio = heads / kv_heads, group = ratio < 4 ? ratio : 4;  // query heads a block takes
     if (ratio != 1 && ratio != 2 && ratio != 4 && ratio != 8) return fail(UNSUPPORTED, "prefill attention: 1, 2, 4 or 8 query heads per key-value head");
@@ -378,8 +403,9 @@ int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, con
         configured[ctx->gpu & 15] = true;
     }
     const dim3 grid((tokens + FT - 1) / FT, heads / group);
-    if (head_dim == 512) prefill_flash_kernel<512, 2><<<grid, group * 64, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
-    else prefill_flash_kernel<256, 1><<<grid, group * 32, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads);
+    const FlashByName named{pos_dev, sscale, out_f32};
+    if (head_dim == 512) prefill_flash_kernel<512, 2><<<grid, group * 64, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads, named);
+    else prefill_flash_kernel<256, 1><<<grid, group * 32, bytes(group), ctx->stream>>>(q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads, named);
     TB_CUDA(cudaGetLastError());
     return OK;
 }

@@ -163,3 +163,63 @@ def test_attention_by_name_writes_q8(ctx, name, per, cap, win, pos, splits, fres
     with pytest.raises(tb.Error) as e:
         ctx.launch(name, (4 * blocks, splits, 1), (256, 1, 1), 0, args[:10] + [("u", 4)] + args[11:])
     assert e.value.status == 9  # sixteen query heads to one key-value head: no kernel here
+
+
+@pytest.mark.parametrize("d,ratio,cap,win,p0", [(256, 4, 1024, 512, 600), (512, 4, 700, 700, 600), (256, 2, 1024, 512, 600)])
+def test_prefill_attention_by_name(ctx, d, ratio, cap, win, p0):
+    """tests/prefill.rs:199-236 (flash_attention_matches_the_reference): kv_* stores a chunk's keys and values, query_* the
+    queries as f16, flash_* gives every token's heads over its window in f32, within a thousandth of the largest output."""
+    from util import f16, f16_to_f32, values_fast
+
+    KV, TOKENS = 2, 40
+    heads, rows = ratio * KV, (ratio + 2) * KV
+    qkv = values_fast(TOKENS * rows * d, 3).reshape(TOKENS, rows, d)
+    qn, kn = (0.2 + 0.1 * values_fast(d, 4)).astype(np.float32), (0.2 + 0.1 * values_fast(d, 5)).astype(np.float32)
+    freq = oracle.rope_freq(10000.0, d, 1.0) if d == 256 else oracle.rope_freq(1e6, d, 0.25)
+    kc, vc = f16(0.3 * values_fast(KV * cap * d, 6)), f16(0.3 * values_fast(KV * cap * d, 7))
+
+    def prepared(x, w, pos, rotate):
+        x = x.astype(np.float64)
+        x = x / np.sqrt((x * x).mean() + 1e-6) * (1.0 if w is None else w.astype(np.float64))
+        if rotate:
+            ang = (np.float32(pos) * freq).astype(np.float64)
+            a, b = x[: d // 2].copy(), x[d // 2:].copy()
+            x = np.concatenate([a * np.cos(ang) - b * np.sin(ang), b * np.cos(ang) + a * np.sin(ang)])
+        return x
+
+    keys, vals = f16_to_f32(kc).astype(np.float64).reshape(KV, cap, d), f16_to_f32(vc).astype(np.float64).reshape(KV, cap, d)
+    for t in range(TOKENS):  # the chunk's own keys and values, unrounded (prefill.rs:161-171)
+        for g in range(KV):
+            keys[g, (p0 + t) % cap] = prepared(qkv[t, heads + g], kn, p0 + t, True)
+            vals[g, (p0 + t) % cap] = prepared(qkv[t, heads + KV + g], None, p0 + t, False)
+    want = np.zeros((TOKENS, heads, d))
+    for t in range(TOKENS):
+        p = p0 + t
+        js = np.arange(max(0, p - win + 1), p + 1)
+        for h in range(heads):
+            q = prepared(qkv[t, h], qn, p, True)
+            s = keys[h // ratio, js % cap] @ q
+            w = np.exp(s - s.max())
+            want[t, h] = (w / w.sum()) @ vals[h // ratio, js % cap]
+
+    b = [ctx.upload(a) for a in (qkv, qn, kn, freq, kc, vc, np.array([p0], np.uint32))]
+    qh, y = ctx.zeros(48 * heads * d * 2), ctx.zeros(TOKENS * heads * d * 4)
+    sfx = "512" if d == 512 else "256"
+    ctx.launch("kv_" + sfx, (KV, TOKENS, 1), (32, 1, 1), 0, [("p", b[0].ptr), ("p", b[2].ptr), ("p", b[3].ptr), ("p", b[4].ptr), ("p", b[5].ptr), ("p", b[6].ptr),
+                                                          ("u", cap), ("u", ratio)])
+    ctx.launch("query_" + sfx, (heads, TOKENS, 1), (32, 1, 1), 0, [("p", b[0].ptr), ("p", b[1].ptr), ("p", b[3].ptr), ("p", qh.ptr), ("p", b[6].ptr), ("u", rows * d)])
+    name = "flash_512" if d == 512 else ("flash_256_2" if ratio == 2 else "flash_256")
+    per, tile = (2, 32) if ratio == 2 else (4, 8 if d == 512 else 16)
+    ctx.launch(name, (-(-TOKENS // tile), heads // per, 1), (256, 1, 1), 0, [("p", qh.ptr), ("p", b[4].ptr), ("p", b[5].ptr), ("p", b[6].ptr), ("u", cap), ("u", win),
+                                                                            ("u", 1), ("u", TOKENS), ("p", y.ptr)])
+    got = y.download(np.float32, TOKENS * heads * d).reshape(TOKENS, heads, d)
+    top = np.abs(want).max()
+    assert np.abs(got - want).max() <= 1e-3 * top, float(np.abs(got - want).max() / top)
+    # the stored keys: the chunk's slots rewritten, every other slot as it was
+    k_after = f16_to_f32(b[4].download(np.uint16, kc.size)).reshape(KV, cap, d)
+    slots = {(p0 + t) % cap for t in range(TOKENS)}
+    untouched = [s for s in range(cap) if s not in slots]
+    assert np.array_equal(k_after[:, untouched], f16_to_f32(kc).reshape(KV, cap, d)[:, untouched])
+    assert np.abs(k_after[:, sorted(slots)] - keys[:, sorted(slots)]).max() <= 2.0**-10 * np.abs(keys).max()
+    with pytest.raises(tb.Error):
+        ctx.launch("flash_256", (3, 2, 1), (256, 1, 1), 0, [("p", qh.ptr), ("p", b[4].ptr)])  # nine arguments
