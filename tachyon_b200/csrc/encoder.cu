@@ -56,17 +56,87 @@ __global__ void __launch_bounds__(256) enc_norm_kernel(const float* x, const __h
 }
 
 // ---- RoPE in place on the q and k parts of f16 [tokens, 3h]: pairs (j, j + d/2) of every head turn by pos * freq[j] -------
-__global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32_t* pos, const float* freq, uint32_t h, uint32_t d) {
-    const uint32_t t = blockIdx.x, half_d = d / 2, pairs = h / 2;  // pairs per part
+// LayerNorm with one warp per token for widths that are multiples of 128 up to 2048: the token stays in registers
+// (16-byte loads, two shuffle reductions, no block barrier).  Same arithmetic as enc_norm_kernel.
+template <int V>  // float4 per lane: h = 128 V
+__global__ void __launch_bounds__(256) enc_norm_warp_kernel(const float* x, const __half* table, const uint32_t* ids, const float* w, float eps, float* out32,
+                                                            __half* out16, uint32_t tokens) {
+    constexpr uint32_t h = 128 * V;
+    const uint32_t t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    float4 v[V];
+    if (ids != nullptr) {
+        const __half* row = table + (size_t)ids[t] * h;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(row + (i * 32 + lane) * 4);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            v[i] = make_float4(a.x, a.y, b.x, b.y);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; i++) v[i] = *reinterpret_cast<const float4*>(x + (size_t)t * h + (i * 32 + lane) * 4);
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; i++) sum += v[i].x + v[i].y + v[i].z + v[i].w;
+    const float mean = warp_sum(sum) / (float)h;
+    float var = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        v[i].x -= mean, v[i].y -= mean, v[i].z -= mean, v[i].w -= mean;
+        var = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, var))));
+    }
+    const float rs = rsqrtf(warp_sum(var) / (float)h + eps);
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        const float4 ww = __ldg(reinterpret_cast<const float4*>(w + (i * 32 + lane) * 4));
+        const float4 y = make_float4(v[i].x * rs * ww.x, v[i].y * rs * ww.y, v[i].z * rs * ww.z, v[i].w * rs * ww.w);
+        if (out32) *reinterpret_cast<float4*>(out32 + (size_t)t * h + (i * 32 + lane) * 4) = y;
+        if (out16) {
+            const __half2 a = __floats2half2_rn(y.x, y.y), b = __floats2half2_rn(y.z, y.w);
+            *reinterpret_cast<uint2*>(out16 + (size_t)t * h + (i * 32 + lane) * 4) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+        }
+    }
+}
+// Picks the warp-per-token kernel where the width allows it.
+static void launch_enc_norm(cudaStream_t s, uint32_t T, const float* x, const __half* table, const uint32_t* ids, const float* w, uint32_t h, float eps, float* out32,
+                            __half* out16);
+// One warp per token: a lane turns eight pairs at a time (16-byte loads and stores of the low and the high half of a head).
+__global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32_t* pos, const float* freq, uint32_t h, uint32_t d, uint32_t tokens) {
+    const uint32_t t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const uint32_t half_d = d / 2, chunks = half_d / 8, heads = h / d, items = 2 * heads * chunks;  // q and k parts
     const float p = (float)pos[t];
-    for (uint32_t i = threadIdx.x; i < 2 * pairs; i += blockDim.x) {
-        const uint32_t part = i / pairs, r = i % pairs, head = r / half_d, j = r % half_d;
-        __half* base = qkv + (size_t)t * 3 * h + part * h + head * d;
-        float sn, cs;
-        sincosf(p * __ldg(freq + j), &sn, &cs);
-        const float a = __half2float(base[j]), b = __half2float(base[j + half_d]);
-        base[j] = __float2half_rn(a * cs - b * sn);
-        base[j + half_d] = __float2half_rn(b * cs + a * sn);
+    for (uint32_t i = lane; i < items; i += 32) {
+        const uint32_t part = i / (heads * chunks), r = i % (heads * chunks), head = r / chunks, j = (r % chunks) * 8;
+        __half* base = qkv + (size_t)t * 3 * h + part * h + head * d + j;
+        uint4 lo = *reinterpret_cast<const uint4*>(base), hi = *reinterpret_cast<const uint4*>(base + half_d);
+        __half2* l2 = reinterpret_cast<__half2*>(&lo);
+        __half2* h2 = reinterpret_cast<__half2*>(&hi);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float2 a = __half22float2(l2[e]), b = __half22float2(h2[e]);
+            float s0, c0, s1, c1;
+            sincosf(p * __ldg(freq + j + 2 * e), &s0, &c0);
+            sincosf(p * __ldg(freq + j + 2 * e + 1), &s1, &c1);
+            l2[e] = __floats2half2_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+            h2[e] = __floats2half2_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+        }
+        *reinterpret_cast<uint4*>(base) = lo;
+        *reinterpret_cast<uint4*>(base + half_d) = hi;
+    }
+}
+static void launch_enc_norm(cudaStream_t s, uint32_t T, const float* x, const __half* table, const uint32_t* ids, const float* w, uint32_t h, float eps, float* out32,
+                            __half* out16) {
+    const uint32_t blocks = (T + 7) / 8;
+    switch (h % 128 == 0 ? h / 128 : 0) {
+        case 6: enc_norm_warp_kernel<6><<<blocks, 256, 0, s>>>(x, table, ids, w, eps, out32, out16, T); break;   // 768
+        case 8: enc_norm_warp_kernel<8><<<blocks, 256, 0, s>>>(x, table, ids, w, eps, out32, out16, T); break;   // 1024
+        case 3: enc_norm_warp_kernel<3><<<blocks, 256, 0, s>>>(x, table, ids, w, eps, out32, out16, T); break;   // 384
+        case 2: enc_norm_warp_kernel<2><<<blocks, 256, 0, s>>>(x, table, ids, w, eps, out32, out16, T); break;   // 256
+        case 1: enc_norm_warp_kernel<1><<<blocks, 256, 0, s>>>(x, table, ids, w, eps, out32, out16, T); break;   // 128
+        default: enc_norm_kernel<<<T, 256, 0, s>>>(x, table, ids, w, h, eps, out32, out16);
     }
 }
 
@@ -509,21 +579,21 @@ int tb_encoder_embed(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, u
     TB_CUDA(cudaMemcpyAsync(e->starts, starts.data(), (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
     TB_CUDA(cudaMemcpyAsync(e->lens, lens, (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
     // embeddings -> norm: x (f32 residual stream) and, since layer 0 has no attention norm, its f16 GEMM input
-    enc_norm_kernel<<<T, 256, 0, s>>>(nullptr, e->embed, e->ids, e->embed_norm, h, c.eps, e->x, e->a16);
+    launch_enc_norm(s, T, nullptr, e->embed, e->ids, e->embed_norm, h, c.eps, e->x, e->a16);
     for (uint32_t l = 0; l < c.layers; l++) {
         ELayer& L = e->layers[l];
-        if (l > 0) enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
+        if (l > 0) launch_enc_norm(s, T, e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
         TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, e->a16, T, 3 * h, h, e->qkv16, 1));
-        enc_rope_kernel<<<T, 256, 0, s>>>(e->qkv16, e->pos, e->freq[L.global ? 0 : 1], h, d);
+        enc_rope_kernel<<<(T + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->freq[L.global ? 0 : 1], h, d, T);
         const int window = L.global ? -1 : (int)c.window;
         if (d == 64) enc_attend_kernel<64><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
         else enc_attend_kernel<32><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
         TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, e->att16, T, h, h, e->x, 3));
-        enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
+        launch_enc_norm(s, T, e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
         TB_TRY(launch_gemm_q8(ctx, L.up.w, L.up.s, e->a16, T, L.up.rows, h, e->g16, c.gated ? 4 : 5));
         TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, e->g16, T, h, c.inter, e->x, 3));
     }
-    enc_norm_kernel<<<T, 256, 0, s>>>(e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
+    launch_enc_norm(s, T, e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
     enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
     TB_CUDA(cudaGetLastError());
     if (out_host) TB_CUDA(cudaMemcpyAsync(out_host, e->pooled, (size_t)sequences * c.dims * 4, cudaMemcpyDeviceToHost, s));
