@@ -148,11 +148,14 @@ constexpr int QT = 64, KT = 64;
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
 }
-__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
 }
-__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+// 2^x by the hardware's approximation; 2^-inf is 0.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -207,38 +210,53 @@ __global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, cons
             uint32_t a[4];
             ldsm_x4(a, Qs + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-            for (int nb = 0; nb < KT / 8; nb++) {
-                uint32_t b[2];
-                ldsm_x2(b, Ks + (nb * 8 + (lane & 7)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
-                mma16816(sc[nb], a, b);
+            for (int nb = 0; nb < KT / 8; nb += 2) {  // two blocks of eight keys per load
+                uint32_t b[4];
+                ldsm_x4(b, Ks + (nb * 8 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma16816(sc[nb], a, b0);
+                mma16816(sc[nb + 1], a, b1);
             }
         }
         float mt[2] = {-INFINITY, -INFINITY};
+        // A tile every query of the block sees whole (all its keys exist and lie inside every query's window, and the block
+        // has all its 64 queries) needs no mask.
+        const bool whole = nq == QT && j0 + KT <= hi && (window < 0 || (j0 + KT - 1 <= q0 + (uint32_t)window && q0 + QT - 1 <= j0 + (uint32_t)window));
+        if (whole) {
 #pragma unroll
-        for (int nb = 0; nb < KT / 8; nb++) {
+            for (int nb = 0; nb < KT / 8; nb++) {
+                sc[nb][0] *= scale, sc[nb][1] *= scale, sc[nb][2] *= scale, sc[nb][3] *= scale;
+                mt[0] = fmaxf(mt[0], fmaxf(sc[nb][0], sc[nb][1]));
+                mt[1] = fmaxf(mt[1], fmaxf(sc[nb][2], sc[nb][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), i = (e < 2) ? ia : ib;
-                const bool seen = j < hi && i < len && (window < 0 || (j <= i + (uint32_t)window && i <= j + (uint32_t)window));
-                sc[nb][e] = seen ? sc[nb][e] * scale : -INFINITY;
-                mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+            for (int nb = 0; nb < KT / 8; nb++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1), i = (e < 2) ? ia : ib;
+                    const bool seen = j < hi && i < len && (window < 0 || (j <= i + (uint32_t)window && i <= j + (uint32_t)window));
+                    sc[nb][e] = seen ? sc[nb][e] * scale : -INFINITY;
+                    mt[e >> 1] = fmaxf(mt[e >> 1], sc[nb][e]);
+                }
             }
         }
-        float corr[2];
+        float corr[2], base[2];
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 1));
             mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 2));
             const float mn = fmaxf(m_run[r], mt[r]);
-            corr[r] = (mn == -INFINITY) ? 1.0f : exp2f(m_run[r] - mn);
+            base[r] = fmaxf(mn, -1e30f);               // finite, so a row that has seen nothing yet gets 2^-inf = 0 and no NaN
+            corr[r] = ex2_approx(m_run[r] - base[r]);  // 1 when the maximum stays; 0 for a row's first keys (its sums are zeros)
             m_run[r] = mn;
         }
         float lt[2] = {0.0f, 0.0f};
         uint32_t pf[KT / 16][4];
 #pragma unroll
         for (int nb = 0; nb < KT / 8; nb++) {
-            const float e0 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][0] - m_run[0]), e1 = m_run[0] == -INFINITY ? 0.0f : exp2f(sc[nb][1] - m_run[0]);
-            const float e2 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][2] - m_run[1]), e3 = m_run[1] == -INFINITY ? 0.0f : exp2f(sc[nb][3] - m_run[1]);
+            const float e0 = ex2_approx(sc[nb][0] - base[0]), e1 = ex2_approx(sc[nb][1] - base[0]);
+            const float e2 = ex2_approx(sc[nb][2] - base[1]), e3 = ex2_approx(sc[nb][3] - base[1]);
             const __half2 h01 = __floats2half2_rn(e0, e1), h23 = __floats2half2_rn(e2, e3);
             lt[0] += __low2float(h01) + __high2float(h01);
             lt[1] += __low2float(h23) + __high2float(h23);
@@ -251,14 +269,20 @@ __global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, cons
             lt[r] += __shfl_xor_sync(0xffffffffu, lt[r], 2);
             l_run[r] = l_run[r] * corr[r] + lt[r];
         }
+        const bool moved = __any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f);  // else the scaling is by one
 #pragma unroll
-        for (int nb = 0; nb < D / 8; nb++) {
-            o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+        for (int nb = 0; nb < D / 8; nb += 2) {  // two blocks of eight dimensions per load
+            if (moved) {
+                o[nb][0] *= corr[0], o[nb][1] *= corr[0], o[nb][2] *= corr[1], o[nb][3] *= corr[1];
+                o[nb + 1][0] *= corr[0], o[nb + 1][1] *= corr[0], o[nb + 1][2] *= corr[1], o[nb + 1][3] *= corr[1];
+            }
 #pragma unroll
             for (int kk = 0; kk < KT / 16; kk++) {
-                uint32_t b[2];
-                ldsm_x2_trans(b, Vs + (kk * 16 + (lane & 15)) * LD + nb * 8);
-                mma16816(o[nb], pf[kk], b);
+                uint32_t b[4];
+                ldsm_x4_trans(b, Vs + (kk * 16 + (lane & 15)) * LD + (nb + (lane >> 4)) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma16816(o[nb], pf[kk], b0);
+                mma16816(o[nb + 1], pf[kk], b1);
             }
         }
     }
