@@ -12,7 +12,10 @@ value is the sum over replicas divided by the slowest replica's time.
 Prints ONE JSON line.  `value` is tokens/s with everything resident on the device; `e2e` is the same loop driven
 through tb_decoder_step with the token crossing the host boundary in both directions every step; `roofline` times
 the dominant kernel (the gate/up projection, 16384x2 rows of 2048 int8 weights plus scales) alone over all layers'
-matrices; `cpu_baseline` is the CPU oracle on the same model (reported, not a target).
+matrices; `cpu_baseline` is the CPU oracle on the same model (reported, not a target).  The metric names prefill
+tokens/s beside decode tokens/s, so the default line also carries `prefill` (configs[3]: a prompt of 2048 tokens), and
+`gemv`, `attend`, `encoder` (configs[0], [1], [4]) as sub-objects with their own rooflines; `--workload X` runs one
+of them alone with more repetitions.
 """
 from __future__ import annotations
 
@@ -35,6 +38,8 @@ SEED = 20251
 CONTEXT_FILLED = 2048
 CONTEXT = 4096
 HBM_SPEC_GBS = 8000.0  # the denominator the benchmark definition fixes
+MIN_TIMED_MS = 250.0  # the decode loop is repeated until this much has been timed; the median repetition is reported
+GATEUP_TRAFFIC_SHAPE = (32768, 2048)  # the shape that capture was taken on
 GATEUP_TRAFFIC = 72_201_216  # bytes per launch of the gate/up kernel under ncu (dram read + write), profiles/gemv_q8_kernel__gate_up_32768x2048.md
 
 
@@ -105,7 +110,7 @@ class Clocks:
         if exe:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen([exe, "-i", str(gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen([exe, "-i", str(gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
     def stop(self):
@@ -188,22 +193,40 @@ def bench_decode(args, ranks: Ranks):
     def fresh():
         dec.fill_cache(SEED + 1, CONTEXT_FILLED)
 
-    # ---- device-resident: K chained graph replays ----
+    # ---- device-resident: K chained graph replays, repeated until at least a quarter of a second has been timed ----
     fresh()
     weight_bytes, cache_bytes = dec.step_bytes()
     dec.run(1, W, want_tokens=False)
     ctx.sync()
-    ranks.barrier()
-    clocks = Clocks(ranks.local) if ranks.rank == 0 else None
+    room = CONTEXT - CONTEXT_FILLED - W  # positions left before the context is full
     e0, e1 = ctx.event(), ctx.event()
     e0.record()
-    dec.run(1, K, want_tokens=False)  # continues from the warm-up's state; weights (4.7 GB) exceed L2 by 37x
+    dec.run(1, min(K, room), want_tokens=False)
     e1.record()
     e1.sync()
-    ms = e0.elapsed_ms(e1)
+    est_ms = max(e0.elapsed_ms(e1), 1e-3) * K / min(K, room)
+    repeats = max(1, min(64, int(np.ceil(MIN_TIMED_MS / est_ms))))
+    fresh()
+    dec.run(1, W, want_tokens=False)
+    ctx.sync()
+    ranks.barrier()
+    clocks = Clocks(ranks.local) if ranks.rank == 0 else None
+    runs, used = [], W
+    for _ in range(repeats):
+        if used + K > CONTEXT - CONTEXT_FILLED:  # start again from the pre-filled context (not timed)
+            fresh()
+            dec.run(1, W, want_tokens=False)
+            ctx.sync()
+            used = W
+        e0.record()
+        dec.run(1, K, want_tokens=False)  # continues from the state before; weights (4.7 GB) exceed L2 by 37x
+        e1.record()
+        e1.sync()
+        runs.append(e0.elapsed_ms(e1))
+        used += K
+    ms = statistics.median(runs)
     ranks.barrier()
     ms_max = ranks.max(ms)
-    clk = clocks.stop() if clocks else None
     if ctx.status() != 0:
         raise RuntimeError("a kernel reported a bounded wait that ran out")
 
@@ -213,14 +236,25 @@ def bench_decode(args, ranks: Ranks):
     for _ in range(W):
         token = dec.step(token)
     ranks.barrier()
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(K):
-        token = dec.step(token)
-    e1.record()
-    e1.sync()
-    e2e_ms = max(e0.elapsed_ms(e1), (time.perf_counter() - t0) * 1e3)
+    e2e_runs, used = [], W
+    for _ in range(repeats):
+        if used + K > CONTEXT - CONTEXT_FILLED:
+            fresh()
+            token = 1
+            for _ in range(W):
+                token = dec.step(token)
+            used = W
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(K):
+            token = dec.step(token)
+        e1.record()
+        e1.sync()
+        e2e_runs.append(max(e0.elapsed_ms(e1), (time.perf_counter() - t0) * 1e3))
+        used += K
+    e2e_ms = statistics.median(e2e_runs)
     e2e_ms_max = ranks.max(e2e_ms)
+    clk = clocks.stop() if clocks else None
 
     # ---- greedy tokens for the parity note: first steps after the pre-fill ----
     fresh()
@@ -236,17 +270,18 @@ def bench_decode(args, ranks: Ranks):
     peak, how = measured_peak_gbs()
     line = {
         "metric": "decode_tokens_per_second", "value": value, "unit": "tok/s", "n_gpus": n, "steps": K, "warmup": W,
-        "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_max / K, "repeats": repeats, "timed_ms": sum(runs), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": ("int4 (the reference's Q4)" if bits == 4 else "int8") + " weights x f32 activations, f32 accumulate",
         "data": "synthetic", "impl": "ours",
         "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape " + ("Q4 (the reference's converted format; not the configuration the metric is quoted on)" if bits == 4 else "Q8")
-                   + ", batch 1, context pre-filled to 2048, greedy, CUDA graph",
-                   "step": "one persistent kernel per step" if args.fused else "one launch per phase, programmatic dependent launch",
+                   + ", batch 1, context pre-filled to 2048, greedy",
+                   "step": "CUDA graph replay; " + ("one persistent kernel per step" if args.fused else "one launch per phase, programmatic dependent launch"),
                    "layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "parallelism": f"{n} independent replicas",
-                   "l2": f"inputs exceed L2: {weight_bytes / 1e9:.2f} GB of weights streamed per step"},
+                   "l2": f"inputs exceed L2: {weight_bytes / 1e9:.2f} GB of weights streamed per step",
+                   "timing": f"{repeats} repetitions of {K} chained steps, CUDA events on the library's stream; the median repetition is reported"},
         "e2e": {"value": n * K / (e2e_ms_max / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
                 "api": "tb_decoder_step: host token in, graph replay, sampled token read from pinned memory"},
-        "gpu_launches": K * launches_per_step,
+        "gpu_launches": K * launches_per_step * repeats,
         "step_bytes": {"weights": weight_bytes, "kv_cache": cache_bytes},
         "step_hbm": {"achieved_gbs": step_bytes / (ms_max / K / 1e3) / 1e9, "frac_of_8tbs": step_bytes / (ms_max / K / 1e3) / 1e9 / HBM_SPEC_GBS,
                      "frac_of_measured_copy": step_bytes / (ms_max / K / 1e3) / 1e9 / peak, "peak_source": how},
@@ -291,7 +326,8 @@ def kernel_roofline(ctx, cfg, warmup: int, steps: int, matrices: int = 0):
     for b in (w, s):
         b.free()
     return {"kernel": "gemv_q8_kernel<1, X_NORM, EPI_GEGLU> (gate/up projection)", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "frac_of_8tbs": achieved / HBM_SPEC_GBS, "peak_source": how, "traffic": GATEUP_TRAFFIC,
+            "frac": achieved / peak, "frac_of_8tbs": achieved / HBM_SPEC_GBS, "peak_source": how,
+            "traffic": GATEUP_TRAFFIC if (rows, cols) == GATEUP_TRAFFIC_SHAPE else None,
             "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of this kernel and shape under ncu (profiles/gemv_q8_kernel__gate_up_32768x2048.md)",
             "bytes_per_launch": alg, "us_per_launch": us, "launches_timed": n,
             "how": f"back-to-back launches cycling over {layers} distinct matrices ({layers * rows * cols / 1e9:.1f} GB), CUDA events on the launching stream"}
@@ -514,21 +550,27 @@ def bench_prefill(args, ranks: Ranks):
     dec.fill_random(SEED)
     dec.build()
     prompt = np.array([(i * 7919 + 13) % cfg.vocab for i in range(T)], np.uint32)  # the reference's prompt (benches/generate.rs:47)
-    times, first = [], None
+    times, dev_times, first = [], [], None
+    e0, e1 = ctx.event(), ctx.event()
     for it in range(args.warmup + args.steps):
         dec.reset()
         ctx.sync()
         ranks.barrier()
         t0 = time.perf_counter()
+        e0.record()
         dec.prefill(prompt[:-1])
         tok = dec.step(int(prompt[-1]))
+        e1.record()
+        e1.sync()
         dt = time.perf_counter() - t0
         first = tok if first is None else first
         assert tok == first, "prefill is deterministic"
         if it >= args.warmup:
             times.append(dt)
+            dev_times.append(e0.elapsed_ms(e1))
     ms = statistics.median(times) * 1e3
     ms_max = ranks.max(ms)
+    dev_ms_max = ranks.max(statistics.median(dev_times))
     # arithmetic of the prompt (the last layer stops after its cache writes; its query/key/value product still runs)
     per_layer = (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden + cfg.hidden * cfg.heads * cfg.head_dim + 3 * cfg.ffn * cfg.hidden
     flops = 2.0 * (T - 1) * (per_layer * (cfg.layers - 1) + (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden)
@@ -541,9 +583,11 @@ def bench_prefill(args, ranks: Ranks):
             "dtype": ("int4" if args.weights == "q4" else "int8") + " weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
             "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape {args.weights.upper()}, chunks of {args.chunk}, last token through the decode step",
                        "timing": "host wall clock around tb_decoder_prefill + tb_decoder_step (token ids cross from host memory)"},
-            "gpu_launches": None, "first_token": int(first),
+            "gpu_launches": None, "first_token": int(first), "device_ms": dev_ms_max,
+            "e2e": {"value": n * T / (ms_max / 1e3), "unit": "tok/s", "h2d_bytes_per_step": T * 4, "d2h_bytes_per_step": 4,
+                    "api": "tb_decoder_prefill + tb_decoder_step: host token ids in, first generated token out"},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained, "peak_source": how + " (sustained)",
-                         "traffic": None, "gemm_flops": flops}}
+                         "frac_of_burst": tf / burst, "traffic": None, "gemm_flops": flops}}
 
 
 def encoder_batch(cfg_vocab: int, sequences: int = 64, seed: int = 5):
@@ -589,6 +633,16 @@ def bench_encoder(args, ranks: Ranks):
             "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "peak_source": how, "traffic": None, "gemm_flops": flops}}
 
 
+def brief(line):
+    """What a sub-object of the default line keeps of a workload's own line."""
+    keep = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "higher_is_better", "dtype", "device_ms", "e2e", "roofline", "cases", "gpu_launches")
+    out = {k: line[k] for k in keep if k in line}
+    out["workload"] = line["config"]["workload"]
+    if "variants" in line["config"]:
+        out["variants"] = line["config"]["variants"]
+    return out
+
+
 def reference_arm(args, ranks: Ranks):
     """The reference's implementation of the path, on the host cores.  The reference (Rust + generated PTX) cannot be
     built in this environment, so this arm times the CPU oracle's restatement of its decode step on the same model."""
@@ -602,7 +656,8 @@ def reference_arm(args, ranks: Ranks):
     return {"metric": "decode_tokens_per_second", "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights x f32 activations, f32 accumulate",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape Q8, batch 1, context pre-filled to 2048, greedy (CPU)"},
+            "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape Q8, batch 1, context pre-filled to 2048, greedy",
+                       "step": "CPU restatement of the reference's decode step, all host cores"},
             "cpu_baseline": base, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -619,6 +674,7 @@ def main():
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="decode workload: skip the prefill / encoder / single-kernel sub-objects")
     ap.add_argument("--weights", default="q8", choices=["q8", "q4"], help="decode workload: the benchmark's Q8 matrices, or the reference's converted Q4 format")
     ap.add_argument("--fused", action="store_true", help="decode with the single persistent step kernel instead of one launch per phase")
     args = ap.parse_args()
@@ -645,6 +701,17 @@ def main():
             line = bench_encoder(args, ranks)
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
+            if not args.no_extras:
+                # The rest of the metric and the other configurations, each a short run of its own workload: prefill and the
+                # encoder on every replica, the single kernels on rank 0.
+                sub = argparse.Namespace(**vars(args))
+                sub.steps, sub.warmup = 5, 3
+                line["prefill"] = brief(bench_prefill(sub, ranks))
+                line["encoder"] = brief(bench_encoder(sub, ranks))
+                if ranks.rank == 0:
+                    sub.steps, sub.warmup = 256, 16
+                    line["gemv"] = brief(bench_gemv(sub, ranks))
+                    line["attend"] = brief(bench_attend(sub, ranks))
             if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu:
                 line["cpu_baseline"], _ = cpu_decode(cfg, 4, 30.0, gpu_tokens, 4 if args.weights == "q4" else 8)
             elif ranks.rank == 0:

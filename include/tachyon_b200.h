@@ -56,6 +56,11 @@ TB_API void tb_context_free(tb_context* ctx);
 TB_API int tb_context_sms(const tb_context* ctx);
 /* Turns programmatic dependent launch on (default) or off for kernels launched after the call. */
 TB_API int tb_context_set_overlap(tb_context* ctx, int on);
+/* Which schedule tb_gemm_q8 / tb_gemm_q4 use from now on: 0 picks by shape and epilogue (default), 1 one tile per block,
+ * 2 persistent blocks, 3 and 4 pairs of SMs with tiles of 256 and 128 weight rows.  The environment variable
+ * TACHYON_B200_GEMM gives the value a new context starts with.  (The reference races its tile shapes per product,
+ * crates/tachyon/src/encoder/race.rs:56-88; this is the knob such a race turns.) */
+TB_API int tb_context_set_gemm_schedule(tb_context* ctx, int which);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
 TB_API int tb_status(tb_context* ctx, uint32_t* word);
 
@@ -230,7 +235,7 @@ TB_API int tb_attend_decode_512(tb_context* ctx, const tb_attend* args);
  * tb_attend_decode for callers that cannot allocate device memory (no counterpart in the reference, which always carves
  * this scratch out of its decoder's arena): an engine whose memory plan is fixed at start-up, or a loop that must not
  * call cudaMalloc because it synchronises the device.  args->partial and args->count are ignored; the scratch is a
- * fixed array inside the library (about 1.03 MiB held by every GPU that loads the library, until the process exits).
+ * fixed array inside the library (1,057,024 bytes, about 1.01 MiB, held by every GPU that loads the library, until the process exits).
  * Limits: kv_heads <= 4, splits <= 64, heads / kv_heads <= 4; anything larger returns TB_OUT_OF_RANGE and launches
  * nothing.  The call itself makes no cudaMalloc, cudaFree or other allocating call.
  * The first call on a GPU resolves the array's device address (once per device); make that first call before any

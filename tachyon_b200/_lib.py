@@ -51,6 +51,7 @@ SIGNATURES = {
     "tb_context_free": (None, [vp]),
     "tb_context_sms": (i32, [vp]),
     "tb_context_set_overlap": (i32, [vp, i32]),
+    "tb_context_set_gemm_schedule": (i32, [vp, i32]),
     "tb_status": (i32, [vp, C.POINTER(u32)]),
     "tb_alloc": (i32, [vp, sz, pp]),
     "tb_free": (i32, [vp, vp]),

@@ -61,6 +61,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->pdl = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_NO_PREFETCH");
     ctx->prefetch = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_GEMM");
+    ctx->gemm_schedule = env != nullptr ? atoi(env) : 0;
     *out = ctx;
     return OK;
 }
@@ -79,6 +81,13 @@ int tb_context_sms(const tb_context* ctx) { return ctx ? ctx->sms : 0; }
 int tb_context_set_overlap(tb_context* ctx, int on) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     ctx->pdl = on != 0;
+    return OK;
+}
+
+int tb_context_set_gemm_schedule(tb_context* ctx, int which) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (which < 0 || which > 4) return fail(OUT_OF_RANGE, "tb_context_set_gemm_schedule: 0 (automatic) or 1..4");
+    ctx->gemm_schedule = which;
     return OK;
 }
 

@@ -13,6 +13,7 @@
 // between launches.  Blocks never wait on one another: a block that is not the last to finish just exits.
 #include "attend_body.cuh"
 
+#include <mutex>
 #include <string>
 
 namespace tb {
@@ -94,12 +95,17 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
     if ((p.q_norm == nullptr) != (p.k_norm == nullptr)) return fail(OUT_OF_RANGE, "attend: q_norm and k_norm go together");
     if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.qkv)) & 15) return fail(OUT_OF_RANGE, "attend: buffers must be 16-byte aligned");
     const dim3 grid(p.kv_heads, p.splits), block(THREADS);
-    static bool configured[16] = {};
-    if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        configured[ctx->gpu & 15] = true;
+    {
+        // Per device, once; threads that own contexts on different GPUs may get here together.
+        static std::mutex guard;
+        static bool configured[64] = {};
+        std::lock_guard<std::mutex> lock(guard);
+        if (!configured[ctx->gpu & 63]) {
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+            configured[ctx->gpu & 63] = true;
+        }
     }
     if (group == 4) TB_CUDA(launch_kernel(ctx, attend_kernel<4>, grid, block, sizeof(Smem), true, p));
     else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(Smem), true, p));
@@ -114,7 +120,7 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
 // to hand out, or a latency-critical loop that may not call cudaMalloc because that call synchronises the whole device.
 // For them the scratch lives here, in the library's own image: a fixed array every GPU that loads the library holds
 // until the process exits.  Its size covers up to STATIC_KV_HEADS key-value heads with up to STATIC_SPLITS blocks each
-// and four query heads per key-value head (about 1.03 MiB); anything larger is refused.
+// and four query heads per key-value head (1,057,024 bytes, about 1.01 MiB); anything larger is refused.
 constexpr uint32_t STATIC_KV_HEADS = 4;
 constexpr uint32_t STATIC_SPLITS = 64;
 constexpr size_t STATIC_FLOATS = (size_t)STATIC_KV_HEADS * STATIC_SPLITS * (2 * MAXG + MAXG * D);
@@ -134,14 +140,20 @@ int launch_attend_static(tb_context* ctx, AttendParams p) {
         return fail(OUT_OF_RANGE, "attend (static scratch): the built-in scratch holds at most 4 key-value heads x 64 splits; got " +
                                       std::to_string(p.kv_heads) + " x " + std::to_string(p.splits) + " (use tb_attend_decode with caller scratch)");
     if (ctx->gpu < 0 || ctx->gpu >= 64) return fail(OUT_OF_RANGE, "attend (static scratch): GPU ordinal out of range");
-    if (g_attend_scratch_ptr[ctx->gpu] == nullptr) {
-        // Once per device, with that device current.
-        TB_CUDA(cudaSetDevice(ctx->gpu));
-        void* ptr = nullptr;
-        TB_CUDA(cudaGetSymbolAddress(&ptr, g_attend_scratch));
-        g_attend_scratch_ptr[ctx->gpu] = static_cast<float*>(ptr);
+    float* base = nullptr;
+    {
+        // Once per device, with that device current; under a lock, since threads with contexts on different GPUs share
+        // the table.
+        static std::mutex guard;
+        std::lock_guard<std::mutex> lock(guard);
+        if (g_attend_scratch_ptr[ctx->gpu] == nullptr) {
+            TB_CUDA(cudaSetDevice(ctx->gpu));
+            void* ptr = nullptr;
+            TB_CUDA(cudaGetSymbolAddress(&ptr, g_attend_scratch));
+            g_attend_scratch_ptr[ctx->gpu] = static_cast<float*>(ptr);
+        }
+        base = g_attend_scratch_ptr[ctx->gpu];
     }
-    float* base = g_attend_scratch_ptr[ctx->gpu];
     p.partial = base;
     p.count = reinterpret_cast<uint32_t*>(base + STATIC_FLOATS);
     // The array keeps whatever the last call left.  The partials are overwritten before they are read; the counters must

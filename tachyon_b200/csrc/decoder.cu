@@ -354,7 +354,10 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         // Heads of 512, or eight query heads to a key-value head: attend512.cu's kernel, which merges its own splits and writes f32 heads.
         const bool wide = L.dim == 512 || c.heads == 8 * L.kvh;
         a.defer = wide ? 0 : 1;  // the o projection merges the splits in its prologue
-        a.early = wide ? 0 : 1;  // caches and position are final long before the kernel in front of this one
+        // Caches and position are final long before the kernel in front of this one, except in a layer that reads another
+        // layer's cache: that layer wrote the newest row during this very step, and with short products between the two
+        // nothing but the order of the launches says it has finished.  Such a layer fetches nothing ahead of its wait.
+        a.early = (!wide && L.source < 0) ? 1 : 0;
         if (wide) {
             if (d->collect) return fail(UNSUPPORTED, "fused step: no attention for this layer's heads");
             TB_TRY(L.dim == 512 ? launch_attend_512(d->ctx, a) : launch_attend_256_shared(d->ctx, a));
@@ -854,11 +857,19 @@ int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
     const char* env = getenv("TACHYON_B200_PREFILL_BY_STEPS");
     const bool by_steps = d->settings.chunk == 0 || d->cfg.ffn % 64 != 0 || (env != nullptr && env[0] == '1');
     if (by_steps) {
-        // Without chunk buffers: every prompt token through the decode step; its sample is dropped.
-        for (uint32_t i = 0; i < n; i++) {
-            TB_CUDA(cudaMemcpyAsync(d->state + 1, tokens + i, 4, cudaMemcpyHostToDevice, d->ctx->stream));
-            TB_TRY(queue(d, 0));
+        // Without chunk buffers: every prompt token through the decode step; its pick is dropped.  The graphs that end in
+        // the greedy pick are used whatever the sampling settings: the sampler marks what it draws as seen, and a prompt
+        // must not count as generated text for the repetition penalty (the chunked path and the reference's prefill sample
+        // nothing either).
+        const bool sampled = d->sampled;
+        d->sampled = false;
+        int st = OK;
+        for (uint32_t i = 0; i < n && st == OK; i++) {
+            if (cudaMemcpyAsync(d->state + 1, tokens + i, 4, cudaMemcpyHostToDevice, d->ctx->stream) != cudaSuccess) st = fail(CUDA, "tb_decoder_prefill: copy of a token");
+            if (st == OK) st = queue(d, 0);
         }
+        d->sampled = sampled;
+        TB_TRY(st);
         TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
         return OK;
     }

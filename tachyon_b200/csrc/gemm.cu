@@ -368,10 +368,10 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         // Schedules: this file's one tile per block; gemm2.cu's persistent blocks, whose epilogue overlaps the next tile's
         // products and whose MMAs read less shared memory per FLOP; gemm3.cu's pairs of SMs.  Measured on the benchmark's
         // shapes the persistent one wins where the epilogue stores f32 (plain or added to the output: 1.2 to 1.7 times
-        // the rate), and loses where it stores f16 or computes a GELU per output.  TACHYON_B200_GEMM=1..4 forces one.
-        // (Read at every launch, so a test can run both.)  Up to 128 tokens the persistent tile of 256 would be half empty.
-        const char* e = getenv("TACHYON_B200_GEMM");
-        const int which = e ? atoi(e) : 0;
+        // the rate), and loses where it stores f16 or computes a GELU per output.  tb_context_set_gemm_schedule (or
+        // TACHYON_B200_GEMM=1..4 when the context is created) forces one, so a test can run all.  Up to 128 tokens the
+        // persistent tile of 256 would be half empty.
+        const int which = ctx->gemm_schedule;
         // 3 and 4: the pair schedule of gemm3.cu with tiles of 256 and 128 weight rows.
         if ((which == 3 || which == 4) && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
         const bool stores_only = (mode == 0 || mode == 3) && M > 128;

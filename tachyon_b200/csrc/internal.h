@@ -16,6 +16,7 @@ struct tb_context {
     uint32_t* status_host = nullptr;  // pinned mirror used by tb_status
     bool pdl = true;                  // launch kernels with programmatic stream serialization
     bool prefetch = true;             // give kernels L2 hints about the next kernel's weights
+    int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
 };
 
 namespace tb {

@@ -111,9 +111,14 @@ int tb_wpk_open(const char* path, tb_wpk** out) {
     if (!path || !out) return fail(OUT_OF_RANGE, "tb_wpk_open: null argument");
     const int fd = open(path, O_RDONLY | O_CLOEXEC);
     if (fd < 0) return io_fail("tb_wpk_open:", path);
-    struct stat st;
+    struct stat st = {};
     uint8_t head[HEADER];
-    if (fstat(fd, &st) != 0 || !read_at(fd, head, HEADER, 0)) {
+    if (fstat(fd, &st) != 0) {
+        const int rc = io_fail("tb_wpk_open:", path);
+        close(fd);
+        return rc;
+    }
+    if (!read_at(fd, head, HEADER, 0)) {
         const int rc = st.st_size < (off_t)HEADER ? fail(FORMAT, std::string(path) + ": the file ends early") : io_fail("tb_wpk_open:", path);
         close(fd);
         return rc;

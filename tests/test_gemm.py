@@ -17,10 +17,11 @@ SCHEDULES = {"one tile per block": "1", "persistent": "2", "pairs of SMs, tiles 
 
 
 @pytest.fixture(params=list(SCHEDULES))
-def schedule(request, monkeypatch):
-    """Every schedule of the GEMM (the library reads the variable at every launch); left to itself it picks by shape."""
-    monkeypatch.setenv("TACHYON_B200_GEMM", SCHEDULES[request.param])
-    return request.param
+def schedule(request, ctx):
+    """Every schedule of the GEMM (tb_context_set_gemm_schedule); left to itself the library picks by shape."""
+    tb.check(ctx.lib.tb_context_set_gemm_schedule(ctx.handle, int(SCHEDULES[request.param])))
+    yield request.param
+    tb.check(ctx.lib.tb_context_set_gemm_schedule(ctx.handle, 0))
 
 
 def reference(w, s, a):
