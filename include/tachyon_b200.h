@@ -61,6 +61,14 @@ TB_API int tb_context_set_overlap(tb_context* ctx, int on);
  * TACHYON_B200_GEMM gives the value a new context starts with.  (The reference races its tile shapes per product,
  * crates/tachyon/src/encoder/race.rs:56-88; this is the knob such a race turns.) */
 TB_API int tb_context_set_gemm_schedule(tb_context* ctx, int which);
+/* The small-footprint matrix-vector kernel (no shared-memory ring, dependents released at once; for the short products of a
+ * decode step, so that the large product behind them is resident early): 0 never, 1 where the decoder marks a product as
+ * short (default), 2 wherever the shape allows (2048 columns, f32 out, at most 32 rows a block), which lets tb_gemv_q8 and
+ * tb_gemv_q8_norm reach it.  TACHYON_B200_NO_LEAN=1 starts a context at 0. */
+TB_API int tb_context_set_lean(tb_context* ctx, int mode);
+/* Whether large matrix-vector products hand their stages of rows to the blocks through a counter (default) or split the
+ * rows evenly beforehand (0).  Results are the same bits either way.  TACHYON_B200_STATIC=1 starts a context at 0. */
+TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
 TB_API int tb_status(tb_context* ctx, uint32_t* word);
 
@@ -223,6 +231,15 @@ typedef struct tb_attend {
 } tb_attend;
 TB_API size_t tb_attend_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t splits);
 TB_API int tb_attend_decode(tb_context* ctx, const tb_attend* args);
+/*
+ * Attention and the output projection as a decode step chains them (model/decode.rs:603-618: attend_*, then gemv(o)):
+ * the attention kernel only leaves its splits' results in args->partial, merged `cluster` neighbouring splits at a time
+ * inside a thread-block cluster (1: not at all; 2, 4 or 8, dividing splits), and the projection's prologue finishes the merge
+ * (the reference merges in its attention kernel's last block, ptx/attend.rs:334-405).  y: device f32 [rows] = W . out with
+ * W int8 [rows, heads * 256] and scales f16 [rows, heads * 8]; heads * 256 must be 2048.  args->out, out_dtype and count
+ * are not used.
+ */
+TB_API int tb_attend_project(tb_context* ctx, const tb_attend* args, uint32_t cluster, const int8_t* w, const uint16_t* scales, uint32_t rows, float* y);
 /*
  * The same for heads of 512: attend_512 (crates/tachyon/src/ptx/attend.rs:1-32, 37-38), Gemma 4's global layers.  The
  * struct's 256s read 512 (freq: f32 [256]); heads / kv_heads in {1, 2, 4, 8}.  A block takes up to four query heads, so

@@ -191,6 +191,16 @@ class Context:
     def attend_decode(self, args: Attend) -> None:
         check(self.lib.tb_attend_decode(self.handle, C.byref(args)))
 
+    def attend_project(self, args: Attend, cluster: int, w: DevBuf, s: DevBuf, rows: int, y: DevBuf) -> None:
+        """tb_attend_project: attention leaving its splits (merged `cluster` at a time), then the output projection."""
+        check(self.lib.tb_attend_project(self.handle, C.byref(args), cluster, w.ptr, s.ptr, rows, y.ptr))
+
+    def set_lean(self, mode: int) -> None:
+        check(self.lib.tb_context_set_lean(self.handle, mode))
+
+    def set_dynamic(self, on: bool) -> None:
+        check(self.lib.tb_context_set_dynamic(self.handle, int(on)))
+
     def attend_decode_512(self, args: Attend) -> None:
         """tb_attend_decode_512: heads of 512 (the reference's attend_512)."""
         check(self.lib.tb_attend_decode_512(self.handle, C.byref(args)))

@@ -52,6 +52,8 @@ SIGNATURES = {
     "tb_context_sms": (i32, [vp]),
     "tb_context_set_overlap": (i32, [vp, i32]),
     "tb_context_set_gemm_schedule": (i32, [vp, i32]),
+    "tb_context_set_lean": (i32, [vp, i32]),
+    "tb_context_set_dynamic": (i32, [vp, i32]),
     "tb_status": (i32, [vp, C.POINTER(u32)]),
     "tb_alloc": (i32, [vp, sz, pp]),
     "tb_free": (i32, [vp, vp]),
@@ -85,6 +87,7 @@ SIGNATURES = {
     "tb_prefill_qkv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, u32]),
     "tb_attend_scratch_bytes": (sz, [u32, u32, u32]),
     "tb_attend_decode": (i32, [vp, C.POINTER(Attend)]),
+    "tb_attend_project": (i32, [vp, C.POINTER(Attend), u32, vp, vp, u32, vp]),
     "tb_attend_decode_static": (i32, [vp, C.POINTER(Attend)]),
     "tb_attend_decode_512": (i32, [vp, C.POINTER(Attend)]),
     "tb_attend_512_scratch_bytes": (C.c_size_t, [u32, u32]),

@@ -53,6 +53,8 @@ int tb_context_new(int gpu, tb_context** out) {
     if (e == cudaSuccess) e = cudaMalloc(&ctx->status, 256);
     if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, 256);
     if (e == cudaSuccess) e = cudaHostAlloc(&ctx->status_host, 256, cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->sched, 64 * 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->sched, 0, 64 * 2 * sizeof(uint32_t));
     if (e != cudaSuccess) {
         tb_context_free(ctx);
         return cuda_fail(e, "tb_context_new");
@@ -61,6 +63,10 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->pdl = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_NO_PREFETCH");
     ctx->prefetch = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_STATIC");
+    ctx->dynamic = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_NO_LEAN");
+    ctx->lean = (env != nullptr && env[0] == '1') ? 0 : 1;
     env = getenv("TACHYON_B200_GEMM");
     ctx->gemm_schedule = env != nullptr ? atoi(env) : 0;
     *out = ctx;
@@ -72,6 +78,7 @@ void tb_context_free(tb_context* ctx) {
     cudaSetDevice(ctx->gpu);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream), cudaStreamDestroy(ctx->stream);
     if (ctx->status) cudaFree(ctx->status);
+    if (ctx->sched) cudaFree(ctx->sched);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
 }
@@ -88,6 +95,19 @@ int tb_context_set_gemm_schedule(tb_context* ctx, int which) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     if (which < 0 || which > 4) return fail(OUT_OF_RANGE, "tb_context_set_gemm_schedule: 0 (automatic) or 1..4");
     ctx->gemm_schedule = which;
+    return OK;
+}
+
+int tb_context_set_lean(tb_context* ctx, int mode) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (mode < 0 || mode > 2) return fail(OUT_OF_RANGE, "tb_context_set_lean: 0, 1 or 2");
+    ctx->lean = mode;
+    return OK;
+}
+
+int tb_context_set_dynamic(tb_context* ctx, int on) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    ctx->dynamic = on != 0;
     return OK;
 }
 
@@ -437,6 +457,24 @@ int tb_attend_decode(tb_context* ctx, const tb_attend* a) {
     p.out = a->out, p.out_f16 = a->out_dtype == TB_F16;
     if (a->kv_heads != 0 && a->heads == 8 * a->kv_heads) return launch_attend_256_shared(ctx, p);  // two blocks of four heads per key-value head
     return launch_attend(ctx, p);
+}
+
+int tb_attend_project(tb_context* ctx, const tb_attend* a, uint32_t cluster, const int8_t* w, const uint16_t* scales, uint32_t rows, float* y) {
+    if (!ctx || !a || !w || !scales || !y) return fail(OUT_OF_RANGE, "tb_attend_project: null argument");
+    if (a->kv_heads == 0 || a->heads * 256 != 2048) return fail(UNSUPPORTED, "tb_attend_project: heads * 256 must be 2048");
+    AttendParams p;
+    p.qkv = a->qkv, p.q_norm = a->q_norm, p.k_norm = a->k_norm, p.freq = a->freq;
+    p.kc = reinterpret_cast<__half*>(a->k_cache), p.vc = reinterpret_cast<__half*>(a->v_cache);
+    p.pos = a->pos, p.cap = a->cap, p.window = a->window, p.fresh = a->fresh, p.heads = a->heads, p.kv_heads = a->kv_heads;
+    p.scale = a->scale, p.eps = a->eps, p.partial = a->partial, p.splits = a->splits;
+    p.defer = 1, p.cluster = cluster;
+    TB_TRY(launch_attend(ctx, p));
+    GemvParams g;
+    g.w = w, g.s = reinterpret_cast<const __half*>(scales), g.rows = rows, g.cols = 2048;
+    g.xmode = X_ATTN, g.att_partial = a->partial, g.att_pos = a->pos, g.att_splits = a->splits, g.att_window = a->window;
+    g.att_heads = a->heads, g.att_kv = a->kv_heads, g.att_cluster = cluster;
+    g.epi = EPI_F32, g.y = y, g.lean = 1;
+    return launch_gemv(ctx, g);
 }
 
 size_t tb_attend_512_scratch_bytes(uint32_t heads, uint32_t splits) { return (size_t)heads * splits * (2 + 512) * sizeof(float); }

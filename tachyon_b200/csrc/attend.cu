@@ -25,7 +25,8 @@ namespace {
 template <int G>
 __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p) {
     extern __shared__ __align__(128) uint8_t raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(raw);
+    ClusterSmem& cs = *reinterpret_cast<ClusterSmem*>(raw);
+    Smem& sm = cs.body;
     const int tid = threadIdx.x;
     // The hint is about weights no kernel writes: ask for them before waiting for the previous kernel.
     if (tid == 0) prefetch_hint(p.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y);
@@ -49,14 +50,17 @@ __global__ void __launch_bounds__(THREADS) attend_kernel(const AttendParams p) {
         if (b == 0 || b == gridDim.x * gridDim.y - 1) stamp = p.stamps + (b == 0 ? 0 : 4);
     }
     if (stamp) stamp[0] = global_ns();
-    pdl_wait();
+    // Nothing this kernel does before its wait depends on the kernels in front of it, and nothing it writes is read
+    // before a kernel's own wait: the kernel behind it may start at once.
     pdl_launch_dependents();
+    pdl_wait();
     if (stamp) stamp[1] = global_ns();
     if (!p.early) {
         pos = ld_cg_u(p.pos);
         trig = rope_trig(p.freq, pos, tid & 31, p.trig);
     }
-    attend_body<G, false>(p, sm, tid, blockIdx.x, blockIdx.y, pos, sent, trig);
+    if (p.cluster > 1) attend_cluster_body<G>(p, cs, tid, blockIdx.x, blockIdx.y, pos, sent, trig);
+    else attend_body<G, false>(p, sm, tid, blockIdx.x, blockIdx.y, pos, sent, trig);
     if (stamp) stamp[3] = global_ns();
 }
 
@@ -93,6 +97,8 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
     if (p.splits == 0 || p.splits > 1024) return fail(OUT_OF_RANGE, "attend: splits out of range");
     if (!p.qkv || !p.kc || !p.vc || !p.pos || (!p.defer && (!p.out || !p.count)) || ((p.splits > 1 || p.defer) && !p.partial)) return fail(OUT_OF_RANGE, "attend: null argument");
     if ((p.q_norm == nullptr) != (p.k_norm == nullptr)) return fail(OUT_OF_RANGE, "attend: q_norm and k_norm go together");
+    if (p.cluster != 1 && ((p.cluster != 2 && p.cluster != 4 && p.cluster != 8) || p.splits % p.cluster != 0 || !p.defer))
+        return fail(OUT_OF_RANGE, "attend: clusters of 2, 4 or 8 splits, dividing the splits, and only with the merge left to the next kernel");
     if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.qkv)) & 15) return fail(OUT_OF_RANGE, "attend: buffers must be 16-byte aligned");
     const dim3 grid(p.kv_heads, p.splits), block(THREADS);
     {
@@ -101,15 +107,16 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
         static bool configured[64] = {};
         std::lock_guard<std::mutex> lock(guard);
         if (!configured[ctx->gpu & 63]) {
-            TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-            TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-            TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
             configured[ctx->gpu & 63] = true;
         }
     }
-    if (group == 4) TB_CUDA(launch_kernel(ctx, attend_kernel<4>, grid, block, sizeof(Smem), true, p));
-    else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(Smem), true, p));
-    else TB_CUDA(launch_kernel(ctx, attend_kernel<1>, grid, block, sizeof(Smem), true, p));
+    const dim3 cluster(1, p.cluster, 1);
+    if (group == 4) TB_CUDA(launch_kernel(ctx, attend_kernel<4>, grid, block, sizeof(ClusterSmem), true, cluster, p));
+    else if (group == 2) TB_CUDA(launch_kernel(ctx, attend_kernel<2>, grid, block, sizeof(ClusterSmem), true, cluster, p));
+    else TB_CUDA(launch_kernel(ctx, attend_kernel<1>, grid, block, sizeof(ClusterSmem), true, cluster, p));
     return OK;
 }
 

@@ -30,6 +30,16 @@ struct Smem {
     uint32_t last;
 };
 
+// The stand-alone kernel's shared memory: the above, and what the other blocks of a thread-block cluster write here
+// (AttendParams::cluster > 1): every split's maxima and sums, and of every split's outputs the slice of dimensions this
+// block merges.  Nothing else may live in these arrays: a neighbour that finishes first writes while this block is still
+// at work.
+struct ClusterSmem {
+    Smem body;
+    float xstats[8][2 * MAXG];
+    float xacc[MAXG * D];  // [split][head][dimension within the slice of D / cluster]
+};
+
 // cos and sin of the position's angle for the four dimension pairs a lane rotates: (4l + i, 128 + 4l + i).  They depend
 // on the position alone, so a kernel can have them ready before its input arrives.
 struct Trig {
@@ -185,14 +195,16 @@ __device__ __forceinline__ bool load_first_tile(const AttendParams& p, Smem& sm,
 //   scores[row][col] = K[row][:] . q[col][:]      M = 64 rows (four 16-row tiles), N = 8, K = 256: warp w takes
 //                                                 row tile w % 4 and dimensions 128 (w / 4) .. + 127
 //   out[m][dim]      = P[m][:] . V[:][dim]        M = 16 (2G rows used), N = 256 (warp w: 32 w .. + 31), K = 64 rows
+// This part leaves the split's statistics in sm.mrun / sm.lrun and its unnormalised outputs in out[h] (dimension tid of
+// head h); false when the split has no positions.
 template <int G, bool FUSED>
-__device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, const int tid, const uint32_t g, const uint32_t sp, const uint32_t pos,
-                                            const bool preloaded, const Trig& trig) {
+__device__ __forceinline__ bool attend_partial(const AttendParams& p, Smem& sm, const int tid, const uint32_t g, const uint32_t sp, const uint32_t pos,
+                                               const bool preloaded, const Trig& trig, float (&out)[G]) {
     const int warp = tid >> 5, lane = tid & 31;
     const uint32_t n = min(pos + 1, p.window), cur = pos % p.cap;
     const uint32_t span = split_span(n, p.splits);
     const uint32_t used = (n + span - 1) / span;
-    if (sp >= used) return;
+    if (sp >= used) return false;
     const uint32_t a_begin = sp * span, a_end = min(n, a_begin + span);  // ages: 0 is the new token
     const bool fresh_here = p.fresh != 0 && sp == 0;
     const bool norms = p.q_norm != nullptr;
@@ -362,10 +374,20 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
         if (orow < G) *reinterpret_cast<float2*>(&sm.q[orow][warp * 32 + t * 8 + 2 * (lane & 3)]) = make_float2(v0, v1);
     }
     block_sync<FUSED>();
-    float out[G];
 #pragma unroll
     for (int h = 0; h < G; h++) out[h] = sm.q[h][tid];
+    return true;
+}
 
+template <int G, bool FUSED>
+__device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, const int tid, const uint32_t g, const uint32_t sp, const uint32_t pos,
+                                            const bool preloaded, const Trig& trig) {
+    float out[G];
+    if (!attend_partial<G, FUSED>(p, sm, tid, g, sp, pos, preloaded, trig, out)) return;
+    const int warp = tid >> 5, lane = tid & 31;
+    const uint32_t n = min(pos + 1, p.window);
+    const uint32_t span = split_span(n, p.splits);
+    const uint32_t used = (n + span - 1) / span;
     const uint32_t stride = 2 * G + G * D;  // floats per partial: maxima, sums, outputs
     if (p.defer) {
         // The consumer of the output merges the splits itself: leave this split's statistics and sums, nothing else.
@@ -442,6 +464,71 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
         else static_cast<float*>(p.out)[at] = r;
     }
     if (tid == 0) p.count[g] = 0;
+}
+
+// ---- splits merged inside a thread-block cluster ---------------------------------------------------------------------
+//
+// With AttendParams::cluster = C > 1 the grid is launched in clusters of C blocks along the splits.  The C splits of a
+// cluster meet in distributed shared memory instead of global memory: every block sends its maxima and sums to all, and of
+// its outputs to each block the slice of D / C dimensions that block merges; after one cluster barrier each block
+// combines its slice over the splits (weights 2^(m_s - M), attend.rs:371-405) and writes it to entry (first split / C) of
+// `partial`, still unnormalised, with the merged maximum and sum.  The product that follows reads one entry per cluster
+// instead of one per split.  A block whose split is empty still takes part: it owns a slice.
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores v at the address `local` has in block `rank` of the cluster.
+__device__ __forceinline__ void st_cluster(const float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <int G>
+__device__ __forceinline__ void attend_cluster_body(const AttendParams& p, ClusterSmem& cs, const int tid, const uint32_t g, const uint32_t sp, const uint32_t pos,
+                                                    const bool preloaded, const Trig& trig) {
+    const uint32_t C = p.cluster, rank = cluster_rank(), slice = D / C;
+    const uint32_t n = min(pos + 1, p.window);
+    const uint32_t span = split_span(n, p.splits);
+    const uint32_t used = (n + span - 1) / span;
+    const uint32_t first = sp - rank;  // the cluster's first split
+    if (first >= used) return;         // a cluster without positions: all of its blocks leave, nobody writes to anybody
+    const uint32_t here = min(C, used - first);  // splits of this cluster that have positions
+    float out[G];
+#pragma unroll
+    for (int h = 0; h < G; h++) out[h] = 0.0f;
+    Smem& sm = cs.body;
+    const bool active = attend_partial<G, false>(p, sm, tid, g, sp, pos, preloaded, trig, out);
+    if (active) {
+        if (tid < 2 * G) {
+            const float v = tid < G ? sm.mrun[tid] : sm.lrun[tid - G];
+            for (uint32_t peer = 0; peer < C; peer++) st_cluster(&cs.xstats[rank][tid], peer, v);
+        }
+        const uint32_t owner = (uint32_t)tid / slice, dd = (uint32_t)tid % slice;
+#pragma unroll
+        for (int h = 0; h < G; h++) st_cluster(&cs.xacc[(rank * G + h) * slice + dd], owner, out[h]);
+    }
+    cluster_sync();
+    if ((uint32_t)tid < G * slice) {
+        const uint32_t h = (uint32_t)tid / slice, dd = (uint32_t)tid % slice;
+        float M = -INFINITY;
+        for (uint32_t s = 0; s < here; s++) M = fmaxf(M, cs.xstats[s][h]);
+        float L = 0.0f, o = 0.0f;
+        for (uint32_t s = 0; s < here; s++) {
+            const float wgt = exp2f(cs.xstats[s][h] - M);
+            L = fmaf(wgt, cs.xstats[s][G + h], L);
+            o = fmaf(wgt, cs.xacc[(s * G + h) * slice + dd], o);
+        }
+        float* entry = p.partial + (size_t)(g * p.splits + first / C) * (2 * G + G * D);
+        entry[2 * G + h * D + rank * slice + dd] = o;
+        if (rank == 0 && dd == 0) entry[h] = M, entry[G + h] = L;
+    }
 }
 
 }  // namespace attend

@@ -130,6 +130,17 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// The same barrier, also telling every participant whether any of them passed a true `pred`.
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+    uint32_t any;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbarrier.red.or.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(any)
+        : "r"((uint32_t)pred), "r"(id), "r"(threads)
+        : "memory");
+    return any != 0;
+}
+
 // dp4a with signed weights: against signed / unsigned activation bytes.
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
     int d;

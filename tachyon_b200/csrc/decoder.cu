@@ -55,6 +55,7 @@ struct Layer {
     int source = -1;  // >= 0: this layer projects no keys or values and attends over that layer's cache
     __half *kc = nullptr, *vc = nullptr;
     uint32_t cap = 0, window = 0, splits = 1;
+    uint32_t cluster = 1;  // splits the attention kernel merges in a thread-block cluster before the output projection sees them
     uint32_t dim = 256, kvh = 0;  // head size and key-value heads of this layer's kind (Config::head_dim, Config::kv_heads)
     uint32_t nq = 0, nkv = 0;      // heads * dim, kvh * dim
 };
@@ -84,6 +85,7 @@ struct tb_decoder {
     float* freq[2] = {nullptr, nullptr};
     float* trig[2] = {nullptr, nullptr};  // cos/sin of every position for the two frequency sets: [context][256]
     uint32_t *count = nullptr, *state = nullptr, *trace = nullptr;
+    uint32_t* sched = nullptr;  // a pair of words per launch of a step: the stage counters of the large products (GemvParams::next)
     unsigned long long* best = nullptr;
     uint32_t* words = nullptr;  // pinned host: [0], [1] the tokens the two graphs write; [2] staging for the token fed in
     cudaGraphExec_t graphs[2] = {nullptr, nullptr};
@@ -240,6 +242,15 @@ void layout(tb_decoder* d, char* base) {
         const uint32_t most = (uint32_t)(2 * d->ctx->sms) / L.kvh;
         if (L.splits > most) L.splits = most;
         if (L.splits == 0) L.splits = 1;
+        // Neighbouring splits meet in a thread-block cluster (attend.cu's kernel, one launch per phase): eight where there
+        // are that many, else the largest power of two that divides them.
+        static const bool no_cluster = getenv("TACHYON_B200_NO_CLUSTER") != nullptr && getenv("TACHYON_B200_NO_CLUSTER")[0] == '1';
+        L.cluster = 1;
+        if (!no_cluster && !d->fused && L.dim == 256 && c.heads != 8 * L.kvh) {
+            if (L.splits >= 8) L.splits = std::min((L.splits + 7) / 8 * 8, std::max(most / 8 * 8, 8u)), L.cluster = 8;
+            else if (L.splits % 4 == 0) L.cluster = 4;
+            else if (L.splits % 2 == 0) L.cluster = 2;
+        }
         if (L.splits > max_splits) max_splits = L.splits;
     }
     vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
@@ -260,6 +271,7 @@ void layout(tb_decoder* d, char* base) {
     d->best = reinterpret_cast<unsigned long long*>(base + t.take(16));
     d->trace = reinterpret_cast<uint32_t*>(base + t.take((size_t)TRACE * 4));
     d->grid_counter = reinterpret_cast<uint32_t*>(base + t.take(4));
+    d->sched = reinterpret_cast<uint32_t*>(base + t.take((size_t)(8 + 7 * c.layers) * 8));
     if (d->settings.chunk > 0) {
         const size_t T = d->settings.chunk;
         auto half = [&](__half*& v, size_t n) { v = reinterpret_cast<__half*>(base + t.take(n * 2)); };
@@ -291,6 +303,7 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
 
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols, p.wbits = m.bits;
+    p.next = d->sched + 2 * (size_t)d->launches;  // a launch's own pair: neighbouring launches overlap
     if (d->stamps) p.stamps = d->stamps + 8 * (size_t)d->launches;
     d->launches++;
     if (d->collect) {
@@ -342,6 +355,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             cur = 1 - cur;
         }
         q.epi = EPI_F32, q.y = d->qkv;
+        q.lean = 1;  // short: the small kernel, so that the chain behind it is resident early
         q.pf = hint(d, L.o, 1, 0, PF);  // what follows attention
         TB_TRY(gemv(d, L.qkv, q));
 
@@ -358,6 +372,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         // layer's cache: that layer wrote the newest row during this very step, and with short products between the two
         // nothing but the order of the launches says it has finished.  Such a layer fetches nothing ahead of its wait.
         a.early = (!wide && L.source < 0) ? 1 : 0;
+        a.cluster = wide ? 1 : L.cluster;
         if (wide) {
             if (d->collect) return fail(UNSUPPORTED, "fused step: no attention for this layer's heads");
             TB_TRY(L.dim == 512 ? launch_attend_512(d->ctx, a) : launch_attend_256_shared(d->ctx, a));
@@ -375,8 +390,9 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
         if (!wide) {
             o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
-            o.att_heads = c.heads, o.att_kv = L.kvh;
+            o.att_heads = c.heads, o.att_kv = L.kvh, o.att_cluster = L.cluster;
         }
+        o.lean = 1;
         o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 

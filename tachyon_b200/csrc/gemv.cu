@@ -58,6 +58,8 @@ struct Layout {
     static constexpr int BESTV = RED + 2 * CONSUMERS * 4;      // float [2 * CONSUMERS]
     static constexpr int BESTI = BESTV + 2 * CONSUMERS * 4;    // uint32 [2 * CONSUMERS]
     static constexpr int SUMS = BESTI + 2 * CONSUMERS * 4;     // float [CONSUMERS][4]
+    static constexpr int STAGE_ROW = SUMS + 4 * CONSUMERS * 4;  // uint32 [8]: first row of the stage's rows
+    static constexpr int STAGE_CNT = STAGE_ROW + 8 * 4;         // uint32 [8]: how many rows the stage holds; 0 ends the block's work
 };
 
 // Four consecutive activations -> one word of each plane.  The eight lanes that share a group of 32 agree on its
@@ -107,7 +109,8 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
         uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
         if (span > 64u) span = (span + 63u) / 64u * 64u;
-        const uint32_t used = (n + span - 1) / span;
+        // The attention kernel merges att_cluster neighbouring splits itself and leaves one entry for each such group.
+        const uint32_t used = ((n + span - 1) / span + p.att_cluster - 1) / p.att_cluster;
         const float* base = p.att_partial + (size_t)g * p.att_splits * stride;
         // A warp's threads share a head.  Lane k fetches split k's maximum and sum, so the statistics of up to 32 splits
         // cost one trip to the L2; the outputs are fetched eight splits at a time, asked for before the statistics so
@@ -200,8 +203,13 @@ __device__ __forceinline__ void fetch_planes(const uint8_t* raw, int b, int firs
     pl.mul = reinterpret_cast<const float*>(raw + L::MUL)[b];
 }
 
-template <int WPR, int XMODE, int EPI, int WB = 8>
-__global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p, uint32_t* status) {
+// The kernel's body.  Rows reach a block in one of two ways.  Static: a contiguous range, balanced to one row (small
+// matrices, where every SM should get some rows).  Dynamic (p.next != nullptr): stages of ROWS rows are handed out by a
+// counter in global memory, the first NST of each block by its index so that its ring fills without waiting for an
+// atomic; blocks that start late or sit far from the memory they read take fewer stages, and nobody waits for a slowest
+// block.  The counter and a second word counting finished blocks are zero between launches (the last block clears them).
+template <int WPR, int XMODE, int EPI, int WB>
+__device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status) {
     extern __shared__ __align__(128) uint8_t raw[];
     using L = Layout<WPR, WB>;
     constexpr int NST = L::NST;
@@ -217,8 +225,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
     const uint32_t r0 = static_cast<uint32_t>((uint64_t)units * blockIdx.x / gridDim.x) * UNIT;
     const uint32_t r1 = static_cast<uint32_t>((uint64_t)units * (blockIdx.x + 1) / gridDim.x) * UNIT;
     const uint32_t nst = (r1 - r0 + ROWS - 1) / ROWS;
+    const bool dynamic = p.next != nullptr;
+    const uint32_t nchunks = (p.rows + ROWS - 1) / ROWS;
     uint64_t* full = reinterpret_cast<uint64_t*>(raw + L::FULL);
     uint64_t* empty = reinterpret_cast<uint64_t*>(raw + L::EMPTY);
+    volatile uint32_t* stage_row = reinterpret_cast<volatile uint32_t*>(raw + L::STAGE_ROW);
+    volatile uint32_t* stage_cnt = reinterpret_cast<volatile uint32_t*>(raw + L::STAGE_CNT);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], CONSUMERS);
@@ -230,18 +242,36 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
     if (warp == CONSUMERS) {
         // Producer: one thread streams this block's rows.  Nothing it reads is written by another kernel.
         if (lane == 0) {
-            for (uint32_t i = 0; i < nst; i++) {
+            // The stage after the last one carries a count of zero: the consumers stop there.
+            uint32_t chunk = blockIdx.x;  // dynamic: the stage's number among all stages of the matrix
+            for (uint32_t i = 0;; i++) {
                 const uint32_t s = i % NST;
                 if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1)) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                     break;
                 }
-                const uint32_t row = r0 + i * ROWS, here = min((uint32_t)ROWS, r1 - row);
+                uint32_t row, here;
+                if (dynamic) {
+                    row = chunk * ROWS;
+                    here = chunk < nchunks ? min((uint32_t)ROWS, p.rows - row) : 0u;
+                } else {
+                    row = r0 + i * ROWS;
+                    here = i < nst ? min((uint32_t)ROWS, r1 - row) : 0u;
+                }
+                stage_row[s] = row, stage_cnt[s] = here;
+                if (here == 0) {
+                    mbar_arrive(&full[s]);  // nothing to copy: the phase completes on this arrival alone
+                    break;
+                }
                 const uint32_t bw = here * (K * WB / 8), bs = here * (K / GROUP * 2);
                 mbar_expect_tx(&full[s], bw + bs);
                 bulk_load(raw + L::W + s * SW, p.w + (size_t)row * (K * WB / 8), bw, &full[s]);
                 bulk_load(raw + L::S + s * SS, p.s + (size_t)row * (K / GROUP), bs, &full[s]);
+                // The next stage's number: by index while the ring fills, from the counter after that.  The atomic is asked
+                // for here and first needed after the wait for a free stage, which hides its trip to the L2.
+                if (dynamic) chunk = i + 1 < (uint32_t)NST ? blockIdx.x + (i + 1) * gridDim.x : (uint32_t)NST * gridDim.x + atomicAdd(p.next, 1u);
             }
+            if (dynamic && atomicAdd(p.next + 1, 1u) == gridDim.x - 1) p.next[0] = 0u, p.next[1] = 0u;  // every block has taken its last stage
             pdl_launch_dependents();
             // Ask the L2 for what the next kernel's block with this index will stream first.
             prefetch_hint(p.pf, blockIdx.x, gridDim.x);
@@ -276,20 +306,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
 
     float bestv = -INFINITY;
     uint32_t besti = 0xffffffffu;
-    bool ok = true;
-    for (uint32_t i = 0; i < nst; i++) {
+    for (uint32_t i = 0;; i++) {
         const uint32_t s = i % NST;
-        if (ok && !mbar_wait(&full[s], (i / NST) & 1)) {
-            atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
-            ok = false;
+        const bool ok = mbar_wait(&full[s], (i / NST) & 1);
+        if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);  // the producer's copies never landed: treated as the end of the work
+        const uint32_t here = ok ? stage_cnt[s] : 0u;
+        // Warps that share rows leave the loop together, through their barrier below (one of them giving up a wait must
+        // not leave the others at a barrier); a warp with rows of its own leaves here.
+        if constexpr (WPR == 1) {
+            if (here == 0) break;
         }
-        const uint32_t row = r0 + i * ROWS + grp * RPW;  // the warp's first row of this stage
+        const uint32_t first_row = stage_row[s], row_end = first_row + here;  // rows of this stage: [first_row, row_end)
+        const uint32_t row = first_row + grp * RPW;  // the warp's first row of this stage
         float v[RPW];
 #pragma unroll
         for (int j = 0; j < RPW; j++) {
             v[j] = 0.0f;
             if constexpr (WB == 4) {
-                if (ok && row + j < r1) {
+                if (row + j < row_end) {
                     // The lane's two blocks of 32 columns are 16 bytes each: 32 lane and 1024 + 32 lane of the segment.
                     const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * (K / 2) + seg * (SEG / 2);
                     const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 64) + seg * 32;
@@ -297,7 +331,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
                     const float s0 = __half2float(sr[lane >> 1]) * pl[0].mul, s1 = __half2float(sr[16 + (lane >> 1)]) * pl[1].mul;
                     v[j] = fmaf(block_dot_q4(w1, pl[1], sx[1]), s1, block_dot_q4(w0, pl[0], sx[0]) * s0);
                 }
-            } else if (ok && row + j < r1) {
+            } else if (row + j < row_end) {
                 const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * K + seg * SEG;
                 const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 32) + seg * 64;
                 const uint4 a0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + first) * 16);
@@ -309,7 +343,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
+        if (lane == 0 && here != 0) mbar_arrive(&empty[s]);
         float r;           // row total: in lane 0 (and, with two rows, the second row's in lane 16)
         uint32_t out_row;  // the row this lane would write
         if constexpr (RPW == 2) {
@@ -330,14 +364,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
         if constexpr (WPR > 1) {
             float* red = reinterpret_cast<float*>(raw + L::RED) + (i & 1) * CONSUMERS;
             if (lane == 0) red[warp] = r;
-            named_bar_sync(2 + grp, WPR * 32);
+            if (named_bar_or(2 + grp, WPR * 32, here == 0)) break;
             if (seg != 0) continue;
             r = 0.0f;
 #pragma unroll
             for (int j = 0; j < WPR; j++) r += red[warp + j];
         }
         const bool writer = (EPI == EPI_GEGLU || RPW == 1) ? lane == 0 : (lane & 15) == 0;
-        if (writer && out_row < r1) {
+        if (writer && out_row < row_end) {
             if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[out_row] = p.gelu_mul ? gelu_tanh(r) * __ldg(p.gelu_mul + out_row) : r;
             if constexpr (EPI == EPI_F16) static_cast<__half*>(p.y)[out_row] = __float2half_rn(r);
             if constexpr (EPI == EPI_GEGLU) static_cast<float*>(p.y)[out_row / 2] = r;
@@ -378,6 +412,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_q8_kernel(const GemvParams p,
     }
 }
 
+// The entry point.  At most 80 registers a thread (17 warps: 43,520 of the SM's 65,536), so that a block of the small
+// kernel below fits beside one of these: the decode step keeps the next large product's block resident, its ring
+// filling, while the short kernels before it run.
+template <int WPR, int XMODE, int EPI, int WB = 8>
+__global__ void __maxnreg__(80) gemv_q8_kernel(const GemvParams p, uint32_t* status) {
+    gemv_body<WPR, XMODE, EPI, WB>(p, status);
+}
+
 // Any shape the staged kernel does not take (cols not a multiple of 2048): one warp per row straight from global
 // memory, with the same block arithmetic.
 template <int XMODE, int EPI>
@@ -405,6 +447,220 @@ __global__ void __launch_bounds__(256) gemv_q8_generic(const GemvParams p) {
     }
 }
 
+// ---- the small-footprint kernel ---------------------------------------------------------------------------------------
+//
+// For the short products of a decode step (query/key/value and output projections: a few megabytes over 148 blocks).
+// A block of SMALL_WARPS warps takes up to 2 * SMALL_WARPS rows per pass of 2048 columns, straight from global memory
+// into registers, no ring and ~7 KiB of shared memory, at most 80 registers a thread: it fits on an SM beside a block
+// of the staged kernel.  It releases its dependents at once and loads its first pass of weights before it waits for the
+// kernel in front of it, so a chain of such kernels is resident, weights in hand, before its input exists, and the large
+// product behind the chain fills its ring while the chain runs.
+constexpr int SMALL_WARPS = 8;
+constexpr int SMALL_THREADS = SMALL_WARPS * 32;
+constexpr int SMALL_ROWS = 2 * SMALL_WARPS;  // rows per pass
+
+struct SmallSmem {
+    uint32_t hi[512], mid[512], lo[512];  // planes of 2048 activations, a word per four
+    float mul[64];
+    float4 sums[SMALL_WARPS];
+};
+
+__device__ __forceinline__ void small_store_planes(SmallSmem& sm, int idx, float v0, float v1, float v2, float v3) {
+    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const uint32_t eb = min(__float_as_uint(amax) >> 23, 254u);
+    const bool zero = eb < 22u;
+    const float sc = zero ? 0.0f : __uint_as_float((275u - eb) << 23);
+    const int x0 = __float2int_rn(v0 * sc), x1 = __float2int_rn(v1 * sc), x2 = __float2int_rn(v2 * sc), x3 = __float2int_rn(v3 * sc);
+    sm.hi[idx] = pack_bytes(x0, x1, x2, x3, 0x0062);
+    sm.mid[idx] = pack_bytes(x0, x1, x2, x3, 0x0051);
+    sm.lo[idx] = pack_bytes(x0, x1, x2, x3, 0x0040);
+    if ((idx & 7) == 0) sm.mul[idx >> 3] = zero ? 0.0f : __uint_as_float((eb - 21u) << 23);
+}
+
+__device__ __forceinline__ void small_fetch_planes(const SmallSmem& sm, int b, Planes& pl) {
+    const uint4 h0 = reinterpret_cast<const uint4*>(sm.hi)[2 * b], h1 = reinterpret_cast<const uint4*>(sm.hi)[2 * b + 1];
+    const uint4 m0 = reinterpret_cast<const uint4*>(sm.mid)[2 * b], m1 = reinterpret_cast<const uint4*>(sm.mid)[2 * b + 1];
+    const uint4 l0 = reinterpret_cast<const uint4*>(sm.lo)[2 * b], l1 = reinterpret_cast<const uint4*>(sm.lo)[2 * b + 1];
+    pl.hi[0] = h0.x, pl.hi[1] = h0.y, pl.hi[2] = h0.z, pl.hi[3] = h0.w, pl.hi[4] = h1.x, pl.hi[5] = h1.y, pl.hi[6] = h1.z, pl.hi[7] = h1.w;
+    pl.mid[0] = m0.x, pl.mid[1] = m0.y, pl.mid[2] = m0.z, pl.mid[3] = m0.w, pl.mid[4] = m1.x, pl.mid[5] = m1.y, pl.mid[6] = m1.z, pl.mid[7] = m1.w;
+    pl.lo[0] = l0.x, pl.lo[1] = l0.y, pl.lo[2] = l0.z, pl.lo[3] = l0.w, pl.lo[4] = l1.x, pl.lo[5] = l1.y, pl.lo[6] = l1.z, pl.lo[7] = l1.w;
+    pl.mul = sm.mul[b];
+}
+
+// A lane's share of two rows: blocks `lane` and `lane + 32` of each (two 16-byte pieces a block), and their scales.
+struct SmallRows {
+    uint4 w[2][4];
+    float s[2][2];
+};
+
+__device__ __forceinline__ void small_load_rows(const GemvParams& p, uint32_t row, uint32_t r1, int lane, SmallRows& q) {
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        if (row + j < r1) {
+            const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)(row + j) * SEG);
+            q.w[j][0] = __ldcs(wr + 2 * lane), q.w[j][1] = __ldcs(wr + 2 * lane + 1);
+            q.w[j][2] = __ldcs(wr + 64 + 2 * lane), q.w[j][3] = __ldcs(wr + 64 + 2 * lane + 1);
+            const __half* sr = p.s + (size_t)(row + j) * (SEG / 32);
+            q.s[j][0] = __half2float(__ldcs(sr + lane)), q.s[j][1] = __half2float(__ldcs(sr + lane + 32));
+        } else {
+            q.w[j][0] = q.w[j][1] = q.w[j][2] = q.w[j][3] = make_uint4(0u, 0u, 0u, 0u);
+            q.s[j][0] = q.s[j][1] = 0.0f;
+        }
+    }
+}
+
+template <int XMODE>
+__global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const GemvParams p) {
+    __shared__ SmallSmem sm;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t r0 = static_cast<uint32_t>((uint64_t)p.rows * blockIdx.x / gridDim.x);
+    const uint32_t r1 = static_cast<uint32_t>((uint64_t)p.rows * (blockIdx.x + 1) / gridDim.x);
+    pdl_launch_dependents();
+    SmallRows q;
+    small_load_rows(p, r0 + 2 * warp, r1, lane, q);
+    // Later passes come through the L2 (asked for now) once the first pass is done with the registers.
+    for (uint32_t row = r0 + SMALL_ROWS + 2 * warp; row < r1; row += SMALL_ROWS)
+        for (uint32_t j = 0; j < 2 && row + j < r1; j++)
+            for (int k = lane; k < SEG / 128; k += 32) prefetch_line_l2(p.w + (size_t)(row + j) * SEG + k * 128);
+    unsigned long long* stamp = nullptr;
+    if (p.stamps != nullptr && t == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) stamp = p.stamps + (blockIdx.x == 0 ? 0 : 4);
+    if (stamp) stamp[0] = global_ns();
+    pdl_wait();
+    if (stamp) stamp[1] = global_ns();
+
+    // The input vector as planes: virtual thread v of 512 takes values 4v .. 4v + 3; this block's threads take v = t, t + 256.
+    if constexpr (XMODE == X_F32) {
+        float4 f[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) f[k] = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)(k * SMALL_THREADS + t) * 4);
+#pragma unroll
+        for (int k = 0; k < 2; k++) small_store_planes(sm, k * SMALL_THREADS + t, f[k].x, f[k].y, f[k].z, f[k].w);
+    } else if constexpr (XMODE == X_NORM) {
+        // The residual step and RMS-norm of gemv_body's prologue (ptx/mod.rs:24-30), two groups of four values a thread.
+        float4 h[2], a[2], w2[2];
+        float sy = 0.0f, sh = 0.0f, sha = 0.0f, sa = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const size_t at = (size_t)(k * SMALL_THREADS + t) * 4;
+            h[k] = ld_cg_f4(p.h + at);
+            a[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (p.yres != nullptr) {
+                const float4 y = ld_cg_f4(p.yres + at), w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
+                a[k] = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
+                sy += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+            }
+            w2[k] = p.w2 != nullptr ? __ldg(reinterpret_cast<const float4*>(p.w2 + at)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            sh += h[k].x * h[k].x + h[k].y * h[k].y + h[k].z * h[k].z + h[k].w * h[k].w;
+            sha += h[k].x * a[k].x + h[k].y * a[k].y + h[k].z * a[k].z + h[k].w * a[k].w;
+            sa += a[k].x * a[k].x + a[k].y * a[k].y + a[k].z * a[k].z + a[k].w * a[k].w;
+        }
+        sy = warp_sum(sy), sh = warp_sum(sh), sha = warp_sum(sha), sa = warp_sum(sa);
+        if (lane == 0) sm.sums[warp] = make_float4(sy, sh, sha, sa);
+        __syncthreads();
+        sy = sh = sha = sa = 0.0f;
+#pragma unroll
+        for (int k = 0; k < SMALL_WARPS; k++) {
+            const float4 u = sm.sums[k];
+            sy += u.x, sh += u.y, sha += u.z, sa += u.w;
+        }
+        const float n = static_cast<float>(p.cols);
+        const float ry = p.yres != nullptr ? rsqrtf(sy / n + p.eps) : 0.0f;
+        const float hs = p.yres != nullptr ? p.hscale : 1.0f;
+        const float sq = hs * hs * (sh + 2.0f * ry * sha + ry * ry * sa);
+        const float rh = p.w2 != nullptr ? rsqrtf(fmaxf(sq, 0.0f) / n + p.eps) : 1.0f;
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const float v0 = fmaf(a[k].x, ry, h[k].x) * hs, v1 = fmaf(a[k].y, ry, h[k].y) * hs, v2 = fmaf(a[k].z, ry, h[k].z) * hs, v3 = fmaf(a[k].w, ry, h[k].w) * hs;
+            if (blockIdx.x == 0 && p.h_out != nullptr) *reinterpret_cast<float4*>(p.h_out + (size_t)(k * SMALL_THREADS + t) * 4) = make_float4(v0, v1, v2, v3);
+            small_store_planes(sm, k * SMALL_THREADS + t, v0 * rh * w2[k].x, v1 * rh * w2[k].y, v2 * rh * w2[k].z, v3 * rh * w2[k].w);
+        }
+    } else {
+        // X_ATTN: the vector is attention's output, left as one entry (maximum, sum, unnormalised output) per group of
+        // att_cluster splits; merge the entries with running-maximum weights (ptx/attend.rs:371-405).
+        const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
+        const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
+        uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
+        if (span > 64u) span = (span + 63u) / 64u * 64u;
+        const uint32_t entries = ((n + span - 1) / span + p.att_cluster - 1) / p.att_cluster;
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const uint32_t v = k * SMALL_THREADS + t, head = v / 64, g = head / G, hh = head % G, d0 = (v * 4) % 256;
+            const float* base = p.att_partial + (size_t)g * p.att_splits * stride;
+            float M = -INFINITY, L = 0.0f;
+            float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (uint32_t e0 = 0; e0 < entries; e0 += 4) {
+                float4 acc[4];
+                float m[4], l[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    m[u] = -INFINITY, l[u] = 0.0f, acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (e0 + u < entries) {
+                        const float* ps = base + (size_t)(e0 + u) * stride;
+                        m[u] = ld_cg_f(ps + hh), l[u] = ld_cg_f(ps + G + hh), acc[u] = ld_cg_f4(ps + 2 * G + hh * 256 + d0);
+                    }
+                }
+                const float Mn = fmaxf(fmaxf(M, fmaxf(m[0], m[1])), fmaxf(m[2], m[3]));
+                const float c = exp2f(M - Mn);  // 0 on the first trip (M = -inf)
+                L *= c, o.x *= c, o.y *= c, o.z *= c, o.w *= c;
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    const float wgt = e0 + u < entries ? exp2f(m[u] - Mn) : 0.0f;
+                    L = fmaf(wgt, l[u], L);
+                    o.x = fmaf(wgt, acc[u].x, o.x), o.y = fmaf(wgt, acc[u].y, o.y), o.z = fmaf(wgt, acc[u].z, o.z), o.w = fmaf(wgt, acc[u].w, o.w);
+                }
+                M = Mn;
+            }
+            const float inv = 1.0f / L;
+            small_store_planes(sm, v, o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        }
+    }
+    __syncthreads();
+    if (stamp) stamp[2] = global_ns();
+
+    for (uint32_t base_row = r0; base_row < r1; base_row += SMALL_ROWS) {
+        const uint32_t row = base_row + 2 * warp;
+        if (base_row != r0) small_load_rows(p, row, r1, lane, q);
+        float v[2];
+        {
+            Planes pl;
+            small_fetch_planes(sm, lane, pl);
+            v[0] = block_dot(q.w[0][0], q.w[0][1], pl) * (q.s[0][0] * pl.mul);
+            v[1] = block_dot(q.w[1][0], q.w[1][1], pl) * (q.s[1][0] * pl.mul);
+            small_fetch_planes(sm, lane + 32, pl);
+            v[0] = fmaf(block_dot(q.w[0][2], q.w[0][3], pl), q.s[0][1] * pl.mul, v[0]);
+            v[1] = fmaf(block_dot(q.w[1][2], q.w[1][3], pl), q.s[1][1] * pl.mul, v[1]);
+        }
+        const bool upper = lane & 16;
+        float r = (upper ? v[1] : v[0]) + __shfl_xor_sync(0xffffffffu, upper ? v[0] : v[1], 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+        const uint32_t out_row = row + (upper ? 1 : 0);
+        if ((lane & 15) == 0 && out_row < r1) static_cast<float*>(p.y)[out_row] = r;
+    }
+    if (stamp) stamp[3] = global_ns();
+}
+
+// Whether the small kernel takes this product: eight-bit weights, 2048 columns, f32 out with no extras, and few enough
+// rows a block that two passes cover them.
+bool small_supports(const GemvParams& p, int sms) {
+    if (p.wbits != 8 || p.cols != SEG || p.epi != EPI_F32 || p.gelu_mul != nullptr) return false;
+    if (p.xmode != X_F32 && p.xmode != X_NORM && p.xmode != X_ATTN) return false;
+    return p.rows <= (uint32_t)sms * 2 * SMALL_ROWS;
+}
+
+int launch_small(tb_context* ctx, const GemvParams& p) {
+    uint32_t grid = (uint32_t)ctx->sms;
+    const uint32_t most = (p.rows + 1) / 2;
+    if (grid > most) grid = most;
+    const dim3 g(grid), b(SMALL_THREADS);
+    if (p.xmode == X_NORM) TB_CUDA(launch_kernel(ctx, gemv_small_kernel<X_NORM>, g, b, 0, true, p));
+    else if (p.xmode == X_ATTN) TB_CUDA(launch_kernel(ctx, gemv_small_kernel<X_ATTN>, g, b, 0, true, p));
+    else TB_CUDA(launch_kernel(ctx, gemv_small_kernel<X_F32>, g, b, 0, true, p));
+    return OK;
+}
+
 template <int WPR, int XMODE, int EPI, int WB = 8>
 int launch_staged(tb_context* ctx, const GemvParams& p) {
     auto kernel = gemv_q8_kernel<WPR, XMODE, EPI, WB>;
@@ -420,8 +676,14 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     constexpr uint32_t LEAST = UNIT > (uint32_t)rows_per_warp(WPR) ? UNIT : (uint32_t)rows_per_warp(WPR);
     const uint32_t most = (p.rows + LEAST - 1) / LEAST;
     if (grid > most) grid = most > 0 ? most : 1;
-    (void)ROWS;
-    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR, WB), true, p, ctx->status));
+    // Matrices of at least two stages a block hand their stages out through a counter; smaller ones are split evenly.
+    GemvParams q = p;
+    if (ctx->dynamic && (p.rows + ROWS - 1) / ROWS >= 2 * grid) {
+        if (q.next == nullptr) q.next = ctx->sched + 2 * (ctx->sched_at++ % 64u);
+    } else {
+        q.next = nullptr;
+    }
+    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR, WB), true, q, ctx->status));
     return OK;
 }
 
@@ -483,6 +745,8 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if (p.epi != EPI_ARGMAX && p.y == nullptr) return fail(OUT_OF_RANGE, "gemv: null output");
     if (p.gelu_mul != nullptr && p.epi != EPI_F32) return fail(OUT_OF_RANGE, "gemv: the GELU-times-vector output is f32");
     if (p.wbits != 8 && p.wbits != 4) return fail(OUT_OF_RANGE, "gemv: weights are 8 or 4 bits");
+    if (p.xmode == X_ATTN && p.att_cluster == 0) return fail(OUT_OF_RANGE, "gemv: att_cluster must be at least 1");
+    if (((p.lean && ctx->lean) || ctx->lean == 2) && small_supports(p, ctx->sms)) return launch_small(ctx, p);
     if (p.wbits == 4) {
         switch (p.cols) {
             case 2048: return dispatch_staged_q4<1>(ctx, p);

@@ -16,6 +16,11 @@ struct tb_context {
     uint32_t* status_host = nullptr;  // pinned mirror used by tb_status
     bool pdl = true;                  // launch kernels with programmatic stream serialization
     bool prefetch = true;             // give kernels L2 hints about the next kernel's weights
+    bool dynamic = true;              // large matrix-vector products hand their stages out through a counter (TACHYON_B200_STATIC=1: never)
+    int lean = 1;                     // the small-footprint kernel for short products: 0 never (TACHYON_B200_NO_LEAN=1), 1 where the caller
+                                      // marks a product as short (GemvParams::lean), 2 wherever the shape allows (tb_context_set_lean)
+    uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
+    uint32_t sched_at = 0;            // which pair the next launch takes
     int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
 };
 
@@ -89,6 +94,12 @@ struct GemvParams {
     uint32_t trace_mask = 0;
     uint32_t wbits = 8;           // 8: int8 codes, an f16 scale per 32; 4: the reference's Q4, two per byte, a scale per 64
     Prefetch pf;                  // optional hint for the L2
+    // Two device words, zero between launches, through which a large product hands out its stages (see gemv_body); null:
+    // the launch takes a pair from the context's pool.  Launches that may overlap need pairs of their own.
+    uint32_t* next = nullptr;
+    // != 0: the product is short and the next kernel in the stream should start as early as possible: run it as the
+    // small-footprint kernel (no ring, weights in registers, dependents released at once) when its shape allows.
+    uint32_t lean = 0;
     // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for
     // the previous kernel, after the prologue and at the end.
     unsigned long long* stamps = nullptr;
@@ -97,6 +108,7 @@ struct GemvParams {
     const float* att_partial = nullptr;
     const uint32_t* att_pos = nullptr;
     uint32_t att_splits = 1, att_window = 1, att_heads = 8, att_kv = 2;
+    uint32_t att_cluster = 1;     // splits merged per entry of att_partial by the attention kernel itself (AttendParams::cluster)
 };
 
 int launch_gemv(tb_context* ctx, const GemvParams& p);
@@ -126,6 +138,9 @@ struct AttendParams {
     uint32_t defer = 0;            // != 0: every split only stores its partial; the product that follows merges them (X_ATTN)
     uint32_t early = 0;            // != 0: the position and the older cache rows are final before the previous kernel in the
                                    // stream started, so the first tile may be fetched ahead of griddepcontrol.wait
+    uint32_t cluster = 1;          // > 1 (2, 4 or 8, dividing splits; needs defer): blocks of that many neighbouring splits form a
+                                   // thread-block cluster and merge their results in distributed shared memory, leaving one entry of
+                                   // `partial` per cluster (entry c of a key-value head = its splits c * cluster ...)
 };
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
@@ -235,6 +250,31 @@ inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (pdl && ctx->pdl) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The same with the grid's blocks grouped into thread-block clusters of `cluster` (1, 1, 1: none).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, dim3 cluster, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (pdl && ctx->pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster.x, attr[n].val.clusterDim.y = cluster.y, attr[n].val.clusterDim.z = cluster.z;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -113,3 +113,50 @@ def test_attention_rejects_bad_descriptors(ctx):
     a.window, a.heads = 16, 6
     with pytest.raises(tb.Error):
         ctx.attend_decode(a)  # three query heads per kv head: no kernel
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+@pytest.mark.parametrize("lean", [1, 0])
+@pytest.mark.parametrize("cap,win,pos,splits,fresh,kv", [(640, 512, 2048, 8, True, 2), (640, 512, 100, 8, True, 2), (640, 512, 40, 8, True, 2), (4096, 4096, 2048, 32, True, 2),
+                                                          (4096, 4096, 4095, 32, False, 2), (4096, 4096, 300, 32, True, 4), (640, 512, 5999, 16, False, 8),
+                                                          (640, 512, 0, 8, True, 2)])
+def test_attention_then_projection_with_splits_merged_in_clusters(ctx, cluster, lean, cap, win, pos, splits, fresh, kv):
+    """tb_attend_project: what a decode step does between its query/key/value and its gate/up products.  Whatever the
+    cluster size (1: every split reaches the projection's prologue; 8: one entry per eight splits, merged in distributed
+    shared memory), with empty splits inside a cluster, whole clusters without positions, and the small or the staged
+    projection kernel, the result is the oracle's attention output times the dequantised matrix."""
+    heads, rows = 8, 512
+    seed = pos + cap + kv
+    qkv = values_fast((heads + 2 * kv) * D, seed)
+    qn, kn = (0.2 + 0.1 * values_fast(D, seed + 1)).astype(np.float32), (0.2 + 0.1 * values_fast(D, seed + 2)).astype(np.float32)
+    freq = oracle.rope_freq(10000.0, D, 1.0)
+    kc, vc = f16(0.3 * values_fast(kv * cap * D, seed + 3)), f16(0.3 * values_fast(kv * cap * D, seed + 4))
+    att = oracle.attend_decode(qkv, qn, kn, freq, kc.copy(), vc.copy(), pos, cap, win, fresh, heads, kv, D, 1.0)
+    from util import q8_weights
+
+    w, s = q8_weights(rows, heads * D, 77)
+    deq = w.astype(np.float64) * np.repeat(f16_to_f32(s).astype(np.float64), 32, axis=1)
+    want, bound = deq @ att, np.abs(deq) @ np.abs(att)
+    bufs = [ctx.upload(a) for a in (qkv, qn, kn, freq, kc, vc, np.array([pos], np.uint32), w, s)]
+    part, y = ctx.zeros(ctx.attend_scratch_bytes(heads, kv, splits)), ctx.zeros(rows * 4)
+    a = tb.Attend(qkv=bufs[0].ptr, q_norm=bufs[1].ptr, k_norm=bufs[2].ptr, freq=bufs[3].ptr, k_cache=bufs[4].ptr, v_cache=bufs[5].ptr, pos=bufs[6].ptr, cap=cap,
+                  window=win, fresh=int(fresh), heads=heads, kv_heads=kv, scale=1.0, eps=1e-6, partial=part.ptr, count=None, splits=splits, out=None, out_dtype=tb.F32)
+    ctx.set_lean(lean)
+    try:
+        for _ in range(2):
+            ctx.attend_project(a, cluster, bufs[7], bufs[8], rows, y)
+    finally:
+        ctx.set_lean(1)
+    got = y.download(np.float32, rows)
+    assert np.all(np.abs(got - want) <= 1e-3 * bound + 1e-6), float(np.abs(got - want).max())
+    assert ctx.status() == 0
+
+
+def test_cluster_sizes_that_do_not_fit_are_refused(ctx):
+    z = ctx.zeros(1 << 16)
+    a = tb.Attend(qkv=z.ptr, k_cache=z.ptr, v_cache=z.ptr, pos=z.ptr, cap=64, window=64, fresh=1, heads=8, kv_heads=2, scale=1.0, eps=1e-6, partial=z.ptr,
+                  count=None, splits=6, out=None, out_dtype=tb.F32)
+    for cluster in (3, 4, 16):  # not a power of two up to 8, not a divisor of the splits, too large
+        with pytest.raises(tb.Error) as e:
+            ctx.attend_project(a, cluster, z, z, 64, z)
+        assert e.value.status == 3

@@ -415,3 +415,54 @@ def test_per_layer_inputs(ctx):
     with pytest.raises(tb.Error) as e:
         tb.Decoder(ctx, cfg, context=96, weight_bits=4)
     assert e.value.status == 9
+
+
+def test_a_layer_sharing_the_cache_of_the_layer_right_before_it(ctx):
+    """The shortest distance between a layer and the layer whose cache it reads (model/mod.rs:138-143 with every layer
+    sliding): layer 2 attends over the row layer 1 appended a few short kernels earlier in the same step, so nothing of
+    layer 2's attention may be fetched before layer 1's has finished."""
+    cfg = small_config(layers=3)
+    cfg.global_every, cfg.shared = 0, 1
+    dec = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True)
+    dec.fill_random(SEED + 9)
+    dec.build()
+    ref = OracleModel(cfg, SEED + 9, context=64, chunk=8)
+    assert ref.tensors["2.qkv.w"].shape[0] == cfg.heads * cfg.head_dim
+    token = 17
+    for pos in range(40):
+        want_token, want_logits, want_hidden = ref.step(token, pos)
+        got_token = dec.step(token)
+        order = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+        check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+        assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+        token = (pos * 7919 + 13) % cfg.vocab
+    # chained replays, where kernels of neighbouring steps overlap the most, give the same tokens as single steps
+    dec.reset()
+    single, t = [], 5
+    for _ in range(24):
+        t = dec.step(t)
+        single.append(t)
+    dec.reset()
+    assert [int(v) for v in dec.run(5, 24)] == single
+    dec.close()
+
+
+def test_a_prompt_fed_step_by_step_does_not_count_as_generated_text(ctx):
+    """Without chunk buffers the prompt goes through the decode step token by token.  Those steps must not mark their
+    dropped picks as seen: the repetition penalty is about generated tokens (the reference's prefill samples nothing,
+    model/prefill.rs:124-141)."""
+    cfg = small_config()
+    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(20)]
+    outs = []
+    for settings_first in (True, False):
+        dec = tb.Decoder(ctx, cfg, context=64, chunk=0, keep_logits=False)  # chunk 0: the prompt is fed by steps
+        dec.fill_random(SEED)
+        dec.build()
+        if settings_first:
+            dec.set_sampling(penalty=1.3, softcap=cfg.softcap)
+        dec.prefill(prompt[:-1])
+        if not settings_first:
+            dec.set_sampling(penalty=1.3, softcap=cfg.softcap)
+        outs.append([int(t) for t in dec.run(prompt[-1], 12)])
+        dec.close()
+    assert outs[0] == outs[1]

@@ -136,3 +136,54 @@ def test_argmax_epilogue_picks_the_lowest_index_of_the_largest(ctx):
     s2[17] = s2[3000] = f16(np.full(cols // 32, 0.01, np.float32))
     ctx.gemv_q8_argmax(ctx.upload(wd2), ctx.upload(s2), xd, tb.F32, None, rows, cols, scratch, state, None)
     assert int(state.download(np.uint32, 2)[1]) == 17
+
+
+@pytest.mark.parametrize("rows", [2048, 3072, 4736, 100, 17, 1])
+def test_the_small_kernel_gives_the_staged_kernels_bits(ctx, rows):
+    """tb_context_set_lean(2): products of 2048 columns and few rows a block go through the small-footprint kernel (weights
+    straight into registers, no ring).  Same block arithmetic, same order: the same bits, with the plain f32 input and
+    with the residual/norm prologue."""
+    cols = 2048
+    w, s = q8_weights(rows, cols, 41 + rows)
+    rng = np.random.default_rng(rows)
+    x = rng.standard_normal(cols).astype(np.float32)
+    h, y, w1, w2 = (rng.uniform(-2, 2, cols).astype(np.float32) for _ in range(4))
+    outs = []
+    for mode in (0, 2):
+        ctx.set_lean(mode)
+        try:
+            plain = run(ctx, w, s, x, tb.F32, tb.F32)
+            bufs = [ctx.upload(a) for a in (w, s, h, y, w1, w2)]
+            hout, yout = ctx.zeros(cols * 4), ctx.zeros(rows * 4)
+            ctx.gemv_q8_norm(bufs[0], bufs[1], bufs[2], bufs[3], bufs[4], bufs[5], 1e-6, 0.75, hout, yout, rows, cols, False)
+            hout2, yout2 = ctx.zeros(cols * 4), ctx.zeros(rows * 4)
+            ctx.gemv_q8_norm(bufs[0], bufs[1], bufs[2], None, None, None, 1e-6, 1.0, hout2, yout2, rows, cols, False)
+            outs.append((plain, yout.download(np.float32, rows), hout.download(np.float32, cols), yout2.download(np.float32, rows)))
+        finally:
+            ctx.set_lean(1)
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
+    _, exact, bound = oracle.gemv_q8(w, s, x)
+    assert np.all(np.abs(outs[1][0].astype(np.float64) - exact) <= 1e-5 * bound + 1e-6)
+    assert ctx.status() == 0
+
+
+@pytest.mark.parametrize("rows,cols", [(32768, 2048), (2048, 16384), (9999, 2048), (40000, 4096)])
+def test_stages_handed_out_by_a_counter_give_the_same_bits(ctx, rows, cols):
+    """Large products give their stages of rows to whichever block is free (a counter in device memory); small ones split
+    the rows evenly.  Which block computes a row does not change the row: same bits, launch after launch, and the
+    counters return to zero (the second launch would otherwise skip rows)."""
+    w, s = q8_weights(rows, cols, 51)
+    x = np.random.default_rng(52).standard_normal(cols).astype(np.float32)
+    ctx.set_dynamic(False)
+    try:
+        static = run(ctx, w, s, x, tb.F32, tb.F32)
+    finally:
+        ctx.set_dynamic(True)
+    wd, sd, xd, yd = ctx.upload(w), ctx.upload(s), ctx.upload(x), ctx.zeros(rows * 4)
+    for _ in range(70):  # more launches than the context has counter pairs
+        ctx.gemv_q8(wd, sd, xd, tb.F32, yd, tb.F32, rows, cols)
+    assert np.array_equal(yd.download(np.float32, rows), static)
+    _, exact, bound = oracle.gemv_q8(w, s, x)
+    assert np.all(np.abs(static.astype(np.float64) - exact) <= 1e-5 * bound + 1e-6)
+    assert ctx.status() == 0
