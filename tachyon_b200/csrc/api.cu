@@ -67,6 +67,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->dynamic = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_NO_LEAN");
     ctx->lean = (env != nullptr && env[0] == '1') ? 0 : 1;
+    env = getenv("TACHYON_B200_NO_CLUSTER");
+    ctx->cluster = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_GEMM");
     ctx->gemm_schedule = env != nullptr ? atoi(env) : 0;
     *out = ctx;

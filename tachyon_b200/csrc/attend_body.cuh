@@ -480,8 +480,11 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    cluster_arrive();
+    cluster_wait();
 }
 // Stores v at the address `local` has in block `rank` of the cluster.
 __device__ __forceinline__ void st_cluster(const float* local, uint32_t rank, float v) {
@@ -500,11 +503,15 @@ __device__ __forceinline__ void attend_cluster_body(const AttendParams& p, Clust
     const uint32_t first = sp - rank;  // the cluster's first split
     if (first >= used) return;         // a cluster without positions: all of its blocks leave, nobody writes to anybody
     const uint32_t here = min(C, used - first);  // splits of this cluster that have positions
+    // A block's shared memory may be written from outside only once the block runs: every block says so here and checks
+    // the others right before its first store to them, with its own work in between.
+    cluster_arrive();
     float out[G];
 #pragma unroll
     for (int h = 0; h < G; h++) out[h] = 0.0f;
     Smem& sm = cs.body;
     const bool active = attend_partial<G, false>(p, sm, tid, g, sp, pos, preloaded, trig, out);
+    cluster_wait();
     if (active) {
         if (tid < 2 * G) {
             const float v = tid < G ? sm.mrun[tid] : sm.lrun[tid - G];

@@ -244,9 +244,8 @@ void layout(tb_decoder* d, char* base) {
         if (L.splits == 0) L.splits = 1;
         // Neighbouring splits meet in a thread-block cluster (attend.cu's kernel, one launch per phase): eight where there
         // are that many, else the largest power of two that divides them.
-        static const bool no_cluster = getenv("TACHYON_B200_NO_CLUSTER") != nullptr && getenv("TACHYON_B200_NO_CLUSTER")[0] == '1';
         L.cluster = 1;
-        if (!no_cluster && !d->fused && L.dim == 256 && c.heads != 8 * L.kvh) {
+        if (d->ctx->cluster && !d->fused && L.dim == 256 && c.heads != 8 * L.kvh) {
             if (L.splits >= 8) L.splits = std::min((L.splits + 7) / 8 * 8, std::max(most / 8 * 8, 8u)), L.cluster = 8;
             else if (L.splits % 4 == 0) L.cluster = 4;
             else if (L.splits % 2 == 0) L.cluster = 2;

@@ -19,6 +19,7 @@ struct tb_context {
     bool dynamic = true;              // large matrix-vector products hand their stages out through a counter (TACHYON_B200_STATIC=1: never)
     int lean = 1;                     // the small-footprint kernel for short products: 0 never (TACHYON_B200_NO_LEAN=1), 1 where the caller
                                       // marks a product as short (GemvParams::lean), 2 wherever the shape allows (tb_context_set_lean)
+    bool cluster = true;              // decode attention merges neighbouring splits in thread-block clusters (TACHYON_B200_NO_CLUSTER=1: never)
     uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
     uint32_t sched_at = 0;            // which pair the next launch takes
     int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
