@@ -67,6 +67,14 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->dynamic = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_NO_LEAN");
     ctx->lean = (env != nullptr && env[0] == '1') ? 0 : 1;
+    env = getenv("TACHYON_B200_LATE_TRIGGER");
+    ctx->early_trigger = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_LEAN_QKV");
+    ctx->lean_qkv = env != nullptr && env[0] == '1';
+    env = getenv("TACHYON_B200_L2_AHEAD");
+    ctx->l2_ahead = env != nullptr ? (uint32_t)atoi(env) : 0u;
+    env = getenv("TACHYON_B200_L2_NEXT");
+    ctx->l2_next = env != nullptr ? (uint32_t)atoi(env) : 0u;
     env = getenv("TACHYON_B200_NO_CLUSTER");
     ctx->cluster = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_GEMM");

@@ -522,8 +522,8 @@ __device__ __forceinline__ void attend_cluster_body(const AttendParams& p, Clust
         for (int h = 0; h < G; h++) st_cluster(&cs.xacc[(rank * G + h) * slice + dd], owner, out[h]);
     }
     cluster_sync();
-    if ((uint32_t)tid < G * slice) {
-        const uint32_t h = (uint32_t)tid / slice, dd = (uint32_t)tid % slice;
+    for (uint32_t idx = (uint32_t)tid; idx < G * slice; idx += THREADS) {  // up to G * D / 2 outputs a block
+        const uint32_t h = idx / slice, dd = idx % slice;
         float M = -INFINITY;
         for (uint32_t s = 0; s < here; s++) M = fmaxf(M, cs.xstats[s][h]);
         float L = 0.0f, o = 0.0f;

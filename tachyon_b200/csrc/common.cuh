@@ -121,6 +121,27 @@ __device__ __forceinline__ void prefetch_hint(const P& pf, uint32_t first, uint3
     }
 }
 
+// Asks the L2 for `rows` rows of a matrix from `row` on: row_bytes of codes and srow_bytes of scales a row.  One thread.
+__device__ __forceinline__ void prefetch_rows_l2(const void* w, const void* s, uint32_t row, uint32_t rows, uint32_t row_bytes, uint32_t srow_bytes) {
+    const char* wb = reinterpret_cast<const char*>(w) + (size_t)row * row_bytes;
+    const size_t wn = (size_t)rows * row_bytes;
+    for (size_t o = 0; o < wn; o += 16384) bulk_prefetch_l2(wb + o, (uint32_t)(wn - o < 16384 ? wn - o : 16384));
+    const char* sb = reinterpret_cast<const char*>(s) + (size_t)row * srow_bytes;
+    const size_t sn = (size_t)rows * srow_bytes;
+    for (size_t o = 0; o < sn; o += 16384) bulk_prefetch_l2(sb + o, (uint32_t)(sn - o < 16384 ? sn - o : 16384));
+}
+
+// The stage form of a hint (see Prefetch in internal.h) for the block with index b.
+template <typename P>
+__device__ __forceinline__ void prefetch_stages(const P& pf, uint32_t b) {
+    if (pf.w == nullptr || pf.stages == 0) return;
+    for (uint32_t k = 0; k < pf.stages; k++) {
+        const uint32_t row = (b + k * pf.grid) * pf.stage_rows;
+        if (row >= pf.rows) break;
+        prefetch_rows_l2(pf.w, pf.s, row, min(pf.stage_rows, pf.rows - row), pf.row_bytes, pf.srow_bytes);
+    }
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its independent prologue / wait for the
 // kernels before this one to have finished and their writes to be visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -303,6 +303,7 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols, p.wbits = m.bits;
     p.next = d->sched + 2 * (size_t)d->launches;  // a launch's own pair: neighbouring launches overlap
+    p.early = d->ctx->early_trigger ? 1 : 0;
     if (d->stamps) p.stamps = d->stamps + 8 * (size_t)d->launches;
     d->launches++;
     if (d->collect) {
@@ -354,7 +355,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             cur = 1 - cur;
         }
         q.epi = EPI_F32, q.y = d->qkv;
-        q.lean = 1;  // short: the small kernel, so that the chain behind it is resident early
+        q.lean = d->ctx->lean_qkv ? 1 : 0;
         q.pf = hint(d, L.o, 1, 0, PF);  // what follows attention
         TB_TRY(gemv(d, L.qkv, q));
 
@@ -391,7 +392,8 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
             o.att_heads = c.heads, o.att_kv = L.kvh, o.att_cluster = L.cluster;
         }
-        o.lean = 1;
+        o.lean = 1;  // short: the small kernel, which fits beside the gate/up product's block, so that block fills its ring meanwhile
+        if (!wide && L.cluster == L.splits) o.att_entries = 1;  // one cluster covers the window: always one entry
         o.pf = hint(d, L.gate_up, 2, PF, PF);
         TB_TRY(gemv(d, L.o, o));
 
@@ -401,6 +403,14 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         cur = 1 - cur;
         gu.epi = EPI_GEGLU, gu.y = d->g;
         gu.pf = hint(d, L.down, 1, 0, PF);
+        gu.l2_ahead = d->ctx->l2_ahead;
+        if (d->ctx->l2_next && L.down.bits == 8 && (c.ffn == 2048 || c.ffn == 4096 || c.ffn == 8192 || c.ffn == 16384)) {
+            // The head of the down projection (its blocks' first stages: 32 * 2048 / ffn rows each, as launch_gemv cuts them) into the L2 while the
+            // short kernels in front of this one run and HBM has nothing else to do.
+            Prefetch& pf = gu.pf;
+            pf.w = L.down.w, pf.s = L.down.s, pf.rows = L.down.rows, pf.cols = L.down.cols, pf.grid = (uint32_t)d->ctx->sms;
+            pf.stage_rows = 32 / (c.ffn / 2048), pf.stages = d->ctx->l2_next, pf.row_bytes = c.ffn, pf.srow_bytes = c.ffn / 16;
+        }
         TB_TRY(gemv(d, L.gate_up, gu));
 
         GemvParams dn;

@@ -27,14 +27,15 @@ constexpr int THREADS = CTHREADS + 32;
 constexpr int SEG = 2048;       // columns one warp covers with its register-resident activation planes
 constexpr int SMEM_LIMIT = 230000;
 
-// Rows a warp takes per stage: two when a row is one segment wide.
-constexpr int rows_per_warp(int wpr) { return wpr == 1 ? 2 : 1; }
+// Rows a warp takes per stage: two, whatever the width (both reduced in one round of five exchanges; with wider rows,
+// half as many meetings of the warps that share them).
+constexpr int rows_per_warp(int) { return 2; }
 constexpr int stage_rows(int wpr) { return CONSUMERS / wpr * rows_per_warp(wpr); }
 // wb: bits per weight, 8 (one f16 scale per 32) or 4 (the reference's Q4: two weights per byte, one scale per 64).
 constexpr int stage_w(int wpr, int wb = 8) { return stage_rows(wpr) * wpr * SEG * wb / 8; }
 constexpr int stage_s(int wpr, int wb = 8) { return stage_w(wpr, wb) / 16; }
 constexpr int plane_bytes(int wpr) { return wpr * 64 * (96 + 4); }
-constexpr int tail_bytes() { return 16 * 8 + 2 * CONSUMERS * 4 + 2 * 2 * CONSUMERS * 4 + 4 * CONSUMERS * 4 + 64; }
+constexpr int tail_bytes() { return 16 * 8 + 2 * 2 * CONSUMERS * 4 + 2 * 2 * CONSUMERS * 4 + 4 * CONSUMERS * 4 + 64; }
 constexpr int stages(int wpr, int wb = 8) {
     const int n = (SMEM_LIMIT - plane_bytes(wpr) - tail_bytes()) / (stage_w(wpr, wb) + stage_s(wpr, wb));
     return n > 8 ? 8 : n;
@@ -54,8 +55,8 @@ struct Layout {
     static constexpr int MUL = LO + WPR * 64 * 32;
     static constexpr int FULL = MUL + WPR * 64 * 4;
     static constexpr int EMPTY = FULL + 8 * 8;
-    static constexpr int RED = EMPTY + 8 * 8;                 // float [2][CONSUMERS]
-    static constexpr int BESTV = RED + 2 * CONSUMERS * 4;      // float [2 * CONSUMERS]
+    static constexpr int RED = EMPTY + 8 * 8;                 // float [2][CONSUMERS][2]
+    static constexpr int BESTV = RED + 2 * 2 * CONSUMERS * 4;  // float [2 * CONSUMERS]
     static constexpr int BESTI = BESTV + 2 * CONSUMERS * 4;    // uint32 [2 * CONSUMERS]
     static constexpr int SUMS = BESTI + 2 * CONSUMERS * 4;     // float [CONSUMERS][4]
     static constexpr int STAGE_ROW = SUMS + 4 * CONSUMERS * 4;  // uint32 [8]: first row of the stage's rows
@@ -242,14 +243,14 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     if (warp == CONSUMERS) {
         // Producer: one thread streams this block's rows.  Nothing it reads is written by another kernel.
         if (lane == 0) {
+            // The kernel behind this one is released at once (p.early: all it does before its own wait is to fetch constants)
+            // or as soon as this block knows its last copy (the grid's launch then overlaps the ring's draining).
+            bool released = p.early != 0;
+            if (released) pdl_launch_dependents();
             // The stage after the last one carries a count of zero: the consumers stop there.
             uint32_t chunk = blockIdx.x;  // dynamic: the stage's number among all stages of the matrix
             for (uint32_t i = 0;; i++) {
                 const uint32_t s = i % NST;
-                if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1)) {
-                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
-                    break;
-                }
                 uint32_t row, here;
                 if (dynamic) {
                     row = chunk * ROWS;
@@ -257,6 +258,20 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
                 } else {
                     row = r0 + i * ROWS;
                     here = i < nst ? min((uint32_t)ROWS, r1 - row) : 0u;
+                }
+                if (!released && (here == 0 || (!dynamic && i + 1 >= nst))) released = true, pdl_launch_dependents();
+                if (i == (uint32_t)NST) {
+                    // The ring is full and the first stage is not yet free: what comes after the ring, and the head of the next
+                    // large matrix, may as well wait in the L2.
+                    for (uint32_t k = 0; k < p.l2_ahead; k++) {
+                        const uint32_t c = dynamic ? ((uint32_t)NST + k) * gridDim.x + blockIdx.x : 0u, far = dynamic ? c * ROWS : r0 + (i + k) * ROWS;
+                        if (far < (dynamic ? p.rows : r1)) prefetch_rows_l2(p.w, p.s, far, min((uint32_t)ROWS, (dynamic ? p.rows : r1) - far), K * WB / 8, K / GROUP * 2);
+                    }
+                    prefetch_stages(p.pf, blockIdx.x);
+                }
+                if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
                 }
                 stage_row[s] = row, stage_cnt[s] = here;
                 if (here == 0) {
@@ -272,7 +287,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
                 if (dynamic) chunk = i + 1 < (uint32_t)NST ? blockIdx.x + (i + 1) * gridDim.x : (uint32_t)NST * gridDim.x + atomicAdd(p.next, 1u);
             }
             if (dynamic && atomicAdd(p.next + 1, 1u) == gridDim.x - 1) p.next[0] = 0u, p.next[1] = 0u;  // every block has taken its last stage
-            pdl_launch_dependents();
+            if (!released) pdl_launch_dependents();
             // Ask the L2 for what the next kernel's block with this index will stream first.
             prefetch_hint(p.pf, blockIdx.x, gridDim.x);
         }
@@ -362,13 +377,14 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
             out_row = row;
         }
         if constexpr (WPR > 1) {
-            float* red = reinterpret_cast<float*>(raw + L::RED) + (i & 1) * CONSUMERS;
-            if (lane == 0) red[warp] = r;
+            // The warps of a row pair meet: each leaves its two partial sums, the first of them adds them up in order.
+            float* red = reinterpret_cast<float*>(raw + L::RED) + (i & 1) * CONSUMERS * 2;
+            if ((lane & 15) == 0) red[warp * 2 + (lane >> 4)] = r;
             if (named_bar_or(2 + grp, WPR * 32, here == 0)) break;
             if (seg != 0) continue;
             r = 0.0f;
 #pragma unroll
-            for (int j = 0; j < WPR; j++) r += red[warp + j];
+            for (int j = 0; j < WPR; j++) r += red[(warp + j) * 2 + (lane >> 4)];
         }
         const bool writer = (EPI == EPI_GEGLU || RPW == 1) ? lane == 0 : (lane & 15) == 0;
         if (writer && out_row < row_end) {
@@ -517,7 +533,7 @@ __global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const Gemv
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const uint32_t r0 = static_cast<uint32_t>((uint64_t)p.rows * blockIdx.x / gridDim.x);
     const uint32_t r1 = static_cast<uint32_t>((uint64_t)p.rows * (blockIdx.x + 1) / gridDim.x);
-    pdl_launch_dependents();
+    pdl_launch_dependents();  // whatever p.early says: this kernel exists to let the chain behind it start
     SmallRows q;
     small_load_rows(p, r0 + 2 * warp, r1, lane, q);
     // Later passes come through the L2 (asked for now) once the first pass is done with the registers.
@@ -580,10 +596,13 @@ __global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const Gemv
         // X_ATTN: the vector is attention's output, left as one entry (maximum, sum, unnormalised output) per group of
         // att_cluster splits; merge the entries with running-maximum weights (ptx/attend.rs:371-405).
         const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
-        const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
-        uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
-        if (span > 64u) span = (span + 63u) / 64u * 64u;
-        const uint32_t entries = ((n + span - 1) / span + p.att_cluster - 1) / p.att_cluster;
+        uint32_t entries = p.att_entries;
+        if (entries == 0) {
+            const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
+            uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
+            if (span > 64u) span = (span + 63u) / 64u * 64u;
+            entries = ((n + span - 1) / span + p.att_cluster - 1) / p.att_cluster;
+        }
 #pragma unroll
         for (int k = 0; k < 2; k++) {
             const uint32_t v = k * SMALL_THREADS + t, head = v / 64, g = head / G, hh = head % G, d0 = (v * 4) % 256;

@@ -19,6 +19,11 @@ struct tb_context {
     bool dynamic = true;              // large matrix-vector products hand their stages out through a counter (TACHYON_B200_STATIC=1: never)
     int lean = 1;                     // the small-footprint kernel for short products: 0 never (TACHYON_B200_NO_LEAN=1), 1 where the caller
                                       // marks a product as short (GemvParams::lean), 2 wherever the shape allows (tb_context_set_lean)
+    bool early_trigger = true;        // kernels of a decode step release the kernel behind them as they start (TACHYON_B200_LATE_TRIGGER=1: when
+                                      // their last copy is issued)
+    bool lean_qkv = false;            // the query/key/value product also runs as the small kernel (TACHYON_B200_LEAN_QKV=1)
+    uint32_t l2_ahead = 0;            // stages beyond its ring a large product asks the L2 for once the ring is full (TACHYON_B200_L2_AHEAD)
+    uint32_t l2_next = 0;             // first stages of the next large product a block asks the L2 for at that point (TACHYON_B200_L2_NEXT)
     bool cluster = true;              // decode attention merges neighbouring splits in thread-block clusters (TACHYON_B200_NO_CLUSTER=1: never)
     uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
     uint32_t sched_at = 0;            // which pair the next launch takes
@@ -67,6 +72,10 @@ struct Prefetch {
     const int8_t* w = nullptr;
     const __half* s = nullptr;
     uint32_t rows = 0, cols = 0, unit = 1, grid = 1, skip = 0, bytes = 0;
+    // The other form of the hint (stages > 0): the later kernel hands out stages of `stage_rows` rows, block b starting
+    // with stages b, b + grid, ...; a block given the hint asks the L2 for the first `stages` of those of its own index,
+    // row_bytes of weights and srow_bytes of scales a row, as soon as its own ring is full.
+    uint32_t stage_rows = 0, stages = 0, row_bytes = 0, srow_bytes = 0;
 };
 
 struct GemvParams {
@@ -101,6 +110,8 @@ struct GemvParams {
     // != 0: the product is short and the next kernel in the stream should start as early as possible: run it as the
     // small-footprint kernel (no ring, weights in registers, dependents released at once) when its shape allows.
     uint32_t lean = 0;
+    uint32_t early = 0;           // != 0: release the kernel behind this one at once (it waits for this one before it reads anything of it)
+    uint32_t l2_ahead = 0;        // stages past the ring to ask the L2 for once the ring is full
     // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for
     // the previous kernel, after the prologue and at the end.
     unsigned long long* stamps = nullptr;
@@ -110,6 +121,7 @@ struct GemvParams {
     const uint32_t* att_pos = nullptr;
     uint32_t att_splits = 1, att_window = 1, att_heads = 8, att_kv = 2;
     uint32_t att_cluster = 1;     // splits merged per entry of att_partial by the attention kernel itself (AttendParams::cluster)
+    uint32_t att_entries = 0;     // != 0: att_partial always holds this many entries a key-value head (one cluster covers the window): no need to read the position
 };
 
 int launch_gemv(tb_context* ctx, const GemvParams& p);

@@ -141,8 +141,8 @@ def test_argmax_epilogue_picks_the_lowest_index_of_the_largest(ctx):
 @pytest.mark.parametrize("rows", [2048, 3072, 4736, 100, 17, 1])
 def test_the_small_kernel_gives_the_staged_kernels_bits(ctx, rows):
     """tb_context_set_lean(2): products of 2048 columns and few rows a block go through the small-footprint kernel (weights
-    straight into registers, no ring).  Same block arithmetic, same order: the same bits, with the plain f32 input and
-    with the residual/norm prologue."""
+    straight into registers, no ring).  Same block arithmetic, same order: the same bits with the plain f32 input; with
+    the residual/norm prologue the same up to the order of the prologue's sums."""
     cols = 2048
     w, s = q8_weights(rows, cols, 41 + rows)
     rng = np.random.default_rng(rows)
@@ -161,8 +161,10 @@ def test_the_small_kernel_gives_the_staged_kernels_bits(ctx, rows):
             outs.append((plain, yout.download(np.float32, rows), hout.download(np.float32, cols), yout2.download(np.float32, rows)))
         finally:
             ctx.set_lean(1)
-    for a, b in zip(outs[0], outs[1]):
-        assert np.array_equal(a, b)
+    assert np.array_equal(outs[0][0], outs[1][0])
+    # with the norm prologue the four sums meet in another order (8 warps of 2 x 4 values, 16 warps of 4): the last bit may differ
+    for a, b in zip(outs[0][1:], outs[1][1:]):
+        assert np.all(np.abs(a - b) <= 2e-6 * np.abs(a).max())
     _, exact, bound = oracle.gemv_q8(w, s, x)
     assert np.all(np.abs(outs[1][0].astype(np.float64) - exact) <= 1e-5 * bound + 1e-6)
     assert ctx.status() == 0
