@@ -86,7 +86,7 @@ int launch_rope_table(tb_context* ctx, const float* freq, uint32_t positions, fl
 
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits) {
     const uint32_t group = heads / kv_heads;
-    return (size_t)kv_heads * splits * (2 * group + (size_t)group * D);
+    return (size_t)kv_heads * splits * (attend_header(group) + (size_t)group * D);
 }
 
 int launch_attend(tb_context* ctx, const AttendParams& p) {
@@ -110,6 +110,11 @@ int launch_attend(tb_context* ctx, const AttendParams& p) {
             TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
             TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
             TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterSmem)));
+            // As much of each SM as possible to shared memory: in a decode step this kernel's blocks move in beside blocks
+            // of the products around it, and an SM's split cannot change while blocks run on it.
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+            TB_CUDA(cudaFuncSetAttribute(attend_kernel<4>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
             configured[ctx->gpu & 63] = true;
         }
     }

@@ -388,13 +388,14 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
     const uint32_t n = min(pos + 1, p.window);
     const uint32_t span = split_span(n, p.splits);
     const uint32_t used = (n + span - 1) / span;
-    const uint32_t stride = 2 * G + G * D;  // floats per partial: maxima, sums, outputs
+    constexpr uint32_t HD = attend_header(G);
+    const uint32_t stride = HD + G * D;  // floats per partial: maxima, sums (padded), outputs
     if (p.defer) {
         // The consumer of the output merges the splits itself: leave this split's statistics and sums, nothing else.
         float* mine = p.partial + (size_t)(g * p.splits + sp) * stride;
         if (tid < G) mine[tid] = sm.mrun[tid], mine[G + tid] = sm.lrun[tid];
 #pragma unroll
-        for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = out[h];
+        for (int h = 0; h < G; h++) mine[HD + h * D + tid] = out[h];
         return;
     }
     if (used == 1) {
@@ -411,7 +412,7 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
     float* mine = p.partial + (size_t)(g * p.splits + sp) * stride;
     if (tid < G) mine[tid] = sm.mrun[tid], mine[G + tid] = sm.lrun[tid];
 #pragma unroll
-    for (int h = 0; h < G; h++) mine[2 * G + h * D + tid] = out[h];
+    for (int h = 0; h < G; h++) mine[HD + h * D + tid] = out[h];
     __threadfence();
     block_sync<FUSED>();
     if (tid == 0) sm.last = (atomicAdd(p.count + g, 1u) == used - 1) ? 1u : 0u;
@@ -446,7 +447,7 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
 #pragma unroll
         for (int u = 0; u < 4; u++)
 #pragma unroll
-            for (int h = 0; h < G; h++) t[u][h] = __ldcg(base + (size_t)(s2 + u) * stride + 2 * G + h * D + tid);
+            for (int h = 0; h < G; h++) t[u][h] = __ldcg(base + (size_t)(s2 + u) * stride + HD + h * D + tid);
 #pragma unroll
         for (int u = 0; u < 4; u++)
 #pragma unroll
@@ -454,7 +455,7 @@ __device__ __forceinline__ void attend_body(const AttendParams& p, Smem& sm, con
     }
     for (; s2 < used; s2++)
 #pragma unroll
-        for (int h = 0; h < G; h++) o[h] = fmaf(wts[s2 * G + h], __ldcg(base + (size_t)s2 * stride + 2 * G + h * D + tid), o[h]);
+        for (int h = 0; h < G; h++) o[h] = fmaf(wts[s2 * G + h], __ldcg(base + (size_t)s2 * stride + HD + h * D + tid), o[h]);
 #pragma unroll
     for (int h = 0; h < G; h++) {
         const float r = o[h] / sm.lrun[h];
@@ -532,8 +533,8 @@ __device__ __forceinline__ void attend_cluster_body(const AttendParams& p, Clust
             L = fmaf(wgt, cs.xstats[s][G + h], L);
             o = fmaf(wgt, cs.xacc[(s * G + h) * slice + dd], o);
         }
-        float* entry = p.partial + (size_t)(g * p.splits + first / C) * (2 * G + G * D);
-        entry[2 * G + h * D + rank * slice + dd] = o;
+        float* entry = p.partial + (size_t)(g * p.splits + first / C) * (attend_header(G) + G * D);
+        entry[attend_header(G) + h * D + rank * slice + dd] = o;
         if (rank == 0 && dd == 0) entry[h] = M, entry[G + h] = L;
     }
 }

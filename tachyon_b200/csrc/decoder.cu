@@ -262,7 +262,7 @@ void layout(tb_decoder* d, char* base) {
     vec(d->sample_partial, (size_t)8 * 1024);
     d->sample_count = reinterpret_cast<uint32_t*>(base + t.take(4));
     // Attention scratch for the larger kind: per key-value head and split the maxima, sums and outputs of its query heads.
-    vec(d->partial, (size_t)c.heads * max_splits * (2 + std::max(dim_of(c, 0), dim_of(c, 1))));
+    vec(d->partial, (size_t)c.heads * max_splits * (4 + std::max(dim_of(c, 0), dim_of(c, 1))));  // at most attend_header(1) = 4 words a head ahead of its outputs
     vec(d->freq[0], dim_of(c, 0) / 2), vec(d->freq[1], dim_of(c, 1) / 2);
     vec(d->trig[0], (size_t)d->settings.context * 256), vec(d->trig[1], (size_t)d->settings.context * 256);  // heads of 256 only
     d->count = reinterpret_cast<uint32_t*>(base + t.take((size_t)c.heads * 4));
@@ -409,7 +409,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
             // short kernels in front of this one run and HBM has nothing else to do.
             Prefetch& pf = gu.pf;
             pf.w = L.down.w, pf.s = L.down.s, pf.rows = L.down.rows, pf.cols = L.down.cols, pf.grid = (uint32_t)d->ctx->sms;
-            pf.stage_rows = 32 / (c.ffn / 2048), pf.stages = d->ctx->l2_next, pf.row_bytes = c.ffn, pf.srow_bytes = c.ffn / 16;
+            pf.stage_rows = gemv_stage_rows(c.ffn), pf.stages = d->ctx->l2_next, pf.row_bytes = c.ffn, pf.srow_bytes = c.ffn / 16;
         }
         TB_TRY(gemv(d, L.gate_up, gu));
 

@@ -17,6 +17,8 @@
 //    shuffles; warps that share a row (cols > 2048) meet on a named barrier.
 #include "planes.cuh"
 
+#include <algorithm>
+
 namespace tb {
 
 namespace {
@@ -30,26 +32,30 @@ constexpr int SMEM_LIMIT = 230000;
 // Rows a warp takes per stage: two, whatever the width (both reduced in one round of five exchanges; with wider rows,
 // half as many meetings of the warps that share them).
 constexpr int rows_per_warp(int) { return 2; }
-constexpr int stage_rows(int wpr) { return CONSUMERS / wpr * rows_per_warp(wpr); }
+// Teams: with rows of 16384 columns the sixteen warps are two row pairs' worth.  Each pair of rows is then a stage of its
+// own, and the two groups of eight warps take the stages in turn: one group's meeting and final sum overlap the other's
+// products, and the stages are small enough (32 KiB) to be handed out evenly.  Otherwise all warps work on every stage.
+constexpr int teams(int wpr) { return wpr == 8 ? 2 : 1; }
+constexpr int stage_rows(int wpr) { return CONSUMERS / wpr / teams(wpr) * rows_per_warp(wpr); }
 // wb: bits per weight, 8 (one f16 scale per 32) or 4 (the reference's Q4: two weights per byte, one scale per 64).
 constexpr int stage_w(int wpr, int wb = 8) { return stage_rows(wpr) * wpr * SEG * wb / 8; }
 constexpr int stage_s(int wpr, int wb = 8) { return stage_w(wpr, wb) / 16; }
 constexpr int plane_bytes(int wpr) { return wpr * 64 * (96 + 4); }
-constexpr int tail_bytes() { return 16 * 8 + 2 * 2 * CONSUMERS * 4 + 2 * 2 * CONSUMERS * 4 + 4 * CONSUMERS * 4 + 64; }
+constexpr int tail_bytes() { return 1024; }  // barriers, reduction slots, stage descriptors (Layout::FULL .. STAGE_CNT), padded
+// The most stages a ring holds (a launch may ask for fewer: a short product then leaves the rest of the SM's shared memory
+// to the kernels around it).
 constexpr int stages(int wpr, int wb = 8) {
     const int n = (SMEM_LIMIT - plane_bytes(wpr) - tail_bytes()) / (stage_w(wpr, wb) + stage_s(wpr, wb));
     return n > 8 ? 8 : n;
 }
-constexpr int smem_bytes(int wpr, int wb = 8) { return stages(wpr, wb) * (stage_w(wpr, wb) + stage_s(wpr, wb)) + plane_bytes(wpr) + tail_bytes(); }
+constexpr int smem_bytes(int wpr, int wb, int nst) { return nst * (stage_w(wpr, wb) + stage_s(wpr, wb)) + plane_bytes(wpr) + tail_bytes(); }
 
-// Shared-memory carve-up, in this order: weight stages, scale stages, planes (hi, mid, lo words, multipliers),
-// barriers, reduction slots.
+// Shared-memory carve-up, in this order: planes (hi, mid, lo words, multipliers), barriers, reduction slots, stage
+// descriptors, then the ring: per stage its weights and behind them its scales.
 template <int WPR, int WB = 8>
 struct Layout {
-    static constexpr int NST = stages(WPR, WB);
-    static constexpr int W = 0;
-    static constexpr int S = W + NST * stage_w(WPR, WB);
-    static constexpr int HI = S + NST * stage_s(WPR, WB);
+    static constexpr int NST_MAX = stages(WPR, WB);
+    static constexpr int HI = 0;
     static constexpr int MID = HI + WPR * 64 * 32;
     static constexpr int LO = MID + WPR * 64 * 32;
     static constexpr int MUL = LO + WPR * 64 * 32;
@@ -61,6 +67,9 @@ struct Layout {
     static constexpr int SUMS = BESTI + 2 * CONSUMERS * 4;     // float [CONSUMERS][4]
     static constexpr int STAGE_ROW = SUMS + 4 * CONSUMERS * 4;  // uint32 [8]: first row of the stage's rows
     static constexpr int STAGE_CNT = STAGE_ROW + 8 * 4;         // uint32 [8]: how many rows the stage holds; 0 ends the block's work
+    static constexpr int RING = plane_bytes(WPR) + tail_bytes();
+    static constexpr int STAGE = stage_w(WPR, WB) + stage_s(WPR, WB);  // a stage: stage_w bytes of weights, then stage_s of scales
+    static_assert(STAGE_CNT + 8 * 4 <= RING, "the tail outgrew its bytes");
 };
 
 // Four consecutive activations -> one word of each plane.  The eight lanes that share a group of 32 agree on its
@@ -105,7 +114,7 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         // sum, unnormalised output) here, four dimensions per thread, with running-maximum rescaling
         // (crates/tachyon/src/ptx/attend.rs:371-405 does this in the attention kernel's last block).
         static_assert(XMODE != X_ATTN || WPR == 1, "the attention merge is built for 2048 columns");
-        const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
+        const uint32_t G = p.att_heads / p.att_kv, HD = attend_header(G), stride = HD + G * 256;
         const uint32_t head = (uint32_t)t / 64, g = head / G, hh = head % G, d0 = ((uint32_t)t * 4) % 256;
         const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
         uint32_t span = max((n + p.att_splits - 1) / p.att_splits, 16u);  // the split rule of the attention kernel
@@ -126,7 +135,7 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
                 float4 a[8];
 #pragma unroll
                 for (uint32_t k = 0; k < 8; k++)
-                    if (b0 + k < nch) a[k] = ld_cg_f4(base + (size_t)(s0 + b0 + k) * stride + 2 * G + hh * 256 + d0);
+                    if (b0 + k < nch) a[k] = ld_cg_f4(base + (size_t)(s0 + b0 + k) * stride + HD + hh * 256 + d0);
                 if (b0 == 0) {
                     float ml = -INFINITY, ll = 0.0f;
                     if (lane < nch) {
@@ -206,16 +215,17 @@ __device__ __forceinline__ void fetch_planes(const uint8_t* raw, int b, int firs
 
 // The kernel's body.  Rows reach a block in one of two ways.  Static: a contiguous range, balanced to one row (small
 // matrices, where every SM should get some rows).  Dynamic (p.next != nullptr): stages of ROWS rows are handed out by a
-// counter in global memory, the first NST of each block by its index so that its ring fills without waiting for an
-// atomic; blocks that start late or sit far from the memory they read take fewer stages, and nobody waits for a slowest
-// block.  The counter and a second word counting finished blocks are zero between launches (the last block clears them).
+// counter in global memory, the first of each block by its index; blocks that start late or sit far from the memory
+// they read take fewer stages, and nobody waits for a slowest block.  The counter and a second word counting finished blocks are zero between launches (the last block clears them).
 template <int WPR, int XMODE, int EPI, int WB>
 __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status) {
     extern __shared__ __align__(128) uint8_t raw[];
     using L = Layout<WPR, WB>;
-    constexpr int NST = L::NST;
+    const uint32_t NST = p.ring;  // stages of this launch's ring (1 .. L::NST_MAX)
     constexpr int RPW = rows_per_warp(WPR);
     constexpr int ROWS = stage_rows(WPR);
+    constexpr int TEAMS = teams(WPR);
+    constexpr int GPS = CONSUMERS / WPR / TEAMS;  // groups of warps (a group shares a pair of rows) that work on one stage
     constexpr int SW = stage_w(WPR, WB), SS = stage_s(WPR, WB);
     constexpr int GROUP = WB == 8 ? 32 : 64;  // weights per scale
     constexpr int UNIT = (EPI == EPI_GEGLU) ? 2 : 1;  // rows that stay in one block
@@ -234,7 +244,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     volatile uint32_t* stage_cnt = reinterpret_cast<volatile uint32_t*>(raw + L::STAGE_CNT);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], CONSUMERS);
+        for (uint32_t i = 0; i < NST; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], CONSUMERS / TEAMS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -247,8 +257,9 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
             // or as soon as this block knows its last copy (the grid's launch then overlaps the ring's draining).
             bool released = p.early != 0;
             if (released) pdl_launch_dependents();
-            // The stage after the last one carries a count of zero: the consumers stop there.
+            // The stages after the last one (one for each team) carry a count of zero: the consumers stop there.
             uint32_t chunk = blockIdx.x;  // dynamic: the stage's number among all stages of the matrix
+            int ends = 0;
             for (uint32_t i = 0;; i++) {
                 const uint32_t s = i % NST;
                 uint32_t row, here;
@@ -260,11 +271,11 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
                     here = i < nst ? min((uint32_t)ROWS, r1 - row) : 0u;
                 }
                 if (!released && (here == 0 || (!dynamic && i + 1 >= nst))) released = true, pdl_launch_dependents();
-                if (i == (uint32_t)NST) {
+                if (i == NST) {
                     // The ring is full and the first stage is not yet free: what comes after the ring, and the head of the next
                     // large matrix, may as well wait in the L2.
                     for (uint32_t k = 0; k < p.l2_ahead; k++) {
-                        const uint32_t c = dynamic ? ((uint32_t)NST + k) * gridDim.x + blockIdx.x : 0u, far = dynamic ? c * ROWS : r0 + (i + k) * ROWS;
+                        const uint32_t c = dynamic ? (NST + k) * gridDim.x + blockIdx.x : 0u, far = dynamic ? c * ROWS : r0 + (i + k) * ROWS;
                         if (far < (dynamic ? p.rows : r1)) prefetch_rows_l2(p.w, p.s, far, min((uint32_t)ROWS, (dynamic ? p.rows : r1) - far), K * WB / 8, K / GROUP * 2);
                     }
                     prefetch_stages(p.pf, blockIdx.x);
@@ -276,15 +287,18 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
                 stage_row[s] = row, stage_cnt[s] = here;
                 if (here == 0) {
                     mbar_arrive(&full[s]);  // nothing to copy: the phase completes on this arrival alone
-                    break;
+                    if (++ends == TEAMS) break;
+                    continue;
                 }
                 const uint32_t bw = here * (K * WB / 8), bs = here * (K / GROUP * 2);
                 mbar_expect_tx(&full[s], bw + bs);
-                bulk_load(raw + L::W + s * SW, p.w + (size_t)row * (K * WB / 8), bw, &full[s]);
-                bulk_load(raw + L::S + s * SS, p.s + (size_t)row * (K / GROUP), bs, &full[s]);
-                // The next stage's number: by index while the ring fills, from the counter after that.  The atomic is asked
-                // for here and first needed after the wait for a free stage, which hides its trip to the L2.
-                if (dynamic) chunk = i + 1 < (uint32_t)NST ? blockIdx.x + (i + 1) * gridDim.x : (uint32_t)NST * gridDim.x + atomicAdd(p.next, 1u);
+                bulk_load(raw + L::RING + s * L::STAGE, p.w + (size_t)row * (K * WB / 8), bw, &full[s]);
+                bulk_load(raw + L::RING + s * L::STAGE + SW, p.s + (size_t)row * (K / GROUP), bs, &full[s]);
+                // The next stage's number, from the counter (the block's first stage is the one with its own index, so that its
+                // first copy does not wait for an atomic).  Once the ring is full the atomic is asked for here and first needed
+                // after the wait for a free stage, which hides its trip to the L2; a block that starts late finds the counter
+                // far along and takes little.
+                if (dynamic) chunk = gridDim.x + atomicAdd(p.next, 1u);
             }
             if (dynamic && atomicAdd(p.next + 1, 1u) == gridDim.x - 1) p.next[0] = 0u, p.next[1] = 0u;  // every block has taken its last stage
             if (!released) pdl_launch_dependents();
@@ -310,7 +324,8 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     build_planes<WPR, XMODE, WB>(p, raw, threadIdx.x, nw1, nw2);
     named_bar_sync(1, CTHREADS);
     if (stamp) stamp[2] = global_ns();
-    const int seg = warp % WPR, grp = warp / WPR;  // the warp's column segment, and its row group within a stage
+    const int seg = warp % WPR;                          // the warp's column segment
+    const int team = warp / WPR / GPS, grp = warp / WPR % GPS;  // which stages it takes, and its row pair within them
     // Which 16-byte half of its blocks the lane loads first (bank spread); four-bit weights are read in their order.
     const int first = WB == 8 ? (lane >> 2) & 1 : 0;
     Planes pl[2];
@@ -321,7 +336,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
 
     float bestv = -INFINITY;
     uint32_t besti = 0xffffffffu;
-    for (uint32_t i = 0;; i++) {
+    for (uint32_t i = team;; i += TEAMS) {
         const uint32_t s = i % NST;
         const bool ok = mbar_wait(&full[s], (i / NST) & 1);
         if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);  // the producer's copies never landed: treated as the end of the work
@@ -340,15 +355,15 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
             if constexpr (WB == 4) {
                 if (row + j < row_end) {
                     // The lane's two blocks of 32 columns are 16 bytes each: 32 lane and 1024 + 32 lane of the segment.
-                    const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * (K / 2) + seg * (SEG / 2);
-                    const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 64) + seg * 32;
+                    const uint8_t* wr = raw + L::RING + s * L::STAGE + (size_t)(grp * RPW + j) * (K / 2) + seg * (SEG / 2);
+                    const __half* sr = reinterpret_cast<const __half*>(raw + L::RING + s * L::STAGE + SW) + (grp * RPW + j) * (K / 64) + seg * 32;
                     const uint4 w0 = *reinterpret_cast<const uint4*>(wr + lane * 16), w1 = *reinterpret_cast<const uint4*>(wr + 512 + lane * 16);
                     const float s0 = __half2float(sr[lane >> 1]) * pl[0].mul, s1 = __half2float(sr[16 + (lane >> 1)]) * pl[1].mul;
                     v[j] = fmaf(block_dot_q4(w1, pl[1], sx[1]), s1, block_dot_q4(w0, pl[0], sx[0]) * s0);
                 }
             } else if (row + j < row_end) {
-                const uint8_t* wr = raw + L::W + s * SW + (size_t)(grp * RPW + j) * K + seg * SEG;
-                const __half* sr = reinterpret_cast<const __half*>(raw + L::S + s * SS) + (grp * RPW + j) * (K / 32) + seg * 64;
+                const uint8_t* wr = raw + L::RING + s * L::STAGE + (size_t)(grp * RPW + j) * K + seg * SEG;
+                const __half* sr = reinterpret_cast<const __half*>(raw + L::RING + s * L::STAGE + SW) + (grp * RPW + j) * (K / 32) + seg * 64;
                 const uint4 a0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + first) * 16);
                 const uint4 b0 = *reinterpret_cast<const uint4*>(wr + (2 * lane + 1 - first) * 16);
                 const uint4 a1 = *reinterpret_cast<const uint4*>(wr + 1024 + (2 * lane + first) * 16);
@@ -378,9 +393,9 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
         }
         if constexpr (WPR > 1) {
             // The warps of a row pair meet: each leaves its two partial sums, the first of them adds them up in order.
-            float* red = reinterpret_cast<float*>(raw + L::RED) + (i & 1) * CONSUMERS * 2;
+            float* red = reinterpret_cast<float*>(raw + L::RED) + ((i / TEAMS) & 1) * CONSUMERS * 2;
             if ((lane & 15) == 0) red[warp * 2 + (lane >> 4)] = r;
-            if (named_bar_or(2 + grp, WPR * 32, here == 0)) break;
+            if (named_bar_or(2 + warp / WPR, WPR * 32, here == 0)) break;
             if (seg != 0) continue;
             r = 0.0f;
 #pragma unroll
@@ -595,7 +610,7 @@ __global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const Gemv
     } else {
         // X_ATTN: the vector is attention's output, left as one entry (maximum, sum, unnormalised output) per group of
         // att_cluster splits; merge the entries with running-maximum weights (ptx/attend.rs:371-405).
-        const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
+        const uint32_t G = p.att_heads / p.att_kv, HD = attend_header(G), stride = HD + G * 256;
         uint32_t entries = p.att_entries;
         if (entries == 0) {
             const uint32_t pos = ld_cg_u(p.att_pos), n = min(pos + 1, p.att_window);
@@ -617,7 +632,7 @@ __global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const Gemv
                     m[u] = -INFINITY, l[u] = 0.0f, acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     if (e0 + u < entries) {
                         const float* ps = base + (size_t)(e0 + u) * stride;
-                        m[u] = ld_cg_f(ps + hh), l[u] = ld_cg_f(ps + G + hh), acc[u] = ld_cg_f4(ps + 2 * G + hh * 256 + d0);
+                        m[u] = ld_cg_f(ps + hh), l[u] = ld_cg_f(ps + G + hh), acc[u] = ld_cg_f4(ps + HD + hh * 256 + d0);
                     }
                 }
                 const float Mn = fmaxf(fmaxf(M, fmaxf(m[0], m[1])), fmaxf(m[2], m[3]));
@@ -670,6 +685,13 @@ bool small_supports(const GemvParams& p, int sms) {
 }
 
 int launch_small(tb_context* ctx, const GemvParams& p) {
+    static bool configured[16] = {};
+    if (!configured[ctx->gpu & 15]) {  // see launch_staged: the SM's split must leave room for the staged kernel's block
+        TB_CUDA(cudaFuncSetAttribute(gemv_small_kernel<X_NORM>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+        TB_CUDA(cudaFuncSetAttribute(gemv_small_kernel<X_ATTN>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+        TB_CUDA(cudaFuncSetAttribute(gemv_small_kernel<X_F32>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+        configured[ctx->gpu & 15] = true;
+    }
     uint32_t grid = (uint32_t)ctx->sms;
     const uint32_t most = (p.rows + 1) / 2;
     if (grid > most) grid = most;
@@ -683,9 +705,13 @@ int launch_small(tb_context* ctx, const GemvParams& p) {
 template <int WPR, int XMODE, int EPI, int WB = 8>
 int launch_staged(tb_context* ctx, const GemvParams& p) {
     auto kernel = gemv_q8_kernel<WPR, XMODE, EPI, WB>;
+    using L = Layout<WPR, WB>;
     static bool configured[16] = {};  // per device ordinal
     if (!configured[ctx->gpu & 15]) {
-        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(WPR, WB)));
+        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(WPR, WB, L::NST_MAX)));
+        // Whatever a launch's ring needs, the SM is to be split with all it can give to shared memory: a block of another
+        // kernel of the step must be able to move in beside this one, and an SM's split cannot change while blocks run on it.
+        TB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         configured[ctx->gpu & 15] = true;
     }
     constexpr uint32_t ROWS = stage_rows(WPR);
@@ -695,14 +721,18 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     constexpr uint32_t LEAST = UNIT > (uint32_t)rows_per_warp(WPR) ? UNIT : (uint32_t)rows_per_warp(WPR);
     const uint32_t most = (p.rows + LEAST - 1) / LEAST;
     if (grid > most) grid = most > 0 ? most : 1;
-    // Matrices of at least two stages a block hand their stages out through a counter; smaller ones are split evenly.
+    // Matrices of at least two stages a block hand their stages out through a counter; smaller ones are split evenly, and
+    // their ring is only as long as a block's share.
     GemvParams q = p;
+    q.ring = (uint32_t)L::NST_MAX;
     if (ctx->dynamic && (p.rows + ROWS - 1) / ROWS >= 2 * grid) {
         if (q.next == nullptr) q.next = ctx->sched + 2 * (ctx->sched_at++ % 64u);
     } else {
         q.next = nullptr;
+        const uint32_t share = ((p.rows / UNIT + grid - 1) / grid) * UNIT;  // the most rows a block gets
+        q.ring = std::max(1u, std::min((uint32_t)L::NST_MAX, (share + ROWS - 1) / ROWS));
     }
-    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR, WB), true, q, ctx->status));
+    TB_CUDA(launch_kernel(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes(WPR, WB, (int)q.ring), true, q, ctx->status));
     return OK;
 }
 
@@ -745,7 +775,9 @@ int dispatch_staged(tb_context* ctx, const GemvParams& p) {
 
 }  // namespace
 
-size_t gemv_smem_bytes() { return smem_bytes(1); }
+size_t gemv_smem_bytes() { return smem_bytes(1, 8, stages(1)); }
+
+uint32_t gemv_stage_rows(uint32_t cols) { return cols == 2048 ? stage_rows(1) : cols == 4096 ? stage_rows(2) : cols == 8192 ? stage_rows(4) : cols == 16384 ? stage_rows(8) : 0; }
 
 int launch_gemv(tb_context* ctx, const GemvParams& p) {
     if (p.rows == 0 || p.cols == 0 || p.cols % 32 != 0) return fail(OUT_OF_RANGE, "gemv: cols must be a positive multiple of 32");

@@ -110,6 +110,7 @@ struct GemvParams {
     // != 0: the product is short and the next kernel in the stream should start as early as possible: run it as the
     // small-footprint kernel (no ring, weights in registers, dependents released at once) when its shape allows.
     uint32_t lean = 0;
+    uint32_t ring = 0;            // stages of the shared-memory ring (set by launch_gemv)
     uint32_t early = 0;           // != 0: release the kernel behind this one at once (it waits for this one before it reads anything of it)
     uint32_t l2_ahead = 0;        // stages past the ring to ask the L2 for once the ring is full
     // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for
@@ -126,6 +127,7 @@ struct GemvParams {
 
 int launch_gemv(tb_context* ctx, const GemvParams& p);
 size_t gemv_smem_bytes();
+uint32_t gemv_stage_rows(uint32_t cols);  // rows of a stage of launch_gemv's staged kernel at this width (0: no staged kernel)
 
 // ---- decode attention ----------------------------------------------------------------------------------------
 struct AttendParams {
@@ -155,6 +157,9 @@ struct AttendParams {
                                    // thread-block cluster and merge their results in distributed shared memory, leaving one entry of
                                    // `partial` per cluster (entry c of a key-value head = its splits c * cluster ...)
 };
+// An entry of `partial`: the maxima and the sums of the group's query heads, padded to whole 16-byte units so that the
+// outputs behind them can be fetched four at a time, then group * 256 unnormalised outputs.
+__host__ __device__ constexpr uint32_t attend_header(uint32_t group) { return (2 * group + 3) & ~3u; }
 int launch_attend(tb_context* ctx, const AttendParams& p);
 size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits);
 int launch_attend_512(tb_context* ctx, const AttendParams& p);  // heads of 512; up to 8 query heads per key-value head (attend512.cu)

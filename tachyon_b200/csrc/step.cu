@@ -106,7 +106,7 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         // sum, unnormalised output) here, four dimensions per thread, with running-maximum rescaling
         // (crates/tachyon/src/ptx/attend.rs:371-405 does this in the attention kernel's last block).
         static_assert(WPR == 1, "the attention merge is built for 2048 columns");
-        const uint32_t G = p.att_heads / p.att_kv, stride = 2 * G + G * 256;
+        const uint32_t G = p.att_heads / p.att_kv, HD = attend_header(G), stride = HD + G * 256;
         const uint32_t head = (uint32_t)t / 64, g = head / G, hh = head % G, d0 = ((uint32_t)t * 4) % 256;
         const uint32_t n = min(pos + 1, p.att_window);  // the step's position, read once at the kernel's start
         const uint32_t span = attend::split_span(n, p.att_splits), used = (n + span - 1) / span;
@@ -117,7 +117,7 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         for (uint32_t s2 = 0; s2 < used; s2++) {
             const float* ps = base + (size_t)s2 * stride;
             const float m = ld_cg_f(ps + hh), l = ld_cg_f(ps + G + hh);
-            const float4 a = ld_cg_f4(ps + 2 * G + hh * 256 + d0);
+            const float4 a = ld_cg_f4(ps + HD + hh * 256 + d0);
             const float Mn = fmaxf(M, m), c = exp2f(M - Mn), w = exp2f(m - Mn);
             L = fmaf(L, c, w * l);
             o.x = fmaf(o.x, c, w * a.x), o.y = fmaf(o.y, c, w * a.y), o.z = fmaf(o.z, c, w * a.z), o.w = fmaf(o.w, c, w * a.w);
