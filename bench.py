@@ -354,15 +354,24 @@ def bench_gemv(args, ranks: Ranks):
     ctx = tb.Context(ranks.local)
     rows, cols, copies = args.rows, args.cols, args.copies
     lib = ctx.lib
-    w, s = ctx.alloc(copies * rows * cols), ctx.alloc(copies * rows * (cols // 32) * 2)
-    tb.check(lib.tb_fill_codes(ctx.handle, 3, 1, w.ptr, copies * rows * cols))
-    tb.check(lib.tb_fill_scales(ctx.handle, 3, 2, s.ptr, copies * rows * (cols // 32), 0.02 / 127))
+    f16w = args.weights == "f16"
+    if f16w:
+        copies = min(copies, 32)  # 67 MB a copy
+        w = ctx.alloc(copies * rows * cols * 2)
+        tb.check(lib.tb_fill_gauss_f16(ctx.handle, 3, 1, w.ptr, copies * rows * cols, 0.02))
+    else:
+        w, s = ctx.alloc(copies * rows * cols), ctx.alloc(copies * rows * (cols // 32) * 2)
+        tb.check(lib.tb_fill_codes(ctx.handle, 3, 1, w.ptr, copies * rows * cols))
+        tb.check(lib.tb_fill_scales(ctx.handle, 3, 2, s.ptr, copies * rows * (cols // 32), 0.02 / 127))
     x = ctx.upload(np.random.default_rng(0).standard_normal(cols).astype(np.float16))
     y = ctx.zeros(rows * 2)
 
     def launch(i):
-        tb.check(lib.tb_gemv_q8(ctx.handle, C.c_void_p(w.ptr + (i % copies) * rows * cols), C.c_void_p(s.ptr + (i % copies) * rows * (cols // 32) * 2), x.ptr,
-                                tb.F16, y.ptr, tb.F16, rows, cols))
+        if f16w:
+            tb.check(lib.tb_gemv_f16(ctx.handle, C.c_void_p(w.ptr + (i % copies) * rows * cols * 2), x.ptr, tb.F16, y.ptr, tb.F16, rows, cols))
+        else:
+            tb.check(lib.tb_gemv_q8(ctx.handle, C.c_void_p(w.ptr + (i % copies) * rows * cols), C.c_void_p(s.ptr + (i % copies) * rows * (cols // 32) * 2), x.ptr,
+                                    tb.F16, y.ptr, tb.F16, rows, cols))
 
     for i in range(args.warmup):
         launch(i)
@@ -374,11 +383,11 @@ def bench_gemv(args, ranks: Ranks):
     e1.record()
     e1.sync()
     us = e0.elapsed_ms(e1) * 1e3 / args.steps
-    alg = rows * cols + rows * (cols // 32) * 2 + cols * 2 + rows * 2
+    alg = (rows * cols * 2 if f16w else rows * cols + rows * (cols // 32) * 2) + cols * 2 + rows * 2
     peak, how = measured_peak_gbs()
-    return {"metric": "gemv_q8_gbs", "value": alg / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
-            "higher_is_better": True, "dtype": "int8 x f16 -> f16, f32 accumulate", "data": "synthetic", "impl": "ours",
-            "config": {"workload": f"configs[0]: Q8 GEMV {rows}x{cols}, {copies} weight copies cycled"}, "gpu_launches": args.steps,
+    return {"metric": "gemv_f16_gbs" if f16w else "gemv_q8_gbs", "value": alg / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": us / 1e3, "higher_is_better": True, "dtype": ("f16" if f16w else "int8") + " x f16 -> f16, f32 accumulate", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[0]: {'f16' if f16w else 'Q8'} GEMV {rows}x{cols}, {copies} weight copies cycled"}, "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak, "unit": "GB/s", "frac": alg / us / 1e3 / peak, "frac_of_8tbs": alg / us / 1e3 / HBM_SPEC_GBS,
                          "peak_source": how, "traffic": None, "bytes_per_launch": alg, "us_per_launch": us}}
 
@@ -675,7 +684,7 @@ def main():
     ap.add_argument("--copies", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="decode workload: skip the prefill / encoder / single-kernel sub-objects")
-    ap.add_argument("--weights", default="q8", choices=["q8", "q4"], help="decode workload: the benchmark's Q8 matrices, or the reference's converted Q4 format")
+    ap.add_argument("--weights", default="q8", choices=["q8", "q4", "f16"], help="gemv workload: Q8 or f16 weights; decode and prefill workloads: the benchmark's Q8 matrices, or the reference's converted Q4 format")
     ap.add_argument("--fused", action="store_true", help="decode with the single persistent step kernel instead of one launch per phase")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

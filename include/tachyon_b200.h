@@ -104,6 +104,16 @@ enum { TB_F32 = 0, TB_F16 = 1 };
 TB_API int tb_gemv_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols);
 
 /*
+ * The same product with f16 weights: w device f16 [rows, cols] row-major, x and y as in tb_gemv_q8, f32 accumulation.
+ * The reference keeps f16 weights for models too small for 8-bit codes to pay (gemm_f16, crates/tachyon/src/ptx/
+ * encoder.rs:498-525, chosen by encoder/convert.rs:26-29); this is that product for one token.  cols: a multiple of 256,
+ * at most 16384.  tb_gemv_f16_norm puts the residual / RMS-norm step of tb_gemv_q8_norm in front (any such cols).
+ */
+TB_API int tb_gemv_f16(tb_context* ctx, const uint16_t* w, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols);
+TB_API int tb_gemv_f16_norm(tb_context* ctx, const uint16_t* w, const float* h, const float* y_res, const float* w1, const float* w2, float eps, float hscale,
+                            float* h_out, void* y, int y_dtype, uint32_t rows, uint32_t cols);
+
+/*
  * The residual / RMS-norm step fused in front of the product: h' = (h + w1 * rmsnorm(y_res)) * hscale (y_res NULL:
  * h' = h), x = w2 * rmsnorm(h') (w2 NULL: x = h'), y = W x; h_out (may be NULL) receives h'.  cols must be 2048.
  * Stands in for norm_q8 followed by gemv_q4 (ptx/mod.rs:24-30, 404-511).  `geglu` != 0: rows are (gate_j, up_j) pairs

@@ -175,6 +175,15 @@ def gemv_q8(w: np.ndarray, scales: np.ndarray, x: np.ndarray):
     return y, e, b
 
 
+def gemv_f16(w_bits: np.ndarray, x: np.ndarray):
+    """(f64 y, bound) for f16 weights given as their bits [rows, cols] and an f32 vector: the product the reference's gemm_f16
+    computes for one token (crates/tachyon/src/ptx/encoder.rs:157-203), restated as a plain f64 sum; bound is the sum of the
+    terms' magnitudes, the measure the reference's tolerance is stated in (tests/common/mod.rs:95-112)."""
+    w = np.ascontiguousarray(w_bits, np.uint16).view(np.float16).astype(np.float64)
+    x = np.asarray(x, np.float32).astype(np.float64)
+    return w @ x, np.abs(w) @ np.abs(x)
+
+
 def rope_freq(theta: float, d: int, fraction: float) -> np.ndarray:
     f = np.zeros(d // 2, np.float32)
     lib().tbo_rope_freq(theta, d, fraction, ptr(f))

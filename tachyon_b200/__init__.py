@@ -121,6 +121,14 @@ class Context:
     def gemv_q8(self, w: DevBuf, s: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, y_dtype: int, rows: int, cols: int) -> None:
         check(self.lib.tb_gemv_q8(self.handle, w.ptr, s.ptr, x.ptr, x_dtype, y.ptr, y_dtype, rows, cols))
 
+    def gemv_f16(self, w: DevBuf, x: DevBuf, x_dtype: int, y: DevBuf, y_dtype: int, rows: int, cols: int) -> None:
+        """tb_gemv_f16: f16 weights [rows, cols] times an f16/f32 vector, f32 accumulation."""
+        check(self.lib.tb_gemv_f16(self.handle, w.ptr, x.ptr, x_dtype, y.ptr, y_dtype, rows, cols))
+
+    def gemv_f16_norm(self, w, h, y_res, w1, w2, eps, hscale, h_out, y, y_dtype, rows, cols) -> None:
+        p = lambda b: None if b is None else b.ptr
+        check(self.lib.tb_gemv_f16_norm(self.handle, w.ptr, h.ptr, p(y_res), p(w1), p(w2), eps, hscale, p(h_out), y.ptr, y_dtype, rows, cols))
+
     def quant_q8(self, x: DevBuf, n: int, q: DevBuf, pairs: DevBuf) -> None:
         """tb_quant_q8 (the reference's quant_q8): f32 x [n] -> i8 codes [n] and f32 pairs [n / 32][2]."""
         check(self.lib.tb_quant_q8(self.handle, x.ptr, n, q.ptr, pairs.ptr))

@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-PATH = os.path.join(HERE, "_native", "libtachyon_b200.so")
+# TACHYON_B200_LIBRARY names another build of the same library (a developer comparing two builds in one process tree).
+PATH = os.environ.get("TACHYON_B200_LIBRARY") or os.path.join(HERE, "_native", "libtachyon_b200.so")
 
 u32, u64, i32, f32, vp, sz, cp = C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_char_p
 pp = C.POINTER(C.c_void_p)
@@ -77,6 +78,8 @@ SIGNATURES = {
     "tb_launch": (i32, [vp, cp, vp, vp, u32, vp, sz]),
     "tb_gemv_q4x": (i32, [vp, vp, vp, vp, i32, vp, u32, u32]),
     "tb_sample": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, vp, u32]),
+    "tb_gemv_f16": (i32, [vp, vp, vp, i32, vp, i32, u32, u32]),
+    "tb_gemv_f16_norm": (i32, [vp, vp, vp, vp, vp, vp, f32, f32, vp, vp, i32, u32, u32]),
     "tb_gemv_q8_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, f32, f32, vp, vp, u32, u32, i32]),
     "tb_gemv_q8_argmax": (i32, [vp, vp, vp, vp, i32, vp, u32, u32, vp, vp, vp]),
     "tb_gemm_q8": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),

@@ -72,7 +72,7 @@ int tb_context_new(int gpu, tb_context** out) {
     env = getenv("TACHYON_B200_LEAN_QKV");
     ctx->lean_qkv = env != nullptr && env[0] == '1';
     env = getenv("TACHYON_B200_L2_AHEAD");
-    ctx->l2_ahead = env != nullptr ? (uint32_t)atoi(env) : 0u;
+    ctx->l2_ahead = env != nullptr ? (uint32_t)atoi(env) : 1u;  // one stage a block: measured 1 % of a decode step; two and more bring nothing
     env = getenv("TACHYON_B200_L2_NEXT");
     ctx->l2_next = env != nullptr ? (uint32_t)atoi(env) : 0u;
     env = getenv("TACHYON_B200_NO_CLUSTER");
@@ -396,6 +396,27 @@ int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, co
     p.xmode = X_NORM, p.h = h, p.yres = y_res, p.w1 = w1, p.w2 = w2, p.eps = eps, p.hscale = hscale, p.h_out = h_out;
     p.epi = geglu ? EPI_GEGLU : EPI_F32, p.y = y;
     return launch_gemv(ctx, p);
+}
+
+int tb_gemv_f16(tb_context* ctx, const uint16_t* w, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols) {
+    if (!ctx) return fail(OUT_OF_RANGE, "tb_gemv_f16: null context");
+    if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return fail(OUT_OF_RANGE, "tb_gemv_f16: unknown dtype");
+    GemvF16Params p;
+    p.w = reinterpret_cast<const __half*>(w), p.rows = rows, p.cols = cols;
+    p.xmode = x_dtype == TB_F16 ? X_F16 : X_F32, p.x = x;
+    p.epi = y_dtype == TB_F16 ? EPI_F16 : EPI_F32, p.y = y;
+    return launch_gemv_f16(ctx, p);
+}
+
+int tb_gemv_f16_norm(tb_context* ctx, const uint16_t* w, const float* h, const float* y_res, const float* w1, const float* w2, float eps, float hscale,
+                     float* h_out, void* y, int y_dtype, uint32_t rows, uint32_t cols) {
+    if (!ctx) return fail(OUT_OF_RANGE, "tb_gemv_f16_norm: null context");
+    if (!dtype_ok(y_dtype)) return fail(OUT_OF_RANGE, "tb_gemv_f16_norm: unknown dtype");
+    GemvF16Params p;
+    p.w = reinterpret_cast<const __half*>(w), p.rows = rows, p.cols = cols;
+    p.xmode = X_NORM, p.h = h, p.yres = y_res, p.w1 = w1, p.w2 = w2, p.eps = eps, p.hscale = hscale, p.h_out = h_out;
+    p.epi = y_dtype == TB_F16 ? EPI_F16 : EPI_F32, p.y = y;
+    return launch_gemv_f16(ctx, p);
 }
 
 int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* scales, const void* x, int x_dtype, float* logits, uint32_t rows, uint32_t cols,

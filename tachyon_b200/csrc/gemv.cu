@@ -253,8 +253,10 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     if (warp == CONSUMERS) {
         // Producer: one thread streams this block's rows.  Nothing it reads is written by another kernel.
         if (lane == 0) {
-            // The kernel behind this one is released at once (p.early: all it does before its own wait is to fetch constants)
-            // or as soon as this block knows its last copy (the grid's launch then overlaps the ring's draining).
+            // This thread's release of the kernel behind this one (at once with p.early, else when the block's last copy is
+            // known).  A block counts as having released its dependents once ALL of its threads have said so or have left, so
+            // with the consumers silent this only ever matters at the block's end; measured on B200, consumers that also say so
+            // at their start let the next kernels move in early but the step as a whole got no faster.
             bool released = p.early != 0;
             if (released) pdl_launch_dependents();
             // The stages after the last one (one for each team) carry a count of zero: the consumers stop there.
@@ -373,7 +375,8 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
             }
         }
         __syncwarp();
-        if (lane == 0 && here != 0) mbar_arrive(&empty[s]);
+        // Released also when it was an end marker: with a short ring the producer needs the stage again for the next team's.
+        if (lane == 0 && ok) mbar_arrive(&empty[s]);
         float r;           // row total: in lane 0 (and, with two rows, the second row's in lane 16)
         uint32_t out_row;  // the row this lane would write
         if constexpr (RPW == 2) {

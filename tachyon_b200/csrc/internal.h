@@ -22,7 +22,7 @@ struct tb_context {
     bool early_trigger = true;        // kernels of a decode step release the kernel behind them as they start (TACHYON_B200_LATE_TRIGGER=1: when
                                       // their last copy is issued)
     bool lean_qkv = false;            // the query/key/value product also runs as the small kernel (TACHYON_B200_LEAN_QKV=1)
-    uint32_t l2_ahead = 0;            // stages beyond its ring a large product asks the L2 for once the ring is full (TACHYON_B200_L2_AHEAD)
+    uint32_t l2_ahead = 1;            // stages beyond its ring a large product asks the L2 for once the ring is full (TACHYON_B200_L2_AHEAD)
     uint32_t l2_next = 0;             // first stages of the next large product a block asks the L2 for at that point (TACHYON_B200_L2_NEXT)
     bool cluster = true;              // decode attention merges neighbouring splits in thread-block clusters (TACHYON_B200_NO_CLUSTER=1: never)
     uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
@@ -128,6 +128,23 @@ struct GemvParams {
 int launch_gemv(tb_context* ctx, const GemvParams& p);
 size_t gemv_smem_bytes();
 uint32_t gemv_stage_rows(uint32_t cols);  // rows of a stage of launch_gemv's staged kernel at this width (0: no staged kernel)
+
+// The same product with f16 weights [rows, cols] (gemv_f16.cu): prologues X_F16, X_F32, X_NORM; outputs EPI_F32, EPI_F16.
+struct GemvF16Params {
+    const __half* w = nullptr;
+    uint32_t rows = 0, cols = 0;
+    int xmode = X_F16;
+    const void* x = nullptr;
+    const float* h = nullptr;
+    const float* yres = nullptr;
+    const float* w1 = nullptr;
+    const float* w2 = nullptr;
+    float eps = 1e-6f, hscale = 1.0f;
+    float* h_out = nullptr;
+    int epi = EPI_F32;
+    void* y = nullptr;
+};
+int launch_gemv_f16(tb_context* ctx, const GemvF16Params& p);
 
 // ---- decode attention ----------------------------------------------------------------------------------------
 struct AttendParams {

@@ -189,3 +189,59 @@ def test_stages_handed_out_by_a_counter_give_the_same_bits(ctx, rows, cols):
     _, exact, bound = oracle.gemv_q8(w, s, x)
     assert np.all(np.abs(static.astype(np.float64) - exact) <= 1e-5 * bound + 1e-6)
     assert ctx.status() == 0
+
+
+# ---- f16 weights -------------------------------------------------------------------------------------------------------
+
+F16_SHAPES = [(16384, 2048), (512, 2048), (37, 2048), (5, 2048), (1, 2048), (3072, 2048), (300, 4096), (64, 8192), (2048, 16384), (37, 16384), (512, 2560),
+              (256, 10240), (2560, 256), (36, 768)]
+
+
+@pytest.mark.parametrize("rows,cols", F16_SHAPES)
+def test_gemv_f16_matches_the_oracle_on_every_shape(ctx, rows, cols):
+    """tb_gemv_f16 on the shapes of tests/gemv.rs:16 (whole and ragged row counts, the benchmark's 16384 x 2048) against the
+    f64 product: 1e-5 of the terms' magnitudes for f32 accumulation (tests/gemv.rs:61-67), plus an f16 rounding for f16 out."""
+    rng = np.random.default_rng(rows + cols)
+    w = f16(rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.02))
+    x = rng.standard_normal(cols).astype(np.float32)
+    wd, y = ctx.upload(w), ctx.zeros((rows + 2) * 4)
+    for x_dtype, xv in ((tb.F32, x), (tb.F16, f16_to_f32(f16(x)))):
+        want, bound = oracle.gemv_f16(w, xv)
+        xd = ctx.upload(f16(x) if x_dtype == tb.F16 else x)
+        y.upload(np.full(rows + 2, 777.0, np.float32))
+        ctx.gemv_f16(wd, xd, x_dtype, y, tb.F32, rows, cols)
+        got = y.download(np.float32, rows + 2)
+        assert np.all(got[rows:] == 777.0), "rows past the matrix were written"
+        assert np.all(np.abs(got[:rows] - want) <= 1e-5 * bound + 1e-6), float(np.abs(got[:rows] - want).max())
+        ctx.gemv_f16(wd, xd, x_dtype, y, tb.F16, rows, cols)
+        got16 = f16_to_f32(y.download(np.uint16, rows))
+        assert np.all(np.abs(got16 - want) <= 2.0**-10 * np.abs(want) + 1e-5 * bound + 1e-6)
+    assert ctx.status() == 0
+
+
+def test_gemv_f16_with_the_norm_prologue(ctx):
+    rows, cols = 333, 2048
+    rng = np.random.default_rng(3)
+    w = f16(rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.02))
+    h, y, w1, w2 = (20 * rng.uniform(-1, 1, cols)).astype(np.float32), (300 * rng.uniform(-1, 1, cols)).astype(np.float32), (1 + rng.uniform(-1, 1, cols)).astype(
+        np.float32), (0.5 + rng.uniform(-1, 1, cols)).astype(np.float32)
+    bufs = [ctx.upload(a) for a in (w, h, y, w1, w2)]
+    for yres, scale in ((y, 0.75), (None, 1.0)):
+        h_want, x_want = oracle.norm_step(h, yres, w1 if yres is not None else None, w2, 1e-6, scale)
+        wf = w.view(np.float16).astype(np.float64)
+        want, bound = wf @ x_want, np.abs(wf) @ np.abs(x_want)
+        hout, yout = ctx.zeros(cols * 4), ctx.zeros(rows * 4)
+        ctx.gemv_f16_norm(bufs[0], bufs[1], bufs[2] if yres is not None else None, bufs[3] if yres is not None else None, bufs[4], 1e-6, scale, hout, yout, tb.F32,
+                          rows, cols)
+        assert np.all(np.abs(hout.download(np.float32, cols) - h_want) <= 1e-5 * np.maximum(np.abs(h_want), 1.0))
+        got = yout.download(np.float32, rows)
+        assert np.all(np.abs(got - want) <= 2e-5 * bound + 1e-5), float(np.abs(got - want).max())
+
+
+def test_gemv_f16_rejects_bad_descriptors(ctx):
+    z = ctx.zeros(4096)
+    with pytest.raises(tb.Error) as e:
+        ctx.gemv_f16(z, z, tb.F32, z, tb.F32, 4, 100)  # cols not a multiple of 256
+    assert e.value.status == 3
+    with pytest.raises(tb.Error):
+        ctx.gemv_f16(z, z, tb.F32, z, tb.F32, 4, 32768)  # wider than the kernel's shared-memory vector
