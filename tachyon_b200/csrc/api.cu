@@ -287,6 +287,32 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         return launch_norm_q8(ctx, static_cast<const float*>(ptr(0)), static_cast<float*>(ptr(1)), static_cast<const float*>(ptr(2)), static_cast<const float*>(ptr(3)),
                               static_cast<const float*>(ptr(4)), static_cast<int8_t*>(ptr(5)), static_cast<float*>(ptr(6)), u32(7), grid[1], f32(8), f32(9));
     }
+    if (name == "quant_q8p") {  // x, q, s, len (ptx/mod.rs:253-287); grid len / 256 (rounded up) blocks of 256
+        TB_TRY(shape(4, 256));
+        return launch_quant_q8p(ctx, static_cast<const float*>(ptr(0)), static_cast<int8_t*>(ptr(1)), static_cast<float*>(ptr(2)), u32(3));
+    }
+    if (name == "geglu_q8p") {  // a, b, q, s, len, width, sa, sb, so: value i is row i / width, read at strides sa, sb, stored at stride so
+        TB_TRY(shape(9, 256));
+        return launch_geglu_q8p(ctx, static_cast<const float*>(ptr(0)), static_cast<const float*>(ptr(1)), static_cast<int8_t*>(ptr(2)), static_cast<float*>(ptr(3)),
+                                u32(4), u32(5), u32(6), u32(7), u32(8));
+    }
+    if (name == "norm_q8p") {  // norm_q8's arguments; grid (len / 256, tokens)
+        TB_TRY(shape(10, 256));
+        if (grid[0] != u32(7) / 256) return fail(OUT_OF_RANGE, "tb_launch: norm_q8p runs len / 256 blocks per token");
+        return launch_norm_q8p(ctx, static_cast<const float*>(ptr(0)), static_cast<float*>(ptr(1)), static_cast<const float*>(ptr(2)), static_cast<const float*>(ptr(3)),
+                               static_cast<const float*>(ptr(4)), static_cast<int8_t*>(ptr(5)), static_cast<float*>(ptr(6)), u32(7), grid[1], f32(8), f32(9));
+    }
+    if (name == "gemm_q4") {
+        // ptx/gemm.rs:18-23: w, ws, q, s (Q8P), y, rows, cols, tokens; grid (tokens / 128 rounded up, rows / 64, slices).  Only the
+        // number of slices is taken from the grid: this build tiles the tokens and rows its own way.
+        if (nargs != 8) return fail(OUT_OF_RANGE, "tb_launch: gemm_q4 takes 8 arguments");
+        return launch_gemm_q4_ref(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const int8_t*>(ptr(2)),
+                                  static_cast<const float*>(ptr(3)), static_cast<float*>(ptr(4)), u32(5), u32(6), u32(7), grid[2]);
+    }
+    if (name == "sum_slices") {  // y, len, slices (ptx/gemm.rs:31-34)
+        TB_TRY(shape(3, 256));
+        return launch_sum_slices(ctx, static_cast<float*>(ptr(0)), u32(1), u32(2));
+    }
     if (name == "embed_q4") {  // packed, scales, token, out, cols, scale; grid (cols / 256, rows)
         TB_TRY(shape(6, 256));
         return launch_embed_q4_rows(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const uint32_t*>(ptr(2)), grid[1],

@@ -256,6 +256,15 @@ int launch_norm_q8(tb_context* ctx, const float* h, float* h_out, const float* y
 int launch_embed_q4_rows(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const uint32_t* tokens, uint32_t rows, float* out, uint32_t cols, float scale);
 int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols);
 
+// The reference's prefill formats by its kernel names (q8p.cu): Q8P quantisers, the Q4 x Q8P product in column slices.
+int launch_quant_q8p(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t len);
+int launch_geglu_q8p(tb_context* ctx, const float* a, const float* b, int8_t* q, float* s, uint32_t len, uint32_t width, uint32_t sa, uint32_t sb, uint32_t so);
+int launch_norm_q8p(tb_context* ctx, const float* h, float* h_out, const float* y, const float* w1, const float* w2, int8_t* q, float* s, uint32_t len,
+                    uint32_t tokens, float eps, float scale);
+int launch_gemm_q4_ref(tb_context* ctx, const uint8_t* w, const uint16_t* ws, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols,
+                       uint32_t tokens, uint32_t slices);
+int launch_sum_slices(tb_context* ctx, float* y, uint32_t len, uint32_t slices);
+
 // The reference's sampler with draws (sample.cu); cfg: 40 bytes of device memory in the reference's Sampling layout.
 int launch_sample_draw(tb_context* ctx, const float* logits, float* work, uint32_t vocab, const void* cfg, uint32_t* state, uint32_t* seen, uint32_t* out,
                        float* partial, uint32_t* count, uint32_t blocks, uint32_t* trace = nullptr, uint32_t trace_mask = 0);
