@@ -52,6 +52,11 @@ TB_API const char* tb_last_error(void);
 /* Context::new (cuda/mod.rs:177-187): binds GPU `gpu`, requires compute capability 10.x, creates the stream. */
 TB_API int tb_context_new(int gpu, tb_context** out);
 TB_API void tb_context_free(tb_context* ctx);
+/* cuda::devices() (crates/tachyon/src/cuda/mod.rs): how many GPUs the driver offers.  This call and tb_context_new load the
+ * driver the way the reference does (cuda/driver.rs:138-167): the library named by $TACHYON_LIBCUDA when that is set, else
+ * libcuda.so.1 (then the WSL path); once per process.  TB_NO_DRIVER with the reference's message when it is not found,
+ * lacks cuDriverGetVersion / cuGetProcAddress_v2, or supports less than CUDA 12.0 (the reference's DriverTooOld). */
+TB_API int tb_devices(int* count);
 /* Context::info().sms */
 TB_API int tb_context_sms(const tb_context* ctx);
 /* Turns programmatic dependent launch on (default) or off for kernels launched after the call. */
@@ -71,6 +76,16 @@ TB_API int tb_context_set_lean(tb_context* ctx, int mode);
 TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
 TB_API int tb_status(tb_context* ctx, uint32_t* word);
+/* Clears that word (after an error has been looked at). */
+TB_API int tb_status_clear(tb_context* ctx);
+/*
+ * Self-test of the bounded waits, for a deployment that wants to see the failure path work before it relies on it: one
+ * block of the matrix-vector kernel whose producer is told to copy nothing, so its consumers' wait runs out after limit_ns
+ * (at most 100 ms).  The kernel returns normally; afterwards tb_status reports TB_DEVICE_WAIT with word 1 (a wait for a full
+ * stage), and the context keeps working once tb_status_clear has run.  Nothing traps, faults or waits without a limit.
+ * The reference's last-block counters never wait (crates/tachyon/src/ptx/attend.rs:334-367), so it has no counterpart.
+ */
+TB_API int tb_selftest_wait(tb_context* ctx, uint64_t limit_ns);
 
 /* Context::alloc / DevBuf drop (cuda/mod.rs:292-298, 337-375). */
 TB_API int tb_alloc(tb_context* ctx, size_t bytes, void** dev);

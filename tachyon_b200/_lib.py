@@ -51,11 +51,14 @@ SIGNATURES = {
     "tb_context_new": (i32, [i32, pp]),
     "tb_context_free": (None, [vp]),
     "tb_context_sms": (i32, [vp]),
+    "tb_devices": (i32, [C.POINTER(i32)]),
     "tb_context_set_overlap": (i32, [vp, i32]),
     "tb_context_set_gemm_schedule": (i32, [vp, i32]),
     "tb_context_set_lean": (i32, [vp, i32]),
     "tb_context_set_dynamic": (i32, [vp, i32]),
     "tb_status": (i32, [vp, C.POINTER(u32)]),
+    "tb_status_clear": (i32, [vp]),
+    "tb_selftest_wait": (i32, [vp, u64]),
     "tb_alloc": (i32, [vp, sz, pp]),
     "tb_free": (i32, [vp, vp]),
     "tb_alloc_host": (i32, [vp, sz, pp]),

@@ -5,6 +5,9 @@
 #include "common.cuh"
 #include "internal.h"
 
+#include <dlfcn.h>
+
+#include <mutex>
 #include <string>
 
 namespace tb {
@@ -24,6 +27,40 @@ int cuda_fail(cudaError_t e, const char* where) {
     return fail(status, std::string(where) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }
 
+// The driver seam (crates/tachyon/src/cuda/driver.rs:138-167): the driver library is looked for at $TACHYON_LIBCUDA when that
+// is set, else under its usual names; it must export cuDriverGetVersion and cuGetProcAddress_v2 and support CUDA 12.0.  The
+// outcome is kept for the life of the process, as the reference keeps it.  The statically linked CUDA runtime then finds the
+// same library (already loaded under its name); all this layer adds is the reference's search order and its clean errors.
+static int driver_probe() {
+    static std::once_flag once;
+    static int outcome = OK;
+    static std::string message;
+    std::call_once(once, [] {
+        const char* custom = getenv("TACHYON_LIBCUDA");
+        const char* search[] = {"libcuda.so.1", "/usr/lib/wsl/lib/libcuda.so.1"};
+        void* lib = nullptr;
+        if (custom != nullptr && custom[0] != 0) {
+            lib = dlopen(custom, RTLD_NOW | RTLD_GLOBAL);
+        } else {
+            for (const char* p : search)
+                if ((lib = dlopen(p, RTLD_NOW | RTLD_GLOBAL)) != nullptr) break;
+        }
+        if (lib == nullptr || dlsym(lib, "cuDriverGetVersion") == nullptr) {
+            outcome = NO_DRIVER;
+            message = "the NVIDIA driver (libcuda.so.1) was not found; install it or set TACHYON_LIBCUDA to its path";  // error.rs:58
+            return;
+        }
+        int version = 0;
+        reinterpret_cast<int (*)(int*)>(dlsym(lib, "cuDriverGetVersion"))(&version);
+        if (version < 12000 || dlsym(lib, "cuGetProcAddress_v2") == nullptr) {
+            outcome = NO_DRIVER;
+            message = "the NVIDIA driver supports CUDA " + std::to_string(version / 1000) + "." + std::to_string(version % 1000 / 10) +
+                      "; tachyon needs 12.0 or newer (driver R525+)";  // error.rs:59 (Error::DriverTooOld)
+        }
+    });
+    return outcome == OK ? OK : fail(outcome, message);
+}
+
 }  // namespace tb
 
 using namespace tb;
@@ -36,9 +73,18 @@ extern "C" {
 
 const char* tb_last_error(void) { return g_error.c_str(); }
 
+int tb_devices(int* count) {
+    if (count == nullptr) return fail(OUT_OF_RANGE, "tb_devices: null count");
+    *count = 0;
+    TB_TRY(driver_probe());
+    TB_CUDA(cudaGetDeviceCount(count));
+    return OK;
+}
+
 int tb_context_new(int gpu, tb_context** out) {
     if (out == nullptr) return fail(OUT_OF_RANGE, "tb_context_new: null out");
     *out = nullptr;
+    TB_TRY(driver_probe());
     int count = 0;
     TB_CUDA(cudaGetDeviceCount(&count));
     if (gpu < 0 || gpu >= count) return fail(OUT_OF_RANGE, "tb_context_new: no such GPU");
@@ -422,6 +468,36 @@ int tb_gemv_q8_norm(tb_context* ctx, const int8_t* w, const uint16_t* scales, co
     p.xmode = X_NORM, p.h = h, p.yres = y_res, p.w1 = w1, p.w2 = w2, p.eps = eps, p.hscale = hscale, p.h_out = h_out;
     p.epi = geglu ? EPI_GEGLU : EPI_F32, p.y = y;
     return launch_gemv(ctx, p);
+}
+
+int tb_selftest_wait(tb_context* ctx, uint64_t limit_ns) {
+    if (!ctx) return fail(OUT_OF_RANGE, "tb_selftest_wait: null context");
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail(OUT_OF_RANGE, "tb_selftest_wait: a limit between 1 ns and 100 ms");
+    // Two rows of 2048 columns: one block, whose producer is told to post nothing.
+    const uint32_t rows = 2, cols = 2048;
+    char* buf = nullptr;
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaMalloc(&buf, rows * cols + 4096 + cols * 4 + 256));
+    cudaError_t e = cudaMemsetAsync(buf, 0, rows * cols + 4096 + cols * 4 + 256, ctx->stream);
+    int st = OK;
+    if (e == cudaSuccess) {
+        GemvParams p;
+        p.w = reinterpret_cast<const int8_t*>(buf), p.s = reinterpret_cast<const __half*>(buf + rows * cols), p.rows = rows, p.cols = cols;
+        p.xmode = X_F32, p.x = buf + rows * cols + 4096, p.epi = EPI_F32, p.y = buf + rows * cols + 4096 + cols * 4;
+        p.silent = 1, p.wait_ns = limit_ns;
+        st = launch_gemv(ctx, p);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(buf);
+    if (e != cudaSuccess) return cuda_fail(e, "tb_selftest_wait");
+    return st;
+}
+
+int tb_status_clear(tb_context* ctx) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    TB_CUDA(cudaMemsetAsync(ctx->status, 0, 4, ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return OK;
 }
 
 int tb_gemv_f16(tb_context* ctx, const uint16_t* w, const void* x, int x_dtype, void* y, int y_dtype, uint32_t rows, uint32_t cols) {

@@ -60,13 +60,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for the phase with `parity` to complete, at most WAIT_LIMIT_NS; false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Waits for the phase with `parity` to complete, at most `limit` nanoseconds (WAIT_LIMIT_NS unless a caller has a reason
+// for less); false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = global_ns();
     for (uint32_t spins = 0;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 255u) == 255u && global_ns() - start > WAIT_LIMIT_NS) return false;
+        if ((spins & 255u) == 255u && global_ns() - start > limit) return false;
     }
 }
 

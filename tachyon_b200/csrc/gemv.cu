@@ -250,9 +250,10 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     }
     __syncthreads();
 
+    const unsigned long long wait_limit = p.wait_ns != 0 ? p.wait_ns : WAIT_LIMIT_NS;
     if (warp == CONSUMERS) {
         // Producer: one thread streams this block's rows.  Nothing it reads is written by another kernel.
-        if (lane == 0) {
+        if (lane == 0 && !p.silent) {
             // This thread's release of the kernel behind this one (at once with p.early, else when the block's last copy is
             // known).  A block counts as having released its dependents once ALL of its threads have said so or have left, so
             // with the consumers silent this only ever matters at the block's end; measured on B200, consumers that also say so
@@ -282,7 +283,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
                     }
                     prefetch_stages(p.pf, blockIdx.x);
                 }
-                if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1)) {
+                if (i >= NST && !mbar_wait(&empty[s], ((i / NST) - 1) & 1, wait_limit)) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                     break;
                 }
@@ -340,7 +341,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t* status)
     uint32_t besti = 0xffffffffu;
     for (uint32_t i = team;; i += TEAMS) {
         const uint32_t s = i % NST;
-        const bool ok = mbar_wait(&full[s], (i / NST) & 1);
+        const bool ok = mbar_wait(&full[s], (i / NST) & 1, wait_limit);
         if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);  // the producer's copies never landed: treated as the end of the work
         const uint32_t here = ok ? stage_cnt[s] : 0u;
         // Warps that share rows leave the loop together, through their barrier below (one of them giving up a wait must

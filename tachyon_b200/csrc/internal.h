@@ -111,6 +111,10 @@ struct GemvParams {
     // small-footprint kernel (no ring, weights in registers, dependents released at once) when its shape allows.
     uint32_t lean = 0;
     uint32_t ring = 0;            // stages of the shared-memory ring (set by launch_gemv)
+    // Self-test of the bounded waits (tb_selftest_wait): the producer posts nothing, so every consumer's wait for its first
+    // stage runs out after wait_ns; the kernel must then leave ERR_WAIT_FULL in the status word and return like any other.
+    uint32_t silent = 0;
+    unsigned long long wait_ns = 0;  // 0: the usual two seconds
     uint32_t early = 0;           // != 0: release the kernel behind this one at once (it waits for this one before it reads anything of it)
     uint32_t l2_ahead = 0;        // stages past the ring to ask the L2 for once the ring is full
     // Optional timeline: 8 words; the first and the last block each leave %globaltimer at entry, after the wait for

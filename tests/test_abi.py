@@ -78,3 +78,24 @@ def test_bad_descriptors_are_rejected_before_launch(lib_path):
     assert lib.tb_sync(None) == 3
     assert b"null" in lib.tb_last_error()
     assert lib.tb_attend_decode(None, None) == 3
+
+
+def test_a_missing_driver_is_reported():
+    """crates/tachyon/tests/no_driver.rs:5-12: with $TACHYON_LIBCUDA naming a file that is not there, listing the devices and
+    opening a context both fail cleanly with NoDriver, and the message names the variable.  Its own process: the driver is
+    looked for once per process."""
+    import subprocess
+    import sys
+
+    code = (
+        "import ctypes as C, sys; sys.path.insert(0, %r)\n"
+        "from tachyon_b200 import _lib\n"
+        "lib = _lib.load(); n = C.c_int(-1); h = C.c_void_p()\n"
+        "a = lib.tb_devices(C.byref(n)); m1 = lib.tb_last_error().decode()\n"
+        "b = lib.tb_context_new(0, C.byref(h)); m2 = lib.tb_last_error().decode()\n"
+        "print(a, b, n.value, h.value, 'TACHYON_LIBCUDA' in m1 and 'TACHYON_LIBCUDA' in m2)\n"
+    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TACHYON_LIBCUDA="/nonexistent/libcuda.so.1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert out.returncode == 0, out.stderr[-1500:]
+    assert out.stdout.split() == ["1", "1", "0", "None", "True"], out.stdout

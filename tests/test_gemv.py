@@ -245,3 +245,32 @@ def test_gemv_f16_rejects_bad_descriptors(ctx):
     assert e.value.status == 3
     with pytest.raises(tb.Error):
         ctx.gemv_f16(z, z, tb.F32, z, tb.F32, 4, 32768)  # wider than the kernel's shared-memory vector
+
+
+def test_a_wait_that_runs_out_comes_back_as_a_status():
+    """Every device-side wait has a limit.  tb_selftest_wait makes one run out (a block whose producer copies nothing, a limit
+    of a millisecond): the kernel returns, the context's status word reads 1 (a wait for a full stage), tb_status says
+    TB_DEVICE_WAIT, and after tb_status_clear the same context computes as before.  A context of its own, so the session's
+    stays clean."""
+    import ctypes as C
+    import time
+
+    c = tb.Context(0)
+    t0 = time.perf_counter()
+    tb.check(c.lib.tb_selftest_wait(c.handle, 1_000_000))
+    assert time.perf_counter() - t0 < 1.0
+    word = C.c_uint32(0)
+    assert c.lib.tb_status(c.handle, C.byref(word)) == 10 and word.value == 1
+    assert "bounded wait" in c.lib.tb_last_error().decode()
+    tb.check(c.lib.tb_status_clear(c.handle))
+    assert c.status() == 0
+    rows, cols = 64, 2048
+    w, s = q8_weights(rows, cols, 3)
+    x = np.random.default_rng(4).standard_normal(cols).astype(np.float32)
+    got = run(c, w, s, x, tb.F32, tb.F32)
+    _, exact, bound = oracle.gemv_q8(w, s, x)
+    assert np.all(np.abs(got.astype(np.float64) - exact) <= 1e-5 * bound + 1e-6)
+    assert c.status() == 0
+    with pytest.raises(tb.Error):
+        tb.check(c.lib.tb_selftest_wait(c.handle, 0))
+    c.close()
