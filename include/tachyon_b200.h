@@ -155,11 +155,18 @@ TB_API int tb_gemv_q8_argmax(tb_context* ctx, const int8_t* w, const uint16_t* s
  * Stands in for gemm_q4 with its split-K slices and sum_slices (crates/tachyon/src/ptx/gemm.rs:18-23, 225-259,
  * 287-325) and, in GeGLU mode, geglu_q8p (ptx/mod.rs:217-249).
  */
-enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2, TB_GEMM_ADD = 3, TB_GEMM_GEGLU_ERF = 4, TB_GEMM_GELU_ERF = 5 };
+enum { TB_GEMM_F32 = 0, TB_GEMM_F16 = 1, TB_GEMM_GEGLU = 2, TB_GEMM_ADD = 3, TB_GEMM_GEGLU_ERF = 4, TB_GEMM_GELU_ERF = 5,
+       /* 6: internal (a product times a per-token vector, the per-layer inputs' gate) */
+       TB_GEMM_RELU = 7,        /* out f16 [m, n] = max(D, 0): the reference's store mode 3 (ptx/encoder.rs:5-9) */
+       TB_GEMM_GATED_SILU = 8   /* out f16 [m, n/2] = silu(D[2j]) * D[2j+1]: its store mode 5 */ };
 TB_API int tb_gemm_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
 /* The same product on the reference's Q4 weights (packed u8 [n, k/2], scales f16 [n, k/64], quant.rs:47-82): the nibbles
  * become f16 (n - 8) * scale in the operand path; stands in for gemm_q4 (ptx/gemm.rs:225-259) on a converted model. */
 TB_API int tb_gemm_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
+/* The same product on f16 weights (w: device f16 [n, k] row-major, as PyTorch's Linear holds them): gemm_f16 and its store
+ * modes (ptx/encoder.rs:5-9, 498-525), which the reference uses for encoders too narrow for 8-bit weights (encoder/convert.rs:
+ * 26-29).  The weight tile goes to the tensor cores as it is. */
+TB_API int tb_gemm_f16(tb_context* ctx, const uint16_t* w, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
 
 /*
  * The reference's own decode formats, for callers that hold a model converted by the reference (quant.rs:47-130):

@@ -170,6 +170,10 @@ class Context:
         """tb_gemm_q8: out[m, n] = a[m, k] (f16) x w[n, k]^T on the tensor cores; mode 0 f32, 1 f16, 2 GeGLU."""
         check(self.lib.tb_gemm_q8(self.handle, w.ptr, s.ptr, a.ptr, m, n, k, out.ptr, mode))
 
+    def gemm_f16(self, w, a, m, n, k, out, mode=0) -> None:
+        """tb_gemm_f16: the same product on f16 weights [n, k]."""
+        check(self.lib.tb_gemm_f16(self.handle, w.ptr, a.ptr, m, n, k, out.ptr, mode))
+
     def gemm_q4(self, packed, s, a, m, n, k, out, mode=0) -> None:
         """tb_gemm_q4: the same product on the reference's Q4 weights."""
         check(self.lib.tb_gemm_q4(self.handle, packed.ptr, s.ptr, a.ptr, m, n, k, out.ptr, mode))

@@ -86,6 +86,7 @@ SIGNATURES = {
     "tb_gemv_q8_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, f32, f32, vp, vp, u32, u32, i32]),
     "tb_gemv_q8_argmax": (i32, [vp, vp, vp, vp, i32, vp, u32, u32, vp, vp, vp]),
     "tb_gemm_q8": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
+    "tb_gemm_f16": (i32, [vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_gemm_q4": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_norm": (i32, [vp, vp, vp, vp, vp, u32, f32, f32, vp, vp]),
     "tb_embed_q8": (i32, [vp, vp, vp, vp, u32, f32, vp]),

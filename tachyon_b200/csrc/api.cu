@@ -544,6 +544,12 @@ int tb_gemm_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* scales, c
     return launch_gemm_q8(ctx, reinterpret_cast<const int8_t*>(packed), reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(a), m, n, k, out, mode, 4);
 }
 
+int tb_gemm_f16(tb_context* ctx, const uint16_t* w, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (mode == 6) return fail(OUT_OF_RANGE, "tb_gemm_f16: unknown output mode");
+    return launch_gemm_q8(ctx, reinterpret_cast<const int8_t*>(w), nullptr, reinterpret_cast<const __half*>(a), m, n, k, out, mode, 16);
+}
+
 int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
             float* x_out) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");

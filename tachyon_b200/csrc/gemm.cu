@@ -104,12 +104,17 @@ struct GemmArgs {
     void* out;
     uint32_t M, N, K;
     int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU (tanh) of column pairs, f16 [M, N / 2]; 3: f32 [M, N] += D;
-               // 4: GeGLU (erf) of column pairs, f16 [M, N / 2]; 5: GELU (erf), f16 [M, N]
+               // 4: GeGLU (erf) of column pairs, f16 [M, N / 2]; 5: GELU (erf), f16 [M, N]; 7: ReLU, f16 [M, N];
+               // 8: SiLU(even) * odd of column pairs, f16 [M, N / 2] (the reference's store modes 3 and 5, ptx/encoder.rs:5-9)
 };
+
+__device__ __forceinline__ float silu(float v) { return v / (1.0f + exp2f(-1.4426950408889634f * v)); }
 
 // MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
 // dequantisation is shared by twice the tensor-core work.
-// WB: bits per weight, 8 (codes, an f16 scale per 32) or 4 (the reference's Q4, a scale per 64 = one per row and K tile).
+// WB: bits per weight, 8 (codes, an f16 scale per 32), 4 (the reference's Q4, a scale per 64 = one per row and K tile) or 16
+// (f16 weights as they are, the reference's gemm_f16, ptx/encoder.rs:498-525: the sixteen warps then only move the tile into
+// the swizzled layout).
 template <int MT, int WB = 8>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const GemmArgs g, uint32_t* status) {
     constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
@@ -181,12 +186,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
         // next tile's codes are fetched before this one's are stored.
         const int j = threadIdx.x - 64, qtr = j & 3;
         uint4 c[PIECES];
+        uint4 c2[WB == 16 ? PIECES : 1];  // f16 weights: the second 16 bytes of a piece of 16 weights
         uint4 sc8[PIECES];  // per piece: the row's eight scales covering tiles kt & ~3 ... + 3
         auto fetch = [&](uint32_t kt) {
 #pragma unroll
             for (int it = 0; it < PIECES; it++) {
                 const uint32_t row = it * (DT / 4) + (j >> 2), n = n0 + row;
                 const bool live = n < g.N;
+                if constexpr (WB == 16) {
+                    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(g.w) + (size_t)n * g.K + (size_t)kt * BK + qtr * 16);
+                    c[it] = live ? __ldg(src) : make_uint4(0u, 0u, 0u, 0u);
+                    c2[it] = live ? __ldg(src + 1) : make_uint4(0u, 0u, 0u, 0u);
+                    continue;
+                }
                 if constexpr (WB == 4) {
                     // A piece is 16 weights = 8 bytes; a row's tile 32 bytes; its one scale per tile comes eight tiles at a time.
                     const uint2 t = live ? __ldg(reinterpret_cast<const uint2*>(g.w + (size_t)n * (g.K / 2) + (size_t)kt * (BK / 2) + qtr * 8))
@@ -229,6 +241,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
 #pragma unroll
             for (int it = 0; it < PIECES; it++) {
                 // scale of this piece's group of 32: tile kt's two scales are halves 2*(kt&3) and 2*(kt&3)+1
+                if constexpr (WB == 16) {
+                    v[it][0] = c[it].x, v[it][1] = c[it].y, v[it][2] = c[it].z, v[it][3] = c[it].w;
+                    v[it][4] = c2[it].x, v[it][5] = c2[it].y, v[it][6] = c2[it].z, v[it][7] = c2[it].w;
+                    continue;
+                }
                 const uint32_t words[4] = {sc8[it].x, sc8[it].y, sc8[it].z, sc8[it].w};
                 if constexpr (WB == 4) {
                     const uint32_t pair = words[(kt & 7) >> 1];
@@ -293,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 8; i++)
                         if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                } else if (g.mode == 1 || g.mode == 5) {
+                } else if (g.mode == 1 || g.mode == 5 || g.mode == 7) {
                     uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
@@ -302,6 +319,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                         for (int e = 0; e < 4; e++) {
                             float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
                             if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                            if (g.mode == 7) f0 = fmaxf(f0, 0.0f), f1 = fmaxf(f1, 0.0f);
                             const __half2 t = __floats2half2_rn(f0, f1);
                             h[e] = *reinterpret_cast<const uint32_t*>(&t);
                         }
@@ -316,8 +334,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
-                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
-                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : g.mode == 8 ? silu(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : g.mode == 8 ? silu(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
                             const __half2 t = __floats2half2_rn(a0, a1);
                             h[e] = *reinterpret_cast<const uint32_t*>(&t);
                         }
@@ -349,10 +367,10 @@ EncodeTiled encode_tiled() {
 
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
                    uint32_t wbits, const float* mul, uint32_t mul_stride) {
-    if (!w || !s || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
+    if (!w || (!s && wbits != 16) || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
     if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
-    if (N % 32 != 0 || ((mode == 2 || mode == 4) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with GeGLU)");
-    if (mode < 0 || mode > 6) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
+    if (N % 32 != 0 || ((mode == 2 || mode == 4 || mode == 8) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with a gated output)");
+    if (mode < 0 || mode > 8) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
     if (mode == 6) {  // only the persistent schedule has this epilogue
         if (!mul || mul_stride < N || (reinterpret_cast<uintptr_t>(mul) & 15) || mul_stride % 4 != 0) return fail(OUT_OF_RANGE, "gemm: the multiplier must be present, 16-byte aligned and at least N wide");
         if (!gemm_persistent_supports(N, K, wbits)) return fail(UNSUPPORTED, "gemm: no kernel for this shape with a multiplier");
@@ -361,10 +379,10 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
             return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
         return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits, mul, mul_stride);
     }
-    if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
+    if (wbits != 8 && wbits != 4 && wbits != 16) return fail(OUT_OF_RANGE, "gemm: weights are 16, 8 or 4 bits");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
-    {
+    if (wbits != 16 && mode != 7 && mode != 8) {  // f16 weights and the two rarer outputs: this file's kernel only
         // Schedules: this file's one tile per block; gemm2.cu's persistent blocks, whose epilogue overlaps the next tile's
         // products and whose MMAs read less shared memory per FLOP; gemm3.cu's pairs of SMs.  Measured on the benchmark's
         // shapes the persistent one wins where the epilogue stores f32 (plain or added to the output: 1.2 to 1.7 times
@@ -394,11 +412,15 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         TB_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<1, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<1, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
     GemmArgs g{w, s, out, M, N, K, mode};
     const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
-    if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
+    if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
+    else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
+    else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
     else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
     else if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
     else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);

@@ -98,3 +98,61 @@ def test_gemm_q4_matches_f64(ctx, schedule, m, n, k):
     got = got[: m * n].reshape(m, n)
     assert np.all(np.abs(got - want) <= 1e-3 * bound + 1e-6), float(np.abs(got - want).max())
     assert ctx.status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (37, 256, 768), (300, 2304, 768), (512, 768, 3072), (129, 3072, 768), (64, 64, 576)])
+def test_gemm_f16_weights_and_every_store_mode(ctx, m, n, k):
+    """tb_gemm_f16: f16 weights as they are (the reference's gemm_f16, tests/encoder.rs:240-355: all modes, rows past the
+    tokens untouched), against f64; and the store modes the Q8 test above does not reach: residual add, exact-form GELU plain
+    and gated, ReLU, gated SiLU."""
+    rng = np.random.default_rng(m + n + k)
+    w = f16(rng.standard_normal((n, k)).astype(np.float32) * np.float32(0.05))
+    a = f16(rng.standard_normal((m, k)).astype(np.float32))
+    w64, a64 = f16_to_f32(w).astype(np.float64), f16_to_f32(a).astype(np.float64)
+    want, bound = a64 @ w64.T, np.abs(a64) @ np.abs(w64).T
+    wd, ad = ctx.upload(w), ctx.upload(a)
+    erf = np.vectorize(lambda v: float(oracle.lib().tbo_erf_as(np.float32(v))))
+    gelu = lambda v: 0.5 * v * (1.0 + erf(v * 0.70710678118))
+    silu = lambda v: v / (1.0 + np.exp(-v))
+    out = ctx.alloc((m + 2) * n * 4)
+    # f32 store, then the residual add on top of it
+    out.upload(np.full((m + 2) * n, 9.0, np.float32))
+    ctx.gemm_f16(wd, ad, m, n, k, out, 0)
+    got = out.download(np.float32, (m + 2) * n)
+    assert np.all(got[m * n:] == 9.0), "rows past the tokens were written"
+    assert np.all(np.abs(got[: m * n].reshape(m, n) - want) <= 1e-5 * bound + 1e-6), float(np.abs(got[: m * n].reshape(m, n) - want).max())
+    ctx.gemm_f16(wd, ad, m, n, k, out, 3)
+    assert np.all(np.abs(out.download(np.float32, m * n).reshape(m, n) - 2 * want) <= 2e-5 * bound + 2e-6)
+    tol16 = lambda ref, b: 2.0**-9 * np.abs(ref) + 1e-4 * b + 1e-5
+    for mode, ref in ((1, want), (5, gelu(want)), (7, np.maximum(want, 0.0))):
+        o16 = ctx.zeros(m * n * 2)
+        ctx.gemm_f16(wd, ad, m, n, k, o16, mode)
+        got16 = f16_to_f32(o16.download(np.uint16, m * n)).reshape(m, n)
+        assert np.all(np.abs(got16 - ref) <= tol16(ref, bound)), (mode, float(np.abs(got16 - ref).max()))
+    if n % 64 == 0:
+        even, odd, be, bo = want[:, 0::2], want[:, 1::2], bound[:, 0::2], bound[:, 1::2]
+        for mode, ref in ((4, gelu(even) * odd), (8, silu(even) * odd)):
+            o16 = ctx.zeros(m * n)
+            ctx.gemm_f16(wd, ad, m, n, k, o16, mode)
+            got16 = f16_to_f32(o16.download(np.uint16, m * n // 2)).reshape(m, n // 2)
+            tol = 2.0**-9 * np.abs(ref) + 1e-4 * (be * (1 + np.abs(odd)) + bo * (1 + np.abs(even))) + 1e-5
+            assert np.all(np.abs(got16 - ref) <= tol), (mode, float(np.abs(got16 - ref).max()))
+    assert ctx.status() == 0
+
+
+def test_gemm_q8_relu_and_gated_silu(ctx):
+    m, n, k = 200, 512, 768
+    w, s = q8_weights(n, k, 9)
+    a = f16_to_f32(f16(np.random.default_rng(10).standard_normal((m, k)).astype(np.float32)))
+    want, bound = reference(w, s, a)
+    wd, sd, ad = ctx.upload(w), ctx.upload(s), ctx.upload(f16(a))
+    o = ctx.zeros(m * n * 2)
+    ctx.gemm_q8(wd, sd, ad, m, n, k, o, 7)
+    got = f16_to_f32(o.download(np.uint16, m * n)).reshape(m, n)
+    assert np.all(np.abs(got - np.maximum(want, 0.0)) <= 2.0**-9 * np.abs(want) + 1e-3 * bound + 1e-5)
+    ctx.gemm_q8(wd, sd, ad, m, n, k, o, 8)
+    even, odd = want[:, 0::2], want[:, 1::2]
+    ref = even / (1.0 + np.exp(-even)) * odd
+    got = f16_to_f32(o.download(np.uint16, m * n // 2)).reshape(m, n // 2)
+    tol = 2.0**-9 * np.abs(ref) + 1e-3 * (bound[:, 0::2] * (1 + np.abs(odd)) + bound[:, 1::2] * (1 + np.abs(even))) + 1e-5
+    assert np.all(np.abs(got - ref) <= tol)

@@ -32,7 +32,8 @@ def test_quant_q8p_matches_the_cpu_exactly(ctx):
     y = values(64 * 7, 8)
     qd, sd = ctx.alloc(64 * 7 + 64), ctx.alloc(7 * 8 + 8)
     qd.upload(np.full(64 * 7 + 64, 0x55, np.uint8)), sd.upload(np.full(7 * 8 + 8, 0x55, np.uint8))
-    ctx.launch("quant_q8p", (2, 1, 1), (256, 1, 1), 0, [("p", ctx.upload(y).ptr), ("p", qd.ptr), ("p", sd.ptr), ("u", y.size)])
+    yd = ctx.upload(y)
+    ctx.launch("quant_q8p", (2, 1, 1), (256, 1, 1), 0, [("p", yd.ptr), ("p", qd.ptr), ("p", sd.ptr), ("u", y.size)])
     cq, cs = oracle.q8p(y)
     assert np.array_equal(qd.download(np.int8, 64 * 7), cq) and np.all(qd.download(np.uint8, 64 * 7 + 64)[64 * 7:] == 0x55)
     assert np.array_equal(sd.download(np.float32, 14).view(np.uint32), cs.ravel().view(np.uint32)) and np.all(sd.download(np.uint8, 64)[56:] == 0x55)
@@ -54,9 +55,9 @@ def test_gemm_q4_matches_the_reference_on_every_shape(ctx, rows, cols, tokens, s
     packed, scales = oracle.q4(wf)
     qd, sd, q, s = launch_quant_q8p(ctx, x, cols)
     slices = min(slices, cols // 128)
-    y = ctx.zeros(slices * tokens * rows * 4)
+    y, wd, wsd = ctx.zeros(slices * tokens * rows * 4), ctx.upload(packed), ctx.upload(scales)  # held until the results are back
     ctx.launch("gemm_q4", (-(-tokens // 128), rows // 64, slices), (128, 1, 1), 0,
-               [("p", ctx.upload(packed).ptr), ("p", ctx.upload(scales).ptr), ("p", qd.ptr), ("p", sd.ptr), ("p", y.ptr), ("u", rows), ("u", cols), ("u", tokens)])
+               [("p", wd.ptr), ("p", wsd.ptr), ("p", qd.ptr), ("p", sd.ptr), ("p", y.ptr), ("u", rows), ("u", cols), ("u", tokens)])
     n = tokens * rows
     ctx.launch("sum_slices", (-(-n // 1024), 1, 1), (256, 1, 1), 0, [("p", y.ptr), ("u", n), ("u", slices)])
     got = y.download(np.float32, n).reshape(tokens, rows).astype(np.float64)
