@@ -191,7 +191,11 @@ TB_API int tb_gemv_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* sc
  * "embed_q4", "gemv_q4", "sample", "attend_256" / "attend_256_2" / "attend_512" (group 1, or 2 for attend_256 and
  * attend_512; Q8 out), and prefill's "kv_256" / "kv_512", "query_256" / "query_512" (attend.rs:472-556) and "flash_256" /
  * "flash_256_2" / "flash_512" (flash.rs:19-22: f32 out; tiles, block and shared memory are this build's own),
- * with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16, sample.rs:21-27 and attend.rs:21-32;
+ * prefill's formats "quant_q8p", "geglu_q8p", "norm_q8p", "gemm_q4" (the slices taken from grid[2]) and "sum_slices"
+ * (ptx/gemm.rs:18-34), and the encoder's "quant_f16", "norm_f16", "embed_f16", "add_rows", "add_rows_f16", "gather_rows",
+ * "gelu_f16", "rope_f16", "attend_f16" / "attend_f16_32", "gemm_f16" / "gemm_f16_128" / "gemm_f16_tall" and "gemm_q8" /
+ * "gemm_q8_128" / "gemm_q8_tall" (ptx/encoder.rs:5-38; the three names of a product are one kernel here),
+ * with the argument lists of ptx/mod.rs:7-41, gemv.rs:1-16, sample.rs:21-27, attend.rs:21-32 and encoder.rs:5-38;
  * args[i] points at argument i's value (a u64 device address, u32 or f32), as the driver's kernelParams do.  Grid and block
  * are checked against the kernel's documented launch shape where it has a meaning here (chunks, rows and block counts
  * are taken from the grid).  An unknown name is TB_NO_MODEL.
@@ -464,25 +468,37 @@ typedef struct tb_encoder_config {
     const uint8_t* global;  /* [layers] != 0 where a layer attends globally; NULL: every global_every-th from layer 0 */
     uint32_t global_every;  /* with global == NULL (0 means 3, as the reference's default) */
     float theta_global, theta_local, eps;
-    uint32_t gated;         /* != 0: Wi is [2*inter, hidden], MLP = gelu(first half) * second half (the reference); 0: plain GELU */
+    uint32_t gated;         /* 1: Wi is [2*inter, hidden], MLP = gelu(first half) * second half (the reference); 2: the same with a
+                             * SiLU for the GELU (Config::silu, encoder/mod.rs:55-56); 0: Wi is [inter, hidden], plain GELU */
     uint32_t mean_pool;     /* != 0: mean over a sequence's tokens; 0: its first token (the reference, run.rs:160-173) */
     uint32_t dims;          /* leading dimensions kept (Matryoshka, encoder/text.rs:56-63); hidden keeps all */
 } tb_encoder_config;
 
 /* Encoder::open without the file loader: room for `tokens` packed tokens and `sequences` sequences a batch
- * (encoder::Settings::tokens, encoder/mod.rs:23-33). */
+ * (encoder::Settings::tokens, encoder/mod.rs:23-33).  A batch runs padded to whole tiles of 64 tokens as a CUDA graph
+ * recorded the first time its padded shape is seen, sixteen shapes kept (Encoder::encode, encoder/run.rs:379-410);
+ * TACHYON_B200_ENCODER_GRAPHS=0 in the environment at this call launches kernel by kernel instead. */
 TB_API int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, tb_encoder** out);
 TB_API void tb_encoder_close(tb_encoder* enc);
 /* Tensors by converted-model name (encoder/convert.rs:79-105): embed (f16 [vocab, hidden]), embed_norm, final_norm,
- * {l}.attn_norm (layer 0's is unused), {l}.mlp_norm (f32 [hidden]); matrices {l}.qkv, {l}.o, {l}.up, {l}.down as
- * <name>.w (int8 codes) and <name>.s (f16 scale per 32 along a row). */
+ * {l}.attn_norm (layer 0's is unused), {l}.mlp_norm (f32 [hidden]); matrices {l}.qkv, {l}.o, {l}.up, {l}.down either as
+ * a converted model holds them, under the plain name: f16 [rows, cols], or Q8E codes i8 [rows, cols] with <name>.scale,
+ * f32 [rows, cols / 64] (quant.rs:107-115; which of the two is told by the size; the scales are kept as f16, one per 32);
+ * or in this build's Q8: <name>.w (int8 codes) and <name>.s (f16 scale per 32 along a row).  The gated Wi ({l}.up) comes
+ * as the file has it, the activation's rows then the gate's, and is interleaved on the device (Encoder::interleave,
+ * encoder/run.rs:449-466). */
 TB_API int tb_encoder_load(tb_encoder* enc, const char* name, const void* data, size_t bytes);
 TB_API int tb_encoder_fill_random(tb_encoder* enc, uint64_t seed);
 /* Encoder::embeddings (run.rs:161-175): ids packed back to back, lens[s] tokens each; out_host: dims f32 per sequence,
- * L2-normalised. */
+ * L2-normalised.  More tokens (or sequences) than the encoder was opened for go in several batches, in order, a batch
+ * closed by the first sequence that no longer fits (Encoder::batches, run.rs:207-221); one sequence longer than the
+ * capacity is TB_TOO_LONG. */
 TB_API int tb_encoder_embed(tb_encoder* enc, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host);
-/* The last batch's final hidden states, f32 [tokens, hidden] (for parity checks). */
+/* The last batch's final hidden states, f32 [tb_encoder_batch_tokens, hidden] (for parity checks). */
 TB_API int tb_encoder_hidden(tb_encoder* enc, float* out_host);
+TB_API uint32_t tb_encoder_batch_tokens(const tb_encoder* enc);
+/* Padded shapes whose graph is held at the moment. */
+TB_API uint32_t tb_encoder_graphs(const tb_encoder* enc);
 
 #ifdef __cplusplus
 }

@@ -91,6 +91,7 @@ def _declare(l: C.CDLL) -> None:
         "tbo_fill_gauss_f16": (None, [u64, u64, vp, sz, f32]),
         "tbo_fill_gauss_f32": (None, [u64, u64, vp, sz, f32]),
         "tbo_decoder_step": (C.c_int32, [C.POINTER(Model), u32, u32, vp, i32, vp]),
+        "tbo_gemm_q8e": (None, [vp, vp, vp, vp, vp, sz, sz, sz, vp]),
         "tbo_encoder_forward": (None, [C.POINTER(EncConfig), vp, vp, C.POINTER(EncLayer), vp, vp, sz, vp]),
         "tbo_erf_as": (f32, [f32]),
         "tbo_threads": (i32, []),
@@ -139,6 +140,33 @@ def q8p(x: np.ndarray):
     q, pairs = q8(x, 64)
     lib().tbo_q8p_pairs(ptr(pairs), pairs.shape[0])
     return q, pairs
+
+
+def q8e(x: np.ndarray):
+    """quant::q8e (crates/tachyon/src/quant.rs:107-115): int8 codes and an f32 scale per block of 64, amax / 127, ties to
+    even; what quant_f16 computes from f16 rows (ptx/encoder.rs:670-743)."""
+    q, pairs = q8(x, 64)
+    return q, np.ascontiguousarray(pairs[:, 0])
+
+
+def gemm_q8e(aq, sa, wq, sw, rows: int, bias=None) -> np.ndarray:
+    """The reference's gemm_q8 sums, bit for bit: f32 [tokens, rows] from Q8E activations and weights, bias added."""
+    aq, wq = np.ascontiguousarray(aq, np.int8), np.ascontiguousarray(wq, np.int8)
+    sa, sw = np.ascontiguousarray(sa, np.float32), np.ascontiguousarray(sw, np.float32)
+    cols = wq.size // rows
+    tokens = aq.size // cols
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    y = np.zeros((tokens, rows), np.float32)
+    lib().tbo_gemm_q8e(ptr(aq), ptr(sa), ptr(wq), ptr(sw), ptr(b) if b is not None else None, tokens, rows, cols, ptr(y))
+    return y
+
+
+def rope_table(theta: float, positions: int, d: int) -> np.ndarray:
+    """rope_tables (crates/tachyon/src/encoder/run.rs:523-537): f32 [positions, d/2, 2] of cos and sin of p * theta^(-2j/d),
+    computed in f64 and rounded once."""
+    j = np.arange(d // 2, dtype=np.float64)
+    angle = np.arange(positions, dtype=np.float64)[:, None] * np.float64(np.float32(theta)) ** (-2.0 * j / d)[None, :]
+    return np.stack([np.cos(angle), np.sin(angle)], axis=2).astype(np.float32)
 
 
 def product_q4(packed, scales, x, rows):

@@ -823,6 +823,8 @@ TBO_API float tbo_erf_as(float x) {
     return copysignf(1.0f - p * expf(-x * x), x);
 }
 static float enc_gelu(float x) { return 0.5f * x * (1.0f + tbo_erf_as(x / 1.41421356237f)); }
+/* tests/encoder.rs:64-66 */
+static float enc_silu(float x) { return x / (1.0f + expf(-x)); }
 
 /* encoder.rs:67-101: RoPE by row index, window |i - j| <= w or none (w < 0), scale 1/sqrt(d). */
 static void enc_attend(const float *qkv, size_t n, size_t heads, size_t d, long window, float theta, float *out) {
@@ -862,7 +864,28 @@ static void enc_attend(const float *qkv, size_t n, size_t heads, size_t d, long 
     free(q); free(k); free(sc);
 }
 
-/* encoder.rs:104-123.  gated: Wi is [2*inter, h] and the MLP is gelu(first half) * second half; otherwise Wi is
+/* The 8-bit product on Q8E activations and weights (codes, an f32 scale per 64 along a row), sum by sum as the reference's
+ * gemm_q8 kernel forms it (crates/tachyon/src/ptx/encoder.rs:315-375): per group of 64 the integer sum i, read as the
+ * float 12582912 + i (exact: |i| < 2^22), then f = fma(12582912 + i, sa, -12582912 sa) and c = fma(f, sw, c), the groups
+ * in order; the bias is added at the store (encoder.rs:418-436).  y: f32 [tokens, rows], before any activation. */
+TBO_API void tbo_gemm_q8e(const int8_t *a, const float *sa, const int8_t *w, const float *sw, const float *bias, size_t tokens, size_t rows, size_t cols,
+                          float *y) {
+    size_t groups = cols / 64;
+    for (size_t t = 0; t < tokens; t++)
+        for (size_t r = 0; r < rows; r++) {
+            float c = 0.0f;
+            for (size_t g = 0; g < groups; g++) {
+                int32_t i = 0;
+                for (size_t k = 0; k < 64; k++) i += (int32_t)a[t * cols + g * 64 + k] * (int32_t)w[r * cols + g * 64 + k];
+                float ts = sa[t * groups + g], tz = ts * -12582912.0f;
+                float f = fmaf(12582912.0f + (float)i, ts, tz);
+                c = fmaf(f, sw[r * groups + g], c);
+            }
+            y[t * rows + r] = c + (bias ? bias[r] : 0.0f);
+        }
+}
+
+/* encoder.rs:104-123.  gated: Wi is [2*inter, h] and the MLP is gelu(first half) * second half (2: silu); otherwise Wi is
  * [inter, h] and the MLP is gelu(Wi x) (the benchmark's plain GeLU FFN).  hidden_out: [n, hidden]. */
 TBO_API void tbo_encoder_forward(const tbo_enc_config *c, const float *embed, const float *embed_norm, const tbo_enc_layer *layers,
                                  const float *final_norm, const uint32_t *ids, size_t n, float *hidden_out) {
@@ -884,7 +907,8 @@ TBO_API void tbo_encoder_forward(const tbo_enc_config *c, const float *embed, co
         enc_linear(a, L->up, n, h, up_rows, up);
         for (size_t r = 0; r < n; r++)
             for (size_t i = 0; i < inter; i++)
-                g[r * inter + i] = c->gated ? enc_gelu(up[r * up_rows + i]) * up[r * up_rows + inter + i] : enc_gelu(up[r * up_rows + i]);
+                g[r * inter + i] = c->gated == 2 ? enc_silu(up[r * up_rows + i]) * up[r * up_rows + inter + i]
+                                 : c->gated    ? enc_gelu(up[r * up_rows + i]) * up[r * up_rows + inter + i] : enc_gelu(up[r * up_rows + i]);
         enc_linear(g, L->down, n, inter, h, a);
         for (size_t i = 0; i < n * h; i++) x[i] += a[i];
     }

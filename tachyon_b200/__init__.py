@@ -439,15 +439,18 @@ class Encoder:
         check(self.lib.tb_encoder_fill_random(self.handle, seed))
 
     def embed(self, sequences) -> np.ndarray:
-        """Embeddings [len(sequences), dims] of lists of token ids, packed into one batch."""
+        """Embeddings [len(sequences), dims] of lists of token ids, packed into batches of at most the capacity."""
         lens = np.array([len(q) for q in sequences], np.uint32)
         ids = np.concatenate([np.asarray(q, np.uint32) for q in sequences])
         out = np.zeros((len(sequences), self.cfg.dims), np.float32)
         check(self.lib.tb_encoder_embed(self.handle, ids.ctypes.data, lens.ctypes.data, len(sequences), out.ctypes.data))
-        self._tokens = int(lens.sum())
         return out
 
+    def graphs(self) -> int:
+        return int(self.lib.tb_encoder_graphs(self.handle))
+
     def hidden(self) -> np.ndarray:
-        out = np.zeros((self._tokens, self.cfg.hidden), np.float32)
+        """The last batch's final hidden states [its tokens, hidden]."""
+        out = np.zeros((int(self.lib.tb_encoder_batch_tokens(self.handle)), self.cfg.hidden), np.float32)
         check(self.lib.tb_encoder_hidden(self.handle, out.ctypes.data))
         return out

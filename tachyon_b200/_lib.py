@@ -136,6 +136,8 @@ SIGNATURES = {
     "tb_encoder_fill_random": (i32, [vp, u64]),
     "tb_encoder_embed": (i32, [vp, vp, vp, u32, vp]),
     "tb_encoder_hidden": (i32, [vp, vp]),
+    "tb_encoder_batch_tokens": (u32, [vp]),
+    "tb_encoder_graphs": (u32, [vp]),
     "tb_decoder_timeline": (i32, [vp, u32, vp, C.POINTER(u32)]),
 }
 

@@ -441,6 +441,52 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         return launch_prefill_flash(ctx, static_cast<const __half*>(ptr(0)), static_cast<const __half*>(ptr(1)), static_cast<const __half*>(ptr(2)), ptr(8), tokens, 0,
                                     u32(4), u32(5), heads, grid[1] / group, d, static_cast<const uint32_t*>(ptr(3)), 1.4426950408889634f, 1);
     }
+    // ---- the encoder's kernels (ptx/encoder.rs:5-38) ----
+    if (name == "quant_f16") {  // a (f16 rows), q, scales, cols; grid (cols / 64 / 8 rounded up, tokens)
+        TB_TRY(shape(4, 256));
+        return launch_quant_f16(ctx, static_cast<const __half*>(ptr(0)), static_cast<int8_t*>(ptr(1)), static_cast<float*>(ptr(2)), u32(3), grid[1]);
+    }
+    if (name == "norm_f16") {  // x, gamma, beta (or 0), a, xo (or 0), h, eps; one block a row, of any size: this build runs 256 threads
+        if (nargs != 7) return fail(OUT_OF_RANGE, "tb_launch: norm_f16 takes 7 arguments");
+        return launch_norm_f16(ctx, static_cast<const float*>(ptr(0)), static_cast<const float*>(ptr(1)), static_cast<const float*>(ptr(2)), static_cast<__half*>(ptr(3)),
+                               static_cast<float*>(ptr(4)), u32(5), f32(6), grid[0]);
+    }
+    if (name == "embed_f16" || name == "add_rows" || name == "add_rows_f16" || name == "gather_rows") {  // table, idx, out, h; grid (h / 256 rounded up, n)
+        TB_TRY(shape(4, 256));
+        if (grid[0] != (u32(3) + 255) / 256) return fail(OUT_OF_RANGE, "tb_launch: " + name + " runs h / 256 (rounded up) blocks a row");
+        const int kind = name == "embed_f16" ? 0 : name == "add_rows" ? 1 : name == "add_rows_f16" ? 2 : 3;
+        return launch_rows(ctx, kind, ptr(0), static_cast<const uint32_t*>(ptr(1)), static_cast<float*>(ptr(2)), u32(3), grid[1]);
+    }
+    if (name == "gelu_f16") {  // x, out, width, len, gated
+        TB_TRY(shape(5, 256));
+        return launch_gelu_f16(ctx, static_cast<const float*>(ptr(0)), static_cast<__half*>(ptr(1)), u32(2), u32(3), u32(4));
+    }
+    if (name == "rope_f16") {  // qkv, table, pos, h, d; grid (h / 2 / 256 rounded up, n)
+        TB_TRY(shape(5, 256));
+        return launch_rope_f16(ctx, static_cast<__half*>(ptr(0)), static_cast<const float*>(ptr(1)), static_cast<const uint32_t*>(ptr(2)), u32(3), u32(4), grid[1]);
+    }
+    if (name == "attend_f16" || name == "attend_f16_32") {  // qkv, out, tiles, h, window (0: all), scale; grid (tiles, h / d) blocks of 128
+        TB_TRY(shape(6, 128));
+        const uint32_t d = name == "attend_f16" ? 64u : 32u, h = u32(3), window = u32(4);
+        if (h == 0 || h % d != 0 || grid[1] != h / d) return fail(OUT_OF_RANGE, "tb_launch: " + name + " runs a block per tile and head");
+        return launch_enc_attend(ctx, static_cast<const __half*>(ptr(0)), static_cast<const uint32_t*>(ptr(2)), static_cast<__half*>(ptr(1)), h, d,
+                                 window == 0 ? -1 : (int)window, f32(5), grid[0]);
+    }
+    if (name == "gemm_f16" || name == "gemm_f16_128" || name == "gemm_f16_tall" || name == "gemm_q8" || name == "gemm_q8_128" || name == "gemm_q8_tall") {
+        // a, w, bias (or 0), y, rows, cols, tokens, mode; the 8-bit ones also a's and w's scales.  The three names of each are
+        // the reference's three block shapes of one product; here one kernel each, which tiles its own way: grid and block
+        // are not used.
+        const bool q8 = name.compare(0, 7, "gemm_q8") == 0;
+        if (nargs != (q8 ? 10u : 8u)) return fail(OUT_OF_RANGE, "tb_launch: " + name + " takes " + (q8 ? "10" : "8") + " arguments");
+        const uint32_t rows = u32(4), cols = u32(5), tokens = u32(6), mode = u32(7);
+        if (mode > 5) return fail(OUT_OF_RANGE, "tb_launch: " + name + " has modes 0 to 5");
+        if (rows % 64 != 0 || cols % 64 != 0) return fail(OUT_OF_RANGE, "tb_launch: " + name + " takes rows and cols in multiples of 64");
+        if (q8) return launch_gemm_q8e(ctx, static_cast<const int8_t*>(ptr(0)), static_cast<const int8_t*>(ptr(1)), static_cast<const float*>(ptr(2)), ptr(3), rows, cols,
+                                       tokens, mode, static_cast<const float*>(ptr(8)), static_cast<const float*>(ptr(9)));
+        static const int store[6] = {TB_GEMM_F32, TB_GEMM_ADD, TB_GEMM_F16, TB_GEMM_RELU, TB_GEMM_GEGLU_ERF, TB_GEMM_GATED_SILU};
+        return launch_gemm_q8(ctx, static_cast<const int8_t*>(ptr(1)), nullptr, static_cast<const __half*>(ptr(0)), tokens, rows, cols, ptr(3), store[mode], 16, nullptr, 0,
+                              static_cast<const float*>(ptr(2)));
+    }
     return fail(NO_MODEL, "tb_launch: no kernel named " + name);
 }
 

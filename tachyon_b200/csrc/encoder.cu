@@ -4,12 +4,15 @@
 // attend_f16 (961-1215), with the products on the tcgen05 GEMM (gemm.cu; its store modes replace ptx/encoder.rs:418-492).
 //
 // Sequences are packed back to back without padding: activations are [tokens, width]; attention works per sequence
-// through a list of 64-query tiles.  Weights are Q8 (int8 codes + f16 scale per 32), the embedding table f16.
+// through a list of 64-query tiles.  Weights are Q8 (int8 codes + f16 scale per 32) or f16, the embedding table f16; a
+// converted model's Q8E matrices (codes + an f32 scale per 64, crates/tachyon/src/quant.rs:107-115) load into the former.
+// A batch runs padded to whole tiles of 64 tokens as a CUDA graph recorded once per padded shape (run.rs:379-410).
 #include "../../include/tachyon_b200.h"
 #include "common.cuh"
 #include "internal.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -55,7 +58,6 @@ __global__ void __launch_bounds__(256) enc_norm_kernel(const float* x, const __h
     }
 }
 
-// ---- RoPE in place on the q and k parts of f16 [tokens, 3h]: pairs (j, j + d/2) of every head turn by pos * freq[j] -------
 // LayerNorm with one warp per token for widths that are multiples of 128 up to 2048: the token stays in registers
 // (16-byte loads, two shuffle reductions, no block barrier).  Same arithmetic as enc_norm_kernel.
 template <int V>  // float4 per lane: h = 128 V
@@ -102,12 +104,14 @@ __global__ void __launch_bounds__(256) enc_norm_warp_kernel(const float* x, cons
 // Picks the warp-per-token kernel where the width allows it.
 static void launch_enc_norm(cudaStream_t s, uint32_t T, const float* x, const __half* table, const uint32_t* ids, const float* w, uint32_t h, float eps, float* out32,
                             __half* out16);
-// One warp per token: a lane turns eight pairs at a time (16-byte loads and stores of the low and the high half of a head).
-__global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32_t* pos, const float* freq, uint32_t h, uint32_t d, uint32_t tokens) {
+// One warp per token: a lane turns eight pairs at a time (16-byte loads and stores of the low and the high half of a head)
+// by the cosines and sines of the token's position from `table` (f32 [positions, d/2, 2]): (a, b) -> (a c - b s, b c + a s),
+// a product then one fused multiply-add each, the reference's operations (ptx/encoder.rs:942-956) and so its bits.
+__global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32_t* pos, const float2* table, uint32_t h, uint32_t d, uint32_t tokens) {
     const uint32_t t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= tokens) return;
     const uint32_t half_d = d / 2, chunks = half_d / 8, heads = h / d, items = 2 * heads * chunks;  // q and k parts
-    const float p = (float)pos[t];
+    const float2* row = table + (size_t)pos[t] * half_d;
     for (uint32_t i = lane; i < items; i += 32) {
         const uint32_t part = i / (heads * chunks), r = i % (heads * chunks), head = r / chunks, j = (r % chunks) * 8;
         __half* base = qkv + (size_t)t * 3 * h + part * h + head * d + j;
@@ -117,11 +121,9 @@ __global__ void __launch_bounds__(256) enc_rope_kernel(__half* qkv, const uint32
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const float2 a = __half22float2(l2[e]), b = __half22float2(h2[e]);
-            float s0, c0, s1, c1;
-            sincosf(p * __ldg(freq + j + 2 * e), &s0, &c0);
-            sincosf(p * __ldg(freq + j + 2 * e + 1), &s1, &c1);
-            l2[e] = __floats2half2_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
-            h2[e] = __floats2half2_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+            const float4 cs = __ldg(reinterpret_cast<const float4*>(row + j + 2 * e));  // (c0, s0, c1, s1)
+            l2[e] = __floats2half2_rn(__fmaf_rn(b.x, -cs.y, __fmul_rn(a.x, cs.x)), __fmaf_rn(b.y, -cs.w, __fmul_rn(a.y, cs.z)));
+            h2[e] = __floats2half2_rn(__fmaf_rn(a.x, cs.y, __fmul_rn(b.x, cs.x)), __fmaf_rn(a.y, cs.w, __fmul_rn(b.y, cs.z)));
         }
         *reinterpret_cast<uint4*>(base) = lo;
         *reinterpret_cast<uint4*>(base + half_d) = hi;
@@ -142,7 +144,8 @@ static void launch_enc_norm(cudaStream_t s, uint32_t T, const float* x, const __
 
 // ---- bidirectional attention over packed sequences -----------------------------------------------------------------------
 // A block: one tile of up to 64 queries of one sequence, one head; 4 warps x 16 query rows; keys in tiles of 64.
-// Query i sees key j of its sequence when |i - j| <= window (window < 0: all).  Scores scale by 1/sqrt(d).
+// Query i sees key j of its sequence when |i - j| <= window (window < 0: all).  `scale` is log2(e) / sqrt(d).  A tile of length
+// 0 (an unused slot of a padded batch) does nothing.
 constexpr int QT = 64, KT = 64;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
@@ -164,7 +167,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 }
 
 template <int D>
-__global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, int window) {
+__global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, int window, float scale) {
     constexpr int LD = D + 8;
     __shared__ __align__(16) __half Qs[QT * LD];
     __shared__ __align__(16) __half Ks[KT * LD];
@@ -186,7 +189,6 @@ __global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, cons
     for (int nb = 0; nb < D / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const uint32_t ia = q0 + warp * 16 + (lane >> 2), ib = ia + 8;  // the two query positions this lane holds
-    const float scale = 1.4426950408889634f * rsqrtf((float)D);
 
     for (uint32_t j0 = lo; j0 < hi; j0 += KT) {
         __syncthreads();
@@ -337,9 +339,18 @@ __global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, cons
     for (uint32_t i = tid; i < dims; i += 256) out[(size_t)s * dims + i] = vec[i] / n2;
 }
 
+// A converted model's Q8E scales (f32, one per 64 along a row) as this build's (f16, one per 32): each rounded and stored twice.
+__global__ void __launch_bounds__(256) enc_scales_kernel(const float* in, __half* out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    const __half v = __float2half_rn(in[i]);
+    out[2 * i] = v, out[2 * i + 1] = v;
+}
+
 struct EMat {
     int8_t* w = nullptr;
     __half* s = nullptr;
+    __half* f16 = nullptr;  // the matrix as f16 [rows, cols] instead, in an allocation of its own (a model too narrow for 8 bits to pay)
     uint32_t rows = 0, cols = 0;
     size_t code_bytes() const { return (size_t)rows * cols; }
     size_t scale_bytes() const { return (size_t)rows * (cols / 32) * 2; }
@@ -351,7 +362,24 @@ struct ELayer {
     bool global = false;
 };
 
+struct EGraph {
+    uint32_t padded = 0, sequences = 0;
+    cudaGraphExec_t exec = nullptr;
+};
+
+constexpr size_t ENC_GRAPHS = 16;  // shapes kept, the oldest dropped first (encoder/run.rs:20)
+
 }  // namespace
+
+int launch_enc_attend(tb_context* ctx, const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, uint32_t d, int window, float scale, uint32_t ntiles) {
+    if (!qkv || !tiles || !out || ntiles == 0 || h == 0 || (d != 32 && d != 64) || h % d != 0) return fail(OUT_OF_RANGE, "encoder attention: null or empty argument, or heads other than 32 or 64 wide");
+    if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) & 15) return fail(OUT_OF_RANGE, "encoder attention: buffers must be 16-byte aligned");
+    if (d == 64) enc_attend_kernel<64><<<dim3(ntiles, h / d), 128, 0, ctx->stream>>>(qkv, tiles, out, h, window, scale);
+    else enc_attend_kernel<32><<<dim3(ntiles, h / d), 128, 0, ctx->stream>>>(qkv, tiles, out, h, window, scale);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
 }  // namespace tb
 
 using namespace tb;
@@ -361,14 +389,20 @@ struct tb_encoder {
     tb_encoder_config cfg = {};
     std::vector<uint8_t> global;
     std::vector<ELayer> layers;
-    uint32_t cap_tokens = 0, cap_seqs = 0, tokens = 0;
+    uint32_t cap_tokens = 0, cap_padded = 0, cap_seqs = 0, tokens = 0;
     char* arena = nullptr;
     size_t arena_bytes = 0;
     __half* embed = nullptr;
-    float *embed_norm = nullptr, *final_norm = nullptr, *freq[2] = {nullptr, nullptr};
+    float *embed_norm = nullptr, *final_norm = nullptr;
+    float2* rope[2] = {nullptr, nullptr};  // cosines and sines [positions, d/2]: global layers', sliding layers'
     float *x = nullptr, *hidden = nullptr, *pooled = nullptr;
     __half *a16 = nullptr, *qkv16 = nullptr, *att16 = nullptr, *g16 = nullptr;
+    // A batch's inputs, one block on the device and its twin in pinned host memory: ids, positions, tiles, first rows, lengths.
+    uint32_t *inputs = nullptr, *stage = nullptr;
+    size_t input_words = 0;
     uint32_t *ids = nullptr, *pos = nullptr, *tiles = nullptr, *starts = nullptr, *lens = nullptr;
+    bool use_graphs = true, warmed = false;
+    std::vector<EGraph> graphs;
 };
 
 namespace {
@@ -386,11 +420,11 @@ size_t enc_layout(tb_encoder* e, char* base) {
         m.w = reinterpret_cast<int8_t*>(take(m.code_bytes()));
         m.s = reinterpret_cast<__half*>(take(m.scale_bytes()));
     };
-    const uint32_t h = c.hidden, up_rows = c.gated ? 2 * c.inter : c.inter, T = e->cap_tokens, S = e->cap_seqs;
+    const uint32_t h = c.hidden, up_rows = c.gated ? 2 * c.inter : c.inter, T = e->cap_padded, S = e->cap_seqs;
     e->embed = reinterpret_cast<__half*>(take((size_t)c.vocab * h * 2));
     e->embed_norm = reinterpret_cast<float*>(take(h * 4));
     e->final_norm = reinterpret_cast<float*>(take(h * 4));
-    for (int k = 0; k < 2; k++) e->freq[k] = reinterpret_cast<float*>(take(h / c.heads / 2 * 4));
+    for (int k = 0; k < 2; k++) e->rope[k] = reinterpret_cast<float2*>(take((size_t)e->cap_tokens * (h / c.heads / 2) * 8));
     for (uint32_t l = 0; l < c.layers; l++) {
         ELayer& L = e->layers[l];
         L.global = e->global[l] != 0;
@@ -405,12 +439,15 @@ size_t enc_layout(tb_encoder* e, char* base) {
     e->qkv16 = reinterpret_cast<__half*>(take((size_t)T * 3 * h * 2));
     e->att16 = reinterpret_cast<__half*>(take((size_t)T * h * 2));
     e->g16 = reinterpret_cast<__half*>(take((size_t)T * c.inter * 2));
-    e->ids = reinterpret_cast<uint32_t*>(take((size_t)T * 4));
-    e->pos = reinterpret_cast<uint32_t*>(take((size_t)T * 4));
-    e->tiles = reinterpret_cast<uint32_t*>(take(((size_t)T / QT + S) * 3 * 4));
-    e->starts = reinterpret_cast<uint32_t*>(take((size_t)S * 4));
-    e->lens = reinterpret_cast<uint32_t*>(take((size_t)S * 4));
+    e->input_words = (size_t)2 * T + ((size_t)T / QT + S) * 3 + 2 * (size_t)S;
+    e->inputs = reinterpret_cast<uint32_t*>(take(e->input_words * 4));
     return end;
+}
+
+// Where each part of a batch's inputs sits in the block at `base` (the device's or the host's).
+void enc_inputs(tb_encoder* e, uint32_t* base, uint32_t*& ids, uint32_t*& pos, uint32_t*& tiles, uint32_t*& starts, uint32_t*& lens) {
+    const size_t T = e->cap_padded, S = e->cap_seqs;
+    ids = base, pos = ids + T, tiles = pos + T, starts = tiles + (T / QT + S) * 3, lens = starts + S;
 }
 
 int enc_validate(const tb_encoder_config& c) {
@@ -420,13 +457,16 @@ int enc_validate(const tb_encoder_config& c) {
     if (c.hidden % 64 != 0 || c.inter % 64 != 0 || c.hidden > 2048) return fail(UNSUPPORTED, "encoder: widths must be multiples of 64, hidden at most 2048");
     if (c.layers == 0 || c.vocab == 0 || c.inter == 0) return fail(OUT_OF_RANGE, "encoder: empty model");
     if (c.dims == 0 || c.dims > c.hidden) return fail(OUT_OF_RANGE, "encoder: dims must be in 1..hidden");
+    if (c.gated > 2) return fail(OUT_OF_RANGE, "encoder: gated is 0 (plain GELU), 1 (GELU gate) or 2 (SiLU gate)");
     return OK;
 }
 
 struct ENamed {
     void* ptr = nullptr;
     size_t bytes = 0;
-    int kind = 0;  // 0 plain, 1 gated up codes, 2 gated up scales
+    int kind = 0;          // 0 vector or table; 1 codes (.w); 2 f16 scales per 32 (.s); 3 a matrix by its size: Q8E codes or f16; 4 f32 scales per 64 (.scale)
+    EMat* mat = nullptr;
+    bool gated_up = false;  // the gated MLP's Wi, whose two halves' rows are interleaved on the device
 };
 
 bool enc_find(tb_encoder* e, const std::string& name, ENamed& out) {
@@ -448,16 +488,107 @@ bool enc_find(tb_encoder* e, const std::string& name, ENamed& out) {
     if (rest == "attn_norm") return out = {L.attn_norm, hb, 0}, true;
     if (rest == "mlp_norm") return out = {L.mlp_norm, hb, 0}, true;
     auto mat = [&](EMat& m, const std::string& suffix, bool gated_up) {
-        if (suffix == ".w") out = {m.w, m.code_bytes(), gated_up ? 1 : 0};
-        else if (suffix == ".s") out = {m.s, m.scale_bytes(), gated_up ? 2 : 0};
+        if (suffix == ".w") out = {m.w, m.code_bytes(), 1, &m, gated_up};
+        else if (suffix == ".s") out = {m.s, m.scale_bytes(), 2, &m, gated_up};
+        else if (suffix.empty()) out = {nullptr, 0, 3, &m, gated_up};
+        else if (suffix == ".scale") out = {m.s, (size_t)m.rows * (m.cols / 64) * 4, 4, &m, gated_up};
         else return false;
         return true;
     };
     if (rest.rfind("qkv", 0) == 0) return mat(L.qkv, rest.substr(3), false);
-    if (rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), false);
+    if (rest == "o" || rest.rfind("o.", 0) == 0) return mat(L.o, rest.substr(1), false);
     if (rest.rfind("up", 0) == 0) return mat(L.up, rest.substr(2), c.gated != 0);
     if (rest.rfind("down", 0) == 0) return mat(L.down, rest.substr(4), false);
     return false;
+}
+
+// One matrix product of the forward pass: the matrix as f16 when it was loaded so, else its codes and scales.
+int enc_product(tb_encoder* e, const EMat& m, const __half* a, uint32_t tokens, void* out, int mode) {
+    if (m.f16 != nullptr) return launch_gemm_q8(e->ctx, reinterpret_cast<const int8_t*>(m.f16), nullptr, a, tokens, m.rows, m.cols, out, mode, 16);
+    return launch_gemm_q8(e->ctx, m.w, m.s, a, tokens, m.rows, m.cols, out, mode);
+}
+
+// The kernels of the batch in the inputs (Encoder::layers, encoder/run.rs:413-447) over `n` rows (the batch padded to whole
+// tiles of 64 tokens: the rows past its tokens hold token 0 at position 0 and belong to no tile), `slots` tiles, `sequences`
+// sequences; leaves the last hidden states in `hidden` and the embeddings in `pooled`.
+int enc_layers(tb_encoder* e, uint32_t n, uint32_t slots, uint32_t sequences) {
+    const tb_encoder_config& c = e->cfg;
+    tb_context* ctx = e->ctx;
+    cudaStream_t s = ctx->stream;
+    const uint32_t h = c.hidden, d = h / c.heads;
+    const float scale = 1.4426950408889634f / sqrtf((float)d);
+    // embeddings -> norm: x (f32 residual stream) and, since layer 0 has no attention norm, its f16 GEMM input
+    launch_enc_norm(s, n, nullptr, e->embed, e->ids, e->embed_norm, h, c.eps, e->x, e->a16);
+    for (uint32_t l = 0; l < c.layers; l++) {
+        ELayer& L = e->layers[l];
+        if (l > 0) launch_enc_norm(s, n, e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
+        TB_TRY(enc_product(e, L.qkv, e->a16, n, e->qkv16, 1));
+        enc_rope_kernel<<<(n + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->rope[L.global ? 0 : 1], h, d, n);
+        TB_TRY(launch_enc_attend(ctx, e->qkv16, e->tiles, e->att16, h, d, L.global ? -1 : (int)c.window, scale, slots));
+        TB_TRY(enc_product(e, L.o, e->att16, n, e->x, 3));
+        launch_enc_norm(s, n, e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
+        TB_TRY(enc_product(e, L.up, e->a16, n, e->g16, c.gated == 2 ? 8 : c.gated ? 4 : 5));
+        TB_TRY(enc_product(e, L.down, e->g16, n, e->x, 3));
+    }
+    launch_enc_norm(s, n, e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
+    enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
+// One batch (Encoder::encode, encoder/run.rs:379-410): its inputs written and copied, then the kernels, as the graph of the
+// batch's padded shape, recorded the first time the shape is seen.
+int enc_batch(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host) {
+    cudaStream_t s = e->ctx->stream;
+    uint32_t *hi, *hp, *ht, *hs, *hl;
+    enc_inputs(e, e->stage, hi, hp, ht, hs, hl);
+    uint32_t T = 0, tiles = 0;
+    for (uint32_t q = 0; q < sequences; q++) {
+        hs[q] = T, hl[q] = lens[q];
+        for (uint32_t i = 0; i < lens[q]; i++) hi[T + i] = ids[T + i], hp[T + i] = i;
+        for (uint32_t q0 = 0; q0 < lens[q]; q0 += QT, tiles++) ht[3 * tiles] = T, ht[3 * tiles + 1] = lens[q], ht[3 * tiles + 2] = q0;
+        T += lens[q];
+    }
+    const uint32_t n = (T + QT - 1) / QT * QT, slots = n / QT + sequences;
+    for (uint32_t i = T; i < n; i++) hi[i] = 0, hp[i] = 0;
+    for (uint32_t i = 3 * tiles; i < 3 * slots; i++) ht[i] = 0;
+    e->tokens = T;
+    TB_CUDA(cudaMemcpyAsync(e->inputs, e->stage, e->input_words * 4, cudaMemcpyHostToDevice, s));
+    if (!e->use_graphs) {
+        TB_TRY(enc_layers(e, n, slots, sequences));
+    } else {
+        size_t at = 0;
+        while (at < e->graphs.size() && !(e->graphs[at].padded == n && e->graphs[at].sequences == sequences)) at++;
+        if (at == e->graphs.size()) {
+            if (!e->warmed) {  // every kernel once outside a recording: their first launches set function attributes
+                TB_TRY(enc_layers(e, n, slots, sequences));
+                e->warmed = true;
+            }
+            TB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            const int st = enc_layers(e, n, slots, sequences);
+            cudaGraph_t graph = nullptr;
+            const cudaError_t ec = cudaStreamEndCapture(s, &graph);
+            if (st != OK || ec != cudaSuccess) {
+                if (graph) cudaGraphDestroy(graph);
+                return st != OK ? st : cuda_fail(ec, "tb_encoder_embed: recording the batch");
+            }
+            EGraph g;
+            g.padded = n, g.sequences = sequences;
+            const cudaError_t ei = cudaGraphInstantiate(&g.exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (ei != cudaSuccess) return cuda_fail(ei, "tb_encoder_embed: cudaGraphInstantiate");
+            if (e->graphs.size() == ENC_GRAPHS) {
+                cudaGraphExecDestroy(e->graphs.front().exec);
+                e->graphs.erase(e->graphs.begin());
+            }
+            e->graphs.push_back(g);
+            at = e->graphs.size() - 1;
+        }
+        TB_CUDA(cudaGraphLaunch(e->graphs[at].exec, s));
+    }
+    if (out_host) TB_CUDA(cudaMemcpyAsync(out_host, e->pooled, (size_t)sequences * e->cfg.dims * 4, cudaMemcpyDeviceToHost, s));
+    TB_CUDA(cudaStreamSynchronize(s));
+    return OK;
 }
 
 }  // namespace
@@ -469,26 +600,34 @@ int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t toke
     *out = nullptr;
     TB_TRY(enc_validate(*cfg));
     tb_encoder* e = new tb_encoder();
-    e->ctx = ctx, e->cfg = *cfg, e->cap_tokens = tokens, e->cap_seqs = sequences;
+    e->ctx = ctx, e->cfg = *cfg, e->cap_tokens = tokens, e->cap_padded = (tokens + QT - 1) / QT * QT, e->cap_seqs = sequences;
     e->global.resize(cfg->layers);
     for (uint32_t l = 0; l < cfg->layers; l++) e->global[l] = cfg->global ? cfg->global[l] : (l % (cfg->global_every ? cfg->global_every : 3) == 0);
     e->cfg.global = nullptr;
     e->layers.resize(cfg->layers);
+    const char* env = getenv("TACHYON_B200_ENCODER_GRAPHS");
+    e->use_graphs = !(env && env[0] == '0');
     e->arena_bytes = enc_layout(e, nullptr);
     cudaError_t err = cudaSetDevice(ctx->gpu);
     if (err == cudaSuccess) err = cudaMalloc(&e->arena, e->arena_bytes);
     if (err == cudaSuccess) err = cudaMemsetAsync(e->arena, 0, e->arena_bytes, ctx->stream);
+    if (err == cudaSuccess) err = cudaMallocHost(&e->stage, e->input_words * 4);
     if (err != cudaSuccess) {
-        delete e;
+        tb_encoder_close(e);
         return cuda_fail(err, "tb_encoder_open");
     }
     enc_layout(e, e->arena);
-    // RoPE frequencies theta^(-2j/d): global layers', sliding layers' (encoder/run.rs:525-537 builds tables of these).
-    const uint32_t d = cfg->hidden / cfg->heads;
+    enc_inputs(e, e->inputs, e->ids, e->pos, e->tiles, e->starts, e->lens);
+    // RoPE's cosines and sines of every position a sequence can have, in f64 and rounded once (rope_tables, encoder/run.rs:523-537).
+    const uint32_t half = cfg->hidden / cfg->heads / 2;
+    std::vector<float2> table((size_t)tokens * half);
     for (int k = 0; k < 2; k++) {
-        std::vector<float> f(d / 2);
-        for (uint32_t j = 0; j < d / 2; j++) f[j] = powf(k ? cfg->theta_local : cfg->theta_global, -2.0f * (float)j / (float)d);
-        err = cudaMemcpyAsync(e->freq[k], f.data(), f.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        const double theta = (double)(k ? cfg->theta_local : cfg->theta_global);
+        for (uint32_t j = 0; j < half; j++) {
+            const double f = pow(theta, -2.0 * (double)j / (double)(2 * half));
+            for (uint32_t p = 0; p < tokens; p++) table[(size_t)p * half + j] = make_float2((float)cos((double)p * f), (float)sin((double)p * f));
+        }
+        err = cudaMemcpyAsync(e->rope[k], table.data(), table.size() * 8, cudaMemcpyHostToDevice, ctx->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
         if (err != cudaSuccess) {
             tb_encoder_close(e);
@@ -502,7 +641,13 @@ int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t toke
 void tb_encoder_close(tb_encoder* e) {
     if (!e) return;
     if (e->ctx && e->ctx->stream) cudaStreamSynchronize(e->ctx->stream);
+    for (EGraph& g : e->graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    for (ELayer& L : e->layers)
+        for (EMat* m : {&L.qkv, &L.o, &L.up, &L.down})
+            if (m->f16) cudaFree(m->f16);
     if (e->arena) cudaFree(e->arena);
+    if (e->stage) cudaFreeHost(e->stage);
     delete e;
 }
 
@@ -510,22 +655,52 @@ int tb_encoder_load(tb_encoder* e, const char* name, const void* data, size_t by
     if (!e || !name || !data) return fail(OUT_OF_RANGE, "tb_encoder_load: null argument");
     ENamed t;
     if (!enc_find(e, name, t)) return fail(NO_MODEL, std::string("tb_encoder_load: no tensor named ") + name);
-    if (bytes != t.bytes) return fail(FORMAT, std::string("tb_encoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
     cudaStream_t s = e->ctx->stream;
-    if (t.kind == 0) {
+    TB_CUDA(cudaSetDevice(e->ctx->gpu));
+    if (t.kind == 3) {  // a matrix under its plain name: Q8E codes or f16, told apart by the size
+        EMat& m = *t.mat;
+        if (bytes == m.code_bytes()) {
+            t.ptr = m.w, t.bytes = bytes, t.kind = 1;
+            if (m.f16) cudaFree(m.f16), m.f16 = nullptr;
+        } else if (bytes == 2 * m.code_bytes()) {
+            if (!m.f16) TB_CUDA(cudaMalloc(&m.f16, bytes));
+            t.ptr = m.f16, t.bytes = bytes;
+        } else {
+            return fail(FORMAT, std::string("tb_encoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, neither i8 nor f16 of its shape");
+        }
+    }
+    if (bytes != t.bytes) return fail(FORMAT, std::string("tb_encoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
+    if (t.kind == 0 || (t.kind != 4 && !t.gated_up)) {
         TB_CUDA(cudaMemcpyAsync(t.ptr, data, bytes, cudaMemcpyHostToDevice, s));
         TB_CUDA(cudaStreamSynchronize(s));
         return OK;
     }
-    // The gated MLP's Wi: activation rows, then gate rows in the file; pairs side by side on the device, so that a GEMM
-    // tile holds both (encoder/run.rs:449-466).
-    void* tmp = nullptr;
+    // Through a scratch copy.  The gated MLP's Wi: activation rows, then gate rows in the file; pairs side by side on the
+    // device, so that a GEMM tile holds both (Encoder::interleave, encoder/run.rs:449-466).  Q8E scales: rounded to f16,
+    // one per 32.
+    void *tmp = nullptr, *tmp2 = nullptr;
     TB_CUDA(cudaMalloc(&tmp, bytes));
     cudaError_t err = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, s);
     int st = OK;
-    if (err == cudaSuccess) st = launch_interleave_rows(e->ctx, tmp, t.ptr, e->cfg.inter, (uint32_t)(bytes / (2 * (size_t)e->cfg.inter)));
+    const uint32_t inter = e->cfg.inter;
+    if (err == cudaSuccess && t.kind == 4) {
+        const void* src = tmp;
+        if (t.gated_up) {
+            err = cudaMalloc(&tmp2, bytes);
+            if (err == cudaSuccess) st = launch_interleave_rows(e->ctx, tmp, tmp2, inter, (uint32_t)(bytes / (2 * (size_t)inter)));
+            src = tmp2;
+        }
+        if (err == cudaSuccess && st == OK) {
+            const size_t n = bytes / 4;
+            enc_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const float*>(src), static_cast<__half*>(t.ptr), n);
+            err = cudaGetLastError();
+        }
+    } else if (err == cudaSuccess) {
+        st = launch_interleave_rows(e->ctx, tmp, t.ptr, inter, (uint32_t)(bytes / (2 * (size_t)inter)));
+    }
     if (err == cudaSuccess) err = cudaStreamSynchronize(s);
     cudaFree(tmp);
+    if (tmp2) cudaFree(tmp2);
     if (err != cudaSuccess) return cuda_fail(err, "tb_encoder_load");
     return st;
 }
@@ -574,54 +749,29 @@ int tb_encoder_fill_random(tb_encoder* e, uint64_t seed) {
 }
 
 // Encoder::embeddings (encoder/run.rs:161-175): `ids` packed back to back, `lens[s]` tokens per sequence; out (host)
-// receives dims floats per sequence.
+// receives dims floats per sequence.  The sequences go in batches of at most the capacity's tokens (and sequences), in
+// order, a batch closed by the first sequence that no longer fits (Encoder::batches, run.rs:207-221).
 int tb_encoder_embed(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host) {
     if (!e || !ids || !lens || sequences == 0) return fail(OUT_OF_RANGE, "tb_encoder_embed: null or empty argument");
-    if (sequences > e->cap_seqs) return fail(TOO_LONG, "tb_encoder_embed: more sequences than the encoder was opened for");
     const tb_encoder_config& c = e->cfg;
-    tb_context* ctx = e->ctx;
-    cudaStream_t s = ctx->stream;
-    const uint32_t h = c.hidden, d = h / c.heads;
-    // Host side of a batch: positions within each sequence, the 64-query tile list [start, len, first query] (run.rs:354-373).
-    std::vector<uint32_t> pos, tiles, starts(sequences);
-    uint32_t T = 0;
+    size_t total = 0;
     for (uint32_t q = 0; q < sequences; q++) {
         if (lens[q] == 0) return fail(OUT_OF_RANGE, "tb_encoder_embed: an empty sequence");
-        starts[q] = T;
-        for (uint32_t i = 0; i < lens[q]; i++) pos.push_back(i);
-        for (uint32_t q0 = 0; q0 < lens[q]; q0 += QT) tiles.insert(tiles.end(), {T, lens[q], q0});
-        T += lens[q];
-        if (T > e->cap_tokens) return fail(TOO_LONG, "tb_encoder_embed: more tokens than the encoder was opened for");
+        if (lens[q] > e->cap_tokens) return fail(TOO_LONG, "tb_encoder_embed: a sequence of " + std::to_string(lens[q]) + " tokens, more than the " + std::to_string(e->cap_tokens) + " the encoder was opened for");
+        total += lens[q];
     }
-    for (uint32_t i = 0; i < T; i++)
+    for (size_t i = 0; i < total; i++)
         if (ids[i] >= c.vocab) return fail(OUT_OF_RANGE, "tb_encoder_embed: token outside the vocabulary");
-    e->tokens = T;
-    const uint32_t ntiles = (uint32_t)tiles.size() / 3;
-    TB_CUDA(cudaMemcpyAsync(e->ids, ids, (size_t)T * 4, cudaMemcpyHostToDevice, s));
-    TB_CUDA(cudaMemcpyAsync(e->pos, pos.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s));
-    TB_CUDA(cudaMemcpyAsync(e->tiles, tiles.data(), tiles.size() * 4, cudaMemcpyHostToDevice, s));
-    TB_CUDA(cudaMemcpyAsync(e->starts, starts.data(), (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
-    TB_CUDA(cudaMemcpyAsync(e->lens, lens, (size_t)sequences * 4, cudaMemcpyHostToDevice, s));
-    // embeddings -> norm: x (f32 residual stream) and, since layer 0 has no attention norm, its f16 GEMM input
-    launch_enc_norm(s, T, nullptr, e->embed, e->ids, e->embed_norm, h, c.eps, e->x, e->a16);
-    for (uint32_t l = 0; l < c.layers; l++) {
-        ELayer& L = e->layers[l];
-        if (l > 0) launch_enc_norm(s, T, e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
-        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, e->a16, T, 3 * h, h, e->qkv16, 1));
-        enc_rope_kernel<<<(T + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->freq[L.global ? 0 : 1], h, d, T);
-        const int window = L.global ? -1 : (int)c.window;
-        if (d == 64) enc_attend_kernel<64><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
-        else enc_attend_kernel<32><<<dim3(ntiles, c.heads), 128, 0, s>>>(e->qkv16, e->tiles, e->att16, h, window);
-        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, e->att16, T, h, h, e->x, 3));
-        launch_enc_norm(s, T, e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
-        TB_TRY(launch_gemm_q8(ctx, L.up.w, L.up.s, e->a16, T, L.up.rows, h, e->g16, c.gated ? 4 : 5));
-        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, e->g16, T, h, c.inter, e->x, 3));
+    TB_CUDA(cudaSetDevice(e->ctx->gpu));
+    uint32_t from = 0, used = 0;
+    size_t first = 0;  // of the open batch: its first sequence, its tokens so far, its first token
+    for (uint32_t q = 0; q <= sequences; q++) {
+        if (q == sequences || used + lens[q] > e->cap_tokens || q - from == e->cap_seqs) {
+            TB_TRY(enc_batch(e, ids + first, lens + from, q - from, out_host ? out_host + (size_t)from * c.dims : nullptr));
+            first += used, from = q, used = 0;
+        }
+        if (q < sequences) used += lens[q];
     }
-    launch_enc_norm(s, T, e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
-    enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
-    TB_CUDA(cudaGetLastError());
-    if (out_host) TB_CUDA(cudaMemcpyAsync(out_host, e->pooled, (size_t)sequences * c.dims * 4, cudaMemcpyDeviceToHost, s));
-    TB_CUDA(cudaStreamSynchronize(s));
     return OK;
 }
 
@@ -631,5 +781,9 @@ int tb_encoder_hidden(tb_encoder* e, float* out_host) {
     TB_CUDA(cudaStreamSynchronize(e->ctx->stream));
     return OK;
 }
+
+uint32_t tb_encoder_batch_tokens(const tb_encoder* e) { return e ? e->tokens : 0; }
+
+uint32_t tb_encoder_graphs(const tb_encoder* e) { return e ? (uint32_t)e->graphs.size() : 0; }
 
 }  // extern "C"

@@ -106,6 +106,7 @@ struct GemmArgs {
     int mode;  // 0: f32 [M, N]; 1: f16 [M, N]; 2: GeGLU (tanh) of column pairs, f16 [M, N / 2]; 3: f32 [M, N] += D;
                // 4: GeGLU (erf) of column pairs, f16 [M, N / 2]; 5: GELU (erf), f16 [M, N]; 7: ReLU, f16 [M, N];
                // 8: SiLU(even) * odd of column pairs, f16 [M, N / 2] (the reference's store modes 3 and 5, ptx/encoder.rs:5-9)
+    const float* bias;  // f32 [N] added to every token's sums before the mode's store, or null (ptx/encoder.rs:418-436)
 };
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + exp2f(-1.4426950408889634f * v)); }
@@ -296,6 +297,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             tmem_load32(tmem + ((32 * q) << 16) + mt * BN + cb * 32, r);
             if (m < g.M && ok) {
                 const uint32_t col = n0 + cb * 32;
+                if (g.bias != nullptr && col < g.N) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col) + i);
+                        r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + b.x), r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + b.y);
+                        r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + b.z), r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + b.w);
+                    }
+                }
                 if (g.mode == 3) {
                     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
 #pragma unroll
@@ -366,12 +375,13 @@ EncodeTiled encode_tiled() {
 }  // namespace
 
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                   uint32_t wbits, const float* mul, uint32_t mul_stride) {
+                   uint32_t wbits, const float* mul, uint32_t mul_stride, const float* bias) {
     if (!w || (!s && wbits != 16) || !a || !out || M == 0 || N == 0 || K == 0) return fail(OUT_OF_RANGE, "gemm: null or empty argument");
     if (K % BK != 0) return fail(OUT_OF_RANGE, "gemm: K must be a multiple of 64");
     if (N % 32 != 0 || ((mode == 2 || mode == 4 || mode == 8) && N % 64 != 0)) return fail(OUT_OF_RANGE, "gemm: N must be a multiple of 32 (64 with a gated output)");
     if (mode < 0 || mode > 8) return fail(OUT_OF_RANGE, "gemm: unknown output mode");
     if (mode == 6) {  // only the persistent schedule has this epilogue
+        if (bias != nullptr) return fail(UNSUPPORTED, "gemm: a bias has no place beside a multiplier");
         if (!mul || mul_stride < N || (reinterpret_cast<uintptr_t>(mul) & 15) || mul_stride % 4 != 0) return fail(OUT_OF_RANGE, "gemm: the multiplier must be present, 16-byte aligned and at least N wide");
         if (!gemm_persistent_supports(N, K, wbits)) return fail(UNSUPPORTED, "gemm: no kernel for this shape with a multiplier");
         if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "gemm: weights are 8 or 4 bits");
@@ -382,7 +392,8 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     if (wbits != 8 && wbits != 4 && wbits != 16) return fail(OUT_OF_RANGE, "gemm: weights are 16, 8 or 4 bits");
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
-    if (wbits != 16 && mode != 7 && mode != 8) {  // f16 weights and the two rarer outputs: this file's kernel only
+    if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15)) return fail(OUT_OF_RANGE, "gemm: the bias must be 16-byte aligned");
+    if (wbits != 16 && mode != 7 && mode != 8 && bias == nullptr) {  // f16 weights, a bias and the two rarer outputs: this file's kernel only
         // Schedules: this file's one tile per block; gemm2.cu's persistent blocks, whose epilogue overlaps the next tile's
         // products and whose MMAs read less shared memory per FLOP; gemm3.cu's pairs of SMs.  Measured on the benchmark's
         // shapes the persistent one wins where the epilogue stores f32 (plain or added to the output: 1.2 to 1.7 times
@@ -416,7 +427,7 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
-    GemmArgs g{w, s, out, M, N, K, mode};
+    GemmArgs g{w, s, out, M, N, K, mode, bias};
     const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
     if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
     else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);

@@ -215,7 +215,7 @@ int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* 
 // D[M, N] = A[M, K] (f16) x W[N, K]^T (Q8); mode 0: f32 out, 1: f16 out, 2: GeGLU of column pairs -> f16 [M, N/2].
 // mode 6 (the per-layer input's gate in prefill): out f16 [M, N] = gelu_tanh(product) * mul[m * mul_stride + n].
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                   uint32_t wbits = 8, const float* mul = nullptr, uint32_t mul_stride = 0);
+                   uint32_t wbits = 8, const float* mul = nullptr, uint32_t mul_stride = 0, const float* bias = nullptr);
 
 // ---- prefill kernels around the GEMMs (prefill.cu) ---------------------------------------------------------------------
 int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out,
@@ -251,6 +251,17 @@ int launch_fill_scales(tb_context* ctx, uint64_t seed, uint64_t stream_id, __hal
 int launch_fill_gauss_f16(tb_context* ctx, uint64_t seed, uint64_t stream_id, __half* x, size_t n, float mul);
 int launch_fill_uniform(tb_context* ctx, uint64_t seed, uint64_t stream_id, float* x, size_t n, float lo, float hi);
 int launch_interleave_rows(tb_context* ctx, const void* src, void* dst, uint32_t half_rows, uint32_t row_bytes);
+
+// The encoder's kernels by the reference's argument lists (enc_ref.cu, encoder.cu).  kind: 0 embed_f16, 1 add_rows, 2 add_rows_f16,
+// 3 gather_rows.  window < 0: every key of the sequence.
+int launch_quant_f16(tb_context* ctx, const __half* a, int8_t* q, float* s, uint32_t cols, uint32_t tokens);
+int launch_norm_f16(tb_context* ctx, const float* x, const float* gamma, const float* beta, __half* a, float* xo, uint32_t h, float eps, uint32_t n);
+int launch_rows(tb_context* ctx, int kind, const void* table, const uint32_t* idx, float* out, uint32_t h, uint32_t n);
+int launch_gelu_f16(tb_context* ctx, const float* x, __half* out, uint32_t width, uint32_t len, uint32_t gated);
+int launch_rope_f16(tb_context* ctx, __half* qkv, const float* table, const uint32_t* pos, uint32_t h, uint32_t d, uint32_t n);
+int launch_gemm_q8e(tb_context* ctx, const int8_t* a, const int8_t* w, const float* bias, void* y, uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t mode,
+                    const float* sa, const float* sw);
+int launch_enc_attend(tb_context* ctx, const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, uint32_t d, int window, float scale, uint32_t ntiles);
 
 // The reference's own formats (q4.cu): f32 -> Q8 codes and [s, s * sum q] pairs; Q4 weights x Q8 activations.
 int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t n);

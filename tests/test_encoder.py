@@ -41,7 +41,10 @@ def quantize(w: np.ndarray):
     return codes.reshape(rows, cols), scale.view(np.uint16), deq
 
 
-def build(ctx, cfg, weights, tokens=1024, sequences=16, mean_pool=0, dims=None):
+def build(ctx, cfg, weights, tokens=1024, sequences=16, mean_pool=0, dims=None, fmt="q8"):
+    """An encoder with `weights` loaded as this build's Q8 ("q8"), as a converted model's Q8E matrices and f32 scales per 64
+    ("q8e", crates/tachyon/src/encoder/convert.rs:8-9) or as its f16 matrices ("f16"); and the weights the GPU then multiplies
+    with, as f32."""
     import tachyon_b200 as tb
 
     glob = np.array([1 if g else 0 for g in cfg["global"]], np.uint8)
@@ -51,7 +54,16 @@ def build(ctx, cfg, weights, tokens=1024, sequences=16, mean_pool=0, dims=None):
     enc = tb.Encoder(ctx, ec, tokens=tokens, sequences=sequences)
     deq = dict(weights)
     for name, w in weights.items():
-        if w.ndim == 2 and name != "embed":
+        if w.ndim == 2 and name != "embed" and fmt == "q8e":
+            q, sc = oracle.q8e(w)
+            enc.load(name, q.reshape(w.shape))
+            enc.load(name + ".scale", sc.reshape(w.shape[0], -1))
+            # the device keeps the scales as f16
+            deq[name] = (q.reshape(w.shape[0], -1, 64).astype(np.float32) * sc.astype(np.float16).astype(np.float32).reshape(w.shape[0], -1, 1)).reshape(w.shape)
+        elif w.ndim == 2 and name != "embed" and fmt == "f16":
+            enc.load(name, w.astype(np.float16))
+            deq[name] = w.astype(np.float16).astype(np.float32)
+        elif w.ndim == 2 and name != "embed":
             codes, scales, d = quantize(w)
             enc.load(name + ".w", codes)
             enc.load(name + ".s", scales)
@@ -131,17 +143,129 @@ def test_benchmark_variant_plain_ffn_mean_pool_truncated(ctx):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt,bound,cosine", [("q8e", 2e-2, 0.9999), ("f16", 1e-2, 0.99999)])
+def test_a_converted_models_matrices_load_as_they_are(ctx, fmt, bound, cosine):
+    """The tiny encoder with its layers in Q8E or f16, as the reference's conversion writes them (encoder/convert.rs:79-95;
+    crates/tachyon/tests/encoder.rs:410-441 wants a cosine of 0.99999 of the f32 reference in Q8 on its own tiny model)."""
+    cfg, weights, cases = fixture()
+    enc, deq = build(ctx, cfg, weights, fmt=fmt)
+    for ids, hidden in cases:
+        enc.embed([ids])
+        got = enc.hidden()
+        want = oracle.encoder_forward(cfg, deq, ids)
+        assert np.abs(got - want).max() < bound, float(np.abs(got - want).max())
+        ref = hidden.reshape(len(ids), -1)
+        cos = (got * ref).sum(1) / (np.linalg.norm(got, axis=1) * np.linalg.norm(ref, axis=1))
+        assert cos.min() > cosine, float(cos.min())
+    enc.close()
+
+
+def random_model(rng, h=256, heads=4, inter=512, vocab=500, layers=3, gated=1):
+    cfg = {"hidden": h, "heads": heads, "inter": inter, "vocab": vocab, "window": 8, "gated": gated, "theta_global": 160000.0, "theta_local": 10000.0, "eps": 1e-5,
+           "global": [l % 3 == 0 for l in range(layers)]}
+    weights = {"embed": rng.standard_normal((vocab, h)).astype(np.float32), "embed_norm": rng.uniform(0.5, 1.5, h).astype(np.float32),
+               "final_norm": rng.uniform(0.5, 1.5, h).astype(np.float32)}
+    for l in range(layers):
+        if l > 0:
+            weights[f"{l}.attn_norm"] = rng.uniform(0.5, 1.5, h).astype(np.float32)
+        weights[f"{l}.mlp_norm"] = rng.uniform(0.5, 1.5, h).astype(np.float32)
+        for name, shape in (("qkv", (3 * h, h)), ("o", (h, h)), ("up", ((2 if gated else 1) * inter, h)), ("down", (h, inter))):
+            weights[f"{l}.{name}"] = (rng.standard_normal(shape) * 0.05).astype(np.float32)
+    return cfg, weights
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["q8", "q8e", "f16"])
+def test_a_silu_gate(ctx, fmt):
+    """Config::silu (encoder/mod.rs:55-56): the gate is a SiLU, store mode 5 of the up product."""
+    rng = np.random.default_rng(21)
+    cfg, weights = random_model(rng, gated=2)
+    enc, deq = build(ctx, cfg, weights, fmt=fmt)
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (33, 90)]
+    enc.embed(seqs)
+    hidden, at = enc.hidden(), 0
+    for q in seqs:
+        want = oracle.encoder_forward(cfg, deq, q)
+        assert np.abs(hidden[at:at + len(q)] - want).max() < 3e-2, float(np.abs(hidden[at:at + len(q)] - want).max())
+        at += len(q)
+    # and it is not the GELU gate
+    other = oracle.encoder_forward(dict(cfg, gated=1), deq, seqs[0])
+    assert np.abs(hidden[:len(seqs[0])] - other).max() > 5e-2
+    enc.close()
+
+
+@pytest.mark.gpu
+def test_batches_fill_the_capacity_in_order(ctx):
+    """Encoder::batches (encoder/run.rs:207-221): more tokens than the capacity go in several batches, each closed by the
+    first sequence that no longer fits; every sequence's embedding has the bits it has alone.  A batch runs as the graph of
+    its padded shape (run.rs:379-410), recorded once."""
+    import tachyon_b200 as tb
+
+    cfg, weights, _ = fixture()
+    enc, _ = build(ctx, cfg, weights, tokens=128, sequences=4)
+    rng = np.random.default_rng(5)
+    lens = (40, 40, 40, 100, 28, 1, 1, 1, 1, 1, 128)  # batches: [40 40 40] [100 28] [1 1 1 1] (four sequences) [1] [128]
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in lens]
+    got = enc.embed(seqs)
+    assert enc.hidden().shape[0] == 128, "the last batch is the last sequence"
+    assert enc.graphs() == 5  # padded tokens and sequences: (128, 3), (128, 2), (64, 4), (64, 1), (128, 1)
+    assert np.allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-5)
+    big, _ = build(ctx, cfg, weights, tokens=1024, sequences=16)
+    assert np.array_equal(big.embed(seqs), got), "one batch or five: the same bits"
+    big.close()
+    enc.close()
+
+
+@pytest.mark.gpu
+def test_a_batchs_graph_gives_the_bits_of_its_kernels(ctx, monkeypatch):
+    cfg, weights, _ = fixture()
+    rng = np.random.default_rng(6)
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (40, 40, 40, 100, 28, 1, 1, 1, 1, 1, 128)]
+    enc, _ = build(ctx, cfg, weights, tokens=128, sequences=4)
+    got = enc.embed(seqs)
+    again = enc.embed(seqs)  # every shape now replays
+    assert enc.graphs() == 5
+    for i, q in enumerate(seqs):
+        assert np.array_equal(enc.embed([q])[0], got[i]), i
+    assert np.array_equal(got, again)
+    enc.close()
+    monkeypatch.setenv("TACHYON_B200_ENCODER_GRAPHS", "0")
+    plain, _ = build(ctx, cfg, weights, tokens=128, sequences=4)
+    assert np.array_equal(plain.embed(seqs), got) and plain.graphs() == 0
+    plain.close()
+
+
+@pytest.mark.gpu
+def test_sixteen_shapes_are_kept(ctx):
+    """GRAPHS = 16 (encoder/run.rs:20): the oldest shape is dropped for the seventeenth."""
+    cfg, weights, _ = fixture()
+    enc, _ = build(ctx, cfg, weights, tokens=1280, sequences=4)
+    first = enc.embed([[5] * 10, [6] * 3])
+    for n in range(1, 19):
+        enc.embed([[7] * (64 * n)])
+        assert enc.graphs() == min(n + 1, 16)
+    assert np.array_equal(enc.embed([[5] * 10, [6] * 3]), first), "a dropped shape is recorded again"
+    enc.close()
+
+
+@pytest.mark.gpu
 def test_encoder_refuses_what_it_cannot_hold(ctx):
     import tachyon_b200 as tb
 
     cfg, weights, _ = fixture()
     enc, _ = build(ctx, cfg, weights, tokens=64, sequences=2)
+    assert enc.embed([[1] * 40, [2] * 40]).shape == (2, cfg["hidden"])  # two batches
     with pytest.raises(tb.Error) as e:
-        enc.embed([[1] * 40, [2] * 40])
-    assert e.value.status == 6
-    with pytest.raises(tb.Error) as e:
-        enc.embed([[1], [2], [3]])
-    assert e.value.status == 6
+        enc.embed([[1] * 10, [2] * 65])
+    assert e.value.status == 6  # TB_TOO_LONG (Error::TooLong, run.rs:208-210)
+    with pytest.raises(tb.Error):
+        enc.embed([[1], []])
     with pytest.raises(tb.Error):
         enc.embed([[cfg["vocab"]]])
+    with pytest.raises(tb.Error) as e:
+        enc.load("0.qkv", np.zeros(7, np.int8))
+    assert e.value.status == 5
+    with pytest.raises(tb.Error) as e:
+        enc.load("9.qkv", np.zeros(7, np.int8))
+    assert e.value.status == 8
     enc.close()

@@ -110,3 +110,34 @@ def test_attention_oracle_matches_plain_numpy_in_plain_mode():
         assert np.allclose(out[h * d:][:d], want, rtol=1e-10, atol=1e-12)
     # the new key/value landed in slot pos % cap, rounded to f16
     assert np.array_equal(kb.reshape(kv, cap, d)[0, pos % cap], qkv[heads * d:][:d].astype(np.float16).view(np.uint16))
+
+
+def test_q8e_is_q8_in_blocks_of_64_with_the_scale_alone():
+    # quant.rs:107-115 over the vector of quant.rs:272-277: the largest magnitude of a block over 127, ties to even
+    x = np.concatenate([np.arange(64, dtype=np.float32) - 20.0, np.zeros(64, np.float32), np.full(64, 0.5, np.float32)])
+    q, s = oracle.q8e(x)
+    assert s.shape == (3,) and s[0] == np.float32(43.0) / np.float32(127.0) and s[1] == 0.0 and s[2] == np.float32(0.5) / np.float32(127.0)
+    inv = np.float32(127.0) / np.float32(43.0)
+    assert np.array_equal(q[:64], np.rint(x[:64] * inv).astype(np.int8)) and not q[64:128].any() and np.all(q[128:] == 127)
+
+
+def test_the_q8e_product_is_the_sum_of_scaled_integer_sums():
+    # crates/tachyon/tests/encoder.rs:329-331: the product of the dequantised values, within the test's bound
+    rows, cols, tokens = 64, 192, 5
+    (aq, sa), (wq, sw) = oracle.q8e(values(tokens * cols, 8)), oracle.q8e(values(rows * cols, 9))
+    bias = values(rows, 10)
+    got = oracle.gemm_q8e(aq, sa, wq, sw, rows, bias)
+    a = aq.astype(np.float64).reshape(tokens, cols // 64, 64) * sa.astype(np.float64).reshape(tokens, cols // 64, 1)
+    w = wq.astype(np.float64).reshape(rows, cols // 64, 64) * sw.astype(np.float64).reshape(rows, cols // 64, 1)
+    want = a.reshape(tokens, cols) @ w.reshape(rows, cols).T + bias
+    # -12582912 s is rounded before the fused multiply-add takes it (ptx/encoder.rs:362): each group carries up to half a unit
+    # in the last place of 12582912 s, times the row's scale; the reference's own bound is 1e-3 + 2e-3 |want|
+    assert np.abs(got - want).max() < 3e-4
+    assert np.array_equal(oracle.gemm_q8e(aq, sa, wq, sw, rows), oracle.gemm_q8e(aq, sa, wq, sw, rows, np.zeros(rows, np.float32)))
+
+
+def test_rope_table_holds_cos_and_sin_of_each_position():
+    # encoder/run.rs:523-537
+    t = oracle.rope_table(10000.0, 5, 8)
+    assert t.shape == (5, 4, 2) and np.all(t[0, :, 0] == 1.0) and np.all(t[0, :, 1] == 0.0)
+    assert t[3, 2, 0] == np.float32(np.cos(3 * 10000.0 ** -0.5)) and t[3, 2, 1] == np.float32(np.sin(3 * 10000.0 ** -0.5))
