@@ -90,8 +90,10 @@ TB_API int tb_selftest_wait(tb_context* ctx, uint64_t limit_ns);
 /* Context::alloc / DevBuf drop (cuda/mod.rs:292-298, 337-375). */
 TB_API int tb_alloc(tb_context* ctx, size_t bytes, void** dev);
 TB_API int tb_free(tb_context* ctx, void* dev);
-/* Context::alloc_host: pinned, device-mapped host memory. */
+/* Context::alloc_host: pinned, device-mapped host memory.  tb_host_device_ptr is HostBuf::device_ptr (cuda/mod.rs:337-375):
+ * the address kernels read it at. */
 TB_API int tb_alloc_host(tb_context* ctx, size_t bytes, void** host);
+TB_API int tb_host_device_ptr(tb_context* ctx, void* host, void** dev);
 TB_API int tb_free_host(tb_context* ctx, void* host);
 /* Stream::upload / download / fill / sync (cuda/mod.rs:382-411).  Copies are queued on the context's stream; the
  * caller keeps host memory alive until tb_sync. */
@@ -366,6 +368,8 @@ typedef struct tb_settings {
     uint32_t fused;        /* != 0: the whole step as one persistent kernel with grid barriers instead of 2 + 5*layers launches */
     uint32_t weight_bits;  /* 0 or 8: int8 codes with an f16 scale per 32 (TB_WEIGHTS_Q8); 4: the reference's converted Q4
                               matrices as they are in weights.wpk, u8 [rows, cols/2] and f16 [rows, cols/64] (TB_WEIGHTS_Q4) */
+    uint32_t host_table;   /* != 0: the per-layer table (embed_per_layer, the reference's host.wpk) stays in pinned, mapped host
+                              memory and every step reads its token's row from there (decode.rs:477-483, 572-573); 0: in HBM */
 } tb_settings;
 enum { TB_WEIGHTS_Q8 = 8, TB_WEIGHTS_Q4 = 4 };
 

@@ -91,6 +91,7 @@ def _declare(l: C.CDLL) -> None:
         "tbo_fill_gauss_f16": (None, [u64, u64, vp, sz, f32]),
         "tbo_fill_gauss_f32": (None, [u64, u64, vp, sz, f32]),
         "tbo_decoder_step": (C.c_int32, [C.POINTER(Model), u32, u32, vp, i32, vp]),
+        "tbo_gemv_q4_narrow": (None, [vp, vp, vp, vp, sz, sz, vp]),
         "tbo_gemm_q8e": (None, [vp, vp, vp, vp, vp, sz, sz, sz, vp]),
         "tbo_encoder_forward": (None, [C.POINTER(EncConfig), vp, vp, C.POINTER(EncLayer), vp, vp, sz, vp]),
         "tbo_erf_as": (f32, [f32]),
@@ -182,6 +183,15 @@ def gemv_q4(packed, scales, q, pairs, rows: int):
     pairs = np.ascontiguousarray(pairs, np.float32)
     y = np.zeros(rows, np.float32)
     lib().tbo_gemv_q4(ptr(packed), ptr(scales), ptr(q), ptr(pairs), rows, q.size, ptr(y))
+    return y
+
+
+def gemv_q4_narrow(packed, scales, q, pairs, rows: int):
+    """The reference's gemv_q4_narrow kernel, bit for bit: rows of at most 256 weights, eight lanes a row."""
+    q = np.ascontiguousarray(q, np.int8)
+    pairs = np.ascontiguousarray(pairs, np.float32)
+    y = np.zeros(rows, np.float32)
+    lib().tbo_gemv_q4_narrow(ptr(packed), ptr(scales), ptr(q), ptr(pairs), rows, q.size, ptr(y))
     return y
 
 

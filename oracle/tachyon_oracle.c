@@ -177,14 +177,14 @@ TBO_API void tbo_product_q4(const uint8_t *packed, const uint16_t *scales, const
  * fma(fma(ss, -8, f32(sum n*q) * sx), f32(scale), sum) to the lane's f32 sum (mul.f32, fma.rn.f32, fma.rn.f32); the 32
  * sums then meet in a butterfly (shfl.bfly 16, 8, 4, 2, 1; add.f32) and lane 0 stores.  All of it is IEEE
  * round-to-nearest, so this C gives the kernel's bits. */
-TBO_API void tbo_gemv_q4(const uint8_t *packed, const uint16_t *scales, const int8_t *q, const float *pairs, size_t rows,
-                         size_t cols, float *y) {
+static void gemv_q4_lanes(const uint8_t *packed, const uint16_t *scales, const int8_t *q, const float *pairs, size_t rows, size_t cols, size_t lanes,
+                          float *y) {
     size_t nch = cols / 32;
     for (size_t r = 0; r < rows; r++) {
         float lane[32];
-        for (size_t l = 0; l < 32; l++) {
+        for (size_t l = 0; l < lanes; l++) {
             float sum = 0.0f;
-            for (size_t c = l; c < nch; c += 32) {
+            for (size_t c = l; c < nch; c += lanes) {
                 int32_t acc = 0;
                 for (size_t j = 0; j < 32; j++) {
                     size_t col = c * 32 + j, g = (r * cols + col) / 64, k = col % 64;
@@ -197,13 +197,25 @@ TBO_API void tbo_gemv_q4(const uint8_t *packed, const uint16_t *scales, const in
             }
             lane[l] = sum;
         }
-        for (size_t k = 16; k > 0; k /= 2) {
+        for (size_t k = lanes / 2; k > 0; k /= 2) {
             float next[32];
-            for (size_t l = 0; l < 32; l++) next[l] = lane[l] + lane[l ^ k];
+            for (size_t l = 0; l < lanes; l++) next[l] = lane[l] + lane[l ^ k];
             memcpy(lane, next, sizeof lane);
         }
         y[r] = lane[0];
     }
+}
+
+TBO_API void tbo_gemv_q4(const uint8_t *packed, const uint16_t *scales, const int8_t *q, const float *pairs, size_t rows,
+                         size_t cols, float *y) {
+    gemv_q4_lanes(packed, scales, q, pairs, rows, cols, 32, y);
+}
+
+/* gemv_q4_narrow (ptx/gemv.rs:7-9, 156-195 with 8 lanes): rows of at most 256 weights, eight lanes a row (lane l takes chunk
+ * l), the eight sums meeting in a butterfly over 4, 2 and 1.  The same steps as gemv_q4 in another order of additions. */
+TBO_API void tbo_gemv_q4_narrow(const uint8_t *packed, const uint16_t *scales, const int8_t *q, const float *pairs, size_t rows,
+                                size_t cols, float *y) {
+    gemv_q4_lanes(packed, scales, q, pairs, rows, cols, 8, y);
 }
 
 /* Q4 weights (quant.rs:47-82) times an f32 vector that is NOT rounded to Q8 first: y[r] = sum_g d_g sum_k (n_k - 8) x_k,
@@ -685,7 +697,8 @@ TBO_API int32_t tbo_decoder_step(tbo_model *m, uint32_t token, uint32_t pos, flo
             rms_f32(proj + l * PL, m->pl_norm, PL, c->eps, pli + l * PL);
             for (size_t i = 0; i < PL; i++) {
                 size_t at = (size_t)token * PLW + l * PL + i;
-                float e = (float)m->embed_pl[at] * tbo_f16_value(m->embed_pl_s[at / 32]) * sqrtf((float)PL);
+                float e = c->weight_bits == 4 ? (float)(nibble((const uint8_t *)m->embed_pl, at) - 8) * tbo_f16_value(m->embed_pl_s[at / 64]) * sqrtf((float)PL)
+                                              : (float)m->embed_pl[at] * tbo_f16_value(m->embed_pl_s[at / 32]) * sqrtf((float)PL);
                 pli[l * PL + i] = (pli[l * PL + i] + e) * 0.70710678118654752f;
             }
         }

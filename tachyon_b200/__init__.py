@@ -31,6 +31,32 @@ def check(status: int) -> None:
         raise Error(status, _lib.load().tb_last_error().decode())
 
 
+class HostBuf:
+    """Pinned, device-mapped host memory (cuda/mod.rs HostBuf): ``array`` is the host's view of it as bytes, ``ptr`` the address
+    kernels read it at."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx, self.nbytes = ctx, nbytes
+        p, d = C.c_void_p(), C.c_void_p()
+        check(ctx.lib.tb_alloc_host(ctx.handle, nbytes, C.byref(p)))
+        self.host = p.value
+        check(ctx.lib.tb_host_device_ptr(ctx.handle, self.host, C.byref(d)))
+        self.ptr = d.value
+        self.array = np.ctypeslib.as_array((C.c_uint8 * nbytes).from_address(self.host))
+
+    def free(self) -> None:
+        if self.host is not None and self.ctx.handle:
+            self.array = None
+            self.ctx.lib.tb_free_host(self.ctx.handle, self.host)
+        self.host = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class DevBuf:
     """Device memory owned by a context (cuda/mod.rs DevBuf): freed on ``free`` or with the object."""
 
@@ -103,6 +129,9 @@ class Context:
 
     def alloc(self, nbytes: int) -> DevBuf:
         return DevBuf(self, nbytes)
+
+    def alloc_host(self, nbytes: int) -> HostBuf:
+        return HostBuf(self, nbytes)
 
     def upload(self, a: np.ndarray) -> DevBuf:
         a = np.ascontiguousarray(a)
@@ -309,9 +338,10 @@ class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
     def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False, fused: bool = False,
-                 weight_bits: int = 8):
+                 weight_bits: int = 8, host_table: bool = False):
         self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
-        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused), weight_bits=weight_bits)
+        self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused), weight_bits=weight_bits,
+                                 host_table=int(host_table))
         h = C.c_void_p()
         check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
         self.handle = h.value

@@ -42,7 +42,7 @@ class WpkInfo(C.Structure):
 
 
 class Settings(C.Structure):
-    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32)]
+    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32), ("host_table", u32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares.
@@ -63,6 +63,7 @@ SIGNATURES = {
     "tb_free": (i32, [vp, vp]),
     "tb_alloc_host": (i32, [vp, sz, pp]),
     "tb_free_host": (i32, [vp, vp]),
+    "tb_host_device_ptr": (i32, [vp, vp, pp]),
     "tb_upload": (i32, [vp, vp, vp, sz]),
     "tb_download": (i32, [vp, vp, vp, sz]),
     "tb_fill": (i32, [vp, vp, i32, sz]),

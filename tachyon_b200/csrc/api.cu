@@ -197,6 +197,13 @@ int tb_alloc_host(tb_context* ctx, size_t bytes, void** host) {
     return OK;
 }
 
+int tb_host_device_ptr(tb_context* ctx, void* host, void** dev) {
+    if (!ctx || !host || !dev) return fail(OUT_OF_RANGE, "tb_host_device_ptr: null argument");
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaHostGetDevicePointer(dev, host, 0));
+    return OK;
+}
+
 int tb_free_host(tb_context* ctx, void* host) {
     if (!ctx) return fail(OUT_OF_RANGE, "tb_free_host: null context");
     TB_CUDA(cudaFreeHost(host));
@@ -368,6 +375,12 @@ int tb_launch(tb_context* ctx, const char* kernel, const uint32_t grid[3], const
         if (nargs != 7) return fail(OUT_OF_RANGE, "tb_launch: gemv_q4 takes 7 arguments");
         return launch_gemv_q4(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const int8_t*>(ptr(2)),
                               static_cast<const float*>(ptr(3)), static_cast<float*>(ptr(4)), u32(5), u32(6));
+    }
+    if (name == "gemv_q4_narrow") {  // gemv_q4's arguments, rows of at most 256 weights; rows / 16 (rounded up) blocks of 128 (gemv.rs:7-9)
+        TB_TRY(shape(7, 128));
+        if (grid[0] != (u32(5) + 15) / 16) return fail(OUT_OF_RANGE, "tb_launch: gemv_q4_narrow runs rows / 16 (rounded up) blocks");
+        return launch_gemv_q4_narrow(ctx, static_cast<const uint8_t*>(ptr(0)), static_cast<const uint16_t*>(ptr(1)), static_cast<const int8_t*>(ptr(2)),
+                                     static_cast<const float*>(ptr(3)), static_cast<float*>(ptr(4)), u32(5), u32(6));
     }
     if (name == "sample") {  // logits, work, vocab, cfg, state, seen, out, partial, count; grid[0] blocks of 1024
         TB_TRY(shape(9, 1024));

@@ -79,6 +79,7 @@ struct tb_decoder {
     float *pf_ple = nullptr, *pf_proj = nullptr, *pf_pli = nullptr;  // prefill: [chunk][layers * per_layer]: table rows, projections, inputs
     __half* pf_g2 = nullptr;                      // prefill: [chunk][per_layer]
     char* arena = nullptr;
+    char* host_table = nullptr;  // settings.host_table: the per-layer table, codes then scales, in pinned mapped host memory
     size_t arena_bytes = 0;
     // step buffers
     float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *y = nullptr, *g = nullptr, *logits = nullptr, *partial = nullptr;
@@ -164,7 +165,6 @@ int validate(const tb_config& c, const tb_settings& s) {
     if (c.ffn == 0 || c.ffn % 32 != 0) return fail(UNSUPPORTED, "decoder: ffn must be a multiple of 32");
     if (c.per_layer != 0) {
         if (c.per_layer % 256 != 0 || c.per_layer > 6144) return fail(UNSUPPORTED, "decoder: per_layer must be a multiple of 256 up to 6144");
-        if (s.weight_bits == 4) return fail(UNSUPPORTED, "decoder: per-layer inputs with four-bit weights (matrices 256 wide) have no product here");
         if (s.fused) return fail(UNSUPPORTED, "decoder: the single-kernel step has no per-layer inputs");
     }
     if (c.layers == 0 || c.vocab == 0 || c.window == 0) return fail(OUT_OF_RANGE, "decoder: empty model");
@@ -202,7 +202,18 @@ void layout(tb_decoder* d, char* base) {
     mat(d->embed, c.vocab, c.hidden);
     vec(d->norm, c.hidden);
     const uint32_t pl = c.per_layer, plw = c.per_layer * c.layers;
-    if (pl) mat(d->embed_pl, c.vocab, plw), mat(d->pl_model_proj, plw, c.hidden), vec(d->pl_norm, pl);
+    if (pl) {
+        if (d->settings.host_table) {
+            // The table stays in pinned, mapped host memory (the reference's host.wpk, decode.rs:477-483): a step reads its
+            // token's row from there.  One allocation, codes then scales, made by tb_decoder_open.
+            d->embed_pl.rows = c.vocab, d->embed_pl.cols = plw, d->embed_pl.bits = d->settings.weight_bits == 4 ? 4 : 8;
+            d->embed_pl.w = reinterpret_cast<int8_t*>(d->host_table);
+            d->embed_pl.s = reinterpret_cast<__half*>(d->host_table + (d->embed_pl.code_bytes() + 255) / 256 * 256);
+        } else {
+            mat(d->embed_pl, c.vocab, plw);
+        }
+        mat(d->pl_model_proj, plw, c.hidden), vec(d->pl_norm, pl);
+    }
     uint32_t max_splits = 1;
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
@@ -557,6 +568,11 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     if (e == cudaSuccess) e = cudaMalloc(&d->arena, d->arena_bytes);
     if (e == cudaSuccess) e = cudaMemsetAsync(d->arena, 0, d->arena_bytes, ctx->stream);
     if (e == cudaSuccess) e = cudaHostAlloc(&d->words, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess && cfg->per_layer && settings->host_table) {
+        const size_t bytes = (d->embed_pl.code_bytes() + 255) / 256 * 256 + d->embed_pl.scale_bytes();
+        e = cudaHostAlloc(&d->host_table, bytes, cudaHostAllocMapped);
+        if (e == cudaSuccess) memset(d->host_table, 0, bytes);
+    }
     for (int g = 0; g < 2 && e == cudaSuccess; g++) e = cudaEventCreateWithFlags(&d->done[g], cudaEventDisableTiming);
     if (e != cudaSuccess) {
         const int s = cuda_fail(e, "tb_decoder_open");
@@ -593,6 +609,7 @@ void tb_decoder_close(tb_decoder* d) {
         if (d->phase_dev[g]) cudaFree(d->phase_dev[g]);
     if (d->arena) cudaFree(d->arena);
     if (d->words) cudaFreeHost(d->words);
+    if (d->host_table) cudaFreeHost(d->host_table);
     delete d;
 }
 
@@ -608,7 +625,7 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
         return OK;
     }
     if (t.kind == 0) {
-        TB_CUDA(cudaMemcpyAsync(t.ptr, data, bytes, cudaMemcpyHostToDevice, s));
+        TB_CUDA(cudaMemcpyAsync(t.ptr, data, bytes, cudaMemcpyDefault, s));  // the per-layer table may live in host memory
         TB_CUDA(cudaStreamSynchronize(s));
         return OK;
     }

@@ -482,6 +482,32 @@ __global__ void __launch_bounds__(256) gemv_q8_generic(const GemvParams p) {
     }
 }
 
+// The same for four-bit weights (crates/tachyon/src/quant.rs:47-82: a scale per 64 along a row, so cols is a multiple of 64): the
+// reference's 256-wide per-layer projections (decode.rs:654-660) and any other width the staged kernel does not take.
+template <int XMODE, int EPI>
+__global__ void __launch_bounds__(256) gemv_q4x_generic(const GemvParams p) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), nb = p.cols / 32;
+    if (row >= p.rows) return;
+    const uint8_t* wr = reinterpret_cast<const uint8_t*>(p.w) + (size_t)row * (p.cols / 2);
+    float sum = 0.0f;
+    for (uint32_t b = lane; b < nb; b += 32) {
+        float v[32];
+        if constexpr (XMODE == X_F16) load32_f16(static_cast<const __half*>(p.x) + (size_t)b * 32, v);
+        else load32_f32(static_cast<const float*>(p.x) + (size_t)b * 32, v);
+        Planes pl;
+        make_planes(v, pl);
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(wr + (size_t)b * 16));
+        sum = fmaf(block_dot_q4(w, pl, plane_sum(pl)), __half2float(p.s[(size_t)row * (nb / 2) + (b >> 1)]) * pl.mul, sum);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) {
+        if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[row] = p.gelu_mul ? gelu_tanh(sum) * __ldg(p.gelu_mul + row) : sum;
+        else static_cast<__half*>(p.y)[row] = __float2half_rn(sum);
+    }
+}
+
 // ---- the small-footprint kernel ---------------------------------------------------------------------------------------
 //
 // For the short products of a decode step (query/key/value and output projections: a few megabytes over 148 blocks).
@@ -808,8 +834,17 @@ int launch_gemv(tb_context* ctx, const GemvParams& p) {
             case 4096: return dispatch_staged_q4<2>(ctx, p);
             case 8192: return dispatch_staged_q4<4>(ctx, p);
             case 16384: return dispatch_staged_q4<8>(ctx, p);
-            default: return fail(UNSUPPORTED, "gemv: four-bit weights need 2048, 4096, 8192 or 16384 columns");
+            default: break;
         }
+        if (p.cols % 64 != 0) return fail(OUT_OF_RANGE, "gemv: four-bit weights come in groups of 64 columns");
+        if (p.xmode == X_NORM || p.xmode == X_ATTN || p.epi == EPI_GEGLU || p.epi == EPI_ARGMAX) return fail(UNSUPPORTED, "gemv: fused prologue/epilogues need cols of 2048");
+        const dim3 grid4((p.rows + 7) / 8), block4(256);
+        if (p.xmode == X_F16 && p.epi == EPI_F32) TB_CUDA(launch_kernel(ctx, gemv_q4x_generic<X_F16, EPI_F32>, grid4, block4, 0, true, p));
+        else if (p.xmode == X_F16 && p.epi == EPI_F16) TB_CUDA(launch_kernel(ctx, gemv_q4x_generic<X_F16, EPI_F16>, grid4, block4, 0, true, p));
+        else if (p.xmode == X_F32 && p.epi == EPI_F32) TB_CUDA(launch_kernel(ctx, gemv_q4x_generic<X_F32, EPI_F32>, grid4, block4, 0, true, p));
+        else if (p.xmode == X_F32 && p.epi == EPI_F16) TB_CUDA(launch_kernel(ctx, gemv_q4x_generic<X_F32, EPI_F16>, grid4, block4, 0, true, p));
+        else return fail(UNSUPPORTED, "gemv: unknown input or output mode");
+        return OK;
     }
     switch (p.cols) {
         case 2048: return dispatch_staged<1>(ctx, p);

@@ -268,6 +268,7 @@ int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32
 int launch_geglu_q8(tb_context* ctx, const float* a, const float* b, int8_t* q, float* s, uint32_t n);
 int launch_norm_q8(tb_context* ctx, const float* h, float* h_out, const float* y, const float* w1, const float* w2, int8_t* q, float* s, uint32_t len,
                    uint32_t chunks, float eps, float scale);
+int launch_gemv_q4_narrow(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols);
 int launch_embed_q4_rows(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const uint32_t* tokens, uint32_t rows, float* out, uint32_t cols, float scale);
 int launch_gemv_q4(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols);
 

@@ -343,7 +343,34 @@ __global__ void __launch_bounds__(128) gemv_q4_generic(const Q4Params p) {
     if (lane == 0) p.y[row] = sum;
 }
 
+// gemv_q4_narrow (ptx/gemv.rs:7-9): rows of at most 256 weights, eight lanes a row (lane l of a row takes chunk l), so a warp
+// takes four rows and a block of 128 threads sixteen; the eight sums meet in a butterfly over 4, 2 and 1.
+__global__ void __launch_bounds__(128) gemv_q4_narrow_kernel(const Q4Params p) {
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 7, row = blockIdx.x * 16 + (threadIdx.x >> 3), nch = p.cols / 32;
+    float sum = 0.0f;
+    if (row < p.rows && lane < nch) {
+        const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)row * (p.cols / 2));
+        const uint4* xq = reinterpret_cast<const uint4*>(p.q);
+        const uint4 w = __ldcs(wr + lane), a = ld_cg_u4(xq + 2 * lane), b = ld_cg_u4(xq + 2 * lane + 1);
+        sum = chunk_step(chunk_dot(w, a, b), __ldcg(p.s + lane), __half2float(p.ws[(size_t)row * (p.cols / 64) + (lane >> 1)]), sum);
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+    if (lane == 0 && row < p.rows) p.y[row] = sum;
+}
+
 }  // namespace
+
+int launch_gemv_q4_narrow(tb_context* ctx, const uint8_t* w, const uint16_t* scales, const int8_t* q, const float* s, float* y, uint32_t rows, uint32_t cols) {
+    if (!w || !scales || !q || !s || !y) return fail(OUT_OF_RANGE, "gemv_q4_narrow: null argument");
+    if (rows == 0 || rows % 4 != 0 || cols == 0 || cols % 64 != 0 || cols > 256) return fail(OUT_OF_RANGE, "gemv_q4_narrow: rows a multiple of 4, columns a multiple of 64 up to 256");
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(q)) & 15) return fail(OUT_OF_RANGE, "gemv_q4_narrow: weights and codes must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(s) & 7) || (reinterpret_cast<uintptr_t>(scales) & 1)) return fail(OUT_OF_RANGE, "gemv_q4_narrow: the pairs must be 8-byte aligned");
+    Q4Params p{w, reinterpret_cast<const __half*>(scales), q, reinterpret_cast<const float2*>(s), y, rows, cols};
+    TB_CUDA(launch_kernel(ctx, gemv_q4_narrow_kernel, dim3((rows + 15) / 16), dim3(128), 0, true, p));
+    return OK;
+}
 
 int launch_quant_q8(tb_context* ctx, const float* x, int8_t* q, float* s, uint32_t n) {
     if (!x || !q || !s) return fail(OUT_OF_RANGE, "quant_q8: null argument");

@@ -412,9 +412,44 @@ def test_per_layer_inputs(ctx):
     b, lb = dec.step(prompt[-1]), dec.logits()
     assert np.abs(la - lb).max() <= 4e-3 * np.abs(la).max()
     dec.close()
-    with pytest.raises(tb.Error) as e:
-        tb.Decoder(ctx, cfg, context=96, weight_bits=4)
-    assert e.value.status == 9
+
+
+@pytest.mark.parametrize("host_table", [False, True])
+def test_per_layer_inputs_in_the_references_q4_with_the_table_in_host_memory(ctx, host_table):
+    """A converted E-model (model/mod.rs:196-204): every matrix Q4, the 256-wide per-layer projections included (decode.rs:654-660),
+    and the per-layer table either in HBM or where the reference keeps it, in pinned mapped host memory (host.wpk,
+    decode.rs:477-483), read a row a step.  Filled from the generators, and loaded tensor by tensor as a converted model's files
+    hold them: the same tokens and logits."""
+    cfg = small_config(layers=5)
+    cfg.per_layer, cfg.global_every, cfg.global_head_dim, cfg.shared = 256, 3, 512, 1
+    dec = tb.Decoder(ctx, cfg, context=96, chunk=40, keep_logits=True, weight_bits=4, host_table=host_table)
+    dec.fill_random(SEED + 9)
+    dec.build()
+    ref = OracleModel(cfg, SEED + 9, context=96, chunk=40, weight_bits=4)
+    assert ref.tensors["3.per_layer_proj.w"].shape == (cfg.hidden, 128) and ref.tensors["embed_per_layer.s"].shape == (cfg.vocab, 5 * 256 // 64)
+    other = tb.Decoder(ctx, cfg, context=96, chunk=40, keep_logits=True, weight_bits=4, host_table=host_table)
+    for name, a in ref.tensors.items():
+        other.load(name, a)
+    other.build()
+    token = 17
+    for pos in range(12):
+        want_token, want_logits, want_hidden = ref.step(token, pos)
+        got_token = dec.step(token)
+        order = np.sort(cfg.softcap * np.tanh(want_logits.astype(np.float64) / cfg.softcap))
+        check_logits(dec.logits(), want_logits, order[-1] - order[-2], got_token, want_token)
+        assert np.abs(dec.hidden() - want_hidden).max() <= 2e-3 * np.abs(want_hidden).max()
+        assert other.step(token) == got_token and np.array_equal(other.logits(), dec.logits()), "loaded or generated: the same bits"
+        token = (pos * 7919 + 13) % cfg.vocab
+    prompt = [(i * 7919 + 13) % cfg.vocab for i in range(70)]
+    dec.reset()
+    for t in prompt[:-1]:
+        dec.step(t)
+    a, la = dec.step(prompt[-1]), dec.logits()
+    dec.reset()
+    dec.prefill(prompt[:-1])  # two chunks
+    b, lb = dec.step(prompt[-1]), dec.logits()
+    assert np.abs(la - lb).max() <= 4e-3 * np.abs(la).max()
+    dec.close(), other.close()
 
 
 def test_a_layer_sharing_the_cache_of_the_layer_right_before_it(ctx):

@@ -15,9 +15,17 @@ def f16_round(a):
     return np.asarray(a, np.float64).astype(np.float16).astype(np.float64)
 
 
-def dequant(model, name):
+def dequant(model, name, bits=8):
     w, s = model.tensors[name + ".w"], model.tensors[name + ".s"]
-    return w.astype(np.float64) * np.repeat(s.view(np.float16).astype(np.float64), 32, axis=1)
+    if bits == 8:
+        return w.astype(np.float64) * np.repeat(s.view(np.float16).astype(np.float64), 32, axis=1)
+    # crates/tachyon/src/quant.rs:47-82: weight k of a group of 64 is nibble k % 8 / 4 of byte k / 8 * 4 + k % 4, minus 8, times the
+    # group's f16 scale
+    rows = w.shape[0]
+    pk = w.view(np.uint8).reshape(rows, -1, 32)
+    k = np.arange(64)
+    nib = (pk[:, :, k // 8 * 4 + k % 4] >> (k % 8 // 4 * 4)) & 15
+    return ((nib.astype(np.float64) - 8.0) * s.view(np.float16).astype(np.float64)[:, :, None]).reshape(rows, -1)
 
 
 def rms(x, w=None, eps=1e-6):
@@ -41,8 +49,8 @@ def gelu(x):
 class Forward:
     """The forward pass over an OracleModel's tensors; caches hold f16-rounded keys and values, as the decoder keeps them."""
 
-    def __init__(self, cfg, model: OracleModel):
-        self.cfg, self.m = cfg, model
+    def __init__(self, cfg, model: OracleModel, bits=8):
+        self.cfg, self.m, self.bits = cfg, model, bits
         self.L = cfg.layers
         self.mats = {}
         self.cache = [dict() for _ in range(self.L)]  # position -> (k [kvh, D], v [kvh, D])
@@ -50,7 +58,7 @@ class Forward:
 
     def mat(self, name):
         if name not in self.mats:
-            self.mats[name] = dequant(self.m, name)
+            self.mats[name] = dequant(self.m, name, self.bits)
         return self.mats[name]
 
     def source(self, i):
@@ -115,13 +123,17 @@ def config(**kw):
 
 
 @pytest.mark.parametrize("kw", [dict(), dict(layers=6, shared=3), dict(layers=6, global_head_dim=512, global_kv_heads=1, shared=2),
-                                dict(layers=5, per_layer=256, global_head_dim=512, shared=1), dict(layers=3, kv_heads=1)],
-                         ids=["plain", "shared caches", "heads of 512", "per-layer inputs", "eight query heads to a key-value head"])
+                                dict(layers=5, per_layer=256, global_head_dim=512, shared=1), dict(layers=3, kv_heads=1),
+                                dict(layers=5, per_layer=256, global_head_dim=512, shared=1, bits=4)],
+                         ids=["plain", "shared caches", "heads of 512", "per-layer inputs", "eight query heads to a key-value head",
+                              "per-layer inputs in four bits"])
 def test_the_c_oracle_and_the_numpy_forward_agree(kw):
+    kw = dict(kw)
+    bits = kw.pop("bits", 8)
     cfg = config(**kw)
     context = 32
-    model = OracleModel(cfg, 4321, context=context, chunk=4)
-    fwd = Forward(cfg, model)
+    model = OracleModel(cfg, 4321, context=context, chunk=4, weight_bits=bits)
+    fwd = Forward(cfg, model, bits)
     token = 7
     for pos in range(14):  # past the window of 8 and the ring of 12
         pick, logits, hidden = model.step(token, pos)

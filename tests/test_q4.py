@@ -33,6 +33,46 @@ def test_oracle_kernel_order_meets_the_reference_bound(i, shape):
     assert np.all(np.abs(y.astype(np.float64) - want) <= 1e-5 * bound + 1e-6)
 
 
+NARROW = [(2560, 256), (36, 64), (4, 192), (16, 128), (260, 256)]  # gemv.rs:7-9: rows a multiple of 4, at most 256 weights each
+
+
+@pytest.mark.parametrize("i,shape", list(enumerate(NARROW)))
+def test_oracle_narrow_order_meets_the_reference_bound(i, shape):
+    """CPU only: eight lanes a row add in another order than thirty-two; both stay within the reference's bound."""
+    rows, cols = shape
+    wf, x = inputs(rows, cols, 40 + i)
+    packed, scales = oracle.q4(wf.reshape(rows, cols))
+    q, pairs = oracle.q8(x)
+    narrow, wide = oracle.gemv_q4_narrow(packed, scales, q, pairs, rows), oracle.gemv_q4(packed, scales, q, pairs, rows)
+    want, bound = oracle.product_q4(packed, scales, x, rows)
+    assert np.all(np.abs(narrow.astype(np.float64) - want) <= 1e-5 * bound + 1e-6)
+    assert np.all(np.abs(narrow.astype(np.float64) - wide) <= 2e-5 * bound + 2e-6)
+    if cols == 64:  # two chunks: lanes 0 and 1 either way, one addition
+        assert np.array_equal(narrow, wide)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("i,shape", list(enumerate(NARROW)))
+def test_gemv_q4_narrow_gives_the_reference_kernels_bits(ctx, i, shape):
+    rows, cols = shape
+    wf, x = inputs(rows, cols, 40 + i)
+    packed, scales = oracle.q4(wf.reshape(rows, cols))
+    xd, qd, sd = ctx.upload(x), ctx.zeros(cols), ctx.zeros(cols // 32 * 8)
+    ctx.quant_q8(xd, cols, qd, sd)
+    wd, wsd, yd = ctx.upload(packed), ctx.upload(scales), ctx.zeros(rows * 4)
+    ctx.launch("gemv_q4_narrow", ((rows + 15) // 16, 1, 1), (128, 1, 1), 0,
+               [("p", wd.ptr), ("p", wsd.ptr), ("p", qd.ptr), ("p", sd.ptr), ("p", yd.ptr), ("u", rows), ("u", cols)])
+    got = yd.download(np.float32, rows)
+    q, pairs = oracle.q8(x)
+    assert np.array_equal(got.view(np.uint32), oracle.gemv_q4_narrow(packed, scales, q, pairs, rows).view(np.uint32)), f"{rows}x{cols}"
+    with pytest.raises(tb.Error):
+        ctx.launch("gemv_q4_narrow", ((rows + 15) // 16, 1, 1), (128, 1, 1), 0,
+                   [("p", wd.ptr), ("p", wsd.ptr), ("p", qd.ptr), ("p", sd.ptr), ("p", yd.ptr), ("u", rows), ("u", 512)])  # rows too long
+    with pytest.raises(tb.Error):
+        ctx.launch("gemv_q4_narrow", (1, 1, 1), (128, 1, 1), 0,
+                   [("p", wd.ptr), ("p", wsd.ptr), ("p", qd.ptr), ("p", sd.ptr), ("p", yd.ptr), ("u", 6), ("u", cols)])  # rows not a multiple of 4
+
+
 @pytest.mark.gpu
 def test_quant_q8_matches_the_cpu_exactly(ctx):
     x = values(4096, 7)
@@ -99,3 +139,25 @@ def test_gemv_q4x_reads_q4_weights_with_an_unrounded_activation(ctx, rows, cols)
     ctx.gemv_q4x(wd, sd, xd, tb.F32, yd, rows, cols)
     got = yd.download(np.float32, rows)
     assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-5 * bound + 1e-6), np.abs(got - want).max()
+
+
+@pytest.mark.gpu
+def test_embed_decodes_a_row_from_device_or_host_memory(ctx):
+    """crates/tachyon/tests/decode.rs:153-177: embed_q4 reads its table from VRAM or from pinned, mapped host memory (the
+    per-layer table of host.wpk): the same row, exactly."""
+    rows, cols, token = 7, 2560, 5
+    packed, scales = oracle.q4(values_fast(rows * cols, 11).reshape(rows, cols))
+    g = np.arange(cols)
+    byte = packed.reshape(rows, cols // 64, 32)[token][g // 64, g % 64 // 8 * 4 + g % 4]
+    nib = ((byte >> (g % 8 // 4 * 4)) & 15).astype(np.float32) - np.float32(8.0)
+    want = nib * np.asarray(scales, np.uint16).view(np.float16).astype(np.float32).reshape(rows, cols // 64)[token][g // 64] * np.float32(50.5)
+    tok, out = ctx.upload(np.array([token], np.uint32)), ctx.zeros(cols * 4)
+    host = ctx.alloc_host(packed.nbytes + scales.nbytes)
+    host.array[:packed.nbytes] = packed.view(np.uint8).ravel()
+    host.array[packed.nbytes:] = scales.view(np.uint8).ravel()
+    dp, ds = ctx.upload(packed), ctx.upload(scales)
+    for pw, ps in ((dp.ptr, ds.ptr), (host.ptr, host.ptr + packed.nbytes)):
+        out.zero()
+        ctx.launch("embed_q4", ((cols + 255) // 256, 1, 1), (256, 1, 1), 0, [("p", pw), ("p", ps), ("p", tok.ptr), ("p", out.ptr), ("u", cols), ("f", 50.5)])
+        assert np.array_equal(out.download(np.float32, cols), want)
+    host.free()

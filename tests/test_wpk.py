@@ -136,3 +136,33 @@ def test_a_converted_q4_model_loads_from_its_wpk(ctx, tmp_path):
         a.load_wpk(path)
     assert e.value.status == 8
     a.close(), b.close(), c.close()
+
+
+@pytest.mark.gpu
+def test_a_converted_model_with_per_layer_inputs_loads_from_both_files(ctx, tmp_path):
+    """An E-model's directory (model/mod.rs:178-204): weights.wpk with everything that lives in VRAM, host.wpk with the per-layer
+    table `embed_per_layer`, which the decoder here keeps where the reference does, in pinned mapped host memory."""
+    from oracle.model import OracleModel
+
+    cfg = tb.gemma4_e4b_shape(layers=3, ffn=2048, vocab=2048)
+    cfg.window, cfg.global_every, cfg.per_layer = 16, 3, 256
+    ref = OracleModel(cfg, 33, context=64, chunk=0, weight_bits=4)
+    files = {"weights.wpk": [], "host.wpk": []}
+    for name, a in ref.tensors.items():
+        kind = "u8" if name.endswith(".w") else "f16" if name.endswith(".s") else "f32"
+        a = np.ascontiguousarray(a)
+        files["host.wpk" if name.startswith("embed_per_layer") else "weights.wpk"].append((name, kind, a.shape, a.view(np.uint8).tobytes()))
+    assert [t[0] for t in files["host.wpk"]] == ["embed_per_layer.w", "embed_per_layer.s"]
+    for name, tensors in files.items():
+        ww.write(str(tmp_path / name), tensors, crc=ww.fast_crc32c)
+    a = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4, host_table=True)
+    a.load_wpk(str(tmp_path / "weights.wpk"))
+    a.load_wpk(str(tmp_path / "host.wpk"))
+    a.build()
+    b = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4)
+    b.fill_random(33)
+    b.build()
+    for pos, token in enumerate([5, 99, 2000, 7]):
+        assert a.step(token) == b.step(token) == ref.step(token, pos)[0]
+        assert np.array_equal(a.logits(), b.logits())
+    a.close(), b.close()
