@@ -35,15 +35,35 @@ __device__ __forceinline__ float dot8(const uint4& w, const float* x) {
     return s;
 }
 
+// Four 16-byte pieces of either row of a pair, from column c0 on (256 columns apart); pieces past the row's end are zeros.
+__device__ __forceinline__ void load_batch(const __half* wa, const __half* wb, uint32_t c0, uint32_t K, uint4 (&a)[4], uint4 (&b)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t c = c0 + j * 256;
+        if (c < K) a[j] = ld_stream_u4(wa + c), b[j] = ld_stream_u4(wb + c);
+        else a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
 template <int XMODE, int EPI>
-__global__ void __launch_bounds__(F16_THREADS) gemv_f16_kernel(const GemvF16Params p) {
+__global__ void __launch_bounds__(F16_THREADS, 2) gemv_f16_kernel(const GemvF16Params p) {
     extern __shared__ __align__(16) float xs[];  // [cols], then four sums a warp
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t threads = blockDim.x, nwarps = threads >> 5;
     const uint32_t K = p.cols;
+    // The weights depend on no kernel: a warp asks for the first pieces of its first pair of rows before it waits for the
+    // kernel in front of this one and before the vector is in shared memory.
+    const uint32_t pairs = (p.rows + 1) / 2, stride = gridDim.x * nwarps;
+    uint32_t pr = blockIdx.x * nwarps + warp;
+    uint4 a[4], b[4];
+    if (pr < pairs) {
+        const uint32_t r0 = 2 * pr, r1 = min(r0 + 1, p.rows - 1);
+        load_batch(p.w + (size_t)r0 * K, p.w + (size_t)r1 * K, lane * 8, K, a, b);
+    }
     pdl_wait();
     // The vector.
     if constexpr (XMODE == X_F16) {
-        for (uint32_t i = t; i < K / 8; i += F16_THREADS) {
+        for (uint32_t i = t; i < K / 8; i += threads) {
             const uint4 u = ld_cg_u4(static_cast<const __half*>(p.x) + (size_t)i * 8);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -53,27 +73,26 @@ __global__ void __launch_bounds__(F16_THREADS) gemv_f16_kernel(const GemvF16Para
             }
         }
     } else if constexpr (XMODE == X_F32) {
-        for (uint32_t i = t; i < K / 4; i += F16_THREADS) *reinterpret_cast<float4*>(xs + i * 4) = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)i * 4);
+        for (uint32_t i = t; i < K / 4; i += threads) *reinterpret_cast<float4*>(xs + i * 4) = ld_cg_f4(static_cast<const float*>(p.x) + (size_t)i * 4);
     } else {
         // h' = (h + w1 * rmsnorm(y)) * hscale, x = w2 * rmsnorm(h'): one pass of four sums, as gemv.cu's prologue.
         float sy = 0.0f, sh = 0.0f, sha = 0.0f, sa = 0.0f;
-        for (uint32_t i = t; i < K; i += F16_THREADS) {
+        for (uint32_t i = t; i < K; i += threads) {
             const float h = ld_cg_f(p.h + i);
-            float a = 0.0f;
+            float av = 0.0f;
             if (p.yres != nullptr) {
                 const float y = ld_cg_f(p.yres + i);
-                a = y * __ldg(p.w1 + i);
+                av = y * __ldg(p.w1 + i);
                 sy = fmaf(y, y, sy);
             }
-            sh = fmaf(h, h, sh), sha = fmaf(h, a, sha), sa = fmaf(a, a, sa);
+            sh = fmaf(h, h, sh), sha = fmaf(h, av, sha), sa = fmaf(av, av, sa);
         }
         sy = warp_sum(sy), sh = warp_sum(sh), sha = warp_sum(sha), sa = warp_sum(sa);
         float4* sums = reinterpret_cast<float4*>(xs + K);
         if (lane == 0) sums[warp] = make_float4(sy, sh, sha, sa);
         __syncthreads();
         sy = sh = sha = sa = 0.0f;
-#pragma unroll
-        for (int k = 0; k < F16_WARPS; k++) {
+        for (uint32_t k = 0; k < nwarps; k++) {
             const float4 q = sums[k];
             sy += q.x, sh += q.y, sha += q.z, sa += q.w;
         }
@@ -82,10 +101,10 @@ __global__ void __launch_bounds__(F16_THREADS) gemv_f16_kernel(const GemvF16Para
         const float hs = p.yres != nullptr ? p.hscale : 1.0f;
         const float sq = hs * hs * (sh + 2.0f * ry * sha + ry * ry * sa);
         const float rh = p.w2 != nullptr ? rsqrtf(fmaxf(sq, 0.0f) / n + p.eps) : 1.0f;
-        for (uint32_t i = t; i < K; i += F16_THREADS) {
+        for (uint32_t i = t; i < K; i += threads) {
             const float h = ld_cg_f(p.h + i);
-            const float a = p.yres != nullptr ? ld_cg_f(p.yres + i) * __ldg(p.w1 + i) : 0.0f;
-            const float v = fmaf(a, ry, h) * hs;
+            const float av = p.yres != nullptr ? ld_cg_f(p.yres + i) * __ldg(p.w1 + i) : 0.0f;
+            const float v = fmaf(av, ry, h) * hs;
             if (blockIdx.x == 0 && p.h_out != nullptr) p.h_out[i] = v;
             xs[i] = v * rh * (p.w2 != nullptr ? __ldg(p.w2 + i) : 1.0f);
         }
@@ -93,22 +112,27 @@ __global__ void __launch_bounds__(F16_THREADS) gemv_f16_kernel(const GemvF16Para
     __syncthreads();
     pdl_launch_dependents();
 
-    // Row pairs, round-robin over all warps of the grid.
-    const uint32_t pairs = (p.rows + 1) / 2, stride = gridDim.x * F16_WARPS;
-    for (uint32_t pr = blockIdx.x * F16_WARPS + warp; pr < pairs; pr += stride) {
+    // Row pairs, round-robin over all warps of the grid.  The first four pieces of a pair's rows are already on their way
+    // when its turn comes: those of the next pair are asked for before this pair's sums are reduced.
+    for (; pr < pairs; pr += stride) {
         const uint32_t r0 = 2 * pr, r1 = min(r0 + 1, p.rows - 1);  // a lone last row is read twice
         const __half* wa = p.w + (size_t)r0 * K;
         const __half* wb = p.w + (size_t)r1 * K;
         float sa = 0.0f, sb = 0.0f;
         uint32_t c = lane * 8;
-        for (; c + 3 * 256 < K; c += 4 * 256) {  // four pieces of either row in flight
-            uint4 a[4], b[4];
+        while (true) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) a[j] = ld_stream_u4(wa + c + j * 256), b[j] = ld_stream_u4(wb + c + j * 256);
-#pragma unroll
-            for (int j = 0; j < 4; j++) sa += dot8(a[j], xs + c + j * 256), sb += dot8(b[j], xs + c + j * 256);
+            for (int j = 0; j < 4; j++)
+                if (c + j * 256 < K) sa += dot8(a[j], xs + c + j * 256), sb += dot8(b[j], xs + c + j * 256);
+            c += 4 * 256;
+            if (c >= K) break;
+            load_batch(wa, wb, c, K, a, b);
         }
-        for (; c < K; c += 256) sa += dot8(ld_stream_u4(wa + c), xs + c), sb += dot8(ld_stream_u4(wb + c), xs + c);
+        const uint32_t next = pr + stride;
+        if (next < pairs) {
+            const uint32_t n0 = 2 * next, n1 = min(n0 + 1, p.rows - 1);
+            load_batch(p.w + (size_t)n0 * K, p.w + (size_t)n1 * K, lane * 8, K, a, b);
+        }
         // Both rows in five exchanges.
         const bool upper = lane & 16;
         float r = (upper ? sb : sa) + __shfl_xor_sync(0xffffffffu, upper ? sa : sb, 16);
@@ -122,6 +146,18 @@ __global__ void __launch_bounds__(F16_THREADS) gemv_f16_kernel(const GemvF16Para
     }
 }
 
+// Warps a block (two blocks an SM) for which the last round of row pairs leaves the fewest warps idle.
+static uint32_t pick_warps(uint32_t pairs, uint32_t sms) {
+    uint32_t best = F16_WARPS;
+    double best_eff = 0.0;
+    for (uint32_t w = F16_WARPS; w >= 10; w--) {
+        const uint64_t slots = (uint64_t)2 * sms * w, rounds = (pairs + slots - 1) / slots;
+        const double eff = (double)pairs / (double)(rounds * slots);
+        if (eff > best_eff + 1e-9) best_eff = eff, best = w;
+    }
+    return best;
+}
+
 template <int XMODE, int EPI>
 int launch_one(tb_context* ctx, const GemvF16Params& p) {
     const size_t smem = (size_t)p.cols * 4 + F16_WARPS * 16;
@@ -131,10 +167,11 @@ int launch_one(tb_context* ctx, const GemvF16Params& p) {
         configured[ctx->gpu & 15] = true;
     }
     const uint32_t pairs = (p.rows + 1) / 2;
-    uint32_t grid = (uint32_t)ctx->sms * 2;  // two blocks of 512 threads an SM
-    const uint32_t most = (pairs + F16_WARPS - 1) / F16_WARPS;
+    const uint32_t warps = pick_warps(pairs, (uint32_t)ctx->sms);
+    uint32_t grid = (uint32_t)ctx->sms * 2;  // two blocks an SM
+    const uint32_t most = (pairs + warps - 1) / warps;
     if (grid > most) grid = most;
-    TB_CUDA(launch_kernel(ctx, gemv_f16_kernel<XMODE, EPI>, dim3(grid), dim3(F16_THREADS), smem, true, p));
+    TB_CUDA(launch_kernel(ctx, gemv_f16_kernel<XMODE, EPI>, dim3(grid), dim3(warps * 32), smem, true, p));
     return OK;
 }
 
