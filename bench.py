@@ -182,7 +182,7 @@ def bench_decode(args, ranks: Ranks):
     import tachyon_b200 as tb
 
     ctx = tb.Context(ranks.local)
-    cfg = tb.gemma4_e4b_shape()
+    cfg = tb.gemma4_e4b_shape(layers=args.layers)
     bits = 4 if args.weights == "q4" else 8
     dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=0, keep_logits=False, fused=args.fused, weight_bits=bits)
     dec.fill_random(SEED)
@@ -273,7 +273,7 @@ def bench_decode(args, ranks: Ranks):
         "ms_per_step": ms_max / K, "repeats": repeats, "timed_ms": sum(runs), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": ("int4 (the reference's Q4)" if bits == 4 else "int8") + " weights x f32 activations, f32 accumulate",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": "configs[2]: full decode step, Gemma-4-E4B-shape " + ("Q4 (the reference's converted format; not the configuration the metric is quoted on)" if bits == 4 else "Q8")
+        "config": {"workload": ("configs[2]" if cfg.layers == 35 else f"a {cfg.layers}-layer cut (for profiling) of configs[2]") + ": full decode step, Gemma-4-E4B-shape " + ("Q4 (the reference's converted format; not the configuration the metric is quoted on)" if bits == 4 else "Q8")
                    + ", batch 1, context pre-filled to 2048, greedy",
                    "step": "CUDA graph replay; " + ("one persistent kernel per step" if args.fused else "one launch per phase, programmatic dependent launch"),
                    "layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "parallelism": f"{n} independent replicas",
@@ -682,6 +682,7 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=35, help="decode workload: layers of the model (35 is the benchmark's; fewer for a profiler capture)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="decode workload: skip the prefill / encoder / single-kernel sub-objects")
     ap.add_argument("--weights", default="q8", choices=["q8", "q4", "f16"], help="gemv workload: Q8 or f16 weights; decode and prefill workloads: the benchmark's Q8 matrices, or the reference's converted Q4 format")

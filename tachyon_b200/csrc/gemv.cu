@@ -755,7 +755,9 @@ int launch_staged(tb_context* ctx, const GemvParams& p) {
     // their ring is only as long as a block's share.
     GemvParams q = p;
     q.ring = (uint32_t)L::NST_MAX;
-    if (ctx->dynamic && (p.rows + ROWS - 1) / ROWS >= 2 * grid) {
+    // (Four-bit stages hold half the bytes, so the counter's trip is paid twice per byte: measured slower there, 1.306 against
+    // 1.262 ms a step.)
+    if (ctx->dynamic && WB == 8 && (p.rows + ROWS - 1) / ROWS >= 2 * grid) {
         if (q.next == nullptr) q.next = ctx->sched + 2 * (ctx->sched_at++ % 64u);
     } else {
         q.next = nullptr;
