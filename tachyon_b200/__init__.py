@@ -242,6 +242,10 @@ class Context:
     def set_dynamic(self, on: bool) -> None:
         check(self.lib.tb_context_set_dynamic(self.handle, int(on)))
 
+    def set_flash(self, which: int) -> None:
+        """tb_context_set_flash: 1 prefill attention on tcgen05 where the shape allows (default), 0 the mma.sync kernel."""
+        check(self.lib.tb_context_set_flash(self.handle, which))
+
     def attend_decode_512(self, args: Attend) -> None:
         """tb_attend_decode_512: heads of 512 (the reference's attend_512)."""
         check(self.lib.tb_attend_decode_512(self.handle, C.byref(args)))

@@ -123,6 +123,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->l2_next = env != nullptr ? (uint32_t)atoi(env) : 0u;
     env = getenv("TACHYON_B200_NO_CLUSTER");
     ctx->cluster = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_FLASH");
+    ctx->flash_tc = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_GEMM");
     ctx->gemm_schedule = env != nullptr ? atoi(env) : 0;
     *out = ctx;
@@ -164,6 +166,13 @@ int tb_context_set_lean(tb_context* ctx, int mode) {
 int tb_context_set_dynamic(tb_context* ctx, int on) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     ctx->dynamic = on != 0;
+    return OK;
+}
+
+int tb_context_set_flash(tb_context* ctx, int which) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (which != 0 && which != 1) return fail(OUT_OF_RANGE, "tb_context_set_flash: 0 (mma.sync kernel) or 1 (tcgen05 where the shape allows)");
+    ctx->flash_tc = which != 0;
     return OK;
 }
 

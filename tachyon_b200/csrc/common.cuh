@@ -216,15 +216,16 @@ __device__ __forceinline__ void q8_store(float x, uint32_t i, int8_t* q, float2*
     if ((i & 31u) == 0) s[i >> 5] = make_float2(d, __fmul_rn(static_cast<float>(sum), d));
 }
 
+// 0.5 x (1 + tanh(u)) = x / (1 + e^(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3); the quotient by the hardware's reciprocal (2 ulp).
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float u = x + 0.044715f * x * x * x;
-    return x / (1.0f + exp2f(-2.0f * 0.7978845608028654f * 1.4426950408889634f * u));
+    return __fdividef(x, 1.0f + exp2f(-2.0f * 0.7978845608028654f * 1.4426950408889634f * u));
 }
 
 // erf to 1.5e-7 (Abramowitz and Stegun 7.1.26) and the exact-form GELU built on it, as the reference's encoder
 // computes them (crates/tachyon/src/ptx/encoder.rs:807-841).
 __device__ __forceinline__ float erf_as(float x) {
-    const float t = 1.0f / (1.0f + 0.3275911f * fabsf(x));
+    const float t = __fdividef(1.0f, 1.0f + 0.3275911f * fabsf(x));
     const float p = t * (0.2548296f + t * (-0.28449674f + t * (1.4214137f + t * (-1.4531521f + t * 1.0614054f))));
     return copysignf(1.0f - p * __expf(-x * x), x);
 }

@@ -313,23 +313,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         if (mb + 2 * k + odd < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * g.N) = pair;
                     }
                 } else {
-                    // Weight rows (2j, 2j + 1) are (gate_j, up_j): lanes 4c .. 4c + 3 hold gate, up, gate, up of outputs n / 2 and
-                    // n / 2 + 1.  The even lanes take their neighbour's `up` and compute gelu(gate) * up for two tokens; then
-                    // lane 4c writes the pair of outputs of the even token and lane 4c + 2 that of the odd token.
-                    const bool even = (lane & 1u) == 0, second = (lane & 2u) != 0;
-                    __half* dst = static_cast<__half*>(g.out) + (size_t)(mb + (second ? 1 : 0)) * (g.N / 2) + (n - (second ? 2 : 0)) / 2;
+                    // Weight rows (2j, 2j + 1) are (gate_j, up_j): an even lane holds gate_j of two tokens, the odd lane beside it
+                    // up_j.  They trade one value each, so that the even lane has (gate, up) of the even token and the odd lane
+                    // those of the odd token, and every lane computes one output.  Lanes 4c .. 4c + 3 then hold outputs j and j + 1
+                    // of two tokens: lanes 4c and 4c + 1 take their neighbour pair's and write two halves each.
+                    const bool odd = (lane & 1u) != 0, second = (lane & 2u) != 0;
+                    __half* dst = static_cast<__half*>(g.out) + (size_t)(mb + (odd ? 1 : 0)) * (g.N / 2) + (n - (lane & 3u)) / 2;
 #pragma unroll
                     for (int k = 0; k < 16; k++) {
-                        const float g0 = __uint_as_float(r[2 * k]), g1 = __uint_as_float(r[2 * k + 1]);
-                        const float u0 = __shfl_down_sync(0xffffffffu, g0, 1), u1 = __shfl_down_sync(0xffffffffu, g1, 1);
-                        float a0 = 0.0f, a1 = 0.0f;
-                        if (even) {
-                            a0 = (g.mode == 2 ? gelu_tanh(g0) : gelu_erf(g0)) * u0;
-                            a1 = (g.mode == 2 ? gelu_tanh(g1) : gelu_erf(g1)) * u1;
-                        }
-                        const float got = __shfl_xor_sync(0xffffffffu, second ? a0 : a1, 2);  // the other pair's output for my token
-                        const __half2 pair = second ? __floats2half2_rn(got, a1) : __floats2half2_rn(a0, got);
-                        if (even && mb + 2 * k + (second ? 1 : 0) < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * (g.N / 2)) = pair;
+                        const float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);  // even: up of the even token; odd: gate of the odd token
+                        const float gate = odd ? got : v0, up = odd ? v1 : got;
+                        const float a = (g.mode == 2 ? gelu_tanh(gate) : gelu_erf(gate)) * up;
+                        const float other = __shfl_xor_sync(0xffffffffu, a, 2);  // output j + 1 (or j) of the same token
+                        const __half2 pair = second ? __floats2half2_rn(other, a) : __floats2half2_rn(a, other);
+                        if (!second && mb + 2 * k + (odd ? 1 : 0) < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * (g.N / 2)) = pair;
                     }
                 }
             }

@@ -27,6 +27,7 @@ struct tb_context {
     bool cluster = true;              // decode attention merges neighbouring splits in thread-block clusters (TACHYON_B200_NO_CLUSTER=1: never)
     uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
     uint32_t sched_at = 0;            // which pair the next launch takes
+    bool flash_tc = true;             // prefill attention on tcgen05 where the shape allows (prefill_tc.cu); TACHYON_B200_FLASH=0, tb_context_set_flash
     int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
 };
 
@@ -235,6 +236,10 @@ int launch_prefill_rows(tb_context* ctx, const float* qkv, const float* q_norm, 
                         const PrefillRows& rows);
 // out: f16 (or f32 with out_f32) [tokens][heads * head_dim].  pos_dev: the first position from device memory instead of pos0;
 // sscale: factor of the scores (1 when the queries already carry scale * log2(e)).
+// The same on tcgen05 (prefill_tc.cu), for the shapes prefill_flash_tc_supports names.
+bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap, const uint32_t* pos_dev);
+int launch_prefill_flash_tc(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                            uint32_t window, uint32_t heads, uint32_t kv_heads, float sscale, int out_f32);
 int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
                          uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim = 256, const uint32_t* pos_dev = nullptr, float sscale = 1.0f,
                          int out_f32 = 0);

@@ -1,0 +1,358 @@
+// Prefill attention on the fifth-generation tensor cores: flash_256 (crates/tachyon/src/ptx/flash.rs:1-23, 246-251) for heads of
+// 256 with four query heads to a key-value head.  Token t of the chunk, at position pos0 + t, attends positions
+// p - window < j <= p of the cache ring.  Same results, to the rounding of the probabilities, as prefill.cu's mma.sync kernel,
+// which stays for every other shape.
+//
+// A block takes 32 tokens x the four query heads of one key-value head = 128 query rows (row = 4 * token + head) and walks
+// the keys in tiles of 128 positions that start at multiples of 128, so a token's sums do not depend on how the prompt was
+// cut into chunks (flash.rs:9-12).  Six warps:
+//   warp 0      one thread issues the TMA loads: the queries once (3-D map over [token][head][256]), then per tile the keys and
+//               the values of 128 ring slots (3-D maps over [key-value head][slot][256]), each as four boxes of 64 dimensions
+//               in the 128-byte swizzle;
+//   warp 1      allocates tensor memory (512 columns: two score buffers of 128, the output of 256); one thread issues
+//               S = Q K^T (M128 N128 K256: both operands K-major) and O += P V (M128 N256 K128: P K-major from shared memory,
+//               V as it lies in the cache, [key][dimension], which is the MN-major form of a B operand);
+//   warps 2-5   softmax: thread r owns query row r (tensor-memory lane r).  Two passes over the tile's scores with tcgen05.ld
+//               (maximum, then exponentials), probabilities rounded to f16 into shared memory in the swizzled K-major layout,
+//               sums taken from the rounded values.  The running maximum only moves when a tile exceeds it by more than 8
+//               (in base 2), so probabilities stay below 2^8 and the output in tensor memory is rescaled (tcgen05.ld, multiply,
+//               tcgen05.st) only on those tiles, usually the first one or two.
+// The score buffers alternate, so S of tile i + 1 is multiplied while tile i is in the softmax; keys of tile i + 1 are
+// loaded as soon as S of tile i is done, values as soon as P V of tile i is done.  Every wait is bounded.
+#include <cuda.h>
+
+#include <string>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int D = 256, G = 4, TQ = 32, ROWS = TQ * G, KT = 128;
+constexpr int CHUNK = ROWS * 128;                          // a box of 64 dimensions (128 bytes) x 128 rows
+constexpr int OFF_Q = 0, OFF_K = 4 * CHUNK, OFF_V = 8 * CHUNK, OFF_P = 12 * CHUNK, OFF_BAR = 14 * CHUNK;
+constexpr int SMEM_BYTES = 1024 + OFF_BAR + 256;
+constexpr int THREADS = 192;
+static_assert(SMEM_BYTES <= 232448, "over the 227 KiB a block may use");
+
+// kind::f16 instruction descriptors: f32 accumulator, f16 operands, A K-major; N >> 3 at bit 17, M >> 4 at bit 24; bit 16 set
+// makes B MN-major.
+constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+
+// Shared-memory descriptors, 128-byte swizzle.  K-major: rows of 128 bytes, 1024 bytes between groups of eight rows.
+// MN-major (the values: 64 dimensions contiguous, eight keys 128 bytes apart form an atom): `lbo` bytes to the next 64
+// dimensions, 1024 bytes to the next eight keys.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo) {
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | ((lbo >> 4) << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_addr(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+        "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+        "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+        "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+        "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Bars {
+    uint64_t q_full, k_full, v_full, s_full[2], p_ready, pv_done;
+    uint32_t tmem;
+};
+
+struct FlashArgs {
+    void* out;
+    uint32_t tokens, pos0, cap, window, heads;
+    float sscale;  // factor of the scores (1 when the queries already carry scale * log2 e)
+    int out_f32;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                                                                      const __grid_constant__ CUtensorMap v_map, const FlashArgs a, uint32_t* status) {
+    extern __shared__ uint8_t raw_unaligned[];
+    uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
+    Bars& bar = *reinterpret_cast<Bars*>(raw + OFF_BAR);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t t0 = blockIdx.x * TQ, kvh = blockIdx.y;
+    const uint32_t p_first = a.pos0 + t0, p_last = a.pos0 + min(t0 + TQ, a.tokens) - 1;
+    const uint32_t lo = p_first + 1 > a.window ? p_first + 1 - a.window : 0;  // oldest position any token of the block sees
+    const uint32_t tile0 = lo / KT * KT, nt = (p_last - tile0) / KT + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar.q_full, 1), mbar_init(&bar.k_full, 1), mbar_init(&bar.v_full, 1);
+        mbar_init(&bar.s_full[0], 1), mbar_init(&bar.s_full[1], 1), mbar_init(&bar.p_ready, 4), mbar_init(&bar.pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&bar.tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bar.tmem;
+    pdl_wait();  // the queries and this chunk's keys and values come from the kernels in front
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bar.q_full, 4 * CHUNK);
+            for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_Q + c * CHUNK, &q_map, 64 * c, (int)(kvh * G), (int)t0, &bar.q_full);
+            for (uint32_t i = 0; i < nt; i++) {
+                const int slot0 = (int)((tile0 + i * KT) % a.cap);
+                // The key buffer is free once S of the tile before is done, the value buffer once its P V is done.
+                if (i > 0 && !mbar_wait(&bar.s_full[(i - 1) & 1], ((i - 1) >> 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(&bar.k_full, 4 * CHUNK);
+                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_K + c * CHUNK, &k_map, 64 * c, slot0, (int)kvh, &bar.k_full);
+                if (i > 0 && !mbar_wait(&bar.pv_done, (i - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(&bar.v_full, 4 * CHUNK);
+                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_V + c * CHUNK, &v_map, 64 * c, slot0, (int)kvh, &bar.v_full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t qa = smem_addr(raw + OFF_Q), ka = smem_addr(raw + OFF_K), va = smem_addr(raw + OFF_V), pa = smem_addr(raw + OFF_P);
+            auto scores = [&](uint32_t i) {  // S[i & 1] = Q K^T over the 256 dimensions: sixteen products of K = 16
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int k = 0; k < D / 16; k++) {
+                    const uint32_t off = (k >> 2) * CHUNK + (k & 3) * 32;
+                    mma_f16(tmem + (i & 1) * KT, desc_k_major(qa + off), desc_k_major(ka + off), IDESC_S, k > 0 ? 1u : 0u);
+                }
+                mma_commit(&bar.s_full[i & 1]);
+            };
+            bool ok = mbar_wait(&bar.q_full, 0) && mbar_wait(&bar.k_full, 0);
+            if (ok) scores(0);
+            for (uint32_t i = 0; i < nt && ok; i++) {
+                if (i + 1 < nt) {
+                    ok = mbar_wait(&bar.k_full, (i + 1) & 1);
+                    if (ok) scores(i + 1);
+                }
+                ok = ok && mbar_wait(&bar.p_ready, i & 1) && mbar_wait(&bar.v_full, i & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int k = 0; k < KT / 16; k++) {  // O += P V over the tile's 128 keys: eight products of K = 16
+                    const uint64_t da = desc_k_major(pa + (k >> 2) * CHUNK + (k & 3) * 32);
+                    const uint64_t db = desc_mn_major(va + k * 2048, CHUNK);
+                    mma_f16(tmem + 2 * KT, da, db, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(&bar.pv_done);
+            }
+            if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+        }
+    } else {
+        // Softmax and epilogue.  This warp reads the tensor-memory lanes of its quarter, warp % 4; thread = query row.
+        const uint32_t quarter = warp & 3, row = 32 * quarter + lane, tl = row / G, head = row % G;
+        const uint32_t p = a.pos0 + t0 + tl;
+        const bool valid = t0 + tl < a.tokens;
+        const uint32_t lane_addr = (32 * quarter) << 16;
+        float m_used = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (uint32_t i = 0; i < nt; i++) {
+            const uint32_t j0 = tile0 + i * KT, sbuf = tmem + lane_addr + (i & 1) * KT;
+            if (!mbar_wait(&bar.s_full[i & 1], (i >> 1) & 1)) {
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // Keys j0 + c are seen when c lies in [c_lo, c_hi): at or before this token, inside its window.
+            const uint32_t first_seen = p + 1 > a.window ? p + 1 - a.window : 0;
+            const int c_lo = valid ? (int)max(first_seen, j0) - (int)j0 : KT;
+            const int c_hi = valid ? (int)min(p, j0 + KT - 1) + 1 - (int)j0 : 0;  // may be <= c_lo: nothing seen
+            float mt = -INFINITY;
+            for (int cb = 0; cb < KT / 32; cb++) {
+                uint32_t r[32];
+                tmem_load32(sbuf + cb * 32, r);
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    const int c = cb * 32 + e;
+                    if (c >= c_lo && c < c_hi) mt = fmaxf(mt, __uint_as_float(r[e]));
+                }
+            }
+            mt *= a.sscale;  // sscale is positive
+            float corr = 1.0f;
+            if (mt > m_used + 8.0f) {  // also a row's first keys (m_used = -inf)
+                corr = ex2(m_used - mt);  // 0 for the first keys
+                m_used = mt;
+            }
+            const float base = fmaxf(m_used, -1e30f);  // finite, so a row that has seen nothing yet gets 2^-inf = 0 and no NaN
+            // The probabilities go where P V of the tile before read its own: wait for it; the output is then also at rest.
+            if (i > 0 && !mbar_wait(&bar.pv_done, (i - 1) & 1)) {
+                ok = false;
+                break;
+            }
+            float sum = 0.0f;
+            for (int cb = 0; cb < KT / 32; cb++) {
+                uint32_t r[32];
+                tmem_load32(sbuf + cb * 32, r);
+                uint8_t* prow = raw + OFF_P + (cb >> 1) * CHUNK + row * 128;
+#pragma unroll
+                for (int pc = 0; pc < 4; pc++) {  // pieces of eight probabilities (16 bytes)
+                    uint32_t h[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int c = cb * 32 + pc * 8 + 2 * e;
+                        const float e0 = (c >= c_lo && c < c_hi) ? ex2(fmaf(__uint_as_float(r[pc * 8 + 2 * e]), a.sscale, -base)) : 0.0f;
+                        const float e1 = (c + 1 >= c_lo && c + 1 < c_hi) ? ex2(fmaf(__uint_as_float(r[pc * 8 + 2 * e + 1]), a.sscale, -base)) : 0.0f;
+                        const __half2 hh = __floats2half2_rn(e0, e1);
+                        sum += __low2float(hh) + __high2float(hh);
+                        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    }
+                    const uint32_t piece = (cb & 1) * 4 + pc;
+                    *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+            }
+            l_run = fmaf(l_run, corr, sum);
+            if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                for (int cb = 0; cb < D / 32; cb++) {
+                    uint32_t r[32];
+                    tmem_load32(tmem + lane_addr + 2 * KT + cb * 32, r);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
+                    tmem_store32(tmem + lane_addr + 2 * KT + cb * 32, r);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar.p_ready);
+        }
+        if (ok && !mbar_wait(&bar.pv_done, (nt - 1) & 1)) ok = false;
+        if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            const size_t at = ((size_t)(t0 + tl) * a.heads + kvh * G + head) * D;
+            for (int cb = 0; cb < D / 32; cb++) {
+                uint32_t r[32];
+                tmem_load32(tmem + lane_addr + 2 * KT + cb * 32, r);
+                if (!valid) continue;
+                if (a.out_f32) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at + cb * 32);
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                        dst[e] = make_float4(__uint_as_float(r[4 * e]) * inv, __uint_as_float(r[4 * e + 1]) * inv, __uint_as_float(r[4 * e + 2]) * inv,
+                                             __uint_as_float(r[4 * e + 3]) * inv);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.out) + at + cb * 32);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const __half2 hh = __floats2half2_rn(__uint_as_float(r[8 * e + 2 * k]) * inv, __uint_as_float(r[8 * e + 2 * k + 1]) * inv);
+                            h[k] = *reinterpret_cast<const uint32_t*>(&hh);
+                        }
+                        dst[e] = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+// The shapes this kernel takes: heads of 256, four query heads to a key-value head, a ring of whole tiles, the first
+// position known on the host.
+bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap, const uint32_t* pos_dev) {
+    return head_dim == (uint32_t)D && kv_heads != 0 && heads == (uint32_t)G * kv_heads && cap % KT == 0 && pos_dev == nullptr;
+}
+
+int launch_prefill_flash_tc(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
+                            uint32_t window, uint32_t heads, uint32_t kv_heads, float sscale, int out_f32) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return fail(NO_DRIVER, "prefill attention: the driver does not export cuTensorMapEncodeTiled");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(OUT_OF_RANGE, "prefill attention: buffers must be 16-byte aligned");
+    if (tokens == 0 || window == 0 || !(sscale > 0.0f)) return fail(OUT_OF_RANGE, "prefill attention: empty chunk or window, or a scale that is not positive");
+    CUtensorMap qm, km, vm;
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)D, heads, tokens};
+        const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
+        const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)TQ}, elem[3] = {1, 1, 1};
+        const CUresult r = enc(&qm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(q), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CUDA, "prefill attention: cuTensorMapEncodeTiled (queries) failed (" + std::to_string((int)r) + ")");
+    }
+    for (int which = 0; which < 2; which++) {
+        const cuuint64_t dims[3] = {(cuuint64_t)D, cap, kv_heads};
+        const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)cap * D * 2};
+        const cuuint32_t box[3] = {64, (cuuint32_t)KT, 1}, elem[3] = {1, 1, 1};
+        const CUresult r = enc(which ? &vm : &km, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(which ? vc : kc), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CUDA, "prefill attention: cuTensorMapEncodeTiled (cache) failed (" + std::to_string((int)r) + ")");
+    }
+    static bool configured[16] = {};
+    if (!configured[ctx->gpu & 15]) {
+        TB_CUDA(cudaFuncSetAttribute(prefill_flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[ctx->gpu & 15] = true;
+    }
+    const FlashArgs a{out, tokens, pos0, cap, window, heads, sscale, out_f32};
+    TB_CUDA(launch_kernel(ctx, prefill_flash_tc_kernel, dim3((tokens + TQ - 1) / TQ, kv_heads), dim3(THREADS), (size_t)SMEM_BYTES, true, qm, km, vm, a, ctx->status));
+    return OK;
+}
+
+}  // namespace tb

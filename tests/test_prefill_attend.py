@@ -49,6 +49,60 @@ def test_prefill_attention_matches_f64(ctx, D, ratio, cap, window, pos0, tokens)
     assert np.abs(got - want).max() <= 1e-3 * top + 2.0**-11 * top, float(np.abs(got - want).max() / top)
 
 
+@pytest.mark.parametrize("cap,window,pos0,tokens", [(1024, 512, 600, 100), (2048, 2048, 0, 300), (640, 512, 1900, 129), (4096, 512, 1000, 33), (128, 128, 0, 128),
+                                                    (256, 64, 500, 31)])
+def test_the_tcgen05_kernel_and_the_mma_sync_kernel_agree(ctx, cap, window, pos0, tokens):
+    """tb_context_set_flash: heads of 256, four query heads to a key-value head and a ring of whole tiles of 128 run on tcgen05
+    (scores and outputs in tensor memory, the running maximum moved only when a tile passes it by 2^8); every other shape, and
+    setting 0, on mma.sync.  Both are the same attention: the same values to the rounding of the probabilities to f16, rows
+    past the tokens left alone, f16 or f32 out (the "flash_256" launch stores f32)."""
+    heads, D = 4 * KV, 256
+    q = f16(0.25 * values_fast(tokens * heads * D, cap + tokens))
+    kc, vc = f16(0.3 * values_fast(KV * cap * D, cap + 1)), f16(0.3 * values_fast(KV * cap * D, cap + 2))
+    qd, kd, vd = ctx.upload(q), ctx.upload(kc), ctx.upload(vc)
+    outs = []
+    for which in (0, 1):
+        ctx.set_flash(which)
+        try:
+            out = ctx.alloc((tokens + 2) * heads * D * 2)
+            out.upload(np.full((tokens + 2) * heads * D, 0x7BFF, np.uint16))
+            ctx.prefill_attend(qd, kd, vd, out, tokens, pos0, cap, window, heads, KV, D)
+            got = out.download(np.uint16, (tokens + 2) * heads * D)
+        finally:
+            ctx.set_flash(1)
+        assert np.all(got[tokens * heads * D:] == 0x7BFF), "rows past the tokens were written"
+        outs.append(f16_to_f32(got[: tokens * heads * D]))
+    top = np.abs(outs[0]).max()
+    assert np.abs(outs[0] - outs[1]).max() <= 2e-3 * top, float(np.abs(outs[0] - outs[1]).max() / top)
+    want = reference(f16_to_f32(q).astype(np.float64).reshape(tokens, heads, D), f16_to_f32(kc).astype(np.float64).reshape(KV, cap, D),
+                     f16_to_f32(vc).astype(np.float64).reshape(KV, cap, D), tokens, pos0, cap, window, heads, D).ravel()
+    for got in outs:
+        assert np.abs(got - want).max() <= 1e-3 * top + 2.0**-11 * top
+    assert ctx.status() == 0
+
+
+def test_scores_far_apart_move_the_running_maximum(ctx):
+    """Keys whose scores rise by more than 2^8 from tile to tile: the tcgen05 kernel rescales its sums and its output in tensor
+    memory on those tiles, and only the last keys carry weight."""
+    heads, D, cap, tokens, window = 4 * KV, 256, 1024, 64, 1024
+    rng = np.random.default_rng(9)
+    q = np.zeros((tokens, heads, D), np.float32)
+    q[:, :, 0] = 1.0
+    kc = 0.01 * rng.standard_normal((KV, cap, D)).astype(np.float32)
+    kc[:, :, 0] = np.arange(cap, dtype=np.float32)[None, :] * 0.25  # the score of key j is j / 4: 32 more a tile
+    vc = rng.standard_normal((KV, cap, D)).astype(np.float32)
+    qh, kh, vh = f16(q), f16(kc), f16(vc)
+    pos0 = 600
+    want = reference(f16_to_f32(qh).astype(np.float64).reshape(tokens, heads, D), f16_to_f32(kh).astype(np.float64).reshape(KV, cap, D),
+                     f16_to_f32(vh).astype(np.float64).reshape(KV, cap, D), tokens, pos0, cap, window, heads, D)
+    out = ctx.zeros(tokens * heads * D * 2)
+    ctx.prefill_attend(ctx.upload(qh), ctx.upload(kh), ctx.upload(vh), out, tokens, pos0, cap, window, heads, KV, D)
+    got = f16_to_f32(out.download(np.uint16, tokens * heads * D)).reshape(tokens, heads * D)
+    top = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-3 * top, float(np.abs(got - want).max() / top)
+    assert ctx.status() == 0
+
+
 @pytest.mark.parametrize("D", [256, 512])
 def test_prefill_attention_does_not_depend_on_the_chunking(ctx, D):
     """flash.rs:9-12: key tiles start at multiples of their size, so a token's sums are the same whichever chunk it is in."""
