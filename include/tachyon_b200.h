@@ -75,7 +75,7 @@ TB_API int tb_context_set_lean(tb_context* ctx, int mode);
  * rows evenly beforehand (0).  Results are the same bits either way.  TACHYON_B200_STATIC=1 starts a context at 0. */
 TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
 /* Which kernel tb_prefill_attend, prefill inside the decoder and "flash_256" use for heads of 256 with four query heads to a
- * key-value head and a ring of a multiple of 128 slots: 1 the tcgen05 kernel (S = Q K^T and O = P V in tensor memory;
+ * key-value head and a ring of a multiple of 64 slots: 1 the tcgen05 kernel (S = Q K^T and O = P V in tensor memory;
  * default), 0 the mma.sync kernel every other shape takes.  TACHYON_B200_FLASH=0 starts a context at 0. */
 TB_API int tb_context_set_flash(tb_context* ctx, int which);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
@@ -230,7 +230,7 @@ TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales,
  * at position pos0 + t, attends positions p - window < j <= p of the cache (f16 [kv_heads][cap][head_dim], position j in
  * slot j % cap, the chunk's own keys and values already stored).  q: device f16 [tokens][heads][head_dim] as the query
  * kernel leaves them, already multiplied by scale * log2(e); out: device f16 [tokens][heads * head_dim].
- * head_dim 256 or 512; heads / kv_heads in {1, 2, 4, 8}.  Key tiles start at multiples of their size (32 positions; 128 in the
+ * head_dim 256 or 512; heads / kv_heads in {1, 2, 4, 8}.  Key tiles start at multiples of their size (32 positions; 64 in the
  * tcgen05 kernel, see tb_context_set_flash), so a token's sums do not depend on how the prompt was cut into chunks.
  */
 TB_API int tb_prefill_attend(tb_context* ctx, const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out, uint32_t tokens,

@@ -4,21 +4,26 @@
 // which stays for every other shape.
 //
 // A block takes 32 tokens x the four query heads of one key-value head = 128 query rows (row = 4 * token + head) and walks
-// the keys in tiles of 128 positions that start at multiples of 128, so a token's sums do not depend on how the prompt was
-// cut into chunks (flash.rs:9-12).  Six warps:
+// the keys in tiles of 64 positions that start at multiples of 64, so a token's sums do not depend on how the prompt was
+// cut into chunks (flash.rs:9-12).  Ten warps:
 //   warp 0      one thread issues the TMA loads: the queries once (3-D map over [token][head][256]), then per tile the keys and
-//               the values of 128 ring slots (3-D maps over [key-value head][slot][256]), each as four boxes of 64 dimensions
-//               in the 128-byte swizzle;
-//   warp 1      allocates tensor memory (512 columns: two score buffers of 128, the output of 256); one thread issues
-//               S = Q K^T (M128 N128 K256: both operands K-major) and O += P V (M128 N256 K128: P K-major from shared memory,
+//               the values of 64 ring slots (3-D maps over [key-value head][slot][256]), each as four boxes of 64 dimensions
+//               in the 128-byte swizzle, two tiles ahead of the products (two stages of keys, two of values);
+//   warp 1      allocates tensor memory (two score buffers of 64 columns, the output of 256); one thread issues
+//               S = Q K^T (M128 N64 K256: both operands K-major) and O += P V (M128 N256 K64: P K-major from shared memory,
 //               V as it lies in the cache, [key][dimension], which is the MN-major form of a B operand);
-//   warps 2-5   softmax: thread r owns query row r (tensor-memory lane r).  Two passes over the tile's scores with tcgen05.ld
-//               (maximum, then exponentials), probabilities rounded to f16 into shared memory in the swizzled K-major layout,
-//               sums taken from the rounded values.  The running maximum only moves when a tile exceeds it by more than 8
-//               (in base 2), so probabilities stay below 2^8 and the output in tensor memory is rescaled (tcgen05.ld, multiply,
-//               tcgen05.st) only on those tiles, usually the first one or two.
-// The score buffers alternate, so S of tile i + 1 is multiplied while tile i is in the softmax; keys of tile i + 1 are
-// loaded as soon as S of tile i is done, values as soon as P V of tile i is done.  Every wait is bounded.
+//   warps 2-9   softmax: two threads own query row r (tensor-memory lane r; warps w and w + 4 read the same quarter of the
+//               lanes), one the tile's first 32 keys and the first 128 output dimensions, the other the rest; they trade their
+//               maxima through shared memory.  Two passes over the tile's scores with tcgen05.ld (maximum, then exponentials;
+//               a half no row of the warp sees is skipped), probabilities rounded to f16 into shared memory in the
+//               swizzled K-major layout.  The running maximum only moves when a tile
+//               exceeds it by more than 8 (in base 2), so probabilities stay below 2^8 and the output in tensor memory is
+//               rescaled (tcgen05.ld, multiply, tcgen05.st) only on those tiles, usually the first one or two.
+// The score buffers and the probability buffers alternate, so S of tile i + 1 is multiplied while tile i is in the softmax and
+// P V of tile i while tile i + 1 is; keys of tile i + 2 are loaded as soon as S of tile i is done, values as soon as P V of
+// tile i is done.  What bounds it, measured by switching parts off: 64 KiB of loads a tile is the SM's rate from the L2
+// (0.6 us), the products and the softmax add 0.6 us each when alone and 0.8 together; they share the 224 KiB of
+// shared-memory traffic a tile causes (the score product re-reads the 64 KiB of queries every tile).  Every wait is bounded.
 #include <cuda.h>
 
 #include <string>
@@ -30,11 +35,13 @@ namespace tb {
 
 namespace {
 
-constexpr int D = 256, G = 4, TQ = 32, ROWS = TQ * G, KT = 128;
-constexpr int CHUNK = ROWS * 128;                          // a box of 64 dimensions (128 bytes) x 128 rows
-constexpr int OFF_Q = 0, OFF_K = 4 * CHUNK, OFF_V = 8 * CHUNK, OFF_P = 12 * CHUNK, OFF_BAR = 14 * CHUNK;
-constexpr int SMEM_BYTES = 1024 + OFF_BAR + 256;
-constexpr int THREADS = 192;
+constexpr int D = 256, G = 4, TQ = 32, ROWS = TQ * G, KT = 64;
+constexpr int CHUNK = ROWS * 128;                          // queries, probabilities: a box of 64 dimensions (128 bytes) x 128 rows
+constexpr int KCH = KT * 128, STAGE = 4 * KCH;             // keys, values: a box of 64 dimensions x 64 slots; a tile is four of them
+constexpr int OFF_Q = 0, OFF_K = 4 * CHUNK, OFF_V = OFF_K + 2 * STAGE, OFF_P = OFF_V + 2 * STAGE, OFF_BAR = OFF_P + 2 * CHUNK;  // two buffers of probabilities
+constexpr int SMEM_BYTES = 1024 + OFF_BAR + 128 + 2 * ROWS * 4;
+constexpr int COL_O = 2 * KT;                              // tensor-memory columns: scores at 0 and KT, the output from here
+constexpr int THREADS = 320;
 static_assert(SMEM_BYTES <= 232448, "over the 227 KiB a block may use");
 
 // kind::f16 instruction descriptors: f32 accumulator, f16 operands, A K-major; N >> 3 at bit 17, M >> 4 at bit 24; bit 16 set
@@ -98,8 +105,9 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 struct Bars {
-    uint64_t q_full, k_full, v_full, s_full[2], p_ready, pv_done;
+    uint64_t q_full, k_full[2], v_full[2], s_full[2], p_ready[2], pv_done[2];
     uint32_t tmem;
+    float xch[2][ROWS];  // [half][row]: what a row's two threads trade: each tile their maxima, at the end their sums
 };
 
 struct FlashArgs {
@@ -121,8 +129,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
     const uint32_t tile0 = lo / KT * KT, nt = (p_last - tile0) / KT + 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bar.q_full, 1), mbar_init(&bar.k_full, 1), mbar_init(&bar.v_full, 1);
-        mbar_init(&bar.s_full[0], 1), mbar_init(&bar.s_full[1], 1), mbar_init(&bar.p_ready, 4), mbar_init(&bar.pv_done, 1);
+        mbar_init(&bar.q_full, 1);
+        for (int k = 0; k < 2; k++)
+            mbar_init(&bar.k_full[k], 1), mbar_init(&bar.v_full[k], 1), mbar_init(&bar.s_full[k], 1), mbar_init(&bar.pv_done[k], 1), mbar_init(&bar.p_ready[k], 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -142,19 +151,20 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
             for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_Q + c * CHUNK, &q_map, 64 * c, (int)(kvh * G), (int)t0, &bar.q_full);
             for (uint32_t i = 0; i < nt; i++) {
                 const int slot0 = (int)((tile0 + i * KT) % a.cap);
-                // The key buffer is free once S of the tile before is done, the value buffer once its P V is done.
-                if (i > 0 && !mbar_wait(&bar.s_full[(i - 1) & 1], ((i - 1) >> 1) & 1)) {
+                const uint32_t st = i & 1, before = ((i - 2) >> 1) & 1;  // the stage, and the parity of the tile that held it last
+                // A key stage is free once S of the tile two before is done, a value stage once that tile's P V is done.
+                if (i >= 2 && !mbar_wait(&bar.s_full[st], before)) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                     break;
                 }
-                mbar_expect_tx(&bar.k_full, 4 * CHUNK);
-                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_K + c * CHUNK, &k_map, 64 * c, slot0, (int)kvh, &bar.k_full);
-                if (i > 0 && !mbar_wait(&bar.pv_done, (i - 1) & 1)) {
+                mbar_expect_tx(&bar.k_full[st], STAGE);
+                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_K + st * STAGE + c * KCH, &k_map, 64 * c, slot0, (int)kvh, &bar.k_full[st]);
+                if (i >= 2 && !mbar_wait(&bar.pv_done[st], before)) {
                     atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
                     break;
                 }
-                mbar_expect_tx(&bar.v_full, 4 * CHUNK);
-                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_V + c * CHUNK, &v_map, 64 * c, slot0, (int)kvh, &bar.v_full);
+                mbar_expect_tx(&bar.v_full[st], STAGE);
+                for (int c = 0; c < 4; c++) tma_load_3d(raw + OFF_V + st * STAGE + c * KCH, &v_map, 64 * c, slot0, (int)kvh, &bar.v_full[st]);
             }
         }
     } else if (warp == 1) {
@@ -162,117 +172,123 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
             const uint32_t qa = smem_addr(raw + OFF_Q), ka = smem_addr(raw + OFF_K), va = smem_addr(raw + OFF_V), pa = smem_addr(raw + OFF_P);
             auto scores = [&](uint32_t i) {  // S[i & 1] = Q K^T over the 256 dimensions: sixteen products of K = 16
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int k = 0; k < D / 16; k++) {
-                    const uint32_t off = (k >> 2) * CHUNK + (k & 3) * 32;
-                    mma_f16(tmem + (i & 1) * KT, desc_k_major(qa + off), desc_k_major(ka + off), IDESC_S, k > 0 ? 1u : 0u);
-                }
+                for (int k = 0; k < D / 16; k++)
+                    mma_f16(tmem + (i & 1) * KT, desc_k_major(qa + (k >> 2) * CHUNK + (k & 3) * 32), desc_k_major(ka + (i & 1) * STAGE + (k >> 2) * KCH + (k & 3) * 32),
+                            IDESC_S, k > 0 ? 1u : 0u);
                 mma_commit(&bar.s_full[i & 1]);
             };
-            bool ok = mbar_wait(&bar.q_full, 0) && mbar_wait(&bar.k_full, 0);
+            bool ok = mbar_wait(&bar.q_full, 0) && mbar_wait(&bar.k_full[0], 0);
             if (ok) scores(0);
             for (uint32_t i = 0; i < nt && ok; i++) {
                 if (i + 1 < nt) {
-                    ok = mbar_wait(&bar.k_full, (i + 1) & 1);
+                    ok = mbar_wait(&bar.k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
                     if (ok) scores(i + 1);
                 }
-                ok = ok && mbar_wait(&bar.p_ready, i & 1) && mbar_wait(&bar.v_full, i & 1);
+                ok = ok && mbar_wait(&bar.p_ready[i & 1], (i >> 1) & 1) && mbar_wait(&bar.v_full[i & 1], (i >> 1) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int k = 0; k < KT / 16; k++) {  // O += P V over the tile's 128 keys: eight products of K = 16
-                    const uint64_t da = desc_k_major(pa + (k >> 2) * CHUNK + (k & 3) * 32);
-                    const uint64_t db = desc_mn_major(va + k * 2048, CHUNK);
-                    mma_f16(tmem + 2 * KT, da, db, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-                }
-                mma_commit(&bar.pv_done);
+                for (int k = 0; k < KT / 16; k++)  // O += P V over the tile's 64 keys: four products of K = 16
+                    mma_f16(tmem + COL_O, desc_k_major(pa + (i & 1) * CHUNK + k * 32), desc_mn_major(va + (i & 1) * STAGE + k * 2048, KCH), IDESC_PV,
+                            (i > 0 || k > 0) ? 1u : 0u);
+                mma_commit(&bar.pv_done[i & 1]);
             }
             if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
         }
     } else {
-        // Softmax and epilogue.  This warp reads the tensor-memory lanes of its quarter, warp % 4; thread = query row.
-        const uint32_t quarter = warp & 3, row = 32 * quarter + lane, tl = row / G, head = row % G;
+        // Softmax and epilogue.  This warp reads the tensor-memory lanes of its quarter, warp % 4; a row's two threads (in warps
+        // w and w + 4) take the tile's keys 32 half .. + 31 and the output's dimensions 128 half .. + 127.
+        const uint32_t quarter = warp & 3, half = (uint32_t)(warp - 2) >> 2, row = 32 * quarter + lane, tl = row / G, head = row % G;
         const uint32_t p = a.pos0 + t0 + tl;
         const bool valid = t0 + tl < a.tokens;
         const uint32_t lane_addr = (32 * quarter) << 16;
+        const uint32_t first_seen = p + 1 > a.window ? p + 1 - a.window : 0;
         float m_used = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (uint32_t i = 0; i < nt; i++) {
-            const uint32_t j0 = tile0 + i * KT, sbuf = tmem + lane_addr + (i & 1) * KT;
-            if (!mbar_wait(&bar.s_full[i & 1], (i >> 1) & 1)) {
-                ok = false;
-                break;
-            }
+            const uint32_t j0 = tile0 + i * KT, sbuf = tmem + lane_addr + (i & 1) * KT + half * 32;
+            // A wait that runs out is reported once; the thread then walks the remaining tiles without waiting, so that it still
+            // meets its partner at every barrier below.
+            if (ok && !mbar_wait(&bar.s_full[i & 1], (i >> 1) & 1)) ok = false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // Keys j0 + c are seen when c lies in [c_lo, c_hi): at or before this token, inside its window.
-            const uint32_t first_seen = p + 1 > a.window ? p + 1 - a.window : 0;
-            const int c_lo = valid ? (int)max(first_seen, j0) - (int)j0 : KT;
-            const int c_hi = valid ? (int)min(p, j0 + KT - 1) + 1 - (int)j0 : 0;  // may be <= c_lo: nothing seen
+            // Key j0 + 32 half + c is seen when c lies in [c_lo, c_hi): at or before this token, inside its window.
+            const int k0 = (int)(j0 + 32 * half);
+            const int c_lo = valid ? max((int)first_seen - k0, 0) : 32;
+            const int c_hi = valid ? min((int)p + 1 - k0, 32) : 0;  // may be <= c_lo: nothing seen
+            const bool any = __any_sync(0xffffffffu, c_lo < c_hi);  // whether any row of the warp sees a key of this half
             float mt = -INFINITY;
-            for (int cb = 0; cb < KT / 32; cb++) {
+            if (any) {
                 uint32_t r[32];
-                tmem_load32(sbuf + cb * 32, r);
+                tmem_load32(sbuf, r);
 #pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    const int c = cb * 32 + e;
-                    if (c >= c_lo && c < c_hi) mt = fmaxf(mt, __uint_as_float(r[e]));
-                }
+                for (int e = 0; e < 32; e++)
+                    if (e >= c_lo && e < c_hi) mt = fmaxf(mt, __uint_as_float(r[e]));
             }
-            mt *= a.sscale;  // sscale is positive
+            bar.xch[half][row] = mt;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (int)quarter) : "memory");  // the row's two threads
+            mt = fmaxf(mt, bar.xch[half ^ 1][row]) * a.sscale;  // sscale is positive
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (int)quarter) : "memory");  // both have read: the slots may be written again
             float corr = 1.0f;
             if (mt > m_used + 8.0f) {  // also a row's first keys (m_used = -inf)
                 corr = ex2(m_used - mt);  // 0 for the first keys
                 m_used = mt;
             }
             const float base = fmaxf(m_used, -1e30f);  // finite, so a row that has seen nothing yet gets 2^-inf = 0 and no NaN
-            // The probabilities go where P V of the tile before read its own: wait for it; the output is then also at rest.
-            if (i > 0 && !mbar_wait(&bar.pv_done, (i - 1) & 1)) {
-                ok = false;
-                break;
-            }
+            // The probabilities go where P V of the tile two before read its own: wait for it.
+            if (ok && i >= 2 && !mbar_wait(&bar.pv_done[i & 1], ((i - 2) >> 1) & 1)) ok = false;
             float sum = 0.0f;
-            for (int cb = 0; cb < KT / 32; cb++) {
+            uint8_t* prow = raw + OFF_P + (i & 1) * CHUNK + row * 128;  // this thread's half of the row: pieces 4 half .. 4 half + 3
+            if (!any) {  // nobody sees these keys: zeros, which P V still multiplies
+#pragma unroll
+                for (int pc = 0; pc < 4; pc++) *reinterpret_cast<uint4*>(prow + (((half * 4 + pc) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            } else {
                 uint32_t r[32];
-                tmem_load32(sbuf + cb * 32, r);
-                uint8_t* prow = raw + OFF_P + (cb >> 1) * CHUNK + row * 128;
+                tmem_load32(sbuf, r);
 #pragma unroll
                 for (int pc = 0; pc < 4; pc++) {  // pieces of eight probabilities (16 bytes)
                     uint32_t h[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        const int c = cb * 32 + pc * 8 + 2 * e;
-                        const float e0 = (c >= c_lo && c < c_hi) ? ex2(fmaf(__uint_as_float(r[pc * 8 + 2 * e]), a.sscale, -base)) : 0.0f;
-                        const float e1 = (c + 1 >= c_lo && c + 1 < c_hi) ? ex2(fmaf(__uint_as_float(r[pc * 8 + 2 * e + 1]), a.sscale, -base)) : 0.0f;
+                        const int c = pc * 8 + 2 * e;
+                        const float e0 = (c >= c_lo && c < c_hi) ? ex2(fmaf(__uint_as_float(r[c]), a.sscale, -base)) : 0.0f;
+                        const float e1 = (c + 1 >= c_lo && c + 1 < c_hi) ? ex2(fmaf(__uint_as_float(r[c + 1]), a.sscale, -base)) : 0.0f;
                         const __half2 hh = __floats2half2_rn(e0, e1);
-                        sum += __low2float(hh) + __high2float(hh);
+                        sum += e0 + e1;  // before the rounding: converting back would cost as much as the exponentials
                         h[e] = *reinterpret_cast<const uint32_t*>(&hh);
                     }
-                    const uint32_t piece = (cb & 1) * 4 + pc;
-                    *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(prow + (((half * 4 + pc) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
             }
             l_run = fmaf(l_run, corr, sum);
             if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                for (int cb = 0; cb < D / 32; cb++) {
+                // The output must be at rest: P V of the tile before is done.
+                if (ok && !mbar_wait(&bar.pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) ok = false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int cb = 0; cb < 4; cb++) {
                     uint32_t r[32];
-                    tmem_load32(tmem + lane_addr + 2 * KT + cb * 32, r);
+                    const uint32_t at = tmem + lane_addr + COL_O + half * 128 + cb * 32;
+                    tmem_load32(at, r);
 #pragma unroll
                     for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
-                    tmem_store32(tmem + lane_addr + 2 * KT + cb * 32, r);
+                    tmem_store32(at, r);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar.p_ready);
+            if (lane == 0) mbar_arrive(&bar.p_ready[i & 1]);
         }
-        if (ok && !mbar_wait(&bar.pv_done, (nt - 1) & 1)) ok = false;
+        if (ok && !mbar_wait(&bar.pv_done[(nt - 1) & 1], ((nt - 1) >> 1) & 1)) ok = false;
         if (!ok) atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        bar.xch[half][row] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + (int)quarter) : "memory");
         if (ok) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            const size_t at = ((size_t)(t0 + tl) * a.heads + kvh * G + head) * D;
-            for (int cb = 0; cb < D / 32; cb++) {
+            const float l_all = l_run + bar.xch[half ^ 1][row];
+            const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+            const size_t at = ((size_t)(t0 + tl) * a.heads + kvh * G + head) * D + half * 128;
+            for (int cb = 0; cb < 4; cb++) {
                 uint32_t r[32];
-                tmem_load32(tmem + lane_addr + 2 * KT + cb * 32, r);
+                tmem_load32(tmem + lane_addr + COL_O + half * 128 + cb * 32, r);
                 if (!valid) continue;
                 if (a.out_f32) {
                     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at + cb * 32);

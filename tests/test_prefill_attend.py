@@ -52,7 +52,7 @@ def test_prefill_attention_matches_f64(ctx, D, ratio, cap, window, pos0, tokens)
 @pytest.mark.parametrize("cap,window,pos0,tokens", [(1024, 512, 600, 100), (2048, 2048, 0, 300), (640, 512, 1900, 129), (4096, 512, 1000, 33), (128, 128, 0, 128),
                                                     (256, 64, 500, 31)])
 def test_the_tcgen05_kernel_and_the_mma_sync_kernel_agree(ctx, cap, window, pos0, tokens):
-    """tb_context_set_flash: heads of 256, four query heads to a key-value head and a ring of whole tiles of 128 run on tcgen05
+    """tb_context_set_flash: heads of 256, four query heads to a key-value head and a ring of whole tiles of 64 run on tcgen05
     (scores and outputs in tensor memory, the running maximum moved only when a tile passes it by 2^8); every other shape, and
     setting 0, on mma.sync.  Both are the same attention: the same values to the rounding of the probabilities to f16, rows
     past the tokens left alone, f16 or f32 out (the "flash_256" launch stores f32)."""
