@@ -76,7 +76,8 @@ TB_API int tb_context_set_lean(tb_context* ctx, int mode);
 TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
 /* Which kernel tb_prefill_attend, prefill inside the decoder and "flash_256" use for heads of 256 with four query heads to a
  * key-value head and a ring of a multiple of 64 slots: 1 the tcgen05 kernel (S = Q K^T and O = P V in tensor memory;
- * default), 0 the mma.sync kernel every other shape takes.  TACHYON_B200_FLASH=0 starts a context at 0. */
+ * default), 0 the mma.sync kernel every other shape takes.  An encoder with heads of 64 opened while this is 1 runs its
+ * attention on tcgen05 as well (tiles of 128 queries of a sequence and head).  TACHYON_B200_FLASH=0 starts a context at 0. */
 TB_API int tb_context_set_flash(tb_context* ctx, int which);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
 TB_API int tb_status(tb_context* ctx, uint32_t* word);

@@ -402,6 +402,7 @@ struct tb_encoder {
     size_t input_words = 0;
     uint32_t *ids = nullptr, *pos = nullptr, *tiles = nullptr, *starts = nullptr, *lens = nullptr;
     bool use_graphs = true, warmed = false;
+    uint32_t tile_q = QT;  // queries a tile of the list holds: 64, or 128 where attention runs on tcgen05 (decided when the encoder is opened)
     std::vector<EGraph> graphs;
 };
 
@@ -524,7 +525,8 @@ int enc_layers(tb_encoder* e, uint32_t n, uint32_t slots, uint32_t sequences) {
         if (l > 0) launch_enc_norm(s, n, e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
         TB_TRY(enc_product(e, L.qkv, e->a16, n, e->qkv16, 1));
         enc_rope_kernel<<<(n + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->rope[L.global ? 0 : 1], h, d, n);
-        TB_TRY(launch_enc_attend(ctx, e->qkv16, e->tiles, e->att16, h, d, L.global ? -1 : (int)c.window, scale, slots));
+        if (e->tile_q == 128) TB_TRY(launch_enc_attend_tc(ctx, e->qkv16, e->tiles, e->att16, h, L.global ? -1 : (int)c.window, scale, slots, n));
+        else TB_TRY(launch_enc_attend(ctx, e->qkv16, e->tiles, e->att16, h, d, L.global ? -1 : (int)c.window, scale, slots));
         TB_TRY(enc_product(e, L.o, e->att16, n, e->x, 3));
         launch_enc_norm(s, n, e->x, nullptr, nullptr, L.mlp_norm, h, c.eps, nullptr, e->a16);
         TB_TRY(enc_product(e, L.up, e->a16, n, e->g16, c.gated == 2 ? 8 : c.gated ? 4 : 5));
@@ -546,7 +548,7 @@ int enc_batch(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t
     for (uint32_t q = 0; q < sequences; q++) {
         hs[q] = T, hl[q] = lens[q];
         for (uint32_t i = 0; i < lens[q]; i++) hi[T + i] = ids[T + i], hp[T + i] = i;
-        for (uint32_t q0 = 0; q0 < lens[q]; q0 += QT, tiles++) ht[3 * tiles] = T, ht[3 * tiles + 1] = lens[q], ht[3 * tiles + 2] = q0;
+        for (uint32_t q0 = 0; q0 < lens[q]; q0 += e->tile_q, tiles++) ht[3 * tiles] = T, ht[3 * tiles + 1] = lens[q], ht[3 * tiles + 2] = q0;
         T += lens[q];
     }
     const uint32_t n = (T + QT - 1) / QT * QT, slots = n / QT + sequences;
@@ -607,6 +609,7 @@ int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t toke
     e->layers.resize(cfg->layers);
     const char* env = getenv("TACHYON_B200_ENCODER_GRAPHS");
     e->use_graphs = !(env && env[0] == '0');
+    e->tile_q = (ctx->flash_tc && enc_attend_tc_supports(cfg->hidden, cfg->hidden / cfg->heads)) ? 128u : (uint32_t)QT;
     e->arena_bytes = enc_layout(e, nullptr);
     cudaError_t err = cudaSetDevice(ctx->gpu);
     if (err == cudaSuccess) err = cudaMalloc(&e->arena, e->arena_bytes);

@@ -266,6 +266,10 @@ int launch_gelu_f16(tb_context* ctx, const float* x, __half* out, uint32_t width
 int launch_rope_f16(tb_context* ctx, __half* qkv, const float* table, const uint32_t* pos, uint32_t h, uint32_t d, uint32_t n);
 int launch_gemm_q8e(tb_context* ctx, const int8_t* a, const int8_t* w, const float* bias, void* y, uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t mode,
                     const float* sa, const float* sw);
+// Heads of 64 on tcgen05 (enc_attend_tc.cu): tiles of up to 128 queries; `rows` is how many rows qkv holds.
+bool enc_attend_tc_supports(uint32_t h, uint32_t d);
+int launch_enc_attend_tc(tb_context* ctx, const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, int window, float scale, uint32_t ntiles,
+                         uint32_t rows);
 int launch_enc_attend(tb_context* ctx, const __half* qkv, const uint32_t* tiles, __half* out, uint32_t h, uint32_t d, int window, float scale, uint32_t ntiles);
 
 // The reference's own formats (q4.cu): f32 -> Q8 codes and [s, s * sum q] pairs; Q4 weights x Q8 activations.

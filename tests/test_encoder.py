@@ -269,3 +269,34 @@ def test_encoder_refuses_what_it_cannot_hold(ctx):
         enc.load("9.qkv", np.zeros(7, np.int8))
     assert e.value.status == 8
     enc.close()
+
+
+@pytest.mark.gpu
+def test_attention_on_tcgen05_and_on_mma_sync_agree(ctx):
+    """An encoder with heads of 64 opened while tb_context_set_flash is 1 (the default) runs its attention on tcgen05, tiles of 128
+    queries of a sequence and head; opened under 0, on mma.sync with tiles of 64.  Same hidden states to the rounding of the
+    probabilities, on sequences shorter and longer than a tile and past the window, alone or packed."""
+    rng = np.random.default_rng(31)
+    cfg, weights = random_model(rng, h=256, heads=4, inter=512, layers=4)  # layers 0 and 3 global, 1 and 2 within 8 either way
+    seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (1, 63, 64, 65, 127, 128, 129, 300, 512, 17)]
+    hidden = []
+    for which in (0, 1):
+        ctx.set_flash(which)
+        try:
+            enc, deq = build(ctx, cfg, weights, tokens=2048, sequences=16)
+        finally:
+            ctx.set_flash(1)
+        emb = enc.embed(seqs)
+        hidden.append(enc.hidden())
+        if which == 1:
+            for i in (0, 4, 7, 8):
+                assert np.array_equal(enc.embed([seqs[i]])[0], emb[i]), "packed or alone: the same bits"
+        enc.close()
+    top = np.abs(hidden[0]).max()
+    assert np.abs(hidden[0] - hidden[1]).max() <= 4e-3 * top, float(np.abs(hidden[0] - hidden[1]).max() / top)
+    at = 0
+    for q in seqs[:8]:
+        want = oracle.encoder_forward(cfg, deq, q)
+        assert np.abs(hidden[1][at:at + len(q)] - want).max() < 3e-2
+        at += len(q)
+    assert ctx.status() == 0
