@@ -237,9 +237,9 @@ int launch_prefill_rows(tb_context* ctx, const float* qkv, const float* q_norm, 
 // out: f16 (or f32 with out_f32) [tokens][heads * head_dim].  pos_dev: the first position from device memory instead of pos0;
 // sscale: factor of the scores (1 when the queries already carry scale * log2(e)).
 // The same on tcgen05 (prefill_tc.cu), for the shapes prefill_flash_tc_supports names.
-bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap, const uint32_t* pos_dev);
+bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap);
 int launch_prefill_flash_tc(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                            uint32_t window, uint32_t heads, uint32_t kv_heads, float sscale, int out_f32);
+                            uint32_t window, uint32_t heads, uint32_t kv_heads, const uint32_t* pos_dev, float sscale, int out_f32);
 int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
                          uint32_t window, uint32_t heads, uint32_t kv_heads, uint32_t head_dim = 256, const uint32_t* pos_dev = nullptr, float sscale = 1.0f,
                          int out_f32 = 0);

@@ -394,8 +394,8 @@ int launch_prefill_flash(tb_context* ctx, const __half* q, const __half* kc, con
     const uint32_t ratio = heads / kv_heads, group = ratio < 4 ? ratio : 4;  // query heads a block takes
     if (ratio != 1 && ratio != 2 && ratio != 4 && ratio != 8) return fail(UNSUPPORTED, "prefill attention: 1, 2, 4 or 8 query heads per key-value head");
     if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill attention: heads of 256 or 512");
-    if (ctx->flash_tc && prefill_flash_tc_supports(heads, kv_heads, head_dim, cap, pos_dev))
-        return launch_prefill_flash_tc(ctx, q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads, sscale, out_f32);
+    if (ctx->flash_tc && prefill_flash_tc_supports(heads, kv_heads, head_dim, cap))
+        return launch_prefill_flash_tc(ctx, q, kc, vc, out, tokens, pos0, cap, window, heads, kv_heads, pos_dev, sscale, out_f32);
     // queries, two stages of keys and values; rows padded by 8 halves
     auto bytes = [&](uint32_t grp) { return (size_t)(grp * FT + 4 * FK) * (head_dim + 8) * 2; };
     static bool configured[16] = {};

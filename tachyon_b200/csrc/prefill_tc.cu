@@ -60,6 +60,7 @@ struct Bars {
 
 struct FlashArgs {
     void* out;
+    const uint32_t* pos_dev;  // the first position from device memory instead of pos0 (the "flash_256" launch), or null
     uint32_t tokens, pos0, cap, window, heads;
     float sscale;  // factor of the scores (1 when the queries already carry scale * log2 e)
     int out_f32;
@@ -72,7 +73,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
     Bars& bar = *reinterpret_cast<Bars*>(raw + OFF_BAR);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t t0 = blockIdx.x * TQ, kvh = blockIdx.y;
-    const uint32_t p_first = a.pos0 + t0, p_last = a.pos0 + min(t0 + TQ, a.tokens) - 1;
+    pdl_wait();  // the queries, this chunk's keys and values and the position come from the kernels in front
+    const uint32_t pos0 = a.pos_dev != nullptr ? __ldg(a.pos_dev) : a.pos0;
+    const uint32_t p_first = pos0 + t0, p_last = pos0 + min(t0 + TQ, a.tokens) - 1;
     const uint32_t lo = p_first + 1 > a.window ? p_first + 1 - a.window : 0;  // oldest position any token of the block sees
     const uint32_t tile0 = lo / KT * KT, nt = (p_last - tile0) / KT + 1;
 
@@ -91,7 +94,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bar.tmem;
-    pdl_wait();  // the queries and this chunk's keys and values come from the kernels in front
 
     if (warp == 0) {
         if (lane == 0) {
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
         // Softmax and epilogue.  This warp reads the tensor-memory lanes of its quarter, warp % 4; a row's two threads (in warps
         // w and w + 4) take the tile's keys 32 half .. + 31 and the output's dimensions 128 half .. + 127.
         const uint32_t quarter = warp & 3, half = (uint32_t)(warp - 2) >> 2, row = 32 * quarter + lane, tl = row / G, head = row % G;
-        const uint32_t p = a.pos0 + t0 + tl;
+        const uint32_t p = pos0 + t0 + tl;
         const bool valid = t0 + tl < a.tokens;
         const uint32_t lane_addr = (32 * quarter) << 16;
         const uint32_t first_seen = p + 1 > a.window ? p + 1 - a.window : 0;
@@ -267,14 +269,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_flash_tc_kernel(const __gr
 
 }  // namespace
 
-// The shapes this kernel takes: heads of 256, four query heads to a key-value head, a ring of whole tiles, the first
-// position known on the host.
-bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap, const uint32_t* pos_dev) {
-    return head_dim == (uint32_t)D && kv_heads != 0 && heads == (uint32_t)G * kv_heads && cap % KT == 0 && pos_dev == nullptr;
+// The shapes this kernel takes: heads of 256, four query heads to a key-value head, a ring of whole tiles.
+bool prefill_flash_tc_supports(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t cap) {
+    return head_dim == (uint32_t)D && kv_heads != 0 && heads == (uint32_t)G * kv_heads && cap % KT == 0;
 }
 
 int launch_prefill_flash_tc(tb_context* ctx, const __half* q, const __half* kc, const __half* vc, void* out, uint32_t tokens, uint32_t pos0, uint32_t cap,
-                            uint32_t window, uint32_t heads, uint32_t kv_heads, float sscale, int out_f32) {
+                            uint32_t window, uint32_t heads, uint32_t kv_heads, const uint32_t* pos_dev, float sscale, int out_f32) {
     tc::EncodeTiled enc = tc::encode_tiled();
     if (!enc) return fail(NO_DRIVER, "prefill attention: the driver does not export cuTensorMapEncodeTiled");
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) | reinterpret_cast<uintptr_t>(out)) & 15)
@@ -302,7 +303,7 @@ int launch_prefill_flash_tc(tb_context* ctx, const __half* q, const __half* kc, 
         TB_CUDA(cudaFuncSetAttribute(prefill_flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured[ctx->gpu & 15] = true;
     }
-    const FlashArgs a{out, tokens, pos0, cap, window, heads, sscale, out_f32};
+    const FlashArgs a{out, pos_dev, tokens, pos0, cap, window, heads, sscale, out_f32};
     TB_CUDA(launch_kernel(ctx, prefill_flash_tc_kernel, dim3((tokens + TQ - 1) / TQ, kv_heads), dim3(THREADS), (size_t)SMEM_BYTES, true, qm, km, vm, a, ctx->status));
     return OK;
 }
