@@ -320,8 +320,14 @@ __global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, cons
     for (uint32_t i = tid; i < h; i += 256) {
         float v = 0.0f;
         if (mean) {
-            for (uint32_t t = 0; t < len; t++) v += hidden[(size_t)(start + t) * h + i];
-            v /= (float)len;
+            // Four running sums, so that several loads are in flight instead of one.
+            const float* col = hidden + (size_t)start * h + i;
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            uint32_t t = 0;
+#pragma unroll 2
+            for (; t + 4 <= len; t += 4) a0 += col[(size_t)t * h], a1 += col[(size_t)(t + 1) * h], a2 += col[(size_t)(t + 2) * h], a3 += col[(size_t)(t + 3) * h];
+            for (; t < len; t++) a0 += col[(size_t)t * h];
+            v = ((a0 + a1) + (a2 + a3)) / (float)len;
         } else {
             v = hidden[(size_t)start * h + i];
         }
