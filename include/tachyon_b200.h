@@ -174,6 +174,10 @@ TB_API int tb_gemm_q4(tb_context* ctx, const uint8_t* packed, const uint16_t* sc
  * modes (ptx/encoder.rs:5-9, 498-525), which the reference uses for encoders too narrow for 8-bit weights (encoder/convert.rs:
  * 26-29).  The weight tile goes to the tensor cores as it is. */
 TB_API int tb_gemm_f16(tb_context* ctx, const uint16_t* w, const uint16_t* a, uint32_t m, uint32_t n, uint32_t k, void* out, int mode);
+/* out f16 [rows, cols] = code * scale, rounded once to f16 as tb_gemm_q8 / tb_gemm_q4 round it in their operand path (bits 8:
+ * codes int8 with an f16 scale per 32; bits 4: the reference's nibbles, (n - 8) * scale with a scale per 64): tb_gemm_f16 on the
+ * result is tb_gemm_q8 on the codes.  The decoder's prefill copy is made with it.  No counterpart in the reference. */
+TB_API int tb_dequant_f16(tb_context* ctx, const void* w, const uint16_t* scales, uint32_t rows, uint32_t cols, uint32_t bits, uint16_t* out);
 
 /*
  * The reference's own decode formats, for callers that hold a model converted by the reference (quant.rs:47-130):
@@ -375,6 +379,11 @@ typedef struct tb_settings {
                               matrices as they are in weights.wpk, u8 [rows, cols/2] and f16 [rows, cols/64] (TB_WEIGHTS_Q4) */
     uint32_t host_table;   /* != 0: the per-layer table (embed_per_layer, the reference's host.wpk) stays in pinned, mapped host
                               memory and every step reads its token's row from there (decode.rs:477-483, 572-573); 0: in HBM */
+    uint32_t prefill_copy; /* the layers' qkv, o, gate/up and down matrices once more as f16 (2 bytes a weight beside the codes),
+                              which prefill's products on 256 tokens and more read by TMA instead of converting codes in their
+                              loop; the values are the codes' own (tb_dequant_f16), decode keeps reading the codes.
+                              0: automatic (when chunk >= 256 and a quarter of the device's memory stays free after it;
+                              TACHYON_B200_PREFILL_COPY=0 turns it off), 1: none, 2: always (TB_OUT_OF_MEMORY without room) */
 } tb_settings;
 enum { TB_WEIGHTS_Q8 = 8, TB_WEIGHTS_Q4 = 4 };
 

@@ -199,6 +199,10 @@ class Context:
         """tb_gemm_q8: out[m, n] = a[m, k] (f16) x w[n, k]^T on the tensor cores; mode 0 f32, 1 f16, 2 GeGLU."""
         check(self.lib.tb_gemm_q8(self.handle, w.ptr, s.ptr, a.ptr, m, n, k, out.ptr, mode))
 
+    def dequant_f16(self, w, s, rows, cols, bits, out) -> None:
+        """tb_dequant_f16: out f16 [rows, cols] = code * scale as the tensor-core products round it."""
+        check(self.lib.tb_dequant_f16(self.handle, w.ptr, s.ptr, rows, cols, bits, out.ptr))
+
     def gemm_f16(self, w, a, m, n, k, out, mode=0) -> None:
         """tb_gemm_f16: the same product on f16 weights [n, k]."""
         check(self.lib.tb_gemm_f16(self.handle, w.ptr, a.ptr, m, n, k, out.ptr, mode))
@@ -342,10 +346,10 @@ class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
     def __init__(self, ctx: Context, cfg: Config, context: int = 4096, chunk: int = 0, keep_logits: bool = False, fused: bool = False,
-                 weight_bits: int = 8, host_table: bool = False):
+                 weight_bits: int = 8, host_table: bool = False, prefill_copy: int = 0):
         self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
         self.settings = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=int(fused), weight_bits=weight_bits,
-                                 host_table=int(host_table))
+                                 host_table=int(host_table), prefill_copy=prefill_copy)
         h = C.c_void_p()
         check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
         self.handle = h.value

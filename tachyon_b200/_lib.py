@@ -42,7 +42,7 @@ class WpkInfo(C.Structure):
 
 
 class Settings(C.Structure):
-    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32), ("host_table", u32)]
+    _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32), ("host_table", u32), ("prefill_copy", u32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares.
@@ -89,6 +89,7 @@ SIGNATURES = {
     "tb_gemv_q8_argmax": (i32, [vp, vp, vp, vp, i32, vp, u32, u32, vp, vp, vp]),
     "tb_gemm_q8": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_gemm_f16": (i32, [vp, vp, vp, u32, u32, u32, vp, i32]),
+    "tb_dequant_f16": (i32, [vp, vp, vp, u32, u32, u32, vp]),
     "tb_gemm_q4": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_norm": (i32, [vp, vp, vp, vp, vp, u32, f32, f32, vp, vp]),
     "tb_embed_q8": (i32, [vp, vp, vp, vp, u32, f32, vp]),

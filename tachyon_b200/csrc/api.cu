@@ -618,6 +618,11 @@ int tb_gemm_f16(tb_context* ctx, const uint16_t* w, const uint16_t* a, uint32_t 
     return launch_gemm_q8(ctx, reinterpret_cast<const int8_t*>(w), nullptr, reinterpret_cast<const __half*>(a), m, n, k, out, mode, 16);
 }
 
+int tb_dequant_f16(tb_context* ctx, const void* w, const uint16_t* scales, uint32_t rows, uint32_t cols, uint32_t bits, uint16_t* out) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    return launch_dequant_f16(ctx, static_cast<const int8_t*>(w), reinterpret_cast<const __half*>(scales), rows, cols, bits, reinterpret_cast<__half*>(out));
+}
+
 int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
             float* x_out) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");

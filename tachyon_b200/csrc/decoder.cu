@@ -41,6 +41,7 @@ struct Mat {
     __half* s = nullptr;
     uint32_t rows = 0, cols = 0;
     uint32_t bits = 8;  // 8: int8 codes, an f16 scale per 32; 4: the reference's Q4 (quant.rs:47-82), a scale per 64
+    __half* f16 = nullptr;  // prefill's copy of the matrix as f16 [rows, cols] (settings.prefill_copy), or null
     size_t code_bytes() const { return (size_t)rows * cols * bits / 8; }
     size_t scale_bytes() const { return (size_t)rows * (cols / (bits == 4 ? 64 : 32)) * 2; }
 };
@@ -79,6 +80,11 @@ struct tb_decoder {
     float *pf_ple = nullptr, *pf_proj = nullptr, *pf_pli = nullptr;  // prefill: [chunk][layers * per_layer]: table rows, projections, inputs
     __half* pf_g2 = nullptr;                      // prefill: [chunk][per_layer]
     char* arena = nullptr;
+    // settings.prefill_copy: the layers' four large matrices once more as f16, which prefill's products on 256 tokens and more
+    // read by TMA instead of converting codes in their loop; decode keeps reading the codes.  Rewritten from the codes when
+    // a tensor was loaded since (copy_valid).
+    __half* copy = nullptr;
+    bool copy_valid = false;
     char* host_table = nullptr;  // settings.host_table: the per-layer table, codes then scales, in pinned mapped host memory
     size_t arena_bytes = 0;
     // step buffers
@@ -542,6 +548,52 @@ int ready(tb_decoder* d, uint32_t steps) {
     return OK;
 }
 
+// The prefill copy (settings.prefill_copy): room for every layer's qkv, o, gate/up and down matrices as f16.  Automatic
+// (0): taken when prefill runs in chunks of 256 tokens and more, the matrices have 8 or 4 bits, and the device keeps a
+// quarter of its memory free after it; 2 asks for it whatever is free; 1 leaves it out.
+constexpr uint32_t COPY_MIN_TOKENS = 256;
+
+int place_copy(tb_decoder* d) {
+    const uint32_t want = d->settings.prefill_copy;
+    if (want > 2) return fail(OUT_OF_RANGE, "tb_settings.prefill_copy is 0 (automatic), 1 (none) or 2 (always)");
+    const char* env = getenv("TACHYON_B200_PREFILL_COPY");
+    if (want == 1 || (want == 0 && env != nullptr && env[0] == '0') || d->settings.chunk == 0 || d->cfg.hidden % 64 != 0 || d->cfg.ffn % 64 != 0) return OK;
+    if (want == 0 && d->settings.chunk < COPY_MIN_TOKENS) return OK;
+    size_t halves = 0;
+    for (Layer& L : d->layers)
+        for (Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) halves += ((size_t)m->rows * m->cols + 127) / 128 * 128;
+    size_t free_bytes = 0, total = 0;
+    TB_CUDA(cudaMemGetInfo(&free_bytes, &total));
+    if (want == 0 && (free_bytes < halves * 2 || free_bytes - halves * 2 < total / 4)) return OK;
+    const cudaError_t e = cudaMalloc(&d->copy, halves * 2);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (want == 0) return d->copy = nullptr, OK;
+        return fail(OUT_OF_MEMORY, "tb_decoder_open: no room for the prefill copy of the weights (" + std::to_string(halves * 2) + " bytes)");
+    }
+    __half* at = d->copy;
+    for (Layer& L : d->layers)
+        for (Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) m->f16 = at, at += ((size_t)m->rows * m->cols + 127) / 128 * 128;
+    d->copy_valid = false;
+    return OK;
+}
+
+// Writes the copy from the codes as they are now.
+int refresh_copy(tb_decoder* d) {
+    if (!d->copy || d->copy_valid) return OK;
+    for (Layer& L : d->layers)
+        for (Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) TB_TRY(launch_dequant_f16(d->ctx, m->w, m->s, m->rows, m->cols, m->bits, m->f16));
+    d->copy_valid = true;
+    return OK;
+}
+
+// One of prefill's four large products: on the f16 copy from 256 tokens on, on the codes below that.
+int prefill_product(tb_decoder* d, const Mat& m, const __half* x, uint32_t tokens, void* out, int mode) {
+    if (m.f16 != nullptr && d->copy_valid && tokens >= COPY_MIN_TOKENS)
+        return launch_gemm_q8(d->ctx, reinterpret_cast<const int8_t*>(m.f16), nullptr, x, tokens, m.rows, m.cols, out, mode, 16);
+    return launch_gemm_q8(d->ctx, m.w, m.s, x, tokens, m.rows, m.cols, out, mode, m.bits);
+}
+
 }  // namespace
 
 extern "C" {
@@ -580,6 +632,13 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
         return s;
     }
     layout(d, d->arena);
+    {
+        const int st = place_copy(d);
+        if (st != OK) {
+            tb_decoder_close(d);
+            return st;
+        }
+    }
     memset(d->words, 0, 64);
     for (int k = 0; k < 2; k++) {
         const std::vector<float> f = rope_freq(k ? cfg->theta_global : cfg->theta_sliding, dim_of(*cfg, k), k ? cfg->fraction_global : 1.0f);
@@ -608,6 +667,7 @@ void tb_decoder_close(tb_decoder* d) {
     for (int g = 0; g < 2; g++)
         if (d->phase_dev[g]) cudaFree(d->phase_dev[g]);
     if (d->arena) cudaFree(d->arena);
+    if (d->copy) cudaFree(d->copy);
     if (d->words) cudaFreeHost(d->words);
     if (d->host_table) cudaFreeHost(d->host_table);
     delete d;
@@ -617,6 +677,7 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
     if (!d || !name || !data) return fail(OUT_OF_RANGE, "tb_decoder_load: null argument");
     Named t;
     if (!find_tensor(d, name, t)) return fail(NO_MODEL, std::string("tb_decoder_load: no tensor named ") + name);
+    d->copy_valid = false;
     if (bytes != t.bytes) return fail(FORMAT, std::string("tb_decoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
     cudaStream_t s = d->ctx->stream;
     if (t.kind == 3) {
@@ -643,6 +704,7 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
 
 int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
     if (!d) return fail(OUT_OF_RANGE, "null decoder");
+    d->copy_valid = false;
     const tb_config& c = d->cfg;
     tb_context* ctx = d->ctx;
     const uint32_t bits = d->embed.bits;
@@ -756,6 +818,7 @@ int tb_decoder_build(tb_decoder* d) {
         cudaGraphDestroy(graph);
         if (ei != cudaSuccess) return cuda_fail(ei, "cudaGraphInstantiate");
     }
+    TB_TRY(refresh_copy(d));
     d->built = true;
     d->running = false;
     // The uncaptured pass advanced the position and wrote a cache slot; start clean.
@@ -869,16 +932,16 @@ static int prefill_chunk(tb_decoder* d, const uint32_t* tokens, uint32_t n, uint
             const Layer& P = d->layers[i - 1];
             TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, pl ? P.post_pl : P.post_ffn, L.input_ln, n, H, c.eps, P.layer_scalar, d->pf_x));
         }
-        TB_TRY(launch_gemm_q8(ctx, L.qkv.w, L.qkv.s, d->pf_x, n, L.qkv.rows, H, d->pf_qkv, 0, L.qkv.bits));
+        TB_TRY(prefill_product(d, L.qkv, d->pf_x, n, d->pf_qkv, 0));
         // A shared layer has query rows only: nothing to append to the cache it reads.
         TB_TRY(launch_prefill_qkv(ctx, d->pf_qkv, L.q_norm, L.k_norm, d->freq[L.global ? 1 : 0], d->pf_q, L.kc, L.vc, n, pos0, L.cap, c.heads,
                                   L.source < 0 ? L.kvh : 0, c.eps, c.attn_scale, L.dim));
         if (i + 1 == c.layers) break;
         TB_TRY(launch_prefill_flash(ctx, d->pf_q, L.kc, L.vc, d->pf_att, n, pos0, L.cap, L.window, c.heads, L.kvh, L.dim));
-        TB_TRY(launch_gemm_q8(ctx, L.o.w, L.o.s, d->pf_att, n, H, L.nq, d->pf_y, 0, L.o.bits));
+        TB_TRY(prefill_product(d, L.o, d->pf_att, n, d->pf_y, 0));
         TB_TRY(launch_prefill_norm(ctx, d->pf_h, d->pf_y, L.post_attn, L.pre_ffn, n, H, c.eps, 1.0f, d->pf_x));
-        TB_TRY(launch_gemm_q8(ctx, L.gate_up.w, L.gate_up.s, d->pf_x, n, 2 * c.ffn, H, d->pf_g, 2, L.gate_up.bits));
-        TB_TRY(launch_gemm_q8(ctx, L.down.w, L.down.s, d->pf_g, n, H, c.ffn, d->pf_y, 0, L.down.bits));
+        TB_TRY(prefill_product(d, L.gate_up, d->pf_x, n, d->pf_g, 2));
+        TB_TRY(prefill_product(d, L.down, d->pf_g, n, d->pf_y, 0));
         if (pl) {
             // decode.rs:654-658 for a chunk: the stream plus the MLP's normed output, unscaled, through the gate; GELU times
             // each token's input of this layer; projected back.  The next layer's norm step adds it.
@@ -915,6 +978,7 @@ int tb_decoder_prefill(tb_decoder* d, const uint32_t* tokens, uint32_t n) {
         TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
         return OK;
     }
+    if (n >= COPY_MIN_TOKENS) TB_TRY(refresh_copy(d));  // a tensor loaded after tb_decoder_build
     for (uint32_t at = 0; at < n; at += d->settings.chunk) {
         const uint32_t m = n - at < d->settings.chunk ? n - at : d->settings.chunk;
         TB_TRY(prefill_chunk(d, tokens + at, m, d->pos));

@@ -357,6 +357,7 @@ struct EMat {
     int8_t* w = nullptr;
     __half* s = nullptr;
     __half* f16 = nullptr;  // the matrix as f16 [rows, cols] instead, in an allocation of its own (a model too narrow for 8 bits to pay)
+    __half* copy = nullptr; // the codes times their scales as f16 [rows, cols], in the arena: what the products read (tb_encoder.use_copy)
     uint32_t rows = 0, cols = 0;
     size_t code_bytes() const { return (size_t)rows * cols; }
     size_t scale_bytes() const { return (size_t)rows * (cols / 32) * 2; }
@@ -408,6 +409,10 @@ struct tb_encoder {
     size_t input_words = 0;
     uint32_t *ids = nullptr, *pos = nullptr, *tiles = nullptr, *starts = nullptr, *lens = nullptr;
     bool use_graphs = true, warmed = false;
+    // The products read an f16 copy of the 8-bit matrices by TMA instead of converting codes in their loop (2 bytes a weight
+    // more; the values are the codes' own, launch_dequant_f16).  Written before a batch when a tensor was loaded since.
+    // TACHYON_B200_ENCODER_COPY=0 leaves it out.
+    bool use_copy = true, copy_valid = false;
     uint32_t tile_q = QT;  // queries a tile of the list holds: 64, or 128 where attention runs on tcgen05 (decided when the encoder is opened)
     std::vector<EGraph> graphs;
 };
@@ -426,6 +431,7 @@ size_t enc_layout(tb_encoder* e, char* base) {
         m.rows = rows, m.cols = cols;
         m.w = reinterpret_cast<int8_t*>(take(m.code_bytes()));
         m.s = reinterpret_cast<__half*>(take(m.scale_bytes()));
+        m.copy = e->use_copy ? reinterpret_cast<__half*>(take(2 * m.code_bytes())) : nullptr;
     };
     const uint32_t h = c.hidden, up_rows = c.gated ? 2 * c.inter : c.inter, T = e->cap_padded, S = e->cap_seqs;
     e->embed = reinterpret_cast<__half*>(take((size_t)c.vocab * h * 2));
@@ -511,7 +517,8 @@ bool enc_find(tb_encoder* e, const std::string& name, ENamed& out) {
 
 // One matrix product of the forward pass: the matrix as f16 when it was loaded so, else its codes and scales.
 int enc_product(tb_encoder* e, const EMat& m, const __half* a, uint32_t tokens, void* out, int mode) {
-    if (m.f16 != nullptr) return launch_gemm_q8(e->ctx, reinterpret_cast<const int8_t*>(m.f16), nullptr, a, tokens, m.rows, m.cols, out, mode, 16);
+    const __half* f16 = m.f16 != nullptr ? m.f16 : (e->copy_valid ? m.copy : nullptr);
+    if (f16 != nullptr) return launch_gemm_q8(e->ctx, reinterpret_cast<const int8_t*>(f16), nullptr, a, tokens, m.rows, m.cols, out, mode, 16);
     return launch_gemm_q8(e->ctx, m.w, m.s, a, tokens, m.rows, m.cols, out, mode);
 }
 
@@ -548,6 +555,12 @@ int enc_layers(tb_encoder* e, uint32_t n, uint32_t slots, uint32_t sequences) {
 // batch's padded shape, recorded the first time the shape is seen.
 int enc_batch(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host) {
     cudaStream_t s = e->ctx->stream;
+    if (e->use_copy && !e->copy_valid) {
+        for (ELayer& L : e->layers)
+            for (EMat* m : {&L.qkv, &L.o, &L.up, &L.down})
+                if (m->f16 == nullptr) TB_TRY(launch_dequant_f16(e->ctx, m->w, m->s, m->rows, m->cols, 8, m->copy));
+        e->copy_valid = true;
+    }
     uint32_t *hi, *hp, *ht, *hs, *hl;
     enc_inputs(e, e->stage, hi, hp, ht, hs, hl);
     uint32_t T = 0, tiles = 0;
@@ -615,6 +628,8 @@ int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t toke
     e->layers.resize(cfg->layers);
     const char* env = getenv("TACHYON_B200_ENCODER_GRAPHS");
     e->use_graphs = !(env && env[0] == '0');
+    env = getenv("TACHYON_B200_ENCODER_COPY");
+    e->use_copy = !(env && env[0] == '0');
     e->tile_q = (ctx->flash_tc && enc_attend_tc_supports(cfg->hidden, cfg->hidden / cfg->heads)) ? 128u : (uint32_t)QT;
     e->arena_bytes = enc_layout(e, nullptr);
     cudaError_t err = cudaSetDevice(ctx->gpu);
@@ -664,6 +679,7 @@ int tb_encoder_load(tb_encoder* e, const char* name, const void* data, size_t by
     if (!e || !name || !data) return fail(OUT_OF_RANGE, "tb_encoder_load: null argument");
     ENamed t;
     if (!enc_find(e, name, t)) return fail(NO_MODEL, std::string("tb_encoder_load: no tensor named ") + name);
+    e->copy_valid = false;
     cudaStream_t s = e->ctx->stream;
     TB_CUDA(cudaSetDevice(e->ctx->gpu));
     if (t.kind == 3) {  // a matrix under its plain name: Q8E codes or f16, told apart by the size
@@ -716,6 +732,7 @@ int tb_encoder_load(tb_encoder* e, const char* name, const void* data, size_t by
 
 int tb_encoder_fill_random(tb_encoder* e, uint64_t seed) {
     if (!e) return fail(OUT_OF_RANGE, "null encoder");
+    e->copy_valid = false;
     const tb_encoder_config& c = e->cfg;
     tb_context* ctx = e->ctx;
     // Streams: 0 embed (f16 N(0,1)*0.02... as values), 1 embed_norm, 2 final_norm; layer l: 16*(l+1) + {0 qkv.w, 1 qkv.s, 2 o.w, 3 o.s,

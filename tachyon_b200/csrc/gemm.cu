@@ -17,6 +17,8 @@
 // tensor rate is the same, and the activations that reach this kernel are normalised.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -114,10 +116,11 @@ __device__ __forceinline__ float silu(float v) { return v / (1.0f + exp2f(-1.442
 // MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
 // dequantisation is shared by twice the tensor-core work.
 // WB: bits per weight, 8 (codes, an f16 scale per 32), 4 (the reference's Q4, a scale per 64 = one per row and K tile) or 16
-// (f16 weights as they are, the reference's gemm_f16, ptx/encoder.rs:498-525: the sixteen warps then only move the tile into
-// the swizzled layout).
+// (f16 weights as they are, the reference's gemm_f16, ptx/encoder.rs:498-525: the weight tile then comes by TMA through
+// w_map like the activations', and the sixteen warps only run the epilogue).
 template <int MT, int WB = 8>
-__global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const GemmArgs g, uint32_t* status) {
+__global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                                                             const GemmArgs g, uint32_t* status) {
     constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
     extern __shared__ uint8_t raw_unaligned[];
     uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
     const uint32_t m0 = blockIdx.x * (MT * BM), n0 = blockIdx.y * BN, nk = g.K / BK;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], DW + 1), mbar_init(&empty[i], 1);
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], WB == 16 ? 1 : DW + 1), mbar_init(&empty[i], 1);
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -156,8 +159,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                     ok = false;
                     break;
                 }
-                mbar_expect_tx(&full[s], AS);
+                mbar_expect_tx(&full[s], WB == 16 ? AS + B_BYTES : AS);
                 tma_load_2d(As + s * AS, &a_map, (int)(kt * BK), (int)m0, &full[s]);
+                if constexpr (WB == 16) tma_load_2d(Bs + s * B_BYTES, &w_map, (int)(kt * BK), (int)n0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -235,8 +239,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
                 }
             }
         };
-        if (nk > 0) fetch(0);
-        for (uint32_t kt = 0; kt < nk; kt++) {
+        if (WB != 16 && nk > 0) fetch(0);
+        for (uint32_t kt = 0; WB != 16 && kt < nk; kt++) {
             const uint32_t s = kt % STAGES;
             uint32_t v[PIECES][8];  // per piece 16 halves
 #pragma unroll
@@ -359,6 +363,31 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(MT * BN)) : "memory");
 }
 
+// Codes to f16 weights once, with the arithmetic of the product's own conversion (dequant4, dequant8_q4), so that a product on
+// the copy has the operands the converting kernel would have made: a thread a piece of sixteen weights.  The scales lie
+// [rows][cols / group] behind one another, so a piece's scale is at piece / (group / 16).
+template <int WB>
+__global__ void __launch_bounds__(256) dequant_f16_kernel(const uint8_t* __restrict__ w, const __half* __restrict__ s, size_t pieces, __half* __restrict__ out) {
+    const size_t stride = (size_t)gridDim.x * 256;
+    for (size_t p = (size_t)blockIdx.x * 256 + threadIdx.x; p < pieces; p += stride) {
+        uint32_t v[8];
+        if constexpr (WB == 8) {
+            const uint4 c = __ldcs(reinterpret_cast<const uint4*>(w) + p);
+            const __half2 s2 = __half2half2(__ldg(s + p / 2));
+            dequant4(c.x, s2, v[0], v[1]), dequant4(c.y, s2, v[2], v[3]), dequant4(c.z, s2, v[4], v[5]), dequant4(c.w, s2, v[6], v[7]);
+        } else {
+            const uint2 c = __ldcs(reinterpret_cast<const uint2*>(w) + p);
+            const __half2 s2 = __half2half2(__ldg(s + p / 4));
+            uint32_t a[4], b[4];
+            dequant8_q4(c.x, s2, a), dequant8_q4(c.y, s2, b);
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = a[e], v[4 + e] = b[e];
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out) + 2 * p;
+        dst[0] = make_uint4(v[0], v[1], v[2], v[3]), dst[1] = make_uint4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -373,6 +402,19 @@ EncodeTiled encode_tiled() {
 }
 
 }  // namespace
+
+int launch_dequant_f16(tb_context* ctx, const int8_t* w, const __half* s, uint32_t rows, uint32_t cols, uint32_t wbits, __half* out) {
+    if (!w || !s || !out || rows == 0 || cols == 0) return fail(OUT_OF_RANGE, "dequantise: null or empty argument");
+    if (wbits != 8 && wbits != 4) return fail(OUT_OF_RANGE, "dequantise: weights are 8 or 4 bits");
+    if (cols % (wbits == 4 ? 64 : 32) != 0) return fail(OUT_OF_RANGE, "dequantise: ragged scale groups");
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) return fail(OUT_OF_RANGE, "dequantise: buffers must be 16-byte aligned");
+    const size_t pieces = (size_t)rows * cols / 16;
+    const unsigned blocks = (unsigned)std::min<size_t>((pieces + 1023) / 1024, (size_t)ctx->sms * 16);
+    if (wbits == 8) dequant_f16_kernel<8><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint8_t*>(w), s, pieces, out);
+    else dequant_f16_kernel<4><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint8_t*>(w), s, pieces, out);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
 
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
                    uint32_t wbits, const float* mul, uint32_t mul_stride, const float* bias) {
@@ -393,7 +435,7 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(OUT_OF_RANGE, "gemm: buffers must be 16-byte aligned");
     if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15)) return fail(OUT_OF_RANGE, "gemm: the bias must be 16-byte aligned");
-    if (wbits != 16 && mode != 7 && mode != 8 && bias == nullptr) {  // f16 weights, a bias and the two rarer outputs: this file's kernel only
+    if (mode != 7 && mode != 8 && bias == nullptr) {  // a bias and the two rarer outputs: this file's kernel only
         // Schedules: this file's one tile per block; gemm2.cu's persistent blocks, whose epilogue overlaps the next tile's
         // products and whose MMAs read less shared memory per FLOP; gemm3.cu's pairs of SMs.  Measured on the benchmark's
         // shapes the persistent one wins where the epilogue stores f32 (plain or added to the output: 1.2 to 1.7 times
@@ -402,9 +444,13 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         // persistent tile of 256 would be half empty.
         const int which = ctx->gemm_schedule;
         // 3 and 4: the pair schedule of gemm3.cu with tiles of 256 and 128 weight rows.
-        if ((which == 3 || which == 4) && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
+        if ((which == 3 || which == 4) && wbits != 16 && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
+        // With f16 weights (no conversion: sixteen more warps drain accumulators) the persistent one wins everywhere but on
+        // the gated outputs over a long K, where this file's larger tile reads less per FLOP (measured at 2048 tokens:
+        // 32768 x 2048 gated 206 against 220 us; 3072 x 2048 33 against 42; at 16384 tokens, 3072 x 768 with a GELU 109 against 121).
         const bool stores_only = (mode == 0 || mode == 3) && M > 128;
-        if ((which == 2 || (which == 0 && stores_only)) && gemm_persistent_supports(N, K, wbits)) return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits);
+        const bool prefer = wbits == 16 ? (M > 128 && !((mode == 2 || mode == 4) && K >= 1536)) : stores_only;
+        if ((which == 2 || (which == 0 && prefer)) && gemm_persistent_supports(N, K, wbits)) return launch_gemm_persistent(ctx, w, s, a, M, N, K, out, mode, wbits);
     }
     EncodeTiled enc = encode_tiled();
     if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
@@ -427,14 +473,22 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
+    CUtensorMap wmap = map;  // f16 weights: [N, K] in tiles of 256 rows x 64 halves; unused otherwise
+    if (wbits == 16) {
+        const cuuint64_t wdims[2] = {K, N};
+        const cuuint32_t wbox[2] = {BK, BN};
+        const CUresult rw = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<int8_t*>(w), wdims, strides, wbox, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rw != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled failed for the weights (" + std::to_string((int)rw) + ")");
+    }
     GemmArgs g{w, s, out, M, N, K, mode, bias};
     const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
-    if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
-    else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
-    else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
-    else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
-    else if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, g, ctx->status);
-    else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, g, ctx->status);
+    if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
     TB_CUDA(cudaGetLastError());
     return OK;
 }

@@ -27,6 +27,8 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64, MT = 2;   // MMA M128 N128; two token sub-tiles share a weight tile
 constexpr int ST = 3;                                // stages of f16 operands
+constexpr int ST16 = 4;                              // the same with f16 weights, which need no ring of codes
+constexpr int stages_of(int wb) { return wb == 16 ? ST16 : ST; }
 constexpr int CS = 8;                                // stages of codes
 constexpr int DW = 16, EW = 8;                       // dequantising and epilogue warps (a multiple of four: TMEM lane quarters)
 constexpr int FIRST_DW = 3, FIRST_EW = FIRST_DW + DW;
@@ -103,7 +105,7 @@ struct Args {
 };
 
 struct Bars {
-    uint64_t full[ST], empty[ST], c_full[CS], c_empty[CS], acc_full[2], acc_empty[2];
+    uint64_t full[ST16], empty[ST16], c_full[CS], c_empty[CS], acc_full[2], acc_empty[2];
     uint32_t tmem;
 };
 
@@ -112,15 +114,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                                                                      uint32_t* status) {
     extern __shared__ uint8_t raw_unaligned[];
     uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
-    uint8_t *As = raw + OFF_A, *Bs = raw + OFF_B, *Cs = raw + OFF_C;
+    // WB == 16: the weights are f16 already; their tiles come by TMA (warp 0) into the operand stages, of which there are four
+    // in place of three and the ring of codes; warp 1 and the dequantising warps have nothing to do.
+    constexpr int ST = stages_of(WB);
+    static_assert(stages_of(16) * (A_BYTES + B_BYTES) <= OFF_BAR, "the f16 stages must end before the barriers");
+    uint8_t *As = raw + OFF_A, *Bs = raw + OFF_A + ST * A_BYTES, *Cs = raw + OFF_C;
     Bars& bar = *reinterpret_cast<Bars*>(raw + OFF_BAR);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nk = g.K / BK, tiles_m = (g.M + MT * BM - 1) / (MT * BM), tiles_n = (g.N + BN - 1) / BN, tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], DW + 1), mbar_init(&bar.empty[i], 1);
+        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], WB == 16 ? 1 : DW + 1), mbar_init(&bar.empty[i], 1);
         for (int i = 0; i < CS; i++) mbar_init(&bar.c_full[i], 1), mbar_init(&bar.c_empty[i], DW);
-        for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], EW);
+        for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], WB == 16 ? DW + EW : EW);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-                const uint32_t m0 = (t % tiles_m) * (MT * BM);
+                const uint32_t m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
                 for (uint32_t kt = 0; kt < nk; kt++, it++) {
                     const uint32_t s = it % ST;
                     if (it >= ST && !mbar_wait(&bar.empty[s], ((it / ST) - 1) & 1)) {
@@ -146,13 +152,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         t = tiles;
                         break;
                     }
-                    mbar_expect_tx(&bar.full[s], A_BYTES);
+                    mbar_expect_tx(&bar.full[s], WB == 16 ? A_BYTES + B_BYTES : A_BYTES);
                     tma_load_2d(As + s * A_BYTES, &a_map, (int)(kt * BK), (int)m0, &bar.full[s]);
+                    if constexpr (WB == 16) tma_load_2d(Bs + s * B_BYTES, &w_map, (int)(kt * BK), (int)n0, &bar.full[s]);
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (WB != 16 && lane == 0) {
             uint32_t ic = 0;
             for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
                 const uint32_t n0 = (t / tiles_m) * BN;
@@ -195,7 +202,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                 mma_commit(&bar.acc_full[b]);  // arrives when the tile's products have finished
             }
         }
-    } else if (warp < FIRST_EW) {
+    } else if (WB != 16 && warp < FIRST_EW) {
         // Dequantisation: thread j takes the 16 codes of piece (row j / 4, quarter j % 4) of every stage.
         const int j = threadIdx.x - 32 * FIRST_DW, row = j >> 2, qtr = j & 3;
         constexpr uint32_t GS = WB == 4 ? 8 : 4;               // k tiles one 16-byte load of scales covers
@@ -260,7 +267,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
         // Epilogue: the accumulator's lanes are weight rows, its columns tokens.  A warp reads the lanes of its quarter
         // q = warp % 4, 32 tokens at a time (the EW / 4 warps of a quarter take alternate blocks of tokens); for each token
         // its 32 lanes then hold 32 consecutive outputs of that token's row, which go out as one 128-byte (f32) store.
-        const uint32_t q = warp & 3, part = (warp - FIRST_EW) >> 2;
+        // With f16 weights the sixteen warps that would convert codes drain accumulators too: six warps a quarter.
+        constexpr int FIRST = WB == 16 ? FIRST_DW : FIRST_EW, PARTS = (WB == 16 ? DW + EW : EW) / 4;
+        const uint32_t q = warp & 3, part = (warp - FIRST) >> 2;
         uint32_t ti = 0;
         for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ti++) {
             const uint32_t b = ti & 1, m0 = (t % tiles_m) * (MT * BM), n = (t / tiles_m) * BN + 32 * q + lane;
@@ -271,7 +280,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool row_ok = n < g.N;  // the same for the whole warp: N is a multiple of 32
 #pragma unroll 1
-            for (int cb = part; cb < MT * BM / 32; cb += EW / 4) {
+            for (int cb = part; cb < MT * BM / 32; cb += PARTS) {
                 uint32_t r[32];
                 tmem_load32(tmem + ((32 * q) << 16) + b * (MT * BM) + cb * 32, r);
                 if (!row_ok) continue;
@@ -356,7 +365,7 @@ EncodeTiled encode_tiled() {
 }  // namespace
 
 // The shapes this schedule takes: everything gemm.cu's kernel takes with whole 16-byte rows of codes.
-bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K % BK == 0 && (K * wbits / 8) % 16 == 0 && N > 0; }
+bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K % BK == 0 && (K * wbits / 8) % 16 == 0 && N > 0; }  // wbits 16: f16 weights
 
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
                            uint32_t wbits, const float* mul, uint32_t mul_stride) {
@@ -372,24 +381,28 @@ int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, co
         if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (activations) failed (" + std::to_string((int)r) + ")");
     }
     {
-        const cuuint64_t row = (cuuint64_t)K * wbits / 8;  // bytes of codes per weight row
-        const cuuint64_t dims[2] = {row, N};
+        const cuuint64_t row = (cuuint64_t)K * wbits / 8;  // bytes of codes (or of f16 weights) per weight row
+        const cuuint64_t dims[2] = {wbits == 16 ? (cuuint64_t)K : row, N};
         const cuuint64_t strides[1] = {row};
-        const cuuint32_t box[2] = {(cuuint32_t)(BK * wbits / 8), BN}, elem[2] = {1, 1};
-        const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint32_t box[2] = {(cuuint32_t)(wbits == 16 ? BK : BK * wbits / 8), BN}, elem[2] = {1, 1};
+        // f16 weights go straight into the operand stage: halves, 128-byte swizzle, like the activations
+        const CUresult r = enc(&wmap, wbits == 16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(w), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, wbits == 16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (codes) failed (" + std::to_string((int)r) + ")");
     }
     static bool configured[16] = {};
     if (!configured[ctx->gpu & 15]) {
         TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured[ctx->gpu & 15] = true;
     }
     const uint32_t tiles = ((M + MT * BM - 1) / (MT * BM)) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
     const Args g{s, out, M, N, K, mode, mul, mul_stride};
-    if (wbits == 4) gemm_persistent_kernel<4><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
+    if (wbits == 16) gemm_persistent_kernel<16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
+    else if (wbits == 4) gemm_persistent_kernel<4><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
     else gemm_persistent_kernel<8><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
     TB_CUDA(cudaGetLastError());
     return OK;

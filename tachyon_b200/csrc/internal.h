@@ -218,6 +218,10 @@ int launch_step(tb_context* ctx, const StepPhase* phases, uint32_t n, uint32_t* 
 int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
                    uint32_t wbits = 8, const float* mul = nullptr, uint32_t mul_stride = 0, const float* bias = nullptr);
 
+// out f16 [rows, cols] = code * scale exactly as the product's own conversion rounds it (gemm.cu); launch_gemm_q8 with wbits 16
+// on the copy gives the product on the codes, with the weight tiles fetched by TMA instead of converted in the loop.
+int launch_dequant_f16(tb_context* ctx, const int8_t* w, const __half* s, uint32_t rows, uint32_t cols, uint32_t wbits, __half* out);
+
 // ---- prefill kernels around the GEMMs (prefill.cu) ---------------------------------------------------------------------
 int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, const uint32_t* tokens, uint32_t n, uint32_t cols, float scale, float* out,
                          uint32_t wbits = 8);

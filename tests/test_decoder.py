@@ -138,6 +138,28 @@ def test_prefill_does_not_depend_on_the_chunking(ctx, models):
     assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1]), "chunks of 8 and of 32 must give the same bits"
 
 
+@pytest.mark.parametrize("bits", [8, 4])
+def test_prefill_on_the_f16_copy_of_the_weights_gives_the_same_bits(ctx, bits):
+    """tb_settings.prefill_copy: products on 256 tokens and more read an f16 copy of the matrices by TMA; the copy holds the
+    values the converting products build, so nothing changes but the speed.  A tensor loaded after the build reaches the copy."""
+    cfg = small_config(layers=3, ffn=2048, vocab=2048, window=128)
+    prompt = [(i * 104729 + 7) % cfg.vocab for i in range(700)]
+    outs = []
+    for copy in (1, 2):
+        d = tb.Decoder(ctx, cfg, context=1024, chunk=512, keep_logits=True, weight_bits=bits, prefill_copy=copy)
+        d.fill_random(SEED)
+        d.build()
+        if bits == 8:  # after the build: the copy has to follow
+            d.load("1.input_layernorm", np.full(cfg.hidden, 1.25, np.float32))
+            w = np.random.default_rng(3).integers(-127, 128, size=(cfg.hidden, cfg.ffn), dtype=np.int8)
+            d.load("1.down.w", w)
+        d.prefill(prompt[:-1])
+        tok = d.step(prompt[-1])
+        outs.append((tok, d.logits()))
+        d.close()
+    assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1])
+
+
 def test_overlap_off_gives_the_same_bits(ctx, models):
     """Programmatic dependent launch only changes when kernels start, never what they compute."""
     cfg, dec, ref = models

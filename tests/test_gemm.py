@@ -156,3 +156,40 @@ def test_gemm_q8_relu_and_gated_silu(ctx):
     got = f16_to_f32(o.download(np.uint16, m * n // 2)).reshape(m, n // 2)
     tol = 2.0**-9 * np.abs(ref) + 1e-3 * (bound[:, 0::2] * (1 + np.abs(odd)) + bound[:, 1::2] * (1 + np.abs(even))) + 1e-5
     assert np.all(np.abs(got - ref) <= tol)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("m,n,k", [(300, 2304, 768), (512, 768, 3072), (37, 96, 128)])
+def test_dequantised_copy_holds_the_products_own_operands(ctx, bits, m, n, k):
+    """tb_dequant_f16 writes code * scale rounded once to f16, the value the Q8 / Q4 products build in their operand path, so
+    tb_gemm_f16 on the copy gives tb_gemm_q8 / tb_gemm_q4's bits (the decoder's prefill copy leans on exactly that)."""
+    rng = np.random.default_rng(bits + m + n + k)
+    if bits == 8:
+        w, s = q8_weights(n, k, 21 + n + k)
+        exact = w.astype(np.float32) * np.repeat(f16_to_f32(s), 32, axis=1)
+        wd, sd = ctx.upload(w), ctx.upload(s)
+    else:
+        packed, s = oracle.q4((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+        packed, s = np.asarray(packed, np.uint8).reshape(n, k // 2), np.asarray(s, np.uint16).reshape(n, k // 64)
+        nib = np.empty((n, k // 8, 8), np.float32)  # a word of four bytes: low nibbles are weights 0..3, high nibbles 4..7
+        words = packed.reshape(n, k // 8, 4)
+        nib[:, :, :4], nib[:, :, 4:] = words & 15, words >> 4
+        exact = (nib.reshape(n, k) - 8.0) * np.repeat(f16_to_f32(s), 64, axis=1)
+        wd, sd = ctx.upload(packed), ctx.upload(s)
+    copy = ctx.zeros(n * k * 2)
+    ctx.dequant_f16(wd, sd, n, k, bits, copy)
+    got = copy.download(np.uint16, n * k).reshape(n, k)
+    assert np.array_equal(got, f16(exact)), "code * scale, rounded once"
+    a = ctx.upload(f16(rng.standard_normal((m, k)).astype(np.float32)))
+    o1, o2 = ctx.zeros(m * n * 4), ctx.zeros(m * n * 4)
+    tb.check(ctx.lib.tb_context_set_gemm_schedule(ctx.handle, 1))
+    try:
+        if bits == 8:
+            ctx.gemm_q8(wd, sd, a, m, n, k, o1, 0)
+        else:
+            tb.check(ctx.lib.tb_gemm_q4(ctx.handle, wd.ptr, sd.ptr, a.ptr, m, n, k, o1.ptr, 0))
+    finally:
+        tb.check(ctx.lib.tb_context_set_gemm_schedule(ctx.handle, 0))
+    ctx.gemm_f16(copy, a, m, n, k, o2, 0)
+    assert np.array_equal(o1.download(np.uint32, m * n), o2.download(np.uint32, m * n)), "the same operands, the same sums"
+    assert ctx.status() == 0
