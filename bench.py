@@ -481,32 +481,41 @@ def measured_peak_tflops():
 
 
 def bench_gemm(args, ranks: Ranks):
-    """configs[3]'s GEMM shapes alone: M tokens x K -> N with Q8 weights dequantised in the operand path (tcgen05)."""
+    """configs[3]'s GEMM shapes alone: M tokens x K -> N on the tensor cores (tcgen05).  --weights q8: the codes are converted in
+    the operand path (tb_gemm_q8); --weights f16: the product reads the codes' f16 copy by TMA (tb_dequant_f16 once, then
+    tb_gemm_f16: what the decoder's prefill and the encoder run).  --mode is the output mode (0 f32, 1 f16, 2 gated GELU ...)."""
     import tachyon_b200 as tb
 
     ctx = tb.Context(ranks.local)
-    m, n, k = args.tokens, args.rows, args.cols
+    m, n, k, mode = args.tokens, args.rows, args.cols, args.mode
     lib = ctx.lib
     w, s = ctx.alloc(n * k), ctx.alloc(n * (k // 32) * 2)
     tb.check(lib.tb_fill_codes(ctx.handle, 3, 1, w.ptr, n * k))
     tb.check(lib.tb_fill_scales(ctx.handle, 3, 2, s.ptr, n * (k // 32), 0.02 / 127))
     a = ctx.upload(np.random.default_rng(0).standard_normal((m, k)).astype(np.float16))
     out = ctx.zeros(m * n * 4)
+    if args.weights == "f16":
+        copy = ctx.alloc(n * k * 2)
+        ctx.dequant_f16(w, s, n, k, 8, copy)
+        run = lambda: ctx.gemm_f16(copy, a, m, n, k, out, mode)
+    else:
+        run = lambda: ctx.gemm_q8(w, s, a, m, n, k, out, mode)
     for _ in range(args.warmup):
-        ctx.gemm_q8(w, s, a, m, n, k, out, 0)
+        run()
     ctx.sync()
     e0, e1 = ctx.event(), ctx.event()
     e0.record()
     for _ in range(args.steps):
-        ctx.gemm_q8(w, s, a, m, n, k, out, 0)
+        run()
     e1.record()
     e1.sync()
     us = e0.elapsed_ms(e1) * 1e3 / args.steps
     tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
     burst, sustained, how = measured_peak_tflops()
-    return {"metric": "gemm_q8_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
-            "higher_is_better": True, "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05)", "data": "synthetic", "impl": "ours",
-            "config": {"workload": f"configs[3] GEMM: M={m} K={k} N={n}"}, "gpu_launches": args.steps,
+    kind = "f16 copy of the int8 weights read by TMA" if args.weights == "f16" else "int8 weights -> f16 in the operand path"
+    return {"metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
+            "higher_is_better": True, "dtype": kind + ", f16 activations, f32 accumulate (tcgen05)", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3] GEMM: M={m} K={k} N={n}, output mode {mode}, weights {args.weights}"}, "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "peak_source": how, "traffic": None,
                          "flops_per_launch": 2.0 * m * n * k, "us_per_launch": us}}
 
@@ -682,6 +691,7 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=64)
+    ap.add_argument("--mode", type=int, default=0, help="gemm workload: the product's output mode (TB_GEMM_*)")
     ap.add_argument("--layers", type=int, default=35, help="decode workload: layers of the model (35 is the benchmark's; fewer for a profiler capture)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="decode workload: skip the prefill / encoder / single-kernel sub-objects")

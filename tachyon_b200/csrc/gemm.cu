@@ -12,7 +12,9 @@
 //               exactly (0x6400 | (code ^ 0x80) is 1024 + code + 128; minus 1152), multiplies by the scale and stores
 //               the row in the same swizzled K-major layout TMA would have produced; after the main loop the same
 //               warps read the accumulator back (tcgen05.ld) and write the output (f32, f16, or GeGLU of column pairs).
-// Stages hand over on mbarriers: full = TMA bytes + the eight dequantising warps, empty = tcgen05.commit.
+// Stages hand over on mbarriers: full = TMA bytes + the dequantising warps, empty = tcgen05.commit.
+// With f16 weights (tb_gemm_f16, and the f16 copies of quantised matrices that prefill and the encoder keep) the weight tile
+// comes by TMA like the activations' and those warps only run the epilogue.
 // Operands are f16 rather than bf16: the code -> f16 step is exact and costs one instruction per two weights, the
 // tensor rate is the same, and the activations that reach this kernel are normalised.
 #include <cuda.h>
@@ -191,19 +193,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
         // next tile's codes are fetched before this one's are stored.
         const int j = threadIdx.x - 64, qtr = j & 3;
         uint4 c[PIECES];
-        uint4 c2[WB == 16 ? PIECES : 1];  // f16 weights: the second 16 bytes of a piece of 16 weights
         uint4 sc8[PIECES];  // per piece: the row's eight scales covering tiles kt & ~3 ... + 3
         auto fetch = [&](uint32_t kt) {
 #pragma unroll
             for (int it = 0; it < PIECES; it++) {
                 const uint32_t row = it * (DT / 4) + (j >> 2), n = n0 + row;
                 const bool live = n < g.N;
-                if constexpr (WB == 16) {
-                    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(g.w) + (size_t)n * g.K + (size_t)kt * BK + qtr * 16);
-                    c[it] = live ? __ldg(src) : make_uint4(0u, 0u, 0u, 0u);
-                    c2[it] = live ? __ldg(src + 1) : make_uint4(0u, 0u, 0u, 0u);
-                    continue;
-                }
                 if constexpr (WB == 4) {
                     // A piece is 16 weights = 8 bytes; a row's tile 32 bytes; its one scale per tile comes eight tiles at a time.
                     const uint2 t = live ? __ldg(reinterpret_cast<const uint2*>(g.w + (size_t)n * (g.K / 2) + (size_t)kt * (BK / 2) + qtr * 8))
@@ -246,11 +241,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
 #pragma unroll
             for (int it = 0; it < PIECES; it++) {
                 // scale of this piece's group of 32: tile kt's two scales are halves 2*(kt&3) and 2*(kt&3)+1
-                if constexpr (WB == 16) {
-                    v[it][0] = c[it].x, v[it][1] = c[it].y, v[it][2] = c[it].z, v[it][3] = c[it].w;
-                    v[it][4] = c2[it].x, v[it][5] = c2[it].y, v[it][6] = c2[it].z, v[it][7] = c2[it].w;
-                    continue;
-                }
                 const uint32_t words[4] = {sc8[it].x, sc8[it].y, sc8[it].z, sc8[it].w};
                 if constexpr (WB == 4) {
                     const uint32_t pair = words[(kt & 7) >> 1];
