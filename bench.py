@@ -598,8 +598,8 @@ def bench_prefill(args, ranks: Ranks):
     n = ranks.world
     return {"metric": "prefill_tokens_per_second", "value": n * T / (ms_max / 1e3), "unit": "tok/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": ("int4" if args.weights == "q4" else "int8") + " weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
-            "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape {args.weights.upper()}, chunks of {args.chunk}, last token through the decode step",
+            "dtype": ("int4" if args.weights == "q4" else "int8") + " weights as their f16 values (a copy made once, read by TMA), f16 activations, f32 accumulate (tcgen05); f16/f32 flash attention", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"configs[3]: prefill of {T} token ids, Gemma-4-E4B-shape {args.weights.upper()}, chunks of {args.chunk}, last token through the decode step; tb_settings.prefill_copy automatic (TACHYON_B200_PREFILL_COPY=0: codes converted in the loop)",
                        "timing": "host wall clock around tb_decoder_prefill + tb_decoder_step (token ids cross from host memory)"},
             "gpu_launches": None, "first_token": int(first), "device_ms": dev_ms_max,
             "e2e": {"value": n * T / (ms_max / 1e3), "unit": "tok/s", "h2d_bytes_per_step": T * 4, "d2h_bytes_per_step": 4,
@@ -643,7 +643,7 @@ def bench_encoder(args, ranks: Ranks):
     enc.close()
     return {"metric": "encoder_sequences_per_second", "value": n * 64 / (ms_max / 1e3), "unit": "seq/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 weights -> f16, f16 activations, f32 accumulate (tcgen05); f16/f32 attention", "data": "synthetic", "impl": "ours",
+            "dtype": "int8 weights as their f16 values (a copy made once, read by TMA), f16 activations, f32 accumulate (tcgen05); f16/f32 attention", "data": "synthetic", "impl": "ours",
             "config": {"workload": f"configs[4]: 64 sequences of 16..512 tokens ({tokens} tokens packed), Granite-311m shape, plain GELU FFN 3072, mean pooling, 256 dims",
                        "parallelism": f"{n} independent replicas on disjoint batches", "timing": "host wall clock around tb_encoder_embed (host ids in, host embeddings out)"},
             "e2e": {"value": n * 64 / (ms_max / 1e3), "unit": "seq/s", "h2d_bytes_per_step": tokens * 8 + 64 * 8, "d2h_bytes_per_step": 64 * 256 * 4},
