@@ -434,7 +434,7 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         // persistent tile of 256 would be half empty.
         const int which = ctx->gemm_schedule;
         // 3 and 4: the pair schedule of gemm3.cu with tiles of 256 and 128 weight rows.
-        if ((which == 3 || which == 4) && wbits != 16 && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
+        if ((which == 3 || which == 4) && gemm_pair_supports(N, K, wbits, mode)) return launch_gemm_pair(ctx, w, s, a, M, N, K, out, mode, wbits, which == 4);
         // With f16 weights (no conversion: sixteen more warps drain accumulators) the persistent one wins everywhere but on
         // the gated outputs over a long K, where this file's larger tile reads less per FLOP (measured at 2048 tokens:
         // 32768 x 2048 gated 206 against 220 us; 3072 x 2048 33 against 42; at 16384 tokens, 3072 x 768 with a GELU 109 against 121).

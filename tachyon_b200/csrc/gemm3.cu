@@ -177,9 +177,11 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
 
     if (threadIdx.x == 0) {
         // full: this block's activation copy and its dequantising warps.  peer_full (the leader's): the other block's relay.
-        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], S::DW + 1), mbar_init(&bar.peer_full[i], 1), mbar_init(&bar.empty[i], 1);
+        // WB == 16 (f16 weights): this block's half of the weight tile comes by TMA with the activations (warp 0), nothing is
+        // converted, and the converting warps join the epilogue.
+        for (int i = 0; i < ST; i++) mbar_init(&bar.full[i], WB == 16 ? 1 : S::DW + 1), mbar_init(&bar.peer_full[i], 1), mbar_init(&bar.empty[i], 1);
         for (int i = 0; i < CS; i++) mbar_init(&bar.c_full[i], 1), mbar_init(&bar.c_empty[i], S::DW);
-        for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], 2 * EW);
+        for (int i = 0; i < 2; i++) mbar_init(&bar.acc_full[i], 1), mbar_init(&bar.acc_empty[i], 2 * (WB == 16 ? S::DW + EW : EW));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t t = pair; t < tiles; t += pairs) {
-                const uint32_t m0 = (t % tiles_m) * (2 * BM) + rank * BM;
+                const uint32_t m0 = (t % tiles_m) * (2 * BM) + rank * BM, n0 = (t / tiles_m) * BN + rank * S::BH;
                 for (uint32_t kt = 0; kt < nk; kt++, it++) {
                     const uint32_t s = it % ST;
                     if (it >= ST && !mbar_wait_cluster(&bar.empty[s], ((it / ST) - 1) & 1)) {
@@ -211,13 +213,14 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                         t = tiles;
                         break;
                     }
-                    mbar_expect_tx(&bar.full[s], S::A_BYTES);
+                    mbar_expect_tx(&bar.full[s], WB == 16 ? S::A_BYTES + S::B_BYTES : S::A_BYTES);
                     tma_load_2d(As + s * S::A_BYTES, &a_map, (int)(kt * BK), (int)m0, &bar.full[s]);
+                    if constexpr (WB == 16) tma_load_2d(Bs + s * S::B_BYTES, &w_map, (int)(kt * BK), (int)n0, &bar.full[s]);
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (WB != 16 && lane == 0) {
             uint32_t ic = 0;
             for (uint32_t t = pair; t < tiles; t += pairs) {
                 const uint32_t n0 = (t / tiles_m) * BN + rank * S::BH;
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
                 mbar_arrive_cluster(in_cta(smem_addr(&bar.peer_full[s]), 0));
             }
         }
-    } else if (warp < S::FIRST_EW) {
+    } else if (WB != 16 && warp < S::FIRST_EW) {
         // Dequantisation: thread j takes the 16 codes of piece (row j / 4, quarter j % 4) of every stage.
         const int j = threadIdx.x - 32 * FIRST_DW, row = j >> 2, qtr = j & 3;
         constexpr uint32_t GS = WB == 4 ? 8 : 4;               // k tiles one 16-byte load of scales covers
@@ -370,7 +373,8 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
     } else {
         // Epilogue: a warp reads the accumulator lanes (this block's token rows) of its quarter q = warp % 4, 32 columns at
         // a time; the two warps of a quarter take alternate column blocks.
-        const uint32_t q = warp & 3, part = (warp - S::FIRST_EW) >> 2;
+        constexpr int FIRST = WB == 16 ? FIRST_DW : S::FIRST_EW, PARTS = (WB == 16 ? S::DW + EW : EW) / 4;
+        const uint32_t q = warp & 3, part = (warp - FIRST) >> 2;
         const uint32_t acc_empty_at_leader[2] = {in_cta(smem_addr(&bar.acc_empty[0]), 0), in_cta(smem_addr(&bar.acc_empty[1]), 0)};
         uint32_t ti = 0;
         for (uint32_t t = pair; t < tiles; t += pairs, ti++) {
@@ -381,7 +385,7 @@ __global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_pair_kernel(const 
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int cb = part; cb < BN / 32; cb += EW / 4) {
+            for (int cb = part; cb < BN / 32; cb += PARTS) {
                 const uint32_t m = m0 + 32 * q + lane;
                 uint32_t r[32];
                 tmem_load32(tmem + ((32 * q) << 16) + b * BN + cb * 32, r);
@@ -496,16 +500,19 @@ int launch_gemm_pair(tb_context* ctx, const int8_t* w, const __half* s, const __
         if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (activations) failed (" + std::to_string((int)r) + ")");
     }
     {
-        const cuuint64_t row = (cuuint64_t)K * wbits / 8;  // bytes of codes per weight row
-        const cuuint64_t dims[2] = {row, N};
+        const cuuint64_t row = (cuuint64_t)K * wbits / 8;  // bytes of codes (or of f16 weights) per weight row
+        const cuuint64_t dims[2] = {wbits == 16 ? (cuuint64_t)K : row, N};
         const cuuint64_t strides[1] = {row};
-        const cuuint32_t box[2] = {(cuuint32_t)(BK * wbits / 8), bn / 2}, elem[2] = {1, 1};
-        const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint32_t box[2] = {(cuuint32_t)(wbits == 16 ? BK : BK * wbits / 8), bn / 2}, elem[2] = {1, 1};
+        // f16 weights go straight into the operand stage: halves, 128-byte swizzle, like the activations
+        const CUresult r = enc(&wmap, wbits == 16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(w), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, wbits == 16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(CUDA, "gemm: cuTensorMapEncodeTiled (codes) failed (" + std::to_string((int)r) + ")");
     }
     const uint32_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn);
     const Args g{s, out, M, N, K, mode};
+    if (wbits == 16) return narrow ? launch_pair<16, 128>(ctx, amap, wmap, g, tiles) : launch_pair<16, 256>(ctx, amap, wmap, g, tiles);
     if (wbits == 4) return narrow ? launch_pair<4, 128>(ctx, amap, wmap, g, tiles) : launch_pair<4, 256>(ctx, amap, wmap, g, tiles);
     return narrow ? launch_pair<8, 128>(ctx, amap, wmap, g, tiles) : launch_pair<8, 256>(ctx, amap, wmap, g, tiles);
 }

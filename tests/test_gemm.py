@@ -101,7 +101,7 @@ def test_gemm_q4_matches_f64(ctx, schedule, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (37, 256, 768), (300, 2304, 768), (512, 768, 3072), (129, 3072, 768), (64, 64, 576)])
-def test_gemm_f16_weights_and_every_store_mode(ctx, m, n, k):
+def test_gemm_f16_weights_and_every_store_mode(ctx, schedule, m, n, k):
     """tb_gemm_f16: f16 weights as they are (the reference's gemm_f16, tests/encoder.rs:240-355: all modes, rows past the
     tokens untouched), against f64; and the store modes the Q8 test above does not reach: residual add, exact-form GELU plain
     and gated, ReLU, gated SiLU."""
