@@ -520,6 +520,51 @@ def bench_gemm(args, ranks: Ranks):
                          "flops_per_launch": 2.0 * m * n * k, "us_per_launch": us}}
 
 
+def bench_switch(args, ranks: Ranks):
+    """A model's return from the host-RAM tier (the reference's benches/switch.rs, host_tier: E4B parked, then resumed): seconds
+    and GB/s of its weights for tb_parked_resume (device memory taken, one copy over the link, buffers laid out, the step's
+    graphs recorded, the prefill copy written), beside a plain copy of 1 GiB of pinned memory into device memory in use."""
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    cfg = tb.gemma4_e4b_shape(layers=args.layers)
+    dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=512, keep_logits=False)
+    dec.fill_random(SEED)
+    dec.build()
+    tok = dec.step(7)
+    weights = dec.parked_bytes()
+    t0 = time.perf_counter()
+    parked = dec.park()
+    first_park = time.perf_counter() - t0
+    back, parks = [], []
+    for _ in range(max(args.steps, 1) if args.steps <= 16 else 5):
+        t0 = time.perf_counter()
+        dec = parked.resume()
+        back.append(time.perf_counter() - t0)
+        assert dec.step(7) == tok, "the resumed model answers as before"
+        t0 = time.perf_counter()
+        parked = dec.park()
+        parks.append(time.perf_counter() - t0)
+    parked.close()
+    # the link alone: 1 GiB of pinned memory into device memory that is already in use
+    n = 1 << 30
+    hb, db = ctx.alloc_host(n), ctx.alloc(n)
+    hb.array[:] = 1
+    copies = []
+    for _ in range(4):
+        t0 = time.perf_counter()
+        tb.check(ctx.lib.tb_upload(ctx.handle, db.ptr, hb.host, n))
+        ctx.sync()
+        copies.append(time.perf_counter() - t0)
+    link = n / min(copies[1:]) / 1e9
+    sec = statistics.median(back)
+    return {"metric": "resume_from_host_tier_gb_per_second", "value": weights / sec / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": len(back), "warmup": 0,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "u8", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"the benchmark's decoder ({args.layers} layers, {weights} B of weights) parked in pinned host memory and resumed (tb_decoder_park / tb_parked_resume)"},
+            "gpu_launches": None, "first_park_s": first_park, "park_with_kept_copy_s": statistics.median(parks), "resume_s": sec,
+            "link_gb_per_second": link, "fraction_of_link": weights / sec / 1e9 / link}
+
+
 def bench_flash(args, ranks: Ranks):
     """configs[3]'s attention alone: 2048 tokens x 8 query / 2 kv heads of 256 over the cache ring, sliding 512 and global."""
     import tachyon_b200 as tb
@@ -685,7 +730,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder", "switch"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -719,6 +764,8 @@ def main():
             line = bench_prefill(args, ranks)
         elif args.workload == "encoder":
             line = bench_encoder(args, ranks)
+        elif args.workload == "switch":
+            line = bench_switch(args, ranks) if ranks.rank == 0 else None
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if not args.no_extras:

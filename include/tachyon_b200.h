@@ -42,6 +42,8 @@ enum {
 
 typedef struct tb_context tb_context;
 typedef struct tb_decoder tb_decoder;
+typedef struct tb_parked tb_parked;
+typedef struct tb_engine tb_engine;
 typedef struct tb_event tb_event;
 
 /* The calling thread's last error message ("" when none). */
@@ -79,6 +81,8 @@ TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
  * default), 0 the mma.sync kernel every other shape takes.  An encoder with heads of 64 opened while this is 1 runs its
  * attention on tcgen05 as well (tiles of 128 queries of a sequence and head).  TACHYON_B200_FLASH=0 starts a context at 0. */
 TB_API int tb_context_set_flash(tb_context* ctx, int which);
+/* Context::memory (cuda/mod.rs:194-198): free and total device memory, in bytes. */
+TB_API int tb_context_memory(tb_context* ctx, size_t* free_bytes, size_t* total_bytes);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */
 TB_API int tb_status(tb_context* ctx, uint32_t* word);
 /* Clears that word (after an error has been looked at). */
@@ -471,6 +475,66 @@ TB_API int tb_wpk_read(const tb_wpk* wpk, uint32_t index, void* host, size_t byt
  * load with TB_NO_MODEL; a size that does not fit with TB_FORMAT.
  */
 TB_API int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify);
+
+/*
+ * The host-RAM tier (Decoder::park, Parked::resume, Decoder::{shadow_bytes, drop_shadow, parked_bytes}: decode.rs:235-247,
+ * 275-295, 452-463).  tb_decoder_park stops a running generation, copies the weights into pinned host memory (unless the decoder
+ * still holds the pinned copy it was resumed from), frees the decoder and every byte of its device memory, and hands back the
+ * parked model; on failure the decoder is untouched.  tb_parked_resume takes the parked model (on success) and gives a built
+ * decoder with `settings` (context and chunk may differ; weight_bits and host_table are the parked model's): one copy of the
+ * weights over the link, then the step's graphs are recorded; the pinned copy stays with the decoder as its shadow.  The
+ * per-layer table in host memory moves along as it is.  Positions, caches and sampler state do not survive: the decoder
+ * starts at position 0 with greedy sampling.
+ */
+TB_API int tb_decoder_park(tb_decoder* dec, tb_parked** out);
+TB_API int tb_parked_resume(tb_parked* parked, const tb_settings* settings, tb_decoder** out);
+TB_API size_t tb_parked_bytes(const tb_parked* parked);   /* pinned host memory it holds: weights + table */
+TB_API void tb_parked_close(tb_parked* parked);
+TB_API size_t tb_decoder_bytes(const tb_decoder* dec);          /* device memory it holds: arena + prefill copy */
+/* The device memory a decoder of this shape and these settings takes, without allocating it (the engine's `need`,
+ * engine.rs:214; an automatic prefill copy is counted whenever chunk >= 256). */
+TB_API int tb_decoder_footprint(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, size_t* bytes);
+TB_API size_t tb_decoder_parked_bytes(tb_decoder* dec);         /* pinned memory parking it would hold */
+TB_API size_t tb_decoder_shadow_bytes(const tb_decoder* dec);   /* pinned memory it keeps from its last resume */
+TB_API void tb_decoder_drop_shadow(tb_decoder* dec);
+
+/*
+ * Model residency: the reference engine's tiers (engine.rs:62-130 Limits / Load / Loaded / Tier, 203-223 load, 243-250 unload,
+ * 271-283 tier, 309-325 expire, 386-453 resident / room / evict).  Decoders only; names are the caller's.  A model is loaded
+ * from its converted files (weights.wpk, and host.wpk for a per-layer table); asking for it brings it into VRAM, moving
+ * out the least recently used models that may go (not pinned, not the one asked for) until `vram_limit` holds; a model
+ * moved out is parked in pinned host memory if `host_limit` allows, after the least recently used pinned memory has given
+ * way (a resident model's kept copy is dropped, a parked model goes to disk), else it goes to disk and is read again when
+ * asked for.  A keep-alive that has run out sends a model to disk at the next call.  Limits of 0 mean 70 % of the GPU's
+ * memory and half the machine's RAM.  tb_decoder_footprint gives a model's VRAM `need`.
+ */
+enum { TB_TIER_VRAM = 0, TB_TIER_HOST = 1, TB_TIER_DISK = 2 };  /* engine.rs:110-118 */
+typedef struct tb_load {   /* engine.rs:72-90 */
+    tb_settings settings;
+    uint64_t keep_alive_ms;  /* how long it stays in memory after its last use; 0: out at the next call; UINT64_MAX: for good */
+    uint32_t pin;            /* != 0: never moves out of VRAM, by keep-alive or to make room */
+} tb_load;
+typedef struct tb_loaded { /* engine.rs:93-107 */
+    char name[64];
+    int tier;
+    size_t vram;             /* the VRAM it takes where it is: 0 out of VRAM */
+    uint64_t left_ms;        /* what is left of its keep-alive; UINT64_MAX: no end (pinned or kept for good) */
+} tb_loaded;
+TB_API int tb_engine_new(tb_context* ctx, size_t vram_limit, size_t host_limit, tb_engine** out);
+TB_API void tb_engine_close(tb_engine* eng);
+/* Engine::load: a model of that name is unloaded first; TB_OUT_OF_MEMORY (nothing loaded) when it cannot be made to fit. */
+TB_API int tb_engine_load(tb_engine* eng, const char* name, const tb_config* cfg, const tb_load* load, const char* weights_path, const char* host_path);
+TB_API int tb_engine_unload(tb_engine* eng, const char* name, int* was_loaded);
+/* The model's decoder, in VRAM (Engine::resident), its keep-alive started again.  The pointer is the engine's and holds
+ * until the next call that may move the model.  TB_NO_MODEL for a name that is not loaded. */
+TB_API int tb_engine_decoder(tb_engine* eng, const char* name, tb_decoder** out);
+/* feed (engine.rs:458-465) without the tokenizer: from position 0, every prompt token but the last through prefill, the
+ * last through a step; *first is the answer's first token.  tb_decoder_next_token etc. on tb_engine_decoder's pointer go on. */
+TB_API int tb_engine_feed(tb_engine* eng, const char* name, const uint32_t* tokens, uint32_t n, uint32_t* first);
+TB_API int tb_engine_tier(const tb_engine* eng, const char* name, int* tier);
+TB_API int tb_engine_models(const tb_engine* eng, tb_loaded* out, size_t capacity, size_t* count);
+TB_API int tb_engine_expire(tb_engine* eng);
+TB_API int tb_engine_usage(const tb_engine* eng, size_t* vram, size_t* host);   /* Engine::used, Engine::hosted */
 
 /* Hidden state after the last step, f32 [hidden] (for layer-wise parity checks). */
 TB_API int tb_decoder_hidden(tb_decoder* dec, float* host_out);

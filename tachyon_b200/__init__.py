@@ -13,7 +13,7 @@ import os
 import numpy as np
 
 from . import _lib
-from ._lib import Attend, Config, EncoderConfig, Settings
+from ._lib import Attend, Config, EncoderConfig, Load, Loaded, Settings
 
 F32, F16 = 0, 1
 
@@ -246,6 +246,12 @@ class Context:
     def set_dynamic(self, on: bool) -> None:
         check(self.lib.tb_context_set_dynamic(self.handle, int(on)))
 
+    def memory(self) -> tuple[int, int]:
+        """Context::memory: free and total device memory in bytes."""
+        f, t = C.c_size_t(0), C.c_size_t(0)
+        check(self.lib.tb_context_memory(self.handle, C.byref(f), C.byref(t)))
+        return f.value, t.value
+
     def set_flash(self, which: int) -> None:
         """tb_context_set_flash: 1 prefill attention on tcgen05 where the shape allows (default), 0 the mma.sync kernel."""
         check(self.lib.tb_context_set_flash(self.handle, which))
@@ -342,6 +348,106 @@ def crc32c(data: bytes, crc: int = 0) -> int:
     return int(_lib.load().tb_crc32c(crc, buf.ctypes.data if buf.size else None, buf.size))
 
 
+class Parked:
+    """model::Parked (decode.rs:101-109, 449-469): a model in the host-RAM tier."""
+
+    def __init__(self, ctx: Context, cfg: Config, settings: Settings, handle: int):
+        self.ctx, self.cfg, self.settings, self.lib, self.handle = ctx, cfg, settings, ctx.lib, handle
+
+    def bytes(self) -> int:
+        return int(self.lib.tb_parked_bytes(self.handle))
+
+    def resume(self, context: int | None = None, chunk: int | None = None, keep_logits: bool | None = None, prefill_copy: int | None = None) -> "Decoder":
+        """Parked::resume: back to VRAM with these settings (those not given stay as they were); this object is spent on success."""
+        old = self.settings
+        st = Settings(context=old.context if context is None else context, chunk=old.chunk if chunk is None else chunk,
+                      keep_logits=old.keep_logits if keep_logits is None else int(keep_logits), fused=old.fused, weight_bits=old.weight_bits,
+                      host_table=old.host_table, prefill_copy=old.prefill_copy if prefill_copy is None else prefill_copy)
+        h = C.c_void_p()
+        check(self.lib.tb_parked_resume(self.handle, C.byref(st), C.byref(h)))
+        self.handle = None
+        return Decoder._adopt(self.ctx, self.cfg, st, h.value)
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_parked_close(self.handle)
+            self.handle = None
+
+
+TIER_VRAM, TIER_HOST, TIER_DISK = 0, 1, 2
+FOR_GOOD = 2**64 - 1
+
+
+class Engine:
+    """Engine's model residency (crates/tachyon/src/engine.rs:190-453), decoders only: load, decoder, feed, tier, models, unload, expire."""
+
+    def __init__(self, ctx: Context, vram_limit: int = 0, host_limit: int = 0):
+        self.ctx, self.lib = ctx, ctx.lib
+        h = C.c_void_p()
+        check(self.lib.tb_engine_new(ctx.handle, vram_limit, host_limit, C.byref(h)))
+        self.handle = h.value
+        self.loaded: dict[str, tuple[Config, Settings]] = {}
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_engine_close(self.handle)
+            self.handle = None
+
+    def load(self, name: str, cfg: Config, weights: str, host: str | None = None, context: int = 4096, chunk: int = 512, keep_alive_ms: int = 300_000,
+             pin: bool = False, keep_logits: bool = False, weight_bits: int = 8, host_table: bool = False, prefill_copy: int = 0) -> None:
+        st = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=0, weight_bits=weight_bits, host_table=int(host_table), prefill_copy=prefill_copy)
+        load = Load(settings=st, keep_alive_ms=keep_alive_ms, pin=int(pin))
+        check(self.lib.tb_engine_load(self.handle, name.encode(), C.byref(cfg), C.byref(load), os.fsencode(weights), os.fsencode(host) if host else None))
+        self.loaded[name] = (cfg, st)
+
+    def unload(self, name: str) -> bool:
+        was = C.c_int(0)
+        check(self.lib.tb_engine_unload(self.handle, name.encode(), C.byref(was)))
+        self.loaded.pop(name, None)
+        return bool(was.value)
+
+    def decoder(self, name: str) -> "Decoder":
+        h = C.c_void_p()
+        check(self.lib.tb_engine_decoder(self.handle, name.encode(), C.byref(h)))
+        cfg, st = self.loaded[name]
+        return Decoder._adopt(self.ctx, cfg, st, h.value, owned=False)
+
+    def feed(self, name: str, tokens) -> int:
+        t = np.ascontiguousarray(tokens, np.uint32)
+        first = C.c_uint32(0)
+        check(self.lib.tb_engine_feed(self.handle, name.encode(), t.ctypes.data, t.size, C.byref(first)))
+        return first.value
+
+    def tier(self, name: str) -> int:
+        t = C.c_int(0)
+        check(self.lib.tb_engine_tier(self.handle, name.encode(), C.byref(t)))
+        return t.value
+
+    def models(self) -> list[dict]:
+        n = C.c_size_t(0)
+        check(self.lib.tb_engine_models(self.handle, None, 0, C.byref(n)))
+        arr = (Loaded * max(n.value, 1))()
+        check(self.lib.tb_engine_models(self.handle, arr, n.value, C.byref(n)))
+        return [{"name": arr[i].name.decode(), "tier": arr[i].tier, "vram": arr[i].vram, "left_ms": arr[i].left_ms} for i in range(n.value)]
+
+    def expire(self) -> None:
+        check(self.lib.tb_engine_expire(self.handle))
+
+    def usage(self) -> tuple[int, int]:
+        v, h = C.c_size_t(0), C.c_size_t(0)
+        check(self.lib.tb_engine_usage(self.handle, C.byref(v), C.byref(h)))
+        return v.value, h.value
+
+
+def decoder_footprint(ctx: Context, cfg: Config, context: int = 4096, chunk: int = 512, keep_logits: bool = False, weight_bits: int = 8,
+                      host_table: bool = False, prefill_copy: int = 0) -> int:
+    """tb_decoder_footprint: the device memory such a decoder takes, nothing allocated."""
+    st = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=0, weight_bits=weight_bits, host_table=int(host_table), prefill_copy=prefill_copy)
+    n = C.c_size_t(0)
+    check(ctx.lib.tb_decoder_footprint(ctx.handle, C.byref(cfg), C.byref(st), C.byref(n)))
+    return n.value
+
+
 class Decoder:
     """model::Decoder (crates/tachyon/src/model/decode.rs:79-99): open, load or fill, build, then step."""
 
@@ -354,10 +460,36 @@ class Decoder:
         check(self.lib.tb_decoder_open(ctx.handle, C.byref(cfg), C.byref(self.settings), C.byref(h)))
         self.handle = h.value
 
+    @classmethod
+    def _adopt(cls, ctx: Context, cfg: Config, settings: Settings, handle: int, owned: bool = True) -> "Decoder":
+        """A decoder the library made (tb_parked_resume, tb_engine_decoder); `owned` False: the engine's, never closed here."""
+        d = cls.__new__(cls)
+        d.ctx, d.cfg, d.lib, d.settings, d.handle, d.owned = ctx, cfg, ctx.lib, settings, handle, owned
+        return d
+
     def close(self) -> None:
-        if self.handle:
+        if self.handle and getattr(self, "owned", True):
             self.lib.tb_decoder_close(self.handle)
-            self.handle = None
+        self.handle = None
+
+    def park(self) -> "Parked":
+        """Decoder::park (decode.rs:235-247): weights to pinned host memory, the device memory freed; this object is spent."""
+        h = C.c_void_p()
+        check(self.lib.tb_decoder_park(self.handle, C.byref(h)))
+        self.handle = None
+        return Parked(self.ctx, self.cfg, self.settings, h.value)
+
+    def bytes(self) -> int:
+        return int(self.lib.tb_decoder_bytes(self.handle))
+
+    def parked_bytes(self) -> int:
+        return int(self.lib.tb_decoder_parked_bytes(self.handle))
+
+    def shadow_bytes(self) -> int:
+        return int(self.lib.tb_decoder_shadow_bytes(self.handle))
+
+    def drop_shadow(self) -> None:
+        self.lib.tb_decoder_drop_shadow(self.handle)
 
     def load(self, name: str, a: np.ndarray) -> None:
         a = np.ascontiguousarray(a)

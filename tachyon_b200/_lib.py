@@ -41,8 +41,21 @@ class WpkInfo(C.Structure):
     _fields_ = [("name", cp), ("dtype", u32), ("rank", u32), ("shape", u64 * 8), ("offset", u64), ("bytes", u64), ("crc32c", u32)]
 
 
+class Load(C.Structure):
+    """tb_load (engine.rs:72-90): settings, keep-alive in ms (2**64 - 1: for good), pin."""
+    pass
+
+
+class Loaded(C.Structure):
+    """tb_loaded (engine.rs:93-107)."""
+    _fields_ = [("name", C.c_char * 64), ("tier", C.c_int), ("vram", C.c_size_t), ("left_ms", C.c_uint64)]
+
+
 class Settings(C.Structure):
     _fields_ = [("context", u32), ("chunk", u32), ("keep_logits", u32), ("fused", u32), ("weight_bits", u32), ("host_table", u32), ("prefill_copy", u32)]
+
+
+Load._fields_ = [("settings", Settings), ("keep_alive_ms", C.c_uint64), ("pin", C.c_uint32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares.
@@ -57,6 +70,7 @@ SIGNATURES = {
     "tb_context_set_lean": (i32, [vp, i32]),
     "tb_context_set_dynamic": (i32, [vp, i32]),
     "tb_context_set_flash": (i32, [vp, i32]),
+    "tb_context_memory": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
     "tb_status": (i32, [vp, C.POINTER(u32)]),
     "tb_status_clear": (i32, [vp]),
     "tb_selftest_wait": (i32, [vp, u64]),
@@ -133,6 +147,25 @@ SIGNATURES = {
     "tb_wpk_tensor": (i32, [vp, u32, vp]),
     "tb_wpk_read": (i32, [vp, u32, vp, sz, i32]),
     "tb_decoder_load_wpk": (i32, [vp, cp, i32]),
+    "tb_decoder_park": (i32, [vp, pp]),
+    "tb_parked_resume": (i32, [vp, C.POINTER(Settings), pp]),
+    "tb_parked_bytes": (sz, [vp]),
+    "tb_parked_close": (None, [vp]),
+    "tb_decoder_bytes": (sz, [vp]),
+    "tb_decoder_parked_bytes": (sz, [vp]),
+    "tb_decoder_shadow_bytes": (sz, [vp]),
+    "tb_decoder_drop_shadow": (None, [vp]),
+    "tb_decoder_footprint": (i32, [vp, C.POINTER(Config), C.POINTER(Settings), C.POINTER(sz)]),
+    "tb_engine_new": (i32, [vp, sz, sz, pp]),
+    "tb_engine_close": (None, [vp]),
+    "tb_engine_load": (i32, [vp, cp, C.POINTER(Config), C.POINTER(Load), cp, cp]),
+    "tb_engine_unload": (i32, [vp, cp, C.POINTER(i32)]),
+    "tb_engine_decoder": (i32, [vp, cp, pp]),
+    "tb_engine_feed": (i32, [vp, cp, vp, u32, C.POINTER(u32)]),
+    "tb_engine_tier": (i32, [vp, cp, C.POINTER(i32)]),
+    "tb_engine_models": (i32, [vp, C.POINTER(Loaded), sz, C.POINTER(sz)]),
+    "tb_engine_expire": (i32, [vp]),
+    "tb_engine_usage": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
     "tb_encoder_open": (i32, [vp, C.POINTER(EncoderConfig), u32, u32, pp]),
     "tb_encoder_close": (None, [vp]),
     "tb_encoder_load": (i32, [vp, cp, vp, sz]),

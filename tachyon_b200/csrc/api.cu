@@ -169,6 +169,13 @@ int tb_context_set_dynamic(tb_context* ctx, int on) {
     return OK;
 }
 
+int tb_context_memory(tb_context* ctx, size_t* free_bytes, size_t* total_bytes) {
+    if (!ctx || !free_bytes || !total_bytes) return fail(OUT_OF_RANGE, "tb_context_memory: null argument");
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+    return OK;
+}
+
 int tb_context_set_flash(tb_context* ctx, int which) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     if (which != 0 && which != 1) return fail(OUT_OF_RANGE, "tb_context_set_flash: 0 (mma.sync kernel) or 1 (tcgen05 where the shape allows)");

@@ -85,6 +85,11 @@ struct tb_decoder {
     // a tensor was loaded since (copy_valid).
     __half* copy = nullptr;
     bool copy_valid = false;
+    // A resumed decoder keeps the pinned copy its weights came from (Decoder::shadow_bytes, decode.rs:275-290): parking it again
+    // then costs no copy.  Dropped when a tensor is loaded (the copy would be stale) or by tb_decoder_drop_shadow.
+    char* shadow = nullptr;
+    size_t shadow_bytes = 0;
+    cudaEvent_t weights_ready = nullptr;  // while resuming: the weights' copy on its own stream; what reads them for keeps waits for it
     char* host_table = nullptr;  // settings.host_table: the per-layer table, codes then scales, in pinned mapped host memory
     size_t arena_bytes = 0;
     // step buffers
@@ -581,6 +586,7 @@ int place_copy(tb_decoder* d) {
 // Writes the copy from the codes as they are now.
 int refresh_copy(tb_decoder* d) {
     if (!d->copy || d->copy_valid) return OK;
+    if (d->weights_ready) TB_CUDA(cudaStreamWaitEvent(d->ctx->stream, d->weights_ready, 0));
     for (Layer& L : d->layers)
         for (Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) TB_TRY(launch_dequant_f16(d->ctx, m->w, m->s, m->rows, m->cols, m->bits, m->f16));
     d->copy_valid = true;
@@ -594,11 +600,51 @@ int prefill_product(tb_decoder* d, const Mat& m, const __half* x, uint32_t token
     return launch_gemm_q8(d->ctx, m.w, m.s, x, tokens, m.rows, m.cols, out, mode, m.bits);
 }
 
+// Every weight tensor in the arena, in the order of the layout (which no setting changes): what parking copies out and
+// resuming copies back.  The per-layer table in host memory is not among them (it moves with the parked model as it is).
+template <typename F>
+void for_each_weight(tb_decoder* d, F&& f) {
+    const tb_config& c = d->cfg;
+    auto mat = [&](Mat& m) { f(static_cast<void*>(m.w), m.code_bytes()), f(static_cast<void*>(m.s), m.scale_bytes()); };
+    auto vec = [&](float* v, size_t n) { f(static_cast<void*>(v), n * 4); };
+    mat(d->embed), vec(d->norm, c.hidden);
+    if (c.per_layer) {
+        if (!d->settings.host_table) mat(d->embed_pl);
+        mat(d->pl_model_proj), vec(d->pl_norm, c.per_layer);
+    }
+    for (Layer& L : d->layers) {
+        mat(L.qkv), mat(L.o), mat(L.gate_up), mat(L.down);
+        vec(L.q_norm, L.dim), vec(L.k_norm, L.dim), vec(L.input_ln, c.hidden), vec(L.post_attn, c.hidden), vec(L.pre_ffn, c.hidden), vec(L.post_ffn, c.hidden);
+        if (c.per_layer) mat(L.pl_gate), mat(L.pl_proj), vec(L.post_pl, c.hidden);
+    }
+}
+
+size_t weight_bytes(tb_decoder* d) {
+    size_t n = 0;
+    for_each_weight(d, [&](void*, size_t bytes) { n += (bytes + 255) / 256 * 256; });
+    return n;
+}
+
+size_t host_table_bytes(const tb_decoder* d) {
+    return d->host_table ? (d->embed_pl.code_bytes() + 255) / 256 * 256 + d->embed_pl.scale_bytes() : 0;
+}
+
+int open_decoder(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, char* adopt_table, tb_decoder** out);
+
 }  // namespace
 
 extern "C" {
 
 int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, tb_decoder** out) {
+    return open_decoder(ctx, cfg, settings, nullptr, out);
+}
+
+}  // extern "C"
+
+namespace {
+
+// adopt_table: a per-layer table already in pinned, mapped host memory (a parked model's), taken over instead of a new one.
+int open_decoder(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, char* adopt_table, tb_decoder** out) {
     if (!ctx || !cfg || !settings || !out) return fail(OUT_OF_RANGE, "tb_decoder_open: null argument");
     *out = nullptr;
     TB_TRY(validate(*cfg, *settings));
@@ -622,12 +668,17 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     if (e == cudaSuccess) e = cudaHostAlloc(&d->words, 64, cudaHostAllocMapped);
     if (e == cudaSuccess && cfg->per_layer && settings->host_table) {
         const size_t bytes = (d->embed_pl.code_bytes() + 255) / 256 * 256 + d->embed_pl.scale_bytes();
-        e = cudaHostAlloc(&d->host_table, bytes, cudaHostAllocMapped);
-        if (e == cudaSuccess) memset(d->host_table, 0, bytes);
+        if (adopt_table != nullptr) {
+            d->host_table = adopt_table;
+        } else {
+            e = cudaHostAlloc(&d->host_table, bytes, cudaHostAllocMapped);
+            if (e == cudaSuccess) memset(d->host_table, 0, bytes);
+        }
     }
     for (int g = 0; g < 2 && e == cudaSuccess; g++) e = cudaEventCreateWithFlags(&d->done[g], cudaEventDisableTiming);
     if (e != cudaSuccess) {
         const int s = cuda_fail(e, "tb_decoder_open");
+        if (adopt_table != nullptr) d->host_table = nullptr;  // still the caller's
         tb_decoder_close(d);
         return s;
     }
@@ -635,7 +686,8 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
     {
         const int st = place_copy(d);
         if (st != OK) {
-            tb_decoder_close(d);
+            if (adopt_table != nullptr) d->host_table = nullptr;  // still the caller's
+        tb_decoder_close(d);
             return st;
         }
     }
@@ -648,13 +700,18 @@ int tb_decoder_open(tb_context* ctx, const tb_config* cfg, const tb_settings* se
         if (e == cudaSuccess && dim_of(*cfg, k) == 256 && launch_rope_table(ctx, d->freq[k], d->settings.context, d->trig[k]) != OK) e = cudaErrorUnknown;
         if (e != cudaSuccess) {
             const int s = cuda_fail(e, "tb_decoder_open: rope tables");
-            tb_decoder_close(d);
+            if (adopt_table != nullptr) d->host_table = nullptr;  // still the caller's
+        tb_decoder_close(d);
             return s;
         }
     }
     *out = d;
     return OK;
 }
+
+}  // namespace
+
+extern "C" {
 
 void tb_decoder_close(tb_decoder* d) {
     if (!d) return;
@@ -670,6 +727,7 @@ void tb_decoder_close(tb_decoder* d) {
     if (d->copy) cudaFree(d->copy);
     if (d->words) cudaFreeHost(d->words);
     if (d->host_table) cudaFreeHost(d->host_table);
+    if (d->shadow) cudaFreeHost(d->shadow);
     delete d;
 }
 
@@ -678,6 +736,7 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
     Named t;
     if (!find_tensor(d, name, t)) return fail(NO_MODEL, std::string("tb_decoder_load: no tensor named ") + name);
     d->copy_valid = false;
+    tb_decoder_drop_shadow(d);
     if (bytes != t.bytes) return fail(FORMAT, std::string("tb_decoder_load: ") + name + " has " + std::to_string(bytes) + " bytes, expected " + std::to_string(t.bytes));
     cudaStream_t s = d->ctx->stream;
     if (t.kind == 3) {
@@ -705,6 +764,7 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
 int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {
     if (!d) return fail(OUT_OF_RANGE, "null decoder");
     d->copy_valid = false;
+    tb_decoder_drop_shadow(d);
     const tb_config& c = d->cfg;
     tb_context* ctx = d->ctx;
     const uint32_t bits = d->embed.bits;
@@ -1078,6 +1138,158 @@ int tb_decoder_hidden(tb_decoder* d, float* host_out) {
     if (!d || !host_out) return fail(OUT_OF_RANGE, "null argument");
     TB_CUDA(cudaMemcpyAsync(host_out, d->x[d->final_x], (size_t)d->cfg.hidden * 4, cudaMemcpyDeviceToHost, d->ctx->stream));
     TB_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    return OK;
+}
+
+// ---- the host-RAM tier: Decoder::park and Parked::resume (crates/tachyon/src/model/decode.rs:235-247, 452-463) ------------
+
+struct tb_parked {
+    tb_context* ctx = nullptr;
+    tb_config cfg = {};
+    tb_settings settings = {};
+    std::vector<uint8_t> global;
+    std::vector<float> scalars;  // every layer's layer_scalar (host-side values, as Parked keeps `scalars`)
+    char* weights = nullptr;     // pinned: every weight tensor, each from a multiple of 256 bytes, in for_each_weight's order
+    size_t weights_bytes = 0;
+    char* host_table = nullptr;  // pinned, mapped: the per-layer table, when the decoder kept it there
+    size_t table_bytes = 0;
+};
+
+size_t tb_decoder_bytes(const tb_decoder* d) {
+    if (!d) return 0;
+    size_t copy = 0;
+    if (d->copy)
+        for (const Layer& L : d->layers)
+            for (const Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) copy += ((size_t)m->rows * m->cols + 127) / 128 * 128 * 2;
+    return d->arena_bytes + copy;
+}
+
+size_t tb_decoder_shadow_bytes(const tb_decoder* d) { return d ? d->shadow_bytes : 0; }
+
+void tb_decoder_drop_shadow(tb_decoder* d) {
+    if (!d || !d->shadow) return;
+    cudaFreeHost(d->shadow);
+    d->shadow = nullptr, d->shadow_bytes = 0;
+}
+
+size_t tb_decoder_parked_bytes(tb_decoder* d) { return d ? weight_bytes(d) + host_table_bytes(d) : 0; }
+
+int tb_decoder_park(tb_decoder* d, tb_parked** out) {
+    if (!d || !out) return fail(OUT_OF_RANGE, "tb_decoder_park: null argument");
+    *out = nullptr;
+    if (d->running) TB_TRY(tb_decoder_stop(d));
+    cudaStream_t s = d->ctx->stream;
+    TB_CUDA(cudaStreamSynchronize(s));
+    const size_t bytes = weight_bytes(d);
+    char* pinned = d->shadow;
+    if (pinned == nullptr) {
+        const cudaError_t e = cudaHostAlloc(&pinned, bytes, cudaHostAllocDefault);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(OUT_OF_MEMORY, "tb_decoder_park: no pinned memory for the weights (" + std::to_string(bytes) + " bytes)");
+        }
+        size_t at = 0;
+        cudaError_t err = cudaSuccess;
+        for_each_weight(d, [&](void* ptr, size_t n) {
+            if (err == cudaSuccess) err = cudaMemcpyAsync(pinned + at, ptr, n, cudaMemcpyDeviceToHost, s);
+            at += (n + 255) / 256 * 256;
+        });
+        if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+        if (err != cudaSuccess) {
+            cudaFreeHost(pinned);
+            return cuda_fail(err, "tb_decoder_park");
+        }
+    }
+    tb_parked* p = new tb_parked();
+    p->ctx = d->ctx, p->cfg = d->cfg, p->settings = d->settings, p->global = d->global;
+    p->cfg.global = nullptr;
+    for (const Layer& L : d->layers) p->scalars.push_back(L.layer_scalar);
+    p->weights = pinned, p->weights_bytes = bytes;
+    p->host_table = d->host_table, p->table_bytes = host_table_bytes(d);
+    d->shadow = nullptr, d->shadow_bytes = 0, d->host_table = nullptr;  // theirs now
+    tb_decoder_close(d);
+    *out = p;
+    return OK;
+}
+
+size_t tb_parked_bytes(const tb_parked* p) { return p ? p->weights_bytes + p->table_bytes : 0; }
+
+void tb_parked_close(tb_parked* p) {
+    if (!p) return;
+    if (p->weights) cudaFreeHost(p->weights);
+    if (p->host_table) cudaFreeHost(p->host_table);
+    delete p;
+}
+
+int tb_parked_resume(tb_parked* p, const tb_settings* settings, tb_decoder** out) {
+    if (!p || !settings || !out) return fail(OUT_OF_RANGE, "tb_parked_resume: null argument");
+    *out = nullptr;
+    if ((settings->weight_bits == 4) != (p->settings.weight_bits == 4) || (settings->host_table != 0) != (p->settings.host_table != 0))
+        return fail(OUT_OF_RANGE, "tb_parked_resume: the weight format and the place of the per-layer table are the parked model's");
+    tb_config cfg = p->cfg;
+    cfg.global = p->global.data();
+    tb_decoder* d = nullptr;
+    TB_TRY(open_decoder(p->ctx, &cfg, settings, p->host_table, &d));
+    p->host_table = nullptr, p->table_bytes = 0;  // the decoder's now
+    for (size_t i = 0; i < d->layers.size(); i++) d->layers[i].layer_scalar = p->scalars[i];
+    // One copy of the weights at the link's speed on a stream of its own, while the step is recorded as tb_decoder_build does
+    // (decode.rs:452-463).  The build's trial pass may read weights that have not arrived: its results are thrown away by
+    // the reset behind it, and the parked copy stays alive and unwritten until both streams are done.
+    cudaStream_t s = d->ctx->stream, cs = nullptr;
+    cudaError_t err = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&d->weights_ready, cudaEventDisableTiming);
+    size_t at = 0;
+    for_each_weight(d, [&](void* ptr, size_t n) {
+        if (err == cudaSuccess) err = cudaMemcpyAsync(ptr, p->weights + at, n, cudaMemcpyHostToDevice, cs);
+        at += (n + 255) / 256 * 256;
+    });
+    if (err == cudaSuccess) err = cudaEventRecord(d->weights_ready, cs);
+    int st = err == cudaSuccess ? OK : cuda_fail(err, "tb_parked_resume");
+    if (st == OK) st = tb_decoder_build(d);
+    if (cs) {
+        const cudaError_t e1 = cudaStreamSynchronize(cs), e2 = cudaStreamSynchronize(s);
+        if (st == OK && (e1 != cudaSuccess || e2 != cudaSuccess)) st = cuda_fail(e1 != cudaSuccess ? e1 : e2, "tb_parked_resume");
+        cudaStreamDestroy(cs);
+    }
+    if (d->weights_ready) cudaEventDestroy(d->weights_ready), d->weights_ready = nullptr;
+    if (st == OK) st = tb_decoder_reset(d);  // whatever the trial pass left behind
+    if (st != OK) {
+        // Back as it was: the table returns to the parked model, which stays usable.
+        p->host_table = d->host_table, p->table_bytes = host_table_bytes(d);
+        d->host_table = nullptr;
+        tb_decoder_close(d);
+        return st;
+    }
+    d->shadow = p->weights, d->shadow_bytes = p->weights_bytes;  // freeing pinned memory costs about as much as the copy (decode.rs:449-451)
+    p->weights = nullptr;
+    tb_parked_close(p);
+    *out = d;
+    return OK;
+}
+
+// The device memory a decoder of this shape takes (Engine's `need`, engine.rs:214): the arena and, where the settings ask for
+// it (2, or automatic with chunks of 256 tokens and more), the prefill copy.  Nothing is allocated.
+int tb_decoder_footprint(tb_context* ctx, const tb_config* cfg, const tb_settings* settings, size_t* bytes) {
+    if (!ctx || !cfg || !settings || !bytes) return fail(OUT_OF_RANGE, "tb_decoder_footprint: null argument");
+    TB_TRY(validate(*cfg, *settings));
+    tb_decoder d;
+    d.ctx = ctx, d.cfg = *cfg, d.settings = *settings;
+    d.fused = settings->fused != 0;
+    d.global.resize(cfg->layers);
+    for (uint32_t i = 0; i < cfg->layers; i++)
+        d.global[i] = cfg->global ? cfg->global[i] : (cfg->global_every ? ((i + 1) % cfg->global_every == 0) : 0);
+    d.cfg.global = nullptr;
+    d.layers.resize(cfg->layers);
+    layout(&d, nullptr);
+    size_t copy = 0;
+    const char* env = getenv("TACHYON_B200_PREFILL_COPY");
+    const uint32_t want = settings->prefill_copy;
+    const bool off = want == 1 || (want == 0 && env != nullptr && env[0] == '0') || settings->chunk == 0 || cfg->hidden % 64 != 0 || cfg->ffn % 64 != 0 ||
+                     (want == 0 && settings->chunk < COPY_MIN_TOKENS);
+    if (!off)
+        for (const Layer& L : d.layers)
+            for (const Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) copy += ((size_t)m->rows * m->cols + 127) / 128 * 128 * 2;
+    *bytes = d.arena_bytes + copy;
     return OK;
 }
 

@@ -1,0 +1,213 @@
+"""The host-RAM tier and the engine's model residency: Decoder::park / Parked::resume (crates/tachyon/src/model/decode.rs:235-247,
+452-463) and Engine's load / tier / expire / unload with its room and evict rules (engine.rs:203-325, 386-453), restating
+crates/tachyon/tests/engine.rs:96-163 on models written as model::convert writes them (weights.wpk, host.wpk)."""
+import time
+
+import numpy as np
+import pytest
+
+import tachyon_b200 as tb
+import wpk_writer as ww
+
+pytestmark = pytest.mark.gpu
+
+PROMPT = [5, 99, 2000, 7, 1234, 42, 77, 3, 900, 11, 12]
+SETTINGS = dict(context=64, chunk=8, weight_bits=4, host_table=True)
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    """A three-layer E-model with per-layer inputs in the reference's Q4: its two files and its configuration."""
+    from oracle.model import OracleModel
+
+    cfg = tb.gemma4_e4b_shape(layers=3, ffn=2048, vocab=2048)
+    cfg.window, cfg.global_every, cfg.per_layer = 16, 3, 256
+    ref = OracleModel(cfg, 41, context=64, chunk=0, weight_bits=4)
+    files = {"weights.wpk": [], "host.wpk": []}
+    for name, a in ref.tensors.items():
+        kind = "u8" if name.endswith(".w") else "f16" if name.endswith(".s") else "f32"
+        a = np.ascontiguousarray(a)
+        files["host.wpk" if name.startswith("embed_per_layer") else "weights.wpk"].append((name, kind, a.shape, a.view(np.uint8).tobytes()))
+    d = tmp_path_factory.mktemp("model")
+    for name, tensors in files.items():
+        ww.write(str(d / name), tensors, crc=ww.fast_crc32c)
+    return cfg, str(d / "weights.wpk"), str(d / "host.wpk")
+
+
+def generate(dec, n=6):
+    dec.reset()
+    dec.prefill(PROMPT[:-1])
+    out = [dec.step(PROMPT[-1])]
+    logits = dec.logits().copy()
+    for _ in range(n - 1):
+        out.append(dec.step(out[-1]))
+    return out, logits
+
+
+def test_a_parked_model_comes_back_with_the_same_answers(ctx, model):
+    cfg, weights, host = model
+    dec = tb.Decoder(ctx, cfg, keep_logits=True, **SETTINGS)
+    dec.load_wpk(weights), dec.load_wpk(host)
+    dec.build()
+    want, want_logits = generate(dec)
+    held, will_hold = dec.bytes(), dec.parked_bytes()
+    assert held == tb.decoder_footprint(ctx, cfg, keep_logits=True, **SETTINGS)
+    assert dec.shadow_bytes() == 0
+    free_before = ctx.memory()[0]
+    parked = dec.park()
+    assert dec.handle is None and parked.bytes() == will_hold
+    assert ctx.memory()[0] >= free_before + held - (2 << 20), "the device memory went back"
+    # other settings on the way back: a longer context, a larger chunk
+    back = parked.resume(context=128, chunk=32)
+    assert parked.handle is None
+    assert 0 < back.shadow_bytes() <= will_hold and back.parked_bytes() == will_hold
+    got, got_logits = generate(back)
+    assert got == want and np.array_equal(got_logits, want_logits)
+    # parked again: the kept copy is the parked model, no copy made; and back once more
+    again = back.park().resume(context=64, chunk=8)
+    got, got_logits = generate(again)
+    assert got == want and np.array_equal(got_logits, want_logits)
+    # a tensor loaded since makes the kept copy stale: it is dropped, and the next parking copies the new weights
+    again.load("1.input_layernorm", np.full(cfg.hidden, 1.5, np.float32))
+    assert again.shadow_bytes() == 0
+    again.build()
+    changed, _ = generate(again)
+    third = again.park().resume()
+    assert generate(third)[0] == changed
+    third.drop_shadow()
+    assert third.shadow_bytes() == 0
+    third.close()
+
+
+def test_a_resume_with_another_format_is_refused_and_the_parked_model_survives(ctx, model):
+    cfg, weights, host = model
+    dec = tb.Decoder(ctx, cfg, keep_logits=True, **SETTINGS)
+    dec.load_wpk(weights), dec.load_wpk(host)
+    dec.build()
+    want, _ = generate(dec)
+    parked = dec.park()
+    import ctypes as C
+
+    st = tb.Settings(context=64, chunk=8, keep_logits=1, fused=0, weight_bits=8, host_table=1, prefill_copy=0)
+    h = C.c_void_p()
+    assert ctx.lib.tb_parked_resume(parked.handle, C.byref(st), C.byref(h)) == 3  # TB_OUT_OF_RANGE
+    assert generate(parked.resume())[0] == want
+
+
+def answer(engine, name, n=6):
+    first = engine.feed(name, PROMPT)
+    dec = engine.decoder(name)
+    out = [first]
+    for _ in range(n - 1):
+        out.append(dec.step(out[-1]))
+    return out
+
+
+def test_models_move_between_tiers_and_answer_the_same(ctx, model):
+    """tests/engine.rs:96-141."""
+    cfg, weights, host = model
+    need = tb.decoder_footprint(ctx, cfg, **SETTINGS)
+    V, H, D = tb.TIER_VRAM, tb.TIER_HOST, tb.TIER_DISK
+    keep = dict(keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    tiers = lambda e, names: [e.tier(n) for n in names]
+    # Room for two: a third moves the least recently used to the host tier, from where it answers the same.
+    e = tb.Engine(ctx, vram_limit=2 * need + need // 2)
+    e.load("a", cfg, weights, host, **keep)
+    e.load("b", cfg, weights, host, **keep)
+    want = answer(e, "a")
+    e.load("c", cfg, weights, host, **keep)
+    assert tiers(e, "abc") == [V, H, V], "b was the least recently used"
+    assert e.usage()[0] == 2 * need and e.usage()[1] > 0
+    assert answer(e, "b") == want, "b back from the host tier"
+    assert tiers(e, "abc") == [H, V, V], "then a was"
+    # A pinned model stays, though the least recently used.
+    e.load("a", cfg, weights, host, pin=True, **keep)
+    answer(e, "b", 1), answer(e, "c", 1)
+    assert tiers(e, "abc") == [V, H, V], "the pinned a stayed"
+    e.load("c", cfg, weights, host, pin=True, **keep)
+    with pytest.raises(tb.Error) as err:
+        e.load("d", cfg, weights, host, **keep)
+    assert err.value.status == 7, "two pinned models leave no room"  # TB_OUT_OF_MEMORY
+    with pytest.raises(tb.Error) as err:
+        e.tier("d")
+    assert err.value.status == 8, "a model that does not fit is not loaded"  # TB_NO_MODEL
+    e.close()
+    # A model whose keep-alive runs out goes to disk, though the host tier has room; and comes back answering the same.
+    e = tb.Engine(ctx)
+    e.load("a", cfg, weights, host, keep_alive_ms=0, **SETTINGS)
+    assert answer(e, "a") == want
+    e.expire()
+    assert e.tier("a") == D, "kept zero"
+    assert answer(e, "a") == want, "a back from disk"
+    e.load("a", cfg, weights, host, keep_alive_ms=50, **SETTINGS)
+    e.load("m", cfg, weights, host, **keep)
+    time.sleep(0.06)
+    e.expire()
+    assert tiers(e, "am") == [D, V], "a's keep-alive ran out; m's never does"
+    assert e.unload("m") and not e.unload("m")
+    with pytest.raises(tb.Error):
+        e.tier("m")
+    e.close()
+
+
+def test_a_parked_model_is_freed_when_its_keep_alive_runs_out(ctx, model):
+    """tests/engine.rs:143-163."""
+    cfg, weights, host = model
+    need = tb.decoder_footprint(ctx, cfg, **SETTINGS)
+    V, H, D = tb.TIER_VRAM, tb.TIER_HOST, tb.TIER_DISK
+    # Room for one: p moves to the host tier for q, then its keep-alive runs out there, freeing its pinned memory.
+    e = tb.Engine(ctx, vram_limit=need + need // 2)
+    e.load("p", cfg, weights, host, keep_alive_ms=50, **SETTINGS)
+    answer(e, "p", 1)
+    e.load("q", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert [e.tier("p"), e.tier("q")] == [H, V], "p made room for q"
+    assert e.usage()[1] > 0
+    time.sleep(0.06)
+    e.expire()
+    assert [e.tier("p"), e.tier("q")] == [D, V], "p's keep-alive ran out on the host tier"
+    listed = e.models()
+    assert [m["name"] for m in listed] == ["p", "q"] and [m["vram"] for m in listed] == [0, need], "only q takes VRAM"
+    assert listed[1]["left_ms"] == tb.FOR_GOOD and e.usage() == (need, 0)
+    e.close()
+
+
+def test_the_host_tier_has_a_limit_too(ctx, model):
+    """Engine::evict (engine.rs:420-441): a model that does not fit the host tier goes to disk; to park one, the least recently used
+    pinned memory gives way: a resident model's kept copy is dropped, a parked model goes to disk."""
+    cfg, weights, host = model
+    need = tb.decoder_footprint(ctx, cfg, **SETTINGS)
+    V, H, D = tb.TIER_VRAM, tb.TIER_HOST, tb.TIER_DISK
+    keep = dict(keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    probe = tb.Decoder(ctx, cfg, **SETTINGS)
+    parked_bytes = probe.parked_bytes()
+    probe.close()
+    # no room on the host: straight to disk
+    e = tb.Engine(ctx, vram_limit=need + need // 2, host_limit=parked_bytes - 1)
+    e.load("a", cfg, weights, host, **keep)
+    want = answer(e, "a")
+    e.load("b", cfg, weights, host, **keep)
+    assert [e.tier("a"), e.tier("b")] == [D, V] and e.usage()[1] == 0
+    assert answer(e, "a") == want and [e.tier("a"), e.tier("b")] == [V, D]
+    e.close()
+    # room for one parked model: the second one parked sends the first to disk
+    e = tb.Engine(ctx, vram_limit=need + need // 2, host_limit=parked_bytes + parked_bytes // 2)
+    for name in "abc":
+        e.load(name, cfg, weights, host, **keep)
+    assert [e.tier(n) for n in "abc"] == [D, H, V], "b was parked last: a went to disk for it"
+    assert e.usage()[1] == parked_bytes
+    assert answer(e, "b") == want and e.usage()[1] == parked_bytes
+    e.close()
+    # a model that came back from the host tier keeps its pinned copy; when the host tier gets tight and that copy is the least
+    # recently used pinned memory, it is dropped rather than a parked model sent to disk
+    e = tb.Engine(ctx, vram_limit=3 * need + need // 2, host_limit=parked_bytes + parked_bytes // 2)
+    for name in "abcd":
+        e.load(name, cfg, weights, host, **keep)
+    assert [e.tier(n) for n in "abcd"] == [H, V, V, V]
+    assert e.unload("d")
+    assert answer(e, "a") == want and e.tier("a") == V
+    assert e.decoder("a").shadow_bytes() > 0 and e.usage()[1] == e.decoder("a").shadow_bytes(), "a keeps the copy it came from"
+    e.load("e", cfg, weights, host, **keep)
+    assert [e.tier(n) for n in "abce"] == [V, H, V, V], "b, the least recently used, made room"
+    assert e.decoder("a").shadow_bytes() == 0 and e.usage()[1] == parked_bytes, "a's kept copy gave way to the parked b"
+    assert answer(e, "b") == want
+    e.close()
