@@ -14,8 +14,9 @@ through tb_decoder_step with the token crossing the host boundary in both direct
 the dominant kernel (the gate/up projection, 16384x2 rows of 2048 int8 weights plus scales) alone over all layers'
 matrices; `cpu_baseline` is the CPU oracle on the same model (reported, not a target).  The metric names prefill
 tokens/s beside decode tokens/s, so the default line also carries `prefill` (configs[3]: a prompt of 2048 tokens), and
-`gemv`, `attend`, `encoder` (configs[0], [1], [4]) as sub-objects with their own rooflines; `--workload X` runs one
-of them alone with more repetitions.
+`gemv`, `attend`, `encoder` (configs[0], [1], [4]) as sub-objects with their own rooflines, and `switch` (the model's
+return from the host-RAM tier, as the reference's benches/switch.rs times it); `--workload X` runs one of them alone
+with more repetitions.
 """
 from __future__ import annotations
 
@@ -779,6 +780,11 @@ def main():
                     sub.steps, sub.warmup = 256, 16
                     line["gemv"] = brief(bench_gemv(sub, ranks))
                     line["attend"] = brief(bench_attend(sub, ranks))
+                    if ranks.world == 1 and args.layers == 35:  # one replica only: pinned host memory for a whole model
+                        sub.steps = 3
+                        sw = bench_switch(sub, ranks)
+                        line["switch"] = {k: sw[k] for k in ("metric", "value", "unit", "resume_s", "first_park_s", "park_with_kept_copy_s", "link_gb_per_second", "fraction_of_link")}
+                        line["switch"]["workload"] = sw["config"]["workload"]
             if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu:
                 line["cpu_baseline"], _ = cpu_decode(cfg, 4, 30.0, gpu_tokens, 4 if args.weights == "q4" else 8)
             elif ranks.rank == 0:
