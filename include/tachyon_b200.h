@@ -81,6 +81,12 @@ TB_API int tb_context_set_dynamic(tb_context* ctx, int on);
  * default), 0 the mma.sync kernel every other shape takes.  An encoder with heads of 64 opened while this is 1 runs its
  * attention on tcgen05 as well (tiles of 128 queries of a sequence and head).  TACHYON_B200_FLASH=0 starts a context at 0. */
 TB_API int tb_context_set_flash(tb_context* ctx, int which);
+/* 1: decoders recorded from now on run the attention half of a layer (norm, q/k/v product, attention, output projection) as one
+ * kernel on two thread-block clusters of 16 blocks, where the layer has the shape for it (hidden 2048, 8 query and 2 key-value
+ * heads of 256, eight-bit matrices, a cache of its own) and the GPU gives it the clusters; same results to rounding.  Off by
+ * default: measured slower than the three launches (the clusters start late and fetch through two GPCs only).
+ * TACHYON_B200_ATTN_BLOCK=1 starts a context with it on. */
+TB_API int tb_context_set_attn_block(tb_context* ctx, int on);
 /* Context::memory (cuda/mod.rs:194-198): free and total device memory, in bytes. */
 TB_API int tb_context_memory(tb_context* ctx, size_t* free_bytes, size_t* total_bytes);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */

@@ -252,6 +252,10 @@ class Context:
         check(self.lib.tb_context_memory(self.handle, C.byref(f), C.byref(t)))
         return f.value, t.value
 
+    def set_attn_block(self, on: bool) -> None:
+        """tb_context_set_attn_block: a layer's attention half as one kernel on clusters of 16 blocks (off by default)."""
+        check(self.lib.tb_context_set_attn_block(self.handle, int(on)))
+
     def set_flash(self, which: int) -> None:
         """tb_context_set_flash: 1 prefill attention on tcgen05 where the shape allows (default), 0 the mma.sync kernel."""
         check(self.lib.tb_context_set_flash(self.handle, which))

@@ -123,6 +123,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->l2_next = env != nullptr ? (uint32_t)atoi(env) : 0u;
     env = getenv("TACHYON_B200_NO_CLUSTER");
     ctx->cluster = !(env != nullptr && env[0] == '1');
+    env = getenv("TACHYON_B200_ATTN_BLOCK");
+    ctx->attn_block = env != nullptr && env[0] == '1';
     env = getenv("TACHYON_B200_FLASH");
     ctx->flash_tc = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_GEMM");
@@ -166,6 +168,13 @@ int tb_context_set_lean(tb_context* ctx, int mode) {
 int tb_context_set_dynamic(tb_context* ctx, int on) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     ctx->dynamic = on != 0;
+    return OK;
+}
+
+int tb_context_set_attn_block(tb_context* ctx, int on) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (on != 0 && on != 1) return fail(OUT_OF_RANGE, "tb_context_set_attn_block: 0 or 1");
+    ctx->attn_block = on != 0;
     return OK;
 }
 

@@ -94,6 +94,8 @@ struct tb_decoder {
     size_t arena_bytes = 0;
     // step buffers
     float *x[2] = {nullptr, nullptr}, *qkv = nullptr, *att = nullptr, *y = nullptr, *g = nullptr, *logits = nullptr, *partial = nullptr;
+    float* y2 = nullptr;  // the output projection's second partial product when a layer's attention half runs as one kernel (attn_block.cu)
+    uint32_t step_count = 0;  // launches of a step, counted when it was last recorded
     float* freq[2] = {nullptr, nullptr};
     float* trig[2] = {nullptr, nullptr};  // cos/sin of every position for the two frequency sets: [context][256]
     uint32_t *count = nullptr, *state = nullptr, *trace = nullptr;
@@ -275,7 +277,7 @@ void layout(tb_decoder* d, char* base) {
         if (L.splits > max_splits) max_splits = L.splits;
     }
     vec(d->x[0], c.hidden), vec(d->x[1], c.hidden);
-    vec(d->qkv, max_nq(c) + 2 * max_nkv(c)), vec(d->att, max_nq(c)), vec(d->y, c.hidden), vec(d->g, c.ffn);
+    vec(d->qkv, max_nq(c) + 2 * max_nkv(c)), vec(d->att, max_nq(c)), vec(d->y, c.hidden), vec(d->y2, c.hidden), vec(d->g, c.ffn);
     vec(d->logits, c.vocab);
     if (pl) vec(d->ple, plw), vec(d->proj, plw), vec(d->pli, plw), vec(d->g2, pl);
     vec(d->work, c.vocab);
@@ -368,59 +370,84 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
     }
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
-        GemvParams q;
-        q.xmode = X_NORM, q.h = d->x[cur], q.w2 = L.input_ln, q.eps = c.eps;
-        if (i > 0) {
-            // The previous layer's closing residual: x = (x + post_ffn_norm(down)) * layer_scalar (decode.rs:631-662).
-            const Layer& P = d->layers[i - 1];
-            q.yres = d->y, q.w1 = pl ? P.post_pl : P.post_ffn, q.hscale = P.layer_scalar, q.h_out = d->x[1 - cur];
-            cur = 1 - cur;
-        }
-        q.epi = EPI_F32, q.y = d->qkv;
-        q.lean = d->ctx->lean_qkv ? 1 : 0;
-        q.pf = hint(d, L.o, 1, 0, PF);  // what follows attention
-        TB_TRY(gemv(d, L.qkv, q));
-
-        AttendParams a;
-        a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0], a.trig = d->trig[L.global ? 1 : 0];
-        a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = L.source < 0 ? 1 : 0;
-        a.heads = c.heads, a.kv_heads = L.kvh, a.scale = c.attn_scale, a.eps = c.eps;
-        a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
-        a.pf = hint(d, L.gate_up, 2, 0, PF);
-        // Heads of 512, or eight query heads to a key-value head: attend512.cu's kernel, which merges its own splits and writes f32 heads.
-        const bool wide = L.dim == 512 || c.heads == 8 * L.kvh;
-        a.defer = wide ? 0 : 1;  // the o projection merges the splits in its prologue
-        // Caches and position are final long before the kernel in front of this one, except in a layer that reads another
-        // layer's cache: that layer wrote the newest row during this very step, and with short products between the two
-        // nothing but the order of the launches says it has finished.  Such a layer fetches nothing ahead of its wait.
-        a.early = (!wide && L.source < 0) ? 1 : 0;
-        a.cluster = wide ? 1 : L.cluster;
-        if (wide) {
-            if (d->collect) return fail(UNSUPPORTED, "fused step: no attention for this layer's heads");
-            TB_TRY(L.dim == 512 ? launch_attend_512(d->ctx, a) : launch_attend_256_shared(d->ctx, a));
-        } else if (d->collect) {
-            StepPhase ph;
-            ph.kind = PH_ATTEND, ph.a = a;
-            d->collect->push_back(ph);
+        // The attention half of the layer as one kernel on two clusters of 16 blocks (attn_block.cu), where the layer has its
+        // shape: hidden 2048, 8 query and 2 key-value heads of 256 with a cache of their own, eight-bit matrices.
+        const bool block = d->ctx->attn_block && !d->collect && !d->fused && c.hidden == 2048 && c.heads == 8 && L.kvh == 2 && L.dim == 256 && L.source < 0 &&
+                           L.qkv.bits == 8 && L.o.bits == 8 && d->trig[L.global ? 1 : 0] != nullptr && attn_block_available(d->ctx);
+        if (block) {
+            AttnBlockParams b;
+            b.h = d->x[cur], b.w2 = L.input_ln, b.eps = c.eps;
+            if (i > 0) {
+                const Layer& P = d->layers[i - 1];
+                b.yres = d->y, b.w1 = pl ? P.post_pl : P.post_ffn, b.hscale = P.layer_scalar, b.h_out = d->x[1 - cur];
+                cur = 1 - cur;
+            }
+            b.wqkv = L.qkv.w, b.sqkv = L.qkv.s, b.q_norm = L.q_norm, b.k_norm = L.k_norm, b.trig = d->trig[L.global ? 1 : 0], b.pos = d->state;
+            b.kc = L.kc, b.vc = L.vc, b.cap = L.cap, b.window = L.window, b.scale = c.attn_scale, b.head_eps = c.eps;
+            b.wo = L.o.w, b.so = L.o.s, b.y[0] = d->y, b.y[1] = d->y2;
+            if (d->stamps) {
+                const char* at = getenv("TACHYON_B200_ATTN_BLOCK_STAMP");
+                b.stamps = d->stamps + 8 * (size_t)d->launches, b.stamp_at = at ? (uint32_t)atoi(at) : 0u;
+            }
+            TB_TRY(launch_attn_block(d->ctx, b));
+            d->launches++;
         } else {
-            if (d->stamps) a.stamps = d->stamps + 8 * (size_t)d->launches;
-            TB_TRY(launch_attend(d->ctx, a));
-        }
-        d->launches++;
+            GemvParams q;
+            q.xmode = X_NORM, q.h = d->x[cur], q.w2 = L.input_ln, q.eps = c.eps;
+            if (i > 0) {
+                // The previous layer's closing residual: x = (x + post_ffn_norm(down)) * layer_scalar (decode.rs:631-662).
+                const Layer& P = d->layers[i - 1];
+                q.yres = d->y, q.w1 = pl ? P.post_pl : P.post_ffn, q.hscale = P.layer_scalar, q.h_out = d->x[1 - cur];
+                cur = 1 - cur;
+            }
+            q.epi = EPI_F32, q.y = d->qkv;
+            q.lean = d->ctx->lean_qkv ? 1 : 0;
+            q.pf = hint(d, L.o, 1, 0, PF);  // what follows attention
+            TB_TRY(gemv(d, L.qkv, q));
 
-        GemvParams o;
-        o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
-        if (!wide) {
-            o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
-            o.att_heads = c.heads, o.att_kv = L.kvh, o.att_cluster = L.cluster;
+            AttendParams a;
+            a.qkv = d->qkv, a.q_norm = L.q_norm, a.k_norm = L.k_norm, a.freq = d->freq[L.global ? 1 : 0], a.trig = d->trig[L.global ? 1 : 0];
+            a.kc = L.kc, a.vc = L.vc, a.pos = d->state, a.cap = L.cap, a.window = L.window, a.fresh = L.source < 0 ? 1 : 0;
+            a.heads = c.heads, a.kv_heads = L.kvh, a.scale = c.attn_scale, a.eps = c.eps;
+            a.partial = d->partial, a.count = d->count, a.splits = L.splits, a.out = d->att, a.out_f16 = 0;
+            a.pf = hint(d, L.gate_up, 2, 0, PF);
+            // Heads of 512, or eight query heads to a key-value head: attend512.cu's kernel, which merges its own splits and writes f32 heads.
+            const bool wide = L.dim == 512 || c.heads == 8 * L.kvh;
+            a.defer = wide ? 0 : 1;  // the o projection merges the splits in its prologue
+            // Caches and position are final long before the kernel in front of this one, except in a layer that reads another
+            // layer's cache: that layer wrote the newest row during this very step, and with short products between the two
+            // nothing but the order of the launches says it has finished.  Such a layer fetches nothing ahead of its wait.
+            a.early = (!wide && L.source < 0) ? 1 : 0;
+            a.cluster = wide ? 1 : L.cluster;
+            if (wide) {
+                if (d->collect) return fail(UNSUPPORTED, "fused step: no attention for this layer's heads");
+                TB_TRY(L.dim == 512 ? launch_attend_512(d->ctx, a) : launch_attend_256_shared(d->ctx, a));
+            } else if (d->collect) {
+                StepPhase ph;
+                ph.kind = PH_ATTEND, ph.a = a;
+                d->collect->push_back(ph);
+            } else {
+                if (d->stamps) a.stamps = d->stamps + 8 * (size_t)d->launches;
+                TB_TRY(launch_attend(d->ctx, a));
+            }
+            d->launches++;
+
+            GemvParams o;
+            o.xmode = X_F32, o.x = d->att, o.epi = EPI_F32, o.y = d->y;
+            if (!wide) {
+                o.xmode = X_ATTN, o.att_partial = d->partial, o.att_pos = d->state, o.att_splits = L.splits, o.att_window = L.window;
+                o.att_heads = c.heads, o.att_kv = L.kvh, o.att_cluster = L.cluster;
+            }
+            o.lean = 1;  // short: the small kernel, which fits beside the gate/up product's block, so that block fills its ring meanwhile
+            if (!wide && L.cluster == L.splits) o.att_entries = 1;  // one cluster covers the window: always one entry
+            o.pf = hint(d, L.gate_up, 2, PF, PF);
+            TB_TRY(gemv(d, L.o, o));
+
         }
-        o.lean = 1;  // short: the small kernel, which fits beside the gate/up product's block, so that block fills its ring meanwhile
-        if (!wide && L.cluster == L.splits) o.att_entries = 1;  // one cluster covers the window: always one entry
-        o.pf = hint(d, L.gate_up, 2, PF, PF);
-        TB_TRY(gemv(d, L.o, o));
 
         GemvParams gu;
         gu.xmode = X_NORM, gu.h = d->x[cur], gu.yres = d->y, gu.w1 = L.post_attn, gu.hscale = 1.0f, gu.w2 = L.pre_ffn, gu.eps = c.eps;
+        if (block) gu.yres2 = d->y2;  // the output projection came as two partial products
         gu.h_out = d->x[1 - cur];
         cur = 1 - cur;
         gu.epi = EPI_GEGLU, gu.y = d->g;
@@ -473,6 +500,7 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         TB_TRY(gemv(d, d->embed, h));
     }
     d->final_x = 1 - cur;
+    if (!d->capture_sampled) d->step_count = d->launches;  // the graphs that end in the sampler have one launch more
     return OK;
 }
 
@@ -1080,14 +1108,14 @@ int tb_decoder_step_bytes(tb_decoder* d, uint64_t* weight_bytes, uint64_t* cache
 
 int tb_decoder_step_launches(tb_decoder* d, uint32_t* launches) {
     if (!d || !launches) return fail(OUT_OF_RANGE, "null argument");
-    *launches = d->fused ? 1 : 2 + 5 * d->cfg.layers;
+    *launches = d->fused ? 1 : (d->step_count ? d->step_count : 2 + 5 * d->cfg.layers);
     return OK;
 }
 
 int tb_decoder_timeline(tb_decoder* d, uint32_t token, uint64_t* host_out, uint32_t* phases) {
     TB_TRY(ready(d, 1));
     if (d->running) return fail(OUT_OF_RANGE, "tb_decoder_timeline: a generation is running; stop it first");
-    const uint32_t count = d->fused ? d->phase_count : 2 + 5 * d->cfg.layers;
+    const uint32_t count = d->fused ? d->phase_count : (d->step_count ? d->step_count : 2 + 5 * d->cfg.layers);
     if (phases) *phases = count;
     if (!host_out) return OK;
     const size_t bytes = (size_t)2 * count * 4 * sizeof(unsigned long long);

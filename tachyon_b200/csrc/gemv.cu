@@ -168,7 +168,11 @@ __device__ __forceinline__ void build_planes(const GemvParams& p, uint8_t* raw, 
         float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float sy = 0.0f;
         if (p.yres != nullptr) {
-            const float4 y = ld_cg_f4(p.yres + at);
+            float4 y = ld_cg_f4(p.yres + at);
+            if (p.yres2 != nullptr) {
+                const float4 y2 = ld_cg_f4(p.yres2 + at);
+                y.x += y2.x, y.y += y2.y, y.z += y2.z, y.w += y2.w;
+            }
             const float4 w = nw1;
             a = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
             sy = y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
@@ -608,7 +612,12 @@ __global__ void __launch_bounds__(SMALL_THREADS, 3) gemv_small_kernel(const Gemv
             h[k] = ld_cg_f4(p.h + at);
             a[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (p.yres != nullptr) {
-                const float4 y = ld_cg_f4(p.yres + at), w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
+                float4 y = ld_cg_f4(p.yres + at);
+                if (p.yres2 != nullptr) {
+                    const float4 y2 = ld_cg_f4(p.yres2 + at);
+                    y.x += y2.x, y.y += y2.y, y.z += y2.z, y.w += y2.w;
+                }
+                const float4 w = __ldg(reinterpret_cast<const float4*>(p.w1 + at));
                 a[k] = make_float4(y.x * w.x, y.y * w.y, y.z * w.z, y.w * w.w);
                 sy += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
             }

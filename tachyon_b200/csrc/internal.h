@@ -27,6 +27,7 @@ struct tb_context {
     bool cluster = true;              // decode attention merges neighbouring splits in thread-block clusters (TACHYON_B200_NO_CLUSTER=1: never)
     uint32_t* sched = nullptr;        // device: 64 pairs of words (next stage, finished blocks) for such products launched outside a decoder
     uint32_t sched_at = 0;            // which pair the next launch takes
+    bool attn_block = false;          // a decode layer's attention half as one kernel on clusters of 16 blocks where the layer has its shape (attn_block.cu: measured slower, so off); TACHYON_B200_ATTN_BLOCK=1, tb_context_set_attn_block
     bool flash_tc = true;             // prefill attention on tcgen05 where the shape allows (prefill_tc.cu); TACHYON_B200_FLASH=0, tb_context_set_flash
     int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
 };
@@ -88,6 +89,7 @@ struct GemvParams {
     // X_NORM: x = w2 * rmsnorm(h'), h' = (h + w1 * rmsnorm(y)) * hscale (y may be null: h' = h; w2 may be null: x = h')
     const float* h = nullptr;
     const float* yres = nullptr;
+    const float* yres2 = nullptr;  // X_NORM: a second partial product added to yres before anything else (attn_block.cu leaves two)
     const float* w1 = nullptr;
     const float* w2 = nullptr;
     float eps = 1e-6f, hscale = 1.0f;
@@ -187,6 +189,35 @@ size_t attend_partial_floats(uint32_t heads, uint32_t kv_heads, uint32_t splits)
 int launch_attend_512(tb_context* ctx, const AttendParams& p);  // heads of 512; up to 8 query heads per key-value head (attend512.cu)
 int launch_attend_256_shared(tb_context* ctx, const AttendParams& p);  // heads of 256, the same simple kernel: 8 query heads per key-value head
 int launch_attend_static(tb_context* ctx, AttendParams p);  // scratch inside the library; see attend.cu
+
+// ---- the attention half of a decode layer as one kernel (attn_block.cu) ---------------------------------------
+struct AttnBlockParams {
+    // the residual step and RMS-norm in front of the product: GemvParams' X_NORM fields
+    const float* h = nullptr;
+    const float* yres = nullptr;   // or null: no residual step (the first layer)
+    const float* w1 = nullptr;
+    const float* w2 = nullptr;
+    float hscale = 1.0f, eps = 1e-6f;
+    float* h_out = nullptr;        // or null
+    const int8_t* wqkv = nullptr;  // [3072][2048] codes: 8 query heads, 2 key heads, 2 value heads of 256
+    const __half* sqkv = nullptr;  // [3072][64]
+    const float* q_norm = nullptr; // [256]
+    const float* k_norm = nullptr;
+    const float* trig = nullptr;   // [positions][256]: cosines then sines (launch_rope_table)
+    const uint32_t* pos = nullptr;
+    __half* kc = nullptr;          // [2][cap][256]
+    __half* vc = nullptr;
+    uint32_t cap = 0, window = 0;
+    float scale = 1.0f, head_eps = 1e-6f;
+    const int8_t* wo = nullptr;    // [2048][2048]
+    const __half* so = nullptr;    // [2048][64]
+    float* y[2] = {nullptr, nullptr};  // f32 [2048] each: the output projection's partial products over the two groups' columns
+    unsigned long long* stamps = nullptr;  // optional timeline, as in GemvParams
+    uint32_t stamp_at = 0;         // what the third stamp marks: 0 the planes ready, 1 phase A done, 2 attention done, 3 the merge done
+};
+// Whether this GPU runs the kernel's two clusters of 16 blocks.
+bool attn_block_available(tb_context* ctx);
+int launch_attn_block(tb_context* ctx, const AttnBlockParams& p);
 
 // ---- fused decode step ---------------------------------------------------------------------------------------
 struct EmbedParams {

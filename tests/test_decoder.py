@@ -176,6 +176,44 @@ def test_overlap_off_gives_the_same_bits(ctx, models):
         ctx.set_overlap(True)
 
 
+def test_the_attention_half_of_a_layer_as_one_kernel(ctx, models):
+    """tb_context_set_attn_block: norm, q/k/v product, attention and output projection of a layer in one kernel on two clusters of
+    16 blocks (attn_block.cu).  The same arithmetic up to the order of the sums (the output projection comes as two partial
+    products, the window is cut into 16 runs), so it is held to the three launches, which the tests above hold to the CPU
+    forward: through a ring wrap, and behind a chunked prefill."""
+    cfg, dec, ref = models
+    ctx.set_attn_block(True)
+    try:
+        one = tb.Decoder(ctx, cfg, context=64, chunk=8, keep_logits=True)
+        one.fill_random(SEED)
+        one.build()
+    finally:
+        ctx.set_attn_block(False)
+    if one.step_launches != 2 + 3 * cfg.layers:
+        one.close()
+        pytest.skip("this GPU does not give the kernel its two clusters of 16 blocks")
+    assert dec.step_launches == 2 + 5 * cfg.layers
+    dec.reset()
+    for pos in range(40):
+        token = (pos * 7919 + 13) % cfg.vocab
+        assert one.step(token) == dec.step(token)
+        a, b = one.logits(), dec.logits()
+        assert np.abs(a - b).max() <= 1e-4 * np.abs(b).max()
+    # a prompt through prefill, then steps: the caches the chunked path wrote are the ones this kernel reads
+    prompt = [(i * 104729 + 7) % cfg.vocab for i in range(21)]
+    outs = []
+    for d in (one, dec):
+        d.reset()
+        d.prefill(prompt[:-1])
+        t = d.step(prompt[-1])
+        seq = [t]
+        for _ in range(5):
+            seq.append(d.step(seq[-1]))
+        outs.append((seq, d.logits()))
+    assert outs[0][0] == outs[1][0] and np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4 * np.abs(outs[1][1]).max()
+    one.close()
+
+
 def test_fused_step_equals_one_launch_per_phase(ctx, models):
     """The persistent step kernel runs the same arithmetic as the 2 + 5*layers separate kernels."""
     cfg, dec, ref = models
