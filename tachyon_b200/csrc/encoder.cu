@@ -297,11 +297,30 @@ __global__ void __launch_bounds__(128) enc_attend_kernel(const __half* qkv, cons
     }
 }
 
-// ---- pooling: one block per sequence ---------------------------------------------------------------------------------------
+// ---- pooling ------------------------------------------------------------------------------------------------------------------
 // The sequence's vector (first token, or the mean over its tokens) L2-normalised (max(len, 1e-12), as
 // encoder/run.rs:160-173), truncated to `dims` and normalised again when truncated (encoder/text.rs:56-63).
-__global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, const uint32_t* starts, const uint32_t* lens, uint32_t h, uint32_t dims, int mean,
-                                                       float* out) {
+// The mean's sums come in POOL_PARTS parts (a block a part of a sequence's tokens: one block a sequence left most of the
+// machine idle over 50 MB of hidden states), which the sequence's block then adds in a fixed order.
+constexpr uint32_t POOL_PARTS = 8;
+
+__global__ void __launch_bounds__(256) enc_pool_part_kernel(const float* hidden, const uint32_t* starts, const uint32_t* lens, uint32_t h, float* part) {
+    const uint32_t s = blockIdx.x, k = blockIdx.y, start = starts[s], len = lens[s];
+    const uint32_t per = (len + POOL_PARTS - 1) / POOL_PARTS, t0 = min(len, k * per), t1 = min(len, t0 + per);
+    for (uint32_t i = threadIdx.x; i < h; i += 256) {
+        // Four running sums, so that several loads are in flight instead of one.
+        const float* col = hidden + (size_t)start * h + i;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        uint32_t t = t0;
+#pragma unroll 2
+        for (; t + 4 <= t1; t += 4) a0 += col[(size_t)t * h], a1 += col[(size_t)(t + 1) * h], a2 += col[(size_t)(t + 2) * h], a3 += col[(size_t)(t + 3) * h];
+        for (; t < t1; t++) a0 += col[(size_t)t * h];
+        part[((size_t)s * POOL_PARTS + k) * h + i] = (a0 + a1) + (a2 + a3);
+    }
+}
+
+__global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, const float* part, const uint32_t* starts, const uint32_t* lens, uint32_t h, uint32_t dims,
+                                                       int mean, float* out) {
     __shared__ float sh[8];
     __shared__ float vec[2048];
     const uint32_t s = blockIdx.x, start = starts[s], len = lens[s];
@@ -320,14 +339,10 @@ __global__ void __launch_bounds__(256) enc_pool_kernel(const float* hidden, cons
     for (uint32_t i = tid; i < h; i += 256) {
         float v = 0.0f;
         if (mean) {
-            // Four running sums, so that several loads are in flight instead of one.
-            const float* col = hidden + (size_t)start * h + i;
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-            uint32_t t = 0;
-#pragma unroll 2
-            for (; t + 4 <= len; t += 4) a0 += col[(size_t)t * h], a1 += col[(size_t)(t + 1) * h], a2 += col[(size_t)(t + 2) * h], a3 += col[(size_t)(t + 3) * h];
-            for (; t < len; t++) a0 += col[(size_t)t * h];
-            v = ((a0 + a1) + (a2 + a3)) / (float)len;
+            const float* p = part + (size_t)s * POOL_PARTS * h + i;
+#pragma unroll
+            for (uint32_t k = 0; k < POOL_PARTS; k++) v += p[(size_t)k * h];
+            v /= (float)len;
         } else {
             v = hidden[(size_t)start * h + i];
         }
@@ -402,7 +417,7 @@ struct tb_encoder {
     __half* embed = nullptr;
     float *embed_norm = nullptr, *final_norm = nullptr;
     float2* rope[2] = {nullptr, nullptr};  // cosines and sines [positions, d/2]: global layers', sliding layers'
-    float *x = nullptr, *hidden = nullptr, *pooled = nullptr;
+    float *x = nullptr, *hidden = nullptr, *pooled = nullptr, *pool_part = nullptr;  // pool_part: [sequences][POOL_PARTS][hidden] partial sums of the mean
     __half *a16 = nullptr, *qkv16 = nullptr, *att16 = nullptr, *g16 = nullptr;
     // A batch's inputs, one block on the device and its twin in pinned host memory: ids, positions, tiles, first rows, lengths.
     uint32_t *inputs = nullptr, *stage = nullptr;
@@ -448,6 +463,7 @@ size_t enc_layout(tb_encoder* e, char* base) {
     e->x = reinterpret_cast<float*>(take((size_t)T * h * 4));
     e->hidden = reinterpret_cast<float*>(take((size_t)T * h * 4));
     e->pooled = reinterpret_cast<float*>(take((size_t)S * h * 4));
+    e->pool_part = reinterpret_cast<float*>(take((size_t)S * POOL_PARTS * h * 4));
     e->a16 = reinterpret_cast<__half*>(take((size_t)T * h * 2));
     e->qkv16 = reinterpret_cast<__half*>(take((size_t)T * 3 * h * 2));
     e->att16 = reinterpret_cast<__half*>(take((size_t)T * h * 2));
@@ -546,7 +562,8 @@ int enc_layers(tb_encoder* e, uint32_t n, uint32_t slots, uint32_t sequences) {
         TB_TRY(enc_product(e, L.down, e->g16, n, e->x, 3));
     }
     launch_enc_norm(s, n, e->x, nullptr, nullptr, e->final_norm, h, c.eps, e->hidden, nullptr);
-    enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
+    if (c.mean_pool) enc_pool_part_kernel<<<dim3(sequences, POOL_PARTS), 256, 0, s>>>(e->hidden, e->starts, e->lens, h, e->pool_part);
+    enc_pool_kernel<<<sequences, 256, 0, s>>>(e->hidden, e->pool_part, e->starts, e->lens, h, c.dims, c.mean_pool ? 1 : 0, e->pooled);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
