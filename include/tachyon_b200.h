@@ -236,6 +236,11 @@ TB_API int tb_gemv_q4x(tb_context* ctx, const uint8_t* packed, const uint16_t* s
 /* Stand-alone residual / RMS-norm step (norm_q8 without its Q8 output, ptx/mod.rs:404-511). All device f32 [n]. */
 TB_API int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1, const float* w2, uint32_t n, float eps, float hscale, float* h_out,
             float* x_out);
+/* The same step for a chunk of prefill (norm_q8p's place, ptx/mod.rs:217-249, model/prefill.rs:144-196), a warp a token:
+ * h [tokens, n] f32 is updated in place to (h + w1 * rmsnorm(y)) * hscale (y null: h stays), x [tokens, n] f16 receives
+ * w2 * rmsnorm(h') (w2 null: h' itself), the next product's operand.  n = 2048. */
+TB_API int tb_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
+                           uint16_t* x);
 
 /* Row *token of a Q8 table times `scale` as f32 [cols]: embed_q4 (ptx/mod.rs:531-598). token: device word. */
 TB_API int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint32_t* token, uint32_t cols, float scale, float* out);

@@ -107,6 +107,7 @@ SIGNATURES = {
     "tb_dequant_f16": (i32, [vp, vp, vp, u32, u32, u32, vp]),
     "tb_gemm_q4": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, i32]),
     "tb_norm": (i32, [vp, vp, vp, vp, vp, u32, f32, f32, vp, vp]),
+    "tb_prefill_norm": (i32, [vp, vp, vp, vp, vp, u32, u32, f32, f32, vp]),
     "tb_embed_q8": (i32, [vp, vp, vp, vp, u32, f32, vp]),
     "tb_prefill_attend": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32]),
     "tb_prefill_qkv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, u32]),

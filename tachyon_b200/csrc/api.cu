@@ -645,6 +645,12 @@ int tb_norm(tb_context* ctx, const float* h, const float* y_res, const float* w1
     return launch_norm(ctx, h, y_res, w1, w2, n, eps, hscale, h_out, x_out);
 }
 
+int tb_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale, uint16_t* x) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (!h || !x || tokens == 0 || (y != nullptr && w1 == nullptr)) return fail(OUT_OF_RANGE, "tb_prefill_norm: null or empty argument");
+    return launch_prefill_norm(ctx, h, y, w1, w2, tokens, n, eps, hscale, reinterpret_cast<__half*>(x));
+}
+
 int tb_embed_q8(tb_context* ctx, const int8_t* w, const uint16_t* scales, const uint32_t* token, uint32_t cols, float scale, float* out) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     return launch_embed_q8(ctx, w, reinterpret_cast<const __half*>(scales), token, cols, scale, out);
