@@ -64,7 +64,8 @@ TB_API int tb_context_sms(const tb_context* ctx);
 /* Turns programmatic dependent launch on (default) or off for kernels launched after the call. */
 TB_API int tb_context_set_overlap(tb_context* ctx, int on);
 /* Which schedule tb_gemm_q8 / tb_gemm_q4 use from now on: 0 picks by shape and epilogue (default), 1 one tile per block,
- * 2 persistent blocks, 3 and 4 pairs of SMs with tiles of 256 and 128 weight rows.  The environment variable
+ * 2 persistent blocks, 3 and 4 pairs of SMs with tiles of 256 and 128 weight rows, 5 the first's tile with one block an SM walking
+ * the tiles (f16 weights; automatic takes it when there are more tiles than SMs).  The environment variable
  * TACHYON_B200_GEMM gives the value a new context starts with.  (The reference races its tile shapes per product,
  * crates/tachyon/src/encoder/race.rs:56-88; this is the knob such a race turns.) */
 TB_API int tb_context_set_gemm_schedule(tb_context* ctx, int which);

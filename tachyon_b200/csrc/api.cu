@@ -125,6 +125,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->cluster = !(env != nullptr && env[0] == '1');
     env = getenv("TACHYON_B200_ATTN_BLOCK");
     ctx->attn_block = env != nullptr && env[0] == '1';
+    env = getenv("TACHYON_B200_GEMM_WALK");
+    ctx->gemm_walk = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_FLASH");
     ctx->flash_tc = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_GEMM");
@@ -153,7 +155,7 @@ int tb_context_set_overlap(tb_context* ctx, int on) {
 
 int tb_context_set_gemm_schedule(tb_context* ctx, int which) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
-    if (which < 0 || which > 4) return fail(OUT_OF_RANGE, "tb_context_set_gemm_schedule: 0 (automatic) or 1..4");
+    if (which < 0 || which > 5) return fail(OUT_OF_RANGE, "tb_context_set_gemm_schedule: 0 (automatic) or 1..5");
     ctx->gemm_schedule = which;
     return OK;
 }

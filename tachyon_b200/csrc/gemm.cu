@@ -115,6 +115,78 @@ struct GemmArgs {
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + exp2f(-1.4426950408889634f * v)); }
 
+// The epilogue of one tile: the accumulator's rows are tokens, its columns weight rows; warp `warp` (2 .. 2 + DW) reads the lanes of
+// its quarter, 32 columns at a time, adds the bias, applies the mode and stores.  (m0, n0): the tile's first token and weight row.
+template <int MT>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint32_t tmem, int warp, int lane, uint32_t m0, uint32_t n0, bool ok) {
+    // Two warps share each quarter of the accumulator's lanes and take alternate column blocks.
+    const uint32_t q = warp & 3, rrow = 32 * q + lane;
+#pragma unroll 1
+    for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += DW / 4) {
+        const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
+        const uint32_t m = m0 + mt * BM + rrow;
+        uint32_t r[32];
+        tmem_load32(tmem + ((32 * q) << 16) + mt * BN + cb * 32, r);
+        if (m < g.M && ok) {
+            const uint32_t col = n0 + cb * 32;
+            if (g.bias != nullptr && col < g.N) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col) + i);
+                    r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + b.x), r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + b.y);
+                    r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + b.z), r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + b.w);
+                }
+            }
+            if (g.mode == 3) {
+                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    if (col + 4 * i < g.N) {
+                        float4 t = dst[i];
+                        t.x += __uint_as_float(r[4 * i]), t.y += __uint_as_float(r[4 * i + 1]), t.z += __uint_as_float(r[4 * i + 2]), t.w += __uint_as_float(r[4 * i + 3]);
+                        dst[i] = t;
+                    }
+            } else if (g.mode == 0) {
+                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            } else if (g.mode == 1 || g.mode == 5 || g.mode == 7) {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    uint32_t h[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
+                        if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                        if (g.mode == 7) f0 = fmaxf(f0, 0.0f), f1 = fmaxf(f1, 0.0f);
+                        const __half2 t = __floats2half2_rn(f0, f1);
+                        h[e] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                    if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+            } else {
+                // columns (2j, 2j+1) are (gate_j, up_j): gelu_tanh(gate) * up, 16 results per 32 columns
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * (g.N / 2) + col / 2);
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    uint32_t h[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
+                        const float a0 = (g.mode == 2 ? gelu_tanh(g0) : g.mode == 8 ? silu(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                        const float a1 = (g.mode == 2 ? gelu_tanh(g1) : g.mode == 8 ? silu(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                        const __half2 t = __floats2half2_rn(a0, a1);
+                        h[e] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                    if (col + 16 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+            }
+        }
+    }
+}
+
 // MT: 128-row sub-tiles of activations a block multiplies with each dequantised weight tile (1 or 2): with two, the
 // dequantisation is shared by twice the tensor-core work.
 // WB: bits per weight, 8 (codes, an f16 scale per 32), 4 (the reference's Q4, a scale per 64 = one per row and K tile) or 16
@@ -281,71 +353,112 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
             ok = false;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // Two warps share each quarter of the accumulator's lanes and take alternate column blocks.
-        const uint32_t q = warp & 3, rrow = 32 * q + lane;
-#pragma unroll 1
-        for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += DW / 4) {
-            const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
-            const uint32_t m = m0 + mt * BM + rrow;
-            uint32_t r[32];
-            tmem_load32(tmem + ((32 * q) << 16) + mt * BN + cb * 32, r);
-            if (m < g.M && ok) {
-                const uint32_t col = n0 + cb * 32;
-                if (g.bias != nullptr && col < g.N) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col) + i);
-                        r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + b.x), r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + b.y);
-                        r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + b.z), r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + b.w);
+        epilogue_tile<MT>(g, tmem, warp, lane, m0, n0, ok);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(MT * BN)) : "memory");
+}
+
+// The same product for f16 weights as a persistent kernel: a block walks the output tiles t = blockIdx.x, + gridDim.x, ...
+// (token tile t % tiles_m, weight tile t / tiles_m, so that blocks running together share weight tiles in the L2).  The
+// accumulator fills all of tensor memory (MT x 256 columns), so a tile's epilogue cannot overlap the next tile's products; what
+// the loop buys is that the copies of the next tile's first stages are under way during the epilogue (the ring is free
+// then), and that tensor memory, barriers and descriptors are set up once a block instead of once a tile.
+template <int MT>
+__global__ void __launch_bounds__(THREADS, 1) gemm_f16_persistent_tile_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                                                                              const GemmArgs g, uint32_t* status) {
+    constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
+    extern __shared__ uint8_t raw_unaligned[];
+    uint8_t* raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_unaligned) + 1023) & ~uintptr_t(1023));
+    uint8_t* As = raw;
+    uint8_t* Bs = raw + STAGES * AS;
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + STAGES * (AS + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nk = g.K / BK, tiles_m = (g.M + MT * BM - 1) / (MT * BM), tiles = tiles_m * ((g.N + BN - 1) / BN);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
+        mbar_init(acc_full, 1), mbar_init(acc_empty, DW);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)(MT * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+                const uint32_t m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
+                for (uint32_t kt = 0; kt < nk; kt++, it++) {
+                    const uint32_t s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
+                        atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                        t = tiles;
+                        break;
                     }
-                }
-                if (g.mode == 3) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
-#pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        if (col + 4 * i < g.N) {
-                            float4 t = dst[i];
-                            t.x += __uint_as_float(r[4 * i]), t.y += __uint_as_float(r[4 * i + 1]), t.z += __uint_as_float(r[4 * i + 2]), t.w += __uint_as_float(r[4 * i + 3]);
-                            dst[i] = t;
-                        }
-                } else if (g.mode == 0) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + (size_t)m * g.N + col);
-#pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        if (col + 4 * i < g.N) dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                } else if (g.mode == 1 || g.mode == 5 || g.mode == 7) {
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * g.N + col);
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
-                            if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
-                            if (g.mode == 7) f0 = fmaxf(f0, 0.0f), f1 = fmaxf(f1, 0.0f);
-                            const __half2 t = __floats2half2_rn(f0, f1);
-                            h[e] = *reinterpret_cast<const uint32_t*>(&t);
-                        }
-                        if (col + 8 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
-                    }
-                } else {
-                    // columns (2j, 2j+1) are (gate_j, up_j): gelu_tanh(gate) * up, 16 results per 32 columns
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(g.out) + (size_t)m * (g.N / 2) + col / 2);
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
-                            const float a0 = (g.mode == 2 ? gelu_tanh(g0) : g.mode == 8 ? silu(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
-                            const float a1 = (g.mode == 2 ? gelu_tanh(g1) : g.mode == 8 ? silu(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
-                            const __half2 t = __floats2half2_rn(a0, a1);
-                            h[e] = *reinterpret_cast<const uint32_t*>(&t);
-                        }
-                        if (col + 16 * i < g.N) dst[i] = make_uint4(h[0], h[1], h[2], h[3]);
-                    }
+                    mbar_expect_tx(&full[s], AS + B_BYTES);
+                    tma_load_2d(As + s * AS, &a_map, (int)(kt * BK), (int)m0, &full[s]);
+                    tma_load_2d(Bs + s * B_BYTES, &w_map, (int)(kt * BK), (int)n0, &full[s]);
                 }
             }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, ti = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ti++) {
+                // the epilogue of the tile before has read the accumulator
+                if (ti > 0 && !mbar_wait(acc_empty, (ti - 1) & 1)) {
+                    atomicCAS(status, ERR_NONE, ERR_WAIT_EMPTY);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (uint32_t kt = 0; kt < nk; kt++, it++) {
+                    const uint32_t s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+                        atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a = smem_addr(As + s * AS), b = smem_addr(Bs + s * B_BYTES);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                        for (int k = 0; k < BK / 16; k++)
+                            mma_f16(tmem + mt * BN, smem_desc(a + mt * A_BYTES + k * 32), smem_desc(b + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&empty[s]);
+                }
+                mma_commit(acc_full);  // arrives when the tile's products have finished (also after an early exit)
+            }
+        }
+    } else {
+        uint32_t ti = 0;
+        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ti++) {
+            const uint32_t m0 = (t % tiles_m) * (MT * BM), n0 = (t / tiles_m) * BN;
+            bool ok = true;
+            if (!mbar_wait(acc_full, ti & 1)) {
+                atomicCAS(status, ERR_NONE, ERR_WAIT_FULL);
+                ok = false;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            epilogue_tile<MT>(g, tmem, warp, lane, m0, n0, ok);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
+            if (!ok) break;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -461,6 +574,8 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<1, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
+        TB_CUDA(cudaFuncSetAttribute(gemm_f16_persistent_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
+        TB_CUDA(cudaFuncSetAttribute(gemm_f16_persistent_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
     CUtensorMap wmap = map;  // f16 weights: [N, K] in tiles of 256 rows x 64 halves; unused otherwise
@@ -473,7 +588,12 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     }
     GemmArgs g{w, s, out, M, N, K, mode, bias};
     const dim3 grid((M + mt * BM - 1) / (mt * BM), (N + BN - 1) / BN);
-    if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    // f16 weights and more tiles than SMs: one block an SM walks the tiles (schedule 5 asks for the walk whatever the count).
+    const uint32_t tiles = grid.x * grid.y, walkers = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
+    const bool walk = wbits == 16 && ((ctx->gemm_walk && tiles > (uint32_t)ctx->sms) || ctx->gemm_schedule == 5);
+    if (walk && mt == 2) gemm_f16_persistent_tile_kernel<2><<<walkers, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (walk) gemm_f16_persistent_tile_kernel<1><<<walkers, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);

@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(128, 128, 64), (128, 128, 256), (1, 128, 2048), (37, 256, 2048), (300, 3072, 2048), (512, 2048, 2048), (129, 2048, 16384), (256, 96, 128)]
 
 
-SCHEDULES = {"one tile per block": "1", "persistent": "2", "pairs of SMs, tiles of 256 weight rows": "3", "pairs of SMs, tiles of 128 weight rows": "4"}
+SCHEDULES = {"one tile per block": "1", "persistent": "2", "pairs of SMs, tiles of 256 weight rows": "3", "pairs of SMs, tiles of 128 weight rows": "4",
+             "one tile at a time, blocks walking the tiles (f16 weights; as the first otherwise)": "5"}
 
 
 @pytest.fixture(params=list(SCHEDULES))
