@@ -211,3 +211,30 @@ def test_the_host_tier_has_a_limit_too(ctx, model):
     assert e.decoder("a").shadow_bytes() == 0 and e.usage()[1] == parked_bytes, "a's kept copy gave way to the parked b"
     assert answer(e, "b") == want
     e.close()
+
+
+def test_the_engine_refuses_what_it_cannot_load_and_stays_as_it_was(ctx, model, tmp_path):
+    cfg, weights, host = model
+    e = tb.Engine(ctx)
+    with pytest.raises(tb.Error) as err:  # no such file: nothing is loaded under that name
+        e.load("ghost", cfg, str(tmp_path / "nothing.wpk"), None, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert err.value.status == 11  # TB_IO
+    with pytest.raises(tb.Error) as err:
+        e.tier("ghost")
+    assert err.value.status == 8 and e.models() == [] and e.usage() == (0, 0)
+    with pytest.raises(tb.Error) as err:  # a model smaller than the file's tensors: the loader's own refusal comes through
+        small = tb.gemma4_e4b_shape(layers=2, ffn=2048, vocab=2048)
+        small.window, small.global_every, small.per_layer = 16, 2, 256
+        e.load("small", small, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert err.value.status in (5, 8)  # TB_FORMAT or TB_NO_MODEL, by which tensor it meets first
+    e.load("a", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    with pytest.raises(tb.Error) as err:
+        e.feed("a", [])
+    assert err.value.status == 3
+    with pytest.raises(tb.Error) as err:
+        e.feed("nobody", PROMPT)
+    assert err.value.status == 8
+    want = answer(e, "a")
+    e.load("a", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)  # loading a name again replaces the model
+    assert [m["name"] for m in e.models()] == ["a"] and answer(e, "a") == want
+    e.close()
