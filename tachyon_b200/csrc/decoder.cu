@@ -114,6 +114,10 @@ struct tb_decoder {
     float* sample_partial = nullptr;
     uint32_t* sample_count = nullptr;
     cudaEvent_t done[2] = {nullptr, nullptr};
+    // ctx->l2_side: a second stream on which a small kernel asks the L2 for a layer's down projection while the layer's short
+    // kernels run (HBM has nothing else to do then); forked from and joined to the step's stream inside the recorded graph.
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
     int at = 0;
     bool running = false, built = false;
     uint32_t pos = 0;  // host mirror of the position
@@ -325,6 +329,29 @@ Prefetch hint(tb_decoder* d, const Mat& m, uint32_t unit, uint32_t skip, uint32_
     return pf;
 }
 
+// Asks the L2 for two byte ranges, a thread a piece of 16 KiB (a bulk prefetch: no destination, nothing waits for it).
+__global__ void __launch_bounds__(128) l2_prefetch_kernel(const char* a, size_t an, const char* b, size_t bn) {
+    constexpr size_t PIECE = 16384;
+    const size_t i = (size_t)blockIdx.x * 128 + threadIdx.x, na = (an + PIECE - 1) / PIECE, nb = (bn + PIECE - 1) / PIECE;
+    if (i < na) bulk_prefetch_l2(a + i * PIECE, (uint32_t)(an - i * PIECE < PIECE ? an - i * PIECE : PIECE));
+    else if (i - na < nb) bulk_prefetch_l2(b + (i - na) * PIECE, (uint32_t)(bn - (i - na) * PIECE < PIECE ? bn - (i - na) * PIECE : PIECE));
+}
+
+// Forks the side stream off the step's stream at this point and has it ask the L2 for matrix m.
+int side_prefetch(tb_decoder* d, const Mat& m) {
+    cudaStream_t s = d->ctx->stream;
+    TB_CUDA(cudaEventRecord(d->fork_ev, s));
+    TB_CUDA(cudaStreamWaitEvent(d->side, d->fork_ev, 0));
+    static const long cap_mb = getenv("TACHYON_B200_L2_SIDE_MB") ? atol(getenv("TACHYON_B200_L2_SIDE_MB")) : -1;  // experiment: how much of it
+    size_t an = m.code_bytes(), bn = m.scale_bytes();
+    if (cap_mb >= 0 && an > (size_t)cap_mb << 20) bn = bn * ((size_t)cap_mb << 20) / an / 16 * 16, an = (size_t)cap_mb << 20;
+    const size_t pieces = (an + 16383) / 16384 + (bn + 16383) / 16384;
+    if (pieces == 0) return OK;
+    l2_prefetch_kernel<<<(unsigned)((pieces + 127) / 128), 128, 0, d->side>>>(reinterpret_cast<const char*>(m.w), an, reinterpret_cast<const char*>(m.s), bn);
+    TB_CUDA(cudaGetLastError());
+    return OK;
+}
+
 int gemv(tb_decoder* d, const Mat& m, GemvParams p) {
     p.w = m.w, p.s = m.s, p.rows = m.rows, p.cols = m.cols, p.wbits = m.bits;
     p.next = d->sched + 2 * (size_t)d->launches;  // a launch's own pair: neighbouring launches overlap
@@ -371,6 +398,8 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
     }
     for (uint32_t i = 0; i < c.layers; i++) {
         Layer& L = d->layers[i];
+        const bool side = d->ctx->l2_side && d->side != nullptr && !d->collect && !d->fused && L.down.bits == 8;
+        if (side) TB_TRY(side_prefetch(d, L.down));  // behind the kernel in front of this layer, beside the layer's short kernels
         // The attention half of the layer as one kernel on two clusters of 16 blocks (attn_block.cu), where the layer has its
         // shape: hidden 2048, 8 query and 2 key-value heads of 256 with a cache of their own, eight-bit matrices.
         const bool block = d->ctx->attn_block && !d->collect && !d->fused && c.hidden == 2048 && c.heads == 8 && L.kvh == 2 && L.dim == 256 && L.source < 0 &&
@@ -501,6 +530,10 @@ int step_ops(tb_decoder* d, uint32_t* token_word) {
         TB_TRY(gemv(d, d->embed, h));
     }
     d->final_x = 1 - cur;
+    if (d->ctx->l2_side && d->side != nullptr && !d->collect && !d->fused) {  // the side stream joins the step
+        TB_CUDA(cudaEventRecord(d->join_ev, d->side));
+        TB_CUDA(cudaStreamWaitEvent(d->ctx->stream, d->join_ev, 0));
+    }
     if (!d->capture_sampled) d->step_count = d->launches;  // the graphs that end in the sampler have one launch more
     return OK;
 }
@@ -705,6 +738,11 @@ int open_decoder(tb_context* ctx, const tb_config* cfg, const tb_settings* setti
         }
     }
     for (int g = 0; g < 2 && e == cudaSuccess; g++) e = cudaEventCreateWithFlags(&d->done[g], cudaEventDisableTiming);
+    if (e == cudaSuccess && ctx->l2_side) {
+        e = cudaStreamCreateWithFlags(&d->side, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&d->fork_ev, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&d->join_ev, cudaEventDisableTiming);
+    }
     if (e != cudaSuccess) {
         const int s = cuda_fail(e, "tb_decoder_open");
         if (adopt_table != nullptr) d->host_table = nullptr;  // still the caller's
@@ -752,6 +790,9 @@ void tb_decoder_close(tb_decoder* d) {
     }
     for (int g = 0; g < 2; g++)
         if (d->phase_dev[g]) cudaFree(d->phase_dev[g]);
+    if (d->fork_ev) cudaEventDestroy(d->fork_ev);
+    if (d->join_ev) cudaEventDestroy(d->join_ev);
+    if (d->side) cudaStreamDestroy(d->side);
     if (d->arena) cudaFree(d->arena);
     if (d->copy) cudaFree(d->copy);
     if (d->words) cudaFreeHost(d->words);
