@@ -33,6 +33,7 @@ constexpr int stages(int mt) { return mt == 2 ? 3 : 4; }
 constexpr int DW = 16;                  // dequantising / epilogue warps: with two per scheduler the loads' latency showed
 constexpr int DT = DW * 32, PIECES = 1024 / DT;  // a weight tile is 1024 pieces of 16 codes
 constexpr int THREADS = 64 + DT;        // TMA warp, MMA warp, the dequantising / epilogue warps
+constexpr int WALK_EW = DW;             // epilogue warps of the kernel that walks tiles of f16 weights (28, seven a quarter at 64 registers, measured slower: 203 against 198 us)
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;  // per 128-row sub-tile of activations, per weight tile
 constexpr int smem_bytes(int mt) { return 1024 + stages(mt) * (mt * A_BYTES + B_BYTES) + 256; }
 
@@ -117,12 +118,12 @@ __device__ __forceinline__ float silu(float v) { return v / (1.0f + exp2f(-1.442
 
 // The epilogue of one tile: the accumulator's rows are tokens, its columns weight rows; warp `warp` (2 .. 2 + DW) reads the lanes of
 // its quarter, 32 columns at a time, adds the bias, applies the mode and stores.  (m0, n0): the tile's first token and weight row.
-template <int MT>
+template <int MT, int EW = DW>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint32_t tmem, int warp, int lane, uint32_t m0, uint32_t n0, bool ok) {
-    // Two warps share each quarter of the accumulator's lanes and take alternate column blocks.
+    // EW / 4 warps share each quarter of the accumulator's lanes and take the column blocks in turn.
     const uint32_t q = warp & 3, rrow = 32 * q + lane;
 #pragma unroll 1
-    for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += DW / 4) {
+    for (int cbi = (warp - 2) >> 2; cbi < MT * (BN / 32); cbi += EW / 4) {
         const int mt = cbi / (BN / 32), cb = cbi % (BN / 32);
         const uint32_t m = m0 + mt * BM + rrow;
         uint32_t r[32];
@@ -365,8 +366,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
 // accumulator fills all of tensor memory (MT x 256 columns), so a tile's epilogue cannot overlap the next tile's products; what
 // the loop buys is that the copies of the next tile's first stages are under way during the epilogue (the ring is free
 // then), and that tensor memory, barriers and descriptors are set up once a block instead of once a tile.
-template <int MT>
-__global__ void __launch_bounds__(THREADS, 1) gemm_f16_persistent_tile_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+template <int MT, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_f16_persistent_tile_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
                                                                               const GemmArgs g, uint32_t* status) {
     constexpr int AS = MT * A_BYTES, STAGES = stages(MT);
     extern __shared__ uint8_t raw_unaligned[];
@@ -383,7 +384,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_f16_persistent_tile_kernel(co
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
-        mbar_init(acc_full, 1), mbar_init(acc_empty, DW);
+        mbar_init(acc_full, 1), mbar_init(acc_empty, EW);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -454,7 +455,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_f16_persistent_tile_kernel(co
                 ok = false;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            epilogue_tile<MT>(g, tmem, warp, lane, m0, n0, ok);
+            epilogue_tile<MT, EW>(g, tmem, warp, lane, m0, n0, ok);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty);
@@ -574,8 +575,8 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<1, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
         TB_CUDA(cudaFuncSetAttribute((gemm_q8_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
-        TB_CUDA(cudaFuncSetAttribute(gemm_f16_persistent_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
-        TB_CUDA(cudaFuncSetAttribute(gemm_f16_persistent_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_f16_persistent_tile_kernel<1, WALK_EW>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(1)));
+        TB_CUDA(cudaFuncSetAttribute((gemm_f16_persistent_tile_kernel<2, WALK_EW>), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(2)));
         configured[ctx->gpu & 15] = true;
     }
     CUtensorMap wmap = map;  // f16 weights: [N, K] in tiles of 256 rows x 64 halves; unused otherwise
@@ -591,8 +592,8 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     // f16 weights and more tiles than SMs: one block an SM walks the tiles (schedule 5 asks for the walk whatever the count).
     const uint32_t tiles = grid.x * grid.y, walkers = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
     const bool walk = wbits == 16 && ((ctx->gemm_walk && tiles > (uint32_t)ctx->sms) || ctx->gemm_schedule == 5);
-    if (walk && mt == 2) gemm_f16_persistent_tile_kernel<2><<<walkers, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (walk) gemm_f16_persistent_tile_kernel<1><<<walkers, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
+    if (walk && mt == 2) gemm_f16_persistent_tile_kernel<2, WALK_EW><<<walkers, 64 + 32 * WALK_EW, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
+    else if (walk) gemm_f16_persistent_tile_kernel<1, WALK_EW><<<walkers, 64 + 32 * WALK_EW, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
     else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
