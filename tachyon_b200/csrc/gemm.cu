@@ -223,6 +223,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_kernel(const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    // Tensor memory, barriers and descriptors are set up: the kernel behind may be scheduled, and this one reads and writes only
+    // once the kernel in front is done (both do nothing where a launch is not programmatic).
+    pdl_launch_dependents();
+    pdl_wait();
     bool ok = true;
 
     if (warp == 0) {
@@ -396,6 +400,10 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_f16_persistent_tile_kern
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    // Tensor memory, barriers and descriptors are set up: the kernel behind may be scheduled, and this one reads and writes only
+    // once the kernel in front is done (both do nothing where a launch is not programmatic).
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -592,15 +600,16 @@ int launch_gemm_q8(tb_context* ctx, const int8_t* w, const __half* s, const __ha
     // f16 weights and more tiles than SMs: one block an SM walks the tiles (schedule 5 asks for the walk whatever the count).
     const uint32_t tiles = grid.x * grid.y, walkers = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
     const bool walk = wbits == 16 && ((ctx->gemm_walk && tiles > (uint32_t)ctx->sms) || ctx->gemm_schedule == 5);
-    if (walk && mt == 2) gemm_f16_persistent_tile_kernel<2, WALK_EW><<<walkers, 64 + 32 * WALK_EW, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (walk) gemm_f16_persistent_tile_kernel<1, WALK_EW><<<walkers, 64 + 32 * WALK_EW, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (wbits == 16 && mt == 2) gemm_q8_kernel<2, 16><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (wbits == 16) gemm_q8_kernel<1, 16><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (wbits == 4 && mt == 2) gemm_q8_kernel<2, 4><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (wbits == 4) gemm_q8_kernel<1, 4><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
-    else if (mt == 2) gemm_q8_kernel<2><<<grid, THREADS, smem_bytes(2), ctx->stream>>>(map, wmap, g, ctx->status);
-    else gemm_q8_kernel<1><<<grid, THREADS, smem_bytes(1), ctx->stream>>>(map, wmap, g, ctx->status);
-    TB_CUDA(cudaGetLastError());
+    cudaError_t le;
+    if (walk && mt == 2) le = launch_kernel(ctx, gemm_f16_persistent_tile_kernel<2, WALK_EW>, dim3(walkers), dim3(64 + 32 * WALK_EW), (size_t)smem_bytes(2), true, map, wmap, g, ctx->status);
+    else if (walk) le = launch_kernel(ctx, gemm_f16_persistent_tile_kernel<1, WALK_EW>, dim3(walkers), dim3(64 + 32 * WALK_EW), (size_t)smem_bytes(1), true, map, wmap, g, ctx->status);
+    else if (wbits == 16 && mt == 2) le = launch_kernel(ctx, gemm_q8_kernel<2, 16>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(2), true, map, wmap, g, ctx->status);
+    else if (wbits == 16) le = launch_kernel(ctx, gemm_q8_kernel<1, 16>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(1), true, map, wmap, g, ctx->status);
+    else if (wbits == 4 && mt == 2) le = launch_kernel(ctx, gemm_q8_kernel<2, 4>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(2), true, map, wmap, g, ctx->status);
+    else if (wbits == 4) le = launch_kernel(ctx, gemm_q8_kernel<1, 4>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(1), true, map, wmap, g, ctx->status);
+    else if (mt == 2) le = launch_kernel(ctx, gemm_q8_kernel<2>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(2), true, map, wmap, g, ctx->status);
+    else le = launch_kernel(ctx, gemm_q8_kernel<1>, dim3(grid), dim3(THREADS), (size_t)smem_bytes(1), true, map, wmap, g, ctx->status);
+    TB_CUDA(le);
     return OK;
 }
 

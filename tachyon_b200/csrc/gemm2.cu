@@ -142,6 +142,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bar.tmem;
+    // Set up: the kernel behind may be scheduled; this one reads and writes only once the kernel in front is done (both do
+    // nothing where a launch is not programmatic).
+    pdl_launch_dependents();
+    pdl_wait();
 
     // Tile t: token tile t % tiles_m, weight tile t / tiles_m: blocks that run together share weight rows.
     if (warp == 0) {
@@ -421,10 +425,11 @@ int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, co
     const uint32_t tiles = ((M + tn - 1) / tn) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
     const Args g{s, out, M, N, K, mode, mul, mul_stride, tn};
-    if (wbits == 16) gemm_persistent_kernel<16><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
-    else if (wbits == 4) gemm_persistent_kernel<4><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
-    else gemm_persistent_kernel<8><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(amap, wmap, g, ctx->status);
-    TB_CUDA(cudaGetLastError());
+    cudaError_t le;
+    if (wbits == 16) le = launch_kernel(ctx, gemm_persistent_kernel<16>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
+    else if (wbits == 4) le = launch_kernel(ctx, gemm_persistent_kernel<4>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
+    else le = launch_kernel(ctx, gemm_persistent_kernel<8>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
+    TB_CUDA(le);
     return OK;
 }
 

@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(float* h, const float
                                                            __half* x) {
     const uint32_t token = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();  // the product behind sets itself up meanwhile; it reads x only after its own wait
+    pdl_wait();               // h and y come from the kernels in front
     if (token >= tokens) return;
     const size_t base = (size_t)token * NORM_N;
     float4 v[NORM_V];
@@ -90,6 +92,8 @@ __global__ void __launch_bounds__(128) prefill_qkv_kernel(const float* qkv, cons
                                                           float eps, float qscale, QkvRows rows_of) {
     constexpr int H2 = DH / 64, NV = 2 * H2;  // values a lane holds of each half, and in all
     const uint32_t item = blockIdx.x * 4 + (threadIdx.x >> 5), token = item / rows_of.count, r = rows_of.first + item % rows_of.count;
+    pdl_launch_dependents();  // the attention kernel behind waits for this one before it reads anything
+    pdl_wait();               // the projections come from the product in front
     if (token >= tokens) return;  // the last block's spare warps (nothing below synchronises the block)
     if (rows_of.pos != nullptr) pos0 = __ldg(rows_of.pos);
     const int lane = threadIdx.x & 31;
@@ -363,7 +367,7 @@ int launch_prefill_embed(tb_context* ctx, const int8_t* w, const __half* s, cons
 int launch_prefill_norm(tb_context* ctx, float* h, const float* y, const float* w1, const float* w2, uint32_t tokens, uint32_t n, float eps, float hscale,
                         __half* x) {
     if (n != 2048) return fail(UNSUPPORTED, "prefill norm: rows of 2048 values");
-    prefill_norm_kernel<<<(tokens + 7) / 8, 256, 0, ctx->stream>>>(h, y, w1, w2, tokens, eps, hscale, x);
+    TB_CUDA(launch_kernel(ctx, prefill_norm_kernel, dim3((tokens + 7) / 8), dim3(256), (size_t)0, true, h, y, w1, w2, tokens, eps, hscale, x));
     TB_CUDA(cudaGetLastError());
     return OK;
 }
@@ -382,8 +386,10 @@ int launch_prefill_rows(tb_context* ctx, const float* qkv, const float* q_norm, 
     if (head_dim != 256 && head_dim != 512) return fail(UNSUPPORTED, "prefill qkv: heads of 256 or 512");
     if (items == 0) return fail(OUT_OF_RANGE, "prefill qkv: nothing to prepare");
     const QkvRows r{rows.first, rows.count, rows.stride, rows.pos};
-    if (head_dim == 512) prefill_qkv_kernel<512><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
-    else prefill_qkv_kernel<256><<<blocks, 128, 0, ctx->stream>>>(qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
+    cudaError_t le;
+    if (head_dim == 512) le = launch_kernel(ctx, prefill_qkv_kernel<512>, dim3(blocks), dim3(128), (size_t)0, true, qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
+    else le = launch_kernel(ctx, prefill_qkv_kernel<256>, dim3(blocks), dim3(128), (size_t)0, true, qkv, q_norm, k_norm, freq, q_out, kc, vc, tokens, pos0, cap, heads, kv_heads, eps, qscale, r);
+    TB_CUDA(le);
     TB_CUDA(cudaGetLastError());
     return OK;
 }
