@@ -88,6 +88,10 @@ TB_API int tb_context_set_flash(tb_context* ctx, int which);
  * default: measured slower than the three launches (the clusters start late and fetch through two GPCs only).
  * TACHYON_B200_ATTN_BLOCK=1 starts a context with it on. */
 TB_API int tb_context_set_attn_block(tb_context* ctx, int on);
+/* Context::trim (cuda/mod.rs): decoders take their device memory from a pool that keeps what they free, so that the next
+ * model to come into VRAM finds it at once (a parked or closed decoder's memory stays with this process); this gives the
+ * pool's unused memory back to the system.  The engine calls it when a model is unloaded or expires, as the reference does. */
+TB_API int tb_context_trim(tb_context* ctx);
 /* Context::memory (cuda/mod.rs:194-198): free and total device memory, in bytes. */
 TB_API int tb_context_memory(tb_context* ctx, size_t* free_bytes, size_t* total_bytes);
 /* First error word a kernel left on the device (0 = none); synchronises the stream.  *word may be NULL. */

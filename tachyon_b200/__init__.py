@@ -252,6 +252,10 @@ class Context:
         check(self.lib.tb_context_memory(self.handle, C.byref(f), C.byref(t)))
         return f.value, t.value
 
+    def trim(self) -> None:
+        """Context::trim: the pool's unused device memory back to the system."""
+        check(self.lib.tb_context_trim(self.handle))
+
     def set_attn_block(self, on: bool) -> None:
         """tb_context_set_attn_block: a layer's attention half as one kernel on clusters of 16 blocks (off by default)."""
         check(self.lib.tb_context_set_attn_block(self.handle, int(on)))

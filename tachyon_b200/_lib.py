@@ -71,6 +71,7 @@ SIGNATURES = {
     "tb_context_set_dynamic": (i32, [vp, i32]),
     "tb_context_set_flash": (i32, [vp, i32]),
     "tb_context_memory": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
+    "tb_context_trim": (i32, [vp]),
     "tb_context_set_attn_block": (i32, [vp, i32]),
     "tb_status": (i32, [vp, C.POINTER(u32)]),
     "tb_status_clear": (i32, [vp]),

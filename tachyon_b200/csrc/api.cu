@@ -27,6 +27,17 @@ int cuda_fail(cudaError_t e, const char* where) {
     return fail(status, std::string(where) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }
 
+cudaError_t pool_alloc(tb_context* ctx, void** out, size_t bytes) {
+    if (ctx->pool == nullptr) return cudaMalloc(out, bytes);
+    return cudaMallocFromPoolAsync(out, bytes, ctx->pool, ctx->stream);
+}
+
+void pool_free(tb_context* ctx, void* p) {
+    if (p == nullptr) return;
+    if (ctx->pool == nullptr) cudaFree(p);
+    else cudaFreeAsync(p, ctx->stream);
+}
+
 // The driver seam (crates/tachyon/src/cuda/driver.rs:138-167): the driver library is looked for at $TACHYON_LIBCUDA when that
 // is set, else under its usual names; it must export cuDriverGetVersion and cuGetProcAddress_v2 and support CUDA 12.0.  The
 // outcome is kept for the life of the process, as the reference keeps it.  The statically linked CUDA runtime then finds the
@@ -96,6 +107,19 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->gpu = gpu;
     ctx->sms = prop.multiProcessorCount;
     cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) {
+        // The pool the decoders' memory comes from: it never gives memory back by itself (tb_context_trim does).
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned, props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice, props.location.id = gpu;
+        if (cudaMemPoolCreate(&ctx->pool, &props) == cudaSuccess) {
+            uint64_t keep = UINT64_MAX;
+            cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        } else {
+            ctx->pool = nullptr;  // no pools on this driver: plain allocations
+            cudaGetLastError();
+        }
+    }
     if (e == cudaSuccess) e = cudaMalloc(&ctx->status, 256);
     if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, 256);
     if (e == cudaSuccess) e = cudaHostAlloc(&ctx->status_host, 256, cudaHostAllocDefault);
@@ -140,7 +164,9 @@ int tb_context_new(int gpu, tb_context** out) {
 void tb_context_free(tb_context* ctx) {
     if (ctx == nullptr) return;
     cudaSetDevice(ctx->gpu);
-    if (ctx->stream) cudaStreamSynchronize(ctx->stream), cudaStreamDestroy(ctx->stream);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->sched) cudaFree(ctx->sched);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -172,6 +198,15 @@ int tb_context_set_lean(tb_context* ctx, int mode) {
 int tb_context_set_dynamic(tb_context* ctx, int on) {
     if (!ctx) return fail(OUT_OF_RANGE, "null context");
     ctx->dynamic = on != 0;
+    return OK;
+}
+
+int tb_context_trim(tb_context* ctx) {
+    if (!ctx) return fail(OUT_OF_RANGE, "null context");
+    if (ctx->pool == nullptr) return OK;
+    TB_CUDA(cudaSetDevice(ctx->gpu));
+    TB_CUDA(cudaStreamSynchronize(ctx->stream));  // frees in the stream's order have to have happened
+    TB_CUDA(cudaMemPoolTrimTo(ctx->pool, 0));
     return OK;
 }
 

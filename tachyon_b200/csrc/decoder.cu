@@ -632,7 +632,7 @@ int place_copy(tb_decoder* d) {
     size_t free_bytes = 0, total = 0;
     TB_CUDA(cudaMemGetInfo(&free_bytes, &total));
     if (want == 0 && (free_bytes < halves * 2 || free_bytes - halves * 2 < total / 4)) return OK;
-    const cudaError_t e = cudaMalloc(&d->copy, halves * 2);
+    const cudaError_t e = pool_alloc(d->ctx, reinterpret_cast<void**>(&d->copy), halves * 2);
     if (e != cudaSuccess) {
         cudaGetLastError();
         if (want == 0) return d->copy = nullptr, OK;
@@ -648,7 +648,6 @@ int place_copy(tb_decoder* d) {
 // Writes the copy from the codes as they are now.
 int refresh_copy(tb_decoder* d) {
     if (!d->copy || d->copy_valid) return OK;
-    if (d->weights_ready) TB_CUDA(cudaStreamWaitEvent(d->ctx->stream, d->weights_ready, 0));
     for (Layer& L : d->layers)
         for (Mat* m : {&L.qkv, &L.o, &L.gate_up, &L.down}) TB_TRY(launch_dequant_f16(d->ctx, m->w, m->s, m->rows, m->cols, m->bits, m->f16));
     d->copy_valid = true;
@@ -725,7 +724,7 @@ int open_decoder(tb_context* ctx, const tb_config* cfg, const tb_settings* setti
     d->embed_scale = bf16_round(sqrtf((float)cfg->hidden));
     layout(d, nullptr);
     cudaError_t e = cudaSetDevice(ctx->gpu);
-    if (e == cudaSuccess) e = cudaMalloc(&d->arena, d->arena_bytes);
+    if (e == cudaSuccess) e = pool_alloc(ctx, reinterpret_cast<void**>(&d->arena), d->arena_bytes);
     if (e == cudaSuccess) e = cudaMemsetAsync(d->arena, 0, d->arena_bytes, ctx->stream);
     if (e == cudaSuccess) e = cudaHostAlloc(&d->words, 64, cudaHostAllocMapped);
     if (e == cudaSuccess && cfg->per_layer && settings->host_table) {
@@ -793,8 +792,8 @@ void tb_decoder_close(tb_decoder* d) {
     if (d->fork_ev) cudaEventDestroy(d->fork_ev);
     if (d->join_ev) cudaEventDestroy(d->join_ev);
     if (d->side) cudaStreamDestroy(d->side);
-    if (d->arena) cudaFree(d->arena);
-    if (d->copy) cudaFree(d->copy);
+    if (d->arena) pool_free(d->ctx, d->arena);
+    if (d->copy) pool_free(d->ctx, d->copy);
     if (d->words) cudaFreeHost(d->words);
     if (d->host_table) cudaFreeHost(d->host_table);
     if (d->shadow) cudaFreeHost(d->shadow);
@@ -948,7 +947,9 @@ int tb_decoder_build(tb_decoder* d) {
         cudaGraphDestroy(graph);
         if (ei != cudaSuccess) return cuda_fail(ei, "cudaGraphInstantiate");
     }
-    TB_TRY(refresh_copy(d));
+    // A model on its way back from the host tier writes its prefill copy when a long prompt first asks for it, not here: its
+    // return is measured to its first answer, and a short prompt never reads the copy.
+    if (!d->weights_ready) TB_TRY(refresh_copy(d));
     d->built = true;
     d->running = false;
     // The uncaptured pass advanced the position and wrote a cache slot; start clean.
@@ -1308,6 +1309,9 @@ int tb_parked_resume(tb_parked* p, const tb_settings* settings, tb_decoder** out
     cudaStream_t s = d->ctx->stream, cs = nullptr;
     cudaError_t err = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
     if (err == cudaSuccess) err = cudaEventCreateWithFlags(&d->weights_ready, cudaEventDisableTiming);
+    // The arena came from the pool in the order of the context's stream: the copies' stream joins that order first.
+    if (err == cudaSuccess) err = cudaEventRecord(d->weights_ready, s);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(cs, d->weights_ready, 0);
     size_t at = 0;
     for_each_weight(d, [&](void* ptr, size_t n) {
         if (err == cudaSuccess) err = cudaMemcpyAsync(ptr, p->weights + at, n, cudaMemcpyHostToDevice, cs);

@@ -159,9 +159,10 @@ struct tb_engine {
     // engine.rs:309-325
     int expire() {
         const Clock::time_point now = Clock::now();
+        bool freed = false;
         for (Model& m : models)
-            if (m.at != AT_DISK && !m.load.pin && m.ends && m.until <= now) m.drop();
-        return tb::OK;
+            if (m.at != AT_DISK && !m.load.pin && m.ends && m.until <= now) freed = freed || m.at == AT_VRAM, m.drop();
+        return freed ? tb_context_trim(ctx) : tb::OK;  // the VRAM goes back to the system, not only to the pool
     }
 };
 
@@ -197,8 +198,10 @@ int tb_engine_unload(tb_engine* e, const char* name, int* was_loaded) {
     const int i = e->find(name);
     if (was_loaded) *was_loaded = i >= 0;
     if (i >= 0) {
+        const bool vram = e->models[i].at == AT_VRAM;
         e->models[i].drop();
         e->models.erase(e->models.begin() + i);
+        if (vram) return tb_context_trim(e->ctx);  // engine.rs:247-248
     }
     return tb::OK;
 }

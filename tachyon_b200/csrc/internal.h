@@ -14,6 +14,9 @@ struct tb_context {
     cudaStream_t stream = nullptr;
     uint32_t* status = nullptr;       // device word: first kernel-side error (tb::ERR_*), 0 when fine
     uint32_t* status_host = nullptr;  // pinned mirror used by tb_status
+    // Decoders take their device memory from this pool, which keeps what they free (cuda/mod.rs `alloc_pooled`: a model moved out
+    // to make room leaves its VRAM in the pool for the next); tb_context_trim gives it back to the system.
+    cudaMemPool_t pool = nullptr;
     bool pdl = true;                  // launch kernels with programmatic stream serialization
     bool prefetch = true;             // give kernels L2 hints about the next kernel's weights
     bool dynamic = true;              // large matrix-vector products hand their stages out through a counter (TACHYON_B200_STATIC=1: never)
@@ -53,6 +56,9 @@ enum Status : int {
 };
 
 int fail(int status, const std::string& what);
+// Device memory from the context's pool, in the order of its stream (falls back to cudaMalloc without a pool); and back.
+cudaError_t pool_alloc(tb_context* ctx, void** out, size_t bytes);
+void pool_free(tb_context* ctx, void* p);
 int cuda_fail(cudaError_t e, const char* where);
 #define TB_CUDA(call)                                             \
     do {                                                          \

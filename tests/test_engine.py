@@ -56,6 +56,7 @@ def test_a_parked_model_comes_back_with_the_same_answers(ctx, model):
     free_before = ctx.memory()[0]
     parked = dec.park()
     assert dec.handle is None and parked.bytes() == will_hold
+    ctx.trim()  # the decoder's memory went to the context's pool; from there to the system
     assert ctx.memory()[0] >= free_before + held - (2 << 20), "the device memory went back"
     # other settings on the way back: a longer context, a larger chunk
     back = parked.resume(context=128, chunk=32)
