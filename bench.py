@@ -264,6 +264,7 @@ def bench_decode(args, ranks: Ranks):
     # ---- the dominant kernel alone: gate/up projection over every layer's matrix in turn (2.5 GB > L2) ----
     roof = kernel_roofline(ctx, cfg, W, K) if ranks.rank == 0 else None
     dec.close()
+    ctx.trim()  # the decoder's memory back to the system, not only to this context's pool
 
     n = ranks.world
     value = n * K / (ms_max / 1e3)
@@ -547,6 +548,7 @@ def bench_switch(args, ranks: Ranks):
         parked = dec.park()
         parks.append(time.perf_counter() - t0)
     parked.close()
+    ctx.trim()
     # the link alone: 1 GiB of pinned memory into device memory that is already in use
     n = 1 << 30
     hb, db = ctx.alloc_host(n), ctx.alloc(n)
@@ -641,6 +643,7 @@ def bench_prefill(args, ranks: Ranks):
     burst, sustained, how = measured_peak_tflops()
     tf = flops / (ms_max * 1e-3) / 1e12
     dec.close()
+    ctx.trim()  # the decoder's memory back to the system, not only to this context's pool
     n = ranks.world
     return {"metric": "prefill_tokens_per_second", "value": n * T / (ms_max / 1e3), "unit": "tok/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
