@@ -587,6 +587,9 @@ TB_API void tb_encoder_close(tb_encoder* enc);
  * encoder/run.rs:449-466). */
 TB_API int tb_encoder_load(tb_encoder* enc, const char* name, const void* data, size_t bytes);
 TB_API int tb_encoder_fill_random(tb_encoder* enc, uint64_t seed);
+/* Every tensor of a converted encoder's file (weights.wpk, host.wpk: encoder/convert.rs) through tb_encoder_load, as
+ * tb_decoder_load_wpk does for a decoder; verify != 0 checks each tensor's CRC32C first. */
+TB_API int tb_encoder_load_wpk(tb_encoder* enc, const char* path, int verify);
 /* Encoder::embeddings (run.rs:161-175): ids packed back to back, lens[s] tokens each; out_host: dims f32 per sequence,
  * L2-normalised.  More tokens (or sequences) than the encoder was opened for go in several batches, in order, a batch
  * closed by the first sequence that no longer fits (Encoder::batches, run.rs:207-221); one sequence longer than the
@@ -597,6 +600,22 @@ TB_API int tb_encoder_hidden(tb_encoder* enc, float* out_host);
 TB_API uint32_t tb_encoder_batch_tokens(const tb_encoder* enc);
 /* Padded shapes whose graph is held at the moment. */
 TB_API uint32_t tb_encoder_graphs(const tb_encoder* enc);
+/* Encoder::bytes (encoder/run.rs:144-147): the VRAM the encoder holds.  encoder::footprint (encoder/run.rs:613-619): what
+ * tb_encoder_open will take for this shape and capacity; f16_matrices != 0 counts the layers' matrices in f16 too, which a
+ * converted f16 model loads beside the arena. */
+TB_API size_t tb_encoder_bytes(const tb_encoder* enc);
+TB_API int tb_encoder_footprint(tb_context* ctx, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, int f16_matrices, size_t* bytes);
+
+/* Encoders in the engine (engine.rs:54-55, 225-232, 244-262): held by name, always in VRAM and counted against the VRAM limit
+ * (tb_engine_usage, tb_engine_models list them after the decoders, tier TB_TIER_VRAM), dropped by tb_engine_expire when their
+ * keep-alive has run out (keep_alive_ms as in tb_load; pin != 0: never).  Loading one moves decoders out to make room, as
+ * loading a decoder does; an encoder never moves out.  tb_engine_unload and tb_engine_tier take an encoder's name too.
+ * tb_engine_encoder starts the keep-alive again; its pointer is the engine's.  tb_engine_embed is Engine::embed from token
+ * ids (the tokenizer stays with the caller): tb_encoder_embed on the held encoder. */
+TB_API int tb_engine_load_encoder(tb_engine* eng, const char* name, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, uint64_t keep_alive_ms, int pin,
+                                  const char* weights_path, const char* host_path);
+TB_API int tb_engine_encoder(tb_engine* eng, const char* name, tb_encoder** out);
+TB_API int tb_engine_embed(tb_engine* eng, const char* name, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host);
 
 #ifdef __cplusplus
 }

@@ -387,7 +387,8 @@ FOR_GOOD = 2**64 - 1
 
 
 class Engine:
-    """Engine's model residency (crates/tachyon/src/engine.rs:190-453), decoders only: load, decoder, feed, tier, models, unload, expire."""
+    """Engine's model residency (crates/tachyon/src/engine.rs:190-453): load, decoder, feed, tier, models, unload, expire; encoders
+    held by name with load_encoder, embed."""
 
     def __init__(self, ctx: Context, vram_limit: int = 0, host_limit: int = 0):
         self.ctx, self.lib = ctx, ctx.lib
@@ -441,6 +442,22 @@ class Engine:
     def expire(self) -> None:
         check(self.lib.tb_engine_expire(self.handle))
 
+    def load_encoder(self, name: str, cfg: EncoderConfig, weights: str, host: str | None = None, tokens: int = 4096, sequences: int = 64,
+                     keep_alive_ms: int = 300_000, pin: bool = False) -> None:
+        """tb_engine_load_encoder: the encoder of these files held as `name`, decoders moved out to make room."""
+        check(self.lib.tb_engine_load_encoder(self.handle, name.encode(), C.byref(cfg), tokens, sequences, keep_alive_ms, int(pin), os.fsencode(weights),
+                                              os.fsencode(host) if host else None))
+        self.dims = getattr(self, "dims", {})
+        self.dims[name] = cfg.dims
+
+    def embed(self, name: str, sequences) -> np.ndarray:
+        """tb_engine_embed: embeddings [len(sequences), dims] of lists of token ids by the held encoder `name`."""
+        lens = np.array([len(q) for q in sequences], np.uint32)
+        ids = np.concatenate([np.asarray(q, np.uint32) for q in sequences])
+        out = np.zeros((len(sequences), getattr(self, "dims", {}).get(name, 0)), np.float32)
+        check(self.lib.tb_engine_embed(self.handle, name.encode(), ids.ctypes.data, lens.ctypes.data, len(sequences), out.ctypes.data if out.size else None))
+        return out
+
     def usage(self) -> tuple[int, int]:
         v, h = C.c_size_t(0), C.c_size_t(0)
         check(self.lib.tb_engine_usage(self.handle, C.byref(v), C.byref(h)))
@@ -453,6 +470,13 @@ def decoder_footprint(ctx: Context, cfg: Config, context: int = 4096, chunk: int
     st = Settings(context=context, chunk=chunk, keep_logits=int(keep_logits), fused=0, weight_bits=weight_bits, host_table=int(host_table), prefill_copy=prefill_copy)
     n = C.c_size_t(0)
     check(ctx.lib.tb_decoder_footprint(ctx.handle, C.byref(cfg), C.byref(st), C.byref(n)))
+    return n.value
+
+
+def encoder_footprint(ctx: Context, cfg: EncoderConfig, tokens: int = 4096, sequences: int = 64, f16_matrices: bool = False) -> int:
+    """tb_encoder_footprint: the device memory such an encoder takes, nothing allocated."""
+    n = C.c_size_t(0)
+    check(ctx.lib.tb_encoder_footprint(ctx.handle, C.byref(cfg), tokens, sequences, int(f16_matrices), C.byref(n)))
     return n.value
 
 
@@ -615,6 +639,14 @@ class Encoder:
 
     def fill_random(self, seed: int) -> None:
         check(self.lib.tb_encoder_fill_random(self.handle, seed))
+
+    def bytes(self) -> int:
+        """tb_encoder_bytes: the VRAM the encoder holds."""
+        return int(self.lib.tb_encoder_bytes(self.handle))
+
+    def load_wpk(self, path: str, verify: bool = True) -> None:
+        """tb_encoder_load_wpk: every tensor of a converted encoder's file, by its name."""
+        check(self.lib.tb_encoder_load_wpk(self.handle, os.fsencode(path), int(verify)))
 
     def embed(self, sequences) -> np.ndarray:
         """Embeddings [len(sequences), dims] of lists of token ids, packed into batches of at most the capacity."""

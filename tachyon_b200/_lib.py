@@ -150,6 +150,7 @@ SIGNATURES = {
     "tb_wpk_tensor": (i32, [vp, u32, vp]),
     "tb_wpk_read": (i32, [vp, u32, vp, sz, i32]),
     "tb_decoder_load_wpk": (i32, [vp, cp, i32]),
+    "tb_encoder_load_wpk": (i32, [vp, cp, i32]),
     "tb_decoder_park": (i32, [vp, pp]),
     "tb_parked_resume": (i32, [vp, C.POINTER(Settings), pp]),
     "tb_parked_bytes": (sz, [vp]),
@@ -169,6 +170,11 @@ SIGNATURES = {
     "tb_engine_models": (i32, [vp, C.POINTER(Loaded), sz, C.POINTER(sz)]),
     "tb_engine_expire": (i32, [vp]),
     "tb_engine_usage": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
+    "tb_engine_load_encoder": (i32, [vp, cp, C.POINTER(EncoderConfig), u32, u32, u64, i32, cp, cp]),
+    "tb_engine_encoder": (i32, [vp, cp, pp]),
+    "tb_engine_embed": (i32, [vp, cp, vp, vp, u32, vp]),
+    "tb_encoder_bytes": (sz, [vp]),
+    "tb_encoder_footprint": (i32, [vp, C.POINTER(EncoderConfig), u32, u32, i32, C.POINTER(sz)]),
     "tb_encoder_open": (i32, [vp, C.POINTER(EncoderConfig), u32, u32, pp]),
     "tb_encoder_close": (None, [vp]),
     "tb_encoder_load": (i32, [vp, cp, vp, sz]),

@@ -829,4 +829,33 @@ uint32_t tb_encoder_batch_tokens(const tb_encoder* e) { return e ? e->tokens : 0
 
 uint32_t tb_encoder_graphs(const tb_encoder* e) { return e ? (uint32_t)e->graphs.size() : 0; }
 
+// Encoder::bytes (encoder/run.rs:144-147): the VRAM it holds, weights, RoPE tables and activations, with the f16 matrices a
+// converted model brought.
+size_t tb_encoder_bytes(const tb_encoder* e) {
+    if (!e) return 0;
+    size_t n = e->arena_bytes;
+    for (const ELayer& L : e->layers)
+        for (const EMat* m : {&L.qkv, &L.o, &L.up, &L.down})
+            if (m->f16) n += 2 * m->code_bytes();
+    return n;
+}
+
+// encoder::footprint (encoder/run.rs:613-619): what tb_encoder_open will take for this shape and capacity, before anything is
+// allocated.  `f16_matrices` != 0 adds the layers' matrices in f16, which a converted f16 model loads beside the arena.
+int tb_encoder_footprint(tb_context* ctx, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, int f16_matrices, size_t* bytes) {
+    if (!ctx || !cfg || !bytes || tokens == 0 || sequences == 0) return fail(OUT_OF_RANGE, "tb_encoder_footprint: null or empty argument");
+    TB_TRY(enc_validate(*cfg));
+    tb_encoder e;
+    e.ctx = ctx, e.cfg = *cfg, e.cap_tokens = tokens, e.cap_padded = (tokens + QT - 1) / QT * QT, e.cap_seqs = sequences;
+    e.global.assign(cfg->layers, 0);
+    e.layers.resize(cfg->layers);
+    const char* env = getenv("TACHYON_B200_ENCODER_COPY");
+    e.use_copy = !(env && env[0] == '0');
+    *bytes = enc_layout(&e, nullptr);
+    if (f16_matrices)
+        for (const ELayer& L : e.layers)
+            for (const EMat* m : {&L.qkv, &L.o, &L.up, &L.down}) *bytes += 2 * m->code_bytes();
+    return OK;
+}
+
 }  // extern "C"

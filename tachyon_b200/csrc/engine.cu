@@ -5,7 +5,9 @@
 // until it fits; a model moved out is parked in the host tier if it fits there, after freeing the least recently used
 // pinned memory (a resident model's kept copy first dropped, a parked model sent to disk), else it goes to disk; a
 // keep-alive that has run out sends a model to disk at the next call.  Host code only: the decoders do the GPU work.
-// Not here: tokenizer, chat template, towers and encoders (an encoder has no host tier in the reference either).
+// Encoders are held by name too (engine.rs:54-55, 225-232, 244-262): always in VRAM, counted against the limit, dropped when
+// their keep-alive runs out; decoders move out to make room for one, an encoder never moves.
+// Not here: tokenizer, chat template and towers.
 #include <unistd.h>
 
 #include <algorithm>
@@ -53,6 +55,24 @@ struct Model {
     }
 };
 
+// Held (engine.rs:158-168): a loaded encoder, how long it stays after a use, whether it is pinned.
+struct Held {
+    std::string name;
+    tb_encoder* enc = nullptr;
+    uint64_t keep_ms = UINT64_MAX;
+    bool pin = false, ends = false;
+    Clock::time_point until;
+
+    void touch() {
+        ends = keep_ms != UINT64_MAX;
+        if (ends) until = Clock::now() + std::chrono::milliseconds(keep_ms);
+    }
+    uint64_t left_ms(Clock::time_point now) const {
+        if (!ends || pin) return UINT64_MAX;
+        return until > now ? (uint64_t)std::chrono::duration_cast<std::chrono::milliseconds>(until - now).count() : 0;
+    }
+};
+
 }  // namespace
 
 struct tb_engine {
@@ -60,6 +80,13 @@ struct tb_engine {
     size_t limits[2] = {0, 0};  // VRAM, host tier
     uint64_t tick = 0;
     std::vector<Model> models;
+    std::vector<Held> encoders;
+
+    int held(const char* name) const {
+        for (size_t i = 0; i < encoders.size(); i++)
+            if (encoders[i].name == name) return (int)i;
+        return -1;
+    }
 
     int find(const char* name) const {
         for (size_t i = 0; i < models.size(); i++)
@@ -68,6 +95,7 @@ struct tb_engine {
     }
     size_t used() const {
         size_t n = 0;
+        for (const Held& h : encoders) n += tb_encoder_bytes(h.enc);
         for (const Model& m : models)
             if (m.at == AT_VRAM) n += m.need;
         return n;
@@ -162,6 +190,12 @@ struct tb_engine {
         bool freed = false;
         for (Model& m : models)
             if (m.at != AT_DISK && !m.load.pin && m.ends && m.until <= now) freed = freed || m.at == AT_VRAM, m.drop();
+        for (size_t i = encoders.size(); i-- > 0;)
+            if (!encoders[i].pin && encoders[i].ends && encoders[i].until <= now) {
+                tb_encoder_close(encoders[i].enc);
+                encoders.erase(encoders.begin() + (long)i);
+                freed = true;
+            }
         return freed ? tb_context_trim(ctx) : tb::OK;  // the VRAM goes back to the system, not only to the pool
     }
 };
@@ -190,18 +224,24 @@ int tb_engine_new(tb_context* ctx, size_t vram_limit, size_t host_limit, tb_engi
 void tb_engine_close(tb_engine* e) {
     if (!e) return;
     for (Model& m : e->models) m.drop();
+    for (Held& h : e->encoders) tb_encoder_close(h.enc);
     delete e;
 }
 
 int tb_engine_unload(tb_engine* e, const char* name, int* was_loaded) {
     if (!e || !name) return tb::fail(tb::OUT_OF_RANGE, "tb_engine_unload: null argument");
-    const int i = e->find(name);
-    if (was_loaded) *was_loaded = i >= 0;
+    const int i = e->find(name), k = e->held(name);
+    if (was_loaded) *was_loaded = i >= 0 || k >= 0;
+    if (k >= 0) {
+        tb_encoder_close(e->encoders[k].enc);
+        e->encoders.erase(e->encoders.begin() + k);
+        if (i < 0) return tb_context_trim(e->ctx);
+    }
     if (i >= 0) {
         const bool vram = e->models[i].at == AT_VRAM;
         e->models[i].drop();
         e->models.erase(e->models.begin() + i);
-        if (vram) return tb_context_trim(e->ctx);  // engine.rs:247-248
+        if (vram || k >= 0) return tb_context_trim(e->ctx);  // engine.rs:247-248
     }
     return tb::OK;
 }
@@ -250,6 +290,7 @@ int tb_engine_feed(tb_engine* e, const char* name, const uint32_t* tokens, uint3
 
 int tb_engine_tier(const tb_engine* e, const char* name, int* tier) {
     if (!e || !name || !tier) return tb::fail(tb::OUT_OF_RANGE, "tb_engine_tier: null argument");
+    if (e->held(name) >= 0) return *tier = TB_TIER_VRAM, tb::OK;
     const int i = e->find(name);
     if (i < 0) return tb::fail(tb::NO_MODEL, std::string("engine: no model named ") + name);
     *tier = e->models[i].at;
@@ -258,7 +299,7 @@ int tb_engine_tier(const tb_engine* e, const char* name, int* tier) {
 
 int tb_engine_models(const tb_engine* e, tb_loaded* out, size_t capacity, size_t* count) {
     if (!e || !count || (capacity && !out)) return tb::fail(tb::OUT_OF_RANGE, "tb_engine_models: null argument");
-    *count = e->models.size();
+    *count = e->models.size() + e->encoders.size();
     const Clock::time_point now = Clock::now();
     for (size_t i = 0; i < e->models.size() && i < capacity; i++) {
         const Model& m = e->models[i];
@@ -269,7 +310,68 @@ int tb_engine_models(const tb_engine* e, tb_loaded* out, size_t capacity, size_t
         out[i].left_ms = UINT64_MAX;
         if (m.ends && !m.load.pin) out[i].left_ms = m.until > now ? (uint64_t)std::chrono::duration_cast<std::chrono::milliseconds>(m.until - now).count() : 0;
     }
+    for (size_t k = 0, i = e->models.size(); k < e->encoders.size() && i < capacity; k++, i++) {  // decoders, then encoders (engine.rs:294)
+        const Held& h = e->encoders[k];
+        memset(&out[i], 0, sizeof(tb_loaded));
+        strncpy(out[i].name, h.name.c_str(), sizeof(out[i].name) - 1);
+        out[i].tier = TB_TIER_VRAM;
+        out[i].vram = tb_encoder_bytes(h.enc);
+        out[i].left_ms = h.left_ms(now);
+    }
     return tb::OK;
+}
+
+// Engine::load_encoder (engine.rs:225-232): room made by moving decoders out, then the encoder opened from its files and kept as
+// asked; one of that name, decoder or encoder, is unloaded first.
+int tb_engine_load_encoder(tb_engine* e, const char* name, const tb_encoder_config* cfg, uint32_t tokens, uint32_t sequences, uint64_t keep_alive_ms, int pin,
+                           const char* weights_path, const char* host_path) {
+    if (!e || !name || !cfg || !weights_path) return tb::fail(tb::OUT_OF_RANGE, "tb_engine_load_encoder: null argument");
+    tb_engine_unload(e, name, nullptr);
+    e->expire();
+    // The layers' matrices come in f16 if the file holds them so: they are allocated beside the arena when loaded.
+    int f16 = 0;
+    {
+        tb_wpk* w = nullptr;
+        TB_TRY(tb_wpk_open(weights_path, &w));
+        tb_wpk_info info;
+        for (uint32_t i = 0; i < tb_wpk_count(w) && !f16; i++)
+            if (tb_wpk_tensor(w, i, &info) == tb::OK && info.rank == 2 && info.dtype == 1 && strcmp(info.name, "embed") != 0) f16 = 1;
+        tb_wpk_close(w);
+    }
+    size_t need = 0;
+    TB_TRY(tb_encoder_footprint(e->ctx, cfg, tokens, sequences, f16, &need));
+    TB_TRY(e->room(need, -1));
+    Held h;
+    h.name = name, h.keep_ms = keep_alive_ms, h.pin = pin != 0;
+    int st = tb_encoder_open(e->ctx, cfg, tokens, sequences, &h.enc);
+    if (st == tb::OK) st = tb_encoder_load_wpk(h.enc, weights_path, 0);
+    if (st == tb::OK && host_path && host_path[0]) st = tb_encoder_load_wpk(h.enc, host_path, 0);
+    if (st != tb::OK) {
+        if (h.enc) tb_encoder_close(h.enc);
+        return st;
+    }
+    h.touch();
+    e->encoders.push_back(h);
+    return tb::OK;
+}
+
+// Engine::encoder (engine.rs:244-250): encoder `name`, its keep-alive started again.
+int tb_engine_encoder(tb_engine* e, const char* name, tb_encoder** out) {
+    if (!e || !name || !out) return tb::fail(tb::OUT_OF_RANGE, "tb_engine_encoder: null argument");
+    *out = nullptr;
+    e->expire();
+    const int k = e->held(name);
+    if (k < 0) return tb::fail(tb::NO_MODEL, std::string("engine: no model named ") + name);
+    e->encoders[k].touch();
+    *out = e->encoders[k].enc;
+    return tb::OK;
+}
+
+// Engine::embed (engine.rs:258-262) from token ids: the tokenizer stays with the caller.
+int tb_engine_embed(tb_engine* e, const char* name, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host) {
+    tb_encoder* enc = nullptr;
+    TB_TRY(tb_engine_encoder(e, name, &enc));
+    return tb_encoder_embed(enc, ids, lens, sequences, out_host);
 }
 
 int tb_engine_usage(const tb_engine* e, size_t* vram, size_t* host) {

@@ -213,8 +213,13 @@ int tb_wpk_read(const tb_wpk* w, uint32_t index, void* host, size_t bytes, int v
     return OK;
 }
 
-int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify) {
-    if (!dec) return fail(OUT_OF_RANGE, "tb_decoder_load_wpk: null decoder");
+}  // extern "C"
+
+namespace {
+
+// Every tensor of the file through `load` (name, bytes in pinned memory, length), in the file's order.
+template <typename F>
+int load_all(const char* what, const char* path, int verify, F&& load) {
     tb_wpk* w = nullptr;
     TB_TRY(tb_wpk_open(path, &w));
     // One pinned staging buffer, as large as the largest tensor: the upload is a straight copy from it.
@@ -223,17 +228,33 @@ int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify) {
     void* stage = nullptr;
     if (most > 0 && cudaMallocHost(&stage, most) != cudaSuccess) {
         tb_wpk_close(w);
-        return fail(OUT_OF_MEMORY, "tb_decoder_load_wpk: no pinned memory for the staging buffer");
+        return fail(OUT_OF_MEMORY, std::string(what) + ": no pinned memory for the staging buffer");
     }
     int st = OK;
     for (uint32_t i = 0; i < w->tensors.size() && st == OK; i++) {
         const tb_wpk::Entry& e = w->tensors[i];
         st = tb_wpk_read(w, i, stage, (size_t)e.len, verify);
-        if (st == OK) st = tb_decoder_load(dec, e.name.c_str(), stage, (size_t)e.len);
+        if (st == OK) st = load(e.name.c_str(), stage, (size_t)e.len);
     }
     if (stage) cudaFreeHost(stage);
     tb_wpk_close(w);
     return st;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify) {
+    if (!dec) return fail(OUT_OF_RANGE, "tb_decoder_load_wpk: null decoder");
+    return load_all("tb_decoder_load_wpk", path, verify, [&](const char* name, const void* data, size_t bytes) { return tb_decoder_load(dec, name, data, bytes); });
+}
+
+// An encoder's converted files (encoder/convert.rs: weights.wpk with the layers' matrices and norms, host.wpk with `embed`), each
+// tensor under its own name through tb_encoder_load.
+int tb_encoder_load_wpk(tb_encoder* enc, const char* path, int verify) {
+    if (!enc) return fail(OUT_OF_RANGE, "tb_encoder_load_wpk: null encoder");
+    return load_all("tb_encoder_load_wpk", path, verify, [&](const char* name, const void* data, size_t bytes) { return tb_encoder_load(enc, name, data, bytes); });
 }
 
 }  // extern "C"

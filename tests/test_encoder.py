@@ -143,6 +143,44 @@ def test_benchmark_variant_plain_ffn_mean_pool_truncated(ctx):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["q8e", "f16"])
+def test_a_converted_encoder_loads_from_its_files(ctx, tmp_path, fmt):
+    """weights.wpk (the layers) and host.wpk (`embed`), as the reference's conversion lays them out (encoder/convert.rs:60-110),
+    through tb_encoder_load_wpk: the bits of the tensor-by-tensor load; a tensor the encoder does not know is an error."""
+    import tachyon_b200 as tb
+    import wpk_writer as ww
+
+    cfg, weights, cases = fixture()
+    a, _ = build(ctx, cfg, weights, fmt=fmt)
+    device, host = [], []
+    for name, w in weights.items():
+        if name == "embed":
+            host.append((name, "f16", list(w.shape), w.astype(np.float16).tobytes()))
+        elif w.ndim == 2 and fmt == "q8e":
+            q, sc = oracle.q8e(w)
+            device.append((name, "i8", list(w.shape), q.astype(np.int8).tobytes()))
+            device.append((name + ".scale", "f32", [w.shape[0], w.shape[1] // 64], sc.astype(np.float32).tobytes()))
+        elif w.ndim == 2:
+            device.append((name, "f16", list(w.shape), w.astype(np.float16).tobytes()))
+        else:
+            device.append((name, "f32", list(w.shape), w.astype(np.float32).tobytes()))
+    ww.write(str(tmp_path / "weights.wpk"), device, crc=ww.fast_crc32c)
+    ww.write(str(tmp_path / "host.wpk"), host, crc=ww.fast_crc32c)
+    b = tb.Encoder(ctx, a.cfg, tokens=1024, sequences=16)
+    b._glob = a._glob
+    b.load_wpk(str(tmp_path / "weights.wpk"))
+    b.load_wpk(str(tmp_path / "host.wpk"))
+    seqs = [ids for ids, _ in cases]
+    assert np.array_equal(a.embed(seqs), b.embed(seqs))
+    ww.write(str(tmp_path / "odd.wpk"), [("nobody", "f32", [4], np.zeros(4, np.float32).tobytes())])
+    with pytest.raises(tb.Error):
+        b.load_wpk(str(tmp_path / "odd.wpk"))
+    with pytest.raises(tb.Error):
+        b.load_wpk(str(tmp_path / "missing.wpk"))
+    a.close(), b.close()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fmt,bound,cosine", [("q8e", 2e-2, 0.9999), ("f16", 1e-2, 0.99999)])
 def test_a_converted_models_matrices_load_as_they_are(ctx, fmt, bound, cosine):
     """The tiny encoder with its layers in Q8E or f16, as the reference's conversion writes them (encoder/convert.rs:79-95;

@@ -239,3 +239,100 @@ def test_the_engine_refuses_what_it_cannot_load_and_stays_as_it_was(ctx, model, 
     e.load("a", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)  # loading a name again replaces the model
     assert [m["name"] for m in e.models()] == ["a"] and answer(e, "a") == want
     e.close()
+
+
+def encoder_files(d, fmt, seed=3, h=256, heads=4, inter=512, vocab=500, layers=3):
+    """A small encoder as encoder::convert writes it (crates/tachyon/src/encoder/convert.rs:60-110): weights.wpk with the layers
+    in Q8E (i8 codes, f32 scales per 64) or f16, host.wpk with `embed`; and its configuration."""
+    import oracle
+
+    rng = np.random.default_rng(seed)
+    glob = np.array([l % 3 == 0 for l in range(layers)], np.uint8)
+    cfg = tb.EncoderConfig(hidden=h, heads=heads, inter=inter, vocab=vocab, layers=layers, window=8, global_=glob.ctypes.data, global_every=0,
+                           theta_global=160000.0, theta_local=10000.0, eps=1e-5, gated=1, mean_pool=1, dims=h)
+    device = [("embed_norm", "f32", [h], rng.uniform(0.5, 1.5, h).astype(np.float32).tobytes()),
+              ("final_norm", "f32", [h], rng.uniform(0.5, 1.5, h).astype(np.float32).tobytes())]
+    for l in range(layers):
+        for name in (["attn_norm"] if l else []) + ["mlp_norm"]:
+            device.append((f"{l}.{name}", "f32", [h], rng.uniform(0.5, 1.5, h).astype(np.float32).tobytes()))
+        for name, shape in (("qkv", (3 * h, h)), ("o", (h, h)), ("up", (2 * inter, h)), ("down", (h, inter))):
+            w = (rng.standard_normal(shape) * 0.05).astype(np.float32)
+            if fmt == "f16":
+                device.append((f"{l}.{name}", "f16", list(shape), w.astype(np.float16).tobytes()))
+            else:
+                q, sc = oracle.q8e(w)
+                device.append((f"{l}.{name}", "i8", list(shape), q.astype(np.int8).tobytes()))
+                device.append((f"{l}.{name}.scale", "f32", [shape[0], shape[1] // 64], sc.astype(np.float32).tobytes()))
+    host = [("embed", "f16", [vocab, h], rng.standard_normal((vocab, h)).astype(np.float16).tobytes())]
+    ww.write(str(d / "weights.wpk"), device, crc=ww.fast_crc32c)
+    ww.write(str(d / "host.wpk"), host, crc=ww.fast_crc32c)
+    return cfg, glob, str(d / "weights.wpk"), str(d / "host.wpk")
+
+
+@pytest.mark.parametrize("fmt", ["q8e", "f16"])
+def test_the_engine_holds_encoders_in_vram(ctx, model, tmp_path, fmt):
+    """engine.rs:225-262, 288-293, 317-319: an encoder is held by name, always in VRAM and counted against the limit; decoders move
+    out to make room for it and it never moves; its keep-alive drops it; its embeddings are the encoder's own."""
+    cfg, weights, host = model
+    need = tb.decoder_footprint(ctx, cfg, **SETTINGS)
+    V, H = tb.TIER_VRAM, tb.TIER_HOST
+    ecfg, glob, ew, eh = encoder_files(tmp_path, fmt)
+    seqs = [[1, 2, 3, 4, 5, 6, 7], list(range(10, 90)), [499, 0, 250]]
+    alone = tb.Encoder(ctx, ecfg, tokens=512, sequences=8)
+    alone.load_wpk(ew), alone.load_wpk(eh)
+    want = alone.embed(seqs)
+    held = alone.bytes()
+    assert held == tb.encoder_footprint(ctx, ecfg, tokens=512, sequences=8, f16_matrices=fmt == "f16")
+    alone.close()
+    assert np.isfinite(want).all() and np.abs(want).max() > 0
+
+    e = tb.Engine(ctx, vram_limit=need + held + held // 2)
+    e.load("a", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    before = answer(e, "a")
+    e.load_encoder("enc", ecfg, ew, eh, tokens=512, sequences=8, keep_alive_ms=tb.FOR_GOOD)
+    assert [e.tier("a"), e.tier("enc")] == [V, V] and e.usage()[0] == need + held
+    assert np.array_equal(e.embed("enc", seqs), want)
+    # A second decoder: `a` gives way, the encoder does not, though it was used before `a`'s last use.
+    answer(e, "a", 1)
+    e.load("b", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert [e.tier("a"), e.tier("b"), e.tier("enc")] == [H, V, V]
+    listed = e.models()
+    assert [m["name"] for m in listed] == ["a", "b", "enc"] and [m["vram"] for m in listed] == [0, need, held]
+    assert listed[2]["tier"] == V and listed[2]["left_ms"] == tb.FOR_GOOD
+    # A second encoder does not fit beside a pinned decoder and the first: refused, nothing changes.
+    e.load("b", cfg, weights, host, pin=True, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    with pytest.raises(tb.Error) as err:
+        e.load_encoder("enc2", ecfg, ew, eh, tokens=512, sequences=8)
+    assert err.value.status == 7  # TB_OUT_OF_MEMORY
+    with pytest.raises(tb.Error):
+        e.tier("enc2")
+    assert np.array_equal(e.embed("enc", seqs), want)
+    with pytest.raises(tb.Error):
+        answer(e, "a")  # the pinned b and the encoder leave no room
+    assert e.tier("a") == H
+    e.load("b", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert answer(e, "a") == before and [e.tier("a"), e.tier("b"), e.tier("enc")] == [V, H, V]
+    # A decoder's name is not an encoder's and the other way round.
+    with pytest.raises(tb.Error) as err:
+        e.embed("b", seqs)
+    assert err.value.status == 8  # TB_NO_MODEL
+    with pytest.raises(tb.Error):
+        e.decoder("enc")
+    # Keep-alive: loaded again with 50 ms, it is dropped by the next call after that.
+    e.load_encoder("enc", ecfg, ew, eh, tokens=512, sequences=8, keep_alive_ms=50)
+    assert e.models()[-1]["left_ms"] <= 50
+    time.sleep(0.06)
+    e.expire()
+    with pytest.raises(tb.Error):
+        e.tier("enc")
+    assert all(m["name"] != "enc" for m in e.models())
+    # Unload takes an encoder's name; a missing file loads nothing.
+    e.load_encoder("enc", ecfg, ew, eh, tokens=512, sequences=8, pin=True, keep_alive_ms=0)
+    e.expire()
+    assert e.tier("enc") == V, "pinned"
+    assert e.unload("enc") and not e.unload("enc")
+    with pytest.raises(tb.Error):
+        e.load_encoder("enc", ecfg, str(tmp_path / "none.wpk"), eh)
+    assert all(m["name"] != "enc" for m in e.models())
+    e.close()
+    del glob
