@@ -160,7 +160,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint32_t tmem, 
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         float f0 = __uint_as_float(r[8 * i + 2 * e]), f1 = __uint_as_float(r[8 * i + 2 * e + 1]);
-                        if (g.mode == 5) f0 = gelu_erf(f0), f1 = gelu_erf(f1);
+                        if (g.mode == 5) f0 = gelu_erf_lean(f0), f1 = gelu_erf_lean(f1);
                         if (g.mode == 7) f0 = fmaxf(f0, 0.0f), f1 = fmaxf(f1, 0.0f);
                         const __half2 t = __floats2half2_rn(f0, f1);
                         h[e] = *reinterpret_cast<const uint32_t*>(&t);
@@ -176,8 +176,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, uint32_t tmem, 
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         const float g0 = __uint_as_float(r[16 * i + 4 * e]), g1 = __uint_as_float(r[16 * i + 4 * e + 2]);
-                        const float a0 = (g.mode == 2 ? gelu_tanh(g0) : g.mode == 8 ? silu(g0) : gelu_erf(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
-                        const float a1 = (g.mode == 2 ? gelu_tanh(g1) : g.mode == 8 ? silu(g1) : gelu_erf(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
+                        const float a0 = (g.mode == 2 ? gelu_tanh(g0) : g.mode == 8 ? silu(g0) : gelu_erf_lean(g0)) * __uint_as_float(r[16 * i + 4 * e + 1]);
+                        const float a1 = (g.mode == 2 ? gelu_tanh(g1) : g.mode == 8 ? silu(g1) : gelu_erf_lean(g1)) * __uint_as_float(r[16 * i + 4 * e + 3]);
                         const __half2 t = __floats2half2_rn(a0, a1);
                         h[e] = *reinterpret_cast<const uint32_t*>(&t);
                     }

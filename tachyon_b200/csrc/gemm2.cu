@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
 #pragma unroll
                     for (int k = 0; k < 16; k++) {
                         float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
-                        if (g.mode == 5) v0 = gelu_erf(v0), v1 = gelu_erf(v1);
+                        if (g.mode == 5) v0 = gelu_erf_lean(v0), v1 = gelu_erf_lean(v1);
                         if (g.mode == 6) {
                             v0 = mb + 2 * k < g.M ? gelu_tanh(v0) * __ldg(mrow + (size_t)(2 * k) * g.mul_stride) : 0.0f;
                             v1 = mb + 2 * k + 1 < g.M ? gelu_tanh(v1) * __ldg(mrow + (size_t)(2 * k + 1) * g.mul_stride) : 0.0f;
@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         const float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
                         const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);  // even: up of the even token; odd: gate of the odd token
                         const float gate = odd ? got : v0, up = odd ? v1 : got;
-                        const float a = (g.mode == 2 ? gelu_tanh(gate) : gelu_erf(gate)) * up;
+                        const float a = (g.mode == 2 ? gelu_tanh(gate) : gelu_erf_lean(gate)) * up;
                         const float other = __shfl_xor_sync(0xffffffffu, a, 2);  // output j + 1 (or j) of the same token
                         const __half2 pair = second ? __floats2half2_rn(other, a) : __floats2half2_rn(a, other);
                         if (!second && mb + 2 * k + (odd ? 1 : 0) < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * (g.N / 2)) = pair;
