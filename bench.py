@@ -568,6 +568,66 @@ def bench_switch(args, ranks: Ranks):
             "link_gb_per_second": link, "fraction_of_link": weights / sec / 1e9 / link}
 
 
+def bench_load(args, ranks: Ranks):
+    """The disk tier's way into VRAM (the reference's benches/load.rs: a .wpk streamed into device memory): the benchmark's decoder
+    written as a converted model's weights.wpk (random codes, the file then in the page cache), and tb_decoder_load_wpk timed with
+    the reader threads and with the reads on the calling thread, unchecked and with every tensor's CRC32C checked."""
+    import shutil
+    import tempfile
+
+    import tachyon_b200 as tb
+
+    ctx = tb.Context(ranks.local)
+    cfg = tb.gemma4_e4b_shape(layers=args.layers)
+    h, q = cfg.hidden, (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim
+    rng = np.random.default_rng(SEED)
+    block = rng.integers(-127, 128, 1 << 26, dtype=np.int8)
+    scales = np.full(1 << 24, 0.02 / 127.0, np.float16)
+    d = tempfile.mkdtemp(prefix="tachyon_b200_load_", dir=os.environ.get("TACHYON_B200_BENCH_DIR"))
+    path = os.path.join(d, "weights.wpk")
+    try:
+        with tb.WpkWriter(path) as w:
+            def mat(name, rows, cols):
+                n = rows * cols
+                codes = block[:n] if n <= block.size else np.tile(block, -(-n // block.size))[:n]
+                w.add(name + ".w", "i8", [rows, cols], codes)
+                w.add(name + ".s", "f16", [rows, cols // 32], scales[: rows * cols // 32])
+
+            mat("embed", cfg.vocab, h)
+            w.add("norm", "f32", [h], np.ones(h, np.float32))
+            for l in range(cfg.layers):
+                mat(f"{l}.qkv", q, h), mat(f"{l}.o", h, cfg.heads * cfg.head_dim), mat(f"{l}.gate_up", 2 * cfg.ffn, h), mat(f"{l}.down", h, cfg.ffn)
+                for name, n in (("q_norm", cfg.head_dim), ("k_norm", cfg.head_dim), ("input_layernorm", h), ("post_attention_layernorm", h),
+                                ("pre_feedforward_layernorm", h), ("post_feedforward_layernorm", h), ("layer_scalar", 1)):
+                    w.add(f"{l}.{name}", "f32", [n], np.ones(n, np.float32))
+        size = os.path.getsize(path)
+        times = {}
+        tok = None
+        for readers, verify in ((8, False), (0, False), (8, True), (0, True), (4, False), (16, False), (8, False)):
+            os.environ["TACHYON_B200_LOAD_READERS"] = str(readers)
+            dec = tb.Decoder(ctx, cfg, context=CONTEXT, chunk=512, keep_logits=False, prefill_copy=1)
+            ctx.sync()
+            t0 = time.perf_counter()
+            dec.load_wpk(path, verify=verify)
+            ctx.sync()
+            times.setdefault((readers, verify), []).append(time.perf_counter() - t0)
+            dec.build()
+            got = dec.step(7)
+            assert tok is None or got == tok, "every way of loading gives the same model"
+            tok = got
+            dec.close()
+        os.environ.pop("TACHYON_B200_LOAD_READERS", None)
+        ctx.trim()
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
+    sec = min(times[(8, False)])
+    return {"metric": "load_from_disk_tier_gb_per_second", "value": size / sec / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": len(times[(8, False)]), "warmup": 0,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "u8", "data": "synthetic", "impl": "ours",
+            "config": {"workload": f"the benchmark's decoder ({args.layers} layers) as a weights.wpk of {size} B in the page cache, read into VRAM by tb_decoder_load_wpk (eight reader threads, pieces of 16 MiB, twelve pinned slots)"},
+            "gpu_launches": None, "streamed_s": sec, "on_the_calling_thread_s": min(times[(0, False)]), "streamed_checked_s": min(times[(8, True)]),
+            "on_the_calling_thread_checked_s": min(times[(0, True)]), "four_readers_s": min(times[(4, False)]), "sixteen_readers_s": min(times[(16, False)])}
+
+
 def bench_flash(args, ranks: Ranks):
     """configs[3]'s attention alone: 2048 tokens x 8 query / 2 kv heads of 256 over the cache ring, sliding 512 and global."""
     import tachyon_b200 as tb
@@ -734,7 +794,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder", "switch"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder", "switch", "load"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -770,6 +830,8 @@ def main():
             line = bench_encoder(args, ranks)
         elif args.workload == "switch":
             line = bench_switch(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "load":
+            line = bench_load(args, ranks) if ranks.rank == 0 else None
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if not args.no_extras:

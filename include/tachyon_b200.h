@@ -476,6 +476,8 @@ typedef struct tb_wpk_info {
 } tb_wpk_info;
 /* CRC32C (Castagnoli) of `bytes` bytes continuing from `crc` (wpk/mod.rs:105-123); tb_crc32c(0, "123456789", 9) is 0xE3069283. */
 TB_API uint32_t tb_crc32c(uint32_t crc, const void* data, size_t bytes);
+/* CRC32C of A followed by B from tb_crc32c(0, A), tb_crc32c(0, B) and B's length: pieces of a tensor checked apart. */
+TB_API uint32_t tb_crc32c_combine(uint32_t crc_a, uint32_t crc_b, uint64_t len_b);
 /* Wpk::open (wpk/mod.rs:190-213): checks the header, the table's checksum and every table entry; TB_FORMAT with the
  * reference's message when a check fails, TB_IO when the file cannot be read. */
 TB_API int tb_wpk_open(const char* path, tb_wpk** out);

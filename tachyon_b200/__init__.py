@@ -356,6 +356,60 @@ def crc32c(data: bytes, crc: int = 0) -> int:
     return int(_lib.load().tb_crc32c(crc, buf.ctypes.data if buf.size else None, buf.size))
 
 
+def crc32c_combine(crc_a: int, crc_b: int, len_b: int) -> int:
+    """tb_crc32c_combine: the checksum of A followed by B from the two checksums and B's length."""
+    return int(_lib.load().tb_crc32c_combine(crc_a, crc_b, len_b))
+
+
+class WpkWriter:
+    """wpk::Writer (crates/tachyon/src/wpk/mod.rs:270-337): writes a `.wpk` tensor by tensor, each on a 4 KiB boundary, then the
+    table and the header.  Host code; the checksums come from tb_crc32c."""
+
+    ALIGN = 4096
+    DTYPES = {"f32": (0, 4), "f16": (1, 2), "bf16": (2, 2), "f8e4m3": (3, 1), "i8": (4, 1), "u8": (5, 1)}
+
+    def __init__(self, path: str):
+        self.f = open(path, "wb")
+        self.f.write(b"\0" * self.ALIGN)
+        self.table, self.data_len = [], 0
+
+    def add(self, name: str, dtype: str, shape, raw) -> None:
+        import struct
+
+        raw = memoryview(raw).cast("B")
+        code, size = self.DTYPES[dtype]
+        n = size
+        for d in shape:
+            n *= int(d)
+        if n != len(raw):
+            raise ValueError(f"{name}: {len(raw)} bytes for {dtype} {tuple(shape)}")
+        entry = struct.pack("<H", len(name.encode())) + name.encode() + bytes([code, len(shape)])
+        entry += b"".join(struct.pack("<Q", int(v)) for v in list(shape) + [self.data_len, len(raw)]) + struct.pack("<I", crc32c(raw))
+        self.table.append(entry)
+        self.f.write(raw)
+        pad = -len(raw) % self.ALIGN
+        self.f.write(b"\0" * pad)
+        self.data_len += len(raw) + pad
+
+    def close(self) -> None:
+        import struct
+
+        table = b"".join(self.table)
+        self.f.write(table)
+        head = b"TACHYWPK" + struct.pack("<QQQQ", 1 | len(self.table) << 32, self.data_len, self.ALIGN + self.data_len, len(table))
+        head += struct.pack("<I", crc32c(table))
+        head += struct.pack("<I", crc32c(head))
+        self.f.seek(0)
+        self.f.write(head)
+        self.f.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 class Parked:
     """model::Parked (decode.rs:101-109, 449-469): a model in the host-RAM tier."""
 

@@ -144,6 +144,7 @@ SIGNATURES = {
     "tb_decoder_hidden": (i32, [vp, vp]),
     "tb_decoder_set_sampling": (i32, [vp, vp]),
     "tb_crc32c": (u32, [u32, vp, sz]),
+    "tb_crc32c_combine": (u32, [u32, u32, u64]),
     "tb_wpk_open": (i32, [cp, pp]),
     "tb_wpk_close": (None, [vp]),
     "tb_wpk_count": (u32, [vp]),

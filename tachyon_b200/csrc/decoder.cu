@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include "internal.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -828,6 +829,50 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
     cudaFree(tmp);
     if (e != cudaSuccess) return cuda_fail(e, "tb_decoder_load");
     return st;
+}
+
+// For the file loader: a tensor may arrive in pieces.  One that is copied to its place as it is has each piece written at its
+// offset.  The gate/up matrix (gate rows, then up rows in the file; pairs (gate_j, up_j) on the device) has each piece's
+// rows scattered by strided copies: file row r goes to device row 2 r, or 2 (r - ffn) + 1 past the first half; a piece
+// that starts or ends inside a row has that part copied alone.
+int tb_decoder_load_part(tb_decoder* d, const char* name, size_t offset, const void* data, size_t bytes, size_t total) {
+    if (!d || !name || !data) return fail(OUT_OF_RANGE, "tb_decoder_load_part: null argument");
+    Named t;
+    if (!find_tensor(d, name, t)) return fail(NO_MODEL, std::string("tb_decoder_load: no tensor named ") + name);
+    if (t.kind == 3 || (offset == 0 && bytes == total && t.kind == 0)) return tb_decoder_load(d, name, data, bytes);
+    if (total != t.bytes) return fail(FORMAT, std::string("tb_decoder_load: ") + name + " has " + std::to_string(total) + " bytes, expected " + std::to_string(t.bytes));
+    if (offset > total || bytes > total - offset) return fail(OUT_OF_RANGE, "tb_decoder_load_part: a piece past the tensor's end");
+    d->copy_valid = false;
+    tb_decoder_drop_shadow(d);
+    cudaStream_t s = d->ctx->stream;
+    char* base = static_cast<char*>(t.ptr);
+    const char* src = static_cast<const char*>(data);
+    if (t.kind == 0) {
+        TB_CUDA(cudaMemcpyAsync(base + offset, src, bytes, cudaMemcpyDefault, s));
+    } else {
+        const size_t half_rows = d->cfg.ffn, row = total / (2 * half_rows);
+        while (bytes > 0) {
+            const size_t r = offset / row, in_row = offset % row;
+            char* dst = base + (r < half_rows ? 2 * r : 2 * (r - half_rows) + 1) * row;
+            size_t n;
+            if (in_row != 0 || bytes < row) {
+                n = std::min(row - in_row, bytes);
+                TB_CUDA(cudaMemcpyAsync(dst + in_row, src, n, cudaMemcpyHostToDevice, s));
+            } else {
+                const size_t rows = std::min(bytes / row, (r < half_rows ? half_rows : 2 * half_rows) - r);
+                n = rows * row;
+                TB_CUDA(cudaMemcpy2DAsync(dst, 2 * row, src, row, row, rows, cudaMemcpyHostToDevice, s));
+            }
+            offset += n, src += n, bytes -= n;
+        }
+    }
+    TB_CUDA(cudaStreamSynchronize(s));
+    return OK;
+}
+
+int tb_decoder_loads_in_parts(tb_decoder* d, const char* name) {
+    Named t;
+    return d && name && find_tensor(d, name, t) && t.kind != 3;
 }
 
 int tb_decoder_fill_random(tb_decoder* d, uint64_t seed) {

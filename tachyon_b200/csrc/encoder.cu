@@ -747,6 +747,26 @@ int tb_encoder_load(tb_encoder* e, const char* name, const void* data, size_t by
     return st;
 }
 
+// For the file loader: a tensor that is copied to its place as it is (the embedding table, the norms) may arrive in pieces.
+int tb_encoder_load_part(tb_encoder* e, const char* name, size_t offset, const void* data, size_t bytes, size_t total) {
+    if (!e || !name || !data) return fail(OUT_OF_RANGE, "tb_encoder_load_part: null argument");
+    if (offset == 0 && bytes == total) return tb_encoder_load(e, name, data, bytes);
+    ENamed t;
+    if (!enc_find(e, name, t)) return fail(NO_MODEL, std::string("tb_encoder_load: no tensor named ") + name);
+    if (t.kind != 0) return fail(UNSUPPORTED, std::string("tb_encoder_load_part: ") + name + " is rearranged on the way and comes whole");
+    if (total != t.bytes) return fail(FORMAT, std::string("tb_encoder_load: ") + name + " has " + std::to_string(total) + " bytes, expected " + std::to_string(t.bytes));
+    if (offset > total || bytes > total - offset) return fail(OUT_OF_RANGE, "tb_encoder_load_part: a piece past the tensor's end");
+    TB_CUDA(cudaSetDevice(e->ctx->gpu));
+    TB_CUDA(cudaMemcpyAsync(static_cast<char*>(t.ptr) + offset, data, bytes, cudaMemcpyHostToDevice, e->ctx->stream));
+    TB_CUDA(cudaStreamSynchronize(e->ctx->stream));
+    return OK;
+}
+
+int tb_encoder_loads_in_parts(tb_encoder* e, const char* name) {
+    ENamed t;
+    return e && name && enc_find(e, name, t) && t.kind == 0;
+}
+
 int tb_encoder_fill_random(tb_encoder* e, uint64_t seed) {
     if (!e) return fail(OUT_OF_RANGE, "null encoder");
     e->copy_valid = false;

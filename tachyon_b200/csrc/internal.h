@@ -391,3 +391,13 @@ inline cudaError_t launch_kernel(tb_context* ctx, void (*kernel)(KArgs...), dim3
 }
 
 }  // namespace tb
+
+// The file loader's way into a model (wpk.cu): a tensor that is copied to its place as it is may arrive in pieces.
+struct tb_decoder;
+struct tb_encoder;
+extern "C" {
+int tb_decoder_load_part(tb_decoder* dec, const char* name, size_t offset, const void* data, size_t bytes, size_t total);
+int tb_decoder_loads_in_parts(tb_decoder* dec, const char* name);
+int tb_encoder_load_part(tb_encoder* enc, const char* name, size_t offset, const void* data, size_t bytes, size_t total);
+int tb_encoder_loads_in_parts(tb_encoder* enc, const char* name);
+}

@@ -2,16 +2,22 @@
 // header (magic, version and tensor count, sizes, CRC32C of the table and of itself), the tensors' bytes each on a
 // 4 KiB boundary, and a table with every tensor's name, element type, shape, offset, length and CRC32C.  Host code only:
 // a converted model's weights.wpk is opened, checked as Wpk::open checks it, and its tensors handed to the decoder by
-// their converted-model names (model/mod.rs:178-286).  The reference's loader streams the file with O_DIRECT into
-// pinned memory (wpk/load.rs); this one reads each tensor with pread into a pinned staging buffer.
+// their converted-model names (model/mod.rs:178-286).  Loading streams the file as the reference's loader does
+// (wpk/load.rs: reads in flight into pinned staging slots, each uploaded while the other reads proceed): reader threads
+// fill a ring of pinned slots with pread, the calling thread uploads them in the file's order.
 #include "../../include/tachyon_b200.h"
 #include "internal.h"
 
+#include <algorithm>
+#include <atomic>
 #include <cerrno>
+#include <condition_variable>
 #include <cstring>
 #include <fcntl.h>
+#include <mutex>
 #include <string>
 #include <sys/stat.h>
+#include <thread>
 #include <unistd.h>
 #include <vector>
 
@@ -47,7 +53,34 @@ struct CrcTable {
     }
 };
 
+// The processor's own CRC32C instruction where it has one (SSE4.2: CPUID leaf 1, ECX bit 20), as the reference's crc32c
+// prefers it over crc32c_soft (wpk/mod.rs:105-123).
+bool has_crc_instruction() {
+#if defined(__x86_64__)
+    static const bool has = [] {
+        uint32_t a = 1, b = 0, c = 0, d = 0;
+        asm volatile("cpuid" : "+a"(a), "=b"(b), "+c"(c), "=d"(d));
+        return (c >> 20 & 1u) != 0;
+    }();
+    return has;
+#else
+    return false;
+#endif
+}
+
 uint32_t crc32c(uint32_t crc, const uint8_t* p, size_t n) {
+#if defined(__x86_64__)
+    if (has_crc_instruction()) {
+        uint64_t c = (uint32_t)~crc;
+        for (; n >= 8; p += 8, n -= 8) {
+            uint64_t v;
+            memcpy(&v, p, 8);
+            asm("crc32q %1, %0" : "+r"(c) : "r"(v));
+        }
+        for (; n > 0; p++, n--) asm("crc32b %1, %0" : "+r"(c) : "r"(*p));
+        return ~(uint32_t)c;
+    }
+#endif
     static const CrcTable tables;  // built once, by whichever thread comes first
     const uint32_t (*table)[256] = tables.t;
     uint32_t c = ~crc;
@@ -61,6 +94,38 @@ uint32_t crc32c(uint32_t crc, const uint8_t* p, size_t n) {
     }
     while (n--) c = (c >> 8) ^ table[0][(c ^ *p++) & 255u];
     return ~c;
+}
+
+// CRC32C of a string A B from crc(A), crc(B) and B's length: crc(A) advanced through len(B) zero bytes (the register times
+// x^(8 len) modulo the polynomial, by squaring a 32 x 32 matrix over GF(2)), then xor crc(B).  It lets the loader's reader
+// threads each check their own piece of a tensor.
+uint32_t gf2_times(const uint32_t* mat, uint32_t vec) {
+    uint32_t sum = 0;
+    for (; vec; vec >>= 1, mat++)
+        if (vec & 1u) sum ^= *mat;
+    return sum;
+}
+
+uint32_t crc32c_combine(uint32_t crc_a, uint32_t crc_b, uint64_t len_b) {
+    if (len_b == 0) return crc_a;
+    uint32_t even[32], odd[32];
+    odd[0] = 0x82F63B78u;  // one zero bit: shift right, the polynomial where a bit falls out
+    for (int n = 1; n < 32; n++) odd[n] = 1u << (n - 1);
+    auto square = [](uint32_t* to, const uint32_t* from) {
+        for (int n = 0; n < 32; n++) to[n] = gf2_times(from, from[n]);
+    };
+    square(even, odd);  // two zero bits
+    square(odd, even);  // four
+    do {                // from here each squaring doubles the zero bytes: one, two, four ...
+        square(even, odd);
+        if (len_b & 1u) crc_a = gf2_times(even, crc_a);
+        len_b >>= 1;
+        if (len_b == 0) break;
+        square(odd, even);
+        if (len_b & 1u) crc_a = gf2_times(odd, crc_a);
+        len_b >>= 1;
+    } while (len_b != 0);
+    return crc_a ^ crc_b;
 }
 
 // Little-endian fields; past the end it yields zeros and remembers it (the reference's Cursor, wpk/mod.rs:125-144).
@@ -106,6 +171,8 @@ using namespace tb;
 extern "C" {
 
 uint32_t tb_crc32c(uint32_t crc, const void* data, size_t bytes) { return crc32c(crc, static_cast<const uint8_t*>(data), bytes); }
+
+uint32_t tb_crc32c_combine(uint32_t crc_a, uint32_t crc_b, uint64_t len_b) { return crc32c_combine(crc_a, crc_b, len_b); }
 
 int tb_wpk_open(const char* path, tb_wpk** out) {
     if (!path || !out) return fail(OUT_OF_RANGE, "tb_wpk_open: null argument");
@@ -217,25 +284,122 @@ int tb_wpk_read(const tb_wpk* w, uint32_t index, void* host, size_t bytes, int v
 
 namespace {
 
-// Every tensor of the file through `load` (name, bytes in pinned memory, length), in the file's order.
-template <typename F>
-int load_all(const char* what, const char* path, int verify, F&& load) {
+// The file's tensors into a model, streamed (Loader::to_device, wpk/load.rs:20-60, with threads and pread where that has an
+// io_uring): the tensors are cut into pieces of at most a slot, READERS threads read pieces into a ring of DEPTH pinned slots,
+// checking each piece's CRC32C if asked, and the calling thread takes the pieces in the file's order, joins the pieces' sums
+// into the tensor's, and hands each piece to `put` (name, offset in the tensor, bytes, length, the tensor's length), which
+// uploads it.  A tensor that `in_parts` refuses comes as one piece, and the slots are as large as the largest of those.
+// TACHYON_B200_LOAD_READERS=0 reads on the calling thread instead (the pieces and the checks are the same);
+// TACHYON_B200_LOAD_SLOT_KB sets the size of a piece (a test cuts small tensors with it).
+constexpr size_t SLOT_BYTES = (size_t)16 << 20;  // wpk/load.rs:19 CHUNK
+constexpr int DEPTH = 12, READERS = 8;
+
+struct Piece {
+    uint32_t tensor;
+    size_t offset, len;
+};
+
+template <typename P, typename F>
+int load_all(const char* what, const char* path, int verify, P&& in_parts, F&& put) {
     tb_wpk* w = nullptr;
     TB_TRY(tb_wpk_open(path, &w));
-    // One pinned staging buffer, as large as the largest tensor: the upload is a straight copy from it.
-    size_t most = 0;
-    for (const tb_wpk::Entry& e : w->tensors) most = e.len > most ? (size_t)e.len : most;
-    void* stage = nullptr;
-    if (most > 0 && cudaMallocHost(&stage, most) != cudaSuccess) {
-        tb_wpk_close(w);
-        return fail(OUT_OF_MEMORY, std::string(what) + ": no pinned memory for the staging buffer");
-    }
-    int st = OK;
-    for (uint32_t i = 0; i < w->tensors.size() && st == OK; i++) {
+    const char* env = getenv("TACHYON_B200_LOAD_SLOT_KB");
+    const size_t SLOT = env && atoll(env) > 0 ? std::max<size_t>(ALIGN, ((size_t)atoll(env) << 10) / ALIGN * ALIGN) : SLOT_BYTES;
+    size_t slot = 0;
+    std::vector<Piece> pieces;
+    for (uint32_t i = 0; i < w->tensors.size(); i++) {
         const tb_wpk::Entry& e = w->tensors[i];
-        st = tb_wpk_read(w, i, stage, (size_t)e.len, verify);
-        if (st == OK) st = load(e.name.c_str(), stage, (size_t)e.len);
+        const size_t len = (size_t)e.len;
+        if (len <= SLOT || !in_parts(e.name.c_str())) {
+            pieces.push_back({i, 0, len});
+            slot = std::max(slot, len);
+        } else {
+            for (size_t at = 0; at < len; at += SLOT) pieces.push_back({i, at, std::min(SLOT, len - at)});
+            slot = std::max(slot, SLOT);
+        }
     }
+    slot = (slot + ALIGN - 1) / ALIGN * ALIGN;
+    const size_t depth = std::min<size_t>(DEPTH, pieces.size());
+    char* stage = nullptr;
+    if (slot > 0 && cudaMallocHost(reinterpret_cast<void**>(&stage), depth * slot) != cudaSuccess) {
+        cudaGetLastError();
+        tb_wpk_close(w);
+        return fail(OUT_OF_MEMORY, std::string(what) + ": no pinned memory for the staging slots");
+    }
+    env = getenv("TACHYON_B200_LOAD_READERS");
+    const int readers = slot == 0 ? 0 : env ? std::max(0, std::min(16, atoi(env))) : READERS;
+
+    // Piece i lives in slot i % depth: read once piece i - depth has been taken (taken > i - depth), taken once it is read.
+    std::mutex m;
+    std::condition_variable cv;
+    std::vector<uint8_t> read_done(pieces.size(), 0);
+    std::vector<uint32_t> sums(pieces.size(), 0);
+    size_t taken = 0;
+    std::atomic<size_t> next{0};
+    bool stop = false;
+    int read_errno = 0;
+    size_t failed_piece = SIZE_MAX;
+    auto read_piece = [&](size_t i) {
+        const Piece& pc = pieces[i];
+        const tb_wpk::Entry& e = w->tensors[pc.tensor];
+        errno = 0;
+        return read_at(w->fd, stage + (i % depth) * slot, pc.len, ALIGN + e.offset + pc.offset);
+    };
+    auto reader = [&] {
+        for (;;) {
+            const size_t i = next.fetch_add(1);
+            if (i >= pieces.size()) return;
+            {
+                std::unique_lock<std::mutex> lock(m);
+                cv.wait(lock, [&] { return stop || taken + depth > i; });
+                if (stop) return;
+            }
+            const bool ok = read_piece(i);
+            const int err = errno;
+            if (ok && verify) sums[i] = crc32c(0, reinterpret_cast<const uint8_t*>(stage + (i % depth) * slot), pieces[i].len);
+            std::lock_guard<std::mutex> lock(m);
+            if (!ok && failed_piece == SIZE_MAX) failed_piece = i, read_errno = err;
+            read_done[i] = 1;
+            cv.notify_all();
+        }
+    };
+    std::vector<std::thread> threads;
+    for (int k = 0; k < readers; k++) threads.emplace_back(reader);
+
+    int st = OK;
+    uint32_t crc = 0;
+    for (size_t i = 0; i < pieces.size() && st == OK; i++) {
+        const Piece& pc = pieces[i];
+        const tb_wpk::Entry& e = w->tensors[pc.tensor];
+        bool ok = true;
+        int err = 0;
+        if (readers == 0) {
+            ok = read_piece(i), err = errno;
+        } else {
+            std::unique_lock<std::mutex> lock(m);
+            cv.wait(lock, [&] { return read_done[i] != 0; });
+            if (failed_piece == i) ok = false, err = read_errno;
+        }
+        const char* data = stage + (i % depth) * slot;
+        if (!ok) st = fail(IO, std::string(what) + ": " + e.name + ": " + (err ? strerror(err) : "the file is truncated"));
+        if (st == OK && verify) {
+            const uint32_t sum = readers == 0 ? crc32c(0, reinterpret_cast<const uint8_t*>(data), pc.len) : sums[i];
+            crc = pc.offset == 0 ? sum : crc32c_combine(crc, sum, pc.len);
+            if (pc.offset + pc.len == e.len && crc != e.crc) st = fail(FORMAT, "tensor \"" + e.name + "\" is corrupt");  // Wpk::verify
+        }
+        if (st == OK) st = put(e.name.c_str(), pc.offset, data, pc.len, (size_t)e.len);
+        if (readers > 0) {
+            std::lock_guard<std::mutex> lock(m);
+            taken = i + 1;
+            cv.notify_all();
+        }
+    }
+    {
+        std::lock_guard<std::mutex> lock(m);
+        stop = true;
+        cv.notify_all();
+    }
+    for (std::thread& t : threads) t.join();
     if (stage) cudaFreeHost(stage);
     tb_wpk_close(w);
     return st;
@@ -247,14 +411,18 @@ extern "C" {
 
 int tb_decoder_load_wpk(tb_decoder* dec, const char* path, int verify) {
     if (!dec) return fail(OUT_OF_RANGE, "tb_decoder_load_wpk: null decoder");
-    return load_all("tb_decoder_load_wpk", path, verify, [&](const char* name, const void* data, size_t bytes) { return tb_decoder_load(dec, name, data, bytes); });
+    return load_all(
+        "tb_decoder_load_wpk", path, verify, [&](const char* name) { return tb_decoder_loads_in_parts(dec, name) != 0; },
+        [&](const char* name, size_t offset, const void* data, size_t bytes, size_t total) { return tb_decoder_load_part(dec, name, offset, data, bytes, total); });
 }
 
 // An encoder's converted files (encoder/convert.rs: weights.wpk with the layers' matrices and norms, host.wpk with `embed`), each
 // tensor under its own name through tb_encoder_load.
 int tb_encoder_load_wpk(tb_encoder* enc, const char* path, int verify) {
     if (!enc) return fail(OUT_OF_RANGE, "tb_encoder_load_wpk: null encoder");
-    return load_all("tb_encoder_load_wpk", path, verify, [&](const char* name, const void* data, size_t bytes) { return tb_encoder_load(enc, name, data, bytes); });
+    return load_all(
+        "tb_encoder_load_wpk", path, verify, [&](const char* name) { return tb_encoder_loads_in_parts(enc, name) != 0; },
+        [&](const char* name, size_t offset, const void* data, size_t bytes, size_t total) { return tb_encoder_load_part(enc, name, offset, data, bytes, total); });
 }
 
 }  // extern "C"

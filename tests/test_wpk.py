@@ -37,6 +37,19 @@ def test_crc32c_matches_the_standard_check_value():
     assert tb.crc32c(b"") == 0
 
 
+def test_checksums_of_pieces_join_into_the_whole(tmp_path):
+    rng = np.random.default_rng(5)
+    data = rng.integers(0, 256, 300_000, dtype=np.uint8).tobytes()
+    whole = tb.crc32c(data)
+    for cut in (0, 1, 7, 4096, 150_001, len(data) - 1, len(data)):
+        a, b = data[:cut], data[cut:]
+        assert tb.crc32c_combine(tb.crc32c(a), tb.crc32c(b), len(b)) == whole, cut
+        assert tb.crc32c(b, tb.crc32c(a)) == whole, cut  # continuing gives the same
+    three = tb.crc32c_combine(tb.crc32c_combine(tb.crc32c(data[:1000]), tb.crc32c(data[1000:70_000]), 69_000), tb.crc32c(data[70_000:]), len(data) - 70_000)
+    assert three == whole
+    assert tb.crc32c(data[:5000]) == ww.crc32c(data[:5000]), "the processor's instruction and the bit-at-a-time loop agree"
+
+
 def test_written_tensors_read_back_aligned(tmp_path):
     path, raw = sample(tmp_path, "roundtrip")
     w = tb.Wpk(path)
@@ -166,3 +179,51 @@ def test_a_converted_model_with_per_layer_inputs_loads_from_both_files(ctx, tmp_
         assert a.step(token) == b.step(token) == ref.step(token, pos)[0]
         assert np.array_equal(a.logits(), b.logits())
     a.close(), b.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("readers", [0, 1, 4])
+def test_a_file_streamed_in_pieces_loads_the_same(ctx, tmp_path, monkeypatch, readers):
+    """The loader cuts tensors that are copied as they are into pieces of a slot, read ahead into a ring of pinned slots by
+    reader threads and uploaded in order (the reference's Loader::to_device, wpk/load.rs:20-60); tensors rearranged on the
+    way come whole.  With slots of 8 KiB every matrix of the small model is in pieces: the same bits as the plain load, with
+    the checksums checked across pieces, and a flipped byte in the middle of a tensor in pieces is found."""
+    from oracle.model import OracleModel
+
+    cfg = tb.gemma4_e4b_shape(layers=3, ffn=2048, vocab=2048)
+    cfg.window, cfg.global_every, cfg.per_layer = 16, 3, 256
+    ref = OracleModel(cfg, 35, context=64, chunk=0, weight_bits=4)
+    files = {"weights.wpk": [], "host.wpk": []}
+    for name, a in ref.tensors.items():
+        kind = "u8" if name.endswith(".w") else "f16" if name.endswith(".s") else "f32"
+        a = np.ascontiguousarray(a)
+        files["host.wpk" if name.startswith("embed_per_layer") else "weights.wpk"].append((name, kind, a.shape, a.view(np.uint8).tobytes()))
+    for name, tensors in files.items():
+        ww.write(str(tmp_path / name), tensors, crc=ww.fast_crc32c)
+    plain = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4, host_table=True)
+    plain.load_wpk(str(tmp_path / "weights.wpk")), plain.load_wpk(str(tmp_path / "host.wpk"))
+    plain.build()
+    monkeypatch.setenv("TACHYON_B200_LOAD_SLOT_KB", "8")
+    monkeypatch.setenv("TACHYON_B200_LOAD_READERS", str(readers))
+    cut = tb.Decoder(ctx, cfg, context=64, keep_logits=True, weight_bits=4, host_table=True)
+    cut.load_wpk(str(tmp_path / "weights.wpk")), cut.load_wpk(str(tmp_path / "host.wpk"))
+    cut.build()
+    for pos, token in enumerate([5, 99, 2000, 7]):
+        assert cut.step(token) == plain.step(token) == ref.step(token, pos)[0]
+        assert np.array_equal(cut.logits(), plain.logits())
+    # a flipped byte in the third piece of the first large tensor
+    w = tb.Wpk(str(tmp_path / "weights.wpk"))
+    big = next({"name": t[0], "offset": t[3], "bytes": t[4]} for t in w.tensors() if t[4] > 64 << 10 and "gate_up" not in t[0])
+    w.close()
+    raw = bytearray(open(tmp_path / "weights.wpk", "rb").read())
+    raw[4096 + big["offset"] + 20000] ^= 0x40
+    open(tmp_path / "damaged.wpk", "wb").write(raw)
+    with pytest.raises(tb.Error) as e:
+        cut.load_wpk(str(tmp_path / "damaged.wpk"))
+    assert e.value.status == 5 and big["name"] in str(e.value)
+    cut.load_wpk(str(tmp_path / "damaged.wpk"), verify=False)  # unchecked it loads
+    # a file cut short: the read fails, the threads end, the error names the tensor
+    open(tmp_path / "short.wpk", "wb").write(bytes(raw[: 4096 + big["offset"] + 30000]))
+    with pytest.raises(tb.Error):
+        cut.load_wpk(str(tmp_path / "short.wpk"))
+    plain.close(), cut.close()
