@@ -619,6 +619,53 @@ TB_API int tb_engine_load_encoder(tb_engine* eng, const char* name, const tb_enc
 TB_API int tb_engine_encoder(tb_engine* eng, const char* name, tb_encoder** out);
 TB_API int tb_engine_embed(tb_engine* eng, const char* name, const uint32_t* ids, const uint32_t* lens, uint32_t sequences, float* out_host);
 
+/* ---- Text to token ids and back (host code; crates/tachyon/src/token/mod.rs, token/chat.rs) ------------------------------------
+ * Tokenizer::from_json (mod.rs:97-127) reads a Hugging Face tokenizer.json of Gemma's kind (BPE with byte fallback, spaces
+ * as U+2581) or of the Metaspace kind; byte-level BPE is refused (TB_FORMAT, "... is not supported").  Tokenizer::to_bytes /
+ * from_bytes (mod.rs:422-455) are the reference's stored form, word for word: a converted model's tokenizer.tok loads as it
+ * is.  Tokenizer::encode (mod.rs:272-301) encodes text literally: a special token's text stays text; special tokens enter by
+ * id, from the chat template.  Output buffers: *count (or *bytes) is always what the whole result needs; with capacity 0
+ * nothing is written and the call only counts; a capacity that is too small is TB_OUT_OF_RANGE. */
+typedef struct tb_tokenizer tb_tokenizer;
+typedef struct tb_detokenizer tb_detokenizer;
+TB_API int tb_tokenizer_from_json(const void* json, size_t bytes, tb_tokenizer** out);
+TB_API int tb_tokenizer_from_bytes(const void* data, size_t bytes, tb_tokenizer** out);
+TB_API int tb_tokenizer_to_bytes(const tb_tokenizer* tok, void* out, size_t capacity, size_t* bytes);
+TB_API void tb_tokenizer_close(tb_tokenizer* tok);
+TB_API size_t tb_tokenizer_len(const tb_tokenizer* tok);                                           /* Tokenizer::len */
+TB_API int tb_tokenizer_encode(const tb_tokenizer* tok, const char* text, size_t bytes, uint32_t* ids, size_t capacity, size_t* count);
+/* Tokenizer::bytes (mod.rs:241-245): the text token `id` decodes to; a byte token is one byte, maybe part of a character.
+ * The pointer is the tokenizer's. */
+TB_API int tb_tokenizer_token(const tb_tokenizer* tok, uint32_t id, const uint8_t** text, size_t* bytes);
+TB_API int tb_tokenizer_is_special(const tb_tokenizer* tok, uint32_t id);                          /* Tokenizer::is_special */
+TB_API int tb_tokenizer_special(const tb_tokenizer* tok, const char* text, uint32_t* id);          /* Tokenizer::special; TB_NO_MODEL if none */
+/* Tokenizer::frame (mod.rs:232-234): the special tokens the post-processor puts before and after a text; UINT32_MAX: none. */
+TB_API void tb_tokenizer_frame(const tb_tokenizer* tok, uint32_t* before, uint32_t* after);
+/* Detokenizer (mod.rs:603-648): generated tokens back into text as they come, whole characters only: a character split across
+ * byte tokens appears once its last byte arrives; special tokens add nothing; finish gives what is left, an unfinished
+ * character as U+FFFD.  A call whose text does not fit consumes nothing. */
+TB_API int tb_detokenizer_new(tb_detokenizer** out);
+TB_API void tb_detokenizer_close(tb_detokenizer* det);
+TB_API int tb_detokenizer_push(tb_detokenizer* det, const tb_tokenizer* tok, uint32_t id, char* out, size_t capacity, size_t* bytes);
+TB_API int tb_detokenizer_finish(tb_detokenizer* det, char* out, size_t capacity, size_t* bytes);
+/* Gemma 4's chat template (token/chat.rs:1-16, 57-72, 124-163), text messages only: <bos>, the system turn when the first
+ * message is a system message or thinking is on (<|think|> switches it on), each message trimmed and closed by <turn|>,
+ * consecutive model messages sharing one turn, then the opening of the model's turn; with `closed` set (Chat::with_template,
+ * chat.rs:97-107: told from the model's chat_template.jinja) an empty thinking block follows when thinking is off. */
+enum { TB_ROLE_SYSTEM = 0, TB_ROLE_USER = 1, TB_ROLE_MODEL = 2 };
+typedef struct tb_chat {
+    uint32_t bos, turn, end, think;
+    uint32_t closed[2];      /* <|channel>, <channel|>, or UINT32_MAX twice */
+} tb_chat;
+typedef struct tb_message {
+    int role;
+    const char* text;
+    size_t bytes;
+} tb_message;
+TB_API int tb_chat_gemma4(const tb_tokenizer* tok, tb_chat* out);                                  /* TB_FORMAT: not Gemma 4's tokenizer */
+TB_API int tb_chat_with_template(const tb_tokenizer* tok, tb_chat* chat, const char* template_text, size_t bytes);
+TB_API int tb_chat_encode(const tb_tokenizer* tok, const tb_chat* chat, const tb_message* messages, size_t n, int think, uint32_t* ids, size_t capacity, size_t* count);
+
 #ifdef __cplusplus
 }
 #endif

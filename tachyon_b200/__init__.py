@@ -361,6 +361,127 @@ def crc32c_combine(crc_a: int, crc_b: int, len_b: int) -> int:
     return int(_lib.load().tb_crc32c_combine(crc_a, crc_b, len_b))
 
 
+class Tokenizer:
+    """token::Tokenizer (crates/tachyon/src/token/mod.rs): text to token ids and back.  Host code, no GPU."""
+
+    def __init__(self, handle: int):
+        self.lib, self.handle = _lib.load(), handle
+
+    @classmethod
+    def from_json(cls, json: bytes) -> "Tokenizer":
+        h = C.c_void_p()
+        check(_lib.load().tb_tokenizer_from_json(json, len(json), C.byref(h)))
+        return cls(h.value)
+
+    @classmethod
+    def from_bytes(cls, data: bytes) -> "Tokenizer":
+        h = C.c_void_p()
+        check(_lib.load().tb_tokenizer_from_bytes(data, len(data), C.byref(h)))
+        return cls(h.value)
+
+    def to_bytes(self) -> bytes:
+        n = C.c_size_t(0)
+        check(self.lib.tb_tokenizer_to_bytes(self.handle, None, 0, C.byref(n)))
+        buf = C.create_string_buffer(n.value)
+        check(self.lib.tb_tokenizer_to_bytes(self.handle, buf, n.value, C.byref(n)))
+        return buf.raw[: n.value]
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_tokenizer_close(self.handle)
+            self.handle = None
+
+    def __len__(self) -> int:
+        return int(self.lib.tb_tokenizer_len(self.handle))
+
+    def encode(self, text: str) -> list[int]:
+        raw = text.encode("utf-8", "surrogatepass")
+        ids = np.empty(len(raw) + 16, np.uint32)  # a token per byte at most, but for the spaces a pre-tokenizer prepends
+        n = C.c_size_t(0)
+        if self.lib.tb_tokenizer_encode(self.handle, raw, len(raw), ids.ctypes.data, ids.size, C.byref(n)) != 0 and n.value > ids.size:
+            ids = np.empty(n.value, np.uint32)
+            check(self.lib.tb_tokenizer_encode(self.handle, raw, len(raw), ids.ctypes.data, ids.size, C.byref(n)))
+        return ids[: n.value].tolist()
+
+    def token(self, id: int) -> bytes:
+        p, n = C.c_void_p(), C.c_size_t(0)
+        check(self.lib.tb_tokenizer_token(self.handle, id, C.byref(p), C.byref(n)))
+        return C.string_at(p.value, n.value) if n.value else b""
+
+    def is_special(self, id: int) -> bool:
+        return bool(self.lib.tb_tokenizer_is_special(self.handle, id))
+
+    def special(self, text: str) -> int:
+        v = C.c_uint32(0)
+        check(self.lib.tb_tokenizer_special(self.handle, text.encode(), C.byref(v)))
+        return v.value
+
+    def frame(self) -> tuple[int | None, int | None]:
+        a, b = C.c_uint32(0), C.c_uint32(0)
+        self.lib.tb_tokenizer_frame(self.handle, C.byref(a), C.byref(b))
+        return tuple(None if v.value == 0xFFFFFFFF else v.value for v in (a, b))
+
+    def decode(self, ids) -> str:
+        d = Detokenizer(self)
+        out = "".join(d.push(i) for i in ids) + d.finish()
+        d.close()
+        return out
+
+
+class Detokenizer:
+    """token::Detokenizer (mod.rs:603-648): tokens back into text as they come, whole characters only."""
+
+    def __init__(self, tok: Tokenizer):
+        self.tok, self.lib = tok, tok.lib
+        h = C.c_void_p()
+        check(self.lib.tb_detokenizer_new(C.byref(h)))
+        self.handle, self.buf = h.value, C.create_string_buffer(1 << 16)
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.tb_detokenizer_close(self.handle)
+            self.handle = None
+
+    def push(self, id: int) -> str:
+        n = C.c_size_t(0)
+        check(self.lib.tb_detokenizer_push(self.handle, self.tok.handle, id, self.buf, len(self.buf), C.byref(n)))
+        return self.buf.raw[: n.value].decode("utf-8")
+
+    def finish(self) -> str:
+        n = C.c_size_t(0)
+        check(self.lib.tb_detokenizer_finish(self.handle, self.buf, len(self.buf), C.byref(n)))
+        return self.buf.raw[: n.value].decode("utf-8")
+
+
+ROLES = {"system": 0, "user": 1, "model": 2, "assistant": 2}
+
+
+class ChatTemplate:
+    """token::Chat (token/chat.rs): Gemma 4's chat template over a tokenizer, text messages only."""
+
+    def __init__(self, tok: Tokenizer, template: str | None = None):
+        self.tok, self.lib, self.chat = tok, tok.lib, _lib.Chat()
+        check(self.lib.tb_chat_gemma4(tok.handle, C.byref(self.chat)))
+        if template is not None:
+            raw = template.encode()
+            check(self.lib.tb_chat_with_template(tok.handle, C.byref(self.chat), raw, len(raw)))
+
+    def end_of_turn(self) -> int:
+        return self.chat.end
+
+    def encode(self, messages, think: bool = False) -> list[int]:
+        """messages: [(role, text)] with role "system", "user", "model" (or "assistant")."""
+        raws = [text.encode("utf-8") for _, text in messages]
+        arr = (_lib.Message * max(len(messages), 1))()
+        for i, ((role, _), raw) in enumerate(zip(messages, raws)):
+            arr[i].role, arr[i].text, arr[i].bytes = ROLES[role], C.cast(C.c_char_p(raw), C.c_void_p), len(raw)
+        n = C.c_size_t(0)
+        check(self.lib.tb_chat_encode(self.tok.handle, C.byref(self.chat), arr, len(messages), int(think), None, 0, C.byref(n)))
+        ids = np.empty(max(n.value, 1), np.uint32)
+        check(self.lib.tb_chat_encode(self.tok.handle, C.byref(self.chat), arr, len(messages), int(think), ids.ctypes.data, ids.size, C.byref(n)))
+        return ids[: n.value].tolist()
+
+
 class WpkWriter:
     """wpk::Writer (crates/tachyon/src/wpk/mod.rs:270-337): writes a `.wpk` tensor by tensor, each on a 4 KiB boundary, then the
     table and the header.  Host code; the checksums come from tb_crc32c."""

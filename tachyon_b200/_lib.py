@@ -41,6 +41,16 @@ class WpkInfo(C.Structure):
     _fields_ = [("name", cp), ("dtype", u32), ("rank", u32), ("shape", u64 * 8), ("offset", u64), ("bytes", u64), ("crc32c", u32)]
 
 
+class Chat(C.Structure):
+    """tb_chat (token/chat.rs:57-72): the ids of Gemma 4's chat marks."""
+    _fields_ = [("bos", u32), ("turn", u32), ("end", u32), ("think", u32), ("closed", u32 * 2)]
+
+
+class Message(C.Structure):
+    """tb_message: a role (0 system, 1 user, 2 model) and a text."""
+    _fields_ = [("role", i32), ("text", vp), ("bytes", sz)]
+
+
 class Load(C.Structure):
     """tb_load (engine.rs:72-90): settings, keep-alive in ms (2**64 - 1: for good), pin."""
     pass
@@ -171,6 +181,23 @@ SIGNATURES = {
     "tb_engine_models": (i32, [vp, C.POINTER(Loaded), sz, C.POINTER(sz)]),
     "tb_engine_expire": (i32, [vp]),
     "tb_engine_usage": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
+    "tb_tokenizer_from_json": (i32, [vp, sz, pp]),
+    "tb_tokenizer_from_bytes": (i32, [vp, sz, pp]),
+    "tb_tokenizer_to_bytes": (i32, [vp, vp, sz, C.POINTER(sz)]),
+    "tb_tokenizer_close": (None, [vp]),
+    "tb_tokenizer_len": (sz, [vp]),
+    "tb_tokenizer_encode": (i32, [vp, vp, sz, vp, sz, C.POINTER(sz)]),
+    "tb_tokenizer_token": (i32, [vp, u32, pp, C.POINTER(sz)]),
+    "tb_tokenizer_is_special": (i32, [vp, u32]),
+    "tb_tokenizer_special": (i32, [vp, cp, C.POINTER(u32)]),
+    "tb_tokenizer_frame": (None, [vp, C.POINTER(u32), C.POINTER(u32)]),
+    "tb_detokenizer_new": (i32, [pp]),
+    "tb_detokenizer_close": (None, [vp]),
+    "tb_detokenizer_push": (i32, [vp, vp, u32, vp, sz, C.POINTER(sz)]),
+    "tb_detokenizer_finish": (i32, [vp, vp, sz, C.POINTER(sz)]),
+    "tb_chat_gemma4": (i32, [vp, C.POINTER(Chat)]),
+    "tb_chat_with_template": (i32, [vp, C.POINTER(Chat), vp, sz]),
+    "tb_chat_encode": (i32, [vp, C.POINTER(Chat), C.POINTER(Message), sz, i32, vp, sz, C.POINTER(sz)]),
     "tb_engine_load_encoder": (i32, [vp, cp, C.POINTER(EncoderConfig), u32, u32, u64, i32, cp, cp]),
     "tb_engine_encoder": (i32, [vp, cp, pp]),
     "tb_engine_embed": (i32, [vp, cp, vp, vp, u32, vp]),
