@@ -628,6 +628,34 @@ def bench_load(args, ranks: Ranks):
             "on_the_calling_thread_checked_s": min(times[(0, True)]), "four_readers_s": min(times[(4, False)]), "sixteen_readers_s": min(times[(16, False)])}
 
 
+def bench_token(args, ranks: Ranks):
+    """The tokenizer on the host (the reference's benches/token.rs): the fixture's strings (a thousand texts of the reference's
+    multilingual set, 200 KB) through tb_tokenizer_encode with the small Gemma-shaped vocabulary, and the ids back through the
+    detokenizer; one thread."""
+    import ctypes as C
+
+    import tachyon_b200 as tb
+
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "token")
+    tok = tb.Tokenizer.from_json(open(os.path.join(golden, "toy.json"), "rb").read())
+    texts = [json.loads(line).encode("utf-8") for line in open(os.path.join(golden, "strings.jsonl"), encoding="utf-8")]
+    ids = np.empty(max(len(t) for t in texts) + 16, np.uint32)
+    n = C.c_size_t(0)
+    rounds, tokens, nbytes = max(args.steps, 3), 0, sum(len(t) for t in texts)
+    best = float("inf")
+    for _ in range(rounds):
+        tokens = 0
+        t0 = time.perf_counter()
+        for t in texts:
+            tb.check(tok.lib.tb_tokenizer_encode(tok.handle, t, len(t), ids.ctypes.data, ids.size, C.byref(n)))
+            tokens += n.value
+        best = min(best, time.perf_counter() - t0)
+    tok.close()
+    return {"metric": "tokenizer_encode_mb_per_second", "value": nbytes / best / 1e6, "unit": "MB/s", "n_gpus": 0, "steps": rounds, "warmup": 0, "ms_per_step": best * 1e3,
+            "higher_is_better": True, "dtype": "u8", "data": "fixture", "impl": "ours", "config": {"workload": f"{len(texts)} fixture strings, {nbytes} B, {tokens} tokens, one host thread"},
+            "gpu_launches": 0, "tokens_per_second": tokens / best}
+
+
 def bench_flash(args, ranks: Ranks):
     """configs[3]'s attention alone: 2048 tokens x 8 query / 2 kv heads of 256 over the cache ring, sliding 512 and global."""
     import tachyon_b200 as tb
@@ -794,7 +822,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder", "switch", "load"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv_q4", "gateup", "attend", "gemm", "flash", "prefill", "encoder", "switch", "load", "token"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=16384)
@@ -832,6 +860,8 @@ def main():
             line = bench_switch(args, ranks) if ranks.rank == 0 else None
         elif args.workload == "load":
             line = bench_load(args, ranks) if ranks.rank == 0 else None
+        elif args.workload == "token":
+            line = bench_token(args, ranks) if ranks.rank == 0 else None
         else:
             line, cfg, gpu_tokens = bench_decode(args, ranks)
             if not args.no_extras:

@@ -617,6 +617,37 @@ class Engine:
     def expire(self) -> None:
         check(self.lib.tb_engine_expire(self.handle))
 
+    def chat(self, name: str, tok: "Tokenizer", messages, think: bool = False, max_tokens: int = 256, template: "ChatTemplate | None" = None):
+        """Engine::chat and TokenStream::next_text (engine.rs:326-337, 515-536): the conversation through the chat template, every
+        prompt token but the last through prefill and the last through a step, then the answer's text piece by piece, whole
+        characters only, until the model ends its turn, `max_tokens` are out or the context is full."""
+        chat = template or ChatTemplate(tok)
+        prompt = chat.encode(messages, think=think)
+        context = self.loaded[name][1].context
+        if len(prompt) >= context:
+            raise Error(3, f"the prompt's {len(prompt)} tokens do not fit the context of {context}")
+        ends = {chat.end_of_turn()}
+        for mark in ("<eos>", "<end_of_turn>"):
+            try:
+                ends.add(tok.special(mark))
+            except Error:
+                pass
+        token = self.feed(name, prompt)
+        dec, detok, left = self.decoder(name), Detokenizer(tok), min(max_tokens, context - len(prompt))
+        try:
+            while left > 0 and token not in ends:
+                left -= 1
+                text = detok.push(token) if token < len(tok) else ""
+                if text:
+                    yield text
+                if left > 0:
+                    token = dec.step(token)
+            text = detok.finish()
+            if text:
+                yield text
+        finally:
+            detok.close()
+
     def load_encoder(self, name: str, cfg: EncoderConfig, weights: str, host: str | None = None, tokens: int = 4096, sequences: int = 64,
                      keep_alive_ms: int = 300_000, pin: bool = False) -> None:
         """tb_engine_load_encoder: the encoder of these files held as `name`, decoders moved out to make room."""

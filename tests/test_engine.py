@@ -336,3 +336,46 @@ def test_the_engine_holds_encoders_in_vram(ctx, model, tmp_path, fmt):
     assert all(m["name"] != "enc" for m in e.models())
     e.close()
     del glob
+
+
+def test_a_conversation_goes_in_as_text_and_the_answer_comes_out_as_text(ctx, tmp_path):
+    """Engine::chat (engine.rs:326-337, 515-536) end to end on a small random model whose vocabulary covers the toy tokenizer
+    with Gemma 4's chat marks: the prompt is the chat template's ids, the answer's pieces join to the detokenized tokens that
+    feed and step give, and it stops at the end of the turn, at max_tokens, or when the context is full."""
+    import json
+    import os
+
+    golden = os.path.join(os.path.dirname(__file__), "golden", "token")
+    tok = tb.Tokenizer.from_json(open(os.path.join(golden, "chat.json"), "rb").read())
+    cfg = tb.gemma4_e4b_shape(layers=2, ffn=2048, vocab=4096)
+    cfg.window, cfg.global_every = 16, 2
+    from oracle.model import OracleModel
+
+    ref = OracleModel(cfg, 51, context=64, chunk=0, weight_bits=4)
+    tensors = []
+    for name, a in ref.tensors.items():
+        kind = "u8" if name.endswith(".w") else "f16" if name.endswith(".s") else "f32"
+        tensors.append((name, kind, a.shape, np.ascontiguousarray(a).view(np.uint8).tobytes()))
+    path = str(tmp_path / "weights.wpk")
+    ww.write(path, tensors, crc=ww.fast_crc32c)
+    e = tb.Engine(ctx)
+    e.load("m", cfg, path, None, context=64, chunk=8, weight_bits=4)
+    messages = [("system", " Be brief. "), ("user", "Hello!")]
+    chat = tb.ChatTemplate(tok)
+    prompt = chat.encode(messages)
+    assert 10 < len(prompt) < 40
+    pieces = list(e.chat("m", tok, messages, max_tokens=12))
+    # the same by hand
+    token, want = e.feed("m", prompt), []
+    dec = e.decoder("m")
+    ends = {chat.end_of_turn(), tok.special("<eos>"), tok.special("<end_of_turn>")}
+    while len(want) < 12 and token not in ends:
+        want.append(token)
+        token = dec.step(token)
+    assert "".join(pieces) == tok.decode([t for t in want if t < len(tok)])
+    # the context bounds the answer; a prompt that fills it is refused
+    long = list(e.chat("m", tok, messages, max_tokens=1000))
+    assert len("".join(long)) >= len("".join(pieces))
+    with pytest.raises(tb.Error):
+        list(e.chat("m", tok, [("user", "word " * 80)]))
+    e.close(), tok.close()
