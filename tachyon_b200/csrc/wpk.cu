@@ -364,7 +364,14 @@ int load_all(const char* what, const char* path, int verify, P&& in_parts, F&& p
         }
     };
     std::vector<std::thread> threads;
-    for (int k = 0; k < readers; k++) threads.emplace_back(reader);
+    for (int k = 0; k < readers; k++) {
+        try {
+            threads.emplace_back(reader);
+        } catch (...) {  // no more threads to be had: go on with the ones there are, or read on this thread
+            break;
+        }
+    }
+    const bool threaded = !threads.empty();
 
     int st = OK;
     uint32_t crc = 0;
@@ -373,7 +380,7 @@ int load_all(const char* what, const char* path, int verify, P&& in_parts, F&& p
         const tb_wpk::Entry& e = w->tensors[pc.tensor];
         bool ok = true;
         int err = 0;
-        if (readers == 0) {
+        if (!threaded) {
             ok = read_piece(i), err = errno;
         } else {
             std::unique_lock<std::mutex> lock(m);
@@ -383,12 +390,12 @@ int load_all(const char* what, const char* path, int verify, P&& in_parts, F&& p
         const char* data = stage + (i % depth) * slot;
         if (!ok) st = fail(IO, std::string(what) + ": " + e.name + ": " + (err ? strerror(err) : "the file is truncated"));
         if (st == OK && verify) {
-            const uint32_t sum = readers == 0 ? crc32c(0, reinterpret_cast<const uint8_t*>(data), pc.len) : sums[i];
+            const uint32_t sum = threaded ? sums[i] : crc32c(0, reinterpret_cast<const uint8_t*>(data), pc.len);
             crc = pc.offset == 0 ? sum : crc32c_combine(crc, sum, pc.len);
             if (pc.offset + pc.len == e.len && crc != e.crc) st = fail(FORMAT, "tensor \"" + e.name + "\" is corrupt");  // Wpk::verify
         }
         if (st == OK) st = put(e.name.c_str(), pc.offset, data, pc.len, (size_t)e.len);
-        if (readers > 0) {
+        if (threaded) {
             std::lock_guard<std::mutex> lock(m);
             taken = i + 1;
             cv.notify_all();
