@@ -153,6 +153,8 @@ int tb_context_new(int gpu, tb_context** out) {
     ctx->gemm_walk = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_L2_SIDE");
     ctx->l2_side = env != nullptr && env[0] == '1';
+    env = getenv("TACHYON_B200_GEMM_RED");
+    ctx->gemm_red = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_FLASH");
     ctx->flash_tc = !(env != nullptr && env[0] == '0');
     env = getenv("TACHYON_B200_GEMM");

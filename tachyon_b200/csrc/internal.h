@@ -32,6 +32,7 @@ struct tb_context {
     uint32_t sched_at = 0;            // which pair the next launch takes
     bool attn_block = false;          // a decode layer's attention half as one kernel on clusters of 16 blocks where the layer has its shape (attn_block.cu: measured slower, so off); TACHYON_B200_ATTN_BLOCK=1, tb_context_set_attn_block
     bool gemm_walk = true;            // the one-tile product on f16 weights walks its tiles with one block an SM (gemm.cu); TACHYON_B200_GEMM_WALK=0
+    bool gemm_red = true;             // the persistent product's += epilogue as reductions at the L2 (red.global.add.f32) instead of load, add, store; TACHYON_B200_GEMM_RED=0
     bool l2_side = false;             // decode: a side stream asks the L2 for a layer's down projection during the layer's short kernels (TACHYON_B200_L2_SIDE=1)
     bool flash_tc = true;             // prefill attention on tcgen05 where the shape allows (prefill_tc.cu); TACHYON_B200_FLASH=0, tb_context_set_flash
     int gemm_schedule = 0;            // 0: chosen by shape and epilogue; 1..4 force one (TACHYON_B200_GEMM at creation, tb_context_set_gemm_schedule)
