@@ -104,6 +104,16 @@ __global__ void __launch_bounds__(256) enc_norm_warp_kernel(const float* x, cons
 // Picks the warp-per-token kernel where the width allows it.
 static void launch_enc_norm(cudaStream_t s, uint32_t T, const float* x, const __half* table, const uint32_t* ids, const float* w, uint32_t h, float eps, float* out32,
                             __half* out16);
+// dst row r = src row of the same head with the halves interleaved (r = head d + i: i even -> i / 2, i odd -> d / 2 + i / 2)
+// for the first `turned` rows; the rest as they are.  Eight halves a thread.
+__global__ void __launch_bounds__(256) enc_pair_rows_kernel(const __half* src, __half* dst, uint32_t rows, uint32_t cols, uint32_t turned, uint32_t d) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x, per_row = cols / 8;
+    if (i >= (size_t)rows * per_row) return;
+    const uint32_t r = (uint32_t)(i / per_row), c = (uint32_t)(i % per_row), in = r % d;
+    const uint32_t from = r < turned ? r - in + ((in & 1u) ? d / 2 + in / 2 : in / 2) : r;
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[(size_t)from * per_row + c];
+}
+
 // One warp per token: a lane turns eight pairs at a time (16-byte loads and stores of the low and the high half of a head)
 // by the cosines and sines of the token's position from `table` (f32 [positions, d/2, 2]): (a, b) -> (a c - b s, b c + a s),
 // a product then one fused multiply-add each, the reference's operations (ptx/encoder.rs:942-956) and so its bits.
@@ -428,6 +438,13 @@ struct tb_encoder {
     // more; the values are the codes' own, launch_dequant_f16).  Written before a batch when a tensor was loaded since.
     // TACHYON_B200_ENCODER_COPY=0 leaves it out.
     bool use_copy = true, copy_valid = false;
+    // The q/k/v product turns the queries and keys in its store (GemmRope): its copy of the matrix has a head's rows j and
+    // j + d/2 side by side, so q and k come out with their dimensions in that order, which the dot products do not mind.
+    // Off unless TACHYON_B200_ENCODER_ROPE=1: measured over forty batches in a row it loses 3 % (9.97 against 9.66 ms a batch:
+    // the table loads and shuffles lengthen an epilogue that is short of issue slots already, and the rotation kernel it
+    // saves finds its 100 MB in the L2).
+    bool rope_fused = false;
+    __half* rope_tmp = nullptr;  // the q/k/v matrix in f16 before its rows are put in that order
     uint32_t tile_q = QT;  // queries a tile of the list holds: 64, or 128 where attention runs on tcgen05 (decided when the encoder is opened)
     std::vector<EGraph> graphs;
 };
@@ -460,6 +477,7 @@ size_t enc_layout(tb_encoder* e, char* base) {
         L.mlp_norm = reinterpret_cast<float*>(take(h * 4));
         mat(L.qkv, 3 * h, h), mat(L.o, h, h), mat(L.up, up_rows, h), mat(L.down, h, c.inter);
     }
+    e->rope_tmp = e->rope_fused ? reinterpret_cast<__half*>(take((size_t)3 * h * h * 2)) : nullptr;
     e->x = reinterpret_cast<float*>(take((size_t)T * h * 4));
     e->hidden = reinterpret_cast<float*>(take((size_t)T * h * 4));
     e->pooled = reinterpret_cast<float*>(take((size_t)S * h * 4));
@@ -552,8 +570,13 @@ int enc_layers(tb_encoder* e, uint32_t n, uint32_t slots, uint32_t sequences) {
     for (uint32_t l = 0; l < c.layers; l++) {
         ELayer& L = e->layers[l];
         if (l > 0) launch_enc_norm(s, n, e->x, nullptr, nullptr, L.attn_norm, h, c.eps, nullptr, e->a16);
-        TB_TRY(enc_product(e, L.qkv, e->a16, n, e->qkv16, 1));
-        enc_rope_kernel<<<(n + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->rope[L.global ? 0 : 1], h, d, n);
+        if (e->rope_fused) {
+            const GemmRope turn{e->rope[L.global ? 0 : 1], e->pos, 2 * h, d};
+            TB_TRY(launch_gemm_persistent(ctx, reinterpret_cast<const int8_t*>(L.qkv.copy), nullptr, e->a16, n, 3 * h, h, e->qkv16, 1, 16, nullptr, 0, &turn));
+        } else {
+            TB_TRY(enc_product(e, L.qkv, e->a16, n, e->qkv16, 1));
+            enc_rope_kernel<<<(n + 7) / 8, 256, 0, s>>>(e->qkv16, e->pos, e->rope[L.global ? 0 : 1], h, d, n);
+        }
         if (e->tile_q == 128) TB_TRY(launch_enc_attend_tc(ctx, e->qkv16, e->tiles, e->att16, h, L.global ? -1 : (int)c.window, scale, slots, n));
         else TB_TRY(launch_enc_attend(ctx, e->qkv16, e->tiles, e->att16, h, d, L.global ? -1 : (int)c.window, scale, slots));
         TB_TRY(enc_product(e, L.o, e->att16, n, e->x, 3));
@@ -574,8 +597,16 @@ int enc_batch(tb_encoder* e, const uint32_t* ids, const uint32_t* lens, uint32_t
     cudaStream_t s = e->ctx->stream;
     if (e->use_copy && !e->copy_valid) {
         for (ELayer& L : e->layers)
-            for (EMat* m : {&L.qkv, &L.o, &L.up, &L.down})
-                if (m->f16 == nullptr) TB_TRY(launch_dequant_f16(e->ctx, m->w, m->s, m->rows, m->cols, 8, m->copy));
+            for (EMat* m : {&L.qkv, &L.o, &L.up, &L.down}) {
+                const bool pairs = e->rope_fused && m == &L.qkv;
+                if (m->f16 == nullptr) TB_TRY(launch_dequant_f16(e->ctx, m->w, m->s, m->rows, m->cols, 8, pairs ? e->rope_tmp : m->copy));
+                if (pairs) {
+                    const size_t items = (size_t)m->rows * (m->cols / 8);
+                    enc_pair_rows_kernel<<<(unsigned)((items + 255) / 256), 256, 0, s>>>(m->f16 ? m->f16 : e->rope_tmp, m->copy, m->rows, m->cols, 2 * e->cfg.hidden,
+                                                                                      e->cfg.hidden / e->cfg.heads);
+                    TB_CUDA(cudaGetLastError());
+                }
+            }
         e->copy_valid = true;
     }
     uint32_t *hi, *hp, *ht, *hs, *hl;
@@ -647,6 +678,8 @@ int tb_encoder_open(tb_context* ctx, const tb_encoder_config* cfg, uint32_t toke
     e->use_graphs = !(env && env[0] == '0');
     env = getenv("TACHYON_B200_ENCODER_COPY");
     e->use_copy = !(env && env[0] == '0');
+    env = getenv("TACHYON_B200_ENCODER_ROPE");
+    e->rope_fused = e->use_copy && env && env[0] == '1' && gemm_persistent_supports(3 * cfg->hidden, cfg->hidden, 16) && cfg->hidden % 16 == 0;
     e->tile_q = (ctx->flash_tc && enc_attend_tc_supports(cfg->hidden, cfg->hidden / cfg->heads)) ? 128u : (uint32_t)QT;
     e->arena_bytes = enc_layout(e, nullptr);
     cudaError_t err = cudaSetDevice(ctx->gpu);
@@ -871,6 +904,8 @@ int tb_encoder_footprint(tb_context* ctx, const tb_encoder_config* cfg, uint32_t
     e.layers.resize(cfg->layers);
     const char* env = getenv("TACHYON_B200_ENCODER_COPY");
     e.use_copy = !(env && env[0] == '0');
+    env = getenv("TACHYON_B200_ENCODER_ROPE");
+    e.rope_fused = e.use_copy && env && env[0] == '1' && gemm_persistent_supports(3 * cfg->hidden, cfg->hidden, 16) && cfg->hidden % 16 == 0;
     *bytes = enc_layout(&e, nullptr);
     if (f16_matrices)
         for (const ELayer& L : e.layers)

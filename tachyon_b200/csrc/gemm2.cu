@@ -106,6 +106,7 @@ struct Args {
     // SMs (192 tiles of 256 tokens are two rounds of 148 at 65 %; 264 tiles of 192 tokens are two shorter rounds at 89 %).
     uint32_t tn;
     int red;           // mode 3: the sums added at the L2 by reductions, no load in the epilogue
+    GemmRope rope;     // mode 1: table != null turns the pairs of the first rope.cols weight rows (internal.h)
 };
 
 struct Bars {
@@ -326,6 +327,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                     const uint32_t odd = lane & 1u;
                     __half* dst = static_cast<__half*>(g.out) + (size_t)(mb + odd) * g.N + (n - odd);
                     const float* mrow = g.mode == 6 ? g.mul + (size_t)mb * g.mul_stride + n : nullptr;
+                    // Rotary embedding in the store: after the trade below a lane holds rows (n - odd, n - odd + 1) of its token,
+                    // the pair (a, b) of rotation j; each is rounded to f16 first, then (a c - b s, b c + a s) as a product and one
+                    // fused multiply-add, so the bits are those of a rotation kernel run on the stored halves.
+                    const bool turn = g.mode == 1 && g.rope.table != nullptr && n < g.rope.cols;
+                    const uint32_t my_pos = turn && mb + lane < g.M ? __ldg(g.rope.pos + mb + lane) : 0u;
+                    const uint32_t rot = ((n - odd) % g.rope.head) / 2;
 #pragma unroll
                     for (int k = 0; k < 16; k++) {
                         float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
@@ -335,7 +342,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                             v1 = mb + 2 * k + 1 < g.M ? gelu_tanh(v1) * __ldg(mrow + (size_t)(2 * k + 1) * g.mul_stride) : 0.0f;
                         }
                         const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);  // the neighbour's value for my token
-                        const __half2 pair = odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
+                        __half2 pair = odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
+                        if (g.mode == 1 && g.rope.table != nullptr) {  // the same for the whole warp, so every lane reaches the shuffle
+                            const uint32_t p = __shfl_sync(0xffffffffu, my_pos, 2 * k + odd);
+                            if (turn) {
+                                const float2 cs = __ldg(g.rope.table + (size_t)p * (g.rope.head / 2) + rot);
+                                const float2 ab = __half22float2(pair);
+                                pair = __floats2half2_rn(__fmaf_rn(ab.y, -cs.y, __fmul_rn(ab.x, cs.x)), __fmaf_rn(ab.x, cs.y, __fmul_rn(ab.y, cs.x)));
+                            }
+                        }
                         if (mb + 2 * k + odd < g.M) *reinterpret_cast<__half2*>(dst + (size_t)(2 * k) * g.N) = pair;
                     }
                 } else {
@@ -385,8 +400,9 @@ EncodeTiled encode_tiled() {
 bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K % BK == 0 && (K * wbits / 8) % 16 == 0 && N > 0; }  // wbits 16: f16 weights
 
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                           uint32_t wbits, const float* mul, uint32_t mul_stride) {
+                           uint32_t wbits, const float* mul, uint32_t mul_stride, const GemmRope* rope) {
     EncodeTiled enc = encode_tiled();
+    if (rope && (mode != 1 || rope->head == 0 || rope->head % 2 != 0 || rope->cols % 32 != 0 || rope->cols > N)) return fail(OUT_OF_RANGE, "gemm: a rotation wants the f16 store, an even head size and whole groups of 32 rows");
     if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
     // Tokens a tile: 256, or 192 or 128 where that fills whole rounds of the SMs so much better that it pays (a tenth at least by
     // rounds x (tokens + 32), the 32 standing for what a tile costs whatever its size).  Other sizes leave the epilogue's six
@@ -433,7 +449,7 @@ int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, co
     }
     const uint32_t tiles = ((M + tn - 1) / tn) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
-    const Args g{s, out, M, N, K, mode, mul, mul_stride, tn, ctx->gemm_red ? 1 : 0};
+    const Args g{s, out, M, N, K, mode, mul, mul_stride, tn, ctx->gemm_red ? 1 : 0, rope ? *rope : GemmRope{nullptr, nullptr, 0, 2}};
     cudaError_t le;
     if (wbits == 16) le = launch_kernel(ctx, gemm_persistent_kernel<16>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
     else if (wbits == 4) le = launch_kernel(ctx, gemm_persistent_kernel<4>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);

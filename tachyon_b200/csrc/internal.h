@@ -347,8 +347,16 @@ int launch_gemm_pair(tb_context* ctx, const int8_t* w, const __half* s, const __
                      uint32_t wbits, bool narrow);
 // The same product as a persistent kernel (gemm2.cu); launch_gemm_q8 validates and dispatches.
 bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits);
+// `rope` (mode 1 only): the outputs of weight rows below `cols` are rotated before they are stored: rows (2j, 2j + 1) of a
+// head of `head` rows hold a pair, turned by (c, s) = table[pos[token] * head / 2 + j].  The caller has put a head's rows
+// j and j + head / 2 side by side for it (the encoder's q and k rows).
+struct GemmRope {
+    const float2* table;
+    const uint32_t* pos;
+    uint32_t cols, head;
+};
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
-                           uint32_t wbits, const float* mul = nullptr, uint32_t mul_stride = 0);
+                           uint32_t wbits, const float* mul = nullptr, uint32_t mul_stride = 0, const GemmRope* rope = nullptr);
 
 // Launch helper: kernel launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>

@@ -338,3 +338,35 @@ def test_attention_on_tcgen05_and_on_mma_sync_agree(ctx):
         assert np.abs(hidden[1][at:at + len(q)] - want).max() < 3e-2
         at += len(q)
     assert ctx.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["q8", "f16"])
+def test_the_rotation_in_the_products_store_matches_the_kernel_of_its_own(ctx, monkeypatch, fmt):
+    """The q/k/v product turns queries and keys as it stores them, from a copy of the matrix with a head's rows j and j + d/2 side
+    by side; q and k then have their dimensions in that order, which changes the order of the dot products' sums and nothing
+    else.  TACHYON_B200_ENCODER_ROPE=1 switches it on; against the rotation as a kernel of its own on the reference's fixture and on a
+    model of heads of 64 with global and sliding layers; a tensor loaded afterwards is paired again."""
+    rng = np.random.default_rng(11)
+    for cfg, weights in (fixture()[:2], random_model(rng, h=256, heads=4, inter=512, layers=4)):
+        monkeypatch.setenv("TACHYON_B200_ENCODER_ROPE", "1")
+        fused, _ = build(ctx, cfg, weights, fmt=fmt)
+        monkeypatch.delenv("TACHYON_B200_ENCODER_ROPE")
+        apart, _ = build(ctx, cfg, weights, fmt=fmt)
+        seqs = [list(rng.integers(0, cfg["vocab"], n)) for n in (5, 64, 65, 130, 300, 17)]
+        a, b = fused.embed(seqs), apart.embed(seqs)
+        assert np.abs(a - b).max() < 2e-3 * max(1.0, np.abs(b).max()), float(np.abs(a - b).max())
+        cos = (a * b).sum(1) / (np.linalg.norm(a, axis=1) * np.linalg.norm(b, axis=1))
+        assert cos.min() > 0.99999, float(cos.min())
+        # another q/k/v matrix for layer 1: both pick it up
+        name = "1.qkv"
+        w = (rng.standard_normal(weights[name].shape) * 0.05).astype(np.float32)
+        for enc in (fused, apart):
+            if fmt == "f16":
+                enc.load(name, w.astype(np.float16))
+            else:
+                codes, scales, _ = quantize(w)
+                enc.load(name + ".w", codes), enc.load(name + ".s", scales)
+        a2, b2 = fused.embed(seqs), apart.embed(seqs)
+        assert np.abs(a2 - b2).max() < 2e-3 * max(1.0, np.abs(b2).max()) and np.abs(a2 - a).max() > 1e-3
+        fused.close(), apart.close()
