@@ -819,16 +819,8 @@ int tb_decoder_load(tb_decoder* d, const char* name, const void* data, size_t by
         TB_CUDA(cudaStreamSynchronize(s));
         return OK;
     }
-    // gate_up: gate rows then up rows in the file; pairs (gate_j, up_j) on the device.
-    void* tmp = nullptr;
-    TB_CUDA(cudaMalloc(&tmp, bytes));
-    cudaError_t e = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, s);
-    int st = OK;
-    if (e == cudaSuccess) st = launch_interleave_rows(d->ctx, tmp, t.ptr, d->cfg.ffn, (uint32_t)(bytes / (2 * (size_t)d->cfg.ffn)));
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    cudaFree(tmp);
-    if (e != cudaSuccess) return cuda_fail(e, "tb_decoder_load");
-    return st;
+    // gate_up: gate rows then up rows in the file; pairs (gate_j, up_j) on the device, scattered by strided copies.
+    return tb_decoder_load_part(d, name, 0, data, bytes, bytes);
 }
 
 // For the file loader: a tensor may arrive in pieces.  One that is copied to its place as it is has each piece written at its
