@@ -114,7 +114,7 @@ struct Bars {
     uint32_t tmem;
 };
 
-template <int WB>
+template <int WB, bool ROPE = false>
 __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map, const Args g,
                                                                      uint32_t* status) {
     extern __shared__ uint8_t raw_unaligned[];
@@ -330,9 +330,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                     // Rotary embedding in the store: after the trade below a lane holds rows (n - odd, n - odd + 1) of its token,
                     // the pair (a, b) of rotation j; each is rounded to f16 first, then (a c - b s, b c + a s) as a product and one
                     // fused multiply-add, so the bits are those of a rotation kernel run on the stored halves.
-                    const bool turn = g.mode == 1 && g.rope.table != nullptr && n < g.rope.cols;
-                    const uint32_t my_pos = turn && mb + lane < g.M ? __ldg(g.rope.pos + mb + lane) : 0u;
-                    const uint32_t rot = ((n - odd) % g.rope.head) / 2;
+                    // (A kernel of its own, ROPE: with this in the common kernel every mode's epilogue paid for it.)
+                    bool turn = false;
+                    uint32_t my_pos = 0, rot = 0;
+                    if constexpr (ROPE) {
+                        turn = n < g.rope.cols;
+                        my_pos = turn && mb + lane < g.M ? __ldg(g.rope.pos + mb + lane) : 0u;
+                        rot = ((n - odd) % g.rope.head) / 2;
+                    }
 #pragma unroll
                     for (int k = 0; k < 16; k++) {
                         float v0 = __uint_as_float(r[2 * k]), v1 = __uint_as_float(r[2 * k + 1]);
@@ -343,7 +348,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_persistent_kernel(const __gri
                         }
                         const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);  // the neighbour's value for my token
                         __half2 pair = odd ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
-                        if (g.mode == 1 && g.rope.table != nullptr) {  // the same for the whole warp, so every lane reaches the shuffle
+                        if constexpr (ROPE) {  // every lane reaches the shuffle
                             const uint32_t p = __shfl_sync(0xffffffffu, my_pos, 2 * k + odd);
                             if (turn) {
                                 const float2 cs = __ldg(g.rope.table + (size_t)p * (g.rope.head / 2) + rot);
@@ -402,7 +407,7 @@ bool gemm_persistent_supports(uint32_t N, uint32_t K, uint32_t wbits) { return K
 int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, const __half* a, uint32_t M, uint32_t N, uint32_t K, void* out, int mode,
                            uint32_t wbits, const float* mul, uint32_t mul_stride, const GemmRope* rope) {
     EncodeTiled enc = encode_tiled();
-    if (rope && (mode != 1 || rope->head == 0 || rope->head % 2 != 0 || rope->cols % 32 != 0 || rope->cols > N)) return fail(OUT_OF_RANGE, "gemm: a rotation wants the f16 store, an even head size and whole groups of 32 rows");
+    if (rope && (mode != 1 || wbits != 16 || rope->head == 0 || rope->head % 2 != 0 || rope->cols % 32 != 0 || rope->cols > N)) return fail(OUT_OF_RANGE, "gemm: a rotation wants the f16 store, an even head size and whole groups of 32 rows");
     if (!enc) return fail(NO_DRIVER, "gemm: the driver does not export cuTensorMapEncodeTiled");
     // Tokens a tile: 256, or 192 or 128 where that fills whole rounds of the SMs so much better that it pays (a tenth at least by
     // rounds x (tokens + 32), the 32 standing for what a tile costs whatever its size).  Other sizes leave the epilogue's six
@@ -445,13 +450,15 @@ int launch_gemm_persistent(tb_context* ctx, const int8_t* w, const __half* s, co
         TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         TB_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TB_CUDA(cudaFuncSetAttribute((gemm_persistent_kernel<16, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured[ctx->gpu & 15] = true;
     }
     const uint32_t tiles = ((M + tn - 1) / tn) * ((N + BN - 1) / BN);
     const uint32_t grid = tiles < (uint32_t)ctx->sms ? tiles : (uint32_t)ctx->sms;
     const Args g{s, out, M, N, K, mode, mul, mul_stride, tn, ctx->gemm_red ? 1 : 0, rope ? *rope : GemmRope{nullptr, nullptr, 0, 2}};
     cudaError_t le;
-    if (wbits == 16) le = launch_kernel(ctx, gemm_persistent_kernel<16>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
+    if (wbits == 16 && rope) le = launch_kernel(ctx, gemm_persistent_kernel<16, true>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
+    else if (wbits == 16) le = launch_kernel(ctx, gemm_persistent_kernel<16>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
     else if (wbits == 4) le = launch_kernel(ctx, gemm_persistent_kernel<4>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
     else le = launch_kernel(ctx, gemm_persistent_kernel<8>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, true, amap, wmap, g, ctx->status);
     TB_CUDA(le);
