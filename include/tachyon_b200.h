@@ -621,7 +621,8 @@ TB_API int tb_engine_embed(tb_engine* eng, const char* name, const uint32_t* ids
 
 /* ---- Text to token ids and back (host code; crates/tachyon/src/token/mod.rs, token/chat.rs) ------------------------------------
  * Tokenizer::from_json (mod.rs:97-127) reads a Hugging Face tokenizer.json of Gemma's kind (BPE with byte fallback, spaces
- * as U+2581) or of the Metaspace kind; byte-level BPE is refused (TB_FORMAT, "... is not supported").  Tokenizer::to_bytes /
+ * as U+2581), of the Metaspace kind, or byte-level BPE cut by GPT-2's, cl100k's or o200k's pattern, with an NFC normalizer
+ * or none; anything else is refused (TB_FORMAT, "... is not supported").  Tokenizer::to_bytes /
  * from_bytes (mod.rs:422-455) are the reference's stored form, word for word: a converted model's tokenizer.tok loads as it
  * is.  Tokenizer::encode (mod.rs:272-301) encodes text literally: a special token's text stays text; special tokens enter by
  * id, from the chat template.  Output buffers: *count (or *bytes) is always what the whole result needs; with capacity 0

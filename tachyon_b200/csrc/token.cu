@@ -5,7 +5,8 @@
 // text; special tokens enter by id only, from the chat template (token/chat.rs), so user text cannot forge a turn.
 // Read from a Hugging Face tokenizer.json, or from the reference's stored form (`TACHYTOK`, mod.rs:422-455), which this
 // file reads and writes word for word so that a converted model's tokenizer.tok loads as it is.  Byte-level BPE (GPT-2's
-// family, token/bytes.rs) is refused by name.  Host code only.
+// scheme, token/bytes.rs: every byte a symbol, the text first cut into pieces by GPT-2's pattern, cl100k's or o200k's, matched
+// by hand) and an NFC normalizer (token/unicode.rs) are taken too, the Unicode data generated into unicode_tables.h.  Host code only.
 #include <algorithm>
 #include <cstring>
 #include <queue>
@@ -15,13 +16,14 @@
 
 #include "../../include/tachyon_b200.h"
 #include "internal.h"
+#include "unicode_tables.h"
 
 namespace {
 
 using tb::fail;
 
 constexpr uint32_t NONE = UINT32_MAX;
-constexpr uint32_t META = 1, BYTES = 2, SPLIT = 4, PREPEND = 8, BYTE_LEVEL = 16;  // mod.rs:25-40
+constexpr uint32_t META = 1, BYTES = 2, SPLIT = 4, PREPEND = 8, BYTE_LEVEL = 16, CL100K = 32, NFC = 64, O200K = 128;  // mod.rs:25-40
 constexpr size_t DIRECT = 0x20000;  // characters with an entry of their own in `chars`: the first two planes
 constexpr uint32_t BAR = 0x2581;    // the visible space
 
@@ -160,6 +162,219 @@ uint32_t next_char(const uint8_t* p, const uint8_t* end, size_t& len) {
 
 }  // namespace
 
+namespace {
+
+// ---- byte-level BPE: the byte a vocabulary character stands for, and the three patterns (token/bytes.rs) ------------------------
+bool printable(uint32_t b) { return (b >= '!' && b <= '~') || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF); }
+
+// Itself if printable, else the nth of the other bytes, written U+0100 + n; -1 if the character stands for no byte.
+int byte_of(uint32_t c) {
+    if (c < 256) return printable(c) ? (int)c : -1;
+    if (c > 323) return -1;
+    uint32_t n = c - 256;
+    for (uint32_t b = 0; b < 256; b++)
+        if (!printable(b) && n-- == 0) return (int)b;
+    return -1;
+}
+
+uint32_t unicode_entry(uint32_t c) {
+    size_t lo = 0, hi = sizeof(tb_unicode::RUNS) / sizeof(tb_unicode::RUNS[0]);
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (tb_unicode::RUNS[mid].last < c) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo < sizeof(tb_unicode::RUNS) / sizeof(tb_unicode::RUNS[0]) && tb_unicode::RUNS[lo].first <= c ? tb_unicode::RUNS[lo].entry : 0;
+}
+
+enum Class { LETTER, NUMBER, SPACE, OTHER };
+bool is_letter(uint32_t c) { return unicode_entry(c) & 1u; }
+bool is_number(uint32_t c) { return (unicode_entry(c) & 2u) != 0; }
+bool is_white(uint32_t c) { return (unicode_entry(c) & 4u) != 0; }
+uint32_t kind_of(uint32_t c) { return unicode_entry(c) >> 3; }  // to o200k: 1 upper or title, 2 lower, 3 either (modifier, other, mark), 0 none
+Class class_of(uint32_t c) {
+    const uint32_t e = unicode_entry(c);
+    return (e & 1u) ? LETTER : (e & 2u) ? NUMBER : (e & 4u) ? SPACE : OTHER;
+}
+
+// ---- Unicode Normalization Form C (token/unicode.rs): canonical decomposition, canonical ordering, canonical composition -----
+template <size_t N>
+const tb_unicode::Run* find_first(const tb_unicode::Run (&table)[N], uint32_t key) {  // the entry whose `first` is key, or null
+    size_t lo = 0, hi = N;
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (table[mid].first < key) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo < N && table[lo].first == key ? &table[lo] : nullptr;
+}
+
+uint32_t combining_class(uint32_t c) {
+    constexpr size_t N = sizeof(tb_unicode::COMBINING) / sizeof(tb_unicode::COMBINING[0]);
+    size_t lo = 0, hi = N;
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (tb_unicode::COMBINING[mid].last < c) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo < N && tb_unicode::COMBINING[lo].first <= c ? tb_unicode::COMBINING[lo].entry : 0;
+}
+
+void decompose(uint32_t c, std::vector<uint32_t>& out) {
+    if (c >= 0xAC00 && c <= 0xD7A3) {  // a Hangul syllable: leading consonant, vowel, and maybe a trailing consonant
+        const uint32_t s = c - 0xAC00, t = s % 28;
+        out.push_back(0x1100 + s / 588), out.push_back(0x1161 + (s % 588) / 28);
+        if (t) out.push_back(0x11A7 + t);
+        return;
+    }
+    const tb_unicode::Run* d = c < 0xC0 ? nullptr : find_first(tb_unicode::DECOMPOSE, c);
+    if (!d) return out.push_back(c);
+    decompose(d->last, out);  // {character, first, second or 0}
+    if (d->entry) out.push_back(d->entry);
+}
+
+uint32_t compose_pair(uint32_t a, uint32_t b) {
+    if (a >= 0x1100 && a < 0x1113 && b >= 0x1161 && b < 0x1176) return 0xAC00 + ((a - 0x1100) * 21 + (b - 0x1161)) * 28;
+    if (a >= 0xAC00 && a <= 0xD7A3 && (a - 0xAC00) % 28 == 0 && b > 0x11A7 && b < 0x11C3) return a + (b - 0x11A7);
+    constexpr size_t N = sizeof(tb_unicode::COMPOSE) / sizeof(tb_unicode::COMPOSE[0]);
+    size_t lo = 0, hi = N;  // {first, second, composite}, sorted by (first, second)
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        const tb_unicode::Run& e = tb_unicode::COMPOSE[mid];
+        if (e.first < a || (e.first == a && e.last < b)) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo < N && tb_unicode::COMPOSE[lo].first == a && tb_unicode::COMPOSE[lo].last == b ? tb_unicode::COMPOSE[lo].entry : 0;
+}
+
+// The text in NFC, or nothing written and false when it is in NFC already as far as a quick look tells (nothing from U+0300 on).
+bool nfc(const uint8_t* p, const uint8_t* end, std::string& out) {
+    bool plain = true;
+    for (const uint8_t* q = p; q < end && plain; q++) plain = *q < 0xCC;  // U+0300 is CC 80
+    if (plain) return false;
+    std::vector<uint32_t> cs;
+    for (size_t n; p < end; p += n) decompose(next_char(p, end, n), cs);
+    for (size_t i = 0; i < cs.size();) {  // canonical ordering: each run of marks sorted by class, equal classes keeping their order
+        if (combining_class(cs[i]) == 0) {
+            i++;
+            continue;
+        }
+        size_t j = i;
+        while (j < cs.size() && combining_class(cs[j]) != 0) j++;
+        std::stable_sort(cs.begin() + (long)i, cs.begin() + (long)j, [](uint32_t a, uint32_t b) { return combining_class(a) < combining_class(b); });
+        i = j;
+    }
+    // canonical composition: a character joins the last starter unless a character stands between them whose class is not
+    // lower than its own (the marks between are sorted, so the last one's class decides; a starter joins only when adjacent)
+    std::vector<uint32_t> r;
+    size_t starter = SIZE_MAX;
+    uint32_t last_class = 0;
+    for (uint32_t c : cs) {
+        const uint32_t k = combining_class(c);
+        if (starter != SIZE_MAX) {
+            const bool blocked = r.size() > starter + 1 && last_class >= k;
+            const uint32_t joined = blocked ? 0 : compose_pair(r[starter], c);
+            if (joined) {
+                r[starter] = joined;
+                continue;
+            }
+        }
+        if (k == 0) starter = r.size();
+        last_class = k;
+        r.push_back(c);
+    }
+    out.clear();
+    for (uint32_t c : r) put_utf8(out, c);
+    return true;
+}
+
+// A stretch of text as characters; the matchers below give the characters of the pattern's match at i (at least one).
+struct Chars {
+    std::vector<uint32_t> c;
+    size_t n() const { return c.size(); }
+    template <typename P>
+    size_t run(size_t i, size_t most, P keep) const {
+        size_t k = 0;
+        while (k < most && i + k < c.size() && keep(c[i + k])) k++;
+        return k;
+    }
+    // 's 't 're 've 'm 'll 'd at i, in any case if `fold`
+    size_t contraction(size_t i, bool fold) const {
+        if (i + 1 >= c.size() || c[i] != '\'') return 0;
+        auto low = [&](size_t j) -> uint32_t { return j < c.size() ? (fold && c[j] >= 'A' && c[j] <= 'Z' ? c[j] + 32 : c[j]) : 0; };
+        const uint32_t a = low(i + 1), b = low(i + 2);
+        if (a == 's' || a == 't' || a == 'm' || a == 'd') return 2;
+        if (((a == 'r' || a == 'v') && b == 'e') || (a == 'l' && b == 'l')) return 3;
+        return 0;
+    }
+    // \s+(?!\S)|\s+ at i: the run, less its last character when more text follows and the run is longer than one
+    size_t spaces(size_t i) const {
+        const size_t k = run(i, SIZE_MAX, is_white);
+        return (i + k < c.size() && k > 1) ? k - 1 : k;
+    }
+    size_t gpt2(size_t i) const {
+        if (const size_t k = contraction(i, false)) return k;
+        const size_t skip = c[i] == ' ' ? 1 : 0;
+        if (i + skip < c.size()) {
+            const Class first = class_of(c[i + skip]);
+            if (first != SPACE) return skip + run(i + skip, SIZE_MAX, [&](uint32_t d) { return class_of(d) == first; });
+        }
+        return spaces(i);
+    }
+    // the last alternatives of cl100k and o200k: ` ?[^\s\p{L}\p{N}]+[\r\n]*` (with `slash`, [\r\n/]*) if `symbols`, else
+    // \s*[\r\n]+|\s+(?!\S)|\s+
+    size_t rest(size_t i, bool symbols, bool slash) const {
+        if (symbols) {
+            const size_t skip = c[i] == ' ' ? 1 : 0;
+            size_t k = skip + run(i + skip, SIZE_MAX, [](uint32_t d) { return class_of(d) == OTHER; });
+            return k + run(i + k, SIZE_MAX, [&](uint32_t d) { return d == '\r' || d == '\n' || (slash && d == '/'); });
+        }
+        const size_t k = run(i, SIZE_MAX, is_white);
+        for (size_t j = k; j-- > 0;)
+            if (c[i + j] == '\r' || c[i + j] == '\n') return j + 1;
+        return spaces(i);
+    }
+    bool symbol_start(size_t i) const { return class_of(c[i]) == OTHER || (c[i] == ' ' && i + 1 < c.size() && class_of(c[i + 1]) == OTHER); }
+    size_t cl100k(size_t i) const {
+        if (const size_t k = contraction(i, true)) return k;
+        const uint32_t c0 = c[i];
+        const Class first = class_of(c0);
+        if (first == LETTER) return run(i, SIZE_MAX, is_letter);
+        if (first == NUMBER) return run(i, 3, is_number);
+        if (c0 != '\r' && c0 != '\n' && i + 1 < c.size() && is_letter(c[i + 1])) return 1 + run(i + 1, SIZE_MAX, is_letter);
+        return rest(i, symbol_start(i), false);
+    }
+    // U*W+ (or with `upper_first`, U+W*) at i, U = upper, title, modifier, other letters and marks, W = lower, modifier, other
+    // letters and marks: the longest run of U that W can still follow, then the longest run of W; 0 if it does not match
+    size_t word(size_t i, bool upper_first) const {
+        size_t len = 0, most = 0;
+        while (i + len < c.size() && kind_of(c[i + len]) != 0) len++;
+        while (most < len && kind_of(c[i + most]) != 2) most++;
+        auto end = [&](size_t a) {
+            while (a < len && kind_of(c[i + a]) >= 2) a++;
+            return a;
+        };
+        if (upper_first) return most > 0 ? end(most) : 0;
+        for (size_t a = most + 1; a-- > 0;)
+            if (end(a) > a) return end(a);
+        return 0;
+    }
+    size_t o200k(size_t i) const {
+        const uint32_t c0 = c[i];
+        const bool prefix = c0 != '\r' && c0 != '\n' && !is_letter(c0) && !is_number(c0);
+        for (int upper_first = 0; upper_first < 2; upper_first++)
+            for (int with = prefix ? 1 : 0; with >= 0; with--) {  // each word alternative with its optional first character, then without
+                if (i + (size_t)with >= c.size() && with) continue;
+                const size_t k = word(i + (size_t)with, upper_first != 0);
+                if (k > 0) return (size_t)with + k + contraction(i + (size_t)with + k, true);
+            }
+        if (is_number(c0)) return run(i, 3, is_number);
+        return rest(i, symbol_start(i), true);
+    }
+};
+
+}  // namespace
+
 // The tables are the stored form's sections (mod.rs:47-78), ready to use as read.
 struct tb_tokenizer {
     uint32_t flags = 0, unk = NONE;
@@ -227,6 +442,21 @@ std::vector<uint32_t> chars_of(const std::string& s) {
 
 // Tokenizer::add_token (mod.rs:170-192): the token's decoded text, and its place in the byte and character tables.
 void add_token(tb_tokenizer& t, uint32_t id, const std::string& name) {
+    if ((t.flags & BYTE_LEVEL) && !t.is_special(id)) {
+        // add_byte_token (mod.rs:199-204): a name of byte characters is those bytes; another (an added token's) is its own text
+        std::vector<uint8_t> decoded;
+        bool all = true;
+        for (uint32_t c : chars_of(name)) {
+            const int b = byte_of(c);
+            all = all && b >= 0;
+            decoded.push_back((uint8_t)(b < 0 ? 0 : b));
+        }
+        if (all && decoded.size() == 1) t.bytes[decoded[0]] = id;
+        if (all) t.text.insert(t.text.end(), decoded.begin(), decoded.end());
+        else t.text.insert(t.text.end(), name.begin(), name.end());
+        t.offsets.push_back((uint32_t)t.text.size());
+        return;
+    }
     int byte = -1;
     if (name.size() == 6 && !name.compare(0, 3, "<0x") && name[5] == '>') {
         auto hex = [](char c) { return c >= '0' && c <= '9' ? c - '0' : c >= 'a' && c <= 'f' ? c - 'a' + 10 : c >= 'A' && c <= 'F' ? c - 'A' + 10 : -1; };
@@ -324,19 +554,42 @@ int from_json(const char* json, size_t bytes, tb_tokenizer& t) {
     if (r.bad || doc.kind != Json::OBJ) return fail(tb::FORMAT, "tokenizer.json: not a JSON object");
     const Json* model = doc.get("model");
     if (!model || !model->is("type", "BPE")) return unsupported("a model other than BPE");
-    bool meta = false;
+    bool meta = false, nfc_flag = false;
     const Json* norm = doc.get("normalizer");
     if (norm && norm->kind != Json::NUL) {
         if (norm->is("type", "Replace") && norm->is("content", "\xE2\x96\x81")) meta = true;
-        else if (norm->is("type", "NFC")) return unsupported("an NFC normalizer (byte-level BPE)");
+        else if (norm->is("type", "NFC")) nfc_flag = true;
         else return unsupported("this normalizer");
     }
     uint32_t pre = 0;
     const Json* p = doc.get("pre_tokenizer");
     if (p && p->kind != Json::NUL) {
         const Json* pattern = p->get("pattern");
-        if (p->is("type", "ByteLevel") || p->get("pretokenizers")) return unsupported("byte-level BPE");
-        if (p->is("type", "Split") && meta && pattern && pattern->is("String", " ")) pre = 0;
+        // byte_level (mod.rs:498-521): a byte-level pre-tokenizer with GPT-2's pattern, or a split by one of the three patterns
+        // (its matches kept) followed by a byte-level one without
+        auto level = [&](const Json& q, bool regex) -> uint32_t {
+            if (!q.is("type", "ByteLevel") || !q.flag("use_regex", regex)) return 0;
+            return BYTE_LEVEL | (q.flag("add_prefix_space", true) ? PREPEND : 0);
+        };
+        const Json* seq = p->get("pretokenizers");
+        if (const uint32_t f = level(*p, true)) pre = f;
+        else if (seq && seq->kind == Json::ARR && seq->arr.size() == 2) {
+            const Json &split = seq->arr[0], *pat = split.get("pattern");
+            const Json* regex = pat ? pat->get("Regex") : nullptr;
+            const bool kept = (split.is("behavior", "Removed") && split.flag("invert", true)) || (split.is("behavior", "Isolated") && split.flag("invert", false));
+            static const char* const PATTERNS[3] = {
+                R"('s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+)",
+                R"((?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+)",
+                R"([^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]*[\p{Ll}\p{Lm}\p{Lo}\p{M}]+(?i:'s|'t|'re|'ve|'m|'ll|'d)?|[^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]+[\p{Ll}\p{Lm}\p{Lo}\p{M}]*(?i:'s|'t|'re|'ve|'m|'ll|'d)?|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n/]*|\s*[\r\n]+|\s+(?!\S)|\s+)"};
+            int which = -1;
+            for (int k = 0; k < 3; k++)
+                if (regex && regex->kind == Json::STR && regex->s == PATTERNS[k]) which = k;
+            const uint32_t f = level(seq->arr[1], false);
+            // (Hugging Face gives a prefix space to every piece of such a split, not to the text: refused rather than encoded otherwise.)
+            if (which < 0 || !kept || f == 0 || (f & PREPEND)) return unsupported("this pre-tokenizer");
+            pre = f | (which == 1 ? CL100K : which == 2 ? O200K : 0);
+        } else if (p->is("type", "ByteLevel") || seq) return unsupported("this pre-tokenizer");
+        else if (p->is("type", "Split") && meta && pattern && pattern->is("String", " ")) pre = 0;
         else if (p->is("type", "Metaspace") && p->is("replacement", "\xE2\x96\x81")) {
             pre = META | (p->flag("split", false) ? 0 : SPLIT) | ((p->is("prepend_scheme", "always") || p->is("prepend_scheme", "first")) ? PREPEND : 0);
         } else return unsupported("this pre-tokenizer");
@@ -364,7 +617,7 @@ int from_json(const char* json, size_t bytes, tb_tokenizer& t) {
     const Json* unk = model->get("unk_token");
     std::vector<uint32_t> skip = special;
     skip.insert(skip.end(), plain.begin(), plain.end());
-    TB_TRY(build(t, vocab, merges, special, plain, unk ? unk->str() : nullptr, pre | (meta ? META : 0) | (fallback ? BYTES : 0)));
+    TB_TRY(build(t, vocab, merges, special, plain, unk ? unk->str() : nullptr, pre | (meta ? META : 0) | (fallback ? BYTES : 0) | (nfc_flag ? NFC : 0)));
     // frame (mod.rs:528-549): the special tokens a TemplateProcessing post-processor puts before and after a single text
     const Json* post = doc.get("post_processor");
     const Json* tpl = nullptr;
@@ -439,10 +692,16 @@ void symbols(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, std::v
 
 // Merges the piece's symbols, lowest-ranked pair first and the leftmost among equals (mod.rs:345-383), and appends what is left.
 void merge_all(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, Work& w, uint32_t* out, size_t cap, size_t& count) {
-    symbols(t, p, end, w.ids);
+    if (t.flags & BYTE_LEVEL) {
+        w.ids.clear();
+        for (; p < end; p++) w.ids.push_back(t.bytes[*p]);
+    } else {
+        symbols(t, p, end, w.ids);
+    }
     const uint32_t n = (uint32_t)w.ids.size();
     w.next.resize(n), w.prev.resize(n), w.heap.clear();
     auto rank_of = [&](uint32_t a, uint32_t b, uint32_t& merged) {
+        if (a == NONE || b == NONE) return NONE;
         const size_t at = find_merge(t.merges, a, b);
         if (t.merges[at] == NONE) return NONE;
         merged = t.merges[at + 3];
@@ -482,9 +741,48 @@ bool is_join(const tb_tokenizer& t, uint32_t c) { return std::binary_search(t.jo
 // each piece merged on its own.
 void segment(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, Work& w, uint32_t* out, size_t cap, size_t& count) {
     std::string prefixed;
-    if ((t.flags & PREPEND) && p < end && p[0] != ' ' && !(end - p >= 3 && p[0] == 0xE2 && p[1] == 0x96 && p[2] == 0x81)) {
-        prefixed = "\xE2\x96\x81" + std::string(reinterpret_cast<const char*>(p), (size_t)(end - p));
+    // (A byte-level pre-tokenizer prepends its space unless the text starts with one, as Hugging Face does; U+2581 is no space to it.)
+    if ((t.flags & PREPEND) && p < end && p[0] != ' ' && ((t.flags & BYTE_LEVEL) || !(end - p >= 3 && p[0] == 0xE2 && p[1] == 0x96 && p[2] == 0x81))) {
+        prefixed = ((t.flags & BYTE_LEVEL) ? std::string(" ") : std::string("\xE2\x96\x81")) + std::string(reinterpret_cast<const char*>(p), (size_t)(end - p));
         p = reinterpret_cast<const uint8_t*>(prefixed.data()), end = p + prefixed.size();
+    }
+    if (t.flags & BYTE_LEVEL) {
+        // byte_segment (mod.rs:328-336): each piece its pattern cuts is a token of its own if the model ignores merges for pieces
+        // that are tokens, else merged on its own
+        Chars cs;
+        std::vector<size_t> at;  // where each character starts, and the end
+        for (const uint8_t* q = p; q < end;) {
+            size_t n;
+            cs.c.push_back(next_char(q, end, n));
+            at.push_back((size_t)(q - p));
+            q += n;
+        }
+        at.push_back((size_t)(end - p));
+        for (size_t i = 0; i < cs.n();) {
+            size_t k = (t.flags & O200K) ? cs.o200k(i) : (t.flags & CL100K) ? cs.cl100k(i) : cs.gpt2(i);
+            if (k == 0 || i + k > cs.n()) k = 1;
+            const uint8_t *from = p + at[i], *to = p + at[i + k];
+            uint32_t whole = NONE;
+            if (!t.words.empty()) {
+                const size_t mask = t.words.size() - 1;
+                for (size_t j = slot_of(fnv(from, (size_t)(to - from)), mask); t.words[j] != NONE; j = (j + 1) & mask) {
+                    size_t n;
+                    const uint8_t* text = t.token(t.words[j], n);
+                    if (n == (size_t)(to - from) && !memcmp(text, from, n)) {
+                        whole = t.words[j];
+                        break;
+                    }
+                }
+            }
+            if (whole != NONE) {
+                if (count < cap) out[count] = whole;
+                count++;
+            } else {
+                merge_all(t, from, to, w, out, cap, count);
+            }
+            i += k;
+        }
+        return;
     }
     const uint8_t *start = p, *at = p;
     uint32_t last = BAR;
@@ -504,6 +802,8 @@ void segment(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, Work& 
 // them goes through `segment`.
 void encode(const tb_tokenizer& t, const uint8_t* text, size_t bytes, uint32_t* out, size_t cap, size_t& count) {
     Work w;
+    std::string normal;
+    if ((t.flags & NFC) && nfc(text, text + bytes, normal)) text = reinterpret_cast<const uint8_t*>(normal.data()), bytes = normal.size();
     const uint8_t *end = text + bytes, *from = text, *at = text;
     while (at < end) {
         uint32_t found = NONE;
@@ -599,7 +899,11 @@ int from_bytes(const uint8_t* data, size_t bytes, tb_tokenizer& t) {
     bool room = false;  // the merge table must have a free entry, or a lookup would never end
     for (size_t k = 0; k < t.merges.size(); k += 4) room = room || t.merges[k] == NONE;
     if (!ids || !room) return damaged();
-    if (t.flags & (BYTE_LEVEL | 64u)) return unsupported("byte-level BPE");
+    if (!t.words.empty()) {
+        bool free_entry = false, tokens = true;
+        for (uint32_t id : t.words) free_entry = free_entry || id == NONE, tokens = tokens && ok(id);
+        if ((t.words.size() & (t.words.size() - 1)) != 0 || !free_entry || !tokens) return damaged();
+    }
     return tb::OK;
 }
 
