@@ -361,6 +361,26 @@ def crc32c_combine(crc_a: int, crc_b: int, len_b: int) -> int:
     return int(_lib.load().tb_crc32c_combine(crc_a, crc_b, len_b))
 
 
+def framed(tok: "Tokenizer", texts, capacity: int) -> list[list[int]]:
+    """Encoder::embed's sequences (encoder/text.rs:40-55): the token the post-processor puts first (else <bos> or [CLS]), the
+    text's tokens cut to the capacity, and the token it puts last, if any."""
+    before, after = tok.frame()
+    if before is None:
+        for name in ("<bos>", "[CLS]"):
+            try:
+                before = tok.special(name)
+                break
+            except Error:
+                pass
+        if before is None:
+            raise Error(5, "the tokenizer has none of ['<bos>', '[CLS]']")
+    out = []
+    for t in texts:
+        ids = ([before] + tok.encode(t))[: capacity - (after is not None)]
+        out.append(ids + ([after] if after is not None else []))
+    return out
+
+
 class Tokenizer:
     """token::Tokenizer (crates/tachyon/src/token/mod.rs): text to token ids and back.  Host code, no GPU."""
 
@@ -655,6 +675,12 @@ class Engine:
                                               os.fsencode(host) if host else None))
         self.dims = getattr(self, "dims", {})
         self.dims[name] = cfg.dims
+        self.capacity = getattr(self, "capacity", {})
+        self.capacity[name] = tokens
+
+    def embed_texts(self, name: str, tok: "Tokenizer", texts) -> np.ndarray:
+        """Engine::embed (engine.rs:258-262) from texts: framed and cut as Encoder::embed does (encoder/text.rs:40-55)."""
+        return self.embed(name, framed(tok, texts, self.capacity[name]))
 
     def embed(self, name: str, sequences) -> np.ndarray:
         """tb_engine_embed: embeddings [len(sequences), dims] of lists of token ids by the held encoder `name`."""
@@ -832,7 +858,7 @@ class Encoder:
         self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
         h = C.c_void_p()
         check(self.lib.tb_encoder_open(ctx.handle, C.byref(cfg), tokens, sequences, C.byref(h)))
-        self.handle = h.value
+        self.handle, self.tokens = h.value, tokens
 
     def close(self) -> None:
         if self.handle:
@@ -861,6 +887,10 @@ class Encoder:
         out = np.zeros((len(sequences), self.cfg.dims), np.float32)
         check(self.lib.tb_encoder_embed(self.handle, ids.ctypes.data, lens.ctypes.data, len(sequences), out.ctypes.data))
         return out
+
+    def embed_texts(self, tok: "Tokenizer", texts) -> np.ndarray:
+        """Encoder::embed (encoder/text.rs:40-65): the texts framed and cut to the capacity, then embed."""
+        return self.embed(framed(tok, texts, self.tokens))
 
     def graphs(self) -> int:
         return int(self.lib.tb_encoder_graphs(self.handle))

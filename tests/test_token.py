@@ -231,3 +231,24 @@ def test_the_chat_template_renders_the_reference_conversations():
         tb.ChatTemplate(tb.Tokenizer.from_json(read("toy.json")))
     assert "not Gemma 4's" in str(e.value)
     tok.close()
+
+
+def test_texts_are_framed_for_an_encoder():
+    """Encoder::embed's sequences (encoder/text.rs:40-55): the post-processor's first token (else <bos>), the text cut to the
+    capacity, the post-processor's last token if it has one."""
+    doc = json.loads(read("toy.json"))
+    toy = tb.Tokenizer.from_json(read("toy.json"))
+    ids = toy.encode("hello there")
+    assert tb.framed(toy, ["hello there", ""], 64) == [[toy.special("<bos>")] + ids, [toy.special("<bos>")]]
+    assert tb.framed(toy, ["word " * 50], 8)[0] == ([toy.special("<bos>")] + toy.encode("word " * 50))[:8]
+    doc["post_processor"] = {"type": "TemplateProcessing", "single": [{"SpecialToken": {"id": "<bos>", "type_id": 0}}, {"Sequence": {"id": "A", "type_id": 0}},
+                                                                     {"SpecialToken": {"id": "<eos>", "type_id": 0}}],
+                             "pair": [], "special_tokens": {"<bos>": {"id": "<bos>", "ids": [2], "tokens": ["<bos>"]}, "<eos>": {"id": "<eos>", "ids": [1], "tokens": ["<eos>"]}}}
+    both = tb.Tokenizer.from_json(json.dumps(doc).encode())
+    assert tb.framed(both, ["hello there"], 64) == [[2] + ids + [1]]
+    cut = tb.framed(both, ["word " * 50], 8)[0]
+    assert len(cut) == 8 and cut[0] == 2 and cut[-1] == 1
+    bare = tb.Tokenizer.from_json(read("bytes_cl100k.json"))
+    with pytest.raises(tb.Error):
+        tb.framed(bare, ["x"], 8)
+    toy.close(), both.close(), bare.close()
