@@ -320,6 +320,69 @@ def gemma4_e4b_shape(layers: int = 35, ffn: int = 16384, vocab: int = 262144) ->
                   theta_sliding=1e4, theta_global=1e6, fraction_global=0.25, eps=1e-6, softcap=30.0, attn_scale=1.0)
 
 
+def config_from_json(text: bytes) -> Config:
+    """model::Config::from_json (crates/tachyon/src/model/mod.rs:63-105): a converted model's (Hugging Face's) config.json, the
+    decoder's part under `text_config` when the model is multimodal.  What this build does not run is refused as the
+    reference refuses what it does not: a double-wide MLP, a mixture of experts."""
+    import json
+
+    doc = json.loads(text)
+    c = doc.get("text_config", doc)
+    need = ["hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads", "head_dim", "global_head_dim", "hidden_size_per_layer_input",
+            "vocab_size", "sliding_window", "rms_norm_eps"]
+    for k in need:
+        if not isinstance(c.get(k), (int, float)):
+            raise Error(5, f"config.json: no {k}")
+    heads, kv = int(c["num_attention_heads"]), int(c["num_key_value_heads"])
+    global_kv = int(c.get("num_global_key_value_heads") or kv)
+    for k in (kv, global_kv):
+        if k == 0 or heads % k != 0 or (heads // k) % 2 != 0:
+            raise Error(9, "a key-value head serving fewer than two query heads, or an odd number")
+    if c.get("use_double_wide_mlp") or int(c.get("num_experts") or 0) > 0:
+        raise Error(9, "a double-wide MLP or a mixture of experts")
+    rope = c.get("rope_parameters") or {}
+    types = c.get("layer_types") or []
+    glob = np.array([t == "full_attention" for t in types], np.uint8)
+    cfg = Config(hidden=int(c["hidden_size"]), ffn=int(c["intermediate_size"]), heads=heads, kv_heads=kv, head_dim=int(c["head_dim"]), vocab=int(c["vocab_size"]),
+                 layers=len(types), window=int(c["sliding_window"]), global_=glob.ctypes.data if len(types) else None, global_every=0,
+                 theta_sliding=float((rope.get("sliding_attention") or {}).get("rope_theta", 1e4)), theta_global=float((rope.get("full_attention") or {}).get("rope_theta", 1e6)),
+                 fraction_global=float((rope.get("full_attention") or {}).get("partial_rotary_factor", 1.0)), eps=float(c["rms_norm_eps"]),
+                 softcap=float(c.get("final_logit_softcapping") or 0.0), attn_scale=1.0, shared=int(c.get("num_kv_shared_layers") or 0),
+                 global_head_dim=int(c["global_head_dim"]), global_kv_heads=global_kv, per_layer=int(c["hidden_size_per_layer_input"]))
+    cfg._global = glob  # the structure points into it
+    return cfg
+
+
+def encoder_config_from_json(text: bytes, mean_pool: bool = False, dims: int = 0) -> EncoderConfig:
+    """encoder::Config::from_json (crates/tachyon/src/encoder/mod.rs:61-117): a ModernBERT's config.json; GELU or SiLU gates, no
+    attention biases."""
+    import json
+
+    c = json.loads(text)
+    if c.get("model_type") != "modernbert":
+        raise Error(9, "an encoder other than ModernBERT")
+    act = c.get("hidden_activation")
+    if act not in ("gelu", "silu") or c.get("attention_bias") is True:
+        raise Error(9, "a ModernBERT with another activation or with biases")
+    hidden, heads, inter, vocab, layers = (int(c.get(k) or 0) for k in ("hidden_size", "num_attention_heads", "intermediate_size", "vocab_size", "num_hidden_layers"))
+    if not (heads > 0 and hidden % heads == 0 and (hidden // heads) % 2 == 0 and inter * vocab * layers > 0):
+        raise Error(5, "config.json: an inconsistent ModernBERT shape")
+    every = max(int(c.get("global_attn_every_n_layers") or 3), 1)
+    types = c.get("layer_types")
+    glob = np.array([t == "full_attention" for t in types] if types else [i % every == 0 for i in range(layers)], np.uint8)
+    rope = c.get("rope_parameters") or {}
+
+    def theta(kind, legacy, default):
+        v = (rope.get(kind) or {}).get("rope_theta")
+        return float(v if v is not None else c.get(legacy, default))
+
+    cfg = EncoderConfig(hidden=hidden, heads=heads, inter=inter, vocab=vocab, layers=len(glob), window=int(c.get("local_attention", 128)) // 2, global_=glob.ctypes.data,
+                        global_every=0, theta_global=theta("full_attention", "global_rope_theta", 160000.0), theta_local=theta("sliding_attention", "local_rope_theta", 10000.0),
+                        eps=float(c.get("norm_eps", 1e-5)), gated=2 if act == "silu" else 1, mean_pool=int(mean_pool), dims=dims or hidden)
+    cfg._global = glob
+    return cfg
+
+
 class Wpk:
     """wpk::Wpk (crates/tachyon/src/wpk/mod.rs): an open weights.wpk, its table checked; no GPU involved."""
 
@@ -604,6 +667,35 @@ class Engine:
         check(self.lib.tb_engine_load(self.handle, name.encode(), C.byref(cfg), C.byref(load), os.fsencode(weights), os.fsencode(host) if host else None))
         self.loaded[name] = (cfg, st)
 
+    def load_dir(self, name: str, directory: str, **how):
+        """Engine::load of a converted model's directory (engine.rs:203-232): config.json tells a decoder from an encoder; weights.wpk,
+        host.wpk if there is one, tokenizer.tok.  A decoder comes in the reference's converted format (four-bit weights, the
+        per-layer table in pinned host memory).  Returns the model's tokenizer, or None if the directory has none; a decoder's
+        chat template is kept for Engine.chat."""
+        import json
+
+        def read(file):
+            path = os.path.join(directory, file)
+            return open(path, "rb").read() if os.path.exists(path) else None
+
+        config = read("config.json")
+        if config is None:
+            raise Error(11, f"{directory}: no config.json")
+        stored = read("tokenizer.tok")
+        tok = Tokenizer.from_bytes(stored) if stored is not None else None
+        weights, host = os.path.join(directory, "weights.wpk"), os.path.join(directory, "host.wpk")
+        host = host if os.path.exists(host) else None
+        if json.loads(config).get("model_type") == "modernbert":
+            self.load_encoder(name, encoder_config_from_json(config, mean_pool=how.pop("mean_pool", False), dims=how.pop("dims", 0)), weights, host, **how)
+            return tok
+        cfg = config_from_json(config)
+        self.load(name, cfg, weights, host, weight_bits=how.pop("weight_bits", 4), host_table=how.pop("host_table", host is not None and cfg.per_layer > 0), **how)
+        if tok is not None:
+            template = read("chat_template.jinja")
+            self.templates = getattr(self, "templates", {})
+            self.templates[name] = ChatTemplate(tok, template.decode("utf-8") if template is not None else None)
+        return tok
+
     def unload(self, name: str) -> bool:
         was = C.c_int(0)
         check(self.lib.tb_engine_unload(self.handle, name.encode(), C.byref(was)))
@@ -641,7 +733,7 @@ class Engine:
         """Engine::chat and TokenStream::next_text (engine.rs:326-337, 515-536): the conversation through the chat template, every
         prompt token but the last through prefill and the last through a step, then the answer's text piece by piece, whole
         characters only, until the model ends its turn, `max_tokens` are out or the context is full."""
-        chat = template or ChatTemplate(tok)
+        chat = template or getattr(self, "templates", {}).get(name) or ChatTemplate(tok)
         prompt = chat.encode(messages, think=think)
         context = self.loaded[name][1].context
         if len(prompt) >= context:

@@ -379,3 +379,43 @@ def test_a_conversation_goes_in_as_text_and_the_answer_comes_out_as_text(ctx, tm
     with pytest.raises(tb.Error):
         list(e.chat("m", tok, [("user", "word " * 80)]))
     e.close(), tok.close()
+
+
+def test_a_converted_models_directory_loads_as_it_is(ctx, model, tmp_path):
+    """Engine::load of a directory (engine.rs:203-232): config.json (Hugging Face's, model/mod.rs:63-105), weights.wpk, host.wpk,
+    tokenizer.tok and chat_template.jinja as model::convert leaves them; then a conversation from text to text."""
+    import json
+    import os
+    import shutil
+
+    cfg, weights, host = model
+    d = tmp_path / "gemma"
+    d.mkdir()
+    shutil.copy(weights, d / "weights.wpk"), shutil.copy(host, d / "host.wpk")
+    types = ["full_attention" if l % cfg.global_every == 0 else "sliding_attention" for l in range(cfg.layers)]
+    text = {"hidden_size": cfg.hidden, "intermediate_size": cfg.ffn, "num_attention_heads": cfg.heads, "num_key_value_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+            "global_head_dim": cfg.global_head_dim or cfg.head_dim, "hidden_size_per_layer_input": cfg.per_layer, "vocab_size": cfg.vocab, "sliding_window": cfg.window,
+            "rms_norm_eps": cfg.eps, "final_logit_softcapping": cfg.softcap, "layer_types": types,
+            "rope_parameters": {"sliding_attention": {"rope_theta": cfg.theta_sliding}, "full_attention": {"rope_theta": cfg.theta_global, "partial_rotary_factor": cfg.fraction_global}}}
+    (d / "config.json").write_text(json.dumps({"model_type": "gemma4", "text_config": text}))
+    golden = os.path.join(os.path.dirname(__file__), "golden", "token")
+    chat_tok = tb.Tokenizer.from_json(open(os.path.join(golden, "chat.json"), "rb").read())
+    (d / "tokenizer.tok").write_bytes(chat_tok.to_bytes())
+    (d / "chat_template.jinja").write_text("{%- if add_generation_prompt -%}{{ '<|turn>model\\n' }}{%- endif -%}")
+    read = tb.config_from_json((d / "config.json").read_bytes())
+    for field, _ in tb.Config._fields_:
+        if field not in ("global_", "global_every", "global_head_dim", "global_kv_heads", "attn_scale"):
+            assert getattr(read, field) == pytest.approx(getattr(cfg, field)), field
+    assert list(read._global) == [int(t == "full_attention") for t in types]
+    e = tb.Engine(ctx)
+    tok = e.load_dir("gemma", str(d), context=64, chunk=8, keep_alive_ms=tb.FOR_GOOD)
+    assert tok.to_bytes() == chat_tok.to_bytes() and e.tier("gemma") == tb.TIER_VRAM
+    # the same model loaded piece by piece answers the same tokens
+    e.load("by_hand", cfg, weights, host, keep_alive_ms=tb.FOR_GOOD, **SETTINGS)
+    assert answer(e, "gemma") == answer(e, "by_hand")
+    # the tokenizer's ids must fit the model's vocabulary for a chat: this toy pair does not (4005 tokens, 2048 rows), so the
+    # conversation is only encoded here; tests above run one end to end on a model that is wide enough
+    assert len(e.templates["gemma"].encode([("user", "hi")])) > 4
+    with pytest.raises(tb.Error):
+        e.load_dir("nothing", str(tmp_path / "absent"))
+    e.close(), chat_tok.close(), tok.close()
