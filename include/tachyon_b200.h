@@ -626,7 +626,8 @@ TB_API int tb_engine_embed(tb_engine* eng, const char* name, const uint32_t* ids
  * from_bytes (mod.rs:422-455) are the reference's stored form, word for word: a converted model's tokenizer.tok loads as it
  * is.  Tokenizer::encode (mod.rs:272-301) encodes text literally: a special token's text stays text; special tokens enter by
  * id, from the chat template.  Output buffers: *count (or *bytes) is always what the whole result needs; with capacity 0
- * nothing is written and the call only counts; a capacity that is too small is TB_OUT_OF_RANGE. */
+ * nothing is written and the call only counts; a capacity that is too small is TB_OUT_OF_RANGE.  A tokenizer is not changed
+ * by any call after it is made: threads may encode with one at the same time; a detokenizer belongs to one stream of tokens. */
 typedef struct tb_tokenizer tb_tokenizer;
 typedef struct tb_detokenizer tb_detokenizer;
 TB_API int tb_tokenizer_from_json(const void* json, size_t bytes, tb_tokenizer** out);
