@@ -665,7 +665,7 @@ int from_json(const char* json, size_t bytes, tb_tokenizer& t) {
 
 // ---- encoding -------------------------------------------------------------------------------------------------------------------
 struct Work {
-    std::vector<uint32_t> ids, next, prev;
+    std::vector<uint32_t> ids, next, prev, rank, merged;  // rank, merged: of the symbol's merge with the one after it, NONE if none
     std::vector<uint64_t> heap;  // (rank << 32 | position) of merges that were possible when pushed; checked again when taken
 };
 
@@ -680,12 +680,16 @@ void symbols(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, std::v
             ids.push_back(id);
             continue;
         }
-        std::string utf8;
-        put_utf8(utf8, c);
+        uint8_t utf8[4];  // the character's own bytes (a byte that started no character came out as U+FFFD and is spelled so)
+        size_t len = 0;
+        if (c < 0x80) utf8[len++] = (uint8_t)c;
+        else if (c < 0x800) utf8[len++] = (uint8_t)(0xC0 | c >> 6), utf8[len++] = (uint8_t)(0x80 | (c & 63));
+        else if (c < 0x10000) utf8[len++] = (uint8_t)(0xE0 | c >> 12), utf8[len++] = (uint8_t)(0x80 | (c >> 6 & 63)), utf8[len++] = (uint8_t)(0x80 | (c & 63));
+        else utf8[len++] = (uint8_t)(0xF0 | c >> 18), utf8[len++] = (uint8_t)(0x80 | (c >> 12 & 63)), utf8[len++] = (uint8_t)(0x80 | (c >> 6 & 63)), utf8[len++] = (uint8_t)(0x80 | (c & 63));
         bool all = (t.flags & BYTES) != 0;
-        for (char b : utf8) all = all && t.bytes[(uint8_t)b] != NONE;
+        for (size_t k = 0; k < len; k++) all = all && t.bytes[utf8[k]] != NONE;
         if (all)
-            for (char b : utf8) ids.push_back(t.bytes[(uint8_t)b]);
+            for (size_t k = 0; k < len; k++) ids.push_back(t.bytes[utf8[k]]);
         else if (t.unk != NONE && (ids.empty() || ids.back() != t.unk)) ids.push_back(t.unk);
     }
 }
@@ -699,19 +703,25 @@ void merge_all(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, Work
         symbols(t, p, end, w.ids);
     }
     const uint32_t n = (uint32_t)w.ids.size();
-    w.next.resize(n), w.prev.resize(n), w.heap.clear();
-    auto rank_of = [&](uint32_t a, uint32_t b, uint32_t& merged) {
-        if (a == NONE || b == NONE) return NONE;
-        const size_t at = find_merge(t.merges, a, b);
-        if (t.merges[at] == NONE) return NONE;
-        merged = t.merges[at + 3];
-        return t.merges[at + 2];
-    };
+    if (n == 1) {  // most pieces of a text with many spaces
+        if (w.ids[0] != NONE) {
+            if (count < cap) out[count] = w.ids[0];
+            count++;
+        }
+        return;
+    }
+    w.next.resize(n), w.prev.resize(n), w.rank.assign(n, NONE), w.merged.resize(n), w.heap.clear();
+    // offer(i): what symbol i and the one after it merge into, kept beside the symbol and put on the heap; an entry taken from
+    // the heap counts only while it is still what is kept (a symbol whose pair changed was offered again since)
     auto offer = [&](uint32_t i) {
-        if (i >= n || w.next[i] >= n) return;
-        uint32_t merged;
-        const uint32_t rank = rank_of(w.ids[i], w.ids[w.next[i]], merged);
-        if (rank != NONE) w.heap.push_back((uint64_t)rank << 32 | i), std::push_heap(w.heap.begin(), w.heap.end(), std::greater<uint64_t>());
+        if (i >= n) return;
+        w.rank[i] = NONE;
+        const uint32_t j = w.next[i];
+        if (j >= n || w.ids[i] == NONE || w.ids[j] == NONE) return;
+        const size_t at = find_merge(t.merges, w.ids[i], w.ids[j]);
+        if (t.merges[at] == NONE) return;
+        w.rank[i] = t.merges[at + 2], w.merged[i] = t.merges[at + 3];
+        w.heap.push_back((uint64_t)w.rank[i] << 32 | i), std::push_heap(w.heap.begin(), w.heap.end(), std::greater<uint64_t>());
     };
     for (uint32_t i = 0; i < n; i++) w.next[i] = i + 1, w.prev[i] = i - 1;  // prev of the first wraps to NONE
     for (uint32_t i = 0; i + 1 < n; i++) offer(i);
@@ -719,11 +729,10 @@ void merge_all(const tb_tokenizer& t, const uint8_t* p, const uint8_t* end, Work
         std::pop_heap(w.heap.begin(), w.heap.end(), std::greater<uint64_t>());
         const uint64_t top = w.heap.back();
         w.heap.pop_back();
-        const uint32_t i = (uint32_t)top, j = w.ids[i] == NONE ? n : w.next[i];
-        if (j >= n) continue;
-        uint32_t merged;
-        if (rank_of(w.ids[i], w.ids[j], merged) != (uint32_t)(top >> 32)) continue;  // what stood here then is gone
-        w.ids[i] = merged, w.ids[j] = NONE, w.next[i] = w.next[j];
+        const uint32_t i = (uint32_t)top;
+        if (w.rank[i] != (uint32_t)(top >> 32)) continue;  // what stood here then is gone
+        const uint32_t j = w.next[i];
+        w.ids[i] = w.merged[i], w.ids[j] = NONE, w.rank[j] = NONE, w.next[i] = w.next[j];
         if (w.next[i] < n) w.prev[w.next[i]] = i;
         offer(w.prev[i]), offer(i);
     }
