@@ -9,7 +9,6 @@
 // by hand) and an NFC normalizer (token/unicode.rs) are taken too, the Unicode data generated into unicode_tables.h.  Host code only.
 #include <algorithm>
 #include <cstring>
-#include <queue>
 #include <string>
 #include <utility>
 #include <vector>

@@ -60,6 +60,7 @@ bool has_crc_instruction() {
     static const bool has = [] {
         uint32_t a = 1, b = 0, c = 0, d = 0;
         asm volatile("cpuid" : "+a"(a), "=b"(b), "+c"(c), "=d"(d));
+        (void)b, (void)d;
         return (c >> 20 & 1u) != 0;
     }();
     return has;
