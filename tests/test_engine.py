@@ -419,3 +419,23 @@ def test_a_converted_models_directory_loads_as_it_is(ctx, model, tmp_path):
     with pytest.raises(tb.Error):
         e.load_dir("nothing", str(tmp_path / "absent"))
     e.close(), chat_tok.close(), tok.close()
+
+
+def test_texts_go_through_a_held_encoder(ctx, tmp_path):
+    """Engine::embed from texts (engine.rs:258-262, encoder/text.rs:40-65): framed by the tokenizer's first token, cut to the
+    capacity, embedded by the held encoder: the vectors of the framed ids, of unit length."""
+    import os
+
+    golden = os.path.join(os.path.dirname(__file__), "golden", "token")
+    tok = tb.Tokenizer.from_json(open(os.path.join(golden, "toy.json"), "rb").read())
+    ecfg, glob, ew, eh = encoder_files(tmp_path, "q8e", vocab=4096)
+    e = tb.Engine(ctx)
+    e.load_encoder("enc", ecfg, ew, eh, tokens=256, sequences=8, keep_alive_ms=tb.FOR_GOOD)
+    texts = ["hello there", "", "Πιο επί ανεπιθύμητη πάντως γεγονός 😀", "word " * 400]
+    got = e.embed_texts("enc", tok, texts)
+    framed = tb.framed(tok, texts, 256)
+    assert [len(f) for f in framed][:2] == [1 + len(tok.encode("hello there")), 1] and len(framed[3]) == 256
+    assert np.array_equal(got, e.embed("enc", framed))
+    assert np.allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-3)
+    e.close(), tok.close()
+    del glob
